@@ -1,0 +1,26 @@
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def golden():
+    """Fixtures produced by the reference's own Python modules (tests/golden/make_golden.py)."""
+    return np.load(ROOT / "tests" / "golden" / "golden.npz")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import tq_oracle
+    tq_oracle.build()
+    return tq_oracle
