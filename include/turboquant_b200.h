@@ -1,0 +1,153 @@
+/*
+ * turboquant_b200 — C ABI of the B200 (sm_100a) TurboQuant KV-cache hot paths.
+ *
+ * Every entry point takes plain device/host pointers, sizes and a CUDA stream (passed as
+ * void*, i.e. a cudaStream_t), returns an int status (0 = TQ_OK), launches asynchronously on
+ * that stream, never synchronises and — unless its comment says otherwise — never allocates.
+ * On a non-zero return tq_last_error() gives a message for the calling thread.
+ *
+ * Each declaration names the reference interface it stands in for (path:line within the
+ * RRoundTable/turboquant tree).
+ */
+#ifndef TURBOQUANT_B200_H
+#define TURBOQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ_ABI_VERSION 1
+
+/* status codes */
+enum {
+    TQ_OK = 0,
+    TQ_ERR_INVALID = 1,     /* bad argument (null pointer, shape, alignment) */
+    TQ_ERR_UNSUPPORTED = 2, /* valid but not implemented for this geometry */
+    TQ_ERR_CUDA = 3,        /* a CUDA runtime call or launch failed */
+    TQ_ERR_WORKSPACE = 4    /* caller-provided workspace too small */
+};
+
+/* element types of caller tensors */
+enum { TQ_F32 = 0, TQ_F16 = 1, TQ_BF16 = 2 };
+/* integer types of index tensors */
+enum { TQ_I32 = 0, TQ_I64 = 1 };
+/* nibble order of flat packed codes */
+enum {
+    TQ_PACK_LOW_FIRST = 0, /* TurboQuantMSE._pack_bits: value i at bit offset i*bits (quantizer.py:17-39) */
+    TQ_PACK_CACHE = 1      /* paged cache / tile order: even dim in the high nibble (tile.py:37-41) */
+};
+/* flags of tq_write_kv_cache */
+enum {
+    TQ_WRITE_DEFAULT = 0,
+    TQ_WRITE_ZERO_PAD = 1 /* also store zeros to the pad bytes after the norms (the reference leaves them alone) */
+};
+
+int tq_abi_version(void);
+const char* tq_last_error(void);
+
+/* Lloyd-Max centroids (2^bits) and decision boundaries (2^bits - 1) for a rotated unit vector
+ * of dimension dim, rounded to fp32 the way the reference builds its tensors.  Host only.
+ * Replaces: Codebook.__init__ (turboquant/codebook.py:72-90). */
+int tq_codebook(int dim, int bits, float* centroids, float* boundaries);
+
+/* ---------------------------------------------------------------------------------------
+ * Cache write.  Quantizes num_tokens x num_kv_heads K rows and V rows (seeded signs -> FWHT ->
+ * L2 norm -> 4-bit Lloyd-Max code -> nibble pack) and scatters them into the paged cache
+ *   kv_cache : uint8 [2][num_blocks][block_size][num_kv_heads][slot_bytes]
+ * at slot_mapping[t] = block*block_size + entry; a negative slot skips the token.  Per slot:
+ * bytes [0, pd/2) codes (even dim high nibble), then the fp16 norm once per 64 dims, pad
+ * untouched.  key/value: [num_tokens][num_kv_heads][head_dim] of in_dtype with
+ * k_token_stride / v_token_stride elements between tokens (heads contiguous).  One launch
+ * covers K and V.  Codes and norms are bit-identical to TurboQuantMSE.quantize on the CPU.
+ * Replaces: torch.ops.turboquant_write.quantize_write_kv_cache
+ *   (csrc/src/quantize_write_binding.cu:207-269, kernel csrc/include/turboquant/quantize_write_kernel.cuh:332-431),
+ *   called from TurboQuantFusedImpl._write_to_cache (turboquant/vllm_backend_fused.py:293-305). */
+int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads,
+                      int slot_bytes, const void* key, const void* value, int in_dtype,
+                      int64_t num_tokens, int64_t k_token_stride, int64_t v_token_stride,
+                      const float* signs, const void* slot_mapping, int slot_dtype, int head_dim,
+                      int flags, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Flat quantizer API (any leading shape flattened to n rows of dim elements, dim <= 256,
+ * padded to the next power of two with zeros).  bits in 1..4.
+ * Replaces: TurboQuantMSE.quantize / .dequantize (turboquant/quantizer.py:77-106). */
+int tq_quantize_flat(const void* x, int x_dtype, int64_t n, int dim, const float* signs, int bits,
+                     int pack_order, uint8_t* packed, float* norms, void* stream);
+int tq_dequantize_flat(const uint8_t* packed, const float* norms, int64_t n, int dim,
+                       const float* signs, int bits, int pack_order, float* out, void* stream);
+
+/* Normalized fast Walsh-Hadamard transform of n rows of padded_dim (power of two <= 256)
+ * fp32 elements: out = FWHT(pre_signs * pad(x)) * post_signs, either sign vector may be NULL.
+ * in_dim <= padded_dim elements are read per row, out_dim <= padded_dim written.
+ * Replaces: fwht, RandomHadamardRotation.rotate / inverse_rotate (turboquant/hadamard.py:21-78). */
+int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
+            const float* pre_signs, const float* post_signs, float* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Paged decode attention over the quantized cache: one query token per sequence,
+ *   out[b, hq, :] = softmax(q[b, hq] . K^[b]^T * sm_scale) V^[b]
+ * evaluated in the rotated domain (Q is rotated once, the output is rotated back after the
+ * split-KV merge).  The KV range of every sequence is cut into page-aligned pieces that are
+ * balanced over num_ctas thread blocks on the device (no host planning, no host sync); the
+ * pieces' normalized partial outputs and base-2 log-sum-exps go to the workspace and a second
+ * kernel merges them, applies the inverse rotation and stores out.
+ *
+ *   q            [batch][num_q_heads][head_dim]            q_dtype (f16 | bf16 | f32)
+ *   kv_cache     uint8 [2][num_blocks][block_size][num_kv_heads][slot_bytes]
+ *   page_indices int32; sequence b's pages are page_indices[page_indptr[b] + i];
+ *                page_indptr == NULL means a dense block table with row stride max_pages
+ *   seq_lens     int32 [batch] (device)
+ *   out          [batch][num_q_heads][head_dim]            out_dtype
+ *   out_lse      optional fp32 [batch][num_q_heads], natural-log LSE of the scaled scores
+ *   workspace    at least tq_decode_workspace_bytes(...) bytes, 256-byte aligned
+ *   num_ctas     thread blocks to balance over; 0 = two per SM of the current device
+ *
+ * Supported geometry: head_dim 128, block_size 16, slot_bytes 80, num_q_heads/num_kv_heads <= 8,
+ * num_kv_heads in {1, 2, 4, 8}.
+ * Replaces: torch.ops.turboquant_v5.decode_v5_from_cache_paged_splitkv_ws and
+ *   decode_v5_from_cache_ws (csrc/src/decode_v5_tc_binding.cu:754-874, 440-551), kernels
+ *   csrc/include/flashinfer_decode_turboquant_v5_tc.cuh:112-795 and
+ *   csrc/include/flashinfer_decode_turboquant_combine.cuh:18-79; the split planning replaces
+ *   TurboQuantFusedImpl._choose_num_splits/_get_v5_ws (turboquant/vllm_backend_fused.py:129-215). */
+size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                                 int num_ctas);
+int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
+                    int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,
+                    int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
+                    int max_pages, const int32_t* seq_lens, const float* signs, float sm_scale,
+                    void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                    float* out_lse, int num_ctas, void* stream);
+
+/* As tq_decode_paged, but stops before the inverse rotation: writes the merged, normalized,
+ * still-rotated output (fp32 [batch][num_q_heads][head_dim]) and its base-2 LSE, restricted to
+ * tokens [kv_begin, kv_end) of every sequence (kv_end < 0: to the end).  This is the per-GPU
+ * half of a KV-axis split across GPUs; the halves are exchanged and finished with
+ * tq_merge_rotated.  No reference counterpart (the reference has no multi-GPU path); it
+ * extends the partial/LSE contract of combine.cuh:18-79. */
+int tq_decode_paged_partial(const void* q, int q_dtype, int batch, int num_q_heads,
+                            int num_kv_heads, int head_dim, const void* kv_cache,
+                            int64_t num_blocks, int block_size, int slot_bytes,
+                            const int32_t* page_indices, const int32_t* page_indptr, int max_pages,
+                            const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
+                            const float* signs, float sm_scale, void* workspace,
+                            size_t workspace_bytes, float* out_rot, float* out_lse2, int num_ctas,
+                            void* stream);
+
+/* Log-sum-exp merge of num_parts rotated partial outputs, then inverse rotation:
+ *   partial_o    fp32 [num_parts][rows][head_dim]   (normalized, rotated domain)
+ *   partial_lse2 fp32 [num_parts][rows]             (base-2 LSE; -inf marks an empty part)
+ *   out          [rows][head_dim] out_dtype; out_lse optional natural-log LSE [rows]
+ * Replaces: SplitKVCombineKernel (csrc/include/flashinfer_decode_turboquant_combine.cuh:18-79)
+ * plus the inverse rotation at flashinfer_decode_turboquant_v5_tc.cuh:709-765. */
+int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_parts,
+                     int64_t rows, int head_dim, const float* signs, void* out, int out_dtype,
+                     float* out_lse, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOQUANT_B200_H */

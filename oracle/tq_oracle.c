@@ -116,12 +116,14 @@ static float row_norm(const float* x, int d) {
     return sqrtf(s);
 }
 
-/* torch.bucketize(v, boundaries) with right=False: number of boundaries strictly below v. */
+/* torch.bucketize(v, boundaries) with right=False: number of boundaries strictly below v.
+ * The comparison is written as torch's lower bound writes it, !(b >= v), so that a NaN lands
+ * in the last bucket as it does there. */
 static int bucketize(float v, const float* b, int nb) {
-    int lo = 0, hi = nb; /* lower_bound */
+    int lo = 0, hi = nb;
     while (lo < hi) {
         int mid = lo + ((hi - lo) >> 1);
-        if (b[mid] < v) lo = mid + 1; else hi = mid;
+        if (!(b[mid] >= v)) lo = mid + 1; else hi = mid;
     }
     return lo;
 }

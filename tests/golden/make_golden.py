@@ -116,6 +116,10 @@ def main():
     rows[518] = 1.0                                              # constant vector
     rows[519] = torch.arange(128, dtype=torch.float32) - 63.5
     rows[520:640] *= torch.logspace(-6, 6, 120).unsqueeze(1)     # wide dynamic range
+    rows[640, 3] = float("inf")                                  # inf element -> NaN spreads
+    rows[641, 5] = float("nan")
+    rows[642] = 1e30 * rows[642]                                 # sum of squares overflows
+    rows[643] = 1e-30 * rows[643]                                # squares underflow to zero
     fx["q_rows"] = rows.numpy()
     tq = TurboQuantMSE(128, 4, CPU, seed=42)
     packed, norms = tq.quantize(rows)

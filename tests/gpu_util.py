@@ -1,0 +1,49 @@
+"""Helpers shared by the GPU parity tests: build caches with the oracle, run the CUDA path."""
+import math
+
+import numpy as np
+import torch
+
+from turboquant_b200 import _cabi, synthetic
+
+DEV = "cuda"
+
+
+def signs_dev():
+    return synthetic.make_signs(128, 42).to(DEV)
+
+
+def oracle_cache(oracle, case, signs_np):
+    H = case.k.shape[1]
+    cache = np.zeros((2, case.num_blocks, 16, H, 80), np.uint8)
+    oracle.write_kv_cache(cache, case.k.float().numpy(), case.v.float().numpy(), signs_np,
+                          case.slot_mapping.numpy(), 128)
+    return cache
+
+
+def run_decode(q, cache_dev, block_table, seq_lens, sm_scale=None, out_dtype=None, num_ctas=0,
+               page_indptr=None, want_lse=False):
+    B, Hq, D = q.shape
+    H = cache_dev.shape[3]
+    sm_scale = 1.0 / math.sqrt(D) if sm_scale is None else sm_scale
+    ws = torch.empty(_cabi.decode_workspace_bytes(B, Hq, H, D, num_ctas), dtype=torch.uint8, device=DEV)
+    out = torch.empty(B, Hq, D, dtype=out_dtype or q.dtype, device=DEV)
+    lse = torch.empty(B, Hq, dtype=torch.float32, device=DEV) if want_lse else None
+    _cabi.decode_paged(q, cache_dev, block_table, seq_lens, signs_dev(), sm_scale, ws, out,
+                       page_indptr=page_indptr, out_lse=lse, num_ctas=num_ctas,
+                       max_pages=block_table.shape[-1] if block_table.dim() == 2 else 1)
+    torch.cuda.synchronize()
+    status = ws[:4].view(torch.int32).item()
+    assert status == 0, f"decode kernel status {status}"
+    return (out, lse) if want_lse else out
+
+
+def assert_attention_close(got, want, what=""):
+    """Parity bar for attention outputs: max-abs 2e-3 and relative (Frobenius) 1e-2."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    max_abs = np.abs(got - want).max()
+    rel = np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)
+    assert max_abs <= 2e-3, f"{what}: max-abs {max_abs:.3e} > 2e-3 (rel {rel:.3e})"
+    assert rel <= 1e-2, f"{what}: relative {rel:.3e} > 1e-2 (max-abs {max_abs:.3e})"
+    return max_abs, rel

@@ -1,0 +1,179 @@
+"""Paged decode-attention parity on the GPU, through the C ABI: against the fixtures made by
+the reference's dequant-attention path, against the CPU oracle, and through size-independent
+properties (split invariance, partial + merge == full) at the benchmark's full size."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from turboquant_b200 import _cabi, synthetic
+from tests.gpu_util import DEV, assert_attention_close, oracle_cache, run_decode, signs_dev
+
+pytestmark = pytest.mark.gpu
+SCALE = 1.0 / math.sqrt(128)
+
+
+def test_golden_ragged_batch(golden):
+    cache = torch.from_numpy(golden["att_cache"]).to(DEV)
+    q = torch.from_numpy(golden["att_q"]).to(DEV)
+    out, lse = run_decode(q, cache, torch.from_numpy(golden["att_block_table"]).to(DEV),
+                          torch.from_numpy(golden["att_seq_lens"]).to(DEV), want_lse=True)
+    assert_attention_close(out.float().cpu().numpy(), golden["att_out"], "golden ragged batch")
+    np.testing.assert_allclose(lse.cpu().numpy(), golden["att_lse"], atol=2e-3)
+
+
+def test_config0_vs_reference_output(golden, oracle):
+    c0 = synthetic.decode_case(seed=0, seq_lens=[1024], dtype=torch.float16, permute_pages=False)
+    cache = oracle_cache(oracle, c0, golden["signs_seed42_d128"])
+    out, lse = run_decode(c0.q.to(DEV), torch.from_numpy(cache).to(DEV), c0.block_table.to(DEV),
+                          c0.seq_lens.to(DEV), want_lse=True)
+    assert_attention_close(out.float().cpu().numpy(), golden["cfg0_out"], "config 0")
+    np.testing.assert_allclose(lse.cpu().numpy(), golden["cfg0_lse"], atol=2e-3)
+
+
+def test_write_then_decode_end_to_end(golden):
+    """Cache produced by the CUDA write kernel, decoded by the CUDA decode kernel (config 0)."""
+    c0 = synthetic.decode_case(seed=0, seq_lens=[1024], dtype=torch.float16, permute_pages=False)
+    cache = torch.zeros((2, c0.num_blocks, 16, 8, 80), dtype=torch.uint8, device=DEV)
+    _cabi.write_kv_cache(cache, c0.k.to(DEV), c0.v.to(DEV), signs_dev(), c0.slot_mapping.to(DEV), 128)
+    out = run_decode(c0.q.to(DEV), cache, c0.block_table.to(DEV), c0.seq_lens.to(DEV))
+    assert_attention_close(out.float().cpu().numpy(), golden["cfg0_out"], "write+decode config 0")
+
+
+@pytest.mark.parametrize("q_dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float32),
+                                               (torch.float32, torch.float16)])
+def test_mixed_lengths_vs_oracle(oracle, golden, q_dtype, out_dtype):
+    lens = [1, 15, 16, 17, 700, 2049, 0, 333]
+    case = synthetic.decode_case(seed=21, seq_lens=lens, dtype=torch.float16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    q = case.q.to(q_dtype)
+    want, want_lse = oracle.decode_paged(q.float().numpy(), cache, case.block_table.numpy(), case.seq_lens.numpy(),
+                                         golden["signs_seed42_d128"], SCALE, return_lse=True)
+    for ctas in (0, 1, 5):
+        out, lse = run_decode(q.to(DEV), torch.from_numpy(cache).to(DEV), case.block_table.to(DEV),
+                              case.seq_lens.to(DEV), out_dtype=out_dtype, num_ctas=ctas, want_lse=True)
+        got = out.float().cpu().numpy()
+        assert_attention_close(got, want, f"mixed lengths, ctas={ctas}")
+        assert (got[6] == 0).all()                                   # empty sequence -> zeros
+        ok = np.isfinite(want_lse)
+        np.testing.assert_allclose(lse.cpu().numpy()[ok], want_lse[ok], atol=2e-3)
+        assert np.isneginf(lse.cpu().numpy()[~ok]).all()
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (16, 4), (16, 2), (8, 1), (8, 8), (64, 8), (4, 4)])
+def test_head_geometries(oracle, golden, hq, hkv):
+    case = synthetic.decode_case(seed=30 + hq + hkv, seq_lens=[300, 45, 1000], dtype=torch.float16, heads=(hq, hkv))
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    want = oracle.decode_paged(case.q.float().numpy(), cache, case.block_table.numpy(), case.seq_lens.numpy(),
+                               golden["signs_seed42_d128"], SCALE)
+    for ctas in (0, 3):
+        out = run_decode(case.q.to(DEV), torch.from_numpy(cache).to(DEV), case.block_table.to(DEV),
+                         case.seq_lens.to(DEV), num_ctas=ctas)
+        assert_attention_close(out.float().cpu().numpy(), want, f"hq={hq} hkv={hkv} ctas={ctas}")
+
+
+def test_peaked_softmax_and_scale(oracle, golden):
+    """A query aligned with one key (one token dominates) and a non-default softmax scale."""
+    case = synthetic.decode_case(seed=41, seq_lens=[513, 64], dtype=torch.float16)
+    case.q[0] = case.k[100].repeat_interleave(4, dim=0) * 2.0
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    for scale in (SCALE, 0.25):
+        want = oracle.decode_paged(case.q.float().numpy(), cache, case.block_table.numpy(), case.seq_lens.numpy(),
+                                   golden["signs_seed42_d128"], scale)
+        out = run_decode(case.q.to(DEV), torch.from_numpy(cache).to(DEV), case.block_table.to(DEV),
+                         case.seq_lens.to(DEV), sm_scale=scale, out_dtype=torch.float32)
+        got = out.cpu().numpy()
+        # outputs are O(1) here; fp16 operand rounding scales with magnitude, so use the mixed bar
+        assert np.abs(got - want).max() <= 2e-3 + 1e-2 * np.abs(want).max()
+        assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-2
+
+
+def test_csr_page_table(oracle, golden):
+    case = synthetic.decode_case(seed=50, seq_lens=[100, 33, 260], dtype=torch.float16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    want = oracle.decode_paged(case.q.float().numpy(), cache, case.block_table.numpy(), case.seq_lens.numpy(),
+                               golden["signs_seed42_d128"], SCALE)
+    pages = [(int(n) + 15) // 16 for n in case.seq_lens]
+    indptr = torch.tensor([0] + list(np.cumsum(pages)), dtype=torch.int32)
+    indices = torch.cat([case.block_table[b, :p] for b, p in enumerate(pages)]).to(torch.int32)
+    out = run_decode(case.q.to(DEV), torch.from_numpy(cache).to(DEV), indices.to(DEV), case.seq_lens.to(DEV),
+                     page_indptr=indptr.to(DEV))
+    assert_attention_close(out.float().cpu().numpy(), want, "CSR page table")
+
+
+def test_partial_plus_merge_equals_full(oracle, golden):
+    """KV-axis split (the multi-GPU contract): per-window rotated partials + LSE merge == full."""
+    case = synthetic.decode_case(seed=60, seq_lens=[1500, 90], dtype=torch.bfloat16)
+    cache = torch.from_numpy(oracle_cache(oracle, case, golden["signs_seed42_d128"])).to(DEV)
+    q, bt, sl = case.q.to(DEV), case.block_table.to(DEV), case.seq_lens.to(DEV)
+    full = run_decode(q, cache, bt, sl, out_dtype=torch.float32)
+    ws = torch.empty(_cabi.decode_workspace_bytes(2, 32, 8), dtype=torch.uint8, device=DEV)
+    windows = [(0, 512), (512, 1024), (1024, -1), (2048, -1)]          # the last one is empty
+    po = torch.empty(len(windows), 2, 32, 128, dtype=torch.float32, device=DEV)
+    pl = torch.empty(len(windows), 2, 32, dtype=torch.float32, device=DEV)
+    for i, (a, b) in enumerate(windows):
+        _cabi.decode_paged_partial(q, cache, bt, sl, signs_dev(), SCALE, ws, po[i], pl[i], kv_begin=a, kv_end=b)
+    assert torch.isneginf(pl[3]).all() and torch.isneginf(pl[1, 1]).all()
+    out = torch.empty(2, 32, 128, dtype=torch.float32, device=DEV)
+    lse = torch.empty(2, 32, dtype=torch.float32, device=DEV)
+    _cabi.merge_rotated(po, pl, signs_dev(), out, lse)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(out.cpu().numpy(), full.cpu().numpy(), atol=2e-5, rtol=1e-4)
+    want, want_lse = oracle.decode_paged(case.q.float().numpy(), cache.cpu().numpy(), case.block_table.numpy(),
+                                         case.seq_lens.numpy(), golden["signs_seed42_d128"], SCALE, return_lse=True)
+    assert_attention_close(out.cpu().numpy(), want, "merged windows")
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=2e-3)
+
+
+def test_merge_rotated_matches_oracle_merge(oracle):
+    gen = torch.Generator().manual_seed(3)
+    po = torch.randn(5, 7, 128, generator=gen)
+    pl = torch.randn(5, 7, generator=gen) * 3
+    pl[2, 3] = -math.inf
+    pl[:, 5] = -math.inf
+    signs = synthetic.make_signs()
+    out = torch.empty(7, 128, dtype=torch.float32, device=DEV)
+    lse = torch.empty(7, dtype=torch.float32, device=DEV)
+    _cabi.merge_rotated(po.to(DEV), pl.to(DEV), signs.to(DEV), out, lse)
+    merged, mlse = oracle.merge_partials(po.numpy(), pl.numpy() * math.log(2.0))   # oracle is natural-log
+    want = np.stack([oracle.fwht(merged[r]) * signs.numpy() for r in range(7)])
+    np.testing.assert_allclose(out.cpu().numpy(), want, atol=1e-5)
+    ok = np.isfinite(mlse)
+    np.testing.assert_allclose(lse.cpu().numpy()[ok], mlse[ok], atol=1e-5)
+    assert (out.cpu().numpy()[5] == 0).all()
+
+
+def test_config1_full_size_properties():
+    """Batch 8 x 32768 tokens (one layer of the benchmark): the result must not depend on how the
+    KV range is cut (296 vs 37 vs 8 thread blocks), and one sequence decoded alone must equal its
+    row in the batch."""
+    B, L = 8, 32768
+    gen = torch.Generator().manual_seed(1)
+    nb = B * L // 16
+    cache = torch.zeros((2, nb, 16, 8, 80), dtype=torch.uint8, device=DEV)
+    perm = torch.randperm(nb, generator=gen)
+    bt = perm.view(B, L // 16).to(torch.int32).to(DEV)
+    signs = signs_dev()
+    for b in range(B):                                              # fill with the CUDA write kernel
+        k = torch.randn(L, 8, 128, generator=gen).to(torch.bfloat16).to(DEV)
+        v = torch.randn(L, 8, 128, generator=gen).to(torch.bfloat16).to(DEV)
+        t = torch.arange(L, device=DEV)
+        slots = bt[b].long()[t // 16] * 16 + t % 16
+        _cabi.write_kv_cache(cache, k, v, signs, slots, 128)
+    q = torch.randn(B, 32, 128, generator=gen).to(torch.bfloat16).to(DEV)
+    sl = torch.full((B,), L, dtype=torch.int32, device=DEV)
+    ref = run_decode(q, cache, bt, sl, out_dtype=torch.float32, num_ctas=296).cpu().numpy()
+    assert np.isfinite(ref).all() and np.abs(ref).max() > 1e-3
+    for ctas in (37, 8):
+        out = run_decode(q, cache, bt, sl, out_dtype=torch.float32, num_ctas=ctas).cpu().numpy()
+        assert np.abs(out - ref).max() <= 2e-4
+    one = run_decode(q[3:4], cache, bt[3:4], sl[3:4], out_dtype=torch.float32).cpu().numpy()
+    assert np.abs(one[0] - ref[3]).max() <= 2e-4
+    # shorter length on a page boundary and off it: later tokens must not leak in
+    sl2 = sl.clone()
+    sl2[0] = 20000
+    sl2[1] = 12345
+    out2 = run_decode(q, cache, bt, sl2, out_dtype=torch.float32).cpu().numpy()
+    assert np.abs(out2[2:] - ref[2:]).max() <= 2e-4
+    assert np.abs(out2[0] - ref[0]).max() > 1e-4

@@ -1,0 +1,234 @@
+"""ctypes binding of libturboquant_b200.so (the C ABI declared in include/turboquant_b200.h).
+
+torch is used for device memory and the current stream only: every call passes raw device
+pointers, sizes and the stream handle.  There is no CPU fallback: if the library is missing or
+a tensor is not on a CUDA device the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "lib" / "libturboquant_b200.so"
+
+TQ_F32, TQ_F16, TQ_BF16 = 0, 1, 2
+TQ_I32, TQ_I64 = 0, 1
+TQ_PACK_LOW_FIRST, TQ_PACK_CACHE = 0, 1
+TQ_WRITE_ZERO_PAD = 1
+
+_DTYPES = {torch.float32: TQ_F32, torch.float16: TQ_F16, torch.bfloat16: TQ_BF16}
+
+EXPORTS = (
+    "tq_abi_version", "tq_last_error", "tq_codebook", "tq_write_kv_cache", "tq_quantize_flat",
+    "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
+    "tq_decode_paged_partial", "tq_merge_rotated",
+)
+
+_lib = None
+
+
+class TurboQuantError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """Load the library or fail loudly (no fallback path exists)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise TurboQuantError(
+                f"{LIB_PATH} is missing: build it with `python -m turboquant_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(str(LIB_PATH))
+        L.tq_last_error.restype = ctypes.c_char_p
+        L.tq_decode_workspace_bytes.restype = ctypes.c_size_t
+        _lib = L
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise TurboQuantError(f"turboquant_b200 error {rc}: {lib().tq_last_error().decode()}")
+
+
+def _ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _cuda(t: torch.Tensor, name: str) -> None:
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise TurboQuantError(f"{name} must be a CUDA tensor (no CPU fallback)")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise TurboQuantError(f"unsupported dtype {dt}") from None
+
+
+def codebook(dim: int, bits: int):
+    """(centroids, boundaries) as CPU fp32 tensors; host-side call."""
+    cen = (ctypes.c_float * (1 << bits))()
+    bnd = (ctypes.c_float * ((1 << bits) - 1))()
+    _check(lib().tq_codebook(ctypes.c_int(dim), ctypes.c_int(bits), cen, bnd))
+    return torch.tensor(list(cen), dtype=torch.float32), torch.tensor(list(bnd), dtype=torch.float32)
+
+
+def write_kv_cache(kv_cache: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                   signs: torch.Tensor, slot_mapping: torch.Tensor, head_dim: int,
+                   zero_pad: bool = False) -> None:
+    """kv_cache uint8-addressable [2, nb, bs, H, slot]; key/value [T, H, D] (token stride free)."""
+    for t, n in ((kv_cache, "kv_cache"), (key, "key"), (value, "value"), (signs, "signs"),
+                 (slot_mapping, "slot_mapping")):
+        _cuda(t, n)
+    if kv_cache.dim() != 5 or kv_cache.shape[0] != 2 or not kv_cache.is_contiguous():
+        raise TurboQuantError("kv_cache must be a contiguous [2, num_blocks, block_size, heads, slot_bytes] tensor")
+    if kv_cache.element_size() != 1:
+        raise TurboQuantError("kv_cache must have a 1-byte element type")
+    _, nb, bs, H, ebs = kv_cache.shape
+    T = slot_mapping.shape[0]
+    if key.dtype != value.dtype:
+        raise TurboQuantError("key and value must share a dtype")
+    for t, n in ((key, "key"), (value, "value")):
+        if t.dim() != 3 or t.shape[1] != H or t.shape[2] != head_dim or t.shape[0] < T:
+            raise TurboQuantError(f"{n} must be [>=num_tokens, {H}, {head_dim}], got {tuple(t.shape)}")
+        if t.stride(2) != 1 or t.stride(1) != head_dim:
+            raise TurboQuantError(f"{n}: heads of one token must be contiguous")
+    if signs.dtype != torch.float32 or signs.numel() < head_dim or not signs.is_contiguous():
+        raise TurboQuantError("signs must be contiguous fp32 of padded head size")
+    if slot_mapping.dtype not in (torch.int32, torch.int64) or not slot_mapping.is_contiguous():
+        raise TurboQuantError("slot_mapping must be contiguous int32 or int64")
+    _check(lib().tq_write_kv_cache(
+        _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(H), ctypes.c_int(ebs),
+        _ptr(key), _ptr(value), ctypes.c_int(dtype_code(key.dtype)), ctypes.c_int64(T),
+        ctypes.c_int64(key.stride(0)), ctypes.c_int64(value.stride(0)), _ptr(signs),
+        _ptr(slot_mapping), ctypes.c_int(TQ_I64 if slot_mapping.dtype == torch.int64 else TQ_I32),
+        ctypes.c_int(head_dim), ctypes.c_int(TQ_WRITE_ZERO_PAD if zero_pad else 0), _stream(kv_cache)))
+
+
+def quantize_flat(x: torch.Tensor, signs: torch.Tensor, bits: int, cache_order: bool = False):
+    _cuda(x, "x")
+    _cuda(signs, "signs")
+    x = x.contiguous()
+    dim = x.shape[-1]
+    padded = 1 if dim <= 1 else 1 << (dim - 1).bit_length()
+    n = x.numel() // dim if dim else 0
+    vpb = 8 // bits
+    nbytes = (padded + vpb - 1) // vpb
+    packed = torch.empty(x.shape[:-1] + (nbytes,), dtype=torch.uint8, device=x.device)
+    norms = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    _check(lib().tq_quantize_flat(
+        _ptr(x), ctypes.c_int(dtype_code(x.dtype)), ctypes.c_int64(n), ctypes.c_int(dim), _ptr(signs),
+        ctypes.c_int(bits), ctypes.c_int(TQ_PACK_CACHE if cache_order else TQ_PACK_LOW_FIRST),
+        _ptr(packed), _ptr(norms), _stream(x)))
+    return packed, norms
+
+
+def dequantize_flat(packed: torch.Tensor, norms: torch.Tensor, signs: torch.Tensor, dim: int,
+                    bits: int, cache_order: bool = False) -> torch.Tensor:
+    _cuda(packed, "packed")
+    _cuda(norms, "norms")
+    packed = packed.contiguous()
+    norms = norms.to(torch.float32).contiguous()
+    n = norms.numel()
+    out = torch.empty(norms.shape + (dim,), dtype=torch.float32, device=packed.device)
+    _check(lib().tq_dequantize_flat(
+        _ptr(packed), _ptr(norms), ctypes.c_int64(n), ctypes.c_int(dim), _ptr(signs),
+        ctypes.c_int(bits), ctypes.c_int(TQ_PACK_CACHE if cache_order else TQ_PACK_LOW_FIRST),
+        _ptr(out), _stream(packed)))
+    return out
+
+
+def fwht(x: torch.Tensor, padded_dim: int, out_dim: int, pre_signs=None, post_signs=None) -> torch.Tensor:
+    _cuda(x, "x")
+    xf = x.to(torch.float32).contiguous()
+    in_dim = xf.shape[-1]
+    n = xf.numel() // in_dim if in_dim else 0
+    out = torch.empty(xf.shape[:-1] + (out_dim,), dtype=torch.float32, device=x.device)
+    _check(lib().tq_fwht(_ptr(xf), ctypes.c_int64(n), ctypes.c_int(in_dim), ctypes.c_int(padded_dim),
+                         ctypes.c_int(out_dim), _ptr(pre_signs), _ptr(post_signs), _ptr(out), _stream(x)))
+    return out
+
+
+def decode_workspace_bytes(batch: int, num_q_heads: int, num_kv_heads: int, head_dim: int = 128,
+                           num_ctas: int = 0) -> int:
+    return int(lib().tq_decode_workspace_bytes(ctypes.c_int(batch), ctypes.c_int(num_q_heads),
+                                               ctypes.c_int(num_kv_heads), ctypes.c_int(head_dim),
+                                               ctypes.c_int(num_ctas)))
+
+
+def _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs):
+    for t, n in ((q, "q"), (kv_cache, "kv_cache"), (page_indices, "page_indices"),
+                 (seq_lens, "seq_lens"), (signs, "signs")):
+        _cuda(t, n)
+    if q.dim() != 3 or not q.is_contiguous():
+        raise TurboQuantError("q must be contiguous [batch, num_q_heads, head_dim]")
+    if kv_cache.dim() != 5 or kv_cache.shape[0] != 2 or not kv_cache.is_contiguous() or kv_cache.element_size() != 1:
+        raise TurboQuantError("kv_cache must be contiguous 1-byte [2, num_blocks, block_size, heads, slot_bytes]")
+    if page_indices.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise TurboQuantError("page_indices and seq_lens must be int32")
+    if not page_indices.is_contiguous() or not seq_lens.is_contiguous():
+        raise TurboQuantError("page_indices and seq_lens must be contiguous")
+    if page_indptr is not None and (page_indptr.dtype != torch.int32 or not page_indptr.is_cuda):
+        raise TurboQuantError("page_indptr must be a CUDA int32 tensor")
+    if seq_lens.shape[0] != q.shape[0]:
+        raise TurboQuantError("seq_lens must have one entry per query row")
+
+
+def decode_paged(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, workspace, out,
+                 page_indptr=None, max_pages: int | None = None, out_lse=None, num_ctas: int = 0):
+    """One decode step; writes ``out`` [batch, Hq, D] (and ``out_lse`` fp32 [batch, Hq])."""
+    if max_pages is None:
+        max_pages = page_indices.shape[-1] if page_indices.dim() == 2 else 0
+    _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs)
+    B, Hq, D = q.shape
+    _, nb, bs, H, ebs = kv_cache.shape
+    _check(lib().tq_decode_paged(
+        _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(Hq), ctypes.c_int(H),
+        ctypes.c_int(D), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(ebs),
+        _ptr(page_indices), _ptr(page_indptr), ctypes.c_int(max_pages), _ptr(seq_lens), _ptr(signs),
+        ctypes.c_float(sm_scale), _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
+        _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), ctypes.c_int(num_ctas), _stream(q)))
+    return out
+
+
+def decode_paged_partial(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, workspace,
+                         out_rot, out_lse2, kv_begin: int = 0, kv_end: int = -1, page_indptr=None,
+                         max_pages: int | None = None, num_ctas: int = 0):
+    """Rotated-domain partial (fp32) + base-2 LSE over tokens [kv_begin, kv_end) of each sequence."""
+    if max_pages is None:
+        max_pages = page_indices.shape[-1] if page_indices.dim() == 2 else 0
+    _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs)
+    B, Hq, D = q.shape
+    _, nb, bs, H, ebs = kv_cache.shape
+    _check(lib().tq_decode_paged_partial(
+        _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(Hq), ctypes.c_int(H),
+        ctypes.c_int(D), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(ebs),
+        _ptr(page_indices), _ptr(page_indptr), ctypes.c_int(max_pages), _ptr(seq_lens),
+        ctypes.c_int64(kv_begin), ctypes.c_int64(kv_end), _ptr(signs), ctypes.c_float(sm_scale),
+        _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
+        _ptr(out_rot), _ptr(out_lse2), ctypes.c_int(num_ctas), _stream(q)))
+    return out_rot, out_lse2
+
+
+def merge_rotated(partial_o, partial_lse2, signs, out, out_lse=None):
+    """partial_o fp32 [parts, rows..., 128], partial_lse2 fp32 [parts, rows...] -> out [rows..., 128]."""
+    _cuda(partial_o, "partial_o")
+    _cuda(partial_lse2, "partial_lse2")
+    if partial_o.dtype != torch.float32 or partial_lse2.dtype != torch.float32:
+        raise TurboQuantError("partials must be fp32")
+    parts = partial_o.shape[0]
+    rows = partial_lse2.numel() // parts
+    _check(lib().tq_merge_rotated(
+        _ptr(partial_o.contiguous()), _ptr(partial_lse2.contiguous()), ctypes.c_int(parts),
+        ctypes.c_int64(rows), ctypes.c_int(partial_o.shape[-1]), _ptr(signs), _ptr(out),
+        ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), _stream(partial_o)))
+    return out

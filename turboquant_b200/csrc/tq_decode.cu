@@ -1,0 +1,755 @@
+// Paged decode attention over the 4-bit quantized KV cache, split-KV, for sm_100a.
+//
+// Replaces the reference's TurboQuantContiguousDecodeKernelV5TC<..., paged=true>
+// (csrc/include/flashinfer_decode_turboquant_v5_tc.cuh:112-795), its launcher
+// decode_v5_from_cache_paged_splitkv_ws (csrc/src/decode_v5_tc_binding.cu:754-874) and
+// SplitKVCombineKernel (csrc/include/flashinfer_decode_turboquant_combine.cuh:18-79).
+//
+// Design (one thread block = all KV heads of a contiguous page range):
+//   * The concatenated page list of the whole batch is cut into equal page ranges, one per
+//     thread block, on the device (a warp scan over seq_lens): no host planning, no host sync,
+//     perfectly balanced for mixed lengths.  A block whose range spans several sequences
+//     processes them as consecutive segments and writes one partial per (block, sequence).
+//   * A producer warp streams whole pages with non-multicast 1-D bulk async copies
+//     (cp.async.bulk, one 16-token x H x 80-byte row per copy) into a ring of shared-memory
+//     stages guarded by full/empty mbarriers, so DRAM sees contiguous 10 KB page reads.  Token
+//     rows are padded in shared memory (K: pitch = 64 mod 128, V: pitch = 16 mod 64) which makes
+//     the fragment loads below bank-conflict free.
+//   * Eight consumer warps, one per (KV head, page lane).  Packed codes go from shared memory
+//     straight into mma.sync.m16n8k16 A-fragments: a thread's 16-byte K chunk is exactly its
+//     k-slices of the eight QK MMAs (the head-dim order inside the contraction is free because Q
+//     is loaded in the same permuted order), and V nibbles of two tokens are zipped into bytes
+//     so that one dequantized half2 is a (token, token+1) pair of the PV contraction.  Tokens
+//     sit on the M axis (16) and the GQA query heads on N (8): 2x padding instead of 4x.
+//   * Dequantization is an 8-entry magnitude lookup done with byte permutes (prmt) on four
+//     nibbles at a time plus a sign flip (the codebook is odd-symmetric); norms are folded into
+//     the scores (K) and into P (V), so there is no per-element multiply.
+//   * Online softmax in the base-2 domain with one consistent base everywhere; the running
+//     max is only raised when the tile max exceeds it by more than 2^6, which makes rescaling of
+//     the output accumulators rare.
+//   * Partials (normalized, rotated domain, fp32) + base-2 LSE go to the workspace; the merge
+//     kernel combines them, applies the inverse rotation once per (sequence, head) and casts.
+//
+// Tensor-core generation: the dequantized operands are produced in registers, so the
+// register-operand mma.sync path is used; tcgen05 needs its A/B tiles in shared memory, which
+// would add a 2-byte-per-element shared-memory round trip to a kernel whose limiter is the
+// nibble->fp16 conversion rate, not MMA throughput (about 10% of the tensor pipe is needed).
+#include <cmath>
+#include <cstring>
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+constexpr int kHeadDim = 128;
+constexpr int kPageTokens = 16;
+constexpr int kSlotBytes = 80;
+constexpr int kConsumerWarps = 8;
+constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
+constexpr int kStages = 4;
+constexpr int kMaxSegments = 96;
+constexpr int kMinPagesPerCta = 4;
+constexpr float kRaiseThreshold = 6.0f;  // log2 units
+
+constexpr int k_pitch(int H) {  // token pitch of K rows in shared memory: = 64 (mod 128)
+    int b = H * kSlotBytes;
+    int pad = (64 - b % 128 + 128) % 128;
+    return b + pad;
+}
+constexpr int v_pitch(int H) {  // token pitch of V rows: = 16 (mod 64)
+    int b = H * kSlotBytes;
+    int pad = (16 - b % 64 + 64) % 64;
+    return b + pad;
+}
+
+struct DecodeParams {
+    const void* q;
+    const uint8_t* kv_cache;
+    const int32_t* page_indices;
+    const int32_t* page_indptr;  // may be null: dense block table with row stride max_pages
+    const int32_t* seq_lens;
+    const float* signs;
+    int32_t* header;        // workspace: [0] status, [1] effective block count, [2] total pages
+    int32_t* page_prefix;   // workspace: [batch + 1]
+    float* partial_lse;     // workspace: [slots][num_q_heads]
+    float* partial_o;       // workspace: [slots][num_q_heads][128]
+    int64_t slab_bytes;
+    int64_t kv_begin, kv_end;  // token window applied to every sequence (kv_end < 0: none)
+    int batch, num_q_heads, group, max_pages, q_dtype;
+    float k_scale;  // (1/sqrt(128)) * sm_scale * log2(e): multiplies raw code-domain scores
+    float v_scale;  // 1/sqrt(128): centroid scale folded into P
+    uint32_t lut_lo[2], lut_hi[2];  // fp16 low/high bytes of |centroid| for code 0..7
+};
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Eight packed 4-bit codes (one 32-bit word) -> four half2 registers, one per byte:
+// r[j] = { low half: centroid(low nibble of byte j), high half: centroid(high nibble) } in units
+// of the N(0,1) codebook.  Codes 0..7 are the negative centroids in ascending order and
+// code 15-k = -code k, so the magnitude index is k for k < 8 and 15-k otherwise.
+__device__ __forceinline__ void dequant8(uint32_t w, const uint32_t (&lo_t)[2],
+                                         const uint32_t (&hi_t)[2], uint32_t (&r)[4]) {
+    const uint32_t u = (w >> 3) & 0x11111111u;   // bit3 of each nibble
+    const uint32_t sel = w ^ (u * 15u);          // fold: nibble -> magnitude index, bit3 cleared
+    const uint32_t w4 = w << 4;
+    {
+        const uint32_t lo = prmt(lo_t[0], lo_t[1], sel);
+        uint32_t hi = prmt(hi_t[0], hi_t[1], sel);
+        const uint32_t pm = prmt(w, w4, 0x9D8Cu);  // 0xFF per nibble 0..3 whose bit3 is set
+        hi ^= (~pm & 0x80808080u);                 // bit3 clear = negative centroid
+        r[0] = prmt(lo, hi, 0x5140u);
+        r[1] = prmt(lo, hi, 0x7362u);
+    }
+    {
+        const uint32_t sel2 = sel >> 16;
+        const uint32_t lo = prmt(lo_t[0], lo_t[1], sel2);
+        uint32_t hi = prmt(hi_t[0], hi_t[1], sel2);
+        const uint32_t pm = prmt(w, w4, 0xBFAEu);  // nibbles 4..7
+        hi ^= (~pm & 0x80808080u);
+        r[2] = prmt(lo, hi, 0x5140u);
+        r[3] = prmt(lo, hi, 0x7362u);
+    }
+}
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float load_q(const void* q, int dtype, int64_t i) {
+    if (dtype == TQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[i]);
+    if (dtype == TQ_F16) return __half2float(reinterpret_cast<const __half*>(q)[i]);
+    return reinterpret_cast<const float*>(q)[i];
+}
+
+// Pages of sequence b inside the token window, and the first page index.
+__device__ __forceinline__ void seq_pages(const DecodeParams& p, int b, int& first_page, int& npages,
+                                          int& len_eff) {
+    int64_t len = p.seq_lens[b];
+    if (p.kv_end >= 0 && p.kv_end < len) len = p.kv_end;
+    const int64_t begin = p.kv_begin > 0 ? p.kv_begin : 0;
+    first_page = (int)(begin / kPageTokens);
+    const int64_t last = (len + kPageTokens - 1) / kPageTokens;
+    npages = last > first_page ? (int)(last - first_page) : 0;
+    len_eff = (int)len;
+}
+
+template <int HKV>
+struct DecodeSmem {
+    static constexpr int kPPS = kConsumerWarps / HKV;  // pages per stage
+    static constexpr int kKPitch = k_pitch(HKV);
+    static constexpr int kVPitch = v_pitch(HKV);
+    static constexpr int kKBytes = kPPS * kPageTokens * kKPitch;
+    static constexpr int kVBytes = kPPS * kPageTokens * kVPitch;
+    static constexpr int kStageBytes = kKBytes + kVBytes;
+    static constexpr int kQBytes = kConsumerWarps * 8 * kHeadDim * 2;  // rotated Q, fp16, per warp
+    static constexpr int kTotal = kStages * kStageBytes + kQBytes;
+};
+
+template <int HKV>
+__global__ void __launch_bounds__(kDecodeThreads, 2)
+decode_paged_kernel(const __grid_constant__ DecodeParams p) {
+    using S = DecodeSmem<HKV>;
+    constexpr int PPS = S::kPPS;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_bar[kStages];
+    __shared__ __align__(8) uint64_t empty_bar[kStages];
+    __shared__ int seg_seq[kMaxSegments], seg_p0[kMaxSegments], seg_p1[kMaxSegments];
+    __shared__ int num_segments, abort_flag;
+    __shared__ int n_eff_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint8_t* stages = smem;
+    __half* q_s = reinterpret_cast<__half*>(smem + kStages * S::kStageBytes);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kConsumerWarps);
+        }
+        num_segments = 0;
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    // ---- plan: warp 0 scans seq_lens, finds this block's page range and its segments ----------
+    if (warp == 0) {
+        // pass 1: total pages
+        int total = 0;
+        for (int base = 0; base < p.batch; base += 32) {
+            int np = 0, fp, le;
+            if (base + lane < p.batch) seq_pages(p, base + lane, fp, np, le);
+            for (int o = 16; o > 0; o >>= 1) np += __shfl_xor_sync(0xffffffffu, np, o);
+            total += np;
+        }
+        int n_eff = (total + kMinPagesPerCta * PPS - 1) / (kMinPagesPerCta * PPS);
+        n_eff = n_eff < 1 ? 1 : (n_eff > (int)gridDim.x ? (int)gridDim.x : n_eff);
+        const int c = blockIdx.x;
+        const int64_t lo = c < n_eff ? ((int64_t)c * total) / n_eff : 0;
+        const int64_t hi = c < n_eff ? ((int64_t)(c + 1) * total) / n_eff : 0;
+        // pass 2: prefix sums, segments, and (block 0) the prefix array for the merge kernel
+        int run = 0, nseg = 0;
+        for (int base = 0; base < p.batch; base += 32) {
+            int np = 0, fp = 0, le;
+            const int b = base + lane;
+            if (b < p.batch) seq_pages(p, b, fp, np, le);
+            int incl = np;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const int start = run + incl - np, end = run + incl;
+            if (c == 0 && b < p.batch) p.page_prefix[b] = start;
+            const bool hit = b < p.batch && np > 0 && start < hi && end > lo;
+            const uint32_t mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int slot = nseg + __popc(mask & ((1u << lane) - 1u));
+                if (slot < kMaxSegments) {
+                    seg_seq[slot] = b;
+                    seg_p0[slot] = (int)((lo > start ? lo : start) - start);
+                    seg_p1[slot] = (int)((hi < end ? hi : end) - start);
+                }
+            }
+            nseg += __popc(mask);
+            run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            if (c == 0) {
+                p.page_prefix[p.batch] = run;
+                p.header[1] = n_eff;
+                p.header[2] = total;
+            }
+            if (nseg > kMaxSegments) {  // more sequences per block than the list holds
+                atomicExch(&p.header[0], 2);
+                nseg = 0;
+            }
+            num_segments = nseg;
+            n_eff_s = n_eff;
+        }
+    }
+    __syncthreads();
+    const int nseg = num_segments;
+    if (nseg == 0) return;
+
+    if (warp == kConsumerWarps) {
+        // =============================== producer warp ======================================
+        int it = 0;
+        for (int sg = 0; sg < nseg && !abort_flag; sg++) {
+            const int b = seg_seq[sg];
+            int first_page, npages_b, len_eff;
+            seq_pages(p, b, first_page, npages_b, len_eff);
+            const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
+            const int p0 = seg_p0[sg], p1 = seg_p1[sg];
+            for (int base = p0; base < p1; base += 32) {
+                const int mine = base + lane;
+                const int my_page = mine < p1 ? p.page_indices[tbl + first_page + mine] : 0;
+                const int cnt = (p1 - base) < 32 ? (p1 - base) : 32;
+                for (int j = 0; j < cnt; j += PPS, it++) {
+                    const int st = it % kStages;
+                    const int np = (cnt - j) < PPS ? (cnt - j) : PPS;
+                    if (it >= kStages) {
+                        if (!mbar_wait(&empty_bar[st], ((it / kStages) - 1) & 1)) {
+                            abort_flag = 1;
+                            atomicExch(&p.header[0], 1);
+                        }
+                    }
+                    if (abort_flag) break;
+                    uint8_t* sk = stages + (size_t)st * S::kStageBytes;
+                    uint8_t* sv = sk + S::kKBytes;
+                    if (lane == 0)
+                        mbar_arrive_expect_tx(&full_bar[st],
+                                              (uint32_t)(np * 2 * kPageTokens * HKV * kSlotBytes));
+                    __syncwarp();
+#pragma unroll
+                    for (int pp = 0; pp < PPS; pp++) {
+                        const int page = __shfl_sync(0xffffffffu, my_page, (j + pp) & 31);
+                        if (pp < np) {
+                            const int tok = lane & 15;
+                            const bool is_v = lane >= 16;
+                            const uint8_t* src = p.kv_cache + (is_v ? p.slab_bytes : 0) +
+                                                 ((int64_t)page * kPageTokens + tok) * (HKV * kSlotBytes);
+                            uint8_t* dst = is_v ? sv + (pp * kPageTokens + tok) * S::kVPitch
+                                                : sk + (pp * kPageTokens + tok) * S::kKPitch;
+                            bulk_g2s(dst, src, HKV * kSlotBytes, &full_bar[st]);
+                        }
+                    }
+                }
+                if (abort_flag) break;
+            }
+        }
+        return;
+    }
+
+    // ================================= consumer warps =======================================
+    const int g = lane >> 2, tg = lane & 3;
+    const int head = warp % HKV;   // KV head of this warp
+    const int sub = warp / HKV;    // page lane inside a stage
+    __half* qw = q_s + warp * 8 * kHeadDim;
+    const uint32_t lut_lo[2] = {p.lut_lo[0], p.lut_lo[1]};
+    const uint32_t lut_hi[2] = {p.lut_hi[0], p.lut_hi[1]};
+
+    int it = 0;
+    for (int sg = 0; sg < nseg; sg++) {
+        const int b = seg_seq[sg];
+        int first_page, npages_b, len_eff;
+        seq_pages(p, b, first_page, npages_b, len_eff);
+        const int p0 = seg_p0[sg], p1 = seg_p1[sg];
+
+        // ---- rotate this KV head's query heads: signs -> FWHT -> 1/sqrt(128) -> fp16 -----------
+        // lane holds elements 4*lane .. 4*lane+3; stages h=1,2 are local, h=4..64 by shuffle.
+        for (int r = 0; r < 8; r++) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (r < p.group) {
+                const int64_t base = ((int64_t)b * p.num_q_heads + head * p.group + r) * kHeadDim + 4 * lane;
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[i] = load_q(p.q, p.q_dtype, base + i) * p.signs[4 * lane + i];
+                float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+                v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float o = __shfl_xor_sync(0xffffffffu, v[i], d);
+                        v[i] = (lane & d) ? o - v[i] : v[i] + o;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[i] *= 0.08838834764831845f;
+            }
+            // stored with each (even, odd) pair swapped: a code byte dequantizes to
+            // {low half: odd dim (low nibble), high half: even dim (high nibble)}
+            __half2* dst = reinterpret_cast<__half2*>(qw + r * kHeadDim + 4 * lane);
+            dst[0] = __floats2half2_rn(v[1], v[0]);
+            dst[1] = __floats2half2_rn(v[3], v[2]);
+        }
+        __syncwarp();
+        // B fragments of the eight QK MMAs: pairs 16*tg .. 16*tg+15 of query head g
+        uint32_t qf[16];
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(qw + g * kHeadDim + 32 * tg);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint4 t = src[i];
+                qf[4 * i] = t.x; qf[4 * i + 1] = t.y; qf[4 * i + 2] = t.z; qf[4 * i + 3] = t.w;
+            }
+        }
+        __syncwarp();
+
+        float o_acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) o_acc[i][j] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+        for (int pg = p0; pg < p1; pg += PPS, it++) {
+            const int st = it % kStages;
+            if (!mbar_wait(&full_bar[st], (it / kStages) & 1)) {
+                abort_flag = 1;
+                atomicExch(&p.header[0], 1);
+            }
+            if (abort_flag) return;
+            const bool have = pg + sub < p1;  // this warp's page lane holds a page
+            if (have) {
+                const uint8_t* sk = stages + (size_t)st * S::kStageBytes +
+                                    (size_t)sub * kPageTokens * S::kKPitch + head * kSlotBytes;
+                const uint8_t* sv = stages + (size_t)st * S::kStageBytes + S::kKBytes +
+                                    (size_t)sub * kPageTokens * S::kVPitch + head * kSlotBytes;
+                const int tok0 = (first_page + pg + sub) * kPageTokens;  // first token of the page
+
+                // ---- K codes and norms for tokens g and g+8 -------------------------------------
+                const uint4 ka = *reinterpret_cast<const uint4*>(sk + g * S::kKPitch + 16 * tg);
+                const uint4 kb = *reinterpret_cast<const uint4*>(sk + (g + 8) * S::kKPitch + 16 * tg);
+                const bool va = tok0 + g < len_eff, vb = tok0 + g + 8 < len_eff;
+                const float nka = __half2float(*reinterpret_cast<const __half*>(sk + g * S::kKPitch + 64));
+                const float nkb = __half2float(*reinterpret_cast<const __half*>(sk + (g + 8) * S::kKPitch + 64));
+                const float nva = __half2float(*reinterpret_cast<const __half*>(sv + g * S::kVPitch + 64));
+                const float nvb = __half2float(*reinterpret_cast<const __half*>(sv + (g + 8) * S::kVPitch + 64));
+                // ---- V codes: bytes 8g..8g+7 of tokens 2tg, 2tg+1, 2tg+8, 2tg+9 -------------------
+                const uint2 v0 = *reinterpret_cast<const uint2*>(sv + (2 * tg) * S::kVPitch + 8 * g);
+                const uint2 v1 = *reinterpret_cast<const uint2*>(sv + (2 * tg + 1) * S::kVPitch + 8 * g);
+                const uint2 v2 = *reinterpret_cast<const uint2*>(sv + (2 * tg + 8) * S::kVPitch + 8 * g);
+                const uint2 v3 = *reinterpret_cast<const uint2*>(sv + (2 * tg + 9) * S::kVPitch + 8 * g);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[st]);  // stage data is in registers now
+
+                // ---- S = K^ Q^T : 16 tokens x 8 heads ---------------------------------------------
+                float s_acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t kwa[4] = {ka.x, ka.y, ka.z, ka.w};
+                const uint32_t kwb[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    uint32_t ra[4], rb[4];
+                    dequant8(kwa[w], lut_lo, lut_hi, ra);
+                    dequant8(kwb[w], lut_lo, lut_hi, rb);
+                    mma16816(s_acc, ra[0], rb[0], ra[1], rb[1], qf[4 * w], qf[4 * w + 1]);
+                    mma16816(s_acc, ra[2], rb[2], ra[3], rb[3], qf[4 * w + 2], qf[4 * w + 3]);
+                }
+                // ---- online softmax (base 2) ------------------------------------------------------
+                const float kfa = va ? nka * p.k_scale : 0.f, kfb = vb ? nkb * p.k_scale : 0.f;
+                float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
+                float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
+                float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+                }
+                const bool raise0 = mx0 > m0 + kRaiseThreshold, raise1 = mx1 > m1 + kRaiseThreshold;
+                if (__any_sync(0xffffffffu, raise0 || raise1)) {
+                    const float c0 = raise0 ? exp2f(m0 - mx0) : 1.f, c1 = raise1 ? exp2f(m1 - mx1) : 1.f;
+                    if (raise0) m0 = mx0;
+                    if (raise1) m1 = mx1;
+                    l0 *= c0;
+                    l1 *= c1;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        o_acc[i][0] *= c0; o_acc[i][1] *= c1; o_acc[i][2] *= c0; o_acc[i][3] *= c1;
+                    }
+                }
+                const float e0 = exp2f(x0 - m0), e1 = exp2f(x1 - m1), e2 = exp2f(x2 - m0), e3 = exp2f(x3 - m1);
+                l0 += e0 + e2;
+                l1 += e1 + e3;
+                const float vfa = va ? nva * p.v_scale : 0.f, vfb = vb ? nvb * p.v_scale : 0.f;
+                // P (token rows g / g+8, head columns 2tg, 2tg+1) -> transposed B fragments
+                const uint32_t pb0 = movmatrix_trans(pack_half2(e0 * vfa, e1 * vfa));
+                const uint32_t pb1 = movmatrix_trans(pack_half2(e2 * vfb, e3 * vfb));
+
+                // ---- O^T += V^^T P : zip the nibbles of a token pair into bytes, dequantize --------
+                const uint32_t vw0[2] = {v0.x, v0.y}, vw1[2] = {v1.x, v1.y};
+                const uint32_t vw2[2] = {v2.x, v2.y}, vw3[2] = {v3.x, v3.y};
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    // low nibbles = odd dims, high nibbles = even dims
+                    const uint32_t lo01 = (vw0[i] & 0x0F0F0F0Fu) | ((vw1[i] << 4) & 0xF0F0F0F0u);
+                    const uint32_t hi01 = ((vw0[i] >> 4) & 0x0F0F0F0Fu) | (vw1[i] & 0xF0F0F0F0u);
+                    const uint32_t lo23 = (vw2[i] & 0x0F0F0F0Fu) | ((vw3[i] << 4) & 0xF0F0F0F0u);
+                    const uint32_t hi23 = ((vw2[i] >> 4) & 0x0F0F0F0Fu) | (vw3[i] & 0xF0F0F0F0u);
+                    uint32_t a_lo01[4], a_hi01[4], a_lo23[4], a_hi23[4];
+                    dequant8(lo01, lut_lo, lut_hi, a_lo01);
+                    dequant8(hi01, lut_lo, lut_hi, a_hi01);
+                    dequant8(lo23, lut_lo, lut_hi, a_lo23);
+                    dequant8(hi23, lut_lo, lut_hi, a_hi23);
+#pragma unroll
+                    for (int j = 0; j < 4; j++)  // rows: g <- odd dim, g+8 <- even dim of byte 4i+j
+                        mma16816(o_acc[4 * i + j], a_lo01[j], a_hi01[j], a_lo23[j], a_hi23[j], pb0, pb1);
+                }
+            } else {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[st]);
+            }
+        }
+
+        // ---- finish the segment: normalize, write the partial and its base-2 LSE ----------------
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+        }
+        const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        const int64_t slot = ((int64_t)blockIdx.x + b) * PPS + sub;
+        const int h0 = 2 * tg, h1 = 2 * tg + 1;
+        float* po = p.partial_o + (slot * p.num_q_heads + head * p.group) * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d_odd = 16 * g + 2 * i + 1, d_even = 16 * g + 2 * i;
+            if (h0 < p.group) {
+                po[h0 * kHeadDim + d_odd] = o_acc[i][0] * inv0;
+                po[h0 * kHeadDim + d_even] = o_acc[i][2] * inv0;
+            }
+            if (h1 < p.group) {
+                po[h1 * kHeadDim + d_odd] = o_acc[i][1] * inv1;
+                po[h1 * kHeadDim + d_even] = o_acc[i][3] * inv1;
+            }
+        }
+        if (g == 0) {
+            float* pl = p.partial_lse + slot * p.num_q_heads + head * p.group;
+            if (h0 < p.group) pl[h0] = l0 > 0.f ? m0 + log2f(l0) : -INFINITY;
+            if (h1 < p.group) pl[h1] = l1 > 0.f ? m1 + log2f(l1) : -INFINITY;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Merge: one block per (row, query head), one thread per rotated dim.
+// ---------------------------------------------------------------------------------------------
+struct MergeParams {
+    const float* partial_o;
+    const float* partial_lse;
+    const int32_t* header;       // decode workspace header (null for the generic merge)
+    const int32_t* page_prefix;  // decode workspace prefix (null for the generic merge)
+    const float* signs;
+    void* out;
+    float* out_lse;   // natural-log LSE (final) or base-2 LSE (rotated output), optional
+    int64_t rows;     // batch (decode merge) or rows (generic merge)
+    int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
+};
+
+__global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__ MergeParams p) {
+    __shared__ float buf[kHeadDim];
+    const int d = threadIdx.x;
+    const int64_t row = blockIdx.x;
+    const int hq = blockIdx.y;
+    float m = -INFINITY, wsum = 0.f, acc = 0.f;
+    auto add = [&](int64_t slot) {
+        const float lse = p.partial_lse[slot * p.num_q_heads + hq];
+        if (lse == -INFINITY) return;
+        const float o = p.partial_o[(slot * p.num_q_heads + hq) * kHeadDim + d];
+        const float mn = fmaxf(m, lse);
+        const float so = exp2f(m - mn), sn = exp2f(lse - mn);
+        acc = acc * so + o * sn;
+        wsum = wsum * so + sn;
+        m = mn;
+    };
+    if (p.header) {
+        // partials of sequence `row` come from the blocks whose page range meets its pages
+        const int64_t n = p.header[1], total = p.header[2];
+        const int64_t s = p.page_prefix[row], e = p.page_prefix[row + 1];
+        if (e > s && total > 0) {
+            const int64_t c_first = ((s + 1) * n + total - 1) / total - 1;
+            const int64_t c_last = (e * n + total - 1) / total - 1;
+            for (int64_t c = c_first; c <= c_last; c++)
+                for (int sub = 0; sub < p.pps; sub++) add((c + row) * p.pps + sub);
+        }
+    } else {
+        // generic layout: partial_o [parts][rows][heads][128]
+        for (int part = 0; part < p.num_parts; part++) add((int64_t)part * p.rows + row);
+    }
+    float o = wsum > 0.f ? acc / wsum : 0.f;
+    const float lse2 = wsum > 0.f ? m + log2f(wsum) : -INFINITY;
+    const int64_t orow = row * p.num_q_heads + hq;
+    if (p.emit_rotated) {
+        reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
+        if (p.out_lse && d == 0) p.out_lse[orow] = lse2;
+        return;
+    }
+    // inverse rotation: FWHT, 1/sqrt(128), signs
+    buf[d] = o;
+    __syncthreads();
+    for (int h = 1; h < kHeadDim; h <<= 1) {
+        const float a = buf[d & ~h], b2 = buf[d | h];
+        __syncthreads();
+        buf[d] = (d & h) ? a - b2 : a + b2;
+        __syncthreads();
+    }
+    o = buf[d] * 0.08838834764831845f * p.signs[d];
+    if (p.out_dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[orow * kHeadDim + d] = __float2bfloat16_rn(o);
+    else if (p.out_dtype == TQ_F16) reinterpret_cast<__half*>(p.out)[orow * kHeadDim + d] = __float2half_rn(o);
+    else reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
+    if (p.out_lse && d == 0) p.out_lse[orow] = lse2 * 0.6931471805599453f;
+}
+
+int device_sm_count(int* out);
+
+struct WorkspaceLayout {
+    size_t header, prefix, lse, o, total;
+    int64_t slots;
+};
+
+static WorkspaceLayout workspace_layout(int batch, int num_q_heads, int num_kv_heads, int num_ctas) {
+    WorkspaceLayout w;
+    const int pps = kConsumerWarps / num_kv_heads;
+    w.slots = ((int64_t)num_ctas + batch) * pps;
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    w.header = 0;
+    w.prefix = up(64);
+    w.lse = w.prefix + up(sizeof(int32_t) * ((size_t)batch + 1));
+    w.o = w.lse + up(sizeof(float) * (size_t)w.slots * num_q_heads);
+    w.total = w.o + up(sizeof(float) * (size_t)w.slots * num_q_heads * kHeadDim);
+    return w;
+}
+
+static int resolve_ctas(int num_ctas, int* out) {
+    if (num_ctas > 0) {
+        *out = num_ctas;
+        return TQ_OK;
+    }
+    int sms = 0;
+    int rc = device_sm_count(&sms);
+    if (rc != TQ_OK) return rc;
+    *out = 2 * sms;
+    return TQ_OK;
+}
+
+template <int HKV>
+static int launch_decode(const DecodeParams& p, int grid, cudaStream_t stream) {
+    constexpr int smem = DecodeSmem<HKV>::kTotal;
+    static bool configured = false;
+    if (!configured) {
+        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    decode_paged_kernel<HKV><<<grid, kDecodeThreads, smem, stream>>>(p);
+    TQ_CUDA(cudaGetLastError());
+    return TQ_OK;
+}
+
+static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
+                         int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,
+                         int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
+                         int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
+                         const float* signs, float sm_scale, void* workspace, size_t workspace_bytes,
+                         void* out, int out_dtype, float* out_lse, int emit_rotated, int num_ctas,
+                         void* stream) {
+    TQ_REQUIRE(batch >= 0, TQ_ERR_INVALID, "negative batch");
+    if (batch == 0) return TQ_OK;
+    TQ_REQUIRE(q && kv_cache && page_indices && seq_lens && signs && workspace && out, TQ_ERR_INVALID, "null pointer");
+    TQ_REQUIRE(head_dim == kHeadDim, TQ_ERR_UNSUPPORTED, "decode supports head_dim 128, got %d", head_dim);
+    TQ_REQUIRE(block_size == kPageTokens, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
+    TQ_REQUIRE(slot_bytes == kSlotBytes, TQ_ERR_UNSUPPORTED, "decode supports 80-byte slots, got %d", slot_bytes);
+    TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8,
+               TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4 or 8, got %d", num_kv_heads);
+    TQ_REQUIRE(num_q_heads % num_kv_heads == 0 && num_q_heads / num_kv_heads >= 1 &&
+                   num_q_heads / num_kv_heads <= 8,
+               TQ_ERR_UNSUPPORTED, "query heads per KV head must be 1..8");
+    TQ_REQUIRE(q_dtype >= TQ_F32 && q_dtype <= TQ_BF16 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16,
+               TQ_ERR_INVALID, "bad dtype");
+    TQ_REQUIRE(((uintptr_t)kv_cache % 16) == 0 && ((uintptr_t)workspace % 256) == 0, TQ_ERR_INVALID,
+               "kv_cache must be 16-byte and workspace 256-byte aligned");
+    TQ_REQUIRE(kv_begin >= 0 && kv_begin % kPageTokens == 0, TQ_ERR_INVALID, "kv_begin must be a multiple of 16");
+    TQ_REQUIRE(page_indptr || max_pages > 0, TQ_ERR_INVALID, "max_pages must be positive for a dense block table");
+    int ctas = 0;
+    int rc = resolve_ctas(num_ctas, &ctas);
+    if (rc != TQ_OK) return rc;
+    const WorkspaceLayout w = workspace_layout(batch, num_q_heads, num_kv_heads, ctas);
+    TQ_REQUIRE(workspace_bytes >= w.total, TQ_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.total);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+
+    DecodeParams p{};
+    p.q = q;
+    p.kv_cache = static_cast<const uint8_t*>(kv_cache);
+    p.page_indices = page_indices;
+    p.page_indptr = page_indptr;
+    p.seq_lens = seq_lens;
+    p.signs = signs;
+    p.header = reinterpret_cast<int32_t*>(ws + w.header);
+    p.page_prefix = reinterpret_cast<int32_t*>(ws + w.prefix);
+    p.partial_lse = reinterpret_cast<float*>(ws + w.lse);
+    p.partial_o = reinterpret_cast<float*>(ws + w.o);
+    p.slab_bytes = num_blocks * (int64_t)block_size * num_kv_heads * slot_bytes;
+    p.kv_begin = kv_begin;
+    p.kv_end = kv_end;
+    p.batch = batch;
+    p.num_q_heads = num_q_heads;
+    p.group = num_q_heads / num_kv_heads;
+    p.max_pages = max_pages;
+    p.q_dtype = q_dtype;
+    const double inv_sqrt_d = 1.0 / std::sqrt((double)kHeadDim);
+    p.k_scale = (float)(inv_sqrt_d * (double)sm_scale * 1.4426950408889634);
+    p.v_scale = (float)inv_sqrt_d;
+    for (int k = 0; k < 8; k++) {  // magnitude of code k (= -centroid k) as fp16 bytes
+        const __half h = __float2half_rn((float)(-kCentroidsN01_4bit[k]));
+        const uint16_t bits = *reinterpret_cast<const uint16_t*>(&h);
+        p.lut_lo[k / 4] |= (uint32_t)(bits & 0xff) << (8 * (k % 4));
+        p.lut_hi[k / 4] |= (uint32_t)(bits >> 8) << (8 * (k % 4));
+    }
+    TQ_CUDA(cudaMemsetAsync(p.header, 0, 64, s));
+    switch (num_kv_heads) {
+        case 8: rc = launch_decode<8>(p, ctas, s); break;
+        case 4: rc = launch_decode<4>(p, ctas, s); break;
+        case 2: rc = launch_decode<2>(p, ctas, s); break;
+        default: rc = launch_decode<1>(p, ctas, s); break;
+    }
+    if (rc != TQ_OK) return rc;
+
+    MergeParams m{};
+    m.partial_o = p.partial_o;
+    m.partial_lse = p.partial_lse;
+    m.header = p.header;
+    m.page_prefix = p.page_prefix;
+    m.signs = signs;
+    m.out = out;
+    m.out_lse = out_lse;
+    m.rows = batch;
+    m.num_q_heads = num_q_heads;
+    m.pps = kConsumerWarps / num_kv_heads;
+    m.grid_ctas = ctas;
+    m.out_dtype = out_dtype;
+    m.emit_rotated = emit_rotated;
+    merge_kernel<<<dim3((unsigned)batch, (unsigned)num_q_heads), kHeadDim, 0, s>>>(m);
+    TQ_CUDA(cudaGetLastError());
+    return TQ_OK;
+}
+
+}  // namespace tq
+
+extern "C" size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads,
+                                            int head_dim, int num_ctas) {
+    (void)head_dim;
+    if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_kv_heads > tq::kConsumerWarps) return 0;
+    int ctas = 0;
+    if (tq::resolve_ctas(num_ctas, &ctas) != TQ_OK) return 0;
+    return tq::workspace_layout(batch, num_q_heads, num_kv_heads, ctas).total;
+}
+
+extern "C" int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads,
+                               int num_kv_heads, int head_dim, const void* kv_cache,
+                               int64_t num_blocks, int block_size, int slot_bytes,
+                               const int32_t* page_indices, const int32_t* page_indptr,
+                               int max_pages, const int32_t* seq_lens, const float* signs,
+                               float sm_scale, void* workspace, size_t workspace_bytes, void* out,
+                               int out_dtype, float* out_lse, int num_ctas, void* stream) {
+    return tq::decode_common(q, q_dtype, batch, num_q_heads, num_kv_heads, head_dim, kv_cache,
+                             num_blocks, block_size, slot_bytes, page_indices, page_indptr,
+                             max_pages, seq_lens, 0, -1, signs, sm_scale, workspace, workspace_bytes,
+                             out, out_dtype, out_lse, 0, num_ctas, stream);
+}
+
+extern "C" int tq_decode_paged_partial(const void* q, int q_dtype, int batch, int num_q_heads,
+                                       int num_kv_heads, int head_dim, const void* kv_cache,
+                                       int64_t num_blocks, int block_size, int slot_bytes,
+                                       const int32_t* page_indices, const int32_t* page_indptr,
+                                       int max_pages, const int32_t* seq_lens, int64_t kv_begin,
+                                       int64_t kv_end, const float* signs, float sm_scale,
+                                       void* workspace, size_t workspace_bytes, float* out_rot,
+                                       float* out_lse2, int num_ctas, void* stream) {
+    return tq::decode_common(q, q_dtype, batch, num_q_heads, num_kv_heads, head_dim, kv_cache,
+                             num_blocks, block_size, slot_bytes, page_indices, page_indptr,
+                             max_pages, seq_lens, kv_begin, kv_end, signs, sm_scale, workspace,
+                             workspace_bytes, out_rot, TQ_F32, out_lse2, 1, num_ctas, stream);
+}
+
+extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_parts,
+                                int64_t rows, int head_dim, const float* signs, void* out,
+                                int out_dtype, float* out_lse, void* stream) {
+    using namespace tq;
+    if (rows == 0) return TQ_OK;
+    TQ_REQUIRE(partial_o && partial_lse2 && signs && out, TQ_ERR_INVALID, "null pointer");
+    TQ_REQUIRE(head_dim == kHeadDim, TQ_ERR_UNSUPPORTED, "merge supports head_dim 128, got %d", head_dim);
+    TQ_REQUIRE(num_parts >= 1 && rows > 0, TQ_ERR_INVALID, "num_parts and rows must be positive");
+    TQ_REQUIRE(out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad out_dtype");
+    MergeParams m{};
+    m.partial_o = partial_o;
+    m.partial_lse = partial_lse2;
+    m.signs = signs;
+    m.out = out;
+    m.out_lse = out_lse;
+    m.rows = rows;
+    m.num_q_heads = 1;
+    m.num_parts = num_parts;
+    m.out_dtype = out_dtype;
+    merge_kernel<<<dim3((unsigned)rows, 1), kHeadDim, 0, static_cast<cudaStream_t>(stream)>>>(m);
+    TQ_CUDA(cudaGetLastError());
+    return TQ_OK;
+}
