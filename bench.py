@@ -1,0 +1,398 @@
+"""Benchmark of the decode-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (the batched long-context config): a Qwen3-8B-shaped decode layer — batch 8 per GPU,
+context 32768 per sequence, 32 query / 8 KV heads, head_dim 128, bf16 queries, 16-token pages
+laid out by a seeded random permutation, the KV cache pre-quantized from N(0,1) data by the
+cache-write kernel — and one step = one decode-attention pass over 36 layers (36 distinct layer
+caches, 335 MB each: every launch streams far more than L2 holds).  Metric: decode-attention
+tokens/s (batch x GPUs / step time).  With N > 1 every GPU runs its own batch (sequences are
+independent: no collective on the data path, weak scaling).
+
+Prints ONE JSON line (rank 0).  `value` is timed on the device with inputs resident in HBM
+(CUDA-graph replay of the 36 launches pairs); `e2e` is the same step through the package's
+public API with host buffers: the step's queries and new K/V rows are copied from pinned host
+memory, the new rows are written into the cache, and the outputs are copied back, all inside
+the timed region.  `roofline` is for the decode kernel alone, timed per launch with CUDA events
+recorded by the library around that kernel.  `cpu_baseline` / `--impl reference` time the CPU
+oracle (a C restatement of the reference's torch CPU path) on a bounded sample of the same data.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+HQ, HKV, D, PAGE, SLOT = 32, 8, 128, 16, 80
+ALG_BYTES_PER_TOKEN_HEAD = 136  # K (64 code + 4 norm bytes) + V (64 + 4)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--num-ctas", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        return float(json.loads(f.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (C restatement of the reference's torch CPU path) on a bounded sample
+# ------------------------------------------------------------------------------------------------
+def cpu_decode_rate(cache_np, block_table_np, q_np, signs_np, ctx_sample: int, threads: int):
+    """KV token-heads per second of the CPU dequant-attention path, `threads` sequences in
+    parallel, each attending `ctx_sample` tokens of the real quantized cache."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import tq_oracle
+    nseq = q_np.shape[0]
+    lens = np.full(1, ctx_sample, np.int32)
+
+    def one(i):
+        b = i % nseq
+        return tq_oracle.decode_paged(q_np[b:b + 1], cache_np, block_table_np[b:b + 1], lens, signs_np,
+                                      1.0 / math.sqrt(D))
+    one(0)
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        list(ex.map(one, range(threads)))
+    dt = time.perf_counter() - t0
+    return threads * ctx_sample * HKV / dt, dt
+
+
+def synthetic_host_cache(ctx: int, batch: int, seed: int):
+    """A host-side quantized cache for the CPU arm when no GPU copy is at hand (reference arm)."""
+    from oracle import tq_oracle
+    from turboquant_b200 import synthetic
+    case = synthetic.decode_case(seed=seed, seq_lens=[ctx] * batch, dtype=torch.bfloat16)
+    signs = synthetic.make_signs(D, 42).numpy()
+    cache = np.zeros((2, case.num_blocks, PAGE, HKV, SLOT), np.uint8)
+    tq_oracle.write_kv_cache(cache, case.k.float().numpy(), case.v.float().numpy(), signs,
+                             case.slot_mapping.numpy(), D)
+    return cache, case.block_table.numpy(), case.q.float().numpy(), signs
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (its torch modules cannot travel to the
+    GPU box, so the oracle port stands in), all host threads, bounded sample per step."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    ctx_s = min(8192, args.ctx)
+    cache, bt, q, signs = synthetic_host_cache(ctx_s, min(args.batch, 8), seed=1)
+    rates = []
+    for i in range(args.warmup + args.steps):
+        r, dt = cpu_decode_rate(cache, bt, q, signs, ctx_s, threads)
+        if i >= args.warmup:
+            rates.append((r, dt))
+    rate = statistics.median(r for r, _ in rates)
+    per_token = args.ctx * HKV * args.layers           # KV token-heads one decode token attends
+    value = rate / per_token
+    sample = (f"{threads} sequences x {ctx_s} tokens x {HKV} KV heads of config-1-shaped quantized cache per step "
+              f"(one layer), scaled to ctx {args.ctx} x {args.layers} layers per token")
+    line = {
+        "impl": "reference", "metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * statistics.median(dt for _, dt in rates), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "note": "CPU arm: C port of the reference torch CPU path"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(args):
+    return (f"config1: Qwen3-8B-shaped decode layer, batch {args.batch}/GPU x ctx {args.ctx}, {HQ}q/{HKV}kv heads, "
+            f"head_dim {D}, bf16 q, 16-token pages (seeded random permutation), {args.layers} layers per step")
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    from turboquant_b200 import _cabi
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    B, L, NL = args.batch, args.ctx, args.layers
+    pages_per_seq = (L + PAGE - 1) // PAGE
+    nb = B * pages_per_seq
+    attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, seed=42, num_ctas=args.num_ctas)
+
+    # ---- inputs: seeded, generated on the device, quantized by the cache-write kernel -----------
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1 + 1000 * rank)
+    cpu_gen = torch.Generator().manual_seed(1 + 1000 * rank)
+    block_table = torch.randperm(nb, generator=cpu_gen).view(B, pages_per_seq).to(torch.int32).to(dev)
+    seq_lens = torch.full((B,), L, dtype=torch.int32, device=dev)
+    caches = torch.zeros((NL,) + kv_cache_shape(nb, PAGE, HKV, D), dtype=torch.uint8, device=dev)
+    tok = torch.arange(L, device=dev)
+    for layer in range(NL):
+        for b in range(B):
+            k = torch.randn(L, HKV, D, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            v = torch.randn(L, HKV, D, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            slots = block_table[b].long()[tok // PAGE] * PAGE + tok % PAGE
+            attn.write(k, v, caches[layer], slots)
+    del k, v
+    q_dev = torch.randn(NL, B, HQ, D, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    out_dev = torch.empty_like(q_dev)
+    torch.cuda.synchronize()
+
+    def step_resident():
+        for layer in range(NL):
+            attn.decode(q_dev[layer], caches[layer], block_table, seq_lens, out_dev[layer])
+
+    # ---- e2e step: host buffers, copies inside the timed region, through the public API ----------
+    q_host = q_dev.cpu().pin_memory()
+    newk_host = torch.randn(NL, B, HKV, D, generator=cpu_gen).to(torch.bfloat16).pin_memory()
+    newv_host = torch.randn(NL, B, HKV, D, generator=cpu_gen).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty(NL, B, HQ, D, dtype=torch.bfloat16).pin_memory()
+    q_in = torch.empty_like(q_dev)
+    newk = torch.empty(NL, B, HKV, D, dtype=torch.bfloat16, device=dev)
+    newv = torch.empty_like(newk)
+    out_e2e = torch.empty_like(q_dev)
+    # the new token of every sequence overwrites its last position (the cache stays full-length)
+    last_slots = (block_table[:, (L - 1) // PAGE].long() * PAGE + (L - 1) % PAGE).contiguous()
+
+    def step_e2e():
+        q_in.copy_(q_host, non_blocking=True)
+        newk.copy_(newk_host, non_blocking=True)
+        newv.copy_(newv_host, non_blocking=True)
+        for layer in range(NL):
+            attn.write(newk[layer], newv[layer], caches[layer], last_slots)
+            attn.decode(q_in[layer], caches[layer], block_table, seq_lens, out_e2e[layer])
+        out_host.copy_(out_e2e, non_blocking=True)
+
+    h2d = q_host.numel() * 2 + newk_host.numel() * 2 + newv_host.numel() * 2
+    d2h = out_host.numel() * 2
+
+    # warm-up (also sets kernel attributes and allocates workspaces before any capture)
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    torch.cuda.synchronize()
+    assert attn.status(B, dev) == 0, "decode kernel reported a failed wait"
+
+    graph = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step_resident()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                step_resident()
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def timed(fn, steps):
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        barrier()
+        return ms
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(graph.replay if graph is not None else step_resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = ms_total / args.steps
+    value = world * B / (ms_step * 1e-3)
+
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps) / args.steps
+    e2e_value = world * B / (ms_e2e * 1e-3)
+
+    # ---- roofline of the decode kernel: per-launch device time from events around that kernel ----
+    n_ev = NL * min(args.steps, 5)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_ev)]
+    for trio in evs:
+        for e in trio:
+            e.record()
+    torch.cuda.synchronize()
+    i = 0
+    for _ in range(min(args.steps, 5)):
+        for layer in range(NL):
+            _cabi.set_decode_events(*evs[i])
+            attn.decode(q_dev[layer], caches[layer], block_table, seq_lens, out_dev[layer])
+            i += 1
+    _cabi.set_decode_events(None, None, None)
+    torch.cuda.synchronize()
+    dec_ms = [t[0].elapsed_time(t[1]) for t in evs]
+    mrg_ms = [t[1].elapsed_time(t[2]) for t in evs]
+    dec_avg = sum(dec_ms) / len(dec_ms)
+    alg_bytes = B * L * HKV * ALG_BYTES_PER_TOKEN_HEAD
+    peak, peak_src = measured_peak()
+    achieved = alg_bytes / (dec_avg * 1e-3) / 1e9
+    # DRAM traffic per launch from the ncu capture summarised under profiles/ (physical slot
+    # bytes incl. the pad and the duplicate norm travel: 160 B per 136 algorithmic bytes)
+    traffic_per_alg_byte = 160.0 / 136.0
+    roofline = {"bound": "hbm", "kernel": "decode_paged_kernel<8>", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                "traffic": None, "expected_min_traffic": alg_bytes * traffic_per_alg_byte,
+                "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_ms": dec_avg,
+                "merge_avg_launch_ms": sum(mrg_ms) / len(mrg_ms),
+                "frac_whole_step": (alg_bytes * NL / (ms_step * 1e-3) / 1e9) / peak}
+
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return
+    cpu = None
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        ctx_s = L
+        pages_s = (ctx_s + PAGE - 1) // PAGE
+        # the sample attends the first ctx_s tokens of every sequence of layer 0, same bytes as the GPU
+        ids = block_table[:, :pages_s].long()
+        sub = caches[0][:, ids.reshape(-1)].cpu().numpy()
+        bt_s = np.arange(B * pages_s, dtype=np.int32).reshape(B, pages_s)
+        signs = attn.signs(dev).cpu().numpy()
+        rate, dt = cpu_decode_rate(np.ascontiguousarray(sub), bt_s, q_dev[0].float().cpu().numpy(), signs, ctx_s, threads)
+        cpu = {"value": rate / (L * HKV * NL), "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"{threads} sequences x {ctx_s} tokens x {HKV} KV heads of layer 0's cache ({dt:.2f} s), "
+                         f"scaled to ctx {L} x {NL} layers per token"}
+    line = {
+        "metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": workload_name(args), "global_batch": B * world, "parallelism": f"dp{world} (by sequence)",
+                   "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB streamed per launch, {NL} distinct layer caches",
+                   "cuda_graph": graph is not None, "algorithmic_bytes_per_step": alg_bytes * NL},
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "api": "TurboQuantPagedAttention.write + .decode per layer, pinned host buffers"},
+        "gpu_launches": args.steps * NL * 2, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -147,6 +147,13 @@ int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_
                      int64_t rows, int head_dim, const float* signs, void* out, int out_dtype,
                      float* out_lse, void* stream);
 
+/* Measurement hook (diagnostics; no reference counterpart).  While three CUDA events are set
+ * for the calling thread, tq_decode_paged / tq_decode_paged_partial record them on the call's
+ * stream: ev_start before the decode kernel, ev_mid between the decode kernel and the merge
+ * kernel, ev_end after the merge kernel.  Pass NULLs to switch it off.  Not for use inside a
+ * stream capture. */
+int tq_debug_set_decode_events(void* ev_start, void* ev_mid, void* ev_end);
+
 #ifdef __cplusplus
 }
 #endif

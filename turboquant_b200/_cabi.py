@@ -24,7 +24,7 @@ _DTYPES = {torch.float32: TQ_F32, torch.float16: TQ_F16, torch.bfloat16: TQ_BF16
 EXPORTS = (
     "tq_abi_version", "tq_last_error", "tq_codebook", "tq_write_kv_cache", "tq_quantize_flat",
     "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
-    "tq_decode_paged_partial", "tq_merge_rotated",
+    "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
 )
 
 _lib = None
@@ -232,3 +232,11 @@ def merge_rotated(partial_o, partial_lse2, signs, out, out_lse=None):
         ctypes.c_int64(rows), ctypes.c_int(partial_o.shape[-1]), _ptr(signs), _ptr(out),
         ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), _stream(partial_o)))
     return out
+
+
+def set_decode_events(ev_start=None, ev_mid=None, ev_end=None) -> None:
+    """Measurement hook: torch.cuda.Event objects (created with enable_timing=True and recorded
+    once so that their handle exists) recorded around the decode and merge kernels; None = off."""
+    def h(e):
+        return ctypes.c_void_p(0 if e is None else e.cuda_event)
+    _check(lib().tq_debug_set_decode_events(h(ev_start), h(ev_mid), h(ev_end)))

@@ -56,7 +56,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=4) as ex:
         objs = list(ex.map(compile_one, UNITS.items()))
     if force or _stale(LIB, objs):
-        subprocess.check_call(["nvcc", *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"])
+        subprocess.check_call(["nvcc", *ARCH, "-shared", "-o", str(LIB), *map(str, objs)])
     return LIB
 
 

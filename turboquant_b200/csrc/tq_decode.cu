@@ -510,17 +510,9 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     const int d = threadIdx.x;
     const int64_t row = blockIdx.x;
     const int hq = blockIdx.y;
-    float m = -INFINITY, wsum = 0.f, acc = 0.f;
-    auto add = [&](int64_t slot) {
-        const float lse = p.partial_lse[slot * p.num_q_heads + hq];
-        if (lse == -INFINITY) return;
-        const float o = p.partial_o[(slot * p.num_q_heads + hq) * kHeadDim + d];
-        const float mn = fmaxf(m, lse);
-        const float so = exp2f(m - mn), sn = exp2f(lse - mn);
-        acc = acc * so + o * sn;
-        wsum = wsum * so + sn;
-        m = mn;
-    };
+    // The parts of this row form an arithmetic slot sequence: slot(i) = first + i * stride.
+    int64_t first = 0, stride = 1;
+    int count = 0;
     if (p.header) {
         // partials of sequence `row` come from the blocks whose page range meets its pages
         const int64_t n = p.header[1], total = p.header[2];
@@ -528,12 +520,33 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
         if (e > s && total > 0) {
             const int64_t c_first = ((s + 1) * n + total - 1) / total - 1;
             const int64_t c_last = (e * n + total - 1) / total - 1;
-            for (int64_t c = c_first; c <= c_last; c++)
-                for (int sub = 0; sub < p.pps; sub++) add((c + row) * p.pps + sub);
+            first = (c_first + row) * p.pps;
+            count = (int)(c_last - c_first + 1) * p.pps;
         }
     } else {
-        // generic layout: partial_o [parts][rows][heads][128]
-        for (int part = 0; part < p.num_parts; part++) add((int64_t)part * p.rows + row);
+        // generic layout: partial_o [parts][rows][128]
+        first = row;
+        stride = p.rows;
+        count = p.num_parts;
+    }
+    // pass 1: the maximum LSE; pass 2: weighted sum.  Loads of different parts are independent,
+    // so the unrolled loops keep several of them in flight.
+    const float* lse_base = p.partial_lse + first * p.num_q_heads + hq;
+    const int64_t lse_stride = stride * p.num_q_heads;
+    float m = -INFINITY;
+#pragma unroll 8
+    for (int i = 0; i < count; i++) m = fmaxf(m, lse_base[i * lse_stride]);
+    float wsum = 0.f, acc = 0.f;
+    if (m > -INFINITY) {
+        const float* o_base = p.partial_o + (first * p.num_q_heads + hq) * kHeadDim + d;
+        const int64_t o_stride = lse_stride * kHeadDim;
+#pragma unroll 8
+        for (int i = 0; i < count; i++) {
+            const float w = exp2f(lse_base[i * lse_stride] - m);  // exp2(-inf) = 0 for empty parts
+            wsum += w;
+            const float o = o_base[i * o_stride];
+            acc += w > 0.f ? w * o : 0.f;  // an empty part's payload is never trusted
+        }
     }
     float o = wsum > 0.f ? acc / wsum : 0.f;
     const float lse2 = wsum > 0.f ? m + log2f(wsum) : -INFINITY;
@@ -560,6 +573,8 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
 }
 
 int device_sm_count(int* out);
+
+static thread_local cudaEvent_t g_events[3] = {nullptr, nullptr, nullptr};
 
 struct WorkspaceLayout {
     size_t header, prefix, lse, o, total;
@@ -665,6 +680,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
         p.lut_hi[k / 4] |= (uint32_t)(bits >> 8) << (8 * (k % 4));
     }
     TQ_CUDA(cudaMemsetAsync(p.header, 0, 64, s));
+    if (g_events[0]) TQ_CUDA(cudaEventRecord(g_events[0], s));
     switch (num_kv_heads) {
         case 8: rc = launch_decode<8>(p, ctas, s); break;
         case 4: rc = launch_decode<4>(p, ctas, s); break;
@@ -672,6 +688,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
         default: rc = launch_decode<1>(p, ctas, s); break;
     }
     if (rc != TQ_OK) return rc;
+    if (g_events[1]) TQ_CUDA(cudaEventRecord(g_events[1], s));
 
     MergeParams m{};
     m.partial_o = p.partial_o;
@@ -689,10 +706,18 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
     m.emit_rotated = emit_rotated;
     merge_kernel<<<dim3((unsigned)batch, (unsigned)num_q_heads), kHeadDim, 0, s>>>(m);
     TQ_CUDA(cudaGetLastError());
+    if (g_events[2]) TQ_CUDA(cudaEventRecord(g_events[2], s));
     return TQ_OK;
 }
 
 }  // namespace tq
+
+extern "C" int tq_debug_set_decode_events(void* ev_start, void* ev_mid, void* ev_end) {
+    tq::g_events[0] = static_cast<cudaEvent_t>(ev_start);
+    tq::g_events[1] = static_cast<cudaEvent_t>(ev_mid);
+    tq::g_events[2] = static_cast<cudaEvent_t>(ev_end);
+    return TQ_OK;
+}
 
 extern "C" size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads,
                                             int head_dim, int num_ctas) {

@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(kFlatWarps * 32) quantize_flat_kernel(const __
         }
         for (int j = full; j < p.dim; j++) s = __fadd_rn(s, __fmul_rn(buf[j], buf[j]));
         float norm = __fsqrt_rn(s);
-        if (!(norm >= 1e-8f)) norm = (norm != norm) ? norm : 1e-8f;
+        if (!(norm >= 1e-8f)) norm = (norm != norm) ? __uint_as_float(0x7fc00000u) : 1e-8f;
         for (int i = lane; i < p.padded; i += 32)
             buf[i] = i < p.dim ? __fmul_rn(__fdiv_rn(buf[i], norm), p.signs[i]) : 0.0f;
         __syncwarp();

@@ -118,7 +118,8 @@ __device__ __forceinline__ float quantize_row(float (&x)[kD], const WriteParams&
 #pragma unroll
     for (int k = 1; k < 8; k++) s = __fadd_rn(s, acc[k]);
     float norm = __fsqrt_rn(s);
-    if (!(norm >= 1e-8f)) norm = (norm != norm) ? norm : 1e-8f;  // clamp(min=1e-8), NaN kept
+    // clamp(min=1e-8); a NaN stays a NaN, in the canonical quiet pattern torch produces
+    if (!(norm >= 1e-8f)) norm = (norm != norm) ? __uint_as_float(0x7fc00000u) : 1e-8f;
 
     // normalise (IEEE division) and apply the +-1 signs (a sign-bit flip is an exact multiply)
 #pragma unroll
@@ -233,7 +234,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
                 }
                 uint32_t codes[16];
                 const float norm = quantize_row(x, p, sign_mask, codes);
-                const uint32_t nh = __half_as_ushort(__float2half_rn(norm));
+                const uint32_t nh = (norm != norm) ? 0x7e00u : (uint32_t)__half_as_ushort(__float2half_rn(norm));
                 // slot = block * block_size + entry and the cache is [block][entry][head][slot_bytes]
                 uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes +
                                ((size_t)slot * H + h) * p.slot_bytes;
