@@ -104,7 +104,7 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *   out          [batch][num_q_heads][head_dim]            out_dtype
  *   out_lse      optional fp32 [batch][num_q_heads], natural-log LSE of the scaled scores
  *   workspace    at least tq_decode_workspace_bytes(...) bytes, 256-byte aligned
- *   num_ctas     thread blocks to balance over; 0 = two per SM of the current device
+ *   num_ctas     thread blocks to balance over; 0 = one per SM of the current device
  *
  * Supported geometry: head_dim 128, block_size 16, slot_bytes 80, num_q_heads/num_kv_heads <= 8,
  * num_kv_heads in {1, 2, 4, 8}.

@@ -11,8 +11,11 @@ from pathlib import Path
 
 import torch
 
+import os
+
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "lib" / "libturboquant_b200.so"
+# TURBOQUANT_B200_LIB points at another build of the same library (e.g. an experimental variant)
+LIB_PATH = Path(os.environ.get("TURBOQUANT_B200_LIB", _PKG / "lib" / "libturboquant_b200.so"))
 
 TQ_F32, TQ_F16, TQ_BF16 = 0, 1, 2
 TQ_I32, TQ_I64 = 0, 1

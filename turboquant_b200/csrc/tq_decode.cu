@@ -15,15 +15,20 @@
 //     stages guarded by full/empty mbarriers, so DRAM sees contiguous 10 KB page reads.  Token
 //     rows are padded in shared memory (K: pitch = 64 mod 128, V: pitch = 16 mod 64) which makes
 //     the fragment loads below bank-conflict free.
-//   * Eight consumer warps, one per (KV head, page lane).  Packed codes go from shared memory
+//   * Sixteen consumer warps, one per (KV head, page lane).  Packed codes go from shared memory
 //     straight into mma.sync.m16n8k16 A-fragments: a thread's 16-byte K chunk is exactly its
 //     k-slices of the eight QK MMAs (the head-dim order inside the contraction is free because Q
 //     is loaded in the same permuted order), and V nibbles of two tokens are zipped into bytes
 //     so that one dequantized half2 is a (token, token+1) pair of the PV contraction.  Tokens
 //     sit on the M axis (16) and the GQA query heads on N (8): 2x padding instead of 4x.
-//   * Dequantization is an 8-entry magnitude lookup done with byte permutes (prmt) on four
-//     nibbles at a time plus a sign flip (the codebook is odd-symmetric); norms are folded into
-//     the scores (K) and into P (V), so there is no per-element multiply.
+//   * Dequantization is a shared-memory table lookup per code BYTE: entry v holds the half2
+//     {centroid(v & 15), centroid(v >> 4)}, replicated once per lane (256 x 32 x 4 B = 32 KB) so
+//     that every lookup of a warp is bank-conflict free.  The logic pipe of the SM runs at half
+//     the FP32 rate, and a pure byte-permute (prmt) dequantizer needs ~17 logic instructions per
+//     8 codes, which capped the first version of this kernel at 31% of HBM peak with the ALU
+//     pipe 65% busy; the lookup needs one permute, one integer multiply-add and one shared load
+//     per 2 codes.  Norms are folded into the scores (K) and into P (V), so there is no
+//     per-element multiply.
 //   * Online softmax in the base-2 domain with one consistent base everywhere; the running
 //     max is only raised when the tile max exceeds it by more than 2^6, which makes rescaling of
 //     the output accumulators rare.
@@ -44,18 +49,25 @@ namespace tq {
 constexpr int kHeadDim = 128;
 constexpr int kPageTokens = 16;
 constexpr int kSlotBytes = 80;
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 16;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;
+constexpr int kLutBytes = 256 * 32 * 4;
+constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxSegments = 96;
 constexpr int kMinPagesPerCta = 4;
 constexpr float kRaiseThreshold = 6.0f;  // log2 units
 
-constexpr int k_pitch(int H) {  // token pitch of K rows in shared memory: = 64 (mod 128)
-    int b = H * kSlotBytes;
+// Token pitch of K rows in shared memory: = 64 (mod 128), with 48 spare bytes because row t is
+// additionally shifted by 16 * ((t & 7) >> 1) bytes (k_row_offset).  The 64-mod-128 pitch keeps
+// the 16-byte fragment loads of a token pair conflict free; the extra shift spreads the eight
+// norm words read by one instruction over eight different banks.
+constexpr int k_pitch(int H) {
+    int b = H * kSlotBytes + 48;
     int pad = (64 - b % 128 + 128) % 128;
     return b + pad;
 }
+__host__ __device__ constexpr int k_row_offset(int t, int pitch) { return t * pitch + 16 * ((t & 7) >> 1); }
 constexpr int v_pitch(int H) {  // token pitch of V rows: = 16 (mod 64)
     int b = H * kSlotBytes;
     int pad = (16 - b % 64 + 64) % 64;
@@ -78,7 +90,8 @@ struct DecodeParams {
     int batch, num_q_heads, group, max_pages, q_dtype;
     float k_scale;  // (1/sqrt(128)) * sm_scale * log2(e): multiplies raw code-domain scores
     float v_scale;  // 1/sqrt(128): centroid scale folded into P
-    uint32_t lut_lo[2], lut_hi[2];  // fp16 low/high bytes of |centroid| for code 0..7
+    int num_stages;         // ring depth (3 or 4), chosen by the host from the shared-memory budget
+    uint16_t centroid_h[16];  // fp16 bit patterns of the N(0,1) centroids
 };
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
@@ -87,31 +100,21 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
 // Eight packed 4-bit codes (one 32-bit word) -> four half2 registers, one per byte:
 // r[j] = { low half: centroid(low nibble of byte j), high half: centroid(high nibble) } in units
-// of the N(0,1) codebook.  Codes 0..7 are the negative centroids in ascending order and
-// code 15-k = -code k, so the magnitude index is k for k < 8 and 15-k otherwise.
-__device__ __forceinline__ void dequant8(uint32_t w, const uint32_t (&lo_t)[2],
-                                         const uint32_t (&hi_t)[2], uint32_t (&r)[4]) {
-    const uint32_t u = (w >> 3) & 0x11111111u;   // bit3 of each nibble
-    const uint32_t sel = w ^ (u * 15u);          // fold: nibble -> magnitude index, bit3 cleared
-    const uint32_t w4 = w << 4;
-    {
-        const uint32_t lo = prmt(lo_t[0], lo_t[1], sel);
-        uint32_t hi = prmt(hi_t[0], hi_t[1], sel);
-        const uint32_t pm = prmt(w, w4, 0x9D8Cu);  // 0xFF per nibble 0..3 whose bit3 is set
-        hi ^= (~pm & 0x80808080u);                 // bit3 clear = negative centroid
-        r[0] = prmt(lo, hi, 0x5140u);
-        r[1] = prmt(lo, hi, 0x7362u);
-    }
-    {
-        const uint32_t sel2 = sel >> 16;
-        const uint32_t lo = prmt(lo_t[0], lo_t[1], sel2);
-        uint32_t hi = prmt(hi_t[0], hi_t[1], sel2);
-        const uint32_t pm = prmt(w, w4, 0xBFAEu);  // nibbles 4..7
-        hi ^= (~pm & 0x80808080u);
-        r[2] = prmt(lo, hi, 0x5140u);
-        r[3] = prmt(lo, hi, 0x7362u);
+// of the N(0,1) codebook.  lut_lane is the shared-memory address of this lane's column of the
+// table: entry v lives at lut_lane + 128 * v.
+__device__ __forceinline__ void dequant8(uint32_t w, uint32_t lut_lane, uint32_t (&r)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t v = prmt(w, 0u, 0x4440u | j);  // byte j, zero extended
+        r[j] = lds32(v * 128u + lut_lane);
     }
 }
 
@@ -153,36 +156,80 @@ __device__ __forceinline__ void seq_pages(const DecodeParams& p, int b, int& fir
     len_eff = (int)len;
 }
 
+// Shared-memory stage layout.  A stage holds kPPS pages; page lane `pp` has a K region and a V
+// region.  Two variants:
+//
+// HKV == 8 (a token row is 640 B = 0 mod 128): each page half is copied as four runs of four
+// tokens (2560 B per bulk copy; copies of 640 B were found to be limited by the copy engine's
+// request rate, 2.5 KB and larger are not).  Tokens of one run share their bank offset, so the
+// runs are placed at distinct offsets mod 128 (K: 0, 64, 16, 80; V: 0, 32, 64, 96) and MMA row
+// r is mapped to token row_token(r) such that every group of lanes served together reads from
+// different runs: rows (2p, 2p+1) of a K fragment load come from runs 64 bytes apart, the four
+// tokens of a V fragment load from four different runs.  Norm loads see a 2-way conflict.
+//
+// HKV < 8: one bulk copy per token row, padded pitches (K: 64 mod 128 plus a per-row shift that
+// spreads the norm words over the banks, V: 16 mod 64), identity row order.
 template <int HKV>
 struct DecodeSmem {
     static constexpr int kPPS = kConsumerWarps / HKV;  // pages per stage
+    static constexpr bool kRuns = HKV == 8;
+    static constexpr int kRowBytes = HKV * kSlotBytes;
     static constexpr int kKPitch = k_pitch(HKV);
     static constexpr int kVPitch = v_pitch(HKV);
-    static constexpr int kKBytes = kPPS * kPageTokens * kKPitch;
-    static constexpr int kVBytes = kPPS * kPageTokens * kVPitch;
+    static constexpr int kKRegion = kRuns ? 10496 : kPageTokens * kKPitch;  // per page lane
+    static constexpr int kVRegion = kRuns ? 10368 : kPageTokens * kVPitch;
+    static constexpr int kKBytes = kPPS * kKRegion;
+    static constexpr int kVBytes = kPPS * kVRegion;
     static constexpr int kStageBytes = kKBytes + kVBytes;
-    static constexpr int kQBytes = kConsumerWarps * 8 * kHeadDim * 2;  // rotated Q, fp16, per warp
-    static constexpr int kTotal = kStages * kStageBytes + kQBytes;
+    static constexpr int kCopiesPerPage = kRuns ? 8 : 32;
+    static constexpr int kCopyBytes = kRuns ? 4 * kRowBytes : kRowBytes;
+
+    // token (0..15 within its page) -> byte offset of its row inside the page lane's region
+    static __device__ __forceinline__ int k_off(int t) {
+        if (kRuns) {
+            const int q = t >> 2;
+            return q * 2560 + (t & 3) * kRowBytes + ((q & 1) ? 64 : 0) + ((q & 2) ? 144 : 0);  // 0, 2624, 5264, 7888
+        }
+        return k_row_offset(t, kKPitch);
+    }
+    static __device__ __forceinline__ int v_off(int t) {
+        if (kRuns) return (t >> 2) * 2592 + (t & 3) * kRowBytes;  // runs at 0, 2592, 5184, 7776
+        return t * kVPitch;
+    }
+    // MMA row / contraction slot r (0..15) -> token within the page
+    static __device__ __forceinline__ int row_token(int r) {
+        if (kRuns) {
+            const int r7 = r & 7;
+            const int q = (0x23013210 >> (4 * r7)) & 3;  // runs 0,1,2,3,1,0,3,2 for rows 0..7
+            return 4 * q + (r7 >> 2) + 2 * (r >> 3);
+        }
+        return r;
+    }
+    // rotated Q, fp16, `group` rows per warp
+    static constexpr int q_bytes(int group) { return kConsumerWarps * group * kHeadDim * 2; }
+    static constexpr int total(int stages, int group) { return stages * kStageBytes + kLutBytes + q_bytes(group); }
 };
 
 template <int HKV>
-__global__ void __launch_bounds__(kDecodeThreads, 2)
+__global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     using S = DecodeSmem<HKV>;
     constexpr int PPS = S::kPPS;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[kStages];
-    __shared__ __align__(8) uint64_t empty_bar[kStages];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
     __shared__ int seg_seq[kMaxSegments], seg_p0[kMaxSegments], seg_p1[kMaxSegments];
     __shared__ int num_segments, abort_flag;
     __shared__ int n_eff_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* stages = smem;
-    __half* q_s = reinterpret_cast<__half*>(smem + kStages * S::kStageBytes);
+    const int nstages = p.num_stages;
+    uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem + nstages * S::kStageBytes);
+    __half* q_s = reinterpret_cast<__half*>(smem + nstages * S::kStageBytes + kLutBytes);
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < kMaxStages; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kConsumerWarps);
         }
@@ -253,7 +300,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
 
     if (warp == kConsumerWarps) {
         // =============================== producer warp ======================================
-        int it = 0;
+        int st = 0, round = 0;
         for (int sg = 0; sg < nseg && !abort_flag; sg++) {
             const int b = seg_seq[sg];
             int first_page, npages_b, len_eff;
@@ -264,11 +311,10 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 const int mine = base + lane;
                 const int my_page = mine < p1 ? p.page_indices[tbl + first_page + mine] : 0;
                 const int cnt = (p1 - base) < 32 ? (p1 - base) : 32;
-                for (int j = 0; j < cnt; j += PPS, it++) {
-                    const int st = it % kStages;
+                for (int j = 0; j < cnt; j += PPS) {
                     const int np = (cnt - j) < PPS ? (cnt - j) : PPS;
-                    if (it >= kStages) {
-                        if (!mbar_wait(&empty_bar[st], ((it / kStages) - 1) & 1)) {
+                    if (round > 0) {
+                        if (!mbar_wait(&empty_bar[st], (round - 1) & 1)) {
                             abort_flag = 1;
                             atomicExch(&p.header[0], 1);
                         }
@@ -277,22 +323,23 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     uint8_t* sk = stages + (size_t)st * S::kStageBytes;
                     uint8_t* sv = sk + S::kKBytes;
                     if (lane == 0)
-                        mbar_arrive_expect_tx(&full_bar[st],
-                                              (uint32_t)(np * 2 * kPageTokens * HKV * kSlotBytes));
+                        mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(np * 2 * kPageTokens * S::kRowBytes));
                     __syncwarp();
 #pragma unroll
                     for (int pp = 0; pp < PPS; pp++) {
                         const int page = __shfl_sync(0xffffffffu, my_page, (j + pp) & 31);
-                        if (pp < np) {
-                            const int tok = lane & 15;
-                            const bool is_v = lane >= 16;
+                        if (pp < np && lane < S::kCopiesPerPage) {
+                            constexpr int kHalf = S::kCopiesPerPage / 2;
+                            const bool is_v = lane >= kHalf;
+                            const int tok = (lane % kHalf) * (kPageTokens / kHalf);  // first token of the copy
                             const uint8_t* src = p.kv_cache + (is_v ? p.slab_bytes : 0) +
-                                                 ((int64_t)page * kPageTokens + tok) * (HKV * kSlotBytes);
-                            uint8_t* dst = is_v ? sv + (pp * kPageTokens + tok) * S::kVPitch
-                                                : sk + (pp * kPageTokens + tok) * S::kKPitch;
-                            bulk_g2s(dst, src, HKV * kSlotBytes, &full_bar[st]);
+                                                 ((int64_t)page * kPageTokens + tok) * S::kRowBytes;
+                            uint8_t* dst = is_v ? sv + pp * S::kVRegion + S::v_off(tok)
+                                                : sk + pp * S::kKRegion + S::k_off(tok);
+                            bulk_g2s(dst, src, S::kCopyBytes, &full_bar[st]);
                         }
                     }
+                    if (++st == nstages) { st = 0; round++; }
                 }
                 if (abort_flag) break;
             }
@@ -304,11 +351,16 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     const int g = lane >> 2, tg = lane & 3;
     const int head = warp % HKV;   // KV head of this warp
     const int sub = warp / HKV;    // page lane inside a stage
-    __half* qw = q_s + warp * 8 * kHeadDim;
-    const uint32_t lut_lo[2] = {p.lut_lo[0], p.lut_lo[1]};
-    const uint32_t lut_hi[2] = {p.lut_hi[0], p.lut_hi[1]};
+    __half* qw = q_s + warp * p.group * kHeadDim;
+    // fill the lookup table: entry v, column c at lut_s[v * 32 + c] = {centroid(v & 15), centroid(v >> 4)}
+    for (int i = tid; i < 256 * 32; i += kConsumerWarps * 32) {
+        const int v = i >> 5;
+        lut_s[i] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");  // consumer warps only
+    const uint32_t lut_lane = smem_u32(lut_s) + 4u * lane;
 
-    int it = 0;
+    int st = 0, round = 0;
     for (int sg = 0; sg < nseg; sg++) {
         const int b = seg_seq[sg];
         int first_page, npages_b, len_eff;
@@ -317,9 +369,9 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
 
         // ---- rotate this KV head's query heads: signs -> FWHT -> 1/sqrt(128) -> fp16 -----------
         // lane holds elements 4*lane .. 4*lane+3; stages h=1,2 are local, h=4..64 by shuffle.
-        for (int r = 0; r < 8; r++) {
+        for (int r = 0; r < p.group; r++) {
             float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (r < p.group) {
+            {
                 const int64_t base = ((int64_t)b * p.num_q_heads + head * p.group + r) * kHeadDim + 4 * lane;
 #pragma unroll
                 for (int i = 0; i < 4; i++) v[i] = load_q(p.q, p.q_dtype, base + i) * p.signs[4 * lane + i];
@@ -349,7 +401,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             const uint4* src = reinterpret_cast<const uint4*>(qw + g * kHeadDim + 32 * tg);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const uint4 t = src[i];
+                const uint4 t = g < p.group ? src[i] : make_uint4(0u, 0u, 0u, 0u);  // padded heads
                 qf[4 * i] = t.x; qf[4 * i + 1] = t.y; qf[4 * i + 2] = t.z; qf[4 * i + 3] = t.w;
             }
         }
@@ -362,34 +414,38 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             for (int j = 0; j < 4; j++) o_acc[i][j] = 0.f;
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-        for (int pg = p0; pg < p1; pg += PPS, it++) {
-            const int st = it % kStages;
-            if (!mbar_wait(&full_bar[st], (it / kStages) & 1)) {
+        for (int pg = p0; pg < p1; pg += PPS) {
+            if (!mbar_wait(&full_bar[st], round & 1)) {
                 abort_flag = 1;
                 atomicExch(&p.header[0], 1);
             }
             if (abort_flag) return;
             const bool have = pg + sub < p1;  // this warp's page lane holds a page
             if (have) {
-                const uint8_t* sk = stages + (size_t)st * S::kStageBytes +
-                                    (size_t)sub * kPageTokens * S::kKPitch + head * kSlotBytes;
-                const uint8_t* sv = stages + (size_t)st * S::kStageBytes + S::kKBytes +
-                                    (size_t)sub * kPageTokens * S::kVPitch + head * kSlotBytes;
+                const uint8_t* sk = stages + (size_t)st * S::kStageBytes + sub * S::kKRegion + head * kSlotBytes;
+                const uint8_t* sv = stages + (size_t)st * S::kStageBytes + S::kKBytes + sub * S::kVRegion +
+                                    head * kSlotBytes;
                 const int tok0 = (first_page + pg + sub) * kPageTokens;  // first token of the page
+                // MMA rows g and g+8 of this lane, and its four contraction slots, as tokens
+                const int ta = S::row_token(g), tb = S::row_token(g + 8);
+                const int ra_off = S::k_off(ta), rb_off = S::k_off(tb);
+                const int va_off = S::v_off(ta), vb_off = S::v_off(tb);
+                const int t0 = S::row_token(2 * tg), t1 = S::row_token(2 * tg + 1);
+                const int t2 = S::row_token(2 * tg + 8), t3 = S::row_token(2 * tg + 9);
 
                 // ---- K codes and norms for tokens g and g+8 -------------------------------------
-                const uint4 ka = *reinterpret_cast<const uint4*>(sk + g * S::kKPitch + 16 * tg);
-                const uint4 kb = *reinterpret_cast<const uint4*>(sk + (g + 8) * S::kKPitch + 16 * tg);
-                const bool va = tok0 + g < len_eff, vb = tok0 + g + 8 < len_eff;
-                const float nka = __half2float(*reinterpret_cast<const __half*>(sk + g * S::kKPitch + 64));
-                const float nkb = __half2float(*reinterpret_cast<const __half*>(sk + (g + 8) * S::kKPitch + 64));
-                const float nva = __half2float(*reinterpret_cast<const __half*>(sv + g * S::kVPitch + 64));
-                const float nvb = __half2float(*reinterpret_cast<const __half*>(sv + (g + 8) * S::kVPitch + 64));
+                const uint4 ka = *reinterpret_cast<const uint4*>(sk + ra_off + 16 * tg);
+                const uint4 kb = *reinterpret_cast<const uint4*>(sk + rb_off + 16 * tg);
+                const bool va = tok0 + ta < len_eff, vb = tok0 + tb < len_eff;
+                const float nka = __half2float(*reinterpret_cast<const __half*>(sk + ra_off + 64));
+                const float nkb = __half2float(*reinterpret_cast<const __half*>(sk + rb_off + 64));
+                const float nva = __half2float(*reinterpret_cast<const __half*>(sv + va_off + 64));
+                const float nvb = __half2float(*reinterpret_cast<const __half*>(sv + vb_off + 64));
                 // ---- V codes: bytes 8g..8g+7 of tokens 2tg, 2tg+1, 2tg+8, 2tg+9 -------------------
-                const uint2 v0 = *reinterpret_cast<const uint2*>(sv + (2 * tg) * S::kVPitch + 8 * g);
-                const uint2 v1 = *reinterpret_cast<const uint2*>(sv + (2 * tg + 1) * S::kVPitch + 8 * g);
-                const uint2 v2 = *reinterpret_cast<const uint2*>(sv + (2 * tg + 8) * S::kVPitch + 8 * g);
-                const uint2 v3 = *reinterpret_cast<const uint2*>(sv + (2 * tg + 9) * S::kVPitch + 8 * g);
+                const uint2 v0 = *reinterpret_cast<const uint2*>(sv + S::v_off(t0) + 8 * g);
+                const uint2 v1 = *reinterpret_cast<const uint2*>(sv + S::v_off(t1) + 8 * g);
+                const uint2 v2 = *reinterpret_cast<const uint2*>(sv + S::v_off(t2) + 8 * g);
+                const uint2 v3 = *reinterpret_cast<const uint2*>(sv + S::v_off(t3) + 8 * g);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[st]);  // stage data is in registers now
 
@@ -400,8 +456,8 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
                     uint32_t ra[4], rb[4];
-                    dequant8(kwa[w], lut_lo, lut_hi, ra);
-                    dequant8(kwb[w], lut_lo, lut_hi, rb);
+                    dequant8(kwa[w], lut_lane, ra);
+                    dequant8(kwb[w], lut_lane, rb);
                     mma16816(s_acc, ra[0], rb[0], ra[1], rb[1], qf[4 * w], qf[4 * w + 1]);
                     mma16816(s_acc, ra[2], rb[2], ra[3], rb[3], qf[4 * w + 2], qf[4 * w + 3]);
                 }
@@ -446,10 +502,10 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     const uint32_t lo23 = (vw2[i] & 0x0F0F0F0Fu) | ((vw3[i] << 4) & 0xF0F0F0F0u);
                     const uint32_t hi23 = ((vw2[i] >> 4) & 0x0F0F0F0Fu) | (vw3[i] & 0xF0F0F0F0u);
                     uint32_t a_lo01[4], a_hi01[4], a_lo23[4], a_hi23[4];
-                    dequant8(lo01, lut_lo, lut_hi, a_lo01);
-                    dequant8(hi01, lut_lo, lut_hi, a_hi01);
-                    dequant8(lo23, lut_lo, lut_hi, a_lo23);
-                    dequant8(hi23, lut_lo, lut_hi, a_hi23);
+                    dequant8(lo01, lut_lane, a_lo01);
+                    dequant8(hi01, lut_lane, a_hi01);
+                    dequant8(lo23, lut_lane, a_lo23);
+                    dequant8(hi23, lut_lane, a_hi23);
 #pragma unroll
                     for (int j = 0; j < 4; j++)  // rows: g <- odd dim, g+8 <- even dim of byte 4i+j
                         mma16816(o_acc[4 * i + j], a_lo01[j], a_hi01[j], a_lo23[j], a_hi23[j], pb0, pb1);
@@ -458,6 +514,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[st]);
             }
+            if (++st == nstages) { st = 0; round++; }
         }
 
         // ---- finish the segment: normalize, write the partial and its base-2 LSE ----------------
@@ -602,16 +659,22 @@ static int resolve_ctas(int num_ctas, int* out) {
     int sms = 0;
     int rc = device_sm_count(&sms);
     if (rc != TQ_OK) return rc;
-    *out = 2 * sms;
+    *out = sms;  // one 17-warp thread block per SM
     return TQ_OK;
 }
 
 template <int HKV>
-static int launch_decode(const DecodeParams& p, int grid, cudaStream_t stream) {
-    constexpr int smem = DecodeSmem<HKV>::kTotal;
+static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
+    using S = DecodeSmem<HKV>;
+    // deepest ring that fits beside the table and the rotated queries (static smem: ~2 KB)
+    int stages = kMaxStages;
+    while (stages > 2 && S::total(stages, p.group) > kMaxSmem - 2048) stages--;
+    p.num_stages = stages;
+    const int smem = S::total(stages, p.group);
     static bool configured = false;
     if (!configured) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kMaxSmem - 2048));
         configured = true;
     }
     decode_paged_kernel<HKV><<<grid, kDecodeThreads, smem, stream>>>(p);
@@ -673,11 +736,9 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
     const double inv_sqrt_d = 1.0 / std::sqrt((double)kHeadDim);
     p.k_scale = (float)(inv_sqrt_d * (double)sm_scale * 1.4426950408889634);
     p.v_scale = (float)inv_sqrt_d;
-    for (int k = 0; k < 8; k++) {  // magnitude of code k (= -centroid k) as fp16 bytes
-        const __half h = __float2half_rn((float)(-kCentroidsN01_4bit[k]));
-        const uint16_t bits = *reinterpret_cast<const uint16_t*>(&h);
-        p.lut_lo[k / 4] |= (uint32_t)(bits & 0xff) << (8 * (k % 4));
-        p.lut_hi[k / 4] |= (uint32_t)(bits >> 8) << (8 * (k % 4));
+    for (int k = 0; k < 16; k++) {
+        const __half h = __float2half_rn((float)kCentroidsN01_4bit[k]);
+        p.centroid_h[k] = *reinterpret_cast<const uint16_t*>(&h);
     }
     TQ_CUDA(cudaMemsetAsync(p.header, 0, 64, s));
     if (g_events[0]) TQ_CUDA(cudaEventRecord(g_events[0], s));

@@ -66,7 +66,10 @@ class TurboQuantPagedAttention:
         return s
 
     def workspace(self, batch: int, device) -> torch.Tensor:
-        key = (torch.device(device), batch)
+        device = torch.device(device)
+        if device.type == "cuda" and device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        key = (device, batch)
         ws = self._workspaces.get(key)
         if ws is None:
             nbytes = _cabi.decode_workspace_bytes(batch, self.num_heads, self.num_kv_heads,
