@@ -12,7 +12,7 @@ tokens/s (batch x GPUs / step time).  With N > 1 every GPU runs its own batch (s
 independent: no collective on the data path, weak scaling).
 
 Prints ONE JSON line (rank 0).  `value` is timed on the device with inputs resident in HBM
-(CUDA-graph replay of the 36 launches pairs); `e2e` is the same step through the package's
+(CUDA-graph replay of the 36 launches); `e2e` is the same step through the package's
 public API with host buffers: the step's queries and new K/V rows are copied from pinned host
 memory, the new rows are written into the cache, and the outputs are copied back, all inside
 the timed region.  `roofline` is for the decode kernel alone, timed per launch with CUDA events

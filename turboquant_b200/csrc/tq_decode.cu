@@ -100,6 +100,21 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_half(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return __half2float(__ushort_as_half(v));
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -360,7 +375,21 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");  // consumer warps only
     const uint32_t lut_lane = smem_u32(lut_s) + 4u * lane;
 
+    // per-thread constants of the fragment loads (byte offsets inside a stage): MMA rows g and
+    // g+8 of this lane and its four contraction slots, mapped to tokens of the page
+    const int ta = S::row_token(g), tb = S::row_token(g + 8);
+    const uint32_t k_base = smem_u32(stages) + sub * S::kKRegion + head * kSlotBytes;
+    const uint32_t v_base = smem_u32(stages) + S::kKBytes + sub * S::kVRegion + head * kSlotBytes;
+    const uint32_t ka_addr = k_base + S::k_off(ta) + 16 * tg, kb_addr = k_base + S::k_off(tb) + 16 * tg;
+    const uint32_t nka_addr = k_base + S::k_off(ta) + 64, nkb_addr = k_base + S::k_off(tb) + 64;
+    const uint32_t nva_addr = v_base + S::v_off(ta) + 64, nvb_addr = v_base + S::v_off(tb) + 64;
+    const uint32_t v0_addr = v_base + S::v_off(S::row_token(2 * tg)) + 8 * g;
+    const uint32_t v1_addr = v_base + S::v_off(S::row_token(2 * tg + 1)) + 8 * g;
+    const uint32_t v2_addr = v_base + S::v_off(S::row_token(2 * tg + 8)) + 8 * g;
+    const uint32_t v3_addr = v_base + S::v_off(S::row_token(2 * tg + 9)) + 8 * g;
+
     int st = 0, round = 0;
+    uint32_t st_off = 0;  // st * kStageBytes
     for (int sg = 0; sg < nseg; sg++) {
         const int b = seg_seq[sg];
         int first_page, npages_b, len_eff;
@@ -422,30 +451,14 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             if (abort_flag) return;
             const bool have = pg + sub < p1;  // this warp's page lane holds a page
             if (have) {
-                const uint8_t* sk = stages + (size_t)st * S::kStageBytes + sub * S::kKRegion + head * kSlotBytes;
-                const uint8_t* sv = stages + (size_t)st * S::kStageBytes + S::kKBytes + sub * S::kVRegion +
-                                    head * kSlotBytes;
                 const int tok0 = (first_page + pg + sub) * kPageTokens;  // first token of the page
-                // MMA rows g and g+8 of this lane, and its four contraction slots, as tokens
-                const int ta = S::row_token(g), tb = S::row_token(g + 8);
-                const int ra_off = S::k_off(ta), rb_off = S::k_off(tb);
-                const int va_off = S::v_off(ta), vb_off = S::v_off(tb);
-                const int t0 = S::row_token(2 * tg), t1 = S::row_token(2 * tg + 1);
-                const int t2 = S::row_token(2 * tg + 8), t3 = S::row_token(2 * tg + 9);
-
-                // ---- K codes and norms for tokens g and g+8 -------------------------------------
-                const uint4 ka = *reinterpret_cast<const uint4*>(sk + ra_off + 16 * tg);
-                const uint4 kb = *reinterpret_cast<const uint4*>(sk + rb_off + 16 * tg);
+                // ---- K codes and norms for tokens ta, tb; V codes: bytes 8g..8g+7 of four tokens ----
+                const uint4 ka = lds128(ka_addr + st_off), kb = lds128(kb_addr + st_off);
                 const bool va = tok0 + ta < len_eff, vb = tok0 + tb < len_eff;
-                const float nka = __half2float(*reinterpret_cast<const __half*>(sk + ra_off + 64));
-                const float nkb = __half2float(*reinterpret_cast<const __half*>(sk + rb_off + 64));
-                const float nva = __half2float(*reinterpret_cast<const __half*>(sv + va_off + 64));
-                const float nvb = __half2float(*reinterpret_cast<const __half*>(sv + vb_off + 64));
-                // ---- V codes: bytes 8g..8g+7 of tokens 2tg, 2tg+1, 2tg+8, 2tg+9 -------------------
-                const uint2 v0 = *reinterpret_cast<const uint2*>(sv + S::v_off(t0) + 8 * g);
-                const uint2 v1 = *reinterpret_cast<const uint2*>(sv + S::v_off(t1) + 8 * g);
-                const uint2 v2 = *reinterpret_cast<const uint2*>(sv + S::v_off(t2) + 8 * g);
-                const uint2 v3 = *reinterpret_cast<const uint2*>(sv + S::v_off(t3) + 8 * g);
+                const float nka = lds_half(nka_addr + st_off), nkb = lds_half(nkb_addr + st_off);
+                const float nva = lds_half(nva_addr + st_off), nvb = lds_half(nvb_addr + st_off);
+                const uint2 v0 = lds64(v0_addr + st_off), v1 = lds64(v1_addr + st_off);
+                const uint2 v2 = lds64(v2_addr + st_off), v3 = lds64(v3_addr + st_off);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[st]);  // stage data is in registers now
 
@@ -514,7 +527,8 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[st]);
             }
-            if (++st == nstages) { st = 0; round++; }
+            st_off += S::kStageBytes;
+            if (++st == nstages) { st = 0; st_off = 0; round++; }
         }
 
         // ---- finish the segment: normalize, write the partial and its base-2 LSE ----------------
@@ -562,9 +576,17 @@ struct MergeParams {
     int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
 };
 
+// One block per (row, query head), four warps.  Warp w takes parts w, w+4, ...; lane l owns
+// rotated dims 4l..4l+3.  A warp first fetches the LSEs of its parts (lane i: its i-th part),
+// forms the weights, then fetches all its payloads with the loads in flight together: the
+// kernel is a handful of L2 round trips long, whatever the number of parts (up to 128 per
+// warp pass).  The four warps' results are combined in shared memory, then the inverse
+// rotation (FWHT, 1/sqrt(128), signs) runs across the 128 threads.
 __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__ MergeParams p) {
     __shared__ float buf[kHeadDim];
-    const int d = threadIdx.x;
+    __shared__ float part_acc[4][kHeadDim];
+    __shared__ float part_m[4], part_w[4];
+    const int d = threadIdx.x, warp = d >> 5, lane = d & 31;
     const int64_t row = blockIdx.x;
     const int hq = blockIdx.y;
     // The parts of this row form an arithmetic slot sequence: slot(i) = first + i * stride.
@@ -586,27 +608,56 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
         stride = p.rows;
         count = p.num_parts;
     }
-    // pass 1: the maximum LSE; pass 2: weighted sum.  Loads of different parts are independent,
-    // so the unrolled loops keep several of them in flight.
     const float* lse_base = p.partial_lse + first * p.num_q_heads + hq;
     const int64_t lse_stride = stride * p.num_q_heads;
-    float m = -INFINITY;
-#pragma unroll 8
-    for (int i = 0; i < count; i++) m = fmaxf(m, lse_base[i * lse_stride]);
-    float wsum = 0.f, acc = 0.f;
-    if (m > -INFINITY) {
-        const float* o_base = p.partial_o + (first * p.num_q_heads + hq) * kHeadDim + d;
-        const int64_t o_stride = lse_stride * kHeadDim;
-#pragma unroll 8
-        for (int i = 0; i < count; i++) {
-            const float w = exp2f(lse_base[i * lse_stride] - m);  // exp2(-inf) = 0 for empty parts
-            wsum += w;
-            const float o = o_base[i * o_stride];
-            acc += w > 0.f ? w * o : 0.f;  // an empty part's payload is never trusted
+    const float4* o_base = reinterpret_cast<const float4*>(p.partial_o + (first * p.num_q_heads + hq) * kHeadDim) + lane;
+    const int64_t o_stride = lse_stride * (kHeadDim / 4);
+    float m = -INFINITY, wsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i0 = warp; i0 < count; i0 += 128) {          // this warp's parts i0, i0+4, ..., 32 per pass
+        const int n = (count - i0 + 3) / 4 < 32 ? (count - i0 + 3) / 4 : 32;
+        const float my_lse = lane < n ? lse_base[(int64_t)(i0 + 4 * lane) * lse_stride] : -INFINITY;
+        float mx = my_lse;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(m, mx);
+        if (m_new == -INFINITY) continue;                 // every part so far is empty
+        const float rescale = exp2f(m - m_new);           // 0 on the first non-empty pass
+        const float my_w = exp2f(my_lse - m_new);         // exp2(-inf) = 0 for empty parts
+        float ws = my_w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+        wsum = wsum * rescale + ws;
+        acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
+        m = m_new;
+        for (int j0 = 0; j0 < n; j0 += 8) {
+            float4 o[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                o[j] = j0 + j < n ? o_base[(int64_t)(i0 + 4 * (j0 + j)) * o_stride] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float w = __shfl_sync(0xffffffffu, my_w, (j0 + j) & 31);
+                if (j0 + j < n && w > 0.f) {              // an empty part's payload is never trusted
+                    acc.x += w * o[j].x; acc.y += w * o[j].y; acc.z += w * o[j].z; acc.w += w * o[j].w;
+                }
+            }
         }
     }
-    float o = wsum > 0.f ? acc / wsum : 0.f;
-    const float lse2 = wsum > 0.f ? m + log2f(wsum) : -INFINITY;
+    reinterpret_cast<float4*>(part_acc[warp])[lane] = acc;
+    if (lane == 0) { part_m[warp] = m; part_w[warp] = wsum; }
+    __syncthreads();
+    float mm = fmaxf(fmaxf(part_m[0], part_m[1]), fmaxf(part_m[2], part_m[3]));
+    float o = 0.f, wtot = 0.f;
+    if (mm > -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float sc = exp2f(part_m[w] - mm);
+            if (sc > 0.f) { o += sc * part_acc[w][d]; wtot += sc * part_w[w]; }
+        }
+    }
+    o = wtot > 0.f ? o / wtot : 0.f;
+    const float lse2 = wtot > 0.f ? mm + log2f(wtot) : -INFINITY;
     const int64_t orow = row * p.num_q_heads + hq;
     if (p.emit_rotated) {
         reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
