@@ -148,6 +148,13 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     return d;
 }
 
+// 2^x, hardware approximation (2 ulp), flushes denormals; exp2(-inf) = 0
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -221,7 +228,10 @@ struct DecodeSmem {
         return r;
     }
     // rotated Q, fp16, `group` rows per warp
-    static constexpr int q_bytes(int group) { return kConsumerWarps * group * kHeadDim * 2; }
+    // per-warp scratch: rotated Q (fp16, `group` rows), reused to transpose the partial output
+    // (2 x 128 floats), hence at least four rows
+    static constexpr int q_rows(int group) { return group < 4 ? 4 : group; }
+    static constexpr int q_bytes(int group) { return kConsumerWarps * q_rows(group) * kHeadDim * 2; }
     static constexpr int total(int stages, int group) { return stages * kStageBytes + kLutBytes + q_bytes(group); }
 };
 
@@ -366,7 +376,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     const int g = lane >> 2, tg = lane & 3;
     const int head = warp % HKV;   // KV head of this warp
     const int sub = warp / HKV;    // page lane inside a stage
-    __half* qw = q_s + warp * p.group * kHeadDim;
+    __half* qw = q_s + warp * S::q_rows(p.group) * kHeadDim;
     // fill the lookup table: entry v, column c at lut_s[v * 32 + c] = {centroid(v & 15), centroid(v >> 4)}
     for (int i = tid; i < 256 * 32; i += kConsumerWarps * 32) {
         const int v = i >> 5;
@@ -398,30 +408,50 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
 
         // ---- rotate this KV head's query heads: signs -> FWHT -> 1/sqrt(128) -> fp16 -----------
         // lane holds elements 4*lane .. 4*lane+3; stages h=1,2 are local, h=4..64 by shuffle.
-        for (int r = 0; r < p.group; r++) {
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            {
-                const int64_t base = ((int64_t)b * p.num_q_heads + head * p.group + r) * kHeadDim + 4 * lane;
+        // The loads of up to four heads are issued together (one memory round trip per batch).
+        const float4 sg4 = reinterpret_cast<const float4*>(p.signs)[lane];
+        for (int r0 = 0; r0 < p.group; r0 += 4) {
+            float v[4][4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) v[i] = load_q(p.q, p.q_dtype, base + i) * p.signs[4 * lane + i];
-                float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
-                v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+            for (int rr = 0; rr < 4; rr++) {
+                const int r = r0 + rr < p.group ? r0 + rr : p.group - 1;
+                const int64_t base = ((int64_t)b * p.num_q_heads + head * p.group + r) * kHeadDim + 4 * lane;
+                if (p.q_dtype == TQ_BF16) {
+                    const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + base);
+                    v[rr][0] = __uint_as_float(t.x << 16); v[rr][1] = __uint_as_float(t.x & 0xffff0000u);
+                    v[rr][2] = __uint_as_float(t.y << 16); v[rr][3] = __uint_as_float(t.y & 0xffff0000u);
+                } else if (p.q_dtype == TQ_F16) {
+                    const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.q) + base);
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+                    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+                    v[rr][0] = lo.x; v[rr][1] = lo.y; v[rr][2] = hi.x; v[rr][3] = hi.y;
+                } else {
+                    const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.q) + base);
+                    v[rr][0] = t.x; v[rr][1] = t.y; v[rr][2] = t.z; v[rr][3] = t.w;
+                }
+            }
+#pragma unroll
+            for (int rr = 0; rr < 4; rr++) {
+                float* w = v[rr];
+                w[0] *= sg4.x; w[1] *= sg4.y; w[2] *= sg4.z; w[3] *= sg4.w;
+                const float a0 = w[0] + w[1], a1 = w[0] - w[1], a2 = w[2] + w[3], a3 = w[2] - w[3];
+                w[0] = a0 + a2; w[1] = a1 + a3; w[2] = a0 - a2; w[3] = a1 - a3;
 #pragma unroll
                 for (int d = 1; d < 32; d <<= 1) {
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        const float o = __shfl_xor_sync(0xffffffffu, v[i], d);
-                        v[i] = (lane & d) ? o - v[i] : v[i] + o;
+                        const float o = __shfl_xor_sync(0xffffffffu, w[i], d);
+                        w[i] = (lane & d) ? o - w[i] : w[i] + o;
                     }
                 }
-#pragma unroll
-                for (int i = 0; i < 4; i++) v[i] *= 0.08838834764831845f;
+                if (r0 + rr < p.group) {
+                    // stored with each (even, odd) pair swapped: a code byte dequantizes to
+                    // {low half: odd dim (low nibble), high half: even dim (high nibble)}
+                    __half2* dst = reinterpret_cast<__half2*>(qw + (r0 + rr) * kHeadDim + 4 * lane);
+                    dst[0] = __floats2half2_rn(w[1] * 0.08838834764831845f, w[0] * 0.08838834764831845f);
+                    dst[1] = __floats2half2_rn(w[3] * 0.08838834764831845f, w[2] * 0.08838834764831845f);
+                }
             }
-            // stored with each (even, odd) pair swapped: a code byte dequantizes to
-            // {low half: odd dim (low nibble), high half: even dim (high nibble)}
-            __half2* dst = reinterpret_cast<__half2*>(qw + r * kHeadDim + 4 * lane);
-            dst[0] = __floats2half2_rn(v[1], v[0]);
-            dst[1] = __floats2half2_rn(v[3], v[2]);
         }
         __syncwarp();
         // B fragments of the eight QK MMAs: pairs 16*tg .. 16*tg+15 of query head g
@@ -486,7 +516,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 }
                 const bool raise0 = mx0 > m0 + kRaiseThreshold, raise1 = mx1 > m1 + kRaiseThreshold;
                 if (__any_sync(0xffffffffu, raise0 || raise1)) {
-                    const float c0 = raise0 ? exp2f(m0 - mx0) : 1.f, c1 = raise1 ? exp2f(m1 - mx1) : 1.f;
+                    const float c0 = raise0 ? fast_exp2(m0 - mx0) : 1.f, c1 = raise1 ? fast_exp2(m1 - mx1) : 1.f;
                     if (raise0) m0 = mx0;
                     if (raise1) m1 = mx1;
                     l0 *= c0;
@@ -496,7 +526,8 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                         o_acc[i][0] *= c0; o_acc[i][1] *= c1; o_acc[i][2] *= c0; o_acc[i][3] *= c1;
                     }
                 }
-                const float e0 = exp2f(x0 - m0), e1 = exp2f(x1 - m1), e2 = exp2f(x2 - m0), e3 = exp2f(x3 - m1);
+                const float e0 = fast_exp2(x0 - m0), e1 = fast_exp2(x1 - m1);
+                const float e2 = fast_exp2(x2 - m0), e3 = fast_exp2(x3 - m1);
                 l0 += e0 + e2;
                 l1 += e1 + e3;
                 const float vfa = va ? nva * p.v_scale : 0.f, vfb = vb ? nvb * p.v_scale : 0.f;
@@ -541,18 +572,28 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         const int64_t slot = ((int64_t)blockIdx.x + b) * PPS + sub;
         const int h0 = 2 * tg, h1 = 2 * tg + 1;
         float* po = p.partial_o + (slot * p.num_q_heads + head * p.group) * kHeadDim;
+        // Two query heads at a time go through the warp's scratch (2 x 128 floats) so that the
+        // global stores are full 512-byte rows instead of scattered words (which cost 7 us per
+        // segment): the lanes with tg == pass own heads 2*pass and 2*pass+1.
+        float* scr = reinterpret_cast<float*>(qw);
+        for (int pass = 0; 2 * pass < p.group; pass++) {
+            __syncwarp();
+            if (tg == pass) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int d_odd = 16 * g + 2 * i + 1, d_even = 16 * g + 2 * i;
-            if (h0 < p.group) {
-                po[h0 * kHeadDim + d_odd] = o_acc[i][0] * inv0;
-                po[h0 * kHeadDim + d_even] = o_acc[i][2] * inv0;
+                for (int i = 0; i < 8; i++) {
+                    const int d_even = 16 * g + 2 * i;
+                    *reinterpret_cast<float2*>(scr + d_even) = make_float2(o_acc[i][2] * inv0, o_acc[i][0] * inv0);
+                    *reinterpret_cast<float2*>(scr + kHeadDim + d_even) =
+                        make_float2(o_acc[i][3] * inv1, o_acc[i][1] * inv1);
+                }
             }
-            if (h1 < p.group) {
-                po[h1 * kHeadDim + d_odd] = o_acc[i][1] * inv1;
-                po[h1 * kHeadDim + d_even] = o_acc[i][3] * inv1;
-            }
+            __syncwarp();
+            const float4 r0 = reinterpret_cast<const float4*>(scr)[lane];
+            const float4 r1 = reinterpret_cast<const float4*>(scr + kHeadDim)[lane];
+            reinterpret_cast<float4*>(po + (2 * pass) * kHeadDim)[lane] = r0;
+            if (2 * pass + 1 < p.group) reinterpret_cast<float4*>(po + (2 * pass + 1) * kHeadDim)[lane] = r1;
         }
+        __syncwarp();
         if (g == 0) {
             float* pl = p.partial_lse + slot * p.num_q_heads + head * p.group;
             if (h0 < p.group) pl[h0] = l0 > 0.f ? m0 + log2f(l0) : -INFINITY;
