@@ -763,11 +763,13 @@ static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
     while (stages > 2 && S::total(stages, p.group) > kMaxSmem - 2048) stages--;
     p.num_stages = stages;
     const int smem = S::total(stages, p.group);
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};  // the attribute is per device
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kMaxSmem - 2048));
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     decode_paged_kernel<HKV><<<grid, kDecodeThreads, smem, stream>>>(p);
     TQ_CUDA(cudaGetLastError());

@@ -256,11 +256,13 @@ template <typename T>
 static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream) {
     constexpr int kPitch = RowLoad<T>::kRowBytes + 16;
     const size_t smem = (size_t)2 * kWriteThreads * kPitch;
-    static bool configured = false;  // per template instance
-    if (!configured) {
+    static bool configured[64] = {};  // per template instance and device
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         TQ_CUDA(cudaFuncSetAttribute(write_kv_cache_kernel<T>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t rows = p.num_tokens * p.num_kv_heads;
     const int64_t tiles = 2 * ((rows + kWriteThreads - 1) / kWriteThreads);
