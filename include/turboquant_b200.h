@@ -147,6 +147,28 @@ int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_
                      int64_t rows, int head_dim, const float* signs, void* out, int out_dtype,
                      float* out_lse, void* stream);
 
+/* tq_decode_paged for callers that cannot hand over (or create) a workspace: an engine plugin
+ * whose device memory pool is already fully assigned, or a caller on a path where cudaMalloc is
+ * not allowed.  It has no counterpart in the reference (there the caller always allocates the
+ * split-KV workspaces, turboquant/vllm_backend_fused.py:158-215).  The split-KV scratch is a
+ * fixed array of TQ_STATIC_SCRATCH_BYTES (8 MiB) inside the library image; every GPU
+ * that loads the library holds it until the process exits.  Arguments and results are those of
+ * tq_decode_paged without the workspace pair.
+ *   - Calls whose scratch need (it grows with batch, num_q_heads and num_ctas; see
+ *     tq_decode_workspace_bytes) exceeds the array fail with TQ_ERR_WORKSPACE and a message; at
+ *     32 query heads that is a batch of roughly 170 with one block per SM on a 148-SM part.
+ *   - The first call on each device looks up the array's device address; make that call before
+ *     starting any stream capture.  No call allocates or frees device memory.
+ *   - All calls on one device share the array: the part that has to start at zero is cleared on
+ *     the stream at every call, the rest is overwritten before it is read.  Two calls that can
+ *     overlap on the GPU (different streams) race on it; keep them on one stream or order them. */
+#define TQ_STATIC_SCRATCH_BYTES (8u << 20)
+int tq_decode_paged_static(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
+                           int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,
+                           int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
+                           int max_pages, const int32_t* seq_lens, const float* signs, float sm_scale,
+                           void* out, int out_dtype, float* out_lse, int num_ctas, void* stream);
+
 /* Measurement hook (diagnostics; no reference counterpart).  While three CUDA events are set
  * for the calling thread, tq_decode_paged / tq_decode_paged_partial record them on the call's
  * stream: ev_start before the decode kernel, ev_mid between the decode kernel and the merge

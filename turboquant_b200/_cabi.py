@@ -21,6 +21,7 @@ TQ_F32, TQ_F16, TQ_BF16 = 0, 1, 2
 TQ_I32, TQ_I64 = 0, 1
 TQ_PACK_LOW_FIRST, TQ_PACK_CACHE = 0, 1
 TQ_WRITE_ZERO_PAD = 1
+STATIC_SCRATCH_BYTES = 8 << 20  # TQ_STATIC_SCRATCH_BYTES
 
 _DTYPES = {torch.float32: TQ_F32, torch.float16: TQ_F16, torch.bfloat16: TQ_BF16}
 
@@ -28,6 +29,7 @@ EXPORTS = (
     "tq_abi_version", "tq_last_error", "tq_codebook", "tq_write_kv_cache", "tq_quantize_flat",
     "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
     "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
+    "tq_decode_paged_static",
 )
 
 _lib = None
@@ -243,3 +245,22 @@ def set_decode_events(ev_start=None, ev_mid=None, ev_end=None) -> None:
     def h(e):
         return ctypes.c_void_p(0 if e is None else e.cuda_event)
     _check(lib().tq_debug_set_decode_events(h(ev_start), h(ev_mid), h(ev_end)))
+
+
+def decode_paged_static(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, out,
+                        page_indptr=None, max_pages: int | None = None, out_lse=None, num_ctas: int = 0):
+    """``decode_paged`` for callers that may not allocate: the split-KV scratch is the fixed array
+    built into the library (8 MiB per GPU), so no workspace tensor is passed.  Raises when the call
+    would need more scratch than that.  Calls on one device share the array and must not overlap."""
+    if max_pages is None:
+        max_pages = page_indices.shape[-1] if page_indices.dim() == 2 else 0
+    _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs)
+    B, Hq, D = q.shape
+    _, nb, bs, H, ebs = kv_cache.shape
+    _check(lib().tq_decode_paged_static(
+        _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(Hq), ctypes.c_int(H),
+        ctypes.c_int(D), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(ebs),
+        _ptr(page_indices), _ptr(page_indptr), ctypes.c_int(max_pages), _ptr(seq_lens), _ptr(signs),
+        ctypes.c_float(sm_scale), _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse),
+        ctypes.c_int(num_ctas), _stream(q)))
+    return out

@@ -933,3 +933,65 @@ extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse
     TQ_CUDA(cudaGetLastError());
     return TQ_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode without any caller-side or library-side allocation.
+//
+// Some hosts of this library may not create device memory at the time they call it: code that
+// runs inside an engine whose memory pool has already been handed out in full, a plugin that is
+// only given the tensors of the model and may not grow the footprint, or a caller on a path
+// where cudaMalloc (an implicitly synchronising call) is forbidden.  For them the split-KV
+// scratch (partials, LSEs, the small header) lives in a fixed array inside the library image.
+// Every GPU that loads the library carries these kStaticScratchBytes until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace tq {
+constexpr size_t kStaticScratchBytes = TQ_STATIC_SCRATCH_BYTES;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address; the
+// address is looked up once per device (with that device current) and cached.
+static int static_scratch_pointer(void** out) {
+    static void* cached[64] = {};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    TQ_REQUIRE(dev >= 0 && dev < 64, TQ_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        TQ_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        TQ_REQUIRE(ptr != nullptr, TQ_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return TQ_OK;
+}
+}  // namespace tq
+
+extern "C" int tq_decode_paged_static(const void* q, int q_dtype, int batch, int num_q_heads,
+                                      int num_kv_heads, int head_dim, const void* kv_cache,
+                                      int64_t num_blocks, int block_size, int slot_bytes,
+                                      const int32_t* page_indices, const int32_t* page_indptr,
+                                      int max_pages, const int32_t* seq_lens, const float* signs,
+                                      float sm_scale, void* out, int out_dtype, float* out_lse,
+                                      int num_ctas, void* stream) {
+    using namespace tq;
+    TQ_REQUIRE(batch >= 0, TQ_ERR_INVALID, "negative batch");
+    if (batch == 0) return TQ_OK;
+    TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8,
+               TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4 or 8, got %d", num_kv_heads);
+    TQ_REQUIRE(num_q_heads > 0, TQ_ERR_INVALID, "num_q_heads must be positive");
+    int ctas = 0;
+    int rc = resolve_ctas(num_ctas, &ctas);
+    if (rc != TQ_OK) return rc;
+    const size_t need = workspace_layout(batch, num_q_heads, num_kv_heads, ctas).total;
+    TQ_REQUIRE(need <= kStaticScratchBytes, TQ_ERR_WORKSPACE,
+               "this call needs %zu bytes of split-KV scratch but the built-in scratch holds %zu: lower batch "
+               "(%d), num_q_heads (%d) or num_ctas (%d), or use tq_decode_paged with your own workspace",
+               need, kStaticScratchBytes, batch, num_q_heads, ctas);
+    void* scratch = nullptr;
+    rc = static_scratch_pointer(&scratch);
+    if (rc != TQ_OK) return rc;
+    return decode_common(q, q_dtype, batch, num_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks,
+                         block_size, slot_bytes, page_indices, page_indptr, max_pages, seq_lens, 0, -1,
+                         signs, sm_scale, scratch, kStaticScratchBytes, out, out_dtype, out_lse, 0, ctas,
+                         stream);
+}
