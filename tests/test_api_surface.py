@@ -1,0 +1,138 @@
+"""Host-side logic of the reference-facing surface (no GPU): presets, packing, sharding helpers,
+op schemas, plugin registration, and the KV-axis split + LSE merge across two gloo ranks."""
+import math
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_tile_pack_known_answer_and_roundtrip():
+    from turboquant_b200.tile import pack_4bit, unpack_4bit
+    assert pack_4bit(torch.tensor([0x0A, 0x05], dtype=torch.uint8)).tolist() == [0xA5]
+    idx = torch.randint(0, 16, (7, 128), dtype=torch.uint8)
+    assert torch.equal(unpack_4bit(pack_4bit(idx), 128), idx)
+
+
+def test_kernel_config_presets():
+    from turboquant_b200.kernel_config import MODEL_PRESETS, ModelConfig, compute_kernel_config
+    assert len(MODEL_PRESETS) == 22
+    q = MODEL_PRESETS["qwen3-8b"]
+    assert (q.num_qo_heads, q.num_kv_heads, q.head_dim, q.gqa_ratio, q.padded_dim) == (32, 8, 128, 4, 128)
+    kc = compute_kernel_config(q)
+    assert kc.supported and kc.threads_per_block == 544 and kc.pages_per_stage == 2 and kc.stages == 4
+    assert kc.stages * kc.stage_bytes + 32768 + 16384 < 227 * 1024
+    assert compute_kernel_config(ModelConfig(64, 8, 128)).stages == 3          # 8 query heads per KV head
+    assert compute_kernel_config(ModelConfig(16, 4, 128)).pages_per_stage == 4  # a TP shard with 4 KV heads
+    assert not compute_kernel_config(MODEL_PRESETS["gemma-2-9b"]).supported    # head_dim 256: not built yet
+    assert not compute_kernel_config(MODEL_PRESETS["llama-2-7b"]).supported    # 32 KV heads on one GPU
+
+
+def test_sequence_sharding_is_balanced_and_complete():
+    from turboquant_b200 import synthetic
+    from turboquant_b200.parallel import kv_ranges, shard_sequences
+    lens = synthetic.mixed_lengths(seed=3, n=64)
+    assert min(lens) >= 512 and max(lens) <= 131072
+    for world in (1, 2, 4, 8):
+        shards = shard_sequences(lens, world)
+        assert sorted(i for s in shards for i in s) == list(range(64))
+        loads = [sum(lens[i] for i in s) for s in shards]
+        assert max(loads) / (sum(loads) / world) < 1.25
+    r = kv_ranges(1_048_576, 8)
+    assert r[0] == (0, 131072) and r[-1][1] == 1_048_576 and all(a % 16 == 0 for a, _ in r)
+    r = kv_ranges(1000, 3)
+    assert r[0][0] == 0 and r[-1][1] == 1000 and all(r[i][1] == r[i + 1][0] for i in range(2))
+
+
+def test_ops_are_registered_with_reference_schemas():
+    from turboquant_b200 import ops  # noqa: F401
+    w = torch.ops.turboquant_write.quantize_write_kv_cache.default._schema
+    assert [a.name for a in w.arguments] == ["kv_cache", "key", "value", "signs", "slot_mapping", "head_dim",
+                                             "padded_dim"]
+    assert w.arguments[0].alias_info is not None and w.arguments[0].alias_info.is_write
+    d = torch.ops.turboquant_v5.decode_v5_from_cache_paged_splitkv_ws.default._schema
+    assert len(d.arguments) == 23 and d.arguments[-1].name == "num_splits"
+    assert len(torch.ops.turboquant_v5.decode_v5_from_cache_ws.default._schema.arguments) == 20
+    with pytest.raises(Exception):      # CUDA-only implementation: CPU tensors are refused by the dispatcher
+        torch.ops.turboquant_write.quantize_write_kv_cache(torch.zeros(2, 1, 16, 8, 80, dtype=torch.uint8),
+                                                           torch.zeros(1, 8, 128), torch.zeros(1, 8, 128),
+                                                           torch.ones(128), torch.zeros(1, dtype=torch.int64), 128, 128)
+
+
+def test_dispatcher_refuses_non_blackwell(monkeypatch):
+    from turboquant_b200 import decoder_dispatch as dd
+    dd.pick_decode_op.cache_clear()
+    monkeypatch.setattr(dd, "_device_capability", lambda: (8, 0))
+    with pytest.raises(RuntimeError, match="sm_100a"):
+        dd.pick_decode_op()
+    dd.pick_decode_op.cache_clear()
+    monkeypatch.setattr(dd, "_device_capability", lambda: (10, 0))
+    op, name = dd.pick_decode_op()
+    assert name == dd.KERNEL_NAME and op is torch.ops.turboquant_v5.decode_v5_from_cache_paged_splitkv_ws
+    dd.pick_decode_op.cache_clear()
+    monkeypatch.setenv("TQ_FORCE_KERNEL", "v5")
+    with pytest.raises(ValueError, match="not recognised"):
+        dd.pick_decode_op()
+    dd.pick_decode_op.cache_clear()
+
+
+def test_vllm_plugin_registers_custom_backend():
+    pytest.importorskip("vllm")
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from turboquant_b200 import vllm_plugin\n"
+            "vllm_plugin.register(); vllm_plugin.register()\n"
+            "from vllm.v1.attention.backends.registry import AttentionBackendEnum\n"
+            "c = AttentionBackendEnum.CUSTOM.get_class()\n"
+            "assert c.get_name() == 'CUSTOM' and c.forward_includes_kv_cache_update is False\n"
+            "assert c.get_kv_cache_shape(10, 16, 8, 128, 'fp8') == (2, 10, 16, 8, 80)\n"
+            "assert c.get_kv_cache_page_size(16, 8, 128, None, 'fp8') == 20480\n"
+            "assert c.get_kv_cache_page_size(16, 8, 128, None, 'auto') is None\n"
+            "assert c.supports_kv_cache_dtype('fp8') and c.get_impl_cls().__name__ == 'TurboQuantFusedImpl'\n"
+            "assert c.get_builder_cls().__name__ == 'TurboQuantMetadataBuilder'\n"
+            "print('ok')\n") % str(ROOT)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd="/tmp", timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+_RANK_SCRIPT = r"""
+import math, os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np, torch, torch.distributed as dist
+from oracle import tq_oracle
+from turboquant_b200 import synthetic
+from turboquant_b200.parallel import all_gather_partials, kv_ranges
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%(port)d", rank=int(sys.argv[1]), world_size=2)
+rank = dist.get_rank()
+case = synthetic.decode_case(seed=90, seq_lens=[777], dtype=torch.float16, num_q_rows=1)
+signs = synthetic.make_signs().numpy()
+cache = np.zeros((2, case.num_blocks, 16, 8, 80), np.uint8)
+tq_oracle.write_kv_cache(cache, case.k.float().numpy(), case.v.float().numpy(), signs, case.slot_mapping.numpy(), 128)
+args = (case.q.float().numpy(), cache, case.block_table.numpy(), case.seq_lens.numpy(), signs, 1 / math.sqrt(128))
+a, b = kv_ranges(777, 2)[rank]                      # this rank's contiguous, page-aligned KV range
+o, lse = tq_oracle.decode_paged(*args, kv_begin=a, kv_end=b, return_lse=True)
+go, gl = all_gather_partials(torch.from_numpy(o), torch.from_numpy(lse))
+merged, _ = tq_oracle.merge_partials(go.numpy(), gl.numpy())
+full = tq_oracle.decode_paged(*args)
+assert np.abs(merged - full).max() < 2e-6, np.abs(merged - full).max()
+dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def test_kv_axis_split_across_two_gloo_ranks(oracle, tmp_path):
+    """Config-4 logic at small size on CPU ranks: each rank attends its KV range, partials are
+    all-gathered, the LSE merge reproduces the unsplit result."""
+    port = 29500 + os.getpid() % 400
+    script = tmp_path / "rank.py"
+    script.write_text(_RANK_SCRIPT % {"root": str(ROOT), "port": port})
+    procs = [subprocess.Popen([sys.executable, str(script), str(r)], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                              text=True) for r in range(2)]
+    for r, p in enumerate(procs):
+        out, err = p.communicate(timeout=240)
+        assert p.returncode == 0 and f"rank {r} ok" in out, err[-2000:]
