@@ -9,10 +9,18 @@
 // from double, strict "boundary < value" tie rule.  This translation unit is compiled with
 // -fmad=false and without fast-math.
 //
-// Mapping: one thread owns one 128-element row, so every butterfly is register-local.  Rows of a
-// 128-row tile are staged into shared memory by per-row bulk async copies (each thread issues
-// the copy of its own row, all complete on one mbarrier); a 16-byte row pad keeps the 16-byte
-// shared loads conflict-free.  Two buffers overlap the copy of the next tile with the math.
+// Mapping: four lanes own one 128-element row; lane m holds elements 8j + 2m + e (j = 0..15,
+// e = 0, 1), i.e. exactly two of the eight norm accumulators and both nibbles of code byte
+// 4j + m.  Butterfly stages 1 and 8..64 are register-local, stages 2 and 4 are two shuffles per
+// element.  Rows of a 64-row tile are staged into shared memory by per-row bulk async copies
+// (one mbarrier per buffer, two buffers); the 16-byte row pad makes the 4-byte loads of a warp
+// (8 rows x 16 bytes) conflict free.  Everything per element runs on the FP32 pipe where it can
+// (the integer/logic pipe has half its rate):
+//   * x / norm is q = x*r, e = fma(-q, norm, x), q' = fma(e, r, q) with r the correctly rounded
+//     reciprocal, which equals the IEEE quotient whenever the intermediates stay normal and the
+//     norm's significand is not all ones (checked per row; otherwise the row takes the division
+//     instruction);
+//   * the code index is a sum of saturated FMAs, sat((|y| - b_j) * 2^40), one per boundary.
 #include <cmath>
 #include <cstring>
 
@@ -20,7 +28,8 @@
 
 namespace tq {
 
-constexpr int kWriteThreads = 128;
+constexpr int kWriteThreads = 256;
+constexpr int kTileRows = kWriteThreads / 4;  // four lanes per row
 constexpr int kD = 128;
 
 struct WriteParams {
@@ -35,140 +44,78 @@ struct WriteParams {
     int slot_bytes;
     int slot_is_i64;
     int zero_pad;
-    const float* signs;           // [128] +-1, device
-    uint32_t pos_bnd_bits[7];     // fp32 bit patterns of boundaries 8..14 (the positive ones)
-    float fwht_scale;             // (float)(1/sqrt(128))
+    const float* signs;       // [128] +-1, device
+    float neg_bnd_big[7];     // -(positive boundary j) * 2^40
+    float fwht_scale;         // (float)(1/sqrt(128))
 };
 
-// Number of boundaries strictly below y, for the symmetric 15-boundary table
-// (boundary 7 is exactly 0, boundary 14-i = -boundary i).  With a = |y| as an integer,
-// y > 0: 8 + #{pb < a};  y <= 0: 7 - #{pb <= a} = 7 - #{pb < a + 1}.  A NaN goes to 15 like
-// torch.bucketize's lower bound.
-__device__ __forceinline__ uint32_t code4(float y, const uint32_t (&pb)[7]) {
-    const uint32_t yb = __float_as_uint(y);
-    const bool pos = !(y <= 0.0f);
-    const uint32_t a = (yb & 0x7fffffffu) + (pos ? 0u : 1u);
-    const bool c2 = a > pb[3];
-    const uint32_t t1 = c2 ? pb[5] : pb[1];
-    const bool c1 = a > t1;
-    const uint32_t t0 = c2 ? (c1 ? pb[6] : pb[4]) : (c1 ? pb[2] : pb[0]);
-    const bool c0 = a > t0;
-    const uint32_t m = (c2 ? 4u : 0u) + (c1 ? 2u : 0u) + (c0 ? 1u : 0u);
-    return pos ? 8u + m : 7u - m;
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Code of y among the 15 symmetric boundaries (boundary 7 is 0, boundary 14-i = -boundary i) as
+// a float in 0..15: the number of boundaries strictly below y.  With a = |y|:
+//   y > 0 : 8 + #{pb_j < a};   y <= 0 : 7 - #{pb_j <= a} = 7 - #{pb_j < a + 1ulp}.
+// Each comparison is sat((a - pb_j) * 2^40): the FMA forms the difference exactly, a positive
+// difference is at least one ulp of pb_j (> 2^-30), so it saturates to exactly 1.
+__device__ __forceinline__ float code_f(float y, const float (&nb)[7]) {
+    const bool pos = y > 0.0f;
+    const float a = __uint_as_float((__float_as_uint(y) & 0x7fffffffu) + (pos ? 0u : 1u));
+    constexpr float kBig = 1099511627776.0f;  // 2^40
+    float m = fma_sat(a, kBig, nb[0]);
+#pragma unroll
+    for (int j = 1; j < 7; j++) m = __fadd_rn(m, fma_sat(a, kBig, nb[j]));
+    return pos ? __fadd_rn(8.0f, m) : __fsub_rn(7.0f, m);
 }
 
 template <typename T>
 struct RowLoad;
 
+// pair(row, j, m): elements 8j + 2m and 8j + 2m + 1 of a staged row
 template <>
 struct RowLoad<float> {
     static constexpr int kRowBytes = kD * 4;
-    // chunk c (0..15) = elements 8c..8c+7
-    static __device__ __forceinline__ void load8(const uint8_t* row, int c, float (&v)[8]) {
-        const float4 a = *reinterpret_cast<const float4*>(row + c * 32);
-        const float4 b = *reinterpret_cast<const float4*>(row + c * 32 + 16);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    static __device__ __forceinline__ float2 pair(const uint8_t* row, int j, int m) {
+        return *reinterpret_cast<const float2*>(row + 32 * j + 8 * m);
     }
 };
-
 template <>
 struct RowLoad<__nv_bfloat16> {
     static constexpr int kRowBytes = kD * 2;
-    static __device__ __forceinline__ void load8(const uint8_t* row, int c, float (&v)[8]) {
-        const uint4 a = *reinterpret_cast<const uint4*>(row + c * 16);
-        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            v[2 * i] = __uint_as_float(w[i] << 16);
-            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-        }
+    static __device__ __forceinline__ float2 pair(const uint8_t* row, int j, int m) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 16 * j + 4 * m);
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
     }
 };
-
 template <>
 struct RowLoad<__half> {
     static constexpr int kRowBytes = kD * 2;
-    static __device__ __forceinline__ void load8(const uint8_t* row, int c, float (&v)[8]) {
-        const uint4 a = *reinterpret_cast<const uint4*>(row + c * 16);
-        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-            v[2 * i] = f.x;
-            v[2 * i + 1] = f.y;
-        }
+    static __device__ __forceinline__ float2 pair(const uint8_t* row, int j, int m) {
+        return __half22float2(*reinterpret_cast<const __half2*>(row + 16 * j + 4 * m));
     }
 };
 
-// Quantize one 128-element row held in registers.  codes[16] are the 64 code bytes as
-// little-endian words (byte b = (idx[2b] << 4) | idx[2b+1]); returns the fp32 norm.
-__device__ __forceinline__ float quantize_row(float (&x)[kD], const WriteParams& p,
-                                              const uint32_t (&sign_mask)[kD / 32],
-                                              uint32_t (&codes)[16]) {
-    // L2 norm: acc[k] += x[8j+k]^2 in order of j, product rounded before the add.
-    float acc[8];
-#pragma unroll
-    for (int k = 0; k < 8; k++) acc[k] = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 16; j++)
-#pragma unroll
-        for (int k = 0; k < 8; k++) acc[k] = __fadd_rn(acc[k], __fmul_rn(x[8 * j + k], x[8 * j + k]));
-    float s = acc[0];
-#pragma unroll
-    for (int k = 1; k < 8; k++) s = __fadd_rn(s, acc[k]);
-    float norm = __fsqrt_rn(s);
-    // clamp(min=1e-8); a NaN stays a NaN, in the canonical quiet pattern torch produces
-    if (!(norm >= 1e-8f)) norm = (norm != norm) ? __uint_as_float(0x7fc00000u) : 1e-8f;
-
-    // normalise (IEEE division) and apply the +-1 signs (a sign-bit flip is an exact multiply)
-#pragma unroll
-    for (int d = 0; d < kD; d++) {
-        const float u = __fdiv_rn(x[d], norm);
-        const uint32_t flip = (sign_mask[d >> 5] << (31 - (d & 31))) & 0x80000000u;
-        x[d] = __uint_as_float(__float_as_uint(u) ^ flip);
-    }
-    // butterflies, stage order h = 1, 2, ..., 64
-#pragma unroll
-    for (int h = 1; h < kD; h <<= 1)
-#pragma unroll
-        for (int i = 0; i < kD; i += 2 * h)
-#pragma unroll
-            for (int k = 0; k < h; k++) {
-                const float a = x[i + k], b = x[i + k + h];
-                x[i + k] = __fadd_rn(a, b);
-                x[i + k + h] = __fsub_rn(a, b);
-            }
-    // scale, bucketize, pack
-#pragma unroll
-    for (int w = 0; w < 16; w++) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-            const int d = 8 * w + 2 * b;
-            const uint32_t hi = code4(__fmul_rn(x[d], p.fwht_scale), p.pos_bnd_bits);
-            const uint32_t lo = code4(__fmul_rn(x[d + 1], p.fwht_scale), p.pos_bnd_bits);
-            word |= ((hi << 4) | lo) << (8 * b);
-        }
-        codes[w] = word;
-    }
-    return norm;
-}
-
 template <typename T>
-__global__ void __launch_bounds__(kWriteThreads)
+__global__ void __launch_bounds__(kWriteThreads, 2)
 write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     using L = RowLoad<T>;
     constexpr int kPitch = L::kRowBytes + 16;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[2];
     __shared__ int abort_flag;
-    __shared__ uint32_t sign_mask_s[kD / 32];  // bit d set: signs[d] < 0
+    __shared__ __align__(16) float signs_s[kD];
+    __shared__ __align__(16) uint8_t out_s[kTileRows][64];  // code bytes of a tile, natural order
 
     const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int m = lane & 3;              // lane within the row
+    const int row_in_tile = tid >> 2;    // row of the tile this lane works on
+    const unsigned quad_base = lane & ~3;
     const int H = p.num_kv_heads;
-    const int64_t rows = p.num_tokens * H;                               // per tensor
-    const int64_t tiles_per_tensor = (rows + kWriteThreads - 1) / kWriteThreads;
+    const int64_t rows = p.num_tokens * H;  // per tensor
+    const int64_t tiles_per_tensor = (rows + kTileRows - 1) / kTileRows;
     const int64_t num_tiles = 2 * tiles_per_tensor;
 
     if (tid == 0) {
@@ -177,29 +124,21 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         abort_flag = 0;
         fence_barrier_init();
     }
-    {
-        const uint32_t neg = __ballot_sync(0xffffffffu, p.signs[tid] < 0.0f);
-        if ((tid & 31) == 0) sign_mask_s[tid >> 5] = neg;
-    }
+    if (tid < kD) signs_s[tid] = p.signs[tid];
     __syncthreads();
-    uint32_t sign_mask[kD / 32];
-#pragma unroll
-    for (int i = 0; i < kD / 32; i++) sign_mask[i] = sign_mask_s[i];
 
     auto issue = [&](int64_t tile, int buf) {
         const int which = tile >= tiles_per_tensor ? 1 : 0;
-        const int64_t row0 = (tile - which * tiles_per_tensor) * kWriteThreads;
+        const int64_t row0 = (tile - which * tiles_per_tensor) * kTileRows;
         const int64_t left = rows - row0;
-        const int64_t nrows = left < kWriteThreads ? left : (int64_t)kWriteThreads;
+        const int64_t nrows = left < kTileRows ? left : (int64_t)kTileRows;
         if (tid == 0) mbar_arrive_expect_tx(&full_bar[buf], (uint32_t)(nrows * L::kRowBytes));
         if (tid < nrows) {
             const int64_t r = row0 + tid;
             const int64_t t = r / H;
             const int h = (int)(r - t * H);
-            const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] +
-                           (int64_t)h * kD;
-            bulk_g2s(smem + (size_t)buf * kWriteThreads * kPitch + (size_t)tid * kPitch, src,
-                     L::kRowBytes, &full_bar[buf]);
+            const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * kD;
+            bulk_g2s(smem + (size_t)buf * kTileRows * kPitch + (size_t)tid * kPitch, src, L::kRowBytes, &full_bar[buf]);
         }
     };
 
@@ -215,47 +154,128 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         if (abort_flag) return;  // copy never landed: leave without touching the cache
 
         const int which = tile >= tiles_per_tensor ? 1 : 0;
-        const int64_t r = (tile - which * tiles_per_tensor) * kWriteThreads + tid;
-        if (r < rows) {
+        const int64_t r = (tile - which * tiles_per_tensor) * kTileRows + row_in_tile;
+        const bool row_ok = r < rows;  // uniform over the four lanes of a row
+        int64_t slot = -1;
+        int h = 0;
+        if (row_ok) {
             const int64_t t = r / H;
-            const int h = (int)(r - t * H);
-            const int64_t slot = p.slot_is_i64
-                                     ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
-                                     : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
-            if (slot >= 0) {
-                const uint8_t* row = smem + (size_t)buf * kWriteThreads * kPitch + (size_t)tid * kPitch;
-                float x[kD];
+            h = (int)(r - t * H);
+            slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
+                                 : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
+        }
+        // all lanes run the arithmetic (the shuffles need whole quads); rows past the end or with
+        // a negative slot read whatever is staged and store nothing
+        const uint8_t* row = smem + (size_t)buf * kTileRows * kPitch + (size_t)row_in_tile * kPitch;
+        float x[16][2];
+        float acc0 = 0.0f, acc1 = 0.0f, minsq = 1.0f;
 #pragma unroll
-                for (int c = 0; c < 16; c++) {
-                    float v[8];
-                    L::load8(row, c, v);
+        for (int j = 0; j < 16; j++) {
+            const float2 v = row_ok ? L::pair(row, j, m) : make_float2(0.f, 0.f);
+            x[j][0] = v.x;
+            x[j][1] = v.y;
+            // accumulators 2m and 2m+1 of the eight interleaved ones, in order of j, product
+            // rounded before the add
+            const float s0 = __fmul_rn(v.x, v.x), s1 = __fmul_rn(v.y, v.y);
+            acc0 = __fadd_rn(acc0, s0);
+            acc1 = __fadd_rn(acc1, s1);
+            minsq = fminf(minsq, fminf(s0, s1));
+        }
+        // combine the eight accumulators left to right
+        float s = 0.0f;
 #pragma unroll
-                    for (int k = 0; k < 8; k++) x[8 * c + k] = v[k];
+        for (int q = 0; q < 4; q++) {
+            const float a = __shfl_sync(0xffffffffu, acc0, quad_base + q);
+            const float b = __shfl_sync(0xffffffffu, acc1, quad_base + q);
+            s = q == 0 ? a : __fadd_rn(s, a);
+            s = __fadd_rn(s, b);
+        }
+        minsq = fminf(minsq, __shfl_xor_sync(0xffffffffu, minsq, 1));
+        minsq = fminf(minsq, __shfl_xor_sync(0xffffffffu, minsq, 2));
+        float norm = __fsqrt_rn(s);
+        // clamp(min=1e-8); a NaN stays a NaN, in the canonical quiet pattern torch produces
+        if (!(norm >= 1e-8f)) norm = (norm != norm) ? __uint_as_float(0x7fc00000u) : 1e-8f;
+
+        // normalise.  Fast path: every square is a normal number (so |x| >= 2^-75 and nonzero)
+        // and the norm is moderate with a significand that is not all ones.
+        const uint32_t nbits = __float_as_uint(norm);
+        const bool fast = minsq >= 1.1754944e-38f && norm >= 9.0949470e-13f && norm <= 1.0995116e12f &&
+                          (nbits & 0x7fffffu) != 0x7fffffu;
+        if (fast) {
+            const float rcp = __frcp_rn(norm);
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float q = __fmul_rn(x[j][e], rcp);
+                    const float err = __fmaf_rn(-q, norm, x[j][e]);
+                    x[j][e] = __fmaf_rn(err, rcp, q);
                 }
-                uint32_t codes[16];
-                const float norm = quantize_row(x, p, sign_mask, codes);
-                const uint32_t nh = (norm != norm) ? 0x7e00u : (uint32_t)__half_as_ushort(__float2half_rn(norm));
-                // slot = block * block_size + entry and the cache is [block][entry][head][slot_bytes]
-                uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes +
-                               ((size_t)slot * H + h) * p.slot_bytes;
+        } else {
 #pragma unroll
-                for (int q = 0; q < 4; q++)
-                    *reinterpret_cast<uint4*>(dst + 16 * q) =
-                        make_uint4(codes[4 * q], codes[4 * q + 1], codes[4 * q + 2], codes[4 * q + 3]);
-                if (p.zero_pad)
-                    *reinterpret_cast<uint4*>(dst + 64) = make_uint4(nh | (nh << 16), 0u, 0u, 0u);
-                else
-                    *reinterpret_cast<uint32_t*>(dst + 64) = nh | (nh << 16);
+            for (int j = 0; j < 16; j++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) x[j][e] = __fdiv_rn(x[j][e], norm);
+        }
+        // signs, then butterflies in stage order h = 1, 2, 4 (lanes), 8..64 (j)
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const float2 sg = *reinterpret_cast<const float2*>(&signs_s[8 * j + 2 * m]);
+            const float a = __fmul_rn(x[j][0], sg.x), b = __fmul_rn(x[j][1], sg.y);
+            x[j][0] = __fadd_rn(a, b);
+            x[j][1] = __fsub_rn(a, b);
+        }
+#pragma unroll
+        for (int d = 1; d < 4; d <<= 1)
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float o = __shfl_xor_sync(0xffffffffu, x[j][e], d);
+                    x[j][e] = (m & d) ? __fsub_rn(o, x[j][e]) : __fadd_rn(x[j][e], o);
+                }
+#pragma unroll
+        for (int hj = 1; hj < 16; hj <<= 1)
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (!(j & hj)) {
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const float a = x[j][e], b = x[j + hj][e];
+                        x[j][e] = __fadd_rn(a, b);
+                        x[j + hj][e] = __fsub_rn(a, b);
+                    }
+                }
+        // scale, code, pack: byte 4j + m = (code(even dim) << 4) | code(odd dim), via the low
+        // byte of a float with 2^23 added
+        const bool all_nan = x[0][0] != x[0][0];  // a non-finite input turns the whole row into NaN
+        uint8_t* orow = out_s[row_in_tile];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const float hi = code_f(__fmul_rn(x[j][0], p.fwht_scale), p.neg_bnd_big);
+            const float lo = code_f(__fmul_rn(x[j][1], p.fwht_scale), p.neg_bnd_big);
+            const float bytef = __fadd_rn(__fmaf_rn(hi, 16.0f, lo), 8388608.0f);
+            orow[4 * j + m] = all_nan ? (uint8_t)0xff : (uint8_t)__float_as_uint(bytef);
+        }
+        __syncwarp();
+        if (row_ok && slot >= 0) {
+            // slot = block * block_size + entry and the cache is [block][entry][head][slot_bytes]
+            uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)slot * H + h) * p.slot_bytes;
+            *reinterpret_cast<uint4*>(dst + 16 * m) = *reinterpret_cast<const uint4*>(orow + 16 * m);
+            if (m == 0) {
+                const uint32_t nh = (norm != norm) ? 0x7e00u : (uint32_t)__half_as_ushort(__float2half_rn(norm));
+                if (p.zero_pad) *reinterpret_cast<uint4*>(dst + 64) = make_uint4(nh | (nh << 16), 0u, 0u, 0u);
+                else *reinterpret_cast<uint32_t*>(dst + 64) = nh | (nh << 16);
             }
         }
-        __syncthreads();  // everyone is done reading this buffer before it is refilled
+        __syncthreads();  // everyone is done reading this buffer (and out_s) before it is refilled
     }
 }
 
 template <typename T>
 static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream) {
     constexpr int kPitch = RowLoad<T>::kRowBytes + 16;
-    const size_t smem = (size_t)2 * kWriteThreads * kPitch;
+    const size_t smem = (size_t)2 * kTileRows * kPitch;
     static bool configured[64] = {};  // per template instance and device
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
@@ -265,8 +285,8 @@ static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream)
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t rows = p.num_tokens * p.num_kv_heads;
-    const int64_t tiles = 2 * ((rows + kWriteThreads - 1) / kWriteThreads);
-    const int per_sm = (int)(227 * 1024 / (smem + 1024));
+    const int64_t tiles = 2 * ((rows + kTileRows - 1) / kTileRows);
+    const int per_sm = 2;  // __launch_bounds__(256, 2)
     const int64_t grid = tiles < (int64_t)sm_count * per_sm ? tiles : (int64_t)sm_count * per_sm;
     write_kv_cache_kernel<T><<<(unsigned)grid, kWriteThreads, smem, stream>>>(p);
     TQ_CUDA(cudaGetLastError());
@@ -319,10 +339,7 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     p.signs = signs;
     float cen[16], bnd[15];
     host_codebook(kD, 4, cen, bnd);
-    for (int i = 0; i < 7; i++) {
-        float b = bnd[8 + i];
-        memcpy(&p.pos_bnd_bits[i], &b, 4);
-    }
+    for (int i = 0; i < 7; i++) p.neg_bnd_big[i] = -bnd[8 + i] * 1099511627776.0f;  // exact: a power of two
     p.fwht_scale = (float)(1.0 / sqrt((double)kD));
     int sms = 0;
     int rc = device_sm_count(&sms);
