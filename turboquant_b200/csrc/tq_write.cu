@@ -103,58 +103,61 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     using L = RowLoad<T>;
     constexpr int kPitch = L::kRowBytes + 16;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[2];
-    __shared__ int abort_flag;
+    // every warp runs its own two-buffer pipeline over 8-row pieces: no block-wide barrier in the loop
+    __shared__ __align__(8) uint64_t full_bar[kWriteThreads / 32][2];
     __shared__ __align__(16) float signs_s[kD];
     __shared__ __align__(16) uint8_t out_s[kTileRows][64];  // code bytes of a tile, natural order
 
     const int tid = threadIdx.x;
-    const int lane = tid & 31;
+    const int lane = tid & 31, warp = tid >> 5;
     const int m = lane & 3;              // lane within the row
-    const int row_in_tile = tid >> 2;    // row of the tile this lane works on
+    const int row_in_warp = lane >> 2;   // row of the warp's 8-row piece this lane works on
+    const int row_in_tile = tid >> 2;
     const unsigned quad_base = lane & ~3;
     const int H = p.num_kv_heads;
     const int64_t rows = p.num_tokens * H;  // per tensor
-    const int64_t tiles_per_tensor = (rows + kTileRows - 1) / kTileRows;
+    constexpr int kPieceRows = 8;
+    const int64_t tiles_per_tensor = (rows + kPieceRows - 1) / kPieceRows;  // pieces per tensor
     const int64_t num_tiles = 2 * tiles_per_tensor;
 
-    if (tid == 0) {
-        mbar_init(&full_bar[0], 1);
-        mbar_init(&full_bar[1], 1);
-        abort_flag = 0;
-        fence_barrier_init();
+    if (lane == 0) {
+        mbar_init(&full_bar[warp][0], 1);
+        mbar_init(&full_bar[warp][1], 1);
     }
+    if (tid == 0) fence_barrier_init();
     if (tid < kD) signs_s[tid] = p.signs[tid];
     __syncthreads();
 
     auto issue = [&](int64_t tile, int buf) {
         const int which = tile >= tiles_per_tensor ? 1 : 0;
-        const int64_t row0 = (tile - which * tiles_per_tensor) * kTileRows;
+        const int64_t row0 = (tile - which * tiles_per_tensor) * kPieceRows;
         const int64_t left = rows - row0;
-        const int64_t nrows = left < kTileRows ? left : (int64_t)kTileRows;
-        if (tid == 0) mbar_arrive_expect_tx(&full_bar[buf], (uint32_t)(nrows * L::kRowBytes));
-        if (tid < nrows) {
-            const int64_t r = row0 + tid;
+        const int64_t nrows = left < kPieceRows ? left : (int64_t)kPieceRows;
+        fence_proxy_async();  // earlier shared-memory reads of this buffer precede the copy engine's writes
+        if (lane == 0) mbar_arrive_expect_tx(&full_bar[warp][buf], (uint32_t)(nrows * L::kRowBytes));
+        __syncwarp();
+        if (lane < nrows) {
+            const int64_t r = row0 + lane;
             const int64_t t = r / H;
             const int h = (int)(r - t * H);
             const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * kD;
-            bulk_g2s(smem + (size_t)buf * kTileRows * kPitch + (size_t)tid * kPitch, src, L::kRowBytes, &full_bar[buf]);
+            bulk_g2s(smem + (size_t)buf * kTileRows * kPitch + (size_t)(warp * kPieceRows + lane) * kPitch, src,
+                     L::kRowBytes, &full_bar[warp][buf]);
         }
     };
 
-    int64_t tile = blockIdx.x;
+    const int64_t warp_stride = (int64_t)gridDim.x * (kWriteThreads / 32);
+    int64_t tile = (int64_t)blockIdx.x * (kWriteThreads / 32) + warp;
     if (tile < num_tiles) issue(tile, 0);
-    for (int it = 0; tile < num_tiles; tile += gridDim.x, it++) {
+    for (int it = 0; tile < num_tiles; tile += warp_stride, it++) {
         const int buf = it & 1;
-        const int64_t next = tile + gridDim.x;
-        if (next < num_tiles) issue(next, buf ^ 1);
+        const int64_t next = tile + warp_stride;
+        if (next < num_tiles) issue(next, buf ^ 1);  // that buffer was read out one iteration ago
 
-        if (!mbar_wait(&full_bar[buf], (it >> 1) & 1)) abort_flag = 1;
-        __syncthreads();
-        if (abort_flag) return;  // copy never landed: leave without touching the cache
+        if (!mbar_wait(&full_bar[warp][buf], (it >> 1) & 1)) return;  // copy never landed: touch nothing
 
         const int which = tile >= tiles_per_tensor ? 1 : 0;
-        const int64_t r = (tile - which * tiles_per_tensor) * kTileRows + row_in_tile;
+        const int64_t r = (tile - which * tiles_per_tensor) * kPieceRows + row_in_warp;
         const bool row_ok = r < rows;  // uniform over the four lanes of a row
         int64_t slot = -1;
         int h = 0;
@@ -268,7 +271,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
                 else *reinterpret_cast<uint32_t*>(dst + 64) = nh | (nh << 16);
             }
         }
-        __syncthreads();  // everyone is done reading this buffer (and out_s) before it is refilled
+        __syncwarp();  // the warp is done with this buffer and with its rows of out_s
     }
 }
 
