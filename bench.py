@@ -54,6 +54,9 @@ def parse():
     ap.add_argument("--num-ctas", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4"],
+                    help="config1 (default, the headline): batch 8 x 32k per GPU; config3: 64 mixed lengths sharded by "
+                         "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge")
     return ap.parse_args()
 
 
@@ -412,10 +415,171 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------
+# Secondary workloads (parity-test shapes timed on request; the default line is config 1)
+# ------------------------------------------------------------------------------------------------
+def _setup_dist():
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    return rank, world, dev
+
+
+def _fill_cache(attn, cache, block_table_row, n_tokens, gen, dev, chunk=65536):
+    """Quantize seeded N(0,1) K/V for one sequence into its pages with the cache-write kernel."""
+    for t0 in range(0, n_tokens, chunk):
+        n = min(chunk, n_tokens - t0)
+        k = torch.randn(n, HKV, D, generator=gen, device=dev).to(torch.bfloat16)
+        v = torch.randn(n, HKV, D, generator=gen, device=dev).to(torch.bfloat16)
+        tok = torch.arange(t0, t0 + n, device=dev)
+        slots = block_table_row.long()[tok // PAGE] * PAGE + tok % PAGE
+        attn.write(k, v, cache, slots)
+
+
+def _timed_steps(fn, steps, world, dev):
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms / steps
+
+
+def run_config3(args):
+    """64 sequences with log-uniform lengths in [512, 131072] (seed 3), sharded over the ranks by
+    sequence (longest first); every rank decodes its shard, no collective on the data path."""
+    from turboquant_b200 import synthetic
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    from turboquant_b200.parallel import shard_sequences
+    rank, world, dev = _setup_dist()
+    lens_all = synthetic.mixed_lengths(seed=3, n=64)
+    shards = shard_sequences(lens_all, world)
+    lens = [lens_all[i] for i in shards[rank]]
+    attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, num_ctas=args.num_ctas)
+    bt_cpu, _, nb = synthetic.paged_layout(lens, seed=3 + rank)
+    bt = bt_cpu.to(dev)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3 + 1000 * rank)
+    ncache = 2   # rotated so that consecutive launches stream different memory (each far larger than L2)
+    caches = [torch.zeros(kv_cache_shape(nb, PAGE, HKV, D), dtype=torch.uint8, device=dev) for _ in range(ncache)]
+    for c in caches:
+        for b, n in enumerate(lens):
+            _fill_cache(attn, c, bt[b], n, gen, dev)
+    q = torch.randn(len(lens), HQ, D, generator=gen, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    state = {"i": 0}
+
+    def step():
+        attn.decode(q, caches[state["i"] % ncache], bt, sl, out)
+        state["i"] += 1
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ms = _timed_steps(step, args.steps, world, dev)
+    loads = [sum(lens_all[i] for i in s) for s in shards]
+    alg = sum(lens_all) * HKV * ALG_BYTES_PER_TOKEN_HEAD
+    peak, peak_src = measured_peak()
+    if rank == 0:
+        ach = alg / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode_attn_tokens_per_s", "value": 64 / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "config3: 64 sequences, lengths log-uniform in [512, 131072] (seed 3), one layer, "
+                                   "sharded over the GPUs by sequence (greedy by length)",
+                       "total_tokens": sum(lens_all), "load_imbalance_max_over_mean": max(loads) / (sum(loads) / world),
+                       "l2": "inputs larger than L2, two caches alternated"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak * world, "unit": "GB/s",
+                         "frac": ach / (peak * world), "peak_source": peak_src, "algorithmic_bytes_per_launch": alg,
+                         "note": "whole call (decode + merge kernels), aggregate over GPUs"},
+            "gpu_launches": args.steps * 2}), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def run_config4(args):
+    """One 1,048,576-token sequence, 8 decode queries; the KV axis is split contiguously over the
+    ranks, each rank computes rotated partials + LSE, the partials are all-gathered over NCCL and
+    every rank finishes with the LSE merge and the inverse rotation."""
+    from turboquant_b200 import synthetic
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    from turboquant_b200.parallel import kv_ranges, kv_split_decode
+    rank, world, dev = _setup_dist()
+    total, nq = 1_048_576, 8
+    a, b = kv_ranges(total, world)[rank]
+    n_local = b - a
+    attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, num_ctas=args.num_ctas)
+    pages = (n_local + PAGE - 1) // PAGE
+    cpu_gen = torch.Generator().manual_seed(4 + rank)
+    bt_row = torch.randperm(pages, generator=cpu_gen).to(torch.int32).to(dev)
+    cache = torch.zeros(kv_cache_shape(pages, PAGE, HKV, D), dtype=torch.uint8, device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4 + 1000 * rank)
+    _fill_cache(attn, cache, bt_row, n_local, gen, dev)
+    qgen = torch.Generator(device=dev)
+    qgen.manual_seed(4)                                   # the same queries on every rank
+    q = torch.randn(nq, HQ, D, generator=qgen, device=dev).to(torch.bfloat16)
+    bt = bt_row.unsqueeze(0).expand(nq, -1).contiguous()  # the 8 queries share the sequence's pages
+    sl = torch.full((nq,), n_local, dtype=torch.int32, device=dev)
+    out = torch.empty_like(q)
+
+    def step():
+        if world > 1:
+            kv_split_decode(attn, q, cache, bt, sl, out)
+        else:
+            attn.decode(q, cache, bt, sl, out)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ms = _timed_steps(step, args.steps, world, dev)
+    alg = total * HKV * ALG_BYTES_PER_TOKEN_HEAD
+    peak, peak_src = measured_peak()
+    if rank == 0:
+        ach = alg / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode_attn_tokens_per_s", "value": nq / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "config4: one 1,048,576-token sequence, 8 decode queries, one layer, KV axis split "
+                                   "contiguously over the GPUs, partial (o, lse) all-gathered over NCCL, merged on every GPU",
+                       "exchange_bytes_per_rank": nq * HQ * (D + 1) * 4,
+                       "note": "the 8 queries are 8 batch rows that each stream the KV (as the reference's API would); "
+                               "the algorithmic bytes below count the KV once",
+                       "l2": "1.34 GB of pages per pass, far larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak * world, "unit": "GB/s",
+                         "frac": ach / (peak * world), "peak_source": peak_src, "algorithmic_bytes_per_launch": alg,
+                         "physical_kv_bytes_streamed": nq * total * HKV * 160},
+            "gpu_launches": args.steps * 2 + (args.steps if world > 1 else 0)}), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "config3":
+        run_config3(args)
+    elif args.workload == "config4":
+        run_config4(args)
     else:
         run_ours(args)
 

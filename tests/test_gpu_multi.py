@@ -1,0 +1,71 @@
+"""KV-axis split of one long sequence over two GPUs (NCCL all-gather of the partials + LSE merge),
+checked against the single-GPU result and the oracle.  Needs two GPUs; skipped otherwise."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+_RANK = r"""
+import math, os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np, torch, torch.distributed as dist
+from oracle import tq_oracle
+from turboquant_b200 import synthetic
+from turboquant_b200.paged_attention import TurboQuantPagedAttention
+from turboquant_b200.parallel import kv_ranges, kv_split_decode
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+dist.init_process_group("nccl", device_id=dev)
+total, nq = 5000, 3
+case = synthetic.decode_case(seed=95, seq_lens=[total], dtype=torch.bfloat16, num_q_rows=nq)
+signs = synthetic.make_signs().numpy()
+full_cache = np.zeros((2, case.num_blocks, 16, 8, 80), np.uint8)
+tq_oracle.write_kv_cache(full_cache, case.k.float().numpy(), case.v.float().numpy(), signs, case.slot_mapping.numpy(), 128)
+bt_full = np.repeat(case.block_table.numpy(), nq, axis=0)
+want = tq_oracle.decode_paged(case.q.float().numpy(), full_cache, bt_full, np.full(nq, total, np.int32), signs, 1 / math.sqrt(128))
+# this rank holds only the pages of its token range, written by the CUDA kernel into a local cache
+a, b = kv_ranges(total, world)[rank]
+n_local = b - a
+pages = (n_local + 15) // 16
+attn = TurboQuantPagedAttention(32, 128, 1 / math.sqrt(128), 8)
+cache = torch.zeros((2, pages, 16, 8, 80), dtype=torch.uint8, device=dev)
+perm = torch.randperm(pages, generator=torch.Generator().manual_seed(rank)).to(dev)
+tok = torch.arange(n_local, device=dev)
+slots = perm[tok // 16] * 16 + tok %% 16
+attn.write(case.k[a:b].to(dev), case.v[a:b].to(dev), cache, slots)
+bt = perm.to(torch.int32).unsqueeze(0).expand(nq, -1).contiguous()
+sl = torch.full((nq,), n_local, dtype=torch.int32, device=dev)
+out = torch.empty(nq, 32, 128, dtype=torch.float32, device=dev)
+kv_split_decode(attn, case.q.to(dev), cache, bt, sl, out)
+torch.cuda.synchronize()
+got = out.cpu().numpy()
+err = np.abs(got - want)
+assert (err <= 2e-3 + 1e-2 * np.abs(want)).all(), err.max()
+assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-2
+gathered = [torch.empty_like(out) for _ in range(world)]
+dist.all_gather(gathered, out)
+assert all(torch.equal(g, gathered[0]) for g in gathered)      # every rank ends with the same result
+dist.barrier(); dist.destroy_process_group()
+print("rank", rank, "ok", float(err.max()))
+"""
+
+
+def test_kv_split_decode_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "rank.py"
+    script.write_text(_RANK % {"root": str(ROOT)})
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29600 + os.getpid() % 300), WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script)], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for r in range(2)]
+    for r, p in enumerate(procs):
+        out, err = p.communicate(timeout=600)
+        assert p.returncode == 0 and f"rank {r} ok" in out, err[-3000:]
