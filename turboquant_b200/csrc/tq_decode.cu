@@ -125,11 +125,19 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
 // r[j] = { low half: centroid(low nibble of byte j), high half: centroid(high nibble) } in units
 // of the N(0,1) codebook.  lut_lane is the shared-memory address of this lane's column of the
 // table: entry v lives at lut_lane + 128 * v.
+// With the wide table (entries 256 bytes apart, table at a 64 KB boundary of the shared window)
+// lut_lane = table address + 4*lane has a zero second byte, and one byte permute drops the code
+// byte into it: address and lookup are two instructions per code byte instead of three.
+template <bool WIDE>
 __device__ __forceinline__ void dequant8(uint32_t w, uint32_t lut_lane, uint32_t (&r)[4]) {
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        const uint32_t v = prmt(w, 0u, 0x4440u | j);  // byte j, zero extended
-        r[j] = lds32(v * 128u + lut_lane);
+        if (WIDE) {
+            r[j] = lds32(prmt(w, lut_lane, 0x7604u | (j << 4)));
+        } else {
+            const uint32_t v = prmt(w, 0u, 0x4440u | j);  // byte j, zero extended
+            r[j] = lds32(v * 128u + lut_lane);
+        }
     }
 }
 
@@ -235,7 +243,14 @@ struct DecodeSmem {
     static constexpr int total(int stages, int group) { return stages * kStageBytes + kLutBytes + q_bytes(group); }
 };
 
-template <int HKV>
+// Shared-memory map.  Narrow table: [stages][table 32 KB][rotated Q].  Wide table (WIDE): the
+// table must start at offset 64 KB of the block's shared window, so the memory below it holds
+// the rotated Q and stage 0, and stages 1.. follow the table:
+//   [rotated Q 16 KB][stage 0] ... | 64 KB: table (64 KB) | 128 KB: [stage 1][stage 2]
+constexpr uint32_t kWideLutAddr = 65536, kWideLutBytes = 65536;
+constexpr int kWideStages = 3;
+
+template <int HKV, bool WIDE>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     using S = DecodeSmem<HKV>;
@@ -248,10 +263,20 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     __shared__ int n_eff_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint8_t* stages = smem;
     const int nstages = p.num_stages;
-    uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem + nstages * S::kStageBytes);
-    __half* q_s = reinterpret_cast<__half*>(smem + nstages * S::kStageBytes + kLutBytes);
+    const uint32_t smem_base = smem_u32(smem);
+    // stage st lives at stage0 + (st ? stage_gap + (st - 1) * kStageBytes : 0) (byte offsets from smem)
+    const uint32_t q_off = WIDE ? 0u : (uint32_t)(nstages * S::kStageBytes + kLutBytes);
+    const uint32_t stage0_off = WIDE ? (uint32_t)S::q_bytes(p.group) : 0u;
+    const uint32_t stage_gap = WIDE ? kWideLutAddr + kWideLutBytes - smem_base - stage0_off : (uint32_t)S::kStageBytes;
+    const uint32_t lut_off = WIDE ? kWideLutAddr - smem_base : (uint32_t)(nstages * S::kStageBytes);
+    uint8_t* stages = smem + stage0_off;
+    uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem + lut_off);
+    __half* q_s = reinterpret_cast<__half*>(smem + q_off);
+    if (WIDE && smem_base + stage0_off + S::kStageBytes > kWideLutAddr) {  // the map above does not fit
+        if (tid == 0) atomicExch(&p.header[0], 3);
+        return;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < kMaxStages; s++) {
@@ -345,7 +370,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                         }
                     }
                     if (abort_flag) break;
-                    uint8_t* sk = stages + (size_t)st * S::kStageBytes;
+                    uint8_t* sk = stages + (st ? stage_gap + (size_t)(st - 1) * S::kStageBytes : 0);
                     uint8_t* sv = sk + S::kKBytes;
                     if (lane == 0)
                         mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(np * 2 * kPageTokens * S::kRowBytes));
@@ -380,7 +405,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     // fill the lookup table: entry v, column c at lut_s[v * 32 + c] = {centroid(v & 15), centroid(v >> 4)}
     for (int i = tid; i < 256 * 32; i += kConsumerWarps * 32) {
         const int v = i >> 5;
-        lut_s[i] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
+        lut_s[WIDE ? (v * 64 + (i & 31)) : i] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");  // consumer warps only
     const uint32_t lut_lane = smem_u32(lut_s) + 4u * lane;
@@ -499,8 +524,8 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
                     uint32_t ra[4], rb[4];
-                    dequant8(kwa[w], lut_lane, ra);
-                    dequant8(kwb[w], lut_lane, rb);
+                    dequant8<WIDE>(kwa[w], lut_lane, ra);
+                    dequant8<WIDE>(kwb[w], lut_lane, rb);
                     mma16816(s_acc, ra[0], rb[0], ra[1], rb[1], qf[4 * w], qf[4 * w + 1]);
                     mma16816(s_acc, ra[2], rb[2], ra[3], rb[3], qf[4 * w + 2], qf[4 * w + 3]);
                 }
@@ -546,10 +571,10 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     const uint32_t lo23 = (vw2[i] & 0x0F0F0F0Fu) | ((vw3[i] << 4) & 0xF0F0F0F0u);
                     const uint32_t hi23 = ((vw2[i] >> 4) & 0x0F0F0F0Fu) | (vw3[i] & 0xF0F0F0F0u);
                     uint32_t a_lo01[4], a_hi01[4], a_lo23[4], a_hi23[4];
-                    dequant8(lo01, lut_lane, a_lo01);
-                    dequant8(hi01, lut_lane, a_hi01);
-                    dequant8(lo23, lut_lane, a_lo23);
-                    dequant8(hi23, lut_lane, a_hi23);
+                    dequant8<WIDE>(lo01, lut_lane, a_lo01);
+                    dequant8<WIDE>(hi01, lut_lane, a_hi01);
+                    dequant8<WIDE>(lo23, lut_lane, a_lo23);
+                    dequant8<WIDE>(hi23, lut_lane, a_hi23);
 #pragma unroll
                     for (int j = 0; j < 4; j++)  // rows: g <- odd dim, g+8 <- even dim of byte 4i+j
                         mma16816(o_acc[4 * i + j], a_lo01[j], a_hi01[j], a_lo23[j], a_hi23[j], pb0, pb1);
@@ -558,7 +583,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[st]);
             }
-            st_off += S::kStageBytes;
+            st_off = st ? st_off + S::kStageBytes : stage_gap;
             if (++st == nstages) { st = 0; st_off = 0; round++; }
         }
 
@@ -755,25 +780,36 @@ static int resolve_ctas(int num_ctas, int* out) {
     return TQ_OK;
 }
 
-template <int HKV>
-static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
-    using S = DecodeSmem<HKV>;
-    // deepest ring that fits beside the table and the rotated queries (static smem: ~2 KB)
-    int stages = kMaxStages;
-    while (stages > 2 && S::total(stages, p.group) > kMaxSmem - 2048) stages--;
-    p.num_stages = stages;
-    const int smem = S::total(stages, p.group);
+template <int HKV, bool WIDE>
+static int launch_decode_impl(DecodeParams& p, int grid, int smem, cudaStream_t stream) {
     static bool configured[64] = {};  // the attribute is per device
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kMaxSmem - 2048));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    decode_paged_kernel<HKV><<<grid, kDecodeThreads, smem, stream>>>(p);
+    decode_paged_kernel<HKV, WIDE><<<grid, kDecodeThreads, smem, stream>>>(p);
     TQ_CUDA(cudaGetLastError());
     return TQ_OK;
+}
+
+template <int HKV>
+static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
+    using S = DecodeSmem<HKV>;
+    // Wide lookup table (one instruction less per code byte) when its fixed shared-memory map fits:
+    // 8 KV heads and at most four query heads per KV head.  See the map above the kernel.
+    if (HKV == 8 && p.group <= 4) {
+        p.num_stages = kWideStages;
+        const int smem = (int)(kWideLutAddr + kWideLutBytes) + (kWideStages - 1) * S::kStageBytes;  // from offset 0: ample
+        return launch_decode_impl<HKV, true>(p, grid, smem, stream);
+    }
+    // narrow table: deepest ring that fits beside the table and the rotated queries (static smem: ~2 KB)
+    int stages = kMaxStages;
+    while (stages > 2 && S::total(stages, p.group) > kMaxSmem - 2048) stages--;
+    p.num_stages = stages;
+    return launch_decode_impl<HKV, false>(p, grid, S::total(stages, p.group), stream);
 }
 
 static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
