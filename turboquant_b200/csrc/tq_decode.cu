@@ -533,14 +533,17 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 const float kfa = va ? nka * p.k_scale : 0.f, kfb = vb ? nkb * p.k_scale : 0.f;
                 float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
                 float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
+                // The running max of a head is raised only when some score of the tile exceeds it by
+                // more than 2^6; one vote decides that, and only then is the tile max reduced across
+                // the lanes (three shuffle rounds) and the accumulators rescaled.
                 float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+                if (__any_sync(0xffffffffu, mx0 > m0 + kRaiseThreshold || mx1 > m1 + kRaiseThreshold)) {
 #pragma unroll
-                for (int o = 4; o < 32; o <<= 1) {
-                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
-                }
-                const bool raise0 = mx0 > m0 + kRaiseThreshold, raise1 = mx1 > m1 + kRaiseThreshold;
-                if (__any_sync(0xffffffffu, raise0 || raise1)) {
+                    for (int o = 4; o < 32; o <<= 1) {
+                        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+                        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+                    }
+                    const bool raise0 = mx0 > m0 + kRaiseThreshold, raise1 = mx1 > m1 + kRaiseThreshold;
                     const float c0 = raise0 ? fast_exp2(m0 - mx0) : 1.f, c1 = raise1 ? fast_exp2(m1 - mx1) : 1.f;
                     if (raise0) m0 = mx0;
                     if (raise1) m1 = mx1;
