@@ -289,8 +289,14 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     }
     __syncthreads();
 
-    // ---- plan: warp 0 scans seq_lens, finds this block's page range and its segments ----------
-    if (warp == 0) {
+    // ---- plan: warp 0 scans seq_lens, finds this block's page range and its segments; the other
+    // warps meanwhile fill the lookup table: entry v, column c = {centroid(v & 15), centroid(v >> 4)}
+    if (warp != 0) {
+        for (int i = tid - 32; i < 256 * 32; i += kDecodeThreads - 32) {
+            const int v = i >> 5;
+            lut_s[WIDE ? (v * 64 + (i & 31)) : i] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
+        }
+    } else {
         // pass 1: total pages
         int total = 0;
         for (int base = 0; base < p.batch; base += 32) {
@@ -402,12 +408,6 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     const int head = warp % HKV;   // KV head of this warp
     const int sub = warp / HKV;    // page lane inside a stage
     __half* qw = q_s + warp * S::q_rows(p.group) * kHeadDim;
-    // fill the lookup table: entry v, column c at lut_s[v * 32 + c] = {centroid(v & 15), centroid(v >> 4)}
-    for (int i = tid; i < 256 * 32; i += kConsumerWarps * 32) {
-        const int v = i >> 5;
-        lut_s[WIDE ? (v * 64 + (i & 31)) : i] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");  // consumer warps only
     const uint32_t lut_lane = smem_u32(lut_s) + 4u * lane;
 
     // per-thread constants of the fragment loads (byte offsets inside a stage): MMA rows g and
@@ -509,9 +509,15 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 const int tok0 = (first_page + pg + sub) * kPageTokens;  // first token of the page
                 // ---- K codes and norms for tokens ta, tb; V codes: bytes 8g..8g+7 of four tokens ----
                 const uint4 ka = lds128(ka_addr + st_off), kb = lds128(kb_addr + st_off);
-                const bool va = tok0 + ta < len_eff, vb = tok0 + tb < len_eff;
-                const float nka = lds_half(nka_addr + st_off), nkb = lds_half(nkb_addr + st_off);
-                const float nva = lds_half(nva_addr + st_off), nvb = lds_half(nvb_addr + st_off);
+                float nka = lds_half(nka_addr + st_off), nkb = lds_half(nkb_addr + st_off);
+                float nva = lds_half(nva_addr + st_off), nvb = lds_half(nvb_addr + st_off);
+                // Only the last page of a sequence can hold tokens past its length: their norms are
+                // zeroed (whatever the unwritten slots contain) and their scores biased to -inf.
+                float bias_a = 0.f, bias_b = 0.f;
+                if (tok0 + kPageTokens > len_eff) {
+                    if (tok0 + ta >= len_eff) { nka = 0.f; nva = 0.f; bias_a = -INFINITY; }
+                    if (tok0 + tb >= len_eff) { nkb = 0.f; nvb = 0.f; bias_b = -INFINITY; }
+                }
                 const uint2 v0 = lds64(v0_addr + st_off), v1 = lds64(v1_addr + st_off);
                 const uint2 v2 = lds64(v2_addr + st_off), v3 = lds64(v3_addr + st_off);
                 __syncwarp();
@@ -530,9 +536,9 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     mma16816(s_acc, ra[2], rb[2], ra[3], rb[3], qf[4 * w + 2], qf[4 * w + 3]);
                 }
                 // ---- online softmax (base 2) ------------------------------------------------------
-                const float kfa = va ? nka * p.k_scale : 0.f, kfb = vb ? nkb * p.k_scale : 0.f;
-                float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
-                float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
+                const float kfa = nka * p.k_scale, kfb = nkb * p.k_scale;
+                const float x0 = fmaf(s_acc[0], kfa, bias_a), x1 = fmaf(s_acc[1], kfa, bias_a);
+                const float x2 = fmaf(s_acc[2], kfb, bias_b), x3 = fmaf(s_acc[3], kfb, bias_b);
                 // The running max of a head is raised only when some score of the tile exceeds it by
                 // more than 2^6; one vote decides that, and only then is the tile max reduced across
                 // the lanes (three shuffle rounds) and the accumulators rescaled.
@@ -558,7 +564,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 const float e2 = fast_exp2(x2 - m0), e3 = fast_exp2(x3 - m1);
                 l0 += e0 + e2;
                 l1 += e1 + e3;
-                const float vfa = va ? nva * p.v_scale : 0.f, vfb = vb ? nvb * p.v_scale : 0.f;
+                const float vfa = nva * p.v_scale, vfb = nvb * p.v_scale;
                 // P (token rows g / g+8, head columns 2tg, 2tg+1) -> transposed B fragments
                 const uint32_t pb0 = movmatrix_trans(pack_half2(e0 * vfa, e1 * vfa));
                 const uint32_t pb1 = movmatrix_trans(pack_half2(e2 * vfb, e3 * vfb));
