@@ -103,7 +103,10 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *   seq_lens     int32 [batch] (device)
  *   out          [batch][num_q_heads][head_dim]            out_dtype
  *   out_lse      optional fp32 [batch][num_q_heads], natural-log LSE of the scaled scores
- *   workspace    at least tq_decode_workspace_bytes(...) bytes, 256-byte aligned
+ *   workspace    at least tq_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its first int32 is a
+ *                sticky status word (0 ok, 1 a bounded wait ran out, 2 too many sequences per block,
+ *                3 shared-memory map did not fit): zero the workspace once if you want to read it;
+ *                no call clears it and nothing else in the workspace needs initialising
  *   num_ctas     thread blocks to balance over; 0 = one per SM of the current device
  *
  * Supported geometry: head_dim 128, block_size 16, slot_bytes 80, num_q_heads/num_kv_heads <= 8,
@@ -159,9 +162,11 @@ int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_
  *     32 query heads that is a batch of roughly 170 with one block per SM on a 148-SM part.
  *   - The first call on each device looks up the array's device address; make that call before
  *     starting any stream capture.  No call allocates or frees device memory.
- *   - All calls on one device share the array: the part that has to start at zero is cleared on
- *     the stream at every call, the rest is overwritten before it is read.  Two calls that can
- *     overlap on the GPU (different streams) race on it; keep them on one stream or order them. */
+ *   - All calls on one device share the array and find the previous call's contents in it: every
+ *     part that a call reads is overwritten by that call first, and the only word that has to
+ *     start at zero, the sticky status word, does so because the array is zero-initialised at
+ *     load.  Two calls that can overlap on the GPU (different streams) race on the array; keep
+ *     them on one stream or order them. */
 #define TQ_STATIC_SCRATCH_BYTES (8u << 20)
 int tq_decode_paged_static(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
                            int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,

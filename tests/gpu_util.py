@@ -26,7 +26,7 @@ def run_decode(q, cache_dev, block_table, seq_lens, sm_scale=None, out_dtype=Non
     B, Hq, D = q.shape
     H = cache_dev.shape[3]
     sm_scale = 1.0 / math.sqrt(D) if sm_scale is None else sm_scale
-    ws = torch.empty(_cabi.decode_workspace_bytes(B, Hq, H, D, num_ctas), dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(B, Hq, H, D, num_ctas), dtype=torch.uint8, device=DEV)
     out = torch.empty(B, Hq, D, dtype=out_dtype or q.dtype, device=DEV)
     lse = torch.empty(B, Hq, dtype=torch.float32, device=DEV) if want_lse else None
     _cabi.decode_paged(q, cache_dev, block_table, seq_lens, signs_dev(), sm_scale, ws, out,

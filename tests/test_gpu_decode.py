@@ -108,7 +108,7 @@ def test_partial_plus_merge_equals_full(oracle, golden):
     cache = torch.from_numpy(oracle_cache(oracle, case, golden["signs_seed42_d128"])).to(DEV)
     q, bt, sl = case.q.to(DEV), case.block_table.to(DEV), case.seq_lens.to(DEV)
     full = run_decode(q, cache, bt, sl, out_dtype=torch.float32)
-    ws = torch.empty(_cabi.decode_workspace_bytes(2, 32, 8), dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(2, 32, 8), dtype=torch.uint8, device=DEV)
     windows = [(0, 512), (512, 1024), (1024, -1), (2048, -1)]          # the last one is empty
     po = torch.empty(len(windows), 2, 32, 128, dtype=torch.float32, device=DEV)
     pl = torch.empty(len(windows), 2, 32, dtype=torch.float32, device=DEV)

@@ -31,7 +31,7 @@ def _case(seed, lens):
 
 
 def _reference(q, cache, bt, sl, signs):
-    ws = torch.empty(_cabi.decode_workspace_bytes(q.shape[0], 32, 8), dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(q.shape[0], 32, 8), dtype=torch.uint8, device=DEV)
     out = torch.empty(q.shape, dtype=torch.float32, device=DEV)
     lse = torch.empty(q.shape[:2], dtype=torch.float32, device=DEV)
     _cabi.decode_paged(q, cache, bt, sl, signs, SCALE, ws, out, out_lse=lse)

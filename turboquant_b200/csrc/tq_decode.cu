@@ -879,7 +879,9 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
         const __half h = __float2half_rn((float)kCentroidsN01_4bit[k]);
         p.centroid_h[k] = *reinterpret_cast<const uint16_t*>(&h);
     }
-    TQ_CUDA(cudaMemsetAsync(p.header, 0, 64, s));
+    // The status word (header[0]) is sticky: the kernels only ever raise it, nobody clears it here
+    // (a memset node per call costs more than it is worth); it means something to a caller who
+    // zeroed the first bytes of the workspace once.
     if (g_events[0]) TQ_CUDA(cudaEventRecord(g_events[0], s));
     switch (num_kv_heads) {
         case 8: rc = launch_decode<8>(p, ctas, s); break;

@@ -41,7 +41,7 @@ def _workspace(batch: int, hq: int, hkv: int, device) -> torch.Tensor:
     key = (device.index, batch, hq, hkv)
     ws = _workspaces.get(key)
     if ws is None:
-        ws = torch.empty(_cabi.decode_workspace_bytes(batch, hq, hkv), dtype=torch.uint8, device=device)
+        ws = torch.zeros(_cabi.decode_workspace_bytes(batch, hq, hkv), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 

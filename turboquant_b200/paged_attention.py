@@ -74,7 +74,7 @@ class TurboQuantPagedAttention:
         if ws is None:
             nbytes = _cabi.decode_workspace_bytes(batch, self.num_heads, self.num_kv_heads,
                                                   self.head_size, self.num_ctas)
-            ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)  # zeroed once: the status word is sticky
             self._workspaces[key] = ws
         return ws
 
