@@ -342,12 +342,14 @@ def run_ours(args):
     alg_bytes = B * L * HKV * ALG_BYTES_PER_TOKEN_HEAD
     peak, peak_src = measured_peak()
     achieved = alg_bytes / (dec_avg * 1e-3) / 1e9
-    # DRAM traffic per launch from the ncu capture summarised under profiles/ (physical slot
-    # bytes incl. the pad and the duplicate norm travel: 160 B per 136 algorithmic bytes)
-    traffic_per_alg_byte = 160.0 / 136.0
+    # DRAM traffic per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this
+    # kernel on this workload (profiles/decode_paged_kernel_config1_layer.md: 336.8 MB + 10.9 MB for
+    # batch 8 x ctx 32768), scaled by the tokens of the launch.  The physical slots are 160 B per 136
+    # algorithmic bytes, so 1.18x is the floor; the rest is the partial outputs.
+    traffic = 347.75e6 * (B * L) / (8 * 32768)
     roofline = {"bound": "hbm", "kernel": "decode_paged_kernel<8>", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-                "traffic": None, "expected_min_traffic": alg_bytes * traffic_per_alg_byte,
+                "traffic": traffic, "expected_min_traffic": alg_bytes * 160.0 / 136.0,
                 "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_ms": dec_avg,
                 "merge_avg_launch_ms": sum(mrg_ms) / len(mrg_ms),
                 "frac_whole_step": (alg_bytes * NL / (ms_step * 1e-3) / 1e9) / peak}
