@@ -45,7 +45,7 @@ struct WriteParams {
     int slot_is_i64;
     int zero_pad;
     const float* signs;       // [128] +-1, device
-    float neg_bnd_big[7];     // -(positive boundary j) * 2^40
+    float2 bin_table[16];     // per coarse bin of |y|: {-(boundary inside the bin) * 2^40 or -inf, boundaries below + 0.5}
     float fwht_scale;         // (float)(1/sqrt(128))
 };
 
@@ -58,16 +58,20 @@ __device__ __forceinline__ float fma_sat(float a, float b, float c) {
 // Code of y among the 15 symmetric boundaries (boundary 7 is 0, boundary 14-i = -boundary i) as
 // a float in 0..15: the number of boundaries strictly below y.  With a = |y|:
 //   y > 0 : 8 + #{pb_j < a};   y <= 0 : 7 - #{pb_j <= a} = 7 - #{pb_j < a + 1ulp}.
-// Each comparison is sat((a - pb_j) * 2^40): the FMA forms the difference exactly, a positive
-// difference is at least one ulp of pb_j (> 2^-30), so it saturates to exactly 1.
-__device__ __forceinline__ float code_f(float y, const float (&nb)[7]) {
+// The positive boundaries are at least 1/64 apart, so the bin k = round(min(64 a, 14)) holds at most
+// one of them: a 16-entry table gives the count of boundaries in lower bins and the boundary
+// inside the bin, and one exact comparison finishes the search.  The comparison is
+// sat((a - b) * 2^40): the FMA forms the difference exactly and a positive difference is at least
+// one ulp of b (> 2^-30), so it saturates to exactly 1.  The host builds the table with the same
+// float operations, which makes the binning consistent by construction.
+__device__ __forceinline__ float code_f(float y, const float2* table) {
     const bool pos = y > 0.0f;
     const float a = __uint_as_float((__float_as_uint(y) & 0x7fffffffu) + (pos ? 0u : 1u));
-    constexpr float kBig = 1099511627776.0f;  // 2^40
-    float m = fma_sat(a, kBig, nb[0]);
-#pragma unroll
-    for (int j = 1; j < 7; j++) m = __fadd_rn(m, fma_sat(a, kBig, nb[j]));
-    return pos ? __fadd_rn(8.0f, m) : __fsub_rn(7.0f, m);
+    const float t = fminf(__fmul_rn(a, 64.0f), 14.0f);
+    const uint32_t k = __float_as_uint(__fadd_rn(t, 8388608.0f)) & 15u;
+    const float2 e = table[k];
+    const float mm = __fadd_rn(e.y, fma_sat(a, 1099511627776.0f, e.x));  // boundaries below a, plus 0.5
+    return __fmaf_rn(pos ? 1.0f : -1.0f, mm, 7.5f);                        // 8 + m or 7 - m
 }
 
 template <typename T>
@@ -106,6 +110,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     // every warp runs its own two-buffer pipeline over 8-row pieces: no block-wide barrier in the loop
     __shared__ __align__(8) uint64_t full_bar[kWriteThreads / 32][2];
     __shared__ __align__(16) float signs_s[kD];
+    __shared__ __align__(8) float2 bins_s[16];
     __shared__ __align__(16) uint8_t out_s[kTileRows][64];  // code bytes of a tile, natural order
 
     const int tid = threadIdx.x;
@@ -126,6 +131,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     }
     if (tid == 0) fence_barrier_init();
     if (tid < kD) signs_s[tid] = p.signs[tid];
+    if (tid < 16) bins_s[tid] = p.bin_table[tid];
     __syncthreads();
 
     auto issue = [&](int64_t tile, int buf) {
@@ -229,14 +235,18 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
             x[j][1] = __fsub_rn(a, b);
         }
 #pragma unroll
-        for (int d = 1; d < 4; d <<= 1)
+        for (int d = 1; d < 4; d <<= 1) {
+            // upper partner: other - mine, lower partner: mine + other; one FMA with +-1 does both
+            // (the product with +-1 is exact, so the rounding is that of the plain add/sub)
+            const float sgn = (m & d) ? -1.0f : 1.0f;
 #pragma unroll
             for (int j = 0; j < 16; j++)
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
                     const float o = __shfl_xor_sync(0xffffffffu, x[j][e], d);
-                    x[j][e] = (m & d) ? __fsub_rn(o, x[j][e]) : __fadd_rn(x[j][e], o);
+                    x[j][e] = __fmaf_rn(x[j][e], sgn, o);
                 }
+        }
 #pragma unroll
         for (int hj = 1; hj < 16; hj <<= 1)
 #pragma unroll
@@ -255,10 +265,14 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         uint8_t* orow = out_s[row_in_tile];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            const float hi = code_f(__fmul_rn(x[j][0], p.fwht_scale), p.neg_bnd_big);
-            const float lo = code_f(__fmul_rn(x[j][1], p.fwht_scale), p.neg_bnd_big);
+            const float hi = code_f(__fmul_rn(x[j][0], p.fwht_scale), bins_s);
+            const float lo = code_f(__fmul_rn(x[j][1], p.fwht_scale), bins_s);
             const float bytef = __fadd_rn(__fmaf_rn(hi, 16.0f, lo), 8388608.0f);
-            orow[4 * j + m] = all_nan ? (uint8_t)0xff : (uint8_t)__float_as_uint(bytef);
+            orow[4 * j + m] = (uint8_t)__float_as_uint(bytef);
+        }
+        if (all_nan) {  // torch's bucketize sends NaN to the last bucket: every code is 15
+#pragma unroll
+            for (int j = 0; j < 16; j++) orow[4 * j + m] = 0xff;
         }
         __syncwarp();
         if (row_ok && slot >= 0) {
@@ -342,7 +356,27 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     p.signs = signs;
     float cen[16], bnd[15];
     host_codebook(kD, 4, cen, bnd);
-    for (int i = 0; i < 7; i++) p.neg_bnd_big[i] = -bnd[8 + i] * 1099511627776.0f;  // exact: a power of two
+    {   // coarse bins of |y| (same float operations as the kernel's code_f)
+        int bin_of[7];
+        for (int i = 0; i < 7; i++) {
+            volatile float t = bnd[8 + i] * 64.0f;
+            volatile float r = (t < 14.0f ? t : 14.0f) + 8388608.0f;
+            float rf = r;
+            uint32_t bits;
+            memcpy(&bits, &rf, 4);
+            bin_of[i] = (int)(bits & 15u);
+            TQ_REQUIRE(i == 0 || bin_of[i] > bin_of[i - 1], TQ_ERR_UNSUPPORTED, "boundaries too close for the bin table");
+        }
+        for (int k = 0; k < 16; k++) {
+            int below = 0;
+            float inside = -INFINITY;  // no boundary in this bin: the comparison yields 0
+            for (int i = 0; i < 7; i++) {
+                if (bin_of[i] < k) below++;
+                if (bin_of[i] == k) inside = -bnd[8 + i] * 1099511627776.0f;  // exact: a power of two
+            }
+            p.bin_table[k] = make_float2(inside, (float)below + 0.5f);
+        }
+    }
     p.fwht_scale = (float)(1.0 / sqrt((double)kD));
     int sms = 0;
     int rc = device_sm_count(&sms);
