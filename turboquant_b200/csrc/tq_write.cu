@@ -74,6 +74,25 @@ __device__ __forceinline__ float code_f(float y, const float2* table) {
     return __fmaf_rn(pos ? 1.0f : -1.0f, mm, 7.5f);                        // 8 + m or 7 - m
 }
 
+// Two fp32 values in one 64-bit register and the packed arithmetic of sm_100 (add/sub/mul/fma
+// .f32x2): each lane of a pair is rounded to nearest exactly like the scalar instruction, at half
+// the instruction count.  A lane's elements (8j + 2m, 8j + 2m + 1) form the natural pairs.
+struct P2 { unsigned long long v; };
+__device__ __forceinline__ P2 pk(float lo, float hi) {
+    P2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void up(P2 a, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.v)); }
+__device__ __forceinline__ P2 add2(P2 a, P2 b) { P2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+__device__ __forceinline__ P2 sub2(P2 a, P2 b) { P2 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+__device__ __forceinline__ P2 mul2(P2 a, P2 b) { P2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+__device__ __forceinline__ P2 fma2(P2 a, P2 b, P2 c) {
+    P2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+    return r;
+}
+
 template <typename T>
 struct RowLoad;
 
@@ -176,20 +195,23 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         // all lanes run the arithmetic (the shuffles need whole quads); rows past the end or with
         // a negative slot read whatever is staged and store nothing
         const uint8_t* row = smem + (size_t)buf * kTileRows * kPitch + (size_t)row_in_tile * kPitch;
-        float x[16][2];
-        float acc0 = 0.0f, acc1 = 0.0f, minsq = 1.0f;
+        P2 x[16];
+        P2 acc = pk(0.0f, 0.0f);
+        float minsq = 1.0f;
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             const float2 v = row_ok ? L::pair(row, j, m) : make_float2(0.f, 0.f);
-            x[j][0] = v.x;
-            x[j][1] = v.y;
+            x[j] = pk(v.x, v.y);
             // accumulators 2m and 2m+1 of the eight interleaved ones, in order of j, product
             // rounded before the add
-            const float s0 = __fmul_rn(v.x, v.x), s1 = __fmul_rn(v.y, v.y);
-            acc0 = __fadd_rn(acc0, s0);
-            acc1 = __fadd_rn(acc1, s1);
+            const P2 sq = mul2(x[j], x[j]);
+            acc = add2(acc, sq);
+            float s0, s1;
+            up(sq, s0, s1);
             minsq = fminf(minsq, fminf(s0, s1));
         }
+        float acc0, acc1;
+        up(acc, acc0, acc1);
         // combine the eight accumulators left to right
         float s = 0.0f;
 #pragma unroll
@@ -212,61 +234,64 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
                           (nbits & 0x7fffffu) != 0x7fffffu;
         if (fast) {
             const float rcp = __frcp_rn(norm);
+            const P2 rcp2 = pk(rcp, rcp), nneg2 = pk(-norm, -norm);
 #pragma unroll
-            for (int j = 0; j < 16; j++)
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const float q = __fmul_rn(x[j][e], rcp);
-                    const float err = __fmaf_rn(-q, norm, x[j][e]);
-                    x[j][e] = __fmaf_rn(err, rcp, q);
-                }
+            for (int j = 0; j < 16; j++) {
+                const P2 q = mul2(x[j], rcp2);
+                const P2 err = fma2(q, nneg2, x[j]);   // x - q * norm, exact
+                x[j] = fma2(err, rcp2, q);
+            }
         } else {
 #pragma unroll
-            for (int j = 0; j < 16; j++)
-#pragma unroll
-                for (int e = 0; e < 2; e++) x[j][e] = __fdiv_rn(x[j][e], norm);
+            for (int j = 0; j < 16; j++) {
+                float a, b;
+                up(x[j], a, b);
+                x[j] = pk(__fdiv_rn(a, norm), __fdiv_rn(b, norm));
+            }
         }
         // signs, then butterflies in stage order h = 1, 2, 4 (lanes), 8..64 (j)
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             const float2 sg = *reinterpret_cast<const float2*>(&signs_s[8 * j + 2 * m]);
-            const float a = __fmul_rn(x[j][0], sg.x), b = __fmul_rn(x[j][1], sg.y);
-            x[j][0] = __fadd_rn(a, b);
-            x[j][1] = __fsub_rn(a, b);
+            float a, b;
+            up(mul2(x[j], pk(sg.x, sg.y)), a, b);
+            x[j] = pk(__fadd_rn(a, b), __fsub_rn(a, b));
         }
 #pragma unroll
         for (int d = 1; d < 4; d <<= 1) {
             // upper partner: other - mine, lower partner: mine + other; one FMA with +-1 does both
             // (the product with +-1 is exact, so the rounding is that of the plain add/sub)
             const float sgn = (m & d) ? -1.0f : 1.0f;
+            const P2 sgn2 = pk(sgn, sgn);
 #pragma unroll
-            for (int j = 0; j < 16; j++)
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const float o = __shfl_xor_sync(0xffffffffu, x[j][e], d);
-                    x[j][e] = __fmaf_rn(x[j][e], sgn, o);
-                }
+            for (int j = 0; j < 16; j++) {
+                float a, b;
+                up(x[j], a, b);
+                const float oa = __shfl_xor_sync(0xffffffffu, a, d), ob = __shfl_xor_sync(0xffffffffu, b, d);
+                x[j] = fma2(x[j], sgn2, pk(oa, ob));
+            }
         }
 #pragma unroll
         for (int hj = 1; hj < 16; hj <<= 1)
 #pragma unroll
             for (int j = 0; j < 16; j++)
                 if (!(j & hj)) {
-#pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const float a = x[j][e], b = x[j + hj][e];
-                        x[j][e] = __fadd_rn(a, b);
-                        x[j + hj][e] = __fsub_rn(a, b);
-                    }
+                    const P2 a = x[j], b = x[j + hj];
+                    x[j] = add2(a, b);
+                    x[j + hj] = sub2(a, b);
                 }
+        const P2 scale2 = pk(p.fwht_scale, p.fwht_scale);
+        float y[16][2];
+#pragma unroll
+        for (int j = 0; j < 16; j++) up(mul2(x[j], scale2), y[j][0], y[j][1]);
         // scale, code, pack: byte 4j + m = (code(even dim) << 4) | code(odd dim), via the low
         // byte of a float with 2^23 added
-        const bool all_nan = x[0][0] != x[0][0];  // a non-finite input turns the whole row into NaN
+        const bool all_nan = y[0][0] != y[0][0];  // a non-finite input turns the whole row into NaN
         uint8_t* orow = out_s[row_in_tile];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            const float hi = code_f(__fmul_rn(x[j][0], p.fwht_scale), bins_s);
-            const float lo = code_f(__fmul_rn(x[j][1], p.fwht_scale), bins_s);
+            const float hi = code_f(y[j][0], bins_s);
+            const float lo = code_f(y[j][1], bins_s);
             const float bytef = __fadd_rn(__fmaf_rn(hi, 16.0f, lo), 8388608.0f);
             orow[4 * j + m] = (uint8_t)__float_as_uint(bytef);
         }
