@@ -125,6 +125,26 @@ int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads, int 
                     void* workspace, size_t workspace_bytes, void* out, int out_dtype,
                     float* out_lse, int num_ctas, void* stream);
 
+/* tq_decode_paged for sequences that carry several decode queries sharing one KV (the 8 queries
+ * of the 1M-token configuration, or any caller that would otherwise repeat a sequence as batch
+ * rows): q and out are [batch][queries_per_seq][num_q_heads][head_dim], out_lse
+ * [batch][queries_per_seq][num_q_heads]; seq_lens and the page table are per sequence.  The
+ * queries ride in the otherwise padded columns of the 8-wide query tile, so the KV is streamed
+ * and dequantized once for all of them: queries_per_seq x (num_q_heads / num_kv_heads) <= 8.
+ * The workspace is sized with tq_decode_workspace_bytes(batch, queries_per_seq * num_q_heads, ...).
+ * kv_begin / kv_end restrict the tokens as in tq_decode_paged_partial (0, -1: all of them);
+ * rotated_partial != 0 makes out (fp32) and out_lse (required) the rotated-domain partial and
+ * base-2 LSE that tq_merge_rotated takes, rows ordered [batch][queries_per_seq][num_q_heads].
+ * The reference's ops have no such mode: there each query is a batch row that re-reads the KV
+ * (csrc/src/decode_v5_tc_binding.cu:783-785). */
+int tq_decode_paged_multi(const void* q, int q_dtype, int batch, int queries_per_seq, int num_q_heads,
+                          int num_kv_heads, int head_dim, const void* kv_cache, int64_t num_blocks,
+                          int block_size, int slot_bytes, const int32_t* page_indices,
+                          const int32_t* page_indptr, int max_pages, const int32_t* seq_lens,
+                          int64_t kv_begin, int64_t kv_end, const float* signs, float sm_scale,
+                          void* workspace, size_t workspace_bytes, void* out, int out_dtype, float* out_lse,
+                          int rotated_partial, int num_ctas, void* stream);
+
 /* As tq_decode_paged, but stops before the inverse rotation: writes the merged, normalized,
  * still-rotated output (fp32 [batch][num_q_heads][head_dim]) and its base-2 LSE, restricted to
  * tokens [kv_begin, kv_end) of every sequence (kv_end < 0: to the end).  This is the per-GPU

@@ -178,3 +178,46 @@ def test_config1_full_size_properties():
     out2 = run_decode(q, cache, bt, sl2, out_dtype=torch.float32).cpu().numpy()
     assert np.abs(out2[2:] - ref[2:]).max() <= 2e-4
     assert np.abs(out2[0] - ref[0]).max() > 1e-4
+
+
+@pytest.mark.parametrize("nq,hq,hkv", [(2, 32, 8), (8, 8, 8), (3, 8, 4), (4, 4, 2), (1, 32, 8)])
+def test_shared_kv_queries_match_repeated_rows(oracle, golden, nq, hq, hkv):
+    """Several queries per sequence (tq_decode_paged_multi) against (a) the oracle with each query
+    as its own batch row and (b) tq_decode_paged on the same repeated rows."""
+    lens = [40, 0, 1000, 16, 2100]
+    B = len(lens)
+    case = synthetic.decode_case(seed=77 + nq, seq_lens=lens, heads=(hq, hkv), dtype=torch.float16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, nq, hq, 128, generator=g).to(torch.float16)
+    rep_bt = case.block_table.repeat_interleave(nq, dim=0)
+    rep_len = case.seq_lens.repeat_interleave(nq)
+    want, want_lse = oracle.decode_paged(q.view(B * nq, hq, 128).float().numpy(), cache, rep_bt.numpy(),
+                                         rep_len.numpy(), golden["signs_seed42_d128"], SCALE, return_lse=True)
+    cache_d = torch.from_numpy(cache).to(DEV)
+    rows, rows_lse = run_decode(q.view(B * nq, hq, 128).to(DEV), cache_d, rep_bt.to(DEV), rep_len.to(DEV),
+                                want_lse=True)
+    for ctas in (0, 3):
+        ws = torch.zeros(_cabi.decode_workspace_bytes(B, nq * hq, hkv, 128, ctas), dtype=torch.uint8, device=DEV)
+        out = torch.full((B, nq, hq, 128), float("nan"), dtype=torch.float16, device=DEV)
+        lse = torch.empty(B, nq, hq, dtype=torch.float32, device=DEV)
+        _cabi.decode_paged_multi(q.to(DEV), cache_d, case.block_table.to(DEV), case.seq_lens.to(DEV), signs_dev(),
+                                 SCALE, ws, out, out_lse=lse, num_ctas=ctas)
+        torch.cuda.synchronize()
+        assert ws[:4].view(torch.int32).item() == 0
+        got = out.float().cpu().numpy().reshape(B * nq, hq, 128)
+        assert_attention_close(got, want, f"shared KV nq={nq} ctas={ctas}")
+        assert_attention_close(got, rows.float().cpu().numpy(), f"shared KV vs repeated rows nq={nq}")
+        assert (got.reshape(B, nq, hq, 128)[1] == 0).all()
+        ok = np.isfinite(want_lse)
+        np.testing.assert_allclose(lse.cpu().numpy().reshape(B * nq, hq)[ok], want_lse[ok], atol=2e-3)
+
+
+def test_shared_kv_rejects_more_than_8_columns():
+    q = torch.zeros(1, 3, 32, 128, dtype=torch.float16, device=DEV)
+    cache = torch.zeros(2, 4, 16, 8, 80, dtype=torch.uint8, device=DEV)
+    bt = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+    sl = torch.ones(1, dtype=torch.int32, device=DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(1, 96, 8, 128, 0), dtype=torch.uint8, device=DEV)
+    with pytest.raises(_cabi.TurboQuantError, match="queries_per_seq"):
+        _cabi.decode_paged_multi(q, cache, bt, sl, signs_dev(), SCALE, ws, torch.empty_like(q))

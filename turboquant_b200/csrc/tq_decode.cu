@@ -87,7 +87,12 @@ struct DecodeParams {
     float* partial_o;       // workspace: [slots][num_q_heads][128]
     int64_t slab_bytes;
     int64_t kv_begin, kv_end;  // token window applied to every sequence (kv_end < 0: none)
+    // A sequence may carry several decode queries that share its KV (queries_per_seq).  Inside the
+    // kernels they are extra columns of the query tile: num_q_heads and group below are the VIRTUAL
+    // counts (queries_per_seq x the real ones), column c of a KV head being query c / real_group,
+    // head c % real_group.  real_heads / real_group / nq give the layout of q and out.
     int batch, num_q_heads, group, max_pages, q_dtype;
+    int nq, real_heads, real_group;
     float k_scale;  // (1/sqrt(128)) * sm_scale * log2(e): multiplies raw code-domain scores
     float v_scale;  // 1/sqrt(128): centroid scale folded into P
     int num_stages;         // ring depth (3 or 4), chosen by the host from the shared-memory budget
@@ -363,10 +368,11 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             seq_pages(p, b, first_page, npages_b, len_eff);
             const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
             const int p0 = seg_p0[sg], p1 = seg_p1[sg];
-            for (int base = p0; base < p1; base += 32) {
+            constexpr int kIdBlock = (32 / PPS) * PPS;  // page ids fetched per round: a whole number of stages
+            for (int base = p0; base < p1; base += kIdBlock) {
                 const int mine = base + lane;
                 const int my_page = mine < p1 ? p.page_indices[tbl + first_page + mine] : 0;
-                const int cnt = (p1 - base) < 32 ? (p1 - base) : 32;
+                const int cnt = (p1 - base) < kIdBlock ? (p1 - base) : kIdBlock;
                 for (int j = 0; j < cnt; j += PPS) {
                     const int np = (cnt - j) < PPS ? (cnt - j) : PPS;
                     if (round > 0) {
@@ -440,7 +446,9 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
 #pragma unroll
             for (int rr = 0; rr < 4; rr++) {
                 const int r = r0 + rr < p.group ? r0 + rr : p.group - 1;
-                const int64_t base = ((int64_t)b * p.num_q_heads + head * p.group + r) * kHeadDim + 4 * lane;
+                const int qi = r / p.real_group, hh = r - qi * p.real_group;
+                const int64_t base = ((((int64_t)b * p.nq + qi) * p.real_heads) + head * p.real_group + hh) * kHeadDim +
+                                     4 * lane;
                 if (p.q_dtype == TQ_BF16) {
                     const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + base);
                     v[rr][0] = __uint_as_float(t.x << 16); v[rr][1] = __uint_as_float(t.x & 0xffff0000u);
@@ -649,6 +657,7 @@ struct MergeParams {
     float* out_lse;   // natural-log LSE (final) or base-2 LSE (rotated output), optional
     int64_t rows;     // batch (decode merge) or rows (generic merge)
     int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
+    int nq, real_heads, real_group;  // virtual head -> (query, real head) of the output row; nq = 1: identity
 };
 
 // One block per (row, query head), four warps.  Warp w takes parts w, w+4, ...; lane l owns
@@ -733,7 +742,13 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     }
     o = wtot > 0.f ? o / wtot : 0.f;
     const float lse2 = wtot > 0.f ? mm + log2f(wtot) : -INFINITY;
-    const int64_t orow = row * p.num_q_heads + hq;
+    int64_t orow = row * p.num_q_heads + hq;
+    if (p.nq > 1) {  // virtual head hq = kv_head * cols + (query * real_group + head_in_group)
+        const int cols = p.nq * p.real_group;
+        const int kvh = hq / cols, col = hq - kvh * cols;
+        const int qi = col / p.real_group, hh = col - qi * p.real_group;
+        orow = (row * p.nq + qi) * p.real_heads + kvh * p.real_group + hh;
+    }
     if (p.emit_rotated) {
         reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
         if (p.out_lse && d == 0) p.out_lse[orow] = lse2;
@@ -821,7 +836,7 @@ static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
     return launch_decode_impl<HKV, false>(p, grid, S::total(stages, p.group), stream);
 }
 
-static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
+static int decode_common(const void* q, int q_dtype, int batch, int nq, int real_q_heads, int num_kv_heads,
                          int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,
                          int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
                          int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
@@ -836,9 +851,11 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
     TQ_REQUIRE(slot_bytes == kSlotBytes, TQ_ERR_UNSUPPORTED, "decode supports 80-byte slots, got %d", slot_bytes);
     TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8,
                TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4 or 8, got %d", num_kv_heads);
-    TQ_REQUIRE(num_q_heads % num_kv_heads == 0 && num_q_heads / num_kv_heads >= 1 &&
-                   num_q_heads / num_kv_heads <= 8,
-               TQ_ERR_UNSUPPORTED, "query heads per KV head must be 1..8");
+    TQ_REQUIRE(nq >= 1 && real_q_heads >= 1 && real_q_heads % num_kv_heads == 0, TQ_ERR_INVALID,
+               "query heads must be a positive multiple of the KV heads, queries_per_seq >= 1");
+    TQ_REQUIRE(nq * (real_q_heads / num_kv_heads) <= 8, TQ_ERR_UNSUPPORTED,
+               "queries_per_seq x query heads per KV head must be 1..8 (got %d x %d)", nq, real_q_heads / num_kv_heads);
+    const int num_q_heads = nq * real_q_heads;  // virtual heads
     TQ_REQUIRE(q_dtype >= TQ_F32 && q_dtype <= TQ_BF16 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16,
                TQ_ERR_INVALID, "bad dtype");
     TQ_REQUIRE(((uintptr_t)kv_cache % 16) == 0 && ((uintptr_t)workspace % 256) == 0, TQ_ERR_INVALID,
@@ -870,6 +887,9 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
     p.batch = batch;
     p.num_q_heads = num_q_heads;
     p.group = num_q_heads / num_kv_heads;
+    p.nq = nq;
+    p.real_heads = real_q_heads;
+    p.real_group = real_q_heads / num_kv_heads;
     p.max_pages = max_pages;
     p.q_dtype = q_dtype;
     const double inv_sqrt_d = 1.0 / std::sqrt((double)kHeadDim);
@@ -902,6 +922,9 @@ static int decode_common(const void* q, int q_dtype, int batch, int num_q_heads,
     m.out_lse = out_lse;
     m.rows = batch;
     m.num_q_heads = num_q_heads;
+    m.nq = nq;
+    m.real_heads = real_q_heads;
+    m.real_group = real_q_heads / num_kv_heads;
     m.pps = kConsumerWarps / num_kv_heads;
     m.grid_ctas = ctas;
     m.out_dtype = out_dtype;
@@ -937,10 +960,28 @@ extern "C" int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_
                                int max_pages, const int32_t* seq_lens, const float* signs,
                                float sm_scale, void* workspace, size_t workspace_bytes, void* out,
                                int out_dtype, float* out_lse, int num_ctas, void* stream) {
-    return tq::decode_common(q, q_dtype, batch, num_q_heads, num_kv_heads, head_dim, kv_cache,
+    return tq::decode_common(q, q_dtype, batch, 1, num_q_heads, num_kv_heads, head_dim, kv_cache,
                              num_blocks, block_size, slot_bytes, page_indices, page_indptr,
                              max_pages, seq_lens, 0, -1, signs, sm_scale, workspace, workspace_bytes,
                              out, out_dtype, out_lse, 0, num_ctas, stream);
+}
+
+extern "C" int tq_decode_paged_multi(const void* q, int q_dtype, int batch, int queries_per_seq,
+                                     int num_q_heads, int num_kv_heads, int head_dim, const void* kv_cache,
+                                     int64_t num_blocks, int block_size, int slot_bytes,
+                                     const int32_t* page_indices, const int32_t* page_indptr, int max_pages,
+                                     const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
+                                     const float* signs, float sm_scale, void* workspace,
+                                     size_t workspace_bytes, void* out, int out_dtype, float* out_lse,
+                                     int rotated_partial, int num_ctas, void* stream) {
+    if (rotated_partial) {
+        TQ_REQUIRE(out_lse != nullptr && out_dtype == TQ_F32, TQ_ERR_INVALID,
+                   "a rotated partial needs fp32 out and out_lse");
+    }
+    return tq::decode_common(q, q_dtype, batch, queries_per_seq, num_q_heads, num_kv_heads, head_dim, kv_cache,
+                             num_blocks, block_size, slot_bytes, page_indices, page_indptr, max_pages,
+                             seq_lens, kv_begin, kv_end, signs, sm_scale, workspace, workspace_bytes, out,
+                             out_dtype, out_lse, rotated_partial ? 1 : 0, num_ctas, stream);
 }
 
 extern "C" int tq_decode_paged_partial(const void* q, int q_dtype, int batch, int num_q_heads,
@@ -951,7 +992,7 @@ extern "C" int tq_decode_paged_partial(const void* q, int q_dtype, int batch, in
                                        int64_t kv_end, const float* signs, float sm_scale,
                                        void* workspace, size_t workspace_bytes, float* out_rot,
                                        float* out_lse2, int num_ctas, void* stream) {
-    return tq::decode_common(q, q_dtype, batch, num_q_heads, num_kv_heads, head_dim, kv_cache,
+    return tq::decode_common(q, q_dtype, batch, 1, num_q_heads, num_kv_heads, head_dim, kv_cache,
                              num_blocks, block_size, slot_bytes, page_indices, page_indptr,
                              max_pages, seq_lens, kv_begin, kv_end, signs, sm_scale, workspace,
                              workspace_bytes, out_rot, TQ_F32, out_lse2, 1, num_ctas, stream);
@@ -974,6 +1015,7 @@ extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse
     m.out_lse = out_lse;
     m.rows = rows;
     m.num_q_heads = 1;
+    m.nq = 1;
     m.num_parts = num_parts;
     m.out_dtype = out_dtype;
     merge_kernel<<<dim3((unsigned)rows, 1), kHeadDim, 0, static_cast<cudaStream_t>(stream)>>>(m);
@@ -1037,7 +1079,7 @@ extern "C" int tq_decode_paged_static(const void* q, int q_dtype, int batch, int
     void* scratch = nullptr;
     rc = static_scratch_pointer(&scratch);
     if (rc != TQ_OK) return rc;
-    return decode_common(q, q_dtype, batch, num_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks,
+    return decode_common(q, q_dtype, batch, 1, num_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks,
                          block_size, slot_bytes, page_indices, page_indptr, max_pages, seq_lens, 0, -1,
                          signs, sm_scale, scratch, kStaticScratchBytes, out, out_dtype, out_lse, 0, ctas,
                          stream);

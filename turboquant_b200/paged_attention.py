@@ -65,14 +65,14 @@ class TurboQuantPagedAttention:
             self._signs[device] = s
         return s
 
-    def workspace(self, batch: int, device) -> torch.Tensor:
+    def workspace(self, batch: int, device, queries: int = 1) -> torch.Tensor:
         device = torch.device(device)
         if device.type == "cuda" and device.index is None:
             device = torch.device("cuda", torch.cuda.current_device())
-        key = (device, batch)
+        key = (device, batch, queries)
         ws = self._workspaces.get(key)
         if ws is None:
-            nbytes = _cabi.decode_workspace_bytes(batch, self.num_heads, self.num_kv_heads,
+            nbytes = _cabi.decode_workspace_bytes(batch, queries * self.num_heads, self.num_kv_heads,
                                                   self.head_size, self.num_ctas)
             ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)  # zeroed once: the status word is sticky
             self._workspaces[key] = ws
@@ -96,6 +96,8 @@ class TurboQuantPagedAttention:
     def decode(self, query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor,
                seq_lens: torch.Tensor, output: torch.Tensor | None = None,
                out_lse: torch.Tensor | None = None) -> torch.Tensor:
+        if query.dim() == 4:
+            return self.decode_shared(query, kv_cache, block_table, seq_lens, output, out_lse)
         if query.dim() == 2:
             query = query.view(query.shape[0], self.num_heads, self.head_size)
         if output is None:
@@ -110,6 +112,27 @@ class TurboQuantPagedAttention:
                            out3, out_lse=out_lse, num_ctas=self.num_ctas, max_pages=block_table.shape[-1])
         return output
 
-    def status(self, batch: int, device) -> int:
+    def decode_shared(self, query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor,
+                      seq_lens: torch.Tensor, output: torch.Tensor | None = None,
+                      out_lse: torch.Tensor | None = None) -> torch.Tensor:
+        """Decode for ``query`` [batch, queries, heads, head_size] where the queries of one row share
+        that row's KV (one ``seq_lens`` / ``block_table`` entry per row).  The reference would repeat
+        the row ``queries`` times in the batch (its decode op has one query per batch row,
+        csrc/src/decode_v5_tc_binding.cu:783-785) and stream the KV once per repeat; here the KV
+        is streamed once.  queries x (heads / kv_heads) must not exceed 8."""
+        B, NQ = query.shape[0], query.shape[1]
+        if output is None:
+            output = torch.empty_like(query)
+        if block_table.dtype != torch.int32:
+            block_table = block_table.to(torch.int32)
+        if seq_lens.dtype != torch.int32:
+            seq_lens = seq_lens.to(torch.int32)
+        _cabi.decode_paged_multi(query.contiguous(), self._as_bytes(kv_cache), block_table.contiguous(), seq_lens,
+                                 self.signs(query.device), self.scale, self.workspace(B, query.device, NQ),
+                                 output.view(B, NQ, self.num_heads, self.head_size), out_lse=out_lse,
+                                 num_ctas=self.num_ctas, max_pages=block_table.shape[-1])
+        return output
+
+    def status(self, batch: int, device, queries: int = 1) -> int:
         """Status word the decode kernel leaves in its workspace (0 = ok); synchronises."""
-        return int(self.workspace(batch, device)[:4].view(torch.int32).item())
+        return int(self.workspace(batch, device, queries)[:4].view(torch.int32).item())

@@ -58,14 +58,20 @@ def all_gather_partials(part_o: torch.Tensor, part_lse2: torch.Tensor, group=Non
 
 def kv_split_decode(attn, query, kv_cache_local, block_table_local, seq_lens_local, output, group=None):
     """Decode ``query`` against a KV cache whose token axis is split over the ranks of ``group``.
-    Every rank passes the part of the cache it holds (its own block table and local lengths)."""
+    Every rank passes the part of the cache it holds (its own block table and local lengths).
+    ``query`` is [rows, heads, D], or [rows, queries, heads, D] when the queries of a row share
+    that row's KV (streamed once for all of them)."""
     from . import _cabi
-    b, hq, d = query.shape
     dev = query.device
-    part_o = torch.empty((b, hq, d), dtype=torch.float32, device=dev)
-    part_l = torch.empty((b, hq), dtype=torch.float32, device=dev)
-    _cabi.decode_paged_partial(query, attn._as_bytes(kv_cache_local), block_table_local, seq_lens_local,
-                               attn.signs(dev), attn.scale, attn.workspace(b, dev), part_o, part_l)
+    part_o = torch.empty(tuple(query.shape), dtype=torch.float32, device=dev)
+    part_l = torch.empty(tuple(query.shape[:-1]), dtype=torch.float32, device=dev)
+    if query.dim() == 4:
+        _cabi.decode_paged_multi(query, attn._as_bytes(kv_cache_local), block_table_local, seq_lens_local,
+                                 attn.signs(dev), attn.scale, attn.workspace(query.shape[0], dev, query.shape[1]),
+                                 part_o, out_lse=part_l, rotated_partial=True)
+    else:
+        _cabi.decode_paged_partial(query, attn._as_bytes(kv_cache_local), block_table_local, seq_lens_local,
+                                   attn.signs(dev), attn.scale, attn.workspace(query.shape[0], dev), part_o, part_l)
     o, l = all_gather_partials(part_o, part_l, group)
     _cabi.merge_rotated(o, l, attn.signs(dev), output)
     return output
