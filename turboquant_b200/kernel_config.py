@@ -68,6 +68,10 @@ def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> Kernel
         kp = row + 48 + ((64 - (row + 48) % 128) % 128)
         vp = row + ((16 - row % 64) % 64)
         stage = pps * PAGE_TOKENS * (kp + vp)
+    if h == 8 and g <= 4:
+        # wide lookup table (256 B per entry at the 64 KB boundary of the shared window): fixed map
+        # with three stages, one below the table and two above it
+        return KernelConfig(CONSUMER_WARPS, pps, 3, stage)
     fixed = 256 * 32 * 4 + CONSUMER_WARPS * max(g, 4) * 128 * 2 + 2048
     stages = 4
     while stages > 2 and stages * stage + fixed > MAX_SMEM:
