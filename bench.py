@@ -54,6 +54,9 @@ def parse():
     ap.add_argument("--num-ctas", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="config4 on several GPUs: partials exchanged by the kernels themselves (peer stores + "
+                         "flags) or by an NCCL all-gather")
     ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4"],
                     help="config1 (default, the headline): batch 8 x 32k per GPU; config3: 64 mixed lengths sharded by "
                          "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge")
@@ -544,8 +547,15 @@ def run_config4(args):
     sl = torch.full((rows,), n_local, dtype=torch.int32, device=dev)
     out = torch.empty_like(q)
 
+    fused = world > 1 and args.exchange == "fused"
+    if fused:
+        from turboquant_b200.parallel import KVSplitExchange
+        ex = KVSplitExchange(attn, rows, share, dev)
+
     def step():
-        if world > 1:
+        if fused:
+            ex.decode(q, cache, bt, sl, out)
+        elif world > 1:
             kv_split_decode(attn, q, cache, bt, sl, out)
         else:
             attn.decode(q, cache, bt, sl, out)
@@ -561,8 +571,11 @@ def run_config4(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "config4: one 1,048,576-token sequence, 8 decode queries, one layer, KV axis split "
-                                   "contiguously over the GPUs, partial (o, lse) all-gathered over NCCL, merged on every GPU",
+                                   "contiguously over the GPUs, partial (o, lse) exchanged, merged on every GPU",
                        "exchange_bytes_per_rank": nq * HQ * (D + 1) * 4,
+                       "exchange": ("none (one GPU)" if world == 1 else
+                                    "kernel-side: peer stores into every rank's buffer + flags, flag-gated merge"
+                                    if fused else "NCCL all-gather of the partials, then merge"),
                        "note": "the 8 queries run as 4 rows of 2 queries that share one pass over the KV (8 batch rows, "
                                "each streaming the KV, through the reference's API); the algorithmic bytes below "
                                "count the KV once",
@@ -570,7 +583,7 @@ def run_config4(args):
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak * world, "unit": "GB/s",
                          "frac": ach / (peak * world), "peak_source": peak_src, "algorithmic_bytes_per_launch": alg,
                          "physical_kv_bytes_streamed": rows * total * HKV * 160},
-            "gpu_launches": args.steps * 2 + (args.steps if world > 1 else 0)}), flush=True)
+            "gpu_launches": args.steps * (3 if world > 1 else 2)}), flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()

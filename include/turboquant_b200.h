@@ -145,6 +145,30 @@ int tq_decode_paged_multi(const void* q, int q_dtype, int batch, int queries_per
                           void* workspace, size_t workspace_bytes, void* out, int out_dtype, float* out_lse,
                           int rotated_partial, int num_ctas, void* stream);
 
+/* One long sequence whose KV axis is split over `world` GPUs (one process per GPU): decode this
+ * rank's token range, push the rotated partial + LSE into EVERY rank's exchange buffer with plain
+ * peer stores (NVLink), release a per-source flag, then wait (bounded, about a second) until all
+ * ranks' partials of this step have arrived in this rank's buffer, merge them and rotate back.
+ * Every rank ends with the same full `out`.  Arguments as tq_decode_paged_multi, plus:
+ *   exchange_bufs  host array [world] of device pointers: rank r's exchange buffer as mapped in
+ *                  THIS process (symmetric memory / IPC); exchange_bufs[rank] is this rank's own.
+ *                  Each is tq_exchange_bytes(batch * queries_per_seq * num_q_heads, world) bytes,
+ *                  256-byte aligned, zeroed once on every rank before any rank's first call.
+ * The step counter lives in the buffer, so the call can be captured in a CUDA graph and replayed.
+ * Word 1 of the buffer is a sticky status: 1 = a wait for a peer ran out (out is then not written).
+ * All ranks must make the same sequence of calls.  Replaces the reference-side plan of an
+ * all-gather of split partials followed by SplitKVCombineKernel (combine.cuh:18-79) across GPUs;
+ * the reference itself has no multi-GPU decode. */
+size_t tq_exchange_bytes(int64_t rows, int world);
+int tq_decode_paged_exchange(const void* q, int q_dtype, int batch, int queries_per_seq, int num_q_heads,
+                             int num_kv_heads, int head_dim, const void* kv_cache, int64_t num_blocks,
+                             int block_size, int slot_bytes, const int32_t* page_indices,
+                             const int32_t* page_indptr, int max_pages, const int32_t* seq_lens,
+                             int64_t kv_begin, int64_t kv_end, const float* signs, float sm_scale,
+                             void* workspace, size_t workspace_bytes, int rank, int world,
+                             void* const* exchange_bufs, size_t exchange_bytes, void* out, int out_dtype,
+                             float* out_lse, int num_ctas, void* stream);
+
 /* As tq_decode_paged, but stops before the inverse rotation: writes the merged, normalized,
  * still-rotated output (fp32 [batch][num_q_heads][head_dim]) and its base-2 LSE, restricted to
  * tokens [kv_begin, kv_end) of every sequence (kv_end < 0: to the end).  This is the per-GPU

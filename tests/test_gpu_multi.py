@@ -1,5 +1,7 @@
-"""KV-axis split of one long sequence over two GPUs (NCCL all-gather of the partials + LSE merge),
-checked against the single-GPU result and the oracle.  Needs two GPUs; skipped otherwise."""
+"""KV-axis split of one long sequence over two GPUs, checked against the single-GPU result and the
+oracle: NCCL all-gather of the partials + LSE merge, and the kernel-side exchange (peer stores +
+flags).  The two-GPU cases are skipped on a single GPU; the exchange protocol with one rank
+(its own buffer as the only peer) runs everywhere."""
 import os
 import subprocess
 import sys
@@ -18,7 +20,7 @@ import numpy as np, torch, torch.distributed as dist
 from oracle import tq_oracle
 from turboquant_b200 import synthetic
 from turboquant_b200.paged_attention import TurboQuantPagedAttention
-from turboquant_b200.parallel import kv_ranges, kv_split_decode
+from turboquant_b200.parallel import kv_ranges, kv_split_decode, KVSplitExchange
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dev = torch.device("cuda", rank)
@@ -53,6 +55,21 @@ assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-2
 gathered = [torch.empty_like(out) for _ in range(world)]
 dist.all_gather(gathered, out)
 assert all(torch.equal(g, gathered[0]) for g in gathered)      # every rank ends with the same result
+# the same through the kernel-side exchange, several steps in a row (both buffer generations), 3 queries = 3 rows
+ex = KVSplitExchange(attn, nq, 1, dev)
+q4 = case.q.to(dev).view(nq, 1, 32, 128)
+for step in range(5):
+    out2 = torch.full((nq, 1, 32, 128), float("nan"), dtype=torch.float32, device=dev)
+    ex.decode(q4 * (1.0 + step), cache, bt, sl, out2)
+    if step == 0:
+        torch.cuda.synchronize()
+        assert ex.status() == 0
+        assert torch.equal(out2.view(nq, 32, 128), out), float((out2.view(nq, 32, 128) - out).abs().max())
+torch.cuda.synchronize()
+assert ex.status() == 0 and attn.status(nq, dev) == 0
+ref = torch.empty(nq, 32, 128, dtype=torch.float32, device=dev)
+kv_split_decode(attn, case.q.to(dev) * 5.0, cache, bt, sl, ref)
+assert torch.equal(out2.view(nq, 32, 128), ref)
 dist.barrier(); dist.destroy_process_group()
 print("rank", rank, "ok", float(err.max()))
 """
@@ -69,3 +86,41 @@ def test_kv_split_decode_two_gpus(tmp_path):
     for r, p in enumerate(procs):
         out, err = p.communicate(timeout=600)
         assert p.returncode == 0 and f"rank {r} ok" in out, err[-3000:]
+
+
+def test_exchange_protocol_single_rank(oracle, golden):
+    """tq_decode_paged_exchange with world = 1 (this rank's buffer is the only peer): push, flag,
+    wait, merge and the step counter over several calls and a graph replay, against
+    tq_decode_paged_multi."""
+    import math
+    from turboquant_b200 import _cabi, synthetic
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention
+    from turboquant_b200.parallel import KVSplitExchange
+    from tests.gpu_util import DEV, oracle_cache
+    lens = [300, 0, 1500]
+    B, nq = len(lens), 2
+    case = synthetic.decode_case(seed=31, seq_lens=lens, dtype=torch.float16)
+    cache = torch.from_numpy(oracle_cache(oracle, case, golden["signs_seed42_d128"])).to(DEV)
+    attn = TurboQuantPagedAttention(32, 128, 1 / math.sqrt(128), 8)
+    q = torch.randn(B, nq, 32, 128, generator=torch.Generator().manual_seed(3)).to(torch.float16).to(DEV)
+    bt, sl = case.block_table.to(DEV), case.seq_lens.to(DEV)
+    want = attn.decode_shared(q, cache, bt, sl)
+    nbytes = _cabi.exchange_bytes(B * nq * 32, 1)
+    buf = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    ex = KVSplitExchange(attn, B, nq, DEV, buffers=[buf])
+    for step in range(3):
+        out = torch.full_like(want, float("nan"))
+        ex.decode(q, cache, bt, sl, out)
+        torch.cuda.synchronize()
+        assert ex.status() == 0 and int(buf[:4].view(torch.int32).item()) == step + 1
+        assert torch.equal(out, want)
+    out = torch.full_like(want, float("nan"))
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ex.decode(q, cache, bt, sl, out)
+    for _ in range(3):
+        out.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want)
+    assert ex.status() == 0

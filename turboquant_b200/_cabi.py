@@ -29,7 +29,7 @@ EXPORTS = (
     "tq_abi_version", "tq_last_error", "tq_codebook", "tq_write_kv_cache", "tq_quantize_flat",
     "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
     "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
-    "tq_decode_paged_static", "tq_decode_paged_multi",
+    "tq_decode_paged_static", "tq_decode_paged_multi", "tq_exchange_bytes", "tq_decode_paged_exchange",
 )
 
 _lib = None
@@ -229,6 +229,42 @@ def decode_paged_multi(q, kv_cache, page_indices, seq_lens, signs, sm_scale: flo
         ctypes.c_float(sm_scale), _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
         _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), ctypes.c_int(1 if rotated_partial else 0),
         ctypes.c_int(num_ctas), _stream(q)))
+    return out
+
+
+def exchange_bytes(rows: int, world: int) -> int:
+    """Bytes of one rank's exchange buffer for ``rows`` output rows (batch x queries x heads)."""
+    f = lib().tq_exchange_bytes
+    f.restype = ctypes.c_size_t
+    n = f(ctypes.c_int64(rows), ctypes.c_int(world))
+    if n == 0:
+        raise TurboQuantError(f"exchange of {rows} rows over {world} ranks is not supported")
+    return n
+
+
+def decode_paged_exchange(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, workspace, rank: int,
+                          exchange_ptrs, exchange_nbytes: int, out, page_indptr=None,
+                          max_pages: int | None = None, out_lse=None, num_ctas: int = 0,
+                          kv_begin: int = 0, kv_end: int = -1):
+    """Decode this rank's KV range of a sequence split over ``len(exchange_ptrs)`` GPUs, exchange the
+    partials through the ranks' mapped buffers and finish; ``q``/``out`` [batch, queries, Hq, D]."""
+    if max_pages is None:
+        max_pages = page_indices.shape[-1] if page_indices.dim() == 2 else 0
+    if q.dim() != 4 or not q.is_contiguous():
+        raise TurboQuantError("q must be contiguous [batch, queries, num_q_heads, head_dim]")
+    _decode_args(q.view(q.shape[0], -1, q.shape[3]), kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs)
+    B, NQ, Hq, D = q.shape
+    _, nb, bs, H, ebs = kv_cache.shape
+    world = len(exchange_ptrs)
+    arr = (ctypes.c_void_p * world)(*[ctypes.c_void_p(int(x)) for x in exchange_ptrs])
+    _check(lib().tq_decode_paged_exchange(
+        _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(NQ), ctypes.c_int(Hq),
+        ctypes.c_int(H), ctypes.c_int(D), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(ebs),
+        _ptr(page_indices), _ptr(page_indptr), ctypes.c_int(max_pages), _ptr(seq_lens),
+        ctypes.c_int64(kv_begin), ctypes.c_int64(kv_end), _ptr(signs), ctypes.c_float(sm_scale),
+        _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
+        ctypes.c_int(rank), ctypes.c_int(world), arr, ctypes.c_size_t(exchange_nbytes),
+        _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), ctypes.c_int(num_ctas), _stream(q)))
     return out
 
 

@@ -54,6 +54,8 @@ constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 4;
 constexpr int kLutBytes = 256 * 32 * 4;
 constexpr int kMaxSmem = 227 * 1024;
+constexpr int kMaxExchangeRanks = 16;
+constexpr int kExchangeSpinLimit = 1 << 22;  // x 256 ns sleeps: a second or so, then status 1
 constexpr int kMaxSegments = 96;
 constexpr int kMinPagesPerCta = 4;
 constexpr float kRaiseThreshold = 6.0f;  // log2 units
@@ -658,7 +660,36 @@ struct MergeParams {
     int64_t rows;     // batch (decode merge) or rows (generic merge)
     int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
     int nq, real_heads, real_group;  // virtual head -> (query, real head) of the output row; nq = 1: identity
+    // Exchange of rotated partials between the GPUs that split one KV axis (xmode != 0):
+    // every rank owns an exchange buffer (ExchangeLayout) that all ranks have mapped.
+    int xmode;                       // 0 none, 1 push this rank's partial to all ranks, 2 wait for all ranks and merge
+    int xrank, xworld;
+    int64_t xrows;                   // output rows (batch x queries x heads) of one rank's partial
+    unsigned char* xbuf[kMaxExchangeRanks];  // xbuf[r] = rank r's exchange buffer as mapped here
 };
+
+// Exchange buffer of one rank: control words, one flag per source rank, then two generations
+// (epoch parity) of [world][rows] base-2 LSEs and [world][rows][128] rotated partials.
+//   ctrl[0] epoch of the last finished step   ctrl[1] sticky status (1 = a wait ran out)
+//   ctrl[2] blocks done pushing               ctrl[3] blocks done merging
+struct ExchangeLayout {
+    size_t flags, lse, o, total;
+    __host__ __device__ ExchangeLayout(int world, int64_t rows) {
+        flags = 64;
+        lse = 256;
+        o = lse + (((size_t)2 * world * rows * sizeof(float) + 255) & ~(size_t)255);
+        total = o + (size_t)2 * world * rows * kHeadDim * sizeof(float);
+    }
+};
+
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 // One block per (row, query head), four warps.  Warp w takes parts w, w+4, ...; lane l owns
 // rotated dims 4l..4l+3.  A warp first fetches the LSEs of its parts (lane i: its i-th part),
@@ -673,6 +704,38 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     const int d = threadIdx.x, warp = d >> 5, lane = d & 31;
     const int64_t row = blockIdx.x;
     const int hq = blockIdx.y;
+    const float* partial_o = p.partial_o;
+    const float* partial_lse = p.partial_lse;
+    int32_t* xctrl = nullptr;
+    int32_t xepoch = 0;
+    if (p.xmode) {
+        xctrl = reinterpret_cast<int32_t*>(p.xbuf[p.xrank]);
+        xepoch = *reinterpret_cast<volatile int32_t*>(xctrl) + 1;  // the step in progress
+    }
+    if (p.xmode == 2) {
+        // Wait (bounded: about a second) until every rank's partial of this step has landed in
+        // this rank's buffer, then merge the [world][rows] parts of the step's generation.
+        __shared__ int x_ok;
+        if (d == 0) {
+            const int32_t* flags = reinterpret_cast<const int32_t*>(p.xbuf[p.xrank] + 64);
+            int ok = 1;
+            for (int w = 0; w < p.xworld && ok; w++) {
+                int spins = 0;
+                while ((int32_t)(ld_acquire_sys(flags + w) - xepoch) < 0) {
+                    if (++spins > kExchangeSpinLimit) { ok = 0; break; }
+                    __nanosleep(256);
+                }
+            }
+            if (!ok) atomicExch(xctrl + 1, 1);
+            x_ok = ok;
+        }
+        __syncthreads();
+        if (!x_ok) return;
+        const ExchangeLayout xl(p.xworld, p.xrows);
+        const int64_t gen = (int64_t)(xepoch & 1) * p.xworld * p.xrows;
+        partial_lse = reinterpret_cast<const float*>(p.xbuf[p.xrank] + xl.lse) + gen;
+        partial_o = reinterpret_cast<const float*>(p.xbuf[p.xrank] + xl.o) + gen * kHeadDim;
+    }
     // The parts of this row form an arithmetic slot sequence: slot(i) = first + i * stride.
     int64_t first = 0, stride = 1;
     int count = 0;
@@ -692,9 +755,9 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
         stride = p.rows;
         count = p.num_parts;
     }
-    const float* lse_base = p.partial_lse + first * p.num_q_heads + hq;
+    const float* lse_base = partial_lse + first * p.num_q_heads + hq;
     const int64_t lse_stride = stride * p.num_q_heads;
-    const float4* o_base = reinterpret_cast<const float4*>(p.partial_o + (first * p.num_q_heads + hq) * kHeadDim) + lane;
+    const float4* o_base = reinterpret_cast<const float4*>(partial_o + (first * p.num_q_heads + hq) * kHeadDim) + lane;
     const int64_t o_stride = lse_stride * (kHeadDim / 4);
     float m = -INFINITY, wsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -749,6 +812,28 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
         const int qi = col / p.real_group, hh = col - qi * p.real_group;
         orow = (row * p.nq + qi) * p.real_heads + kvh * p.real_group + hh;
     }
+    if (p.xmode == 1) {
+        // Push this rank's rotated partial into every rank's buffer (plain stores over NVLink, or
+        // local), then publish: the last block to finish releases this rank's flag everywhere.
+        const ExchangeLayout xl(p.xworld, p.xrows);
+        const int64_t at = ((int64_t)(xepoch & 1) * p.xworld + p.xrank) * p.xrows + orow;
+        for (int w = 0; w < p.xworld; w++) {
+            reinterpret_cast<float*>(p.xbuf[w] + xl.o)[at * kHeadDim + d] = o;
+            if (d == 0) reinterpret_cast<float*>(p.xbuf[w] + xl.lse)[at] = lse2;
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (d == 0) {
+            const int blocks = gridDim.x * gridDim.y;
+            if (atomicAdd(xctrl + 2, 1) == blocks - 1) {
+                xctrl[2] = 0;
+                __threadfence_system();
+                for (int w = 0; w < p.xworld; w++)
+                    st_release_sys(reinterpret_cast<int32_t*>(p.xbuf[w] + 64) + p.xrank, xepoch);
+            }
+        }
+        return;
+    }
     if (p.emit_rotated) {
         reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
         if (p.out_lse && d == 0) p.out_lse[orow] = lse2;
@@ -768,6 +853,17 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     else if (p.out_dtype == TQ_F16) reinterpret_cast<__half*>(p.out)[orow * kHeadDim + d] = __float2half_rn(o);
     else reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
     if (p.out_lse && d == 0) p.out_lse[orow] = lse2 * 0.6931471805599453f;
+    if (p.xmode == 2) {  // the last block to finish closes the step
+        __syncthreads();
+        if (d == 0) {
+            const int blocks = gridDim.x * gridDim.y;
+            __threadfence();
+            if (atomicAdd(xctrl + 3, 1) == blocks - 1) {
+                xctrl[3] = 0;
+                *reinterpret_cast<volatile int32_t*>(xctrl) = xepoch;
+            }
+        }
+    }
 }
 
 int device_sm_count(int* out);
@@ -836,15 +932,30 @@ static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
     return launch_decode_impl<HKV, false>(p, grid, S::total(stages, p.group), stream);
 }
 
+struct ExchangeArgs {
+    int rank, world;
+    void* const* bufs;  // host array [world]: every rank's exchange buffer as mapped in this process
+    size_t bytes;       // size of each buffer
+};
+
 static int decode_common(const void* q, int q_dtype, int batch, int nq, int real_q_heads, int num_kv_heads,
                          int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,
                          int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
                          int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
                          const float* signs, float sm_scale, void* workspace, size_t workspace_bytes,
                          void* out, int out_dtype, float* out_lse, int emit_rotated, int num_ctas,
-                         void* stream) {
+                         void* stream, const ExchangeArgs* x = nullptr) {
     TQ_REQUIRE(batch >= 0, TQ_ERR_INVALID, "negative batch");
     if (batch == 0) return TQ_OK;
+    if (x) {
+        TQ_REQUIRE(x->world >= 1 && x->world <= kMaxExchangeRanks && x->rank >= 0 && x->rank < x->world && x->bufs,
+                   TQ_ERR_INVALID, "exchange: rank %d of %d (at most %d ranks)", x->rank, x->world, kMaxExchangeRanks);
+        const ExchangeLayout xl(x->world, (int64_t)batch * nq * real_q_heads);
+        TQ_REQUIRE(x->bytes >= xl.total, TQ_ERR_WORKSPACE, "exchange buffer too small: %zu < %zu", x->bytes, xl.total);
+        for (int w = 0; w < x->world; w++)
+            TQ_REQUIRE(x->bufs[w] && ((uintptr_t)x->bufs[w] % 256) == 0, TQ_ERR_INVALID,
+                       "exchange buffer %d is null or not 256-byte aligned", w);
+    }
     TQ_REQUIRE(q && kv_cache && page_indices && seq_lens && signs && workspace && out, TQ_ERR_INVALID, "null pointer");
     TQ_REQUIRE(head_dim == kHeadDim, TQ_ERR_UNSUPPORTED, "decode supports head_dim 128, got %d", head_dim);
     TQ_REQUIRE(block_size == kPageTokens, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
@@ -929,8 +1040,29 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     m.grid_ctas = ctas;
     m.out_dtype = out_dtype;
     m.emit_rotated = emit_rotated;
+    if (x) {
+        m.xmode = 1;
+        m.xrank = x->rank;
+        m.xworld = x->world;
+        m.xrows = (int64_t)batch * num_q_heads;
+        for (int w = 0; w < x->world; w++) m.xbuf[w] = static_cast<unsigned char*>(x->bufs[w]);
+    }
     merge_kernel<<<dim3((unsigned)batch, (unsigned)num_q_heads), kHeadDim, 0, s>>>(m);
     TQ_CUDA(cudaGetLastError());
+    if (x) {
+        // second pass: wait for every rank's partial in this rank's buffer, merge, rotate back
+        MergeParams f = m;
+        f.xmode = 2;
+        f.header = nullptr;
+        f.page_prefix = nullptr;
+        f.rows = m.xrows;
+        f.num_q_heads = 1;
+        f.nq = 1;
+        f.num_parts = x->world;
+        f.emit_rotated = 0;
+        merge_kernel<<<dim3((unsigned)m.xrows, 1), kHeadDim, 0, s>>>(f);
+        TQ_CUDA(cudaGetLastError());
+    }
     if (g_events[2]) TQ_CUDA(cudaEventRecord(g_events[2], s));
     return TQ_OK;
 }
@@ -982,6 +1114,27 @@ extern "C" int tq_decode_paged_multi(const void* q, int q_dtype, int batch, int 
                              num_blocks, block_size, slot_bytes, page_indices, page_indptr, max_pages,
                              seq_lens, kv_begin, kv_end, signs, sm_scale, workspace, workspace_bytes, out,
                              out_dtype, out_lse, rotated_partial ? 1 : 0, num_ctas, stream);
+}
+
+extern "C" size_t tq_exchange_bytes(int64_t rows, int world) {
+    if (rows <= 0 || world < 1 || world > tq::kMaxExchangeRanks) return 0;
+    return tq::ExchangeLayout(world, rows).total;
+}
+
+extern "C" int tq_decode_paged_exchange(const void* q, int q_dtype, int batch, int queries_per_seq,
+                                        int num_q_heads, int num_kv_heads, int head_dim, const void* kv_cache,
+                                        int64_t num_blocks, int block_size, int slot_bytes,
+                                        const int32_t* page_indices, const int32_t* page_indptr, int max_pages,
+                                        const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
+                                        const float* signs, float sm_scale, void* workspace,
+                                        size_t workspace_bytes, int rank, int world, void* const* exchange_bufs,
+                                        size_t exchange_bytes, void* out, int out_dtype, float* out_lse,
+                                        int num_ctas, void* stream) {
+    const tq::ExchangeArgs x{rank, world, exchange_bufs, exchange_bytes};
+    return tq::decode_common(q, q_dtype, batch, queries_per_seq, num_q_heads, num_kv_heads, head_dim, kv_cache,
+                             num_blocks, block_size, slot_bytes, page_indices, page_indptr, max_pages,
+                             seq_lens, kv_begin, kv_end, signs, sm_scale, workspace, workspace_bytes, out,
+                             out_dtype, out_lse, 0, num_ctas, stream, &x);
 }
 
 extern "C" int tq_decode_paged_partial(const void* q, int q_dtype, int batch, int num_q_heads,

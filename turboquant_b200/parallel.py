@@ -9,6 +9,10 @@ Two ways the decode path shards:
   ``tq_decode_paged_partial``, the partials are all-gathered (132 KB per rank at 8 queries x 32
   heads) and every rank finishes with the LSE merge + inverse rotation (``tq_merge_rotated``).
 
+``KVSplitExchange`` is the fused form of the second path: the decode's merge epilogue stores the
+partial straight into every rank's exchange buffer over NVLink and a flag-gated merge finishes,
+so no collective library call sits between the two kernels.
+
 ``merge_gathered`` is the collective-free core of the second path and is what the CPU (gloo)
 tests exercise with oracle-made partials.
 """
@@ -75,3 +79,55 @@ def kv_split_decode(attn, query, kv_cache_local, block_table_local, seq_lens_loc
     o, l = all_gather_partials(part_o, part_l, group)
     _cabi.merge_rotated(o, l, attn.signs(dev), output)
     return output
+
+
+class KVSplitExchange:
+    """KV-axis split decode whose exchange is done by the kernels themselves
+    (``tq_decode_paged_exchange``): plain peer stores into every rank's buffer, a per-source flag,
+    a bounded wait, then the LSE merge and the inverse rotation on every rank.
+
+    The buffers are symmetric memory (``torch.distributed._symmetric_memory``), zeroed and
+    rendezvoused once here; ``decode`` itself allocates nothing and can be graph-captured.
+    Multicast (NVLS) binding of the buffer is switched off: the kernels use plain peer stores only.
+    """
+
+    def __init__(self, attn, batch: int, queries: int, device, group=None, buffers=None):
+        from . import _cabi
+        self.attn = attn
+        self.batch, self.queries = batch, queries
+        self.group = group
+        self.world = dist.get_world_size(group) if buffers is None else len(buffers)
+        self.rank = dist.get_rank(group) if buffers is None else 0
+        rows = batch * queries * attn.num_heads
+        self.nbytes = _cabi.exchange_bytes(rows, self.world)
+        if buffers is not None:            # caller-mapped buffers (tests on one GPU: world 1)
+            self._keep = buffers
+            self.ptrs = [int(b.data_ptr()) for b in buffers]
+            return
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        buf.zero_()
+        pg = group if group is not None else dist.group.WORLD
+        handle = symm_mem.rendezvous(buf, pg.group_name)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                # every buffer is zero before any rank pushes
+        self._keep = (buf, handle)
+        self.ptrs = [int(x) for x in handle.buffer_ptrs]
+
+    def decode(self, query, kv_cache_local, block_table_local, seq_lens_local, output, out_lse=None):
+        """``query`` [batch, queries, heads, D] (the same on every rank); every rank gets ``output``."""
+        from . import _cabi
+        a = self.attn
+        dev = query.device
+        _cabi.decode_paged_exchange(query, a._as_bytes(kv_cache_local), block_table_local, seq_lens_local,
+                                    a.signs(dev), a.scale, a.workspace(self.batch, dev, self.queries),
+                                    self.rank, self.ptrs, self.nbytes, output, out_lse=out_lse,
+                                    num_ctas=a.num_ctas, max_pages=block_table_local.shape[-1])
+        return output
+
+    def status(self) -> int:
+        """Sticky status word of this rank's exchange buffer (0 ok, 1 a wait for a peer ran out)."""
+        buf = self._keep[0]
+        return int(buf[4:8].view(torch.int32).item())
