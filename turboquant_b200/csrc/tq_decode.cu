@@ -122,6 +122,26 @@ __device__ __forceinline__ float lds_half(uint32_t addr) {
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
     return __half2float(__ushort_as_half(v));
 }
+// The same with a compile-time byte offset folded into the instruction's address field.
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_at(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64_at(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ float lds_half_at(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(addr), "n"(OFF));
+    return __half2float(__ushort_as_half(v));
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -242,7 +262,10 @@ struct DecodeSmem {
         }
         return r;
     }
-    // rotated Q, fp16, `group` rows per warp
+    // MMA rows r and r+8 sit a fixed distance apart in both regions (runs: two tokens further in
+    // the same run; pitched rows: eight rows further)
+    static constexpr int kKRow8 = kRuns ? 2 * kRowBytes : 8 * kKPitch;
+    static constexpr int kVRow8 = kRuns ? 2 * kRowBytes : 8 * kVPitch;
     // per-warp scratch: rotated Q (fp16, `group` rows), reused to transpose the partial output
     // (2 x 128 floats), hence at least four rows
     static constexpr int q_rows(int group) { return group < 4 ? 4 : group; }
@@ -423,13 +446,13 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     const int ta = S::row_token(g), tb = S::row_token(g + 8);
     const uint32_t k_base = smem_u32(stages) + sub * S::kKRegion + head * kSlotBytes;
     const uint32_t v_base = smem_u32(stages) + S::kKBytes + sub * S::kVRegion + head * kSlotBytes;
-    const uint32_t ka_addr = k_base + S::k_off(ta) + 16 * tg, kb_addr = k_base + S::k_off(tb) + 16 * tg;
-    const uint32_t nka_addr = k_base + S::k_off(ta) + 64, nkb_addr = k_base + S::k_off(tb) + 64;
-    const uint32_t nva_addr = v_base + S::v_off(ta) + 64, nvb_addr = v_base + S::v_off(tb) + 64;
+    // Rows g+8, 2tg+8 and 2tg+9 are a compile-time distance from rows g, 2tg and 2tg+1: five
+    // address registers serve the twelve loads of a tile.
+    const uint32_t ka_addr = k_base + S::k_off(ta) + 16 * tg;
+    const uint32_t nka_addr = k_base + S::k_off(ta) + 64;
+    const uint32_t nva_addr = v_base + S::v_off(ta) + 64;
     const uint32_t v0_addr = v_base + S::v_off(S::row_token(2 * tg)) + 8 * g;
     const uint32_t v1_addr = v_base + S::v_off(S::row_token(2 * tg + 1)) + 8 * g;
-    const uint32_t v2_addr = v_base + S::v_off(S::row_token(2 * tg + 8)) + 8 * g;
-    const uint32_t v3_addr = v_base + S::v_off(S::row_token(2 * tg + 9)) + 8 * g;
 
     int st = 0, round = 0;
     uint32_t st_off = 0;  // st * kStageBytes
@@ -509,18 +532,19 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
         for (int pg = p0; pg < p1; pg += PPS) {
-            if (!mbar_wait(&full_bar[st], round & 1)) {
+            if (!mbar_wait(&full_bar[st], round & 1)) {  // bounded; every other warp's waits run out too
                 abort_flag = 1;
                 atomicExch(&p.header[0], 1);
+                return;
             }
-            if (abort_flag) return;
             const bool have = pg + sub < p1;  // this warp's page lane holds a page
             if (have) {
                 const int tok0 = (first_page + pg + sub) * kPageTokens;  // first token of the page
                 // ---- K codes and norms for tokens ta, tb; V codes: bytes 8g..8g+7 of four tokens ----
-                const uint4 ka = lds128(ka_addr + st_off), kb = lds128(kb_addr + st_off);
-                float nka = lds_half(nka_addr + st_off), nkb = lds_half(nkb_addr + st_off);
-                float nva = lds_half(nva_addr + st_off), nvb = lds_half(nvb_addr + st_off);
+                const uint32_t ka_at = ka_addr + st_off, nka_at = nka_addr + st_off, nva_at = nva_addr + st_off;
+                const uint4 ka = lds128_at<0>(ka_at), kb = lds128_at<S::kKRow8>(ka_at);
+                float nka = lds_half_at<0>(nka_at), nkb = lds_half_at<S::kKRow8>(nka_at);
+                float nva = lds_half_at<0>(nva_at), nvb = lds_half_at<S::kVRow8>(nva_at);
                 // Only the last page of a sequence can hold tokens past its length: their norms are
                 // zeroed (whatever the unwritten slots contain) and their scores biased to -inf.
                 float bias_a = 0.f, bias_b = 0.f;
@@ -528,13 +552,14 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     if (tok0 + ta >= len_eff) { nka = 0.f; nva = 0.f; bias_a = -INFINITY; }
                     if (tok0 + tb >= len_eff) { nkb = 0.f; nvb = 0.f; bias_b = -INFINITY; }
                 }
-                const uint2 v0 = lds64(v0_addr + st_off), v1 = lds64(v1_addr + st_off);
-                const uint2 v2 = lds64(v2_addr + st_off), v3 = lds64(v3_addr + st_off);
+                const uint32_t v0_at = v0_addr + st_off, v1_at = v1_addr + st_off;
+                const uint2 v0 = lds64_at<0>(v0_at), v1 = lds64_at<0>(v1_at);
+                const uint2 v2 = lds64_at<S::kVRow8>(v0_at), v3 = lds64_at<S::kVRow8>(v1_at);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[st]);  // stage data is in registers now
 
                 // ---- S = K^ Q^T : 16 tokens x 8 heads ---------------------------------------------
-                float s_acc[4] = {0.f, 0.f, 0.f, 0.f};
+                float s_acc[4] = {0.f, 0.f, 0.f, 0.f}, s_acc2[4] = {0.f, 0.f, 0.f, 0.f};  // two MMA chains
                 const uint32_t kwa[4] = {ka.x, ka.y, ka.z, ka.w};
                 const uint32_t kwb[4] = {kb.x, kb.y, kb.z, kb.w};
 #pragma unroll
@@ -543,8 +568,10 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     dequant8<WIDE>(kwa[w], lut_lane, ra);
                     dequant8<WIDE>(kwb[w], lut_lane, rb);
                     mma16816(s_acc, ra[0], rb[0], ra[1], rb[1], qf[4 * w], qf[4 * w + 1]);
-                    mma16816(s_acc, ra[2], rb[2], ra[3], rb[3], qf[4 * w + 2], qf[4 * w + 3]);
+                    mma16816(s_acc2, ra[2], rb[2], ra[3], rb[3], qf[4 * w + 2], qf[4 * w + 3]);
                 }
+#pragma unroll
+                for (int i = 0; i < 4; i++) s_acc[i] += s_acc2[i];
                 // ---- online softmax (base 2) ------------------------------------------------------
                 const float kfa = nka * p.k_scale, kfb = nkb * p.k_scale;
                 const float x0 = fmaf(s_acc[0], kfa, bias_a), x1 = fmaf(s_acc[1], kfa, bias_a);
