@@ -45,7 +45,8 @@ class KernelConfig:
 
     @property
     def threads_per_block(self) -> int:
-        return (self.consumer_warps + 1) * 32
+        # consumer warps + a producer warpgroup (the producer warp and three register donors)
+        return (self.consumer_warps + 4) * 32
 
     @property
     def tile_tokens(self) -> int:
