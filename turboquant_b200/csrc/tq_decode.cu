@@ -106,6 +106,30 @@ struct DecodeParams {
     uint16_t centroid_h[16];  // fp16 bit patterns of the N(0,1) centroids
 };
 
+// Programmatic dependent launch: the decode and merge kernels are launched with programmatic
+// stream serialization, so a kernel's blocks may be scheduled (and run their on-chip prologue)
+// while the kernel before it in the stream drains.  grid_dependency_wait() returns once that
+// kernel has completed and its writes are visible; nothing before it may touch global memory.
+// Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename P>
+static cudaError_t launch_serialized(void (*kernel)(P), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     const P& params) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -308,7 +332,9 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     uint8_t* stages = smem + stage0_off;
     uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem + lut_off);
     __half* q_s = reinterpret_cast<__half*>(smem + q_off);
+    grid_launch_dependents();  // the merge's blocks may be scheduled as soon as there is room
     if (WIDE && smem_base + stage0_off + S::kStageBytes > kWideLutAddr) {  // the map above does not fit
+        grid_dependency_wait();
         if (tid == 0) atomicExch(&p.header[0], 3);
         return;
     }
@@ -331,7 +357,9 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             const int v = i >> 5;
             lut_s[WIDE ? (v * 64 + (i & 31)) : i] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
         }
+        grid_dependency_wait();
     } else {
+        grid_dependency_wait();  // seq_lens, the page table, Q and the workspace belong to earlier kernels
         // pass 1: total pages
         int total = 0;
         for (int base = 0; base < p.batch; base += 32) {
@@ -739,6 +767,8 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     const int d = threadIdx.x, warp = d >> 5, lane = d & 31;
     const int64_t row = blockIdx.x;
     const int hq = blockIdx.y;
+    grid_launch_dependents();
+    grid_dependency_wait();  // the partials (and the exchange words) come from the kernel before
     const float* partial_o = p.partial_o;
     const float* partial_lse = p.partial_lse;
     int32_t* xctrl = nullptr;
@@ -945,8 +975,7 @@ static int launch_decode_impl(DecodeParams& p, int grid, int smem, cudaStream_t 
                                      kMaxSmem - 2048));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    decode_paged_kernel<HKV, WIDE><<<grid, kDecodeThreads, smem, stream>>>(p);
-    TQ_CUDA(cudaGetLastError());
+    TQ_CUDA(launch_serialized(decode_paged_kernel<HKV, WIDE>, dim3(grid), dim3(kDecodeThreads), smem, stream, p));
     return TQ_OK;
 }
 
@@ -1082,8 +1111,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
         m.xrows = (int64_t)batch * num_q_heads;
         for (int w = 0; w < x->world; w++) m.xbuf[w] = static_cast<unsigned char*>(x->bufs[w]);
     }
-    merge_kernel<<<dim3((unsigned)batch, (unsigned)num_q_heads), kHeadDim, 0, s>>>(m);
-    TQ_CUDA(cudaGetLastError());
+    TQ_CUDA(launch_serialized(merge_kernel, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(kHeadDim), 0, s, m));
     if (x) {
         // second pass: wait for every rank's partial in this rank's buffer, merge, rotate back
         MergeParams f = m;
@@ -1095,8 +1123,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
         f.nq = 1;
         f.num_parts = x->world;
         f.emit_rotated = 0;
-        merge_kernel<<<dim3((unsigned)m.xrows, 1), kHeadDim, 0, s>>>(f);
-        TQ_CUDA(cudaGetLastError());
+        TQ_CUDA(launch_serialized(merge_kernel, dim3((unsigned)m.xrows, 1), dim3(kHeadDim), 0, s, f));
     }
     if (g_events[2]) TQ_CUDA(cudaEventRecord(g_events[2], s));
     return TQ_OK;
@@ -1206,8 +1233,7 @@ extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse
     m.nq = 1;
     m.num_parts = num_parts;
     m.out_dtype = out_dtype;
-    merge_kernel<<<dim3((unsigned)rows, 1), kHeadDim, 0, static_cast<cudaStream_t>(stream)>>>(m);
-    TQ_CUDA(cudaGetLastError());
+    TQ_CUDA(launch_serialized(merge_kernel, dim3((unsigned)rows, 1), dim3(kHeadDim), 0, static_cast<cudaStream_t>(stream), m));
     return TQ_OK;
 }
 
