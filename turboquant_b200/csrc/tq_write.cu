@@ -20,7 +20,8 @@
 //     reciprocal, which equals the IEEE quotient whenever the intermediates stay normal and the
 //     norm's significand is not all ones (checked per row; otherwise the row takes the division
 //     instruction);
-//   * the code index is a sum of saturated FMAs, sat((|y| - b_j) * 2^40), one per boundary.
+//   * the code index comes from a table over 1/64-wide bins of y (each bin holds at most one of
+//     the 15 boundaries): boundaries below the bin + one exact comparison with the boundary inside.
 #include <cmath>
 #include <cstring>
 
@@ -31,6 +32,11 @@ namespace tq {
 constexpr int kWriteThreads = 256;
 constexpr int kTileRows = kWriteThreads / 4;  // four lanes per row
 constexpr int kD = 128;
+// Bins of the code search: bin(y) = round(64 y) + kBinZero.  |y| <= 1 up to rounding for a
+// normalized row, so kBins = 2 * 96 + 1 bins (|y| <= 1.5) cover every value the search can see.
+constexpr int kBinZero = 96;
+constexpr int kBins = 2 * kBinZero + 1;
+constexpr float kBinMagic = 8388608.0f + (float)kBinZero;  // 2^23 + kBinZero: the sum's low mantissa bits are the bin
 
 struct WriteParams {
     uint8_t* kv_cache;
@@ -45,33 +51,26 @@ struct WriteParams {
     int slot_is_i64;
     int zero_pad;
     const float* signs;       // [128] +-1, device
-    float2 bin_table[16];     // per coarse bin of |y|: {-(boundary inside the bin) * 2^40 or -inf, boundaries below + 0.5}
+    float2 bin_table[kBins];  // per bin of y: {boundary inside the bin or +inf, number of boundaries in lower bins}
     float fwht_scale;         // (float)(1/sqrt(128))
 };
 
-__device__ __forceinline__ float fma_sat(float a, float b, float c) {
-    float d;
-    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-
-// Code of y among the 15 symmetric boundaries (boundary 7 is 0, boundary 14-i = -boundary i) as
-// a float in 0..15: the number of boundaries strictly below y.  With a = |y|:
-//   y > 0 : 8 + #{pb_j < a};   y <= 0 : 7 - #{pb_j <= a} = 7 - #{pb_j < a + 1ulp}.
-// The positive boundaries are at least 1/64 apart, so the bin k = round(min(64 a, 14)) holds at most
-// one of them: a 16-entry table gives the count of boundaries in lower bins and the boundary
-// inside the bin, and one exact comparison finishes the search.  The comparison is
-// sat((a - b) * 2^40): the FMA forms the difference exactly and a positive difference is at least
-// one ulp of b (> 2^-30), so it saturates to exactly 1.  The host builds the table with the same
-// float operations, which makes the binning consistent by construction.
-__device__ __forceinline__ float code_f(float y, const float2* table) {
-    const bool pos = y > 0.0f;
-    const float a = __uint_as_float((__float_as_uint(y) & 0x7fffffffu) + (pos ? 0u : 1u));
-    const float t = fminf(__fmul_rn(a, 64.0f), 14.0f);
-    const uint32_t k = __float_as_uint(__fadd_rn(t, 8388608.0f)) & 15u;
-    const float2 e = table[k];
-    const float mm = __fadd_rn(e.y, fma_sat(a, 1099511627776.0f, e.x));  // boundaries below a, plus 0.5
-    return __fmaf_rn(pos ? 1.0f : -1.0f, mm, 7.5f);                        // 8 + m or 7 - m
+// Code of y among the 15 boundaries: the number of boundaries strictly below y (torch.bucketize,
+// right = False), as a float.  The boundaries are at least 1/64 apart, so the bin
+// k = round(64 y) + kBinZero holds at most one of them; the binning is monotone in y, hence every
+// boundary in a lower bin is below y and every boundary in a higher bin is not.  Table entry k =
+// {the boundary inside bin k, or +inf; the number of boundaries in lower bins}: one lookup and one
+// exact comparison finish the search.  The table is replicated per lane (entry k of lane l at
+// k * 256 + 8 l), so a warp's lookups never conflict, and the address is one integer multiply-add
+// of the float's bit pattern: (0x4B000000 + k) * 256 + lane_base wraps to lane_base' + 256 k.
+// The host fills the table with the same float operations, which makes it consistent with this
+// binning by construction.  NaN rows never get here.
+__device__ __forceinline__ float code_f(float y, uint32_t table_lane) {
+    const float kf = __fmaf_rn(y, 64.0f, kBinMagic);
+    const uint32_t addr = __float_as_uint(kf) * 256u + table_lane;
+    float bnd, below;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(bnd), "=f"(below) : "r"(addr));
+    return y > bnd ? __fadd_rn(below, 1.0f) : below;
 }
 
 // Two fp32 values in one 64-bit register and the packed arithmetic of sm_100 (add/sub/mul/fma
@@ -129,7 +128,6 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     // every warp runs its own two-buffer pipeline over 8-row pieces: no block-wide barrier in the loop
     __shared__ __align__(8) uint64_t full_bar[kWriteThreads / 32][2];
     __shared__ __align__(16) float signs_s[kD];
-    __shared__ __align__(8) float2 bins_s[16];
     __shared__ __align__(16) uint8_t out_s[kTileRows][64];  // code bytes of a tile, natural order
 
     const int tid = threadIdx.x;
@@ -150,7 +148,10 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     }
     if (tid == 0) fence_barrier_init();
     if (tid < kD) signs_s[tid] = p.signs[tid];
-    if (tid < 16) bins_s[tid] = p.bin_table[tid];
+    // code-search table, one column per lane, behind the two staging buffers
+    float2* bins_s = reinterpret_cast<float2*>(smem + (size_t)2 * kTileRows * kPitch);
+    for (int i = tid; i < kBins * 32; i += kWriteThreads) bins_s[i] = p.bin_table[i >> 5];
+    const uint32_t table_lane = smem_u32(bins_s) + 8u * lane;
     __syncthreads();
 
     auto issue = [&](int64_t tile, int buf) {
@@ -208,7 +209,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
             acc = add2(acc, sq);
             float s0, s1;
             up(sq, s0, s1);
-            minsq = fminf(minsq, fminf(s0, s1));
+            asm("min.f32 %0, %0, %1, %2;" : "+f"(minsq) : "f"(s0), "f"(s1));  // three-input minimum
         }
         float acc0, acc1;
         up(acc, acc0, acc1);
@@ -286,16 +287,19 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         for (int j = 0; j < 16; j++) up(mul2(x[j], scale2), y[j][0], y[j][1]);
         // scale, code, pack: byte 4j + m = (code(even dim) << 4) | code(odd dim), via the low
         // byte of a float with 2^23 added
-        const bool all_nan = y[0][0] != y[0][0];  // a non-finite input turns the whole row into NaN
+        // A non-finite input turns the whole row into NaN (every output of the transform depends
+        // on every input); torch's bucketize sends NaN to the last bucket: every code is 15.
+        const bool all_nan = y[0][0] != y[0][0];
         uint8_t* orow = out_s[row_in_tile];
+        if (!all_nan) {
 #pragma unroll
-        for (int j = 0; j < 16; j++) {
-            const float hi = code_f(y[j][0], bins_s);
-            const float lo = code_f(y[j][1], bins_s);
-            const float bytef = __fadd_rn(__fmaf_rn(hi, 16.0f, lo), 8388608.0f);
-            orow[4 * j + m] = (uint8_t)__float_as_uint(bytef);
-        }
-        if (all_nan) {  // torch's bucketize sends NaN to the last bucket: every code is 15
+            for (int j = 0; j < 16; j++) {
+                const float hi = code_f(y[j][0], table_lane);
+                const float lo = code_f(y[j][1], table_lane);
+                const float bytef = __fadd_rn(__fmaf_rn(hi, 16.0f, lo), 8388608.0f);
+                orow[4 * j + m] = (uint8_t)__float_as_uint(bytef);
+            }
+        } else {
 #pragma unroll
             for (int j = 0; j < 16; j++) orow[4 * j + m] = 0xff;
         }
@@ -317,7 +321,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
 template <typename T>
 static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream) {
     constexpr int kPitch = RowLoad<T>::kRowBytes + 16;
-    const size_t smem = (size_t)2 * kTileRows * kPitch;
+    const size_t smem = (size_t)2 * kTileRows * kPitch + (size_t)kBins * 32 * sizeof(float2);
     static bool configured[64] = {};  // per template instance and device
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
@@ -381,25 +385,25 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     p.signs = signs;
     float cen[16], bnd[15];
     host_codebook(kD, 4, cen, bnd);
-    {   // coarse bins of |y| (same float operations as the kernel's code_f)
-        int bin_of[7];
-        for (int i = 0; i < 7; i++) {
-            volatile float t = bnd[8 + i] * 64.0f;
-            volatile float r = (t < 14.0f ? t : 14.0f) + 8388608.0f;
-            float rf = r;
+    {   // bins of y (same float operations as the kernel's code_f)
+        int bin_of[15];
+        for (int i = 0; i < 15; i++) {
+            volatile float kf = fmaf(bnd[i], 64.0f, kBinMagic);
+            float kff = kf;
             uint32_t bits;
-            memcpy(&bits, &rf, 4);
-            bin_of[i] = (int)(bits & 15u);
-            TQ_REQUIRE(i == 0 || bin_of[i] > bin_of[i - 1], TQ_ERR_UNSUPPORTED, "boundaries too close for the bin table");
+            memcpy(&bits, &kff, 4);
+            bin_of[i] = (int)(bits - 0x4B000000u);
+            TQ_REQUIRE(bin_of[i] >= 0 && bin_of[i] < kBins && (i == 0 || bin_of[i] > bin_of[i - 1]), TQ_ERR_UNSUPPORTED,
+                       "boundaries too close for the bin table");
         }
-        for (int k = 0; k < 16; k++) {
+        for (int k = 0; k < kBins; k++) {
             int below = 0;
-            float inside = -INFINITY;  // no boundary in this bin: the comparison yields 0
-            for (int i = 0; i < 7; i++) {
+            float inside = INFINITY;  // no boundary in this bin: the comparison is never true
+            for (int i = 0; i < 15; i++) {
                 if (bin_of[i] < k) below++;
-                if (bin_of[i] == k) inside = -bnd[8 + i] * 1099511627776.0f;  // exact: a power of two
+                if (bin_of[i] == k) inside = bnd[i];
             }
-            p.bin_table[k] = make_float2(inside, (float)below + 0.5f);
+            p.bin_table[k] = make_float2(inside, (float)below);
         }
     }
     p.fwht_scale = (float)(1.0 / sqrt((double)kD));
