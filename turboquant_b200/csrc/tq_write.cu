@@ -46,6 +46,7 @@ struct WriteParams {
     int64_t num_tokens;
     int64_t slab_bytes;       // bytes between the K slab and the V slab
     int num_kv_heads;
+    int head_shift;           // log2(num_kv_heads) when that is a power of two, else -1
     int block_size;
     int slot_bytes;
     int slot_is_i64;
@@ -92,6 +93,22 @@ __device__ __forceinline__ P2 fma2(P2 a, P2 b, P2 c) {
     return r;
 }
 
+// row index -> (token, head).  A 64-bit division by a run-time value is a long subroutine; the
+// usual head counts are powers of two (shift and mask), and below 2^31 rows a 32-bit division does.
+__device__ __forceinline__ void split_row(int64_t r, int H, int head_shift, int64_t& t, int& h) {
+    if (head_shift >= 0) {
+        t = r >> head_shift;
+        h = (int)r & (H - 1);
+    } else if (r < 0x7fffffffLL) {
+        const uint32_t q = (uint32_t)r / (uint32_t)H;
+        t = q;
+        h = (int)((uint32_t)r - q * (uint32_t)H);
+    } else {
+        t = r / H;
+        h = (int)(r - t * H);
+    }
+}
+
 template <typename T>
 struct RowLoad;
 
@@ -128,7 +145,9 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     // every warp runs its own two-buffer pipeline over 8-row pieces: no block-wide barrier in the loop
     __shared__ __align__(8) uint64_t full_bar[kWriteThreads / 32][2];
     __shared__ __align__(16) float signs_s[kD];
-    __shared__ __align__(16) uint8_t out_s[kTileRows][64];  // code bytes of a tile, natural order
+    // code bytes of a tile, natural order; rows 80 bytes apart so that the byte stores of a warp's
+    // eight rows fall into eight different banks
+    __shared__ __align__(16) uint8_t out_s[kTileRows][80];
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -164,8 +183,9 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         __syncwarp();
         if (lane < nrows) {
             const int64_t r = row0 + lane;
-            const int64_t t = r / H;
-            const int h = (int)(r - t * H);
+            int64_t t;
+            int h;
+            split_row(r, H, p.head_shift, t, h);
             const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * kD;
             bulk_g2s(smem + (size_t)buf * kTileRows * kPitch + (size_t)(warp * kPieceRows + lane) * kPitch, src,
                      L::kRowBytes, &full_bar[warp][buf]);
@@ -188,8 +208,8 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         int64_t slot = -1;
         int h = 0;
         if (row_ok) {
-            const int64_t t = r / H;
-            h = (int)(r - t * H);
+            int64_t t;
+            split_row(r, H, p.head_shift, t, h);
             slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
                                  : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
         }
@@ -378,6 +398,9 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     p.num_tokens = num_tokens;
     p.slab_bytes = num_blocks * block_size * (int64_t)num_kv_heads * slot_bytes;
     p.num_kv_heads = num_kv_heads;
+    p.head_shift = -1;
+    for (int sft = 0; sft < 16; sft++)
+        if ((1 << sft) == num_kv_heads) p.head_shift = sft;
     p.block_size = block_size;
     p.slot_bytes = slot_bytes;
     p.slot_is_i64 = slot_dtype == TQ_I64;
