@@ -173,9 +173,10 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     const uint32_t table_lane = smem_u32(bins_s) + 8u * lane;
     __syncthreads();
 
+    // piece index -> tensor and rows: K and V pieces alternate (tile = 2 * piece + tensor)
     auto issue = [&](int64_t tile, int buf) {
-        const int which = tile >= tiles_per_tensor ? 1 : 0;
-        const int64_t row0 = (tile - which * tiles_per_tensor) * kPieceRows;
+        const int which = (int)(tile & 1);
+        const int64_t row0 = (tile >> 1) * kPieceRows;
         const int64_t left = rows - row0;
         const int64_t nrows = left < kPieceRows ? left : (int64_t)kPieceRows;
         fence_proxy_async();  // earlier shared-memory reads of this buffer precede the copy engine's writes
@@ -202,8 +203,8 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
 
         if (!mbar_wait(&full_bar[warp][buf], (it >> 1) & 1)) return;  // copy never landed: touch nothing
 
-        const int which = tile >= tiles_per_tensor ? 1 : 0;
-        const int64_t r = (tile - which * tiles_per_tensor) * kPieceRows + row_in_warp;
+        const int which = (int)(tile & 1);
+        const int64_t r = (tile >> 1) * kPieceRows + row_in_warp;
         const bool row_ok = r < rows;  // uniform over the four lanes of a row
         int64_t slot = -1;
         int h = 0;
@@ -221,7 +222,9 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         float minsq = 1.0f;
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            const float2 v = row_ok ? L::pair(row, j, m) : make_float2(0.f, 0.f);
+            // rows past the end compute on whatever the buffer holds (any bit pattern is handled:
+            // finite rows normalize to |y| <= 1, anything else becomes an all-NaN row) and store nothing
+            const float2 v = L::pair(row, j, m);
             x[j] = pk(v.x, v.y);
             // accumulators 2m and 2m+1 of the eight interleaved ones, in order of j, product
             // rounded before the add
