@@ -9,12 +9,13 @@
 // from double, strict "boundary < value" tie rule.  This translation unit is compiled with
 // -fmad=false and without fast-math.
 //
-// Mapping: four lanes own one 128-element row; lane m holds elements 8j + 2m + e (j = 0..15,
-// e = 0, 1), i.e. exactly two of the eight norm accumulators and both nibbles of code byte
-// 4j + m.  Butterfly stages 1 and 8..64 are register-local, stages 2 and 4 are two shuffles per
-// element.  Rows of a 64-row tile are staged into shared memory by per-row bulk async copies
-// (one mbarrier per buffer, two buffers); the 16-byte row pad makes the 4-byte loads of a warp
-// (8 rows x 16 bytes) conflict free.  Everything per element runs on the FP32 pipe where it can
+// Mapping: two lanes own one 128-element row; lane m holds elements 8j + 4m .. 8j + 4m + 3
+// (j = 0..15), i.e. four of the eight norm accumulators and code bytes 4j + 2m, 4j + 2m + 1.
+// Butterfly stages 1, 2 and 8..64 are register-local, stage 4 is one shuffle per element.  A warp
+// works on 16 rows per pass, which halves the per-row share of everything that is done once per
+// pass (pipeline, slot lookup, norm reduction, store).  Rows are staged into shared memory by
+// per-row bulk async copies, each warp running its own two-buffer pipeline.  Everything per
+// element runs on the FP32 pipe where it can
 // (the integer/logic pipe has half its rate):
 //   * x / norm is q = x*r, e = fma(-q, norm, x), q' = fma(e, r, q) with r the correctly rounded
 //     reciprocal, which equals the IEEE quotient whenever the intermediates stay normal and the
@@ -29,8 +30,6 @@
 
 namespace tq {
 
-constexpr int kWriteThreads = 256;
-constexpr int kTileRows = kWriteThreads / 4;  // four lanes per row
 constexpr int kD = 128;
 // Bins of the code search: bin(y) = round(64 y) + kBinZero.  |y| <= 1 up to rounding for a
 // normalized row, so kBins = 2 * 96 + 1 bins (|y| <= 1.5) cover every value the search can see.
@@ -61,14 +60,15 @@ struct WriteParams {
 // k = round(64 y) + kBinZero holds at most one of them; the binning is monotone in y, hence every
 // boundary in a lower bin is below y and every boundary in a higher bin is not.  Table entry k =
 // {the boundary inside bin k, or +inf; the number of boundaries in lower bins}: one lookup and one
-// exact comparison finish the search.  The table is replicated per lane (entry k of lane l at
-// k * 256 + 8 l), so a warp's lookups never conflict, and the address is one integer multiply-add
-// of the float's bit pattern: (0x4B000000 + k) * 256 + lane_base wraps to lane_base' + 256 k.
+// exact comparison finish the search.  The table has 16 columns (entry k of column c at
+// k * 128 + 8 c; an 8-byte load is served half a warp at a time), so a warp's lookups never
+// conflict, and the address is one integer multiply-add of the float's bit pattern:
+// (0x4B000000 + k) * 128 wraps to 128 k + 2^31, and the column base has 2^31 subtracted.
 // The host fills the table with the same float operations, which makes it consistent with this
 // binning by construction.  NaN rows never get here.
 __device__ __forceinline__ float code_f(float y, uint32_t table_lane) {
     const float kf = __fmaf_rn(y, 64.0f, kBinMagic);
-    const uint32_t addr = __float_as_uint(kf) * 256u + table_lane;
+    const uint32_t addr = __float_as_uint(kf) * 128u + table_lane;
     float bnd, below;
     asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(bnd), "=f"(below) : "r"(addr));
     return y > bnd ? __fadd_rn(below, 1.0f) : below;
@@ -112,54 +112,73 @@ __device__ __forceinline__ void split_row(int64_t r, int H, int head_shift, int6
 template <typename T>
 struct RowLoad;
 
-// pair(row, j, m): elements 8j + 2m and 8j + 2m + 1 of a staged row
+// quad(row, j, m): elements 8j + 4m .. 8j + 4m + 3 of a staged row, as two pairs.  kPad keeps the
+// loads of a warp (16 rows x 2 lanes) conflict free: 16-bit rows are read 8 bytes per lane in
+// half-warps (8 rows: row * 68 words -> 4 banks apart), 32-bit rows 16 bytes per lane in
+// quarter-warps (4 rows: row * 136 words -> 8 banks apart).
 template <>
 struct RowLoad<float> {
-    static constexpr int kRowBytes = kD * 4;
-    static __device__ __forceinline__ float2 pair(const uint8_t* row, int j, int m) {
-        return *reinterpret_cast<const float2*>(row + 32 * j + 8 * m);
+    static constexpr int kRowBytes = kD * 4, kPad = 32;
+    static __device__ __forceinline__ void quad(const uint8_t* row, int j, int m, float2& a, float2& b) {
+        const float4 v = *reinterpret_cast<const float4*>(row + 32 * j + 16 * m);
+        a = make_float2(v.x, v.y);
+        b = make_float2(v.z, v.w);
     }
 };
 template <>
 struct RowLoad<__nv_bfloat16> {
-    static constexpr int kRowBytes = kD * 2;
-    static __device__ __forceinline__ float2 pair(const uint8_t* row, int j, int m) {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 16 * j + 4 * m);
-        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    static constexpr int kRowBytes = kD * 2, kPad = 16;
+    static __device__ __forceinline__ void quad(const uint8_t* row, int j, int m, float2& a, float2& b) {
+        const uint2 w = *reinterpret_cast<const uint2*>(row + 16 * j + 8 * m);
+        a = make_float2(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u));
+        b = make_float2(__uint_as_float(w.y << 16), __uint_as_float(w.y & 0xffff0000u));
     }
 };
 template <>
 struct RowLoad<__half> {
-    static constexpr int kRowBytes = kD * 2;
-    static __device__ __forceinline__ float2 pair(const uint8_t* row, int j, int m) {
-        return __half22float2(*reinterpret_cast<const __half2*>(row + 16 * j + 4 * m));
+    static constexpr int kRowBytes = kD * 2, kPad = 16;
+    static __device__ __forceinline__ void quad(const uint8_t* row, int j, int m, float2& a, float2& b) {
+        const uint2 w = *reinterpret_cast<const uint2*>(row + 16 * j + 8 * m);
+        a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+        b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
     }
 };
 
+// Threads per block: one block per SM.  16-bit inputs run 16 warps; fp32 rows need twice the
+// staging space, so they run 8.
 template <typename T>
-__global__ void __launch_bounds__(kWriteThreads, 2)
+struct WriteShape {
+    static constexpr int kThreads = sizeof(T) == 4 ? 256 : 512;
+    static constexpr int kWarps = kThreads / 32;
+    static constexpr int kPieceRows = 16;                 // rows per warp and pass: two lanes per row
+    static constexpr int kTileRows = kWarps * kPieceRows;
+    static constexpr int kPitch = RowLoad<T>::kRowBytes + RowLoad<T>::kPad;
+    static constexpr int kOutPitch = 72;                  // 18 words: 16 rows -> 16 different banks
+    static constexpr size_t kStageBytes = (size_t)2 * kTileRows * kPitch;
+    static constexpr size_t kTableBytes = (size_t)kBins * 16 * sizeof(float2);
+    static constexpr size_t kOutBytes = (size_t)kTileRows * kOutPitch;
+    static constexpr size_t kSmem = kStageBytes + kTableBytes + kOutBytes;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(WriteShape<T>::kThreads, 1)
 write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     using L = RowLoad<T>;
-    constexpr int kPitch = L::kRowBytes + 16;
+    using W = WriteShape<T>;
+    constexpr int kPitch = W::kPitch, kPieceRows = W::kPieceRows;
     extern __shared__ __align__(128) uint8_t smem[];
-    // every warp runs its own two-buffer pipeline over 8-row pieces: no block-wide barrier in the loop
-    __shared__ __align__(8) uint64_t full_bar[kWriteThreads / 32][2];
+    // every warp runs its own two-buffer pipeline over 16-row pieces: no block-wide barrier in the loop
+    __shared__ __align__(8) uint64_t full_bar[W::kWarps][2];
     __shared__ __align__(16) float signs_s[kD];
-    // code bytes of a tile, natural order; rows 80 bytes apart so that the byte stores of a warp's
-    // eight rows fall into eight different banks
-    __shared__ __align__(16) uint8_t out_s[kTileRows][80];
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    const int m = lane & 3;              // lane within the row
-    const int row_in_warp = lane >> 2;   // row of the warp's 8-row piece this lane works on
-    const int row_in_tile = tid >> 2;
-    const unsigned quad_base = lane & ~3;
+    const int m = lane & 1;              // lane within the row: elements 8j + 4m .. 8j + 4m + 3
+    const int row_in_warp = lane >> 1;   // row of the warp's 16-row piece this lane works on
+    const int row_in_tile = warp * kPieceRows + row_in_warp;
     const int H = p.num_kv_heads;
     const int64_t rows = p.num_tokens * H;  // per tensor
-    constexpr int kPieceRows = 8;
-    const int64_t tiles_per_tensor = (rows + kPieceRows - 1) / kPieceRows;  // pieces per tensor
-    const int64_t num_tiles = 2 * tiles_per_tensor;
+    const int64_t num_tiles = 2 * ((rows + kPieceRows - 1) / kPieceRows);  // K and V pieces alternate
 
     if (lane == 0) {
         mbar_init(&full_bar[warp][0], 1);
@@ -167,13 +186,17 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     }
     if (tid == 0) fence_barrier_init();
     if (tid < kD) signs_s[tid] = p.signs[tid];
-    // code-search table, one column per lane, behind the two staging buffers
-    float2* bins_s = reinterpret_cast<float2*>(smem + (size_t)2 * kTileRows * kPitch);
-    for (int i = tid; i < kBins * 32; i += kWriteThreads) bins_s[i] = p.bin_table[i >> 5];
-    const uint32_t table_lane = smem_u32(bins_s) + 8u * lane;
+    // Code-search table behind the staging buffers: entry k of column c at (16 k + c) * 8 bytes.
+    // An 8-byte load is served half a warp at a time, so 16 columns (lane & 15) are enough for
+    // conflict-free lookups.
+    float2* bins_s = reinterpret_cast<float2*>(smem + W::kStageBytes);
+    for (int i = tid; i < kBins * 16; i += W::kThreads) bins_s[i] = p.bin_table[i >> 4];
+    // (the bit pattern of 2^23 + k) * 128 = 2^31 + 128 k modulo 2^32: take the 2^31 out here
+    const uint32_t table_lane = smem_u32(bins_s) + 8u * (lane & 15) - 0x80000000u;
+    uint8_t* out_s = smem + W::kStageBytes + W::kTableBytes;
     __syncthreads();
 
-    // piece index -> tensor and rows: K and V pieces alternate (tile = 2 * piece + tensor)
+    // piece index -> tensor and rows: tile = 2 * piece + tensor
     auto issue = [&](int64_t tile, int buf) {
         const int which = (int)(tile & 1);
         const int64_t row0 = (tile >> 1) * kPieceRows;
@@ -188,13 +211,13 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
             int h;
             split_row(r, H, p.head_shift, t, h);
             const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * kD;
-            bulk_g2s(smem + (size_t)buf * kTileRows * kPitch + (size_t)(warp * kPieceRows + lane) * kPitch, src,
+            bulk_g2s(smem + (size_t)buf * W::kTileRows * kPitch + (size_t)(warp * kPieceRows + lane) * kPitch, src,
                      L::kRowBytes, &full_bar[warp][buf]);
         }
     };
 
-    const int64_t warp_stride = (int64_t)gridDim.x * (kWriteThreads / 32);
-    int64_t tile = (int64_t)blockIdx.x * (kWriteThreads / 32) + warp;
+    const int64_t warp_stride = (int64_t)gridDim.x * W::kWarps;
+    int64_t tile = (int64_t)blockIdx.x * W::kWarps + warp;
     if (tile < num_tiles) issue(tile, 0);
     for (int it = 0; tile < num_tiles; tile += warp_stride, it++) {
         const int buf = it & 1;
@@ -205,7 +228,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
 
         const int which = (int)(tile & 1);
         const int64_t r = (tile >> 1) * kPieceRows + row_in_warp;
-        const bool row_ok = r < rows;  // uniform over the four lanes of a row
+        const bool row_ok = r < rows;  // uniform over the two lanes of a row
         int64_t slot = -1;
         int h = 0;
         if (row_ok) {
@@ -214,39 +237,41 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
             slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
                                  : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
         }
-        // all lanes run the arithmetic (the shuffles need whole quads); rows past the end or with
-        // a negative slot read whatever is staged and store nothing
-        const uint8_t* row = smem + (size_t)buf * kTileRows * kPitch + (size_t)row_in_tile * kPitch;
-        P2 x[16];
-        P2 acc = pk(0.0f, 0.0f);
+        // All lanes run the arithmetic (the shuffles need whole pairs).  Rows past the end compute
+        // on whatever the buffer holds (any bit pattern is handled: finite rows normalize to
+        // |y| <= 1, anything else becomes an all-NaN row) and store nothing.
+        const uint8_t* row = smem + (size_t)buf * W::kTileRows * kPitch + (size_t)row_in_tile * kPitch;
+        P2 x[32];  // x[2j] = elements (8j+4m, 8j+4m+1), x[2j+1] = (8j+4m+2, 8j+4m+3)
+        P2 acc_a = pk(0.0f, 0.0f), acc_b = pk(0.0f, 0.0f);  // accumulators 4m, 4m+1 and 4m+2, 4m+3 of the eight
         float minsq = 1.0f;
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            // rows past the end compute on whatever the buffer holds (any bit pattern is handled:
-            // finite rows normalize to |y| <= 1, anything else becomes an all-NaN row) and store nothing
-            const float2 v = L::pair(row, j, m);
-            x[j] = pk(v.x, v.y);
-            // accumulators 2m and 2m+1 of the eight interleaved ones, in order of j, product
-            // rounded before the add
-            const P2 sq = mul2(x[j], x[j]);
-            acc = add2(acc, sq);
-            float s0, s1;
-            up(sq, s0, s1);
+            float2 va, vb;
+            L::quad(row, j, m, va, vb);
+            x[2 * j] = pk(va.x, va.y);
+            x[2 * j + 1] = pk(vb.x, vb.y);
+            // in order of j, product rounded before the add
+            const P2 sa = mul2(x[2 * j], x[2 * j]), sb = mul2(x[2 * j + 1], x[2 * j + 1]);
+            acc_a = add2(acc_a, sa);
+            acc_b = add2(acc_b, sb);
+            float s0, s1, s2, s3;
+            up(sa, s0, s1);
+            up(sb, s2, s3);
             asm("min.f32 %0, %0, %1, %2;" : "+f"(minsq) : "f"(s0), "f"(s1));  // three-input minimum
+            asm("min.f32 %0, %0, %1, %2;" : "+f"(minsq) : "f"(s2), "f"(s3));
         }
-        float acc0, acc1;
-        up(acc, acc0, acc1);
-        // combine the eight accumulators left to right
-        float s = 0.0f;
+        // combine the eight accumulators left to right: lane m = 0 holds 0..3, lane m = 1 holds 4..7
+        float mine[4], other[4];
+        up(acc_a, mine[0], mine[1]);
+        up(acc_b, mine[2], mine[3]);
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const float a = __shfl_sync(0xffffffffu, acc0, quad_base + q);
-            const float b = __shfl_sync(0xffffffffu, acc1, quad_base + q);
-            s = q == 0 ? a : __fadd_rn(s, a);
-            s = __fadd_rn(s, b);
-        }
+        for (int k = 0; k < 4; k++) other[k] = __shfl_xor_sync(0xffffffffu, mine[k], 1);
+        float s = m ? other[0] : mine[0];
+#pragma unroll
+        for (int k = 1; k < 4; k++) s = __fadd_rn(s, m ? other[k] : mine[k]);
+#pragma unroll
+        for (int k = 0; k < 4; k++) s = __fadd_rn(s, m ? mine[k] : other[k]);
         minsq = fminf(minsq, __shfl_xor_sync(0xffffffffu, minsq, 1));
-        minsq = fminf(minsq, __shfl_xor_sync(0xffffffffu, minsq, 2));
         float norm = __fsqrt_rn(s);
         // clamp(min=1e-8); a NaN stays a NaN, in the canonical quiet pattern torch produces
         if (!(norm >= 1e-8f)) norm = (norm != norm) ? __uint_as_float(0x7fc00000u) : 1e-8f;
@@ -260,39 +285,42 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
             const float rcp = __frcp_rn(norm);
             const P2 rcp2 = pk(rcp, rcp), nneg2 = pk(-norm, -norm);
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const P2 q = mul2(x[j], rcp2);
-                const P2 err = fma2(q, nneg2, x[j]);   // x - q * norm, exact
-                x[j] = fma2(err, rcp2, q);
+            for (int i = 0; i < 32; i++) {
+                const P2 q = mul2(x[i], rcp2);
+                const P2 err = fma2(q, nneg2, x[i]);   // x - q * norm, exact
+                x[i] = fma2(err, rcp2, q);
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
+            for (int i = 0; i < 32; i++) {
                 float a, b;
-                up(x[j], a, b);
-                x[j] = pk(__fdiv_rn(a, norm), __fdiv_rn(b, norm));
+                up(x[i], a, b);
+                x[i] = pk(__fdiv_rn(a, norm), __fdiv_rn(b, norm));
             }
         }
-        // signs, then butterflies in stage order h = 1, 2, 4 (lanes), 8..64 (j)
+        // signs, then butterflies in stage order: h = 1 inside a pair, h = 2 between the two pairs
+        // of a j, h = 4 between the two lanes, h = 8..64 across j
 #pragma unroll
         for (int j = 0; j < 16; j++) {
-            const float2 sg = *reinterpret_cast<const float2*>(&signs_s[8 * j + 2 * m]);
-            float a, b;
-            up(mul2(x[j], pk(sg.x, sg.y)), a, b);
-            x[j] = pk(__fadd_rn(a, b), __fsub_rn(a, b));
+            const float4 sg = *reinterpret_cast<const float4*>(&signs_s[8 * j + 4 * m]);
+            float a, b, c, d;
+            up(mul2(x[2 * j], pk(sg.x, sg.y)), a, b);
+            up(mul2(x[2 * j + 1], pk(sg.z, sg.w)), c, d);
+            const P2 lo = pk(__fadd_rn(a, b), __fsub_rn(a, b)), hi = pk(__fadd_rn(c, d), __fsub_rn(c, d));
+            x[2 * j] = add2(lo, hi);
+            x[2 * j + 1] = sub2(lo, hi);
         }
-#pragma unroll
-        for (int d = 1; d < 4; d <<= 1) {
+        {
             // upper partner: other - mine, lower partner: mine + other; one FMA with +-1 does both
             // (the product with +-1 is exact, so the rounding is that of the plain add/sub)
-            const float sgn = (m & d) ? -1.0f : 1.0f;
+            const float sgn = m ? -1.0f : 1.0f;
             const P2 sgn2 = pk(sgn, sgn);
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
+            for (int i = 0; i < 32; i++) {
                 float a, b;
-                up(x[j], a, b);
-                const float oa = __shfl_xor_sync(0xffffffffu, a, d), ob = __shfl_xor_sync(0xffffffffu, b, d);
-                x[j] = fma2(x[j], sgn2, pk(oa, ob));
+                up(x[i], a, b);
+                const float oa = __shfl_xor_sync(0xffffffffu, a, 1), ob = __shfl_xor_sync(0xffffffffu, b, 1);
+                x[i] = fma2(x[i], sgn2, pk(oa, ob));
             }
         }
 #pragma unroll
@@ -300,51 +328,60 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
 #pragma unroll
             for (int j = 0; j < 16; j++)
                 if (!(j & hj)) {
-                    const P2 a = x[j], b = x[j + hj];
-                    x[j] = add2(a, b);
-                    x[j + hj] = sub2(a, b);
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const P2 a = x[2 * j + e], b = x[2 * (j + hj) + e];
+                        x[2 * j + e] = add2(a, b);
+                        x[2 * (j + hj) + e] = sub2(a, b);
+                    }
                 }
         const P2 scale2 = pk(p.fwht_scale, p.fwht_scale);
-        float y[16][2];
-#pragma unroll
-        for (int j = 0; j < 16; j++) up(mul2(x[j], scale2), y[j][0], y[j][1]);
-        // scale, code, pack: byte 4j + m = (code(even dim) << 4) | code(odd dim), via the low
-        // byte of a float with 2^23 added
+        // scale, code, pack: code bytes 4j + 2m and 4j + 2m + 1 (even dim in the high nibble) as one
+        // 16-bit store, taken from the low bits of a float with 2^23 added
+        float y0, y1;
+        up(mul2(x[0], scale2), y0, y1);
         // A non-finite input turns the whole row into NaN (every output of the transform depends
         // on every input); torch's bucketize sends NaN to the last bucket: every code is 15.
-        const bool all_nan = y[0][0] != y[0][0];
-        uint8_t* orow = out_s[row_in_tile];
+        const bool all_nan = y0 != y0;
+        uint8_t* orow = out_s + (size_t)row_in_tile * W::kOutPitch;
         if (!all_nan) {
 #pragma unroll
             for (int j = 0; j < 16; j++) {
-                const float hi = code_f(y[j][0], table_lane);
-                const float lo = code_f(y[j][1], table_lane);
-                const float bytef = __fadd_rn(__fmaf_rn(hi, 16.0f, lo), 8388608.0f);
-                orow[4 * j + m] = (uint8_t)__float_as_uint(bytef);
+                float a, b, c, d;
+                up(mul2(x[2 * j], scale2), a, b);
+                up(mul2(x[2 * j + 1], scale2), c, d);
+                const float b0 = __fmaf_rn(code_f(a, table_lane), 16.0f, code_f(b, table_lane));
+                const float b1 = __fmaf_rn(code_f(c, table_lane), 16.0f, code_f(d, table_lane));
+                const float both = __fadd_rn(__fmaf_rn(b1, 256.0f, b0), 8388608.0f);
+                *reinterpret_cast<uint16_t*>(orow + 4 * j + 2 * m) = (uint16_t)__float_as_uint(both);
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 16; j++) orow[4 * j + m] = 0xff;
+            for (int j = 0; j < 16; j++) *reinterpret_cast<uint16_t*>(orow + 4 * j + 2 * m) = 0xffffu;
         }
         __syncwarp();
         if (row_ok && slot >= 0) {
             // slot = block * block_size + entry and the cache is [block][entry][head][slot_bytes]
             uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)slot * H + h) * p.slot_bytes;
-            *reinterpret_cast<uint4*>(dst + 16 * m) = *reinterpret_cast<const uint4*>(orow + 16 * m);
+            const uint2* src8 = reinterpret_cast<const uint2*>(orow + 32 * m);
+            const uint2 c0 = src8[0], c1 = src8[1], c2 = src8[2], c3 = src8[3];
+            uint4* dst16 = reinterpret_cast<uint4*>(dst + 32 * m);
+            dst16[0] = make_uint4(c0.x, c0.y, c1.x, c1.y);
+            dst16[1] = make_uint4(c2.x, c2.y, c3.x, c3.y);
             if (m == 0) {
                 const uint32_t nh = (norm != norm) ? 0x7e00u : (uint32_t)__half_as_ushort(__float2half_rn(norm));
                 if (p.zero_pad) *reinterpret_cast<uint4*>(dst + 64) = make_uint4(nh | (nh << 16), 0u, 0u, 0u);
                 else *reinterpret_cast<uint32_t*>(dst + 64) = nh | (nh << 16);
             }
         }
-        __syncwarp();  // the warp is done with this buffer and with its rows of out_s
+        __syncwarp();  // the warp is done with this buffer and with its rows of the output staging
     }
 }
 
 template <typename T>
 static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream) {
-    constexpr int kPitch = RowLoad<T>::kRowBytes + 16;
-    const size_t smem = (size_t)2 * kTileRows * kPitch + (size_t)kBins * 32 * sizeof(float2);
+    using W = WriteShape<T>;
+    const size_t smem = W::kSmem;
     static bool configured[64] = {};  // per template instance and device
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
@@ -354,10 +391,9 @@ static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream)
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t rows = p.num_tokens * p.num_kv_heads;
-    const int64_t tiles = 2 * ((rows + kTileRows - 1) / kTileRows);
-    const int per_sm = 2;  // __launch_bounds__(256, 2)
-    const int64_t grid = tiles < (int64_t)sm_count * per_sm ? tiles : (int64_t)sm_count * per_sm;
-    write_kv_cache_kernel<T><<<(unsigned)grid, kWriteThreads, smem, stream>>>(p);
+    const int64_t tiles = 2 * ((rows + W::kTileRows - 1) / W::kTileRows);  // block-sized groups of pieces
+    const int64_t grid = tiles < (int64_t)sm_count ? tiles : (int64_t)sm_count;  // one block per SM
+    write_kv_cache_kernel<T><<<(unsigned)grid, W::kThreads, smem, stream>>>(p);
     TQ_CUDA(cudaGetLastError());
     return TQ_OK;
 }
