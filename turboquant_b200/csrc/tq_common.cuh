@@ -87,6 +87,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
+// Programmatic dependent launch: the write, decode and merge kernels are launched with programmatic
+// stream serialization, so a kernel's blocks may be scheduled (and run their on-chip prologue)
+// while the kernel before it in the stream drains.  grid_dependency_wait() returns once that
+// kernel has completed and its writes are visible; nothing before it may touch global memory.
+// Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename P>
+static cudaError_t launch_serialized(void (*kernel)(P), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     const P& params) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 // 1-D bulk async copy global -> this CTA's shared memory, completing on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16.  No multicast.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,

@@ -106,30 +106,6 @@ struct DecodeParams {
     uint16_t centroid_h[16];  // fp16 bit patterns of the N(0,1) centroids
 };
 
-// Programmatic dependent launch: the decode and merge kernels are launched with programmatic
-// stream serialization, so a kernel's blocks may be scheduled (and run their on-chip prologue)
-// while the kernel before it in the stream drains.  grid_dependency_wait() returns once that
-// kernel has completed and its writes are visible; nothing before it may touch global memory.
-// Both are no-ops for a launch without the attribute.
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
-
-template <typename P>
-static cudaError_t launch_serialized(void (*kernel)(P), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                     const P& params) {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, params);
-}
-
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));

@@ -55,25 +55,6 @@ struct WriteParams {
     float fwht_scale;         // (float)(1/sqrt(128))
 };
 
-// Code of y among the 15 boundaries: the number of boundaries strictly below y (torch.bucketize,
-// right = False), as a float.  The boundaries are at least 1/64 apart, so the bin
-// k = round(64 y) + kBinZero holds at most one of them; the binning is monotone in y, hence every
-// boundary in a lower bin is below y and every boundary in a higher bin is not.  Table entry k =
-// {the boundary inside bin k, or +inf; the number of boundaries in lower bins}: one lookup and one
-// exact comparison finish the search.  The table has 16 columns (entry k of column c at
-// k * 128 + 8 c; an 8-byte load is served half a warp at a time), so a warp's lookups never
-// conflict, and the address is one integer multiply-add of the float's bit pattern:
-// (0x4B000000 + k) * 128 wraps to 128 k + 2^31, and the column base has 2^31 subtracted.
-// The host fills the table with the same float operations, which makes it consistent with this
-// binning by construction.  NaN rows never get here.
-__device__ __forceinline__ float code_f(float y, uint32_t table_lane) {
-    const float kf = __fmaf_rn(y, 64.0f, kBinMagic);
-    const uint32_t addr = __float_as_uint(kf) * 128u + table_lane;
-    float bnd, below;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(bnd), "=f"(below) : "r"(addr));
-    return y > bnd ? __fadd_rn(below, 1.0f) : below;
-}
-
 // Two fp32 values in one 64-bit register and the packed arithmetic of sm_100 (add/sub/mul/fma
 // .f32x2): each lane of a pair is rounded to nearest exactly like the scalar instruction, at half
 // the instruction count.  A lane's elements (8j + 2m, 8j + 2m + 1) form the natural pairs.
@@ -91,6 +72,31 @@ __device__ __forceinline__ P2 fma2(P2 a, P2 b, P2 c) {
     P2 r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
     return r;
+}
+
+// Code of y among the 15 boundaries: the number of boundaries strictly below y (torch.bucketize,
+// right = False), as a float.  The boundaries are at least 1/64 apart, so the bin
+// k = round(64 y) + kBinZero holds at most one of them; the binning is monotone in y, hence every
+// boundary in a lower bin is below y and every boundary in a higher bin is not.  Table entry k =
+// {the boundary inside bin k, or +inf; the number of boundaries in lower bins}: one lookup and one
+// exact comparison finish the search.  The table has 16 columns (entry k of column c at
+// k * 128 + 8 c; an 8-byte load is served half a warp at a time), so a warp's lookups never
+// conflict, and the address is one integer multiply-add of the float's bit pattern:
+// (0x4B000000 + k) * 128 wraps to 128 k + 2^31, and the column base has 2^31 subtracted.
+// The host fills the table with the same float operations, which makes it consistent with this
+// binning by construction.  NaN rows never get here.
+__device__ __forceinline__ float code_lookup(float y, float kf, uint32_t table_lane) {
+    const uint32_t addr = __float_as_uint(kf) * 128u + table_lane;
+    float bnd, below;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(bnd), "=f"(below) : "r"(addr));
+    return y > bnd ? __fadd_rn(below, 1.0f) : below;
+}
+// code byte of a pair (even dim in the high nibble), as a float in 0..255
+__device__ __forceinline__ float code_byte(P2 y2, uint32_t table_lane) {
+    float y0, y1, k0, k1;
+    up(y2, y0, y1);
+    up(fma2(y2, pk(64.0f, 64.0f), pk(kBinMagic, kBinMagic)), k0, k1);  // bins of both, one instruction
+    return __fmaf_rn(code_lookup(y0, k0, table_lane), 16.0f, code_lookup(y1, k1, table_lane));
 }
 
 // row index -> (token, head).  A 64-bit division by a run-time value is a long subroutine; the
@@ -180,12 +186,12 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     const int64_t rows = p.num_tokens * H;  // per tensor
     const int64_t num_tiles = 2 * ((rows + kPieceRows - 1) / kPieceRows);  // K and V pieces alternate
 
+    grid_launch_dependents();
     if (lane == 0) {
         mbar_init(&full_bar[warp][0], 1);
         mbar_init(&full_bar[warp][1], 1);
     }
     if (tid == 0) fence_barrier_init();
-    if (tid < kD) signs_s[tid] = p.signs[tid];
     // Code-search table behind the staging buffers: entry k of column c at (16 k + c) * 8 bytes.
     // An 8-byte load is served half a warp at a time, so 16 columns (lane & 15) are enough for
     // conflict-free lookups.
@@ -194,6 +200,8 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     // (the bit pattern of 2^23 + k) * 128 = 2^31 + 128 k modulo 2^32: take the 2^31 out here
     const uint32_t table_lane = smem_u32(bins_s) + 8u * (lane & 15) - 0x80000000u;
     uint8_t* out_s = smem + W::kStageBytes + W::kTableBytes;
+    grid_dependency_wait();  // K, V, the slots, the signs and the cache belong to earlier kernels
+    if (tid < kD) signs_s[tid] = p.signs[tid];
     __syncthreads();
 
     // piece index -> tensor and rows: tile = 2 * piece + tensor
@@ -347,11 +355,8 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         if (!all_nan) {
 #pragma unroll
             for (int j = 0; j < 16; j++) {
-                float a, b, c, d;
-                up(mul2(x[2 * j], scale2), a, b);
-                up(mul2(x[2 * j + 1], scale2), c, d);
-                const float b0 = __fmaf_rn(code_f(a, table_lane), 16.0f, code_f(b, table_lane));
-                const float b1 = __fmaf_rn(code_f(c, table_lane), 16.0f, code_f(d, table_lane));
+                const float b0 = code_byte(mul2(x[2 * j], scale2), table_lane);
+                const float b1 = code_byte(mul2(x[2 * j + 1], scale2), table_lane);
                 const float both = __fadd_rn(__fmaf_rn(b1, 256.0f, b0), 8388608.0f);
                 *reinterpret_cast<uint16_t*>(orow + 4 * j + 2 * m) = (uint16_t)__float_as_uint(both);
             }
@@ -393,8 +398,7 @@ static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream)
     const int64_t rows = p.num_tokens * p.num_kv_heads;
     const int64_t tiles = 2 * ((rows + W::kTileRows - 1) / W::kTileRows);  // block-sized groups of pieces
     const int64_t grid = tiles < (int64_t)sm_count ? tiles : (int64_t)sm_count;  // one block per SM
-    write_kv_cache_kernel<T><<<(unsigned)grid, W::kThreads, smem, stream>>>(p);
-    TQ_CUDA(cudaGetLastError());
+    TQ_CUDA(launch_serialized(write_kv_cache_kernel<T>, dim3((unsigned)grid), dim3(W::kThreads), smem, stream, p));
     return TQ_OK;
 }
 
