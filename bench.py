@@ -359,6 +359,7 @@ def run_ours(args):
 
     # ---- cache-write path (the prefill-quantization config): 32768 tokens x 8 KV heads, bf16 ------
     write = None
+    dequant = None
     if rank == 0:
         from turboquant_b200 import synthetic
         wk, wv, wslots, wnb = synthetic.write_case(seed=2, num_tokens=32768)
@@ -382,6 +383,31 @@ def run_ours(args):
                  "achieved": w_ach, "peak": peak, "unit": "GB/s", "frac": w_ach / peak,
                  "tokens_per_s": 32768 / (wt[len(wt) // 2] * 1e-3)}
         del wk, wv, wcaches
+        # ---- bulk dequantization of cached tokens (continuation of a prefill): layer caches of the
+        # decode workload, first ctx_d tokens of every sequence -> dense bf16 K / V
+        ctx_d = min(L, 8192)
+        cu_d = torch.arange(B + 1, dtype=torch.int32, device=dev) * ctx_d
+        sl_d = torch.full((B,), ctx_d, dtype=torch.int32, device=dev)
+        dk, dv = attn.dequant_cached(caches[0], block_table, sl_d, cu_d, B * ctx_d)
+        torch.cuda.synchronize()
+        dt_ = []
+        from turboquant_b200 import _cabi as _c
+        for i in range(8):
+            out_dev.zero_(); caches[(i + 1) % NL].add_(0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _c.dequant_paged(caches[i % NL], block_table, sl_d, cu_d, attn.signs(dev), dk, dv)
+            e1.record()
+            torch.cuda.synchronize()
+            dt_.append(e0.elapsed_time(e1))
+        dt_.sort()
+        d_alg = B * ctx_d * HKV * (136 + 2 * D * 2)      # 136 B of codes + norms in, 2 x 128 bf16 out
+        d_ach = d_alg / (dt_[len(dt_) // 2] * 1e-3) / 1e9
+        dequant = {"workload": f"cached tokens -> dense bf16 K/V: {B} sequences x {ctx_d} tokens x {HKV} KV heads",
+                   "kernel": "dequant_paged_kernel<bf16>", "ms": dt_[len(dt_) // 2], "algorithmic_bytes": d_alg,
+                   "achieved": d_ach, "peak": peak, "unit": "GB/s", "frac": d_ach / peak,
+                   "tokens_per_s": B * ctx_d / (dt_[len(dt_) // 2] * 1e-3)}
+        del dk, dv
 
     if rank != 0:
         if world > 1:
@@ -409,7 +435,7 @@ def run_ours(args):
         "config": {"workload": workload_name(args), "global_batch": B * world, "parallelism": f"dp{world} (by sequence)",
                    "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB streamed per launch, {NL} distinct layer caches",
                    "cuda_graph": graph is not None, "algorithmic_bytes_per_step": alg_bytes * NL},
-        "roofline": roofline, "write": write, "cpu_baseline": cpu,
+        "roofline": roofline, "write": write, "dequant": dequant, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "api": "TurboQuantPagedAttention.write + .decode per layer, pinned host buffers"},
         "gpu_launches": args.steps * NL * 2, "clocks": clocks,

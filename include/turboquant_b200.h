@@ -145,6 +145,22 @@ int tq_decode_paged_multi(const void* q, int q_dtype, int batch, int queries_per
                           void* workspace, size_t workspace_bytes, void* out, int out_dtype, float* out_lse,
                           int rotated_partial, int num_ctas, void* stream);
 
+/* Bulk dequantization of the cached tokens of `batch` sequences into dense, varlen-packed K and V
+ * ([total_tokens][num_kv_heads][head_dim], row cu_seqlens[b] + t for token t of sequence b,
+ * out_token_stride elements between tokens): what a chunk of new query tokens needs in order to
+ * attend to KV that already sits quantized in the cache (continuation of a prefill) through a
+ * dense varlen attention kernel.  Per row: centroid lookup, inverse rotation (butterflies h = 1..64,
+ * 1/sqrt(128), signs), times the slot's fp16 norm — TurboQuantMSE.dequantize (quantizer.py:93-106)
+ * on cache slots, as in the reference's dequant-attention check (tests/test_fused_integration.py:
+ * 127-159).  The reference backend itself never reads the cache during prefill
+ * (vllm_backend_fused.py:336-369).  fp32 output is bit-identical to that arithmetic; fp16/bf16
+ * output is its rounding.  seq_lens, cu_seqlens [batch + 1] and the page table are device int32. */
+int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads,
+                     int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
+                     int max_pages, const int32_t* seq_lens, const int32_t* cu_seqlens, int batch,
+                     const float* signs, int head_dim, void* k_out, void* v_out, int out_dtype,
+                     int64_t out_token_stride, void* stream);
+
 /* One long sequence whose KV axis is split over `world` GPUs (one process per GPU): decode this
  * rank's token range, push the rotated partial + LSE into EVERY rank's exchange buffer with plain
  * peer stores (NVLink), release a per-source flag, then wait (bounded, about a second) until all

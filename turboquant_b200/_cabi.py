@@ -30,6 +30,7 @@ EXPORTS = (
     "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
     "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
     "tq_decode_paged_static", "tq_decode_paged_multi", "tq_exchange_bytes", "tq_decode_paged_exchange",
+    "tq_dequant_paged",
 )
 
 _lib = None
@@ -230,6 +231,36 @@ def decode_paged_multi(q, kv_cache, page_indices, seq_lens, signs, sm_scale: flo
         _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), ctypes.c_int(1 if rotated_partial else 0),
         ctypes.c_int(num_ctas), _stream(q)))
     return out
+
+
+def dequant_paged(kv_cache, page_indices, seq_lens, cu_seqlens, signs, k_out, v_out, page_indptr=None,
+                  max_pages: int | None = None):
+    """Cached tokens of every sequence -> dense K / V ``[total_tokens, H, 128]`` (row
+    ``cu_seqlens[b] + t``), dequantized; ``k_out`` / ``v_out`` fp32, fp16 or bf16, last two dims
+    contiguous."""
+    for t, n in ((kv_cache, "kv_cache"), (page_indices, "page_indices"), (seq_lens, "seq_lens"),
+                 (cu_seqlens, "cu_seqlens"), (signs, "signs"), (k_out, "k_out"), (v_out, "v_out")):
+        _cuda(t, n)
+    if kv_cache.dim() != 5 or kv_cache.shape[0] != 2 or not kv_cache.is_contiguous() or kv_cache.element_size() != 1:
+        raise TurboQuantError("kv_cache must be contiguous 1-byte [2, num_blocks, block_size, heads, slot_bytes]")
+    for t, n in ((page_indices, "page_indices"), (seq_lens, "seq_lens"), (cu_seqlens, "cu_seqlens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise TurboQuantError(f"{n} must be contiguous int32")
+    if max_pages is None:
+        max_pages = page_indices.shape[-1] if page_indices.dim() == 2 else 0
+    _, nb, bs, H, ebs = kv_cache.shape
+    B = seq_lens.shape[0]
+    if cu_seqlens.shape[0] != B + 1:
+        raise TurboQuantError("cu_seqlens must have batch + 1 entries")
+    if k_out.dim() != 3 or k_out.shape != v_out.shape or k_out.dtype != v_out.dtype or k_out.shape[1] != H \
+            or k_out.stride(2) != 1 or k_out.stride(1) != k_out.shape[2] or v_out.stride() != k_out.stride():
+        raise TurboQuantError("k_out / v_out must be [tokens, H, D] with contiguous heads and equal layout")
+    _check(lib().tq_dequant_paged(
+        _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(H), ctypes.c_int(ebs),
+        _ptr(page_indices), _ptr(page_indptr), ctypes.c_int(max_pages), _ptr(seq_lens), _ptr(cu_seqlens),
+        ctypes.c_int(B), _ptr(signs), ctypes.c_int(k_out.shape[2]), _ptr(k_out), _ptr(v_out),
+        ctypes.c_int(dtype_code(k_out.dtype)), ctypes.c_int64(k_out.stride(0)), _stream(kv_cache)))
+    return k_out, v_out
 
 
 def exchange_bytes(rows: int, world: int) -> int:

@@ -2,7 +2,7 @@
 
     python -m turboquant_b200.build [--force]
 
-The cache-write and flat-quantizer translation units are compiled with -fmad=false: their
+The cache-write, flat-quantizer and bulk-dequantizer translation units are compiled with -fmad=false: their
 arithmetic must round every product and sum separately to stay bit-identical to the torch
 quantizer.  No torch headers are involved; the library exports plain C symbols only.
 """
@@ -26,6 +26,7 @@ UNITS = {
     "tq_write.cu": ["-fmad=false"],
     "tq_flat.cu": ["-fmad=false"],
     "tq_decode.cu": [],
+    "tq_dequant.cu": ["-fmad=false"],
 }
 
 

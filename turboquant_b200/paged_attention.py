@@ -133,6 +133,24 @@ class TurboQuantPagedAttention:
                                  num_ctas=self.num_ctas, max_pages=block_table.shape[-1])
         return output
 
+    def dequant_cached(self, kv_cache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                       cu_seqlens: torch.Tensor, total_tokens: int, dtype=torch.bfloat16):
+        """Dense K / V ``[total_tokens, kv_heads, head_size]`` of the tokens already in the cache
+        (row ``cu_seqlens[b] + t``), for a chunk of new queries that continues a prefill: concatenate
+        with the chunk's fresh K / V and run a varlen attention kernel on the result.  The reference's
+        prefill ignores the cache (vllm_backend_fused.py:336-369); this is the missing piece for
+        chunked prefill over a quantized cache.  ``total_tokens`` is passed by the caller (no sync)."""
+        dev = kv_cache.device
+        k = torch.empty((total_tokens, self.num_kv_heads, self.head_size), dtype=dtype, device=dev)
+        v = torch.empty_like(k)
+        if total_tokens == 0:
+            return k, v
+        if block_table.dtype != torch.int32:
+            block_table = block_table.to(torch.int32)
+        _cabi.dequant_paged(self._as_bytes(kv_cache), block_table.contiguous(), seq_lens.to(torch.int32),
+                            cu_seqlens.to(torch.int32), self.signs(dev), k, v, max_pages=block_table.shape[-1])
+        return k, v
+
     def status(self, batch: int, device, queries: int = 1) -> int:
         """Status word the decode kernel leaves in its workspace (0 = ok); synchronises."""
         return int(self.workspace(batch, device, queries)[:4].view(torch.int32).item())
