@@ -161,6 +161,21 @@ int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int block_size, i
                      const float* signs, int head_dim, void* k_out, void* v_out, int out_dtype,
                      int64_t out_token_stride, void* stream);
 
+/* Offload / restore of packed cache pages: the K and V halves of the pages listed in page_ids
+ * (device int32) are gathered into / scattered from one contiguous buffer
+ *   packed[n_pages][2][block_size][num_kv_heads][68]   (64 code bytes + the fp16 norm twice);
+ * the 12 pad bytes of a slot are not moved and stay as they are on restore.  `packed` is device
+ * memory, sized by tq_pages_packed_bytes; copy it to and from pinned host memory on the same
+ * stream.  The reference measures this trade (restore over PCIe against re-running the prefill)
+ * with a raw copy of a whole slab, pad bytes included (tests/bench_kv_offload.py:23-62). */
+size_t tq_pages_packed_bytes(int n_pages, int block_size, int num_kv_heads);
+int tq_pages_gather(const void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads,
+                    int slot_bytes, const int32_t* page_ids, int n_pages, void* packed,
+                    size_t packed_bytes, void* stream);
+int tq_pages_scatter(void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads,
+                     int slot_bytes, const int32_t* page_ids, int n_pages, const void* packed,
+                     size_t packed_bytes, void* stream);
+
 /* One long sequence whose KV axis is split over `world` GPUs (one process per GPU): decode this
  * rank's token range, push the rotated partial + LSE into EVERY rank's exchange buffer with plain
  * peer stores (NVLink), release a per-source flag, then wait (bounded, about a second) until all

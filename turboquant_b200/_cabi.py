@@ -30,7 +30,7 @@ EXPORTS = (
     "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
     "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
     "tq_decode_paged_static", "tq_decode_paged_multi", "tq_exchange_bytes", "tq_decode_paged_exchange",
-    "tq_dequant_paged",
+    "tq_dequant_paged", "tq_pages_packed_bytes", "tq_pages_gather", "tq_pages_scatter",
 )
 
 _lib = None
@@ -261,6 +261,43 @@ def dequant_paged(kv_cache, page_indices, seq_lens, cu_seqlens, signs, k_out, v_
         ctypes.c_int(B), _ptr(signs), ctypes.c_int(k_out.shape[2]), _ptr(k_out), _ptr(v_out),
         ctypes.c_int(dtype_code(k_out.dtype)), ctypes.c_int64(k_out.stride(0)), _stream(kv_cache)))
     return k_out, v_out
+
+
+def pages_packed_bytes(n_pages: int, block_size: int, num_kv_heads: int) -> int:
+    f = lib().tq_pages_packed_bytes
+    f.restype = ctypes.c_size_t
+    return f(ctypes.c_int(n_pages), ctypes.c_int(block_size), ctypes.c_int(num_kv_heads))
+
+
+def _pages_args(kv_cache, page_ids, packed):
+    for t, n in ((kv_cache, "kv_cache"), (page_ids, "page_ids"), (packed, "packed")):
+        _cuda(t, n)
+    if kv_cache.dim() != 5 or kv_cache.shape[0] != 2 or not kv_cache.is_contiguous() or kv_cache.element_size() != 1:
+        raise TurboQuantError("kv_cache must be contiguous 1-byte [2, num_blocks, block_size, heads, slot_bytes]")
+    if page_ids.dtype != torch.int32 or not page_ids.is_contiguous() or page_ids.dim() != 1:
+        raise TurboQuantError("page_ids must be a contiguous 1-D int32 tensor")
+    if packed.dtype != torch.uint8 or not packed.is_contiguous():
+        raise TurboQuantError("packed must be a contiguous uint8 tensor")
+
+
+def pages_gather(kv_cache, page_ids, packed):
+    """Pages ``page_ids`` of ``kv_cache`` -> ``packed`` uint8 [n, 2, block_size, H, 68] (device)."""
+    _pages_args(kv_cache, page_ids, packed)
+    _, nb, bs, H, ebs = kv_cache.shape
+    _check(lib().tq_pages_gather(_ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(H),
+                                 ctypes.c_int(ebs), _ptr(page_ids), ctypes.c_int(page_ids.shape[0]), _ptr(packed),
+                                 ctypes.c_size_t(packed.numel()), _stream(kv_cache)))
+    return packed
+
+
+def pages_scatter(kv_cache, page_ids, packed):
+    """The reverse of ``pages_gather``: ``packed`` -> pages ``page_ids`` of ``kv_cache``."""
+    _pages_args(kv_cache, page_ids, packed)
+    _, nb, bs, H, ebs = kv_cache.shape
+    _check(lib().tq_pages_scatter(_ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(H),
+                                  ctypes.c_int(ebs), _ptr(page_ids), ctypes.c_int(page_ids.shape[0]), _ptr(packed),
+                                  ctypes.c_size_t(packed.numel()), _stream(kv_cache)))
+    return kv_cache
 
 
 def exchange_bytes(rows: int, world: int) -> int:

@@ -27,6 +27,7 @@ UNITS = {
     "tq_flat.cu": ["-fmad=false"],
     "tq_decode.cu": [],
     "tq_dequant.cu": ["-fmad=false"],
+    "tq_pages.cu": [],
 }
 
 

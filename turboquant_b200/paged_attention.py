@@ -151,6 +151,32 @@ class TurboQuantPagedAttention:
                             cu_seqlens.to(torch.int32), self.signs(dev), k, v, max_pages=block_table.shape[-1])
         return k, v
 
+    def offload_pages(self, kv_cache: torch.Tensor, page_ids: torch.Tensor, host: torch.Tensor | None = None):
+        """Packed copy of pages ``page_ids`` (K and V halves, 68 bytes per slot) in pinned host
+        memory; asynchronous on the current stream (synchronise before reading ``host``).  The
+        reference's offload study copies a whole slab, pad bytes included (tests/bench_kv_offload.py)."""
+        _, _, bs, H, _ = kv_cache.shape
+        n = page_ids.shape[0]
+        nbytes = _cabi.pages_packed_bytes(n, bs, H) if n else 0
+        staging = torch.empty(nbytes, dtype=torch.uint8, device=kv_cache.device)
+        if host is None:
+            host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+        if n:
+            _cabi.pages_gather(self._as_bytes(kv_cache), page_ids.to(torch.int32), staging)
+            host[:nbytes].copy_(staging, non_blocking=True)
+        return host
+
+    def restore_pages(self, kv_cache: torch.Tensor, page_ids: torch.Tensor, host: torch.Tensor) -> None:
+        """Bring pages offloaded by ``offload_pages`` back into (possibly different) pages ``page_ids``."""
+        _, _, bs, H, _ = kv_cache.shape
+        n = page_ids.shape[0]
+        if n == 0:
+            return
+        nbytes = _cabi.pages_packed_bytes(n, bs, H)
+        staging = torch.empty(nbytes, dtype=torch.uint8, device=kv_cache.device)
+        staging.copy_(host[:nbytes], non_blocking=True)
+        _cabi.pages_scatter(self._as_bytes(kv_cache), page_ids.to(torch.int32), staging)
+
     def status(self, batch: int, device, queries: int = 1) -> int:
         """Status word the decode kernel leaves in its workspace (0 = ok); synchronises."""
         return int(self.workspace(batch, device, queries)[:4].view(torch.int32).item())
