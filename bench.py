@@ -151,6 +151,26 @@ def cpu_decode_rate(cache_np, block_table_np, q_np, signs_np, ctx_sample: int, t
     return threads * ctx_sample * HKV / dt, dt
 
 
+def cpu_write_rate(k_np, v_np, slots_np, signs_np, num_blocks: int, threads: int):
+    """Tokens per second of the CPU cache write (the C port of the torch quantizer + pack + scatter),
+    `threads` chunks of the sample in parallel (ctypes releases the GIL)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import tq_oracle
+    cache = np.zeros((2, num_blocks, PAGE, HKV, SLOT), np.uint8)
+    n = k_np.shape[0]
+    chunks = [(i * n // threads, (i + 1) * n // threads) for i in range(threads)]
+
+    def one(c):
+        a, b = c
+        tq_oracle.write_kv_cache(cache, k_np[a:b], v_np[a:b], signs_np, slots_np[a:b], D)
+    one((0, min(n, 16)))
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        list(ex.map(one, chunks))
+    dt = time.perf_counter() - t0
+    return n / dt, dt
+
+
 def synthetic_host_cache(ctx: int, batch: int, seed: int):
     """A host-side quantized cache for the CPU arm when no GPU copy is at hand (reference arm)."""
     from oracle import tq_oracle
@@ -398,6 +418,13 @@ def run_ours(args):
                  "kernel": "write_kv_cache_kernel<bf16>", "ms": wt[len(wt) // 2], "algorithmic_bytes": w_alg,
                  "achieved": w_ach, "peak": peak, "unit": "GB/s", "frac": w_ach / peak,
                  "tokens_per_s": 32768 / (wt[len(wt) // 2] * 1e-3)}
+        if not args.no_cpu_baseline:
+            nsample = 8192
+            w_rate, w_dt = cpu_write_rate(wk[:nsample].float().cpu().numpy(), wv[:nsample].float().cpu().numpy(),
+                                          wslots[:nsample].cpu().numpy(), attn.signs(dev).cpu().numpy(), wnb,
+                                          os.cpu_count() or 1)
+            write["cpu_baseline"] = {"value": w_rate, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                     "sample": f"first {nsample} tokens of the same case ({w_dt:.2f} s)"}
         del wk, wv, wcaches
         # ---- bulk dequantization of cached tokens (continuation of a prefill): layer caches of the
         # decode workload, first ctx_d tokens of every sequence -> dense bf16 K / V
