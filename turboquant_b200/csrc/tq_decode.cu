@@ -65,22 +65,6 @@ constexpr int kMaxSegments = 96;
 constexpr int kMinPagesPerCta = 4;
 constexpr float kRaiseThreshold = 6.0f;  // log2 units
 
-// Token pitch of K rows in shared memory: = 64 (mod 128), with 48 spare bytes because row t is
-// additionally shifted by 16 * ((t & 7) >> 1) bytes (k_row_offset).  The 64-mod-128 pitch keeps
-// the 16-byte fragment loads of a token pair conflict free; the extra shift spreads the eight
-// norm words read by one instruction over eight different banks.
-constexpr int k_pitch(int H) {
-    int b = H * kSlotBytes + 48;
-    int pad = (64 - b % 128 + 128) % 128;
-    return b + pad;
-}
-__host__ __device__ constexpr int k_row_offset(int t, int pitch) { return t * pitch + 16 * ((t & 7) >> 1); }
-constexpr int v_pitch(int H) {  // token pitch of V rows: = 16 (mod 64)
-    int b = H * kSlotBytes;
-    int pad = (16 - b % 64 + 64) % 64;
-    return b + pad;
-}
-
 struct DecodeParams {
     const void* q;
     const uint8_t* kv_cache;
@@ -219,58 +203,59 @@ __device__ __forceinline__ void seq_pages(const DecodeParams& p, int b, int& fir
 }
 
 // Shared-memory stage layout.  A stage holds kPPS pages; page lane `pp` has a K region and a V
-// region.  Two variants:
-//
-// HKV == 8 (a token row is 640 B = 0 mod 128): each page half is copied as four runs of four
-// tokens (2560 B per bulk copy; copies of 640 B were found to be limited by the copy engine's
-// request rate, 2.5 KB and larger are not).  Tokens of one run share their bank offset, so the
-// runs are placed at distinct offsets mod 128 (K: 0, 64, 16, 80; V: 0, 32, 64, 96) and MMA row
-// r is mapped to token row_token(r) such that every group of lanes served together reads from
-// different runs: rows (2p, 2p+1) of a K fragment load come from runs 64 bytes apart, the four
-// tokens of a V fragment load from four different runs.  Norm loads see a 2-way conflict.
-//
-// HKV < 8: one bulk copy per token row, padded pitches (K: 64 mod 128 plus a per-row shift that
-// spreads the norm words over the banks, V: 16 mod 64), identity row order.
+// region.  Each page half is copied as runs of kRunTokens consecutive token rows, one bulk copy
+// per run: 2560 bytes for 8, 4 and 2 KV heads, 1280 for one (copies of a few hundred bytes were
+// found to be limited by the copy engine's request rate, 2.5 KB and larger are not).  A run is
+// dense, so the bank of a row is fixed by the row size (640, 320, 160, 80 bytes = 0, 64, 32, 80
+// mod 128); the runs' base offsets and the map from MMA row r to token row_token(r) are chosen per
+// head count such that every group of lanes served together reads different banks: rows
+// (2p, 2p+1) of a K fragment load lie 64 bytes apart mod 128, the four tokens of a V fragment
+// load 32 bytes apart (checked for every head by a bank simulation; the only exception is the K
+// load with one KV head, two wavefronts instead of one).  Rows r and r + 8 map to tokens a fixed
+// distance apart inside one run, so five address registers serve the twelve loads of a tile.
 template <int HKV>
 struct DecodeSmem {
     static constexpr int kPPS = kConsumerWarps / HKV;  // pages per stage
-    static constexpr bool kRuns = HKV == 8;
     static constexpr int kRowBytes = HKV * kSlotBytes;
-    static constexpr int kKPitch = k_pitch(HKV);
-    static constexpr int kVPitch = v_pitch(HKV);
-    static constexpr int kKRegion = kRuns ? 10496 : kPageTokens * kKPitch;  // per page lane
-    static constexpr int kVRegion = kRuns ? 10368 : kPageTokens * kVPitch;
+    static constexpr int kRunTokens = HKV == 8 ? 4 : HKV == 4 ? 8 : 16;
+    static constexpr int kRunsPerHalf = kPageTokens / kRunTokens;
+    static constexpr int kCopyBytes = kRunTokens * kRowBytes;
+    static constexpr int kCopiesPerPage = 2 * kRunsPerHalf;
+    static constexpr int kCopiesPerStage = kPPS * kCopiesPerPage;  // 16, 16, 16, 32: one lane each
+    static constexpr int kKRegion = HKV == 8 ? 10496 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;  // per page lane
+    static constexpr int kVRegion = HKV == 8 ? 10368 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;
     static constexpr int kKBytes = kPPS * kKRegion;
     static constexpr int kVBytes = kPPS * kVRegion;
     static constexpr int kStageBytes = kKBytes + kVBytes;
-    static constexpr int kCopiesPerPage = kRuns ? 8 : 32;
-    static constexpr int kCopyBytes = kRuns ? 4 * kRowBytes : kRowBytes;
 
-    // token (0..15 within its page) -> byte offset of its row inside the page lane's region
-    static __device__ __forceinline__ int k_off(int t) {
-        if (kRuns) {
-            const int q = t >> 2;
-            return q * 2560 + (t & 3) * kRowBytes + ((q & 1) ? 64 : 0) + ((q & 2) ? 144 : 0);  // 0, 2624, 5264, 7888
-        }
-        return k_row_offset(t, kKPitch);
+    // run q of a page half -> byte offset of its first row inside the page lane's region
+    static __host__ __device__ __forceinline__ constexpr int k_run(int q) {
+        return HKV == 8 ? q * 2560 + ((q & 1) ? 64 : 0) + ((q & 2) ? 144 : 0)  // 0, 2624, 5264, 7888
+               : HKV == 4 ? q * 2576                                             // 0, 2576
+                          : 0;
     }
-    static __device__ __forceinline__ int v_off(int t) {
-        if (kRuns) return (t >> 2) * 2592 + (t & 3) * kRowBytes;  // runs at 0, 2592, 5184, 7776
-        return t * kVPitch;
+    static __host__ __device__ __forceinline__ constexpr int v_run(int q) {
+        return HKV == 8 ? q * 2592 : HKV == 4 ? q * 2592 : 0;
+    }
+    // token (0..15 within its page) -> byte offset of its row inside the page lane's region
+    static __host__ __device__ __forceinline__ constexpr int k_off(int t) {
+        return k_run(t / kRunTokens) + (t % kRunTokens) * kRowBytes;
+    }
+    static __host__ __device__ __forceinline__ constexpr int v_off(int t) {
+        return v_run(t / kRunTokens) + (t % kRunTokens) * kRowBytes;
     }
     // MMA row / contraction slot r (0..15) -> token within the page
-    static __device__ __forceinline__ int row_token(int r) {
-        if (kRuns) {
-            const int r7 = r & 7;
-            const int q = (0x23013210 >> (4 * r7)) & 3;  // runs 0,1,2,3,1,0,3,2 for rows 0..7
-            return 4 * q + (r7 >> 2) + 2 * (r >> 3);
-        }
-        return r;
+    static __host__ __device__ __forceinline__ constexpr int row_token(int r) {
+        const int r7 = r & 7, up = r >> 3;
+        return HKV == 8   ? 4 * ((0x23013210 >> (4 * r7)) & 3) + (r7 >> 2) + 2 * up   // runs 0,1,2,3,1,0,3,2
+               : HKV == 4 ? ((0xAB239810u >> (4 * r7)) & 15) + 4 * up                 // 0,1,8,9,3,2,11,10
+               : HKV == 2 ? ((0x53427160u >> (4 * r7)) & 7) + 8 * up                  // 0,6,1,7,2,4,3,5
+                          : r;
     }
     // MMA rows r and r+8 sit a fixed distance apart in both regions (runs: two tokens further in
     // the same run; pitched rows: eight rows further)
-    static constexpr int kKRow8 = kRuns ? 2 * kRowBytes : 8 * kKPitch;
-    static constexpr int kVRow8 = kRuns ? 2 * kRowBytes : 8 * kVPitch;
+    static constexpr int kKRow8 = k_off(row_token(8)) - k_off(row_token(0));
+    static constexpr int kVRow8 = v_off(row_token(8)) - v_off(row_token(0));
     // per-warp scratch: rotated Q (fp16, `group` rows), reused to transpose the partial output
     // (2 x 128 floats), hence at least four rows
     static constexpr int q_rows(int group) { return group < 4 ? 4 : group; }
@@ -423,13 +408,13 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     if (lane == 0)
                         mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(np * 2 * kPageTokens * S::kRowBytes));
                     __syncwarp();
-#pragma unroll
-                    for (int pp = 0; pp < PPS; pp++) {
+                    {
+                        // one copy per lane: lane = page lane * copies per page + (K runs, then V runs)
+                        const int pp = lane / S::kCopiesPerPage, c = lane % S::kCopiesPerPage;
                         const int page = __shfl_sync(0xffffffffu, my_page, (j + pp) & 31);
-                        if (pp < np && lane < S::kCopiesPerPage) {
-                            constexpr int kHalf = S::kCopiesPerPage / 2;
-                            const bool is_v = lane >= kHalf;
-                            const int tok = (lane % kHalf) * (kPageTokens / kHalf);  // first token of the copy
+                        if (lane < S::kCopiesPerStage && pp < np) {
+                            const bool is_v = c >= S::kRunsPerHalf;
+                            const int tok = (c % S::kRunsPerHalf) * S::kRunTokens;  // first token of the run
                             const uint8_t* src = p.kv_cache + (is_v ? p.slab_bytes : 0) +
                                                  ((int64_t)page * kPageTokens + tok) * S::kRowBytes;
                             uint8_t* dst = is_v ? sv + pp * S::kVRegion + S::v_off(tok)
@@ -959,8 +944,8 @@ template <int HKV>
 static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
     using S = DecodeSmem<HKV>;
     // Wide lookup table (one instruction less per code byte) when its fixed shared-memory map fits:
-    // 8 KV heads and at most four query heads per KV head.  See the map above the kernel.
-    if (HKV == 8 && p.group <= 4) {
+    // at most four query columns per KV head.  See the map above the kernel.
+    if (p.group <= 4) {
         p.num_stages = kWideStages;
         const int smem = (int)(kWideLutAddr + kWideLutBytes) + (kWideStages - 1) * S::kStageBytes;  // from offset 0: ample
         return launch_decode_impl<HKV, true>(p, grid, smem, stream);

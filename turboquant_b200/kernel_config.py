@@ -62,14 +62,9 @@ def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> Kernel
     if not 1 <= g <= 8:
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"GQA ratio {g}: 1..8 is implemented")
     pps = CONSUMER_WARPS // h
-    row = h * SLOT_BYTES
-    if h == 8:
-        stage = pps * (10496 + 10368)
-    else:
-        kp = row + 48 + ((64 - (row + 48) % 128) % 128)
-        vp = row + ((16 - row % 64) % 64)
-        stage = pps * PAGE_TOKENS * (kp + vp)
-    if h == 8 and g <= 4:
+    # per page lane: K region + V region (runs of token rows, placed for conflict-free fragment loads)
+    stage = pps * {8: 10496 + 10368, 4: 5248 + 5248, 2: 2560 + 2560, 1: 1280 + 1280}[h]
+    if g <= 4:
         # wide lookup table (256 B per entry at the 64 KB boundary of the shared window): fixed map
         # with three stages, one below the table and two above it
         return KernelConfig(CONSUMER_WARPS, pps, 3, stage)
