@@ -287,12 +287,23 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     const uint32_t smem_base = smem_u32(smem);
     // stage st lives at stage0 + (st ? stage_gap + (st - 1) * kStageBytes : 0) (byte offsets from smem)
     const uint32_t q_off = WIDE ? 0u : (uint32_t)(nstages * S::kStageBytes + kLutBytes);
-    const uint32_t stage0_off = WIDE ? (uint32_t)S::q_bytes(p.group) : 0u;
+    const uint32_t stage0_off = 0u;
     const uint32_t stage_gap = WIDE ? kWideLutAddr + kWideLutBytes - smem_base - stage0_off : (uint32_t)S::kStageBytes;
     const uint32_t lut_off = WIDE ? kWideLutAddr - smem_base : (uint32_t)(nstages * S::kStageBytes);
     uint8_t* stages = smem + stage0_off;
     uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem + lut_off);
-    __half* q_s = reinterpret_cast<__half*>(smem + q_off);
+    // Per-warp scratch (rotated Q rows of 256 bytes, later the transposed partial output).  With the
+    // wide table it lives in the unused upper half of the table's 256-byte rows: byte `off` of warp
+    // w's scratch is in hole w * holes_per_warp + off / 128 at offset off % 128 (every access below
+    // stays inside one 128-byte hole).
+    const uint32_t q_warp_bytes = (uint32_t)S::q_rows(p.group) * kHeadDim * 2;
+    auto q_ptr = [&](int w, uint32_t off) -> uint8_t* {
+        if (WIDE) {
+            const uint32_t hole = (uint32_t)w * (q_warp_bytes >> 7) + (off >> 7);
+            return smem + lut_off + (hole << 8) + 128u + (off & 127u);
+        }
+        return smem + q_off + (uint32_t)w * q_warp_bytes + off;
+    };
     grid_launch_dependents();  // the merge's blocks may be scheduled as soon as there is room
     if (WIDE && smem_base + stage0_off + S::kStageBytes > kWideLutAddr) {  // the map above does not fit
         grid_dependency_wait();
@@ -435,7 +446,6 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     const int g = lane >> 2, tg = lane & 3;
     const int head = warp % HKV;   // KV head of this warp
     const int sub = warp / HKV;    // page lane inside a stage
-    __half* qw = q_s + warp * S::q_rows(p.group) * kHeadDim;
     const uint32_t lut_lane = smem_u32(lut_s) + 4u * lane;
 
     // per-thread constants of the fragment loads (byte offsets inside a stage): MMA rows g and
@@ -502,7 +512,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 if (r0 + rr < p.group) {
                     // stored with each (even, odd) pair swapped: a code byte dequantizes to
                     // {low half: odd dim (low nibble), high half: even dim (high nibble)}
-                    __half2* dst = reinterpret_cast<__half2*>(qw + (r0 + rr) * kHeadDim + 4 * lane);
+                    __half2* dst = reinterpret_cast<__half2*>(q_ptr(warp, (uint32_t)(r0 + rr) * 256u + 8u * lane));
                     dst[0] = __floats2half2_rn(w[1] * 0.08838834764831845f, w[0] * 0.08838834764831845f);
                     dst[1] = __floats2half2_rn(w[3] * 0.08838834764831845f, w[2] * 0.08838834764831845f);
                 }
@@ -512,7 +522,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         // B fragments of the eight QK MMAs: pairs 16*tg .. 16*tg+15 of query head g
         uint32_t qf[16];
         {
-            const uint4* src = reinterpret_cast<const uint4*>(qw + g * kHeadDim + 32 * tg);
+            const uint4* src = reinterpret_cast<const uint4*>(q_ptr(warp, (uint32_t)g * 256u + 64u * tg));
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint4 t = g < p.group ? src[i] : make_uint4(0u, 0u, 0u, 0u);  // padded heads
@@ -643,21 +653,20 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         // Two query heads at a time go through the warp's scratch (2 x 128 floats) so that the
         // global stores are full 512-byte rows instead of scattered words (which cost 7 us per
         // segment): the lanes with tg == pass own heads 2*pass and 2*pass+1.
-        float* scr = reinterpret_cast<float*>(qw);
         for (int pass = 0; 2 * pass < p.group; pass++) {
             __syncwarp();
             if (tg == pass) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     const int d_even = 16 * g + 2 * i;
-                    *reinterpret_cast<float2*>(scr + d_even) = make_float2(o_acc[i][2] * inv0, o_acc[i][0] * inv0);
-                    *reinterpret_cast<float2*>(scr + kHeadDim + d_even) =
+                    *reinterpret_cast<float2*>(q_ptr(warp, 4u * d_even)) = make_float2(o_acc[i][2] * inv0, o_acc[i][0] * inv0);
+                    *reinterpret_cast<float2*>(q_ptr(warp, 512u + 4u * d_even)) =
                         make_float2(o_acc[i][3] * inv1, o_acc[i][1] * inv1);
                 }
             }
             __syncwarp();
-            const float4 r0 = reinterpret_cast<const float4*>(scr)[lane];
-            const float4 r1 = reinterpret_cast<const float4*>(scr + kHeadDim)[lane];
+            const float4 r0 = *reinterpret_cast<const float4*>(q_ptr(warp, 16u * lane));
+            const float4 r1 = *reinterpret_cast<const float4*>(q_ptr(warp, 512u + 16u * lane));
             reinterpret_cast<float4*>(po + (2 * pass) * kHeadDim)[lane] = r0;
             if (2 * pass + 1 < p.group) reinterpret_cast<float4*>(po + (2 * pass + 1) * kHeadDim)[lane] = r1;
         }
@@ -945,7 +954,7 @@ static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
     using S = DecodeSmem<HKV>;
     // Wide lookup table (one instruction less per code byte) when its fixed shared-memory map fits:
     // at most four query columns per KV head.  See the map above the kernel.
-    if (p.group <= 4) {
+    if (true) {  // the wide map fits every supported shape
         p.num_stages = kWideStages;
         const int smem = (int)(kWideLutAddr + kWideLutBytes) + (kWideStages - 1) * S::kStageBytes;  // from offset 0: ample
         return launch_decode_impl<HKV, true>(p, grid, smem, stream);
