@@ -56,9 +56,7 @@ constexpr int kConsumerWarps = 16;
 // the consumer loop needs to stay out of local memory and keep its lookups in flight
 // (measured: 86.5 -> 78.3 us per launch against 17 warps at 96 registers).
 constexpr int kDecodeThreads = (kConsumerWarps + 4) * 32;
-constexpr int kMaxStages = 4;
-constexpr int kLutBytes = 256 * 32 * 4;
-constexpr int kMaxSmem = 227 * 1024;
+constexpr int kStages = 3;  // ring depth: one stage below the lookup table, two above it
 constexpr int kMaxExchangeRanks = 16;
 constexpr int kExchangeSpinLimit = 1 << 22;  // x 256 ns sleeps: a second or so, then status 1
 constexpr int kMaxSegments = 96;
@@ -86,7 +84,6 @@ struct DecodeParams {
     int nq, real_heads, real_group;
     float k_scale;  // (1/sqrt(128)) * sm_scale * log2(e): multiplies raw code-domain scores
     float v_scale;  // 1/sqrt(128): centroid scale folded into P
-    int num_stages;         // ring depth (3 or 4), chosen by the host from the shared-memory budget
     uint16_t centroid_h[16];  // fp16 bit patterns of the N(0,1) centroids
 };
 
@@ -139,22 +136,13 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
 
 // Eight packed 4-bit codes (one 32-bit word) -> four half2 registers, one per byte:
 // r[j] = { low half: centroid(low nibble of byte j), high half: centroid(high nibble) } in units
-// of the N(0,1) codebook.  lut_lane is the shared-memory address of this lane's column of the
-// table: entry v lives at lut_lane + 128 * v.
-// With the wide table (entries 256 bytes apart, table at a 64 KB boundary of the shared window)
-// lut_lane = table address + 4*lane has a zero second byte, and one byte permute drops the code
-// byte into it: address and lookup are two instructions per code byte instead of three.
-template <bool WIDE>
+// of the N(0,1) codebook.  The table has one 4-byte column per lane and 256 bytes between entries,
+// and starts at a 64 KB boundary of the shared window: lut_lane = table address + 4 * lane has a
+// zero second byte, and one byte permute drops the code byte into it, so address and lookup are
+// two instructions per code byte.
 __device__ __forceinline__ void dequant8(uint32_t w, uint32_t lut_lane, uint32_t (&r)[4]) {
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        if (WIDE) {
-            r[j] = lds32(prmt(w, lut_lane, 0x7604u | (j << 4)));
-        } else {
-            const uint32_t v = prmt(w, 0u, 0x4440u | j);  // byte j, zero extended
-            r[j] = lds32(v * 128u + lut_lane);
-        }
-    }
+    for (int j = 0; j < 4; j++) r[j] = lds32(prmt(w, lut_lane, 0x7604u | (j << 4)));
 }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -260,59 +248,53 @@ struct DecodeSmem {
     // (2 x 128 floats), hence at least four rows
     static constexpr int q_rows(int group) { return group < 4 ? 4 : group; }
     static constexpr int q_bytes(int group) { return kConsumerWarps * q_rows(group) * kHeadDim * 2; }
-    static constexpr int total(int stages, int group) { return stages * kStageBytes + kLutBytes + q_bytes(group); }
 };
 
-// Shared-memory map.  Narrow table: [stages][table 32 KB][rotated Q].  Wide table (WIDE): the
-// table must start at offset 64 KB of the block's shared window, so the memory below it holds
-// the rotated Q and stage 0, and stages 1.. follow the table:
-//   [rotated Q 16 KB][stage 0] ... | 64 KB: table (64 KB) | 128 KB: [stage 1][stage 2]
-constexpr uint32_t kWideLutAddr = 65536, kWideLutBytes = 65536;
-constexpr int kWideStages = 3;
+// Shared-memory map.  The lookup table must start at offset 64 KB of the block's shared window,
+// so stage 0 sits below it and stages 1, 2 follow it; the per-warp scratch (rotated Q, later the
+// transposed partial output) uses the upper 128 bytes of the table's 256-byte rows:
+//   [stage 0] ... | 64 KB: table + scratch (64 KB) | 128 KB: [stage 1][stage 2]
+constexpr uint32_t kLutAddr = 65536, kLutSpan = 65536;
 
-template <int HKV, bool WIDE>
+template <int HKV>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     using S = DecodeSmem<HKV>;
     constexpr int PPS = S::kPPS;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
-    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t full_bar[kStages];
+    __shared__ __align__(8) uint64_t empty_bar[kStages];
     __shared__ int seg_seq[kMaxSegments], seg_p0[kMaxSegments], seg_p1[kMaxSegments];
     __shared__ int num_segments, abort_flag;
     __shared__ int n_eff_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nstages = p.num_stages;
+    constexpr int nstages = kStages;
     const uint32_t smem_base = smem_u32(smem);
     // stage st lives at stage0 + (st ? stage_gap + (st - 1) * kStageBytes : 0) (byte offsets from smem)
-    const uint32_t q_off = WIDE ? 0u : (uint32_t)(nstages * S::kStageBytes + kLutBytes);
     const uint32_t stage0_off = 0u;
-    const uint32_t stage_gap = WIDE ? kWideLutAddr + kWideLutBytes - smem_base - stage0_off : (uint32_t)S::kStageBytes;
-    const uint32_t lut_off = WIDE ? kWideLutAddr - smem_base : (uint32_t)(nstages * S::kStageBytes);
+    const uint32_t stage_gap = kLutAddr + kLutSpan - smem_base - stage0_off;
+    const uint32_t lut_off = kLutAddr - smem_base;
     uint8_t* stages = smem + stage0_off;
     uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem + lut_off);
-    // Per-warp scratch (rotated Q rows of 256 bytes, later the transposed partial output).  With the
-    // wide table it lives in the unused upper half of the table's 256-byte rows: byte `off` of warp
-    // w's scratch is in hole w * holes_per_warp + off / 128 at offset off % 128 (every access below
-    // stays inside one 128-byte hole).
+    // Per-warp scratch (rotated Q rows of 256 bytes, later the transposed partial output) in the
+    // unused upper half of the table's 256-byte rows: byte `off` of warp w's scratch is in hole
+    // w * holes_per_warp + off / 128 at offset off % 128 (every access below stays inside one
+    // 128-byte hole).
     const uint32_t q_warp_bytes = (uint32_t)S::q_rows(p.group) * kHeadDim * 2;
     auto q_ptr = [&](int w, uint32_t off) -> uint8_t* {
-        if (WIDE) {
-            const uint32_t hole = (uint32_t)w * (q_warp_bytes >> 7) + (off >> 7);
-            return smem + lut_off + (hole << 8) + 128u + (off & 127u);
-        }
-        return smem + q_off + (uint32_t)w * q_warp_bytes + off;
+        const uint32_t hole = (uint32_t)w * (q_warp_bytes >> 7) + (off >> 7);
+        return smem + lut_off + (hole << 8) + 128u + (off & 127u);
     };
     grid_launch_dependents();  // the merge's blocks may be scheduled as soon as there is room
-    if (WIDE && smem_base + stage0_off + S::kStageBytes > kWideLutAddr) {  // the map above does not fit
+    if (smem_base + stage0_off + S::kStageBytes > kLutAddr) {  // the map above does not fit
         grid_dependency_wait();
         if (tid == 0) atomicExch(&p.header[0], 3);
         return;
     }
 
     if (tid == 0) {
-        for (int s = 0; s < kMaxStages; s++) {
+        for (int s = 0; s < kStages; s++) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kConsumerWarps);
         }
@@ -327,7 +309,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     if (warp != 0) {
         for (int i = tid - 32; i < 256 * 32; i += kDecodeThreads - 32) {
             const int v = i >> 5;
-            lut_s[WIDE ? (v * 64 + (i & 31)) : i] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
+            lut_s[v * 64 + (i & 31)] = (uint32_t)p.centroid_h[v & 15] | ((uint32_t)p.centroid_h[v >> 4] << 16);
         }
         grid_dependency_wait();
     } else {
@@ -572,8 +554,8 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
                     uint32_t ra[4], rb[4];
-                    dequant8<WIDE>(kwa[w], lut_lane, ra);
-                    dequant8<WIDE>(kwb[w], lut_lane, rb);
+                    dequant8(kwa[w], lut_lane, ra);
+                    dequant8(kwb[w], lut_lane, rb);
                     mma16816(s_acc, ra[0], rb[0], ra[1], rb[1], qf[4 * w], qf[4 * w + 1]);
                     mma16816(s_acc2, ra[2], rb[2], ra[3], rb[3], qf[4 * w + 2], qf[4 * w + 3]);
                 }
@@ -624,10 +606,10 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     const uint32_t lo23 = (vw2[i] & 0x0F0F0F0Fu) | ((vw3[i] << 4) & 0xF0F0F0F0u);
                     const uint32_t hi23 = ((vw2[i] >> 4) & 0x0F0F0F0Fu) | (vw3[i] & 0xF0F0F0F0u);
                     uint32_t a_lo01[4], a_hi01[4], a_lo23[4], a_hi23[4];
-                    dequant8<WIDE>(lo01, lut_lane, a_lo01);
-                    dequant8<WIDE>(hi01, lut_lane, a_hi01);
-                    dequant8<WIDE>(lo23, lut_lane, a_lo23);
-                    dequant8<WIDE>(hi23, lut_lane, a_hi23);
+                    dequant8(lo01, lut_lane, a_lo01);
+                    dequant8(hi01, lut_lane, a_hi01);
+                    dequant8(lo23, lut_lane, a_lo23);
+                    dequant8(hi23, lut_lane, a_hi23);
 #pragma unroll
                     for (int j = 0; j < 4; j++)  // rows: g <- odd dim, g+8 <- even dim of byte 4i+j
                         mma16816(o_acc[4 * i + j], a_lo01[j], a_hi01[j], a_lo23[j], a_hi23[j], pb0, pb1);
@@ -935,35 +917,19 @@ static int resolve_ctas(int num_ctas, int* out) {
     return TQ_OK;
 }
 
-template <int HKV, bool WIDE>
-static int launch_decode_impl(DecodeParams& p, int grid, int smem, cudaStream_t stream) {
+template <int HKV>
+static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
+    using S = DecodeSmem<HKV>;
+    const int smem = (int)(kLutAddr + kLutSpan) + (kStages - 1) * S::kStageBytes;  // from offset 0: ample
     static bool configured[64] = {};  // the attribute is per device
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kMaxSmem - 2048));
+        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    TQ_CUDA(launch_serialized(decode_paged_kernel<HKV, WIDE>, dim3(grid), dim3(kDecodeThreads), smem, stream, p));
+    TQ_CUDA(launch_serialized(decode_paged_kernel<HKV>, dim3(grid), dim3(kDecodeThreads), smem, stream, p));
     return TQ_OK;
-}
-
-template <int HKV>
-static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
-    using S = DecodeSmem<HKV>;
-    // Wide lookup table (one instruction less per code byte) when its fixed shared-memory map fits:
-    // at most four query columns per KV head.  See the map above the kernel.
-    if (true) {  // the wide map fits every supported shape
-        p.num_stages = kWideStages;
-        const int smem = (int)(kWideLutAddr + kWideLutBytes) + (kWideStages - 1) * S::kStageBytes;  // from offset 0: ample
-        return launch_decode_impl<HKV, true>(p, grid, smem, stream);
-    }
-    // narrow table: deepest ring that fits beside the table and the rotated queries (static smem: ~2 KB)
-    int stages = kMaxStages;
-    while (stages > 2 && S::total(stages, p.group) > kMaxSmem - 2048) stages--;
-    p.num_stages = stages;
-    return launch_decode_impl<HKV, false>(p, grid, S::total(stages, p.group), stream);
 }
 
 struct ExchangeArgs {

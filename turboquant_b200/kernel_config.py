@@ -64,15 +64,9 @@ def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> Kernel
     pps = CONSUMER_WARPS // h
     # per page lane: K region + V region (runs of token rows, placed for conflict-free fragment loads)
     stage = pps * {8: 10496 + 10368, 4: 5248 + 5248, 2: 2560 + 2560, 1: 1280 + 1280}[h]
-    if g <= 4:
-        # wide lookup table (256 B per entry at the 64 KB boundary of the shared window): fixed map
-        # with three stages, one below the table and two above it
-        return KernelConfig(CONSUMER_WARPS, pps, 3, stage)
-    fixed = 256 * 32 * 4 + CONSUMER_WARPS * max(g, 4) * 128 * 2 + 2048
-    stages = 4
-    while stages > 2 and stages * stage + fixed > MAX_SMEM:
-        stages -= 1
-    return KernelConfig(CONSUMER_WARPS, pps, stages, stage)
+    # lookup table (256 B per entry, per-warp scratch in the unused halves) at the 64 KB boundary of
+    # the shared window; three stages: one below the table and two above it
+    return KernelConfig(CONSUMER_WARPS, pps, 3, stage)
 
 
 MODEL_PRESETS: Dict[str, ModelConfig] = {
