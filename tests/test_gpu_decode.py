@@ -221,3 +221,31 @@ def test_shared_kv_rejects_more_than_8_columns():
     ws = torch.zeros(_cabi.decode_workspace_bytes(1, 96, 8, 128, 0), dtype=torch.uint8, device=DEV)
     with pytest.raises(_cabi.TurboQuantError, match="queries_per_seq"):
         _cabi.decode_paged_multi(q, cache, bt, sl, signs_dev(), SCALE, ws, torch.empty_like(q))
+
+
+def test_many_short_sequences(oracle, golden):
+    """A large batch of short sequences (several sequences per thread block, empty ones among them)."""
+    rng = np.random.default_rng(5)
+    lens = [int(x) for x in rng.integers(0, 200, size=300)]
+    case = synthetic.decode_case(seed=33, seq_lens=lens, dtype=torch.float16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    want = oracle.decode_paged(case.q.float().numpy(), cache, case.block_table.numpy(), case.seq_lens.numpy(),
+                               golden["signs_seed42_d128"], SCALE)
+    for ctas in (0, 7):
+        out = run_decode(case.q.to(DEV), torch.from_numpy(cache).to(DEV), case.block_table.to(DEV),
+                         case.seq_lens.to(DEV), num_ctas=ctas)
+        assert_attention_close(out.float().cpu().numpy(), want, f"300 short sequences, ctas={ctas}")
+
+
+def test_too_many_sequences_per_block_is_reported():
+    """More than 96 sequences inside one block's page range: status 2 in the workspace, no fault."""
+    B = 200
+    cache = torch.zeros(2, B, 16, 8, 80, dtype=torch.uint8, device=DEV)
+    bt = torch.arange(B, dtype=torch.int32, device=DEV).view(B, 1)
+    sl = torch.full((B,), 5, dtype=torch.int32, device=DEV)
+    q = torch.zeros(B, 32, 128, dtype=torch.float16, device=DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(B, 32, 8, 128, 1), dtype=torch.uint8, device=DEV)
+    out = torch.empty_like(q)
+    _cabi.decode_paged(q, cache, bt, sl, signs_dev(), SCALE, ws, out, num_ctas=1)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 2
