@@ -136,3 +136,62 @@ def test_vllm_backend_impl_write_and_decode(oracle, golden):
     want = oracle.decode_paged(case.q.float().numpy(), kv_cache.cpu().numpy(), case.block_table.numpy(),
                                case.seq_lens.numpy(), golden["signs_seed42_d128"], SCALE)
     assert_attention_close(out.float().cpu().numpy().reshape(4, 32, 128), want, "vLLM impl decode")
+
+
+def test_vllm_backend_continuation_prefill(oracle, golden):
+    """A chunk of new tokens over sequences with cached context: the backend dequantizes the cached
+    tokens, appends the chunk's fresh K/V and runs causal varlen attention; checked against plain
+    torch attention over the same dense K/V (oracle-dequantized cache + fresh chunk)."""
+    pytest.importorskip("vllm")
+    from turboquant_b200.vllm_backend_fused import TurboQuantBackend, TurboQuantFusedImpl
+    try:
+        impl = TurboQuantFusedImpl(32, 128, SCALE, 8, None, None, "fp8")
+        from vllm.vllm_flash_attn import flash_attn_varlen_func  # noqa: F401
+    except Exception as e:
+        pytest.skip(f"vLLM attention pieces not usable here: {type(e).__name__}: {e}")
+    cached = [100, 0, 37]
+    chunk = [5, 8, 3]
+    total = [c + q for c, q in zip(cached, chunk)]
+    case = synthetic.decode_case(seed=83, seq_lens=total, dtype=torch.bfloat16)
+    shape = TurboQuantBackend.get_kv_cache_shape(case.num_blocks, 16, 8, 128, "fp8")
+    kv_cache = torch.zeros(shape, dtype=torch.uint8, device=DEV)
+    impl.do_kv_cache_update(None, case.k.to(DEV), case.v.to(DEV), kv_cache, case.slot_mapping.to(DEV))
+    # the chunk: the last chunk[b] tokens of every sequence (their K/V are case.k / case.v rows)
+    starts = np.concatenate([[0], np.cumsum(total)])
+    rows = np.concatenate([np.arange(starts[b] + cached[b], starts[b + 1]) for b in range(3)])
+    n = len(rows)
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(n, 32, 128, generator=g).to(torch.bfloat16)
+    key, value = case.k[rows], case.v[rows]
+    qsl = torch.tensor(np.concatenate([[0], np.cumsum(chunk)]), dtype=torch.int32, device=DEV)
+    md = types.SimpleNamespace(max_query_len=max(chunk), num_actual_tokens=n, block_table=case.block_table.to(DEV),
+                               seq_lens=case.seq_lens.to(DEV), query_start_loc=qsl, max_seq_len=max(total))
+    out = torch.zeros(n, 32 * 128, dtype=torch.bfloat16, device=DEV)
+    try:
+        impl.forward(None, q.to(DEV).reshape(n, -1), key.to(DEV), value.to(DEV), kv_cache, md, output=out)
+    except (RuntimeError, ImportError) as e:
+        if "flash" in str(e).lower() or "FA" in str(e):
+            pytest.skip(f"vLLM's FlashAttention does not run on this device: {e}")
+        raise
+    got = out.float().cpu().numpy().reshape(n, 32, 128)
+    # reference: dense K/V per sequence = oracle dequant of the cached rows + the fresh chunk, fp32 softmax
+    cache_np = kv_cache.cpu().numpy()
+    signs = golden["signs_seed42_d128"]
+    want = np.zeros_like(got)
+    qi = 0
+    for b in range(3):
+        t = np.arange(cached[b])
+        pages = case.block_table.numpy()[b, t // 16]
+        kc = oracle.dequant_cache_rows(cache_np[0, pages, t % 16], signs, 128).reshape(-1, 8, 128)
+        vc = oracle.dequant_cache_rows(cache_np[1, pages, t % 16], signs, 128).reshape(-1, 8, 128)
+        kc = torch.from_numpy(kc).to(torch.bfloat16).float()        # the backend holds them in the query dtype
+        vc = torch.from_numpy(vc).to(torch.bfloat16).float()
+        ka = torch.cat([kc, case.k[starts[b] + cached[b]:starts[b + 1]].float()])
+        va = torch.cat([vc, case.v[starts[b] + cached[b]:starts[b + 1]].float()])
+        for i in range(chunk[b]):
+            kk, vv = ka[: cached[b] + i + 1], va[: cached[b] + i + 1]
+            qq = q[qi].float().view(8, 4, 128)
+            sc = torch.einsum("hgd,thd->hgt", qq, kk) * SCALE
+            want[qi] = torch.einsum("hgt,thd->hgd", torch.softmax(sc, -1), vv).reshape(32, 128).numpy()
+            qi += 1
+    assert_attention_close(got, want, "continuation prefill")

@@ -8,8 +8,12 @@ methods and cache layout of the reference (turboquant/vllm_backend_fused.py:32-4
 * ``TurboQuantFusedImpl.do_kv_cache_update``: quantizes K and V of the step and scatters them into
   the cache (one launch; bf16/fp16 K/V and int64 slots are read as they are).
 * ``TurboQuantFusedImpl.forward``: decode steps (``max_query_len == 1``) run the paged decode
-  kernel on the quantized cache; prefill runs FlashAttention on the step's fresh K/V, exactly as
-  the reference does (its prefill never reads the quantized cache).
+  kernel on the quantized cache.  A prefill step whose sequences have nothing cached yet runs
+  FlashAttention on the step's fresh K/V, exactly as the reference does.  A prefill chunk that
+  continues sequences with cached context (which the reference does not handle: its prefill never
+  reads the quantized cache, vllm_backend_fused.py:336-369) first dequantizes the cached tokens
+  into a dense varlen K/V (``tq_dequant_paged``), puts the chunk's fresh K/V behind them and runs
+  the same varlen FlashAttention with bottom-right causal masking.
 * ``TurboQuantMetadataBuilder``: the reference's is an empty subclass that sizes a uniform split
   count on the host; here the split plan is made inside the kernel from ``seq_lens``, so the
   builder only has to keep the FlashAttention metadata (block table, lengths) as it is.
@@ -115,10 +119,16 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
                                    output_block_scale, **kwargs)
         n = attn_metadata.num_actual_tokens
         if attn_metadata.max_query_len != 1:
-            # prefill: attention over the fresh K/V of this step; the quantized cache is not read
             from vllm.vllm_flash_attn import flash_attn_varlen_func
             if output is None:
                 output = torch.empty_like(query[:n])
+            max_seq_len = getattr(attn_metadata, "max_seq_len", attn_metadata.max_query_len)
+            if max_seq_len > attn_metadata.max_query_len:
+                out = self._continuation_prefill(query[:n], key[:n], value[:n], kv_cache, attn_metadata, max_seq_len,
+                                                 flash_attn_varlen_func)
+                output[:n] = out.to(output.dtype).view(output[:n].shape)
+                return output
+            # first chunk: attention over the fresh K/V of this step; the quantized cache is not read
             out = flash_attn_varlen_func(query[:n], key[:n], value[:n],
                                          cu_seqlens_q=attn_metadata.query_start_loc,
                                          cu_seqlens_k=attn_metadata.query_start_loc,
@@ -133,3 +143,37 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         out = output[:n].view(n, self.num_heads, self.head_size)
         self._attn.decode(q, kv_cache, attn_metadata.block_table[:n], attn_metadata.seq_lens[:n], out)
         return output
+
+    def _continuation_prefill(self, query, key, value, kv_cache, md, max_seq_len, flash_attn_varlen_func):
+        """Chunk of new tokens over sequences with cached context.  Sequence b contributes
+        ``seq_lens[b]`` keys: its ``seq_lens[b] - q_len[b]`` cached tokens, dequantized from the
+        cache, then the chunk's own fresh K/V (the chunk is already in the cache as well, quantized;
+        its fresh values are used, as a first chunk would).  No host synchronisation: the dense
+        buffer is sized by the ``batch x max_seq_len`` bound, rows beyond ``cu_k[-1]`` are unused."""
+        dev = query.device
+        qsl = md.query_start_loc.to(torch.int32)
+        B = qsl.shape[0] - 1
+        seq_lens = md.seq_lens[:B].to(torch.int32)
+        q_lens = qsl[1:] - qsl[:-1]
+        cached = seq_lens - q_lens
+        cu_k = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+        cu_k[1:] = torch.cumsum(seq_lens, 0)
+        rows = B * int(max_seq_len)
+        k_all = torch.empty((rows, self.num_kv_heads, self.head_size), dtype=query.dtype, device=dev)
+        v_all = torch.empty_like(k_all)
+        from . import _cabi
+        bt = md.block_table[:B]
+        if bt.dtype != torch.int32:
+            bt = bt.to(torch.int32)
+        _cabi.dequant_paged(self._attn._as_bytes(kv_cache), bt.contiguous(), cached.contiguous(), cu_k,
+                            self._attn.signs(dev), k_all, v_all, max_pages=bt.shape[-1])
+        # fresh rows of the chunk go behind the cached rows of their sequence
+        n = query.shape[0]
+        tok = torch.arange(n, device=dev, dtype=torch.int32)
+        seq_of = torch.bucketize(tok, qsl[1:], right=True)
+        dest = (cu_k[:-1][seq_of] + cached[seq_of] + (tok - qsl[:-1][seq_of])).long()
+        k_all[dest] = key.view(n, self.num_kv_heads, self.head_size).to(k_all.dtype)
+        v_all[dest] = value.view(n, self.num_kv_heads, self.head_size).to(v_all.dtype)
+        return flash_attn_varlen_func(query.view(n, self.num_heads, self.head_size), k_all, v_all,
+                                      cu_seqlens_q=qsl, cu_seqlens_k=cu_k, max_seqlen_q=md.max_query_len,
+                                      max_seqlen_k=int(max_seq_len), softmax_scale=self.scale, causal=True)
