@@ -38,7 +38,7 @@ struct DequantParams {
     const float* signs;
     void* out[2];                 // K, V: [total_tokens][H][128]
     int64_t out_token_stride;     // elements between tokens
-    int max_pages, H, block_size, slot_bytes, out_dtype, batch;
+    int max_pages, H, head_shift, block_size, slot_bytes, out_dtype, batch;  // head_shift: log2(H) or -1
     float cen[16];                // (float)(C[i] / sqrt(128))
     float scale;                  // (float)(1 / sqrt(128))
 };
@@ -59,52 +59,56 @@ __device__ __forceinline__ Q2 qfma(Q2 a, Q2 b, Q2 c) {
     return r;
 }
 
+// 16-byte piece i of a lane's 64 output elements in the output type.
 template <int DT>
-__device__ __forceinline__ void store_pairs(void* dst, const Q2 (&x)[32]);
+__device__ __forceinline__ uint4 out_piece(const Q2 (&x)[32], int i);
 
 template <>
-__device__ __forceinline__ void store_pairs<TQ_F32>(void* dst, const Q2 (&x)[32]) {
-    float4* d = reinterpret_cast<float4*>(dst);
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-        float a, b, c, e;
-        qup(x[2 * i], a, b);
-        qup(x[2 * i + 1], c, e);
-        d[i] = make_float4(a, b, c, e);
-    }
+__device__ __forceinline__ uint4 out_piece<TQ_F32>(const Q2 (&x)[32], int i) {  // 16 pieces of 4 floats
+    float a, b, c, e;
+    qup(x[2 * i], a, b);
+    qup(x[2 * i + 1], c, e);
+    return make_uint4(__float_as_uint(a), __float_as_uint(b), __float_as_uint(c), __float_as_uint(e));
 }
 template <>
-__device__ __forceinline__ void store_pairs<TQ_F16>(void* dst, const Q2 (&x)[32]) {
-    uint4* d = reinterpret_cast<uint4*>(dst);
+__device__ __forceinline__ uint4 out_piece<TQ_F16>(const Q2 (&x)[32], int i) {  // 8 pieces of 8 halves
+    uint32_t w[4];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        uint32_t w[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            float a, b;
-            qup(x[4 * i + k], a, b);
-            const __half2 h = __floats2half2_rn(a, b);
-            w[k] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int k = 0; k < 4; k++) {
+        float a, b;
+        qup(x[4 * i + k], a, b);
+        const __half2 h = __floats2half2_rn(a, b);
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
     }
+    return make_uint4(w[0], w[1], w[2], w[3]);
 }
 template <>
-__device__ __forceinline__ void store_pairs<TQ_BF16>(void* dst, const Q2 (&x)[32]) {
-    uint4* d = reinterpret_cast<uint4*>(dst);
+__device__ __forceinline__ uint4 out_piece<TQ_BF16>(const Q2 (&x)[32], int i) {
+    uint32_t w[4];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        uint32_t w[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            float a, b;
-            qup(x[4 * i + k], a, b);
-            const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-            w[k] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int k = 0; k < 4; k++) {
+        float a, b;
+        qup(x[4 * i + k], a, b);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
     }
+    return make_uint4(w[0], w[1], w[2], w[3]);
 }
+
+// Output staging of one warp pass: 16 rows in the output type, 16-byte pieces.  Piece j of the half
+// row (row, m) sits at position j ^ ((2 row + m) & 7) of that half row: the eight lanes served
+// together hit eight different bank groups both when the lanes write their own half rows and when
+// they read the pass back in linear order for the global stores.
+template <int DT>
+struct DqStage {
+    static constexpr int kEsz = DT == TQ_F32 ? 4 : 2;
+    static constexpr int kRowBytes = kDqDim * kEsz;
+    static constexpr int kHalfPieces = kRowBytes / 32;     // 16-byte pieces per lane: 8 or 16
+    static constexpr int kRowPieces = 2 * kHalfPieces;
+    static constexpr int kWarpBytes = 16 * kRowBytes;      // 4 KB or 8 KB
+    static constexpr int kTableBytes = 256 * 16 * 8;
+    static constexpr int kSmem = kTableBytes + (kDqThreads / 32) * kWarpBytes;
+};
 
 // What one warp needs of one work item (the K or V half of one page): its rows' codes and norm
 // are fetched one item ahead, so that the loads of the next page are in flight during the
@@ -150,8 +154,11 @@ template <int DT>
 __global__ void __launch_bounds__(kDqThreads) dequant_paged_kernel(const __grid_constant__ DequantParams p) {
     // byte -> {centroid(high nibble), centroid(low nibble)}, 16 columns: an 8-byte load is served
     // half a warp at a time, so the lookups of a warp never conflict
-    __shared__ __align__(16) float2 table_s[256 * 16];
-    __shared__ __align__(16) float sgn_s[kDqDim];
+    extern __shared__ __align__(128) uint8_t dq_smem[];
+    float2* table_s = reinterpret_cast<float2*>(dq_smem);
+    // scale * sign of dims 0..63 and 64..127 in different banks: a half warp reads both halves
+    __shared__ __align__(16) float sgn_s[2][kDqDim / 2 + 2];
+    using St = DqStage<DT>;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     grid_launch_dependents();
@@ -160,10 +167,20 @@ __global__ void __launch_bounds__(kDqThreads) dequant_paged_kernel(const __grid_
         table_s[i] = make_float2(p.cen[v >> 4], p.cen[v & 15]);
     }
     grid_dependency_wait();  // the cache, the page table and the lengths belong to earlier kernels
-    if (tid < kDqDim) sgn_s[tid] = __fmul_rn(p.signs[tid], p.scale);  // exact: the sign is +-1
+    if (tid < kDqDim) sgn_s[tid >> 6][tid & 63] = __fmul_rn(p.signs[tid], p.scale);  // exact: the sign is +-1
     __syncthreads();
 
-    constexpr int kEsz = DT == TQ_F32 ? 4 : 2;
+    constexpr int kEsz = St::kEsz;
+    uint8_t* stage = dq_smem + St::kTableBytes + (size_t)warp * St::kWarpBytes;
+    // Linear read-back of a staged pass: iteration i of lane l takes piece lin_pin of row
+    // lin_row + i * kLinRows, stored at position piece ^ ((2 row + half) & 7) of its half row.
+    constexpr int kLinRows = 32 / St::kRowPieces;            // rows covered by one warp-wide access: 2 or 1
+    constexpr int kLinIters = 16 / kLinRows;
+    const int lin_row = lane / St::kRowPieces, lin_pin = lane % St::kRowPieces;
+    const int lin_half = lin_pin / St::kHalfPieces, lin_pp = lin_pin % St::kHalfPieces;
+    const int lin_key = 2 * lin_row + lin_half;
+    const int lin_base = lin_row * St::kRowBytes + lin_half * (St::kRowBytes / 2);
+    const bool dense = p.out_token_stride == (int64_t)p.H * kDqDim;
     const int m = lane & 1;
     const uint32_t table_lane = smem_u32(table_s) + 8u * (lane & 15);
     const float hsgn = m ? -1.0f : 1.0f;
@@ -225,20 +242,65 @@ __global__ void __launch_bounds__(kDqThreads) dequant_paged_kernel(const __grid_
             const Q2 n2 = qpk(norm, norm);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
-                const float2 sg = *reinterpret_cast<const float2*>(&sgn_s[64 * m + 2 * i]);
+                const float2 sg = *reinterpret_cast<const float2*>(&sgn_s[m][2 * i]);
                 x[i] = qmul(qmul(x[i], qpk(sg.x, sg.y)), n2);
             }
-            if (ok) {
-                const int t = r / p.H, h = r - t * p.H;
-                uint8_t* dst = out_base + (((cur.out_row0 + t) * p.out_token_stride + (int64_t)h * kDqDim) + 64 * m) * kEsz;
-                store_pairs<DT>(dst, x);
+            // stage the 16 rows, then store them in linear order: every store instruction of the warp
+            // covers whole rows (512 contiguous bytes when the heads of a token are contiguous)
+            {
+                uint8_t* half_row = stage + (lane >> 1) * St::kRowBytes + m * (St::kRowBytes / 2);
+                const int key = lane & 7;  // (2 row + m) & 7
+#pragma unroll
+                for (int i = 0; i < St::kHalfPieces; i++)
+                    *reinterpret_cast<uint4*>(half_row + ((i ^ key) << 4)) = out_piece<DT>(x, i);
             }
+            __syncwarp();
+            if (dense) {
+                // heads of a token contiguous: the rows of the page half are one contiguous range
+                uint8_t* dst = out_base + ((cur.out_row0 * p.H + r0 + lin_row) * (int64_t)St::kRowBytes) + lin_pin * 16;
+#pragma unroll
+                for (int i = 0; i < kLinIters; i++) {
+                    const uint4 piece = *reinterpret_cast<const uint4*>(stage + lin_base + i * kLinRows * St::kRowBytes +
+                                                                        ((lin_pp ^ ((lin_key + 2 * i * kLinRows) & 7)) << 4));
+                    if (r0 + lin_row + i * kLinRows < cur.rows)
+                        *reinterpret_cast<uint4*>(dst + (size_t)i * kLinRows * St::kRowBytes) = piece;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < kLinIters; i++) {
+                    const uint4 piece = *reinterpret_cast<const uint4*>(stage + lin_base + i * kLinRows * St::kRowBytes +
+                                                                        ((lin_pp ^ ((lin_key + 2 * i * kLinRows) & 7)) << 4));
+                    const int rr = r0 + lin_row + i * kLinRows;
+                    if (rr < cur.rows) {
+                        int t, h;
+                        if (p.head_shift >= 0) { t = rr >> p.head_shift; h = rr & (p.H - 1); }
+                        else { t = rr / p.H; h = rr - t * p.H; }
+                        uint8_t* dst = out_base + ((cur.out_row0 + t) * p.out_token_stride + (int64_t)h * kDqDim) * kEsz;
+                        *reinterpret_cast<uint4*>(dst + lin_pin * 16) = piece;
+                    }
+                }
+            }
+            __syncwarp();
         }
         cur = nxt;
     }
 }
 
 int device_sm_count(int* out);
+
+template <int DT>
+static int launch_dequant(const DequantParams& p, dim3 grid, cudaStream_t stream) {
+    static bool configured[64] = {};  // per template instance and device
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(dequant_paged_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     DqStage<DT>::kSmem));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    TQ_CUDA(launch_serialized(dequant_paged_kernel<DT>, grid, dim3(kDqThreads), DqStage<DT>::kSmem, stream, p));
+    return TQ_OK;
+}
 void host_codebook(int dim, int bits, float* centroids, float* boundaries);
 
 }  // namespace tq
@@ -273,6 +335,9 @@ extern "C" int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int bl
     p.out_token_stride = out_token_stride;
     p.max_pages = max_pages;
     p.H = num_kv_heads;
+    p.head_shift = -1;
+    for (int sft = 0; sft < 16; sft++)
+        if ((1 << sft) == num_kv_heads) p.head_shift = sft;
     p.block_size = block_size;
     p.slot_bytes = slot_bytes;
     p.out_dtype = out_dtype;
@@ -287,9 +352,8 @@ extern "C" int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int bl
     const dim3 grid((unsigned)(items < 2 * (int64_t)sms ? items : 2 * (int64_t)sms));  // two resident blocks per SM
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (out_dtype) {
-        case TQ_F32: TQ_CUDA(launch_serialized(dequant_paged_kernel<TQ_F32>, grid, dim3(kDqThreads), 0, s, p)); break;
-        case TQ_F16: TQ_CUDA(launch_serialized(dequant_paged_kernel<TQ_F16>, grid, dim3(kDqThreads), 0, s, p)); break;
-        default: TQ_CUDA(launch_serialized(dequant_paged_kernel<TQ_BF16>, grid, dim3(kDqThreads), 0, s, p)); break;
+        case TQ_F32: return launch_dequant<TQ_F32>(p, grid, s);
+        case TQ_F16: return launch_dequant<TQ_F16>(p, grid, s);
+        default: return launch_dequant<TQ_BF16>(p, grid, s);
     }
-    return TQ_OK;
 }
