@@ -211,7 +211,8 @@ __global__ void __launch_bounds__(kDqThreads) dequant_paged_kernel(const __grid_
             Q2 x[32];  // x[i] = dims (64m + 2i, 64m + 2i + 1) = code byte 32m + i
 #pragma unroll
             for (int i = 0; i < 32; i++) {
-                const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+                uint32_t byte;  // byte i & 3 of the word, zero extended, by one byte permute
+                asm("prmt.b32 %0, %1, 0, %2;" : "=r"(byte) : "r"(w[i >> 2]), "r"(0x4440u | (uint32_t)(i & 3)));
                 float hi, lo;
                 asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(hi), "=f"(lo) : "r"(byte * 128u + table_lane));
                 // stage h = 1 inside the pair
