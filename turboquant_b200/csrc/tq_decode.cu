@@ -316,9 +316,11 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         grid_dependency_wait();  // seq_lens, the page table, Q and the workspace belong to earlier kernels
         // pass 1: total pages
         int total = 0;
+        int np_first = 0;  // this lane's sequence of the first 32: kept for pass 2 (one global round trip less)
         for (int base = 0; base < p.batch; base += 32) {
             int np = 0, fp, le;
             if (base + lane < p.batch) seq_pages(p, base + lane, fp, np, le);
+            if (base == 0) np_first = np;
             for (int o = 16; o > 0; o >>= 1) np += __shfl_xor_sync(0xffffffffu, np, o);
             total += np;
         }
@@ -332,7 +334,8 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         for (int base = 0; base < p.batch; base += 32) {
             int np = 0, fp = 0, le;
             const int b = base + lane;
-            if (b < p.batch) seq_pages(p, b, fp, np, le);
+            if (base == 0) np = np_first;
+            else if (b < p.batch) seq_pages(p, b, fp, np, le);
             int incl = np;
             for (int o = 1; o < 32; o <<= 1) {
                 const int t = __shfl_up_sync(0xffffffffu, incl, o);
