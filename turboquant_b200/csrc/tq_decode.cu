@@ -61,6 +61,11 @@ constexpr int kMaxExchangeRanks = 16;
 constexpr int kExchangeSpinLimit = 1 << 22;  // x 256 ns sleeps: a second or so, then status 1
 constexpr int kMaxSegments = 96;
 constexpr int kMinPagesPerCta = 4;
+// Starting a sequence inside a block (rotate its queries, later write its partial) costs about as
+// much as three stages of streaming.  The page list is therefore split in a virtual space where
+// every non-empty sequence is preceded by kSegCostStages x pages-per-stage virtual pages: a block
+// that takes on an additional sequence gets correspondingly fewer real pages.
+constexpr int kSegCostStages = 3;
 constexpr float kRaiseThreshold = 6.0f;  // log2 units
 
 struct DecodeParams {
@@ -315,12 +320,14 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     } else {
         grid_dependency_wait();  // seq_lens, the page table, Q and the workspace belong to earlier kernels
         // pass 1: total pages
+        constexpr int kSegCost = kSegCostStages * PPS;
         int total = 0;
         int np_first = 0;  // this lane's sequence of the first 32: kept for pass 2 (one global round trip less)
         for (int base = 0; base < p.batch; base += 32) {
             int np = 0, fp, le;
             if (base + lane < p.batch) seq_pages(p, base + lane, fp, np, le);
             if (base == 0) np_first = np;
+            np = np > 0 ? np + kSegCost : 0;  // virtual pages
             for (int o = 16; o > 0; o >>= 1) np += __shfl_xor_sync(0xffffffffu, np, o);
             total += np;
         }
@@ -336,13 +343,15 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             const int b = base + lane;
             if (base == 0) np = np_first;
             else if (b < p.batch) seq_pages(p, b, fp, np, le);
-            int incl = np;
+            const int vnp = np > 0 ? np + kSegCost : 0;
+            int incl = vnp;
             for (int o = 1; o < 32; o <<= 1) {
                 const int t = __shfl_up_sync(0xffffffffu, incl, o);
                 if (lane >= o) incl += t;
             }
-            const int start = run + incl - np, end = run + incl;
-            if (c == 0 && b < p.batch) p.page_prefix[b] = start;
+            // virtual span of the sequence [vstart, end); its real pages are [start, end)
+            const int vstart = run + incl - vnp, end = run + incl, start = vstart + kSegCost;
+            if (c == 0 && b < p.batch) p.page_prefix[b] = vstart;
             const bool hit = b < p.batch && np > 0 && start < hi && end > lo;
             const uint32_t mask = __ballot_sync(0xffffffffu, hit);
             if (hit) {
@@ -677,6 +686,7 @@ struct MergeParams {
     float* out_lse;   // natural-log LSE (final) or base-2 LSE (rotated output), optional
     int64_t rows;     // batch (decode merge) or rows (generic merge)
     int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
+    int seg_cost;  // virtual pages in front of every non-empty sequence in the decode kernel's split
     int nq, real_heads, real_group;  // virtual head -> (query, real head) of the output row; nq = 1: identity
     // Exchange of rotated partials between the GPUs that split one KV axis (xmode != 0):
     // every rank owns an exchange buffer (ExchangeLayout) that all ranks have mapped.
@@ -762,7 +772,9 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     if (p.header) {
         // partials of sequence `row` come from the blocks whose page range meets its pages
         const int64_t n = p.header[1], total = p.header[2];
-        const int64_t s = p.page_prefix[row], e = p.page_prefix[row + 1];
+        // virtual span [page_prefix[row], page_prefix[row + 1]); real pages start seg_cost further
+        const int64_t e = p.page_prefix[row + 1];
+        const int64_t s = p.page_prefix[row] + p.seg_cost;
         if (e > s && total > 0) {
             const int64_t c_first = ((s + 1) * n + total - 1) / total - 1;
             const int64_t c_last = (e * n + total - 1) / total - 1;
@@ -1040,6 +1052,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     m.real_heads = real_q_heads;
     m.real_group = real_q_heads / num_kv_heads;
     m.pps = kConsumerWarps / num_kv_heads;
+    m.seg_cost = kSegCostStages * m.pps;
     m.grid_ctas = ctas;
     m.out_dtype = out_dtype;
     m.emit_rotated = emit_rotated;
