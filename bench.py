@@ -57,7 +57,7 @@ def parse():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="config4 on several GPUs: partials exchanged by the kernels themselves (peer stores + "
                          "flags) or by an NCCL all-gather")
-    ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4"],
+    ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4", "sweep"],
                     help="config1 (default, the headline): batch 8 x 32k per GPU; config3: 64 mixed lengths sharded by "
                          "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge")
     return ap.parse_args()
@@ -659,6 +659,65 @@ def run_config4(args):
 
 
 
+def run_sweep(args):
+    """The shapes of the reference's published kernel tables (batch 1, ctx 256 ... 32768; batch
+    1/4/16/32 at ctx 4096/16384/32768; measured by its authors on an A100, CUDA-graph replays of the
+    decode op): one decode call (decode + merge kernels) per graph replay, p50 over 100 replays, four
+    caches rotated.  Context only: other hardware, so no ratio is formed."""
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    rank, world, dev = _setup_dist()
+    attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, num_ctas=args.num_ctas)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    shapes = [(1, c) for c in (256, 512, 1024, 2048, 4096, 8192, 16384, 32768)]
+    shapes += [(b, c) for c in (4096, 16384, 32768) for b in (4, 16, 32)]
+    rows = []
+    for B, L in shapes:
+        pages = (L + PAGE - 1) // PAGE
+        nb = B * pages
+        ncache = 4 if B * L <= 16 * 32768 else 2
+        bt = torch.randperm(nb, generator=torch.Generator().manual_seed(B * 131 + L)).view(B, pages).to(torch.int32).to(dev)
+        caches = [torch.zeros(kv_cache_shape(nb, PAGE, HKV, D), dtype=torch.uint8, device=dev) for _ in range(ncache)]
+        for c in caches:
+            for b in range(B):
+                _fill_cache(attn, c, bt[b], L, gen, dev)
+        sl = torch.full((B,), L, dtype=torch.int32, device=dev)
+        q = torch.randn(B, HQ, D, generator=gen, device=dev).to(torch.float16)
+        out = torch.empty_like(q)
+        for c in caches:
+            attn.decode(q, c, bt, sl, out)
+        torch.cuda.synchronize()
+        graphs = []
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for c in caches:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    attn.decode(q, c, bt, sl, out)
+                graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        ts = []
+        for i in range(104):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graphs[i % ncache].replay()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 4:
+                ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.sort()
+        rows.append({"batch": B, "ctx": L, "p50_us": round(ts[len(ts) // 2], 2),
+                     "GBps": round(B * L * HKV * ALG_BYTES_PER_TOKEN_HEAD / ts[len(ts) // 2] / 1e3, 1)})
+        del caches
+    if rank == 0:
+        print(json.dumps({"metric": "decode_call_latency_us", "unit": "us", "n_gpus": 1, "higher_is_better": False,
+                          "vs_baseline": None, "data": "synthetic",
+                          "config": {"workload": "sweep: 32 q / 8 kv heads, head_dim 128, fp16 q, one decode call per CUDA-graph "
+                                                 "replay (decode + merge), p50 of 100"},
+                          "rows": rows}), flush=True)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -667,6 +726,8 @@ def main():
         run_config3(args)
     elif args.workload == "config4":
         run_config4(args)
+    elif args.workload == "sweep":
+        run_sweep(args)
     else:
         run_ours(args)
 

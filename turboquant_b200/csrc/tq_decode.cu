@@ -66,6 +66,7 @@ constexpr int kMinPagesPerCta = 4;
 // every non-empty sequence is preceded by kSegCostStages x pages-per-stage virtual pages: a block
 // that takes on an additional sequence gets correspondingly fewer real pages.
 constexpr int kSegCostStages = 3;
+constexpr int kSegCostMinStages = 16;  // ... and only when a block streams at least this many stages
 constexpr float kRaiseThreshold = 6.0f;  // log2 units
 
 struct DecodeParams {
@@ -75,7 +76,7 @@ struct DecodeParams {
     const int32_t* page_indptr;  // may be null: dense block table with row stride max_pages
     const int32_t* seq_lens;
     const float* signs;
-    int32_t* header;        // workspace: [0] status, [1] effective block count, [2] total pages
+    int32_t* header;        // workspace: [0] status, [1] effective block count, [2] total (virtual) pages, [3] pages charged per sequence start
     int32_t* page_prefix;   // workspace: [batch + 1]
     float* partial_lse;     // workspace: [slots][num_q_heads]
     float* partial_o;       // workspace: [slots][num_q_heads][128]
@@ -319,20 +320,22 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         grid_dependency_wait();
     } else {
         grid_dependency_wait();  // seq_lens, the page table, Q and the workspace belong to earlier kernels
-        // pass 1: total pages
-        constexpr int kSegCost = kSegCostStages * PPS;
-        int total = 0;
+        // pass 1: total pages and the number of non-empty sequences
+        int total_real = 0, nonempty = 0;
         int np_first = 0;  // this lane's sequence of the first 32: kept for pass 2 (one global round trip less)
         for (int base = 0; base < p.batch; base += 32) {
             int np = 0, fp, le;
             if (base + lane < p.batch) seq_pages(p, base + lane, fp, np, le);
             if (base == 0) np_first = np;
-            np = np > 0 ? np + kSegCost : 0;  // virtual pages
+            nonempty += __popc(__ballot_sync(0xffffffffu, np > 0));
             for (int o = 16; o > 0; o >>= 1) np += __shfl_xor_sync(0xffffffffu, np, o);
-            total += np;
+            total_real += np;
         }
-        int n_eff = (total + kMinPagesPerCta * PPS - 1) / (kMinPagesPerCta * PPS);
+        int n_eff = (total_real + kMinPagesPerCta * PPS - 1) / (kMinPagesPerCta * PPS);
         n_eff = n_eff < 1 ? 1 : (n_eff > (int)gridDim.x ? (int)gridDim.x : n_eff);
+        // the charge for a sequence start only makes sense against blocks that stream for a while
+        const int kSegCost = total_real / n_eff >= kSegCostMinStages * PPS ? kSegCostStages * PPS : 0;
+        const int total = total_real + nonempty * kSegCost;  // virtual pages
         const int c = blockIdx.x;
         const int64_t lo = c < n_eff ? ((int64_t)c * total) / n_eff : 0;
         const int64_t hi = c < n_eff ? ((int64_t)(c + 1) * total) / n_eff : 0;
@@ -370,6 +373,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 p.page_prefix[p.batch] = run;
                 p.header[1] = n_eff;
                 p.header[2] = total;
+                p.header[3] = kSegCost;
             }
             if (nseg > kMaxSegments) {  // more sequences per block than the list holds
                 atomicExch(&p.header[0], 2);
@@ -686,7 +690,6 @@ struct MergeParams {
     float* out_lse;   // natural-log LSE (final) or base-2 LSE (rotated output), optional
     int64_t rows;     // batch (decode merge) or rows (generic merge)
     int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
-    int seg_cost;  // virtual pages in front of every non-empty sequence in the decode kernel's split
     int nq, real_heads, real_group;  // virtual head -> (query, real head) of the output row; nq = 1: identity
     // Exchange of rotated partials between the GPUs that split one KV axis (xmode != 0):
     // every rank owns an exchange buffer (ExchangeLayout) that all ranks have mapped.
@@ -774,7 +777,7 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
         const int64_t n = p.header[1], total = p.header[2];
         // virtual span [page_prefix[row], page_prefix[row + 1]); real pages start seg_cost further
         const int64_t e = p.page_prefix[row + 1];
-        const int64_t s = p.page_prefix[row] + p.seg_cost;
+        const int64_t s = p.page_prefix[row] + p.header[3];
         if (e > s && total > 0) {
             const int64_t c_first = ((s + 1) * n + total - 1) / total - 1;
             const int64_t c_last = (e * n + total - 1) / total - 1;
@@ -1052,7 +1055,6 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     m.real_heads = real_q_heads;
     m.real_group = real_q_heads / num_kv_heads;
     m.pps = kConsumerWarps / num_kv_heads;
-    m.seg_cost = kSegCostStages * m.pps;
     m.grid_ctas = ctas;
     m.out_dtype = out_dtype;
     m.emit_rotated = emit_rotated;
