@@ -722,16 +722,20 @@ __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// One block per (row, query head), four warps.  Warp w takes parts w, w+4, ...; lane l owns
+// One block per (row, query head), kMergeWarps warps (4, or 16 when one sequence is spread over
+// many blocks of the decode grid).  Warp w takes parts w, w + kMergeWarps, ...; lane l owns
 // rotated dims 4l..4l+3.  A warp first fetches the LSEs of its parts (lane i: its i-th part),
 // forms the weights, then fetches all its payloads with the loads in flight together: the
-// kernel is a handful of L2 round trips long, whatever the number of parts (up to 128 per
-// warp pass).  The four warps' results are combined in shared memory, then the inverse
-// rotation (FWHT, 1/sqrt(128), signs) runs across the 128 threads.
-__global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__ MergeParams p) {
+// kernel is a handful of L2 round trips long up to 32 parts per warp (one sequence spread over
+// every block of the decode grid: 296 parts).  The warps' results are combined in shared memory, then
+// the first four warps run the inverse rotation (FWHT, 1/sqrt(128), signs), one thread per dim.
+__device__ __forceinline__ void sync_first_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int kMergeWarps>
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_constant__ MergeParams p) {
     __shared__ float buf[kHeadDim];
-    __shared__ float part_acc[4][kHeadDim];
-    __shared__ float part_m[4], part_w[4];
+    __shared__ float part_acc[kMergeWarps][kHeadDim];
+    __shared__ float part_m[kMergeWarps], part_w[kMergeWarps];
     const int d = threadIdx.x, warp = d >> 5, lane = d & 31;
     const int64_t row = blockIdx.x;
     const int hq = blockIdx.y;
@@ -796,9 +800,10 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     const int64_t o_stride = lse_stride * (kHeadDim / 4);
     float m = -INFINITY, wsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int i0 = warp; i0 < count; i0 += 128) {          // this warp's parts i0, i0+4, ..., 32 per pass
-        const int n = (count - i0 + 3) / 4 < 32 ? (count - i0 + 3) / 4 : 32;
-        const float my_lse = lane < n ? lse_base[(int64_t)(i0 + 4 * lane) * lse_stride] : -INFINITY;
+    for (int i0 = warp; i0 < count; i0 += kMergeWarps * 32) {  // this warp's parts i0, i0+16, ..., 32 per pass
+        const int left = (count - i0 + kMergeWarps - 1) / kMergeWarps;
+        const int n = left < 32 ? left : 32;
+        const float my_lse = lane < n ? lse_base[(int64_t)(i0 + kMergeWarps * lane) * lse_stride] : -INFINITY;
         float mx = my_lse;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -816,7 +821,7 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
             float4 o[8];
 #pragma unroll
             for (int j = 0; j < 8; j++)
-                o[j] = j0 + j < n ? o_base[(int64_t)(i0 + 4 * (j0 + j)) * o_stride] : make_float4(0.f, 0.f, 0.f, 0.f);
+                o[j] = j0 + j < n ? o_base[(int64_t)(i0 + kMergeWarps * (j0 + j)) * o_stride] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const float w = __shfl_sync(0xffffffffu, my_w, (j0 + j) & 31);
@@ -829,11 +834,14 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     reinterpret_cast<float4*>(part_acc[warp])[lane] = acc;
     if (lane == 0) { part_m[warp] = m; part_w[warp] = wsum; }
     __syncthreads();
-    float mm = fmaxf(fmaxf(part_m[0], part_m[1]), fmaxf(part_m[2], part_m[3]));
+    if (d >= kHeadDim) return;  // the rest runs on one thread per dim; its barriers count 128 threads
+    float mm = part_m[0];
+#pragma unroll
+    for (int w = 1; w < kMergeWarps; w++) mm = fmaxf(mm, part_m[w]);
     float o = 0.f, wtot = 0.f;
     if (mm > -INFINITY) {
 #pragma unroll
-        for (int w = 0; w < 4; w++) {
+        for (int w = 0; w < kMergeWarps; w++) {
             const float sc = exp2f(part_m[w] - mm);
             if (sc > 0.f) { o += sc * part_acc[w][d]; wtot += sc * part_w[w]; }
         }
@@ -857,7 +865,7 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
             if (d == 0) reinterpret_cast<float*>(p.xbuf[w] + xl.lse)[at] = lse2;
         }
         __threadfence_system();
-        __syncthreads();
+        sync_first_128();
         if (d == 0) {
             const int blocks = gridDim.x * gridDim.y;
             if (atomicAdd(xctrl + 2, 1) == blocks - 1) {
@@ -876,12 +884,12 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     }
     // inverse rotation: FWHT, 1/sqrt(128), signs
     buf[d] = o;
-    __syncthreads();
+    sync_first_128();
     for (int h = 1; h < kHeadDim; h <<= 1) {
         const float a = buf[d & ~h], b2 = buf[d | h];
-        __syncthreads();
+        sync_first_128();
         buf[d] = (d & h) ? a - b2 : a + b2;
-        __syncthreads();
+        sync_first_128();
     }
     o = buf[d] * 0.08838834764831845f * p.signs[d];
     if (p.out_dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[orow * kHeadDim + d] = __float2bfloat16_rn(o);
@@ -889,7 +897,7 @@ __global__ void __launch_bounds__(kHeadDim) merge_kernel(const __grid_constant__
     else reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
     if (p.out_lse && d == 0) p.out_lse[orow] = lse2 * 0.6931471805599453f;
     if (p.xmode == 2) {  // the last block to finish closes the step
-        __syncthreads();
+        sync_first_128();
         if (d == 0) {
             const int blocks = gridDim.x * gridDim.y;
             __threadfence();
@@ -1065,7 +1073,11 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
         m.xrows = (int64_t)batch * num_q_heads;
         for (int w = 0; w < x->world; w++) m.xbuf[w] = static_cast<unsigned char*>(x->bufs[w]);
     }
-    TQ_CUDA(launch_serialized(merge_kernel, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(kHeadDim), 0, s, m));
+    // parts per sequence: about (blocks x page lanes) / batch; many of them -> the wide merge
+    if ((int64_t)ctas * m.pps > (int64_t)64 * batch)
+        TQ_CUDA(launch_serialized(merge_kernel<16>, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(512), 0, s, m));
+    else
+        TQ_CUDA(launch_serialized(merge_kernel<4>, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(128), 0, s, m));
     if (x) {
         // second pass: wait for every rank's partial in this rank's buffer, merge, rotate back
         MergeParams f = m;
@@ -1077,7 +1089,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
         f.nq = 1;
         f.num_parts = x->world;
         f.emit_rotated = 0;
-        TQ_CUDA(launch_serialized(merge_kernel, dim3((unsigned)m.xrows, 1), dim3(kHeadDim), 0, s, f));
+        TQ_CUDA(launch_serialized(merge_kernel<4>, dim3((unsigned)m.xrows, 1), dim3(128), 0, s, f));
     }
     if (g_events[2]) TQ_CUDA(cudaEventRecord(g_events[2], s));
     return TQ_OK;
@@ -1187,7 +1199,10 @@ extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse
     m.nq = 1;
     m.num_parts = num_parts;
     m.out_dtype = out_dtype;
-    TQ_CUDA(launch_serialized(merge_kernel, dim3((unsigned)rows, 1), dim3(kHeadDim), 0, static_cast<cudaStream_t>(stream), m));
+    if (num_parts > 64)
+        TQ_CUDA(launch_serialized(merge_kernel<16>, dim3((unsigned)rows, 1), dim3(512), 0, static_cast<cudaStream_t>(stream), m));
+    else
+        TQ_CUDA(launch_serialized(merge_kernel<4>, dim3((unsigned)rows, 1), dim3(128), 0, static_cast<cudaStream_t>(stream), m));
     return TQ_OK;
 }
 
