@@ -198,7 +198,7 @@ __device__ __forceinline__ void seq_pages(const DecodeParams& p, int b, int& fir
 
 // Shared-memory stage layout.  A stage holds kPPS pages; page lane `pp` has a K region and a V
 // region.  Each page half is copied as runs of kRunTokens consecutive token rows, one bulk copy
-// per run: 2560 bytes for 8, 4 and 2 KV heads, 1280 for one (copies of a few hundred bytes were
+// per run: 2560 bytes for 16, 8, 4 and 2 KV heads, 1280 for one (copies of a few hundred bytes were
 // found to be limited by the copy engine's request rate, 2.5 KB and larger are not).  A run is
 // dense, so the bank of a row is fixed by the row size (640, 320, 160, 80 bytes = 0, 64, 32, 80
 // mod 128); the runs' base offsets and the map from MMA row r to token row_token(r) are chosen per
@@ -211,25 +211,26 @@ template <int HKV>
 struct DecodeSmem {
     static constexpr int kPPS = kConsumerWarps / HKV;  // pages per stage
     static constexpr int kRowBytes = HKV * kSlotBytes;
-    static constexpr int kRunTokens = HKV == 8 ? 4 : HKV == 4 ? 8 : 16;
+    static constexpr int kRunTokens = HKV == 16 ? 2 : HKV == 8 ? 4 : HKV == 4 ? 8 : 16;
     static constexpr int kRunsPerHalf = kPageTokens / kRunTokens;
     static constexpr int kCopyBytes = kRunTokens * kRowBytes;
     static constexpr int kCopiesPerPage = 2 * kRunsPerHalf;
     static constexpr int kCopiesPerStage = kPPS * kCopiesPerPage;  // 16, 16, 16, 32: one lane each
-    static constexpr int kKRegion = HKV == 8 ? 10496 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;  // per page lane
-    static constexpr int kVRegion = HKV == 8 ? 10368 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;
+    static constexpr int kKRegion = HKV == 16 ? 20736 : HKV == 8 ? 10496 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;  // per page lane
+    static constexpr int kVRegion = HKV == 16 ? 20736 : HKV == 8 ? 10368 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;
     static constexpr int kKBytes = kPPS * kKRegion;
     static constexpr int kVBytes = kPPS * kVRegion;
     static constexpr int kStageBytes = kKBytes + kVBytes;
 
     // run q of a page half -> byte offset of its first row inside the page lane's region
     static __host__ __device__ __forceinline__ constexpr int k_run(int q) {
-        return HKV == 8 ? q * 2560 + ((q & 1) ? 64 : 0) + ((q & 2) ? 144 : 0)  // 0, 2624, 5264, 7888
+        return HKV == 16  ? q * 2560 + 32 * (q & 3) + 128 * (q >> 2)                               // eight runs, 32 bytes apart mod 128
+               : HKV == 8 ? q * 2560 + ((q & 1) ? 64 : 0) + ((q & 2) ? 144 : 0)  // 0, 2624, 5264, 7888
                : HKV == 4 ? q * 2576                                             // 0, 2576
                           : 0;
     }
     static __host__ __device__ __forceinline__ constexpr int v_run(int q) {
-        return HKV == 8 ? q * 2592 : HKV == 4 ? q * 2592 : 0;
+        return HKV == 16 ? q * 2560 + 32 * (q & 3) + 128 * (q >> 2) : HKV == 8 ? q * 2592 : HKV == 4 ? q * 2592 : 0;
     }
     // token (0..15 within its page) -> byte offset of its row inside the page lane's region
     static __host__ __device__ __forceinline__ constexpr int k_off(int t) {
@@ -241,10 +242,17 @@ struct DecodeSmem {
     // MMA row / contraction slot r (0..15) -> token within the page
     static __host__ __device__ __forceinline__ constexpr int row_token(int r) {
         const int r7 = r & 7, up = r >> 3;
-        return HKV == 8   ? 4 * ((0x23013210 >> (4 * r7)) & 3) + (r7 >> 2) + 2 * up   // runs 0,1,2,3,1,0,3,2
+        return HKV == 16  ? 2 * ((0x13467520u >> (4 * r7)) & 7) + up                   // runs 0,2,5,7,6,4,3,1
+               : HKV == 8 ? 4 * ((0x23013210 >> (4 * r7)) & 3) + (r7 >> 2) + 2 * up   // runs 0,1,2,3,1,0,3,2
                : HKV == 4 ? ((0xAB239810u >> (4 * r7)) & 15) + 4 * up                 // 0,1,8,9,3,2,11,10
                : HKV == 2 ? ((0x53427160u >> (4 * r7)) & 7) + 8 * up                  // 0,6,1,7,2,4,3,5
                           : r;
+    }
+    // the runs of a region neither overlap nor leave it
+    static constexpr bool runs_fit() {
+        for (int q = 0; q + 1 < kRunsPerHalf; q++)
+            if (k_run(q) + kCopyBytes > k_run(q + 1) || v_run(q) + kCopyBytes > v_run(q + 1)) return false;
+        return k_run(kRunsPerHalf - 1) + kCopyBytes <= kKRegion && v_run(kRunsPerHalf - 1) + kCopyBytes <= kVRegion;
     }
     // MMA rows r and r+8 sit a fixed distance apart in both regions (runs: two tokens further in
     // the same run; pitched rows: eight rows further)
@@ -266,6 +274,7 @@ template <int HKV>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_paged_kernel(const __grid_constant__ DecodeParams p) {
     using S = DecodeSmem<HKV>;
+    static_assert(S::runs_fit(), "stage layout: runs overlap or leave their region");
     constexpr int PPS = S::kPPS;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kStages];
@@ -986,8 +995,8 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     TQ_REQUIRE(head_dim == kHeadDim, TQ_ERR_UNSUPPORTED, "decode supports head_dim 128, got %d", head_dim);
     TQ_REQUIRE(block_size == kPageTokens, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
     TQ_REQUIRE(slot_bytes == kSlotBytes, TQ_ERR_UNSUPPORTED, "decode supports 80-byte slots, got %d", slot_bytes);
-    TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8,
-               TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4 or 8, got %d", num_kv_heads);
+    TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8 || num_kv_heads == 16,
+               TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4, 8 or 16, got %d", num_kv_heads);
     TQ_REQUIRE(nq >= 1 && real_q_heads >= 1 && real_q_heads % num_kv_heads == 0, TQ_ERR_INVALID,
                "query heads must be a positive multiple of the KV heads, queries_per_seq >= 1");
     TQ_REQUIRE(nq * (real_q_heads / num_kv_heads) <= 8, TQ_ERR_UNSUPPORTED,
@@ -1041,6 +1050,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     // zeroed the first bytes of the workspace once.
     if (g_events[0]) TQ_CUDA(cudaEventRecord(g_events[0], s));
     switch (num_kv_heads) {
+        case 16: rc = launch_decode<16>(p, ctas, s); break;
         case 8: rc = launch_decode<8>(p, ctas, s); break;
         case 4: rc = launch_decode<4>(p, ctas, s); break;
         case 2: rc = launch_decode<2>(p, ctas, s); break;
@@ -1248,8 +1258,8 @@ extern "C" int tq_decode_paged_static(const void* q, int q_dtype, int batch, int
     using namespace tq;
     TQ_REQUIRE(batch >= 0, TQ_ERR_INVALID, "negative batch");
     if (batch == 0) return TQ_OK;
-    TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8,
-               TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4 or 8, got %d", num_kv_heads);
+    TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8 || num_kv_heads == 16,
+               TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4, 8 or 16, got %d", num_kv_heads);
     TQ_REQUIRE(num_q_heads > 0, TQ_ERR_INVALID, "num_q_heads must be positive");
     int ctas = 0;
     int rc = resolve_ctas(num_ctas, &ctas);

@@ -57,13 +57,13 @@ def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> Kernel
     h, g = model.num_kv_heads, model.gqa_ratio
     if model.head_dim != 128:
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"head_dim {model.head_dim}: only 128 is implemented")
-    if h not in (1, 2, 4, 8):
-        return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"{h} KV heads per GPU: shard to 1, 2, 4 or 8")
+    if h not in (1, 2, 4, 8, 16):
+        return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"{h} KV heads per GPU: shard to 1, 2, 4, 8 or 16")
     if not 1 <= g <= 8:
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"GQA ratio {g}: 1..8 is implemented")
     pps = CONSUMER_WARPS // h
     # per page lane: K region + V region (runs of token rows, placed for conflict-free fragment loads)
-    stage = pps * {8: 10496 + 10368, 4: 5248 + 5248, 2: 2560 + 2560, 1: 1280 + 1280}[h]
+    stage = pps * {16: 20736 + 20736, 8: 10496 + 10368, 4: 5248 + 5248, 2: 2560 + 2560, 1: 1280 + 1280}[h]
     # lookup table (256 B per entry, per-warp scratch in the unused halves) at the 64 KB boundary of
     # the shared window; three stages: one below the table and two above it
     return KernelConfig(CONSUMER_WARPS, pps, 3, stage)
