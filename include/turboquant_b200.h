@@ -62,6 +62,8 @@ int tq_codebook(int dim, int bits, float* centroids, float* boundaries);
  * untouched.  key/value: [num_tokens][num_kv_heads][head_dim] of in_dtype with
  * k_token_stride / v_token_stride elements between tokens (heads contiguous).  One launch
  * covers K and V.  Codes and norms are bit-identical to TurboQuantMSE.quantize on the CPU.
+ * head_dim 128, or 96 (rows of 96 elements, zero-padded to 128 by the rotation; signs has 128
+ * entries either way).
  * Replaces: torch.ops.turboquant_write.quantize_write_kv_cache
  *   (csrc/src/quantize_write_binding.cu:207-269, kernel csrc/include/turboquant/quantize_write_kernel.cuh:332-431),
  *   called from TurboQuantFusedImpl._write_to_cache (turboquant/vllm_backend_fused.py:293-305). */
@@ -109,8 +111,9 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *                no call clears it and nothing else in the workspace needs initialising
  *   num_ctas     thread blocks to balance over; 0 = one per SM of the current device
  *
- * Supported geometry: head_dim 128, block_size 16, slot_bytes 80, num_q_heads/num_kv_heads <= 8,
- * num_kv_heads in {1, 2, 4, 8}.
+ * Supported geometry: head_dim 128, or 96 (q and out rows of 96 elements; the rotation pads them
+ * with zeros to 128 and the slot is the same 80 bytes); block_size 16, slot_bytes 80,
+ * num_q_heads/num_kv_heads <= 8, num_kv_heads in {1, 2, 4, 8, 16}.
  * Replaces: torch.ops.turboquant_v5.decode_v5_from_cache_paged_splitkv_ws and
  *   decode_v5_from_cache_ws (csrc/src/decode_v5_tc_binding.cu:754-874, 440-551), kernels
  *   csrc/include/flashinfer_decode_turboquant_v5_tc.cuh:112-795 and
@@ -201,7 +204,7 @@ int tq_decode_paged_exchange(const void* q, int q_dtype, int batch, int queries_
                              float* out_lse, int num_ctas, void* stream);
 
 /* As tq_decode_paged, but stops before the inverse rotation: writes the merged, normalized,
- * still-rotated output (fp32 [batch][num_q_heads][head_dim]) and its base-2 LSE, restricted to
+ * still-rotated output (fp32 [batch][num_q_heads][128], the padded width) and its base-2 LSE, restricted to
  * tokens [kv_begin, kv_end) of every sequence (kv_end < 0: to the end).  This is the per-GPU
  * half of a KV-axis split across GPUs; the halves are exchanged and finished with
  * tq_merge_rotated.  No reference counterpart (the reference has no multi-GPU path); it
@@ -216,9 +219,9 @@ int tq_decode_paged_partial(const void* q, int q_dtype, int batch, int num_q_hea
                             void* stream);
 
 /* Log-sum-exp merge of num_parts rotated partial outputs, then inverse rotation:
- *   partial_o    fp32 [num_parts][rows][head_dim]   (normalized, rotated domain)
+ *   partial_o    fp32 [num_parts][rows][128]        (normalized, rotated domain: always 128 wide)
  *   partial_lse2 fp32 [num_parts][rows]             (base-2 LSE; -inf marks an empty part)
- *   out          [rows][head_dim] out_dtype; out_lse optional natural-log LSE [rows]
+ *   out          [rows][head_dim] out_dtype (head_dim 128 or 96); out_lse optional natural-log LSE [rows]
  * Replaces: SplitKVCombineKernel (csrc/include/flashinfer_decode_turboquant_combine.cuh:18-79)
  * plus the inverse rotation at flashinfer_decode_turboquant_v5_tc.cuh:709-765. */
 int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_parts,

@@ -108,7 +108,7 @@ def write_kv_cache(kv_cache: torch.Tensor, key: torch.Tensor, value: torch.Tenso
             raise TurboQuantError(f"{n} must be [>=num_tokens, {H}, {head_dim}], got {tuple(t.shape)}")
         if t.stride(2) != 1 or t.stride(1) != head_dim:
             raise TurboQuantError(f"{n}: heads of one token must be contiguous")
-    if signs.dtype != torch.float32 or signs.numel() < head_dim or not signs.is_contiguous():
+    if signs.dtype != torch.float32 or signs.numel() < 128 or not signs.is_contiguous():
         raise TurboQuantError("signs must be contiguous fp32 of padded head size")
     if slot_mapping.dtype not in (torch.int32, torch.int64) or not slot_mapping.is_contiguous():
         raise TurboQuantError("slot_mapping must be contiguous int32 or int64")
@@ -365,7 +365,7 @@ def merge_rotated(partial_o, partial_lse2, signs, out, out_lse=None):
     rows = partial_lse2.numel() // parts
     _check(lib().tq_merge_rotated(
         _ptr(partial_o.contiguous()), _ptr(partial_lse2.contiguous()), ctypes.c_int(parts),
-        ctypes.c_int64(rows), ctypes.c_int(partial_o.shape[-1]), _ptr(signs), _ptr(out),
+        ctypes.c_int64(rows), ctypes.c_int(out.shape[-1]), _ptr(signs), _ptr(out),
         ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), _stream(partial_o)))
     return out
 

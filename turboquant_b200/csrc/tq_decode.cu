@@ -88,6 +88,7 @@ struct DecodeParams {
     // head c % real_group.  real_heads / real_group / nq give the layout of q and out.
     int batch, num_q_heads, group, max_pages, q_dtype;
     int nq, real_heads, real_group;
+    int head_dim;  // elements per q / out row: 128, or 96 (the rotation pads it with zeros to 128)
     float k_scale;  // (1/sqrt(128)) * sm_scale * log2(e): multiplies raw code-domain scores
     float v_scale;  // 1/sqrt(128): centroid scale folded into P
     uint16_t centroid_h[16];  // fp16 bit patterns of the N(0,1) centroids
@@ -486,9 +487,11 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             for (int rr = 0; rr < 4; rr++) {
                 const int r = r0 + rr < p.group ? r0 + rr : p.group - 1;
                 const int qi = r / p.real_group, hh = r - qi * p.real_group;
-                const int64_t base = ((((int64_t)b * p.nq + qi) * p.real_heads) + head * p.real_group + hh) * kHeadDim +
+                const int64_t base = ((((int64_t)b * p.nq + qi) * p.real_heads) + head * p.real_group + hh) * p.head_dim +
                                      4 * lane;
-                if (p.q_dtype == TQ_BF16) {
+                if (4 * lane >= p.head_dim) {  // padding of a short head
+                    v[rr][0] = v[rr][1] = v[rr][2] = v[rr][3] = 0.f;
+                } else if (p.q_dtype == TQ_BF16) {
                     const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + base);
                     v[rr][0] = __uint_as_float(t.x << 16); v[rr][1] = __uint_as_float(t.x & 0xffff0000u);
                     v[rr][2] = __uint_as_float(t.y << 16); v[rr][3] = __uint_as_float(t.y & 0xffff0000u);
@@ -700,6 +703,7 @@ struct MergeParams {
     int64_t rows;     // batch (decode merge) or rows (generic merge)
     int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
     int nq, real_heads, real_group;  // virtual head -> (query, real head) of the output row; nq = 1: identity
+    int head_dim;                    // elements per output row (128, or 96: the padded dims are dropped)
     // Exchange of rotated partials between the GPUs that split one KV axis (xmode != 0):
     // every rank owns an exchange buffer (ExchangeLayout) that all ranks have mapped.
     int xmode;                       // 0 none, 1 push this rank's partial to all ranks, 2 wait for all ranks and merge
@@ -901,9 +905,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
         sync_first_128();
     }
     o = buf[d] * 0.08838834764831845f * p.signs[d];
-    if (p.out_dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[orow * kHeadDim + d] = __float2bfloat16_rn(o);
-    else if (p.out_dtype == TQ_F16) reinterpret_cast<__half*>(p.out)[orow * kHeadDim + d] = __float2half_rn(o);
-    else reinterpret_cast<float*>(p.out)[orow * kHeadDim + d] = o;
+    if (d < p.head_dim) {
+        if (p.out_dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[orow * p.head_dim + d] = __float2bfloat16_rn(o);
+        else if (p.out_dtype == TQ_F16) reinterpret_cast<__half*>(p.out)[orow * p.head_dim + d] = __float2half_rn(o);
+        else reinterpret_cast<float*>(p.out)[orow * p.head_dim + d] = o;
+    }
     if (p.out_lse && d == 0) p.out_lse[orow] = lse2 * 0.6931471805599453f;
     if (p.xmode == 2) {  // the last block to finish closes the step
         sync_first_128();
@@ -992,7 +998,8 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
                        "exchange buffer %d is null or not 256-byte aligned", w);
     }
     TQ_REQUIRE(q && kv_cache && page_indices && seq_lens && signs && workspace && out, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == kHeadDim, TQ_ERR_UNSUPPORTED, "decode supports head_dim 128, got %d", head_dim);
+    TQ_REQUIRE(head_dim == kHeadDim || head_dim == 96, TQ_ERR_UNSUPPORTED,
+               "decode supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
     TQ_REQUIRE(block_size == kPageTokens, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
     TQ_REQUIRE(slot_bytes == kSlotBytes, TQ_ERR_UNSUPPORTED, "decode supports 80-byte slots, got %d", slot_bytes);
     TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8 || num_kv_heads == 16,
@@ -1038,6 +1045,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     p.real_group = real_q_heads / num_kv_heads;
     p.max_pages = max_pages;
     p.q_dtype = q_dtype;
+    p.head_dim = head_dim;
     const double inv_sqrt_d = 1.0 / std::sqrt((double)kHeadDim);
     p.k_scale = (float)(inv_sqrt_d * (double)sm_scale * 1.4426950408889634);
     p.v_scale = (float)inv_sqrt_d;
@@ -1072,6 +1080,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     m.nq = nq;
     m.real_heads = real_q_heads;
     m.real_group = real_q_heads / num_kv_heads;
+    m.head_dim = emit_rotated ? kHeadDim : head_dim;
     m.pps = kConsumerWarps / num_kv_heads;
     m.grid_ctas = ctas;
     m.out_dtype = out_dtype;
@@ -1195,7 +1204,8 @@ extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse
     using namespace tq;
     if (rows == 0) return TQ_OK;
     TQ_REQUIRE(partial_o && partial_lse2 && signs && out, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == kHeadDim, TQ_ERR_UNSUPPORTED, "merge supports head_dim 128, got %d", head_dim);
+    TQ_REQUIRE(head_dim == kHeadDim || head_dim == 96, TQ_ERR_UNSUPPORTED,
+               "merge supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
     TQ_REQUIRE(num_parts >= 1 && rows > 0, TQ_ERR_INVALID, "num_parts and rows must be positive");
     TQ_REQUIRE(out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad out_dtype");
     MergeParams m{};
@@ -1207,6 +1217,7 @@ extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse
     m.rows = rows;
     m.num_q_heads = 1;
     m.nq = 1;
+    m.head_dim = head_dim;
     m.num_parts = num_parts;
     m.out_dtype = out_dtype;
     if (num_parts > 64)

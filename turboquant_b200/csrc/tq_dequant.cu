@@ -39,6 +39,7 @@ struct DequantParams {
     void* out[2];                 // K, V: [total_tokens][H][128]
     int64_t out_token_stride;     // elements between tokens
     int max_pages, H, head_shift, block_size, slot_bytes, out_dtype, batch;  // head_shift: log2(H) or -1
+    int head_dim;                 // elements per output row: 128, or 96 (the padded dims are dropped)
     float cen[16];                // (float)(C[i] / sqrt(128))
     float scale;                  // (float)(1 / sqrt(128))
 };
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(kDqThreads) dequant_paged_kernel(const __grid_
     const int lin_half = lin_pin / St::kHalfPieces, lin_pp = lin_pin % St::kHalfPieces;
     const int lin_key = 2 * lin_row + lin_half;
     const int lin_base = lin_row * St::kRowBytes + lin_half * (St::kRowBytes / 2);
-    const bool dense = p.out_token_stride == (int64_t)p.H * kDqDim;
+    const bool dense = p.head_dim == kDqDim && p.out_token_stride == (int64_t)p.H * kDqDim;
     const int m = lane & 1;
     const uint32_t table_lane = smem_u32(table_s) + 8u * (lane & 15);
     const float hsgn = m ? -1.0f : 1.0f;
@@ -272,11 +273,11 @@ __global__ void __launch_bounds__(kDqThreads) dequant_paged_kernel(const __grid_
                     const uint4 piece = *reinterpret_cast<const uint4*>(stage + lin_base + i * kLinRows * St::kRowBytes +
                                                                         ((lin_pp ^ ((lin_key + 2 * i * kLinRows) & 7)) << 4));
                     const int rr = r0 + lin_row + i * kLinRows;
-                    if (rr < cur.rows) {
+                    if (rr < cur.rows && lin_pin * 16 < p.head_dim * kEsz) {
                         int t, h;
                         if (p.head_shift >= 0) { t = rr >> p.head_shift; h = rr & (p.H - 1); }
                         else { t = rr / p.H; h = rr - t * p.H; }
-                        uint8_t* dst = out_base + ((cur.out_row0 + t) * p.out_token_stride + (int64_t)h * kDqDim) * kEsz;
+                        uint8_t* dst = out_base + ((cur.out_row0 + t) * p.out_token_stride + (int64_t)h * p.head_dim) * kEsz;
                         *reinterpret_cast<uint4*>(dst + lin_pin * 16) = piece;
                     }
                 }
@@ -315,7 +316,8 @@ extern "C" int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int bl
     TQ_REQUIRE(batch >= 0 && num_blocks >= 0, TQ_ERR_INVALID, "negative size");
     if (batch == 0 || max_pages == 0) return TQ_OK;
     TQ_REQUIRE(kv_cache && page_indices && seq_lens && cu_seqlens && signs && k_out && v_out, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == kDqDim, TQ_ERR_UNSUPPORTED, "bulk dequantization supports head_dim 128, got %d", head_dim);
+    TQ_REQUIRE(head_dim == kDqDim || head_dim == 96, TQ_ERR_UNSUPPORTED,
+               "bulk dequantization supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
     TQ_REQUIRE(slot_bytes >= 80 && slot_bytes % 16 == 0, TQ_ERR_INVALID, "slot_bytes must be a multiple of 16 and >= 80");
     TQ_REQUIRE(block_size >= 1 && num_kv_heads >= 1 && max_pages >= 1 && batch >= 1, TQ_ERR_INVALID, "bad geometry");
     TQ_REQUIRE(out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad out_dtype");
@@ -343,6 +345,7 @@ extern "C" int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int bl
     p.slot_bytes = slot_bytes;
     p.out_dtype = out_dtype;
     p.batch = batch;
+    p.head_dim = head_dim;
     float bnd[15];
     host_codebook(kDqDim, 4, p.cen, bnd);
     p.scale = (float)(1.0 / std::sqrt((double)kDqDim));

@@ -124,7 +124,7 @@ struct RowLoad;
 // quarter-warps (4 rows: row * 136 words -> 8 banks apart).
 template <>
 struct RowLoad<float> {
-    static constexpr int kRowBytes = kD * 4, kPad = 32;
+    static constexpr int kElemBytes = 4, kPad = 32;
     static __device__ __forceinline__ void quad(const uint8_t* row, int j, int m, float2& a, float2& b) {
         const float4 v = *reinterpret_cast<const float4*>(row + 32 * j + 16 * m);
         a = make_float2(v.x, v.y);
@@ -133,7 +133,7 @@ struct RowLoad<float> {
 };
 template <>
 struct RowLoad<__nv_bfloat16> {
-    static constexpr int kRowBytes = kD * 2, kPad = 16;
+    static constexpr int kElemBytes = 2, kPad = 16;
     static __device__ __forceinline__ void quad(const uint8_t* row, int j, int m, float2& a, float2& b) {
         const uint2 w = *reinterpret_cast<const uint2*>(row + 16 * j + 8 * m);
         a = make_float2(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u));
@@ -142,7 +142,7 @@ struct RowLoad<__nv_bfloat16> {
 };
 template <>
 struct RowLoad<__half> {
-    static constexpr int kRowBytes = kD * 2, kPad = 16;
+    static constexpr int kElemBytes = 2, kPad = 16;
     static __device__ __forceinline__ void quad(const uint8_t* row, int j, int m, float2& a, float2& b) {
         const uint2 w = *reinterpret_cast<const uint2*>(row + 16 * j + 8 * m);
         a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
@@ -152,13 +152,16 @@ struct RowLoad<__half> {
 
 // Threads per block: one block per SM.  16-bit inputs run 16 warps; fp32 rows need twice the
 // staging space, so they run 8.
-template <typename T>
+// D = elements per input row: 128, or fewer (a multiple of 8) for heads that the rotation pads
+// with zeros to 128 (turboquant/hadamard.py:66-68); the cache slot is the same either way.
+template <typename T, int D>
 struct WriteShape {
+    static constexpr int kRowBytes = D * RowLoad<T>::kElemBytes;
     static constexpr int kThreads = sizeof(T) == 4 ? 256 : 512;
     static constexpr int kWarps = kThreads / 32;
     static constexpr int kPieceRows = 16;                 // rows per warp and pass: two lanes per row
     static constexpr int kTileRows = kWarps * kPieceRows;
-    static constexpr int kPitch = RowLoad<T>::kRowBytes + RowLoad<T>::kPad;
+    static constexpr int kPitch = kRowBytes + RowLoad<T>::kPad;
     static constexpr int kOutPitch = 72;                  // 18 words: 16 rows -> 16 different banks
     static constexpr size_t kStageBytes = (size_t)2 * kTileRows * kPitch;
     static constexpr size_t kTableBytes = (size_t)kBins * 16 * sizeof(float2);
@@ -166,11 +169,11 @@ struct WriteShape {
     static constexpr size_t kSmem = kStageBytes + kTableBytes + kOutBytes;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(WriteShape<T>::kThreads, 1)
+template <typename T, int D>
+__global__ void __launch_bounds__(WriteShape<T, D>::kThreads, 1)
 write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     using L = RowLoad<T>;
-    using W = WriteShape<T>;
+    using W = WriteShape<T, D>;
     constexpr int kPitch = W::kPitch, kPieceRows = W::kPieceRows;
     extern __shared__ __align__(128) uint8_t smem[];
     // every warp runs its own two-buffer pipeline over 16-row pieces: no block-wide barrier in the loop
@@ -211,16 +214,16 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         const int64_t left = rows - row0;
         const int64_t nrows = left < kPieceRows ? left : (int64_t)kPieceRows;
         fence_proxy_async();  // earlier shared-memory reads of this buffer precede the copy engine's writes
-        if (lane == 0) mbar_arrive_expect_tx(&full_bar[warp][buf], (uint32_t)(nrows * L::kRowBytes));
+        if (lane == 0) mbar_arrive_expect_tx(&full_bar[warp][buf], (uint32_t)(nrows * W::kRowBytes));
         __syncwarp();
         if (lane < nrows) {
             const int64_t r = row0 + lane;
             int64_t t;
             int h;
             split_row(r, H, p.head_shift, t, h);
-            const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * kD;
+            const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * D;
             bulk_g2s(smem + (size_t)buf * W::kTileRows * kPitch + (size_t)(warp * kPieceRows + lane) * kPitch, src,
-                     L::kRowBytes, &full_bar[warp][buf]);
+                     W::kRowBytes, &full_bar[warp][buf]);
         }
     };
 
@@ -254,6 +257,11 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         float minsq = 1.0f;
 #pragma unroll
         for (int j = 0; j < 16; j++) {
+            if (8 * j >= D) {  // padding of a short head: zeros, which add nothing to the norm
+                x[2 * j] = pk(0.0f, 0.0f);
+                x[2 * j + 1] = pk(0.0f, 0.0f);
+                continue;
+            }
             float2 va, vb;
             L::quad(row, j, m, va, vb);
             x[2 * j] = pk(va.x, va.y);
@@ -383,22 +391,22 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     }
 }
 
-template <typename T>
+template <typename T, int D>
 static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream) {
-    using W = WriteShape<T>;
+    using W = WriteShape<T, D>;
     const size_t smem = W::kSmem;
     static bool configured[64] = {};  // per template instance and device
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(write_kv_cache_kernel<T>,
+        TQ_CUDA(cudaFuncSetAttribute(write_kv_cache_kernel<T, D>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t rows = p.num_tokens * p.num_kv_heads;
     const int64_t tiles = 2 * ((rows + W::kTileRows - 1) / W::kTileRows);  // block-sized groups of pieces
     const int64_t grid = tiles < (int64_t)sm_count ? tiles : (int64_t)sm_count;  // one block per SM
-    TQ_CUDA(launch_serialized(write_kv_cache_kernel<T>, dim3((unsigned)grid), dim3(W::kThreads), smem, stream, p));
+    TQ_CUDA(launch_serialized(write_kv_cache_kernel<T, D>, dim3((unsigned)grid), dim3(W::kThreads), smem, stream, p));
     return TQ_OK;
 }
 
@@ -416,7 +424,8 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     TQ_REQUIRE(num_tokens >= 0 && num_blocks >= 0, TQ_ERR_INVALID, "negative size");
     if (num_tokens == 0) return TQ_OK;
     TQ_REQUIRE(kv_cache && key && value && signs && slot_mapping, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == kD, TQ_ERR_UNSUPPORTED, "cache write supports head_dim 128, got %d", head_dim);
+    TQ_REQUIRE(head_dim == 128 || head_dim == 96, TQ_ERR_UNSUPPORTED,
+               "cache write supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
     TQ_REQUIRE(num_kv_heads >= 1 && block_size >= 1, TQ_ERR_INVALID, "bad geometry");
     TQ_REQUIRE(slot_bytes >= 80 && slot_bytes % 16 == 0, TQ_ERR_INVALID,
                "slot_bytes must be a multiple of 16 and >= 80, got %d", slot_bytes);
@@ -477,9 +486,16 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     int rc = device_sm_count(&sms);
     if (rc != TQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_dim == 96) {
+        switch (in_dtype) {
+            case TQ_F32: return launch_write<float, 96>(p, sms, s);
+            case TQ_F16: return launch_write<__half, 96>(p, sms, s);
+            default: return launch_write<__nv_bfloat16, 96>(p, sms, s);
+        }
+    }
     switch (in_dtype) {
-        case TQ_F32: return launch_write<float>(p, sms, s);
-        case TQ_F16: return launch_write<__half>(p, sms, s);
-        default: return launch_write<__nv_bfloat16>(p, sms, s);
+        case TQ_F32: return launch_write<float, 128>(p, sms, s);
+        case TQ_F16: return launch_write<__half, 128>(p, sms, s);
+        default: return launch_write<__nv_bfloat16, 128>(p, sms, s);
     }
 }

@@ -55,8 +55,9 @@ class KernelConfig:
 
 def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> KernelConfig:
     h, g = model.num_kv_heads, model.gqa_ratio
-    if model.head_dim != 128:
-        return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"head_dim {model.head_dim}: only 128 is implemented")
+    if model.head_dim not in (128, 96):
+        return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False,
+                            f"head_dim {model.head_dim}: 128 (and 96, padded to 128) are implemented")
     if h not in (1, 2, 4, 8, 16):
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"{h} KV heads per GPU: shard to 1, 2, 4, 8 or 16")
     if not 1 <= g <= 8:

@@ -47,15 +47,15 @@ def _workspace(batch: int, hq: int, hkv: int, device) -> torch.Tensor:
 
 
 def _quantize_write_kv_cache(kv_cache, key, value, signs, slot_mapping, head_dim, padded_dim):
-    if padded_dim != 128 or head_dim != 128:
-        raise _cabi.TurboQuantError(f"head_dim {head_dim} / padded_dim {padded_dim}: only 128 is implemented")
+    if padded_dim != 128 or head_dim not in (128, 96):
+        raise _cabi.TurboQuantError(f"head_dim {head_dim} / padded_dim {padded_dim}: 128 (and 96 padded to 128) are implemented")
     _cabi.write_kv_cache(_bytes(kv_cache), key, value, signs, slot_mapping, head_dim)
 
 
 def _decode(q, kv_cache, indices, indptr, seq_lens, num_kv_heads, page_size, head_dim, padded_dim, sm_scale,
             signs, o_ws):
     if padded_dim != 128:
-        raise _cabi.TurboQuantError("decode supports head_dim 128 only")       # as the reference's v5 op
+        raise _cabi.TurboQuantError("decode supports padded head size 128 only")  # as the reference's v5 op
     b, hq, _ = q.shape
     ws = _workspace(b, hq, num_kv_heads, q.device)
     _cabi.decode_paged(q.contiguous(), _bytes(kv_cache), indices.to(torch.int32), seq_lens.to(torch.int32), signs,

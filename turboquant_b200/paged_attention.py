@@ -45,8 +45,8 @@ class TurboQuantPagedAttention:
 
     def __init__(self, num_heads: int, head_size: int, scale: float, num_kv_heads: int,
                  seed: int = 42, num_ctas: int = 0):
-        if head_size != 128:
-            raise _cabi.TurboQuantError(f"head_size {head_size} is not supported (128 only)")
+        if head_size not in (128, 96):
+            raise _cabi.TurboQuantError(f"head_size {head_size} is not supported (128, or 96 padded to 128)")
         self.num_heads = num_heads
         self.head_size = head_size
         self.scale = float(scale)
