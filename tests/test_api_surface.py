@@ -31,8 +31,9 @@ def test_kernel_config_presets():
     assert compute_kernel_config(ModelConfig(64, 8, 128)).stages == 3          # 8 query heads per KV head
     assert compute_kernel_config(ModelConfig(16, 4, 128)).pages_per_stage == 4  # a TP shard with 4 KV heads
     assert not compute_kernel_config(MODEL_PRESETS["gemma-2-9b"]).supported    # head_dim 256: not built yet
-    assert not compute_kernel_config(MODEL_PRESETS["llama-2-7b"]).supported    # 32 KV heads on one GPU
-    assert compute_kernel_config(ModelConfig(16, 16, 128)).pages_per_stage == 1  # ... 16 are fine: a TP-2 shard of it
+    assert compute_kernel_config(MODEL_PRESETS["llama-2-7b"]).supported        # 32 KV heads: two launches of 16
+    assert compute_kernel_config(ModelConfig(16, 16, 128)).pages_per_stage == 1
+    assert not compute_kernel_config(ModelConfig(6, 6, 128)).supported
 
 
 def test_sequence_sharding_is_balanced_and_complete():

@@ -62,7 +62,7 @@ def test_mixed_lengths_vs_oracle(oracle, golden, q_dtype, out_dtype):
 
 
 @pytest.mark.parametrize("hq,hkv", [(32, 8), (16, 4), (16, 2), (8, 1), (8, 8), (64, 8), (4, 4), (16, 16), (32, 16),
-                                    (64, 16)])
+                                    (64, 16), (32, 32), (40, 40), (24, 12), (40, 20), (64, 32)])
 def test_head_geometries(oracle, golden, hq, hkv):
     case = synthetic.decode_case(seed=30 + hq + hkv, seq_lens=[300, 45, 1000], dtype=torch.float16, heads=(hq, hkv))
     cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])

@@ -89,6 +89,10 @@ struct DecodeParams {
     int batch, num_q_heads, group, max_pages, q_dtype;
     int nq, real_heads, real_group;
     int head_dim;  // elements per q / out row: 128, or 96 (the rotation pads it with zeros to 128)
+    // the KV heads of this launch inside the cache's token rows, and its query heads inside q / out
+    int64_t kv_row_bytes;  // bytes between tokens in the cache (all KV heads of the cache)
+    int kv_head_off;       // byte offset of this launch's first KV head inside a token row
+    int q_head_base;       // first real query head of this launch
     float k_scale;  // (1/sqrt(128)) * sm_scale * log2(e): multiplies raw code-domain scores
     float v_scale;  // 1/sqrt(128): centroid scale folded into P
     uint16_t centroid_h[16];  // fp16 bit patterns of the N(0,1) centroids
@@ -208,30 +212,41 @@ __device__ __forceinline__ void seq_pages(const DecodeParams& p, int b, int& fir
 // load 32 bytes apart (checked for every head by a bank simulation; the only exception is the K
 // load with one KV head, two wavefronts instead of one).  Rows r and r + 8 map to tokens a fixed
 // distance apart inside one run, so five address registers serve the twelve loads of a tile.
-template <int HKV>
+//
+// STRIDED: the HKV heads are a slice of a wider token row (more KV heads in the cache than one
+// launch handles), so consecutive tokens are not contiguous and every token row is its own copy
+// (1280, 640 or 320 bytes: slower, bound by the copy engine's request rate).  Rows then sit at a
+// padded pitch, 64 mod 128 for K and 16 mod 128 for V, with the identity row -> token map.
+template <int HKV, bool STRIDED = false>
 struct DecodeSmem {
     static constexpr int kPPS = kConsumerWarps / HKV;  // pages per stage
     static constexpr int kRowBytes = HKV * kSlotBytes;
-    static constexpr int kRunTokens = HKV == 16 ? 2 : HKV == 8 ? 4 : HKV == 4 ? 8 : 16;
+    static constexpr int kRunTokens = STRIDED ? 1 : HKV == 16 ? 2 : HKV == 8 ? 4 : HKV == 4 ? 8 : 16;
     static constexpr int kRunsPerHalf = kPageTokens / kRunTokens;
     static constexpr int kCopyBytes = kRunTokens * kRowBytes;
     static constexpr int kCopiesPerPage = 2 * kRunsPerHalf;
-    static constexpr int kCopiesPerStage = kPPS * kCopiesPerPage;  // 16, 16, 16, 32: one lane each
-    static constexpr int kKRegion = HKV == 16 ? 20736 : HKV == 8 ? 10496 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;  // per page lane
-    static constexpr int kVRegion = HKV == 16 ? 20736 : HKV == 8 ? 10368 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;
+    static constexpr int kCopiesPerStage = kPPS * kCopiesPerPage;  // 16 or 32 (dense), 32 .. 128 (strided)
+    static constexpr int kKPitch = kRowBytes + (64 - kRowBytes % 128 + 128) % 128;  // strided rows
+    static constexpr int kVPitch = kRowBytes + (16 - kRowBytes % 128 + 128) % 128;
+    static constexpr int kKRegion = STRIDED ? kPageTokens * kKPitch
+                                    : HKV == 16 ? 20736 : HKV == 8 ? 10496 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;  // per page lane
+    static constexpr int kVRegion = STRIDED ? kPageTokens * kVPitch
+                                    : HKV == 16 ? 20736 : HKV == 8 ? 10368 : HKV == 4 ? 5248 : kPageTokens * kRowBytes;
     static constexpr int kKBytes = kPPS * kKRegion;
     static constexpr int kVBytes = kPPS * kVRegion;
     static constexpr int kStageBytes = kKBytes + kVBytes;
 
     // run q of a page half -> byte offset of its first row inside the page lane's region
     static __host__ __device__ __forceinline__ constexpr int k_run(int q) {
-        return HKV == 16  ? q * 2560 + 32 * (q & 3) + 128 * (q >> 2)                               // eight runs, 32 bytes apart mod 128
+        return STRIDED    ? q * kKPitch
+               : HKV == 16 ? q * 2560 + 32 * (q & 3) + 128 * (q >> 2)                              // eight runs, 32 bytes apart mod 128
                : HKV == 8 ? q * 2560 + ((q & 1) ? 64 : 0) + ((q & 2) ? 144 : 0)  // 0, 2624, 5264, 7888
                : HKV == 4 ? q * 2576                                             // 0, 2576
                           : 0;
     }
     static __host__ __device__ __forceinline__ constexpr int v_run(int q) {
-        return HKV == 16 ? q * 2560 + 32 * (q & 3) + 128 * (q >> 2) : HKV == 8 ? q * 2592 : HKV == 4 ? q * 2592 : 0;
+        return STRIDED ? q * kVPitch
+               : HKV == 16 ? q * 2560 + 32 * (q & 3) + 128 * (q >> 2) : HKV == 8 ? q * 2592 : HKV == 4 ? q * 2592 : 0;
     }
     // token (0..15 within its page) -> byte offset of its row inside the page lane's region
     static __host__ __device__ __forceinline__ constexpr int k_off(int t) {
@@ -243,7 +258,8 @@ struct DecodeSmem {
     // MMA row / contraction slot r (0..15) -> token within the page
     static __host__ __device__ __forceinline__ constexpr int row_token(int r) {
         const int r7 = r & 7, up = r >> 3;
-        return HKV == 16  ? 2 * ((0x13467520u >> (4 * r7)) & 7) + up                   // runs 0,2,5,7,6,4,3,1
+        return STRIDED    ? r
+               : HKV == 16 ? 2 * ((0x13467520u >> (4 * r7)) & 7) + up                  // runs 0,2,5,7,6,4,3,1
                : HKV == 8 ? 4 * ((0x23013210 >> (4 * r7)) & 3) + (r7 >> 2) + 2 * up   // runs 0,1,2,3,1,0,3,2
                : HKV == 4 ? ((0xAB239810u >> (4 * r7)) & 15) + 4 * up                 // 0,1,8,9,3,2,11,10
                : HKV == 2 ? ((0x53427160u >> (4 * r7)) & 7) + 8 * up                  // 0,6,1,7,2,4,3,5
@@ -271,10 +287,10 @@ struct DecodeSmem {
 //   [stage 0] ... | 64 KB: table + scratch (64 KB) | 128 KB: [stage 1][stage 2]
 constexpr uint32_t kLutAddr = 65536, kLutSpan = 65536;
 
-template <int HKV>
+template <int HKV, bool STRIDED>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_paged_kernel(const __grid_constant__ DecodeParams p) {
-    using S = DecodeSmem<HKV>;
+    using S = DecodeSmem<HKV, STRIDED>;
     static_assert(S::runs_fit(), "stage layout: runs overlap or leave their region");
     constexpr int PPS = S::kPPS;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -427,15 +443,17 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                     if (lane == 0)
                         mbar_arrive_expect_tx(&full_bar[st], (uint32_t)(np * 2 * kPageTokens * S::kRowBytes));
                     __syncwarp();
-                    {
-                        // one copy per lane: lane = page lane * copies per page + (K runs, then V runs)
-                        const int pp = lane / S::kCopiesPerPage, c = lane % S::kCopiesPerPage;
+#pragma unroll
+                    for (int c0 = 0; c0 < S::kCopiesPerStage; c0 += 32) {
+                        // copy index = page lane * copies per page + (K runs, then V runs), one per lane and pass
+                        const int ci = c0 + lane;
+                        const int pp = ci / S::kCopiesPerPage, c = ci % S::kCopiesPerPage;
                         const int page = __shfl_sync(0xffffffffu, my_page, (j + pp) & 31);
-                        if (lane < S::kCopiesPerStage && pp < np) {
+                        if (ci < S::kCopiesPerStage && pp < np) {
                             const bool is_v = c >= S::kRunsPerHalf;
                             const int tok = (c % S::kRunsPerHalf) * S::kRunTokens;  // first token of the run
                             const uint8_t* src = p.kv_cache + (is_v ? p.slab_bytes : 0) +
-                                                 ((int64_t)page * kPageTokens + tok) * S::kRowBytes;
+                                                 ((int64_t)page * kPageTokens + tok) * p.kv_row_bytes + p.kv_head_off;
                             uint8_t* dst = is_v ? sv + pp * S::kVRegion + S::v_off(tok)
                                                 : sk + pp * S::kKRegion + S::k_off(tok);
                             bulk_g2s(dst, src, S::kCopyBytes, &full_bar[st]);
@@ -487,8 +505,8 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             for (int rr = 0; rr < 4; rr++) {
                 const int r = r0 + rr < p.group ? r0 + rr : p.group - 1;
                 const int qi = r / p.real_group, hh = r - qi * p.real_group;
-                const int64_t base = ((((int64_t)b * p.nq + qi) * p.real_heads) + head * p.real_group + hh) * p.head_dim +
-                                     4 * lane;
+                const int64_t base = ((((int64_t)b * p.nq + qi) * p.real_heads) + p.q_head_base + head * p.real_group + hh) *
+                                         p.head_dim + 4 * lane;
                 if (4 * lane >= p.head_dim) {  // padding of a short head
                     v[rr][0] = v[rr][1] = v[rr][2] = v[rr][3] = 0.f;
                 } else if (p.q_dtype == TQ_BF16) {
@@ -704,6 +722,7 @@ struct MergeParams {
     int num_q_heads, num_parts, pps, grid_ctas, out_dtype, emit_rotated;
     int nq, real_heads, real_group;  // virtual head -> (query, real head) of the output row; nq = 1: identity
     int head_dim;                    // elements per output row (128, or 96: the padded dims are dropped)
+    int q_head_base;                 // first real query head of this launch (KV heads handled in several launches)
     // Exchange of rotated partials between the GPUs that split one KV axis (xmode != 0):
     // every rank owns an exchange buffer (ExchangeLayout) that all ranks have mapped.
     int xmode;                       // 0 none, 1 push this rank's partial to all ranks, 2 wait for all ranks and merge
@@ -862,11 +881,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     o = wtot > 0.f ? o / wtot : 0.f;
     const float lse2 = wtot > 0.f ? mm + log2f(wtot) : -INFINITY;
     int64_t orow = row * p.num_q_heads + hq;
-    if (p.nq > 1) {  // virtual head hq = kv_head * cols + (query * real_group + head_in_group)
+    if (p.header) {  // virtual head hq = kv_head * cols + (query * real_group + head_in_group) of this launch
         const int cols = p.nq * p.real_group;
         const int kvh = hq / cols, col = hq - kvh * cols;
         const int qi = col / p.real_group, hh = col - qi * p.real_group;
-        orow = (row * p.nq + qi) * p.real_heads + kvh * p.real_group + hh;
+        orow = (row * p.nq + qi) * p.real_heads + p.q_head_base + kvh * p.real_group + hh;
     }
     if (p.xmode == 1) {
         // Push this rank's rotated partial into every rank's buffer (plain stores over NVLink, or
@@ -958,20 +977,28 @@ static int resolve_ctas(int num_ctas, int* out) {
     return TQ_OK;
 }
 
-template <int HKV>
+template <int HKV, bool STRIDED>
 static int launch_decode(DecodeParams& p, int grid, cudaStream_t stream) {
-    using S = DecodeSmem<HKV>;
+    using S = DecodeSmem<HKV, STRIDED>;
     const int smem = (int)(kLutAddr + kLutSpan) + (kStages - 1) * S::kStageBytes;  // from offset 0: ample
     static bool configured[64] = {};  // the attribute is per device
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_paged_kernel<HKV, STRIDED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    TQ_CUDA(launch_serialized(decode_paged_kernel<HKV>, dim3(grid), dim3(kDecodeThreads), smem, stream, p));
+    TQ_CUDA(launch_serialized(decode_paged_kernel<HKV, STRIDED>, dim3(grid), dim3(kDecodeThreads), smem, stream, p));
     return TQ_OK;
 }
+
+// KV heads one launch handles.  Up to 16 heads that fill the token rows of the cache: one launch
+// on dense rows.  More heads (a multiple of 4): launches of 16, 8 or 4 heads on strided rows.
+static bool single_launch(int num_kv_heads) {
+    return num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8 || num_kv_heads == 16;
+}
+static int chunk_heads(int remaining) { return remaining >= 16 ? 16 : remaining >= 8 ? 8 : 4; }
+static int largest_chunk(int num_kv_heads) { return single_launch(num_kv_heads) ? num_kv_heads : chunk_heads(num_kv_heads); }
 
 struct ExchangeArgs {
     int rank, world;
@@ -1002,13 +1029,16 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
                "decode supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
     TQ_REQUIRE(block_size == kPageTokens, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
     TQ_REQUIRE(slot_bytes == kSlotBytes, TQ_ERR_UNSUPPORTED, "decode supports 80-byte slots, got %d", slot_bytes);
-    TQ_REQUIRE(num_kv_heads == 1 || num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8 || num_kv_heads == 16,
-               TQ_ERR_UNSUPPORTED, "num_kv_heads must be 1, 2, 4, 8 or 16, got %d", num_kv_heads);
+    TQ_REQUIRE(single_launch(num_kv_heads) || (num_kv_heads > 8 && num_kv_heads % 4 == 0), TQ_ERR_UNSUPPORTED,
+               "num_kv_heads must be 1, 2, 4, 8, 16 or a larger multiple of 4, got %d", num_kv_heads);
+    TQ_REQUIRE(!x || single_launch(num_kv_heads), TQ_ERR_UNSUPPORTED,
+               "the kernel-side exchange takes at most 16 KV heads per GPU, got %d", num_kv_heads);
     TQ_REQUIRE(nq >= 1 && real_q_heads >= 1 && real_q_heads % num_kv_heads == 0, TQ_ERR_INVALID,
                "query heads must be a positive multiple of the KV heads, queries_per_seq >= 1");
     TQ_REQUIRE(nq * (real_q_heads / num_kv_heads) <= 8, TQ_ERR_UNSUPPORTED,
                "queries_per_seq x query heads per KV head must be 1..8 (got %d x %d)", nq, real_q_heads / num_kv_heads);
-    const int num_q_heads = nq * real_q_heads;  // virtual heads
+    const int real_group = real_q_heads / num_kv_heads;
+    const int first_chunk = largest_chunk(num_kv_heads);
     TQ_REQUIRE(q_dtype >= TQ_F32 && q_dtype <= TQ_BF16 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16,
                TQ_ERR_INVALID, "bad dtype");
     TQ_REQUIRE(((uintptr_t)kv_cache % 16) == 0 && ((uintptr_t)workspace % 256) == 0, TQ_ERR_INVALID,
@@ -1018,7 +1048,8 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     int ctas = 0;
     int rc = resolve_ctas(num_ctas, &ctas);
     if (rc != TQ_OK) return rc;
-    const WorkspaceLayout w = workspace_layout(batch, num_q_heads, num_kv_heads, ctas);
+    // the workspace is sized for the largest launch and reused by the others (stream order)
+    const WorkspaceLayout w = workspace_layout(batch, nq * real_group * first_chunk, first_chunk, ctas);
     TQ_REQUIRE(workspace_bytes >= w.total, TQ_ERR_WORKSPACE, "workspace too small: %zu < %zu", workspace_bytes, w.total);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -1038,14 +1069,14 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     p.kv_begin = kv_begin;
     p.kv_end = kv_end;
     p.batch = batch;
-    p.num_q_heads = num_q_heads;
-    p.group = num_q_heads / num_kv_heads;
     p.nq = nq;
     p.real_heads = real_q_heads;
-    p.real_group = real_q_heads / num_kv_heads;
+    p.real_group = real_group;
+    p.group = nq * real_group;
     p.max_pages = max_pages;
     p.q_dtype = q_dtype;
     p.head_dim = head_dim;
+    p.kv_row_bytes = (int64_t)num_kv_heads * slot_bytes;
     const double inv_sqrt_d = 1.0 / std::sqrt((double)kHeadDim);
     p.k_scale = (float)(inv_sqrt_d * (double)sm_scale * 1.4426950408889634);
     p.v_scale = (float)inv_sqrt_d;
@@ -1057,58 +1088,76 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     // (a memset node per call costs more than it is worth); it means something to a caller who
     // zeroed the first bytes of the workspace once.
     if (g_events[0]) TQ_CUDA(cudaEventRecord(g_events[0], s));
-    switch (num_kv_heads) {
-        case 16: rc = launch_decode<16>(p, ctas, s); break;
-        case 8: rc = launch_decode<8>(p, ctas, s); break;
-        case 4: rc = launch_decode<4>(p, ctas, s); break;
-        case 2: rc = launch_decode<2>(p, ctas, s); break;
-        default: rc = launch_decode<1>(p, ctas, s); break;
-    }
-    if (rc != TQ_OK) return rc;
-    if (g_events[1]) TQ_CUDA(cudaEventRecord(g_events[1], s));
+    const bool strided = !single_launch(num_kv_heads);
+    for (int kv0 = 0; kv0 < num_kv_heads;) {
+        const int hk = strided ? chunk_heads(num_kv_heads - kv0) : num_kv_heads;  // KV heads of this launch
+        const int vheads = nq * real_group * hk;                                    // its virtual query heads
+        p.num_q_heads = vheads;
+        p.kv_head_off = kv0 * slot_bytes;
+        p.q_head_base = kv0 * real_group;
+        if (strided) {
+            switch (hk) {
+                case 16: rc = launch_decode<16, true>(p, ctas, s); break;
+                case 8: rc = launch_decode<8, true>(p, ctas, s); break;
+                default: rc = launch_decode<4, true>(p, ctas, s); break;
+            }
+        } else {
+            switch (hk) {
+                case 16: rc = launch_decode<16, false>(p, ctas, s); break;
+                case 8: rc = launch_decode<8, false>(p, ctas, s); break;
+                case 4: rc = launch_decode<4, false>(p, ctas, s); break;
+                case 2: rc = launch_decode<2, false>(p, ctas, s); break;
+                default: rc = launch_decode<1, false>(p, ctas, s); break;
+            }
+        }
+        if (rc != TQ_OK) return rc;
+        if (g_events[1] && kv0 == 0) TQ_CUDA(cudaEventRecord(g_events[1], s));
 
-    MergeParams m{};
-    m.partial_o = p.partial_o;
-    m.partial_lse = p.partial_lse;
-    m.header = p.header;
-    m.page_prefix = p.page_prefix;
-    m.signs = signs;
-    m.out = out;
-    m.out_lse = out_lse;
-    m.rows = batch;
-    m.num_q_heads = num_q_heads;
-    m.nq = nq;
-    m.real_heads = real_q_heads;
-    m.real_group = real_q_heads / num_kv_heads;
-    m.head_dim = emit_rotated ? kHeadDim : head_dim;
-    m.pps = kConsumerWarps / num_kv_heads;
-    m.grid_ctas = ctas;
-    m.out_dtype = out_dtype;
-    m.emit_rotated = emit_rotated;
-    if (x) {
-        m.xmode = 1;
-        m.xrank = x->rank;
-        m.xworld = x->world;
-        m.xrows = (int64_t)batch * num_q_heads;
-        for (int w = 0; w < x->world; w++) m.xbuf[w] = static_cast<unsigned char*>(x->bufs[w]);
-    }
-    // parts per sequence: about (blocks x page lanes) / batch; many of them -> the wide merge
-    if ((int64_t)ctas * m.pps > (int64_t)64 * batch)
-        TQ_CUDA(launch_serialized(merge_kernel<16>, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(512), 0, s, m));
-    else
-        TQ_CUDA(launch_serialized(merge_kernel<4>, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(128), 0, s, m));
-    if (x) {
-        // second pass: wait for every rank's partial in this rank's buffer, merge, rotate back
-        MergeParams f = m;
-        f.xmode = 2;
-        f.header = nullptr;
-        f.page_prefix = nullptr;
-        f.rows = m.xrows;
-        f.num_q_heads = 1;
-        f.nq = 1;
-        f.num_parts = x->world;
-        f.emit_rotated = 0;
-        TQ_CUDA(launch_serialized(merge_kernel<4>, dim3((unsigned)m.xrows, 1), dim3(128), 0, s, f));
+        MergeParams m{};
+        m.partial_o = p.partial_o;
+        m.partial_lse = p.partial_lse;
+        m.header = p.header;
+        m.page_prefix = p.page_prefix;
+        m.signs = signs;
+        m.out = out;
+        m.out_lse = out_lse;
+        m.rows = batch;
+        m.num_q_heads = vheads;
+        m.nq = nq;
+        m.real_heads = real_q_heads;
+        m.real_group = real_group;
+        m.q_head_base = p.q_head_base;
+        m.head_dim = emit_rotated ? kHeadDim : head_dim;
+        m.pps = kConsumerWarps / hk;
+        m.grid_ctas = ctas;
+        m.out_dtype = out_dtype;
+        m.emit_rotated = emit_rotated;
+        if (x) {
+            m.xmode = 1;
+            m.xrank = x->rank;
+            m.xworld = x->world;
+            m.xrows = (int64_t)batch * nq * real_q_heads;
+            for (int w = 0; w < x->world; w++) m.xbuf[w] = static_cast<unsigned char*>(x->bufs[w]);
+        }
+        // parts per sequence: about (blocks x page lanes) / batch; many of them -> the wide merge
+        if ((int64_t)ctas * m.pps > (int64_t)64 * batch)
+            TQ_CUDA(launch_serialized(merge_kernel<16>, dim3((unsigned)batch, (unsigned)vheads), dim3(512), 0, s, m));
+        else
+            TQ_CUDA(launch_serialized(merge_kernel<4>, dim3((unsigned)batch, (unsigned)vheads), dim3(128), 0, s, m));
+        if (x) {
+            // second pass: wait for every rank's partial in this rank's buffer, merge, rotate back
+            MergeParams f = m;
+            f.xmode = 2;
+            f.header = nullptr;
+            f.page_prefix = nullptr;
+            f.rows = m.xrows;
+            f.num_q_heads = 1;
+            f.nq = 1;
+            f.num_parts = x->world;
+            f.emit_rotated = 0;
+            TQ_CUDA(launch_serialized(merge_kernel<4>, dim3((unsigned)m.xrows, 1), dim3(128), 0, s, f));
+        }
+        kv0 += hk;
     }
     if (g_events[2]) TQ_CUDA(cudaEventRecord(g_events[2], s));
     return TQ_OK;
@@ -1126,10 +1175,12 @@ extern "C" int tq_debug_set_decode_events(void* ev_start, void* ev_mid, void* ev
 extern "C" size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads,
                                             int head_dim, int num_ctas) {
     (void)head_dim;
-    if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_kv_heads > tq::kConsumerWarps) return 0;
+    if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return 0;
+    if (!tq::single_launch(num_kv_heads) && !(num_kv_heads > 8 && num_kv_heads % 4 == 0)) return 0;
     int ctas = 0;
     if (tq::resolve_ctas(num_ctas, &ctas) != TQ_OK) return 0;
-    return tq::workspace_layout(batch, num_q_heads, num_kv_heads, ctas).total;
+    const int chunk = tq::largest_chunk(num_kv_heads);  // the launches of a call share the workspace
+    return tq::workspace_layout(batch, num_q_heads / num_kv_heads * chunk, chunk, ctas).total;
 }
 
 extern "C" int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads,

@@ -59,7 +59,13 @@ def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> Kernel
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False,
                             f"head_dim {model.head_dim}: 128 (and 96, padded to 128) are implemented")
     if h not in (1, 2, 4, 8, 16):
-        return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"{h} KV heads per GPU: shard to 1, 2, 4, 8 or 16")
+        if h > 8 and h % 4 == 0:
+            # several launches of 16, 8 or 4 heads on strided token rows (one copy per token row)
+            c = 16 if h >= 16 else 8
+            row = c * SLOT_BYTES
+            kp, vp = row + (64 - row % 128) % 128, row + (16 - row % 128) % 128
+            return KernelConfig(CONSUMER_WARPS, CONSUMER_WARPS // c, 3, (CONSUMER_WARPS // c) * PAGE_TOKENS * (kp + vp))
+        return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"{h} KV heads per GPU: 1, 2, 4, 8, 16 or a larger multiple of 4")
     if not 1 <= g <= 8:
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False, f"GQA ratio {g}: 1..8 is implemented")
     pps = CONSUMER_WARPS // h
