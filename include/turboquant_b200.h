@@ -113,7 +113,8 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *
  * Supported geometry: head_dim 128, or 96 (q and out rows of 96 elements; the rotation pads them
  * with zeros to 128 and the slot is the same 80 bytes); block_size 16, slot_bytes 80,
- * num_q_heads/num_kv_heads <= 8, num_kv_heads in {1, 2, 4, 8, 16}.
+ * num_q_heads/num_kv_heads <= 8, num_kv_heads in {1, 2, 4, 8, 16} (one launch) or a larger
+ * multiple of 4 (several launches of 16 / 8 / 4 heads; the workspace is sized for the largest).
  * Replaces: torch.ops.turboquant_v5.decode_v5_from_cache_paged_splitkv_ws and
  *   decode_v5_from_cache_ws (csrc/src/decode_v5_tc_binding.cu:754-874, 440-551), kernels
  *   csrc/include/flashinfer_decode_turboquant_v5_tc.cuh:112-795 and
