@@ -48,7 +48,7 @@ def test_write_head96_matches_reference_fixture(golden, oracle):
     np.testing.assert_array_equal(norms.view(np.uint16), want.view(np.uint16))
 
 
-@pytest.mark.parametrize("heads", [(32, 8), (8, 2)])
+@pytest.mark.parametrize("heads", [(32, 8), (8, 2), (32, 32)])
 def test_decode_and_dequant_head96(oracle, golden, heads):
     lens = [700, 0, 33, 2049]
     case = _case(6, lens, heads)
