@@ -8,26 +8,26 @@
 // Design (one thread block = all KV heads of a contiguous page range):
 //   * The concatenated page list of the whole batch is cut into equal page ranges, one per
 //     thread block, on the device (a warp scan over seq_lens): no host planning, no host sync,
-//     perfectly balanced for mixed lengths.  A block whose range spans several sequences
-//     processes them as consecutive segments and writes one partial per (block, sequence).
-//   * A producer warp streams whole pages with non-multicast 1-D bulk async copies
-//     (cp.async.bulk, one 16-token x H x 80-byte row per copy) into a ring of shared-memory
-//     stages guarded by full/empty mbarriers, so DRAM sees contiguous 10 KB page reads.  Token
-//     rows are padded in shared memory (K: pitch = 64 mod 128, V: pitch = 16 mod 64) which makes
-//     the fragment loads below bank-conflict free.
+//     balanced for mixed lengths.  "Equal" is measured with a charge for every sequence a block
+//     has to start (kSegCostStages).  A block whose range spans several sequences processes them
+//     as consecutive segments and writes one partial per (block, sequence).
+//   * A producer warp streams pages with non-multicast 1-D bulk async copies (cp.async.bulk,
+//     2560 bytes = a run of token rows per copy) into a ring of three shared-memory stages
+//     guarded by full/empty mbarriers.  The runs are placed, and MMA rows mapped to tokens, such
+//     that the fragment loads below are bank-conflict free (DecodeSmem).
 //   * Sixteen consumer warps, one per (KV head, page lane).  Packed codes go from shared memory
 //     straight into mma.sync.m16n8k16 A-fragments: a thread's 16-byte K chunk is exactly its
 //     k-slices of the eight QK MMAs (the head-dim order inside the contraction is free because Q
 //     is loaded in the same permuted order), and V nibbles of two tokens are zipped into bytes
 //     so that one dequantized half2 is a (token, token+1) pair of the PV contraction.  Tokens
-//     sit on the M axis (16) and the GQA query heads on N (8): 2x padding instead of 4x.
+//     sit on the M axis (16) and the query columns of the KV head on N (8).
 //   * Dequantization is a shared-memory table lookup per code BYTE: entry v holds the half2
-//     {centroid(v & 15), centroid(v >> 4)}, replicated once per lane (256 x 32 x 4 B = 32 KB) so
-//     that every lookup of a warp is bank-conflict free.  The logic pipe of the SM runs at half
-//     the FP32 rate, and a pure byte-permute (prmt) dequantizer needs ~17 logic instructions per
-//     8 codes, which capped the first version of this kernel at 31% of HBM peak with the ALU
-//     pipe 65% busy; the lookup needs one permute, one integer multiply-add and one shared load
-//     per 2 codes.  Norms are folded into the scores (K) and into P (V), so there is no
+//     {centroid(v & 15), centroid(v >> 4)}, one column per lane, so that every lookup of a warp
+//     is bank-conflict free; entries are 256 bytes apart at a 64 KB boundary of the shared window,
+//     which lets one byte permute build the address (dequant8).  The logic pipe of the SM runs at
+//     half the FP32 rate, and a pure byte-permute (prmt) dequantizer needs ~17 logic instructions
+//     per 8 codes, which capped the first version of this kernel at 31% of HBM peak with the ALU
+//     pipe 65% busy.  Norms are folded into the scores (K) and into P (V), so there is no
 //     per-element multiply.
 //   * Online softmax in the base-2 domain with one consistent base everywhere; the running
 //     max is only raised when the tile max exceeds it by more than 2^6, which makes rescaling of
@@ -37,8 +37,8 @@
 //
 // Tensor-core generation: the dequantized operands are produced in registers, so the
 // register-operand mma.sync path is used; tcgen05 needs its A/B tiles in shared memory, which
-// would add a 2-byte-per-element shared-memory round trip to a kernel whose limiter is the
-// nibble->fp16 conversion rate, not MMA throughput (about 10% of the tensor pipe is needed).
+// would add a 2-byte-per-element shared-memory round trip to a kernel whose limiters are the
+// shared-memory lookups and instruction issue, not MMA throughput (the tensor pipe is 22% busy).
 #include <cmath>
 #include <cstring>
 
@@ -973,7 +973,7 @@ static int resolve_ctas(int num_ctas, int* out) {
     int sms = 0;
     int rc = device_sm_count(&sms);
     if (rc != TQ_OK) return rc;
-    *out = sms;  // one 17-warp thread block per SM
+    *out = sms;  // one thread block per SM
     return TQ_OK;
 }
 
