@@ -203,8 +203,9 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
     // (the bit pattern of 2^23 + k) * 128 = 2^31 + 128 k modulo 2^32: take the 2^31 out here
     const uint32_t table_lane = smem_u32(bins_s) + 8u * (lane & 15) - 0x80000000u;
     uint8_t* out_s = smem + W::kStageBytes + W::kTableBytes;
-    grid_dependency_wait();  // K, V, the slots, the signs and the cache belong to earlier kernels
+    // the signs, like the table, are constants of the context: both are read ahead of the wait
     if (tid < kD) signs_s[tid] = p.signs[tid];
+    grid_dependency_wait();  // K, V, the slots and the cache belong to earlier kernels
     __syncthreads();
 
     // piece index -> tensor and rows: tile = 2 * piece + tensor
@@ -227,27 +228,29 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         }
     };
 
+    // consecutive pieces go to different blocks: a small write spreads over as many SMs as it has
+    // pieces instead of filling the warps of one
     const int64_t warp_stride = (int64_t)gridDim.x * W::kWarps;
-    int64_t tile = (int64_t)blockIdx.x * W::kWarps + warp;
+    int64_t tile = (int64_t)warp * gridDim.x + blockIdx.x;
     if (tile < num_tiles) issue(tile, 0);
     for (int it = 0; tile < num_tiles; tile += warp_stride, it++) {
         const int buf = it & 1;
         const int64_t next = tile + warp_stride;
         if (next < num_tiles) issue(next, buf ^ 1);  // that buffer was read out one iteration ago
 
-        if (!mbar_wait(&full_bar[warp][buf], (it >> 1) & 1)) return;  // copy never landed: touch nothing
-
         const int which = (int)(tile & 1);
         const int64_t r = (tile >> 1) * kPieceRows + row_in_warp;
         const bool row_ok = r < rows;  // uniform over the two lanes of a row
         int64_t slot = -1;
         int h = 0;
-        if (row_ok) {
+        if (row_ok) {  // the slot is fetched while the rows are still on their way
             int64_t t;
             split_row(r, H, p.head_shift, t, h);
             slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
                                  : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
         }
+
+        if (!mbar_wait(&full_bar[warp][buf], (it >> 1) & 1)) return;  // copy never landed: touch nothing
         // All lanes run the arithmetic (the shuffles need whole pairs).  Rows past the end compute
         // on whatever the buffer holds (any bit pattern is handled: finite rows normalize to
         // |y| <= 1, anything else becomes an all-NaN row) and store nothing.
@@ -404,8 +407,8 @@ static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream)
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int64_t rows = p.num_tokens * p.num_kv_heads;
-    const int64_t tiles = 2 * ((rows + W::kTileRows - 1) / W::kTileRows);  // block-sized groups of pieces
-    const int64_t grid = tiles < (int64_t)sm_count ? tiles : (int64_t)sm_count;  // one block per SM
+    const int64_t pieces = 2 * ((rows + W::kPieceRows - 1) / W::kPieceRows);  // one warp pass each
+    const int64_t grid = pieces < (int64_t)sm_count ? pieces : (int64_t)sm_count;  // one block per SM
     TQ_CUDA(launch_serialized(write_kv_cache_kernel<T, D>, dim3((unsigned)grid), dim3(W::kThreads), smem, stream, p));
     return TQ_OK;
 }
