@@ -63,7 +63,9 @@ int tq_codebook(int dim, int bits, float* centroids, float* boundaries);
  * k_token_stride / v_token_stride elements between tokens (heads contiguous).  One launch
  * covers K and V.  Codes and norms are bit-identical to TurboQuantMSE.quantize on the CPU.
  * head_dim 128, or 96 (rows of 96 elements, zero-padded to 128 by the rotation; signs has 128
- * entries either way).
+ * entries either way).  signs is a constant of the context, as in the reference (one seeded
+ * vector per process): the kernel reads it ahead of its wait on the preceding kernel, so it must
+ * be complete before that kernel is launched.
  * Replaces: torch.ops.turboquant_write.quantize_write_kv_cache
  *   (csrc/src/quantize_write_binding.cu:207-269, kernel csrc/include/turboquant/quantize_write_kernel.cuh:332-431),
  *   called from TurboQuantFusedImpl._write_to_cache (turboquant/vllm_backend_fused.py:293-305). */
