@@ -87,6 +87,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
+// Brings one line into L2 without handing a value to the kernel (L2 is the point of coherence, so a
+// line fetched early still shows later writes of other kernels).
+__device__ __forceinline__ void prefetch_l2(const void* ptr) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+}
+
 // Programmatic dependent launch: the write, decode and merge kernels are launched with programmatic
 // stream serialization, so a kernel's blocks may be scheduled (and run their on-chip prologue)
 // while the kernel before it in the stream drains.  grid_dependency_wait() returns once that

@@ -325,6 +325,25 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         return;
     }
 
+    // Warm L2 with the small inputs while the kernel before this one drains: a whole KV stream has
+    // passed through the cache since they were last touched.  A prefetch hands no value to this
+    // kernel, so it may precede the wait.
+    {
+        const size_t first = ((size_t)blockIdx.x * kDecodeThreads + tid) * 128;
+        const size_t step = (size_t)gridDim.x * kDecodeThreads * 128;
+        auto warm = [&](const void* base, size_t bytes) {
+            for (size_t off = first; off < bytes; off += step) prefetch_l2(static_cast<const uint8_t*>(base) + off);
+        };
+        warm(p.seq_lens, (size_t)p.batch * 4);
+        if (p.page_indptr) {
+            warm(p.page_indptr, (size_t)(p.batch + 1) * 4);
+        } else {
+            const size_t table = (size_t)p.batch * p.max_pages * 4;
+            warm(p.page_indices, table < ((size_t)8 << 20) ? table : ((size_t)8 << 20));
+        }
+        warm(p.q, (size_t)p.batch * p.nq * p.real_heads * p.head_dim * (p.q_dtype == TQ_F32 ? 4 : 2));
+    }
+
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
             mbar_init(&full_bar[s], 1);
