@@ -437,6 +437,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         if (warp > kConsumerWarps) return;
         // =============================== producer warp ======================================
         int st = 0, round = 0;
+        const uint64_t stream_policy = l2_policy_evict_first();  // the cache is read once per launch
         for (int sg = 0; sg < nseg && !abort_flag; sg++) {
             const int b = seg_seq[sg];
             int first_page, npages_b, len_eff;
@@ -475,7 +476,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                                                  ((int64_t)page * kPageTokens + tok) * p.kv_row_bytes + p.kv_head_off;
                             uint8_t* dst = is_v ? sv + pp * S::kVRegion + S::v_off(tok)
                                                 : sk + pp * S::kKRegion + S::k_off(tok);
-                            bulk_g2s(dst, src, S::kCopyBytes, &full_bar[st]);
+                            bulk_g2s_hint(dst, src, S::kCopyBytes, &full_bar[st], stream_policy);
                         }
                     }
                     if (++st == nstages) { st = 0; round++; }
