@@ -405,10 +405,10 @@ def run_ours(args):
     peak, peak_src = measured_peak()
     achieved = alg_bytes / (dec_avg * 1e-3) / 1e9
     # DRAM traffic per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this
-    # kernel on this workload (profiles/decode_paged_kernel_config1_layer.md: 335.8 MB + 4.2 MB for
+    # kernel on this workload (profiles/decode_paged_kernel_config1_layer.md: 335.7 MB + 3.3 MB for
     # batch 8 x ctx 32768), scaled by the tokens of the launch.  The physical slots are 160 B per 136
     # algorithmic bytes, so 1.18x is the floor; the rest is the partial outputs.
-    traffic = 340.07e6 * (B * L) / (8 * 32768)
+    traffic = 339.09e6 * (B * L) / (8 * 32768)
     roofline = {"bound": "hbm", "kernel": "decode_paged_kernel<8>", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                 "traffic": traffic, "expected_min_traffic": alg_bytes * 160.0 / 136.0,
