@@ -57,7 +57,8 @@ int tq_codebook(int dim, int bits, float* centroids, float* boundaries);
  * Cache write.  Quantizes num_tokens x num_kv_heads K rows and V rows (seeded signs -> FWHT ->
  * L2 norm -> 4-bit Lloyd-Max code -> nibble pack) and scatters them into the paged cache
  *   kv_cache : uint8 [2][num_blocks][block_size][num_kv_heads][slot_bytes]
- * at slot_mapping[t] = block*block_size + entry; a negative slot skips the token.  Per slot:
+ * at slot_mapping[t] = block*block_size + entry; a negative slot skips the token, and so does a
+ * slot at or beyond num_blocks * block_size (counted, see tq_fault_counts).  Per slot:
  * bytes [0, pd/2) codes (even dim high nibble), then the fp16 norm once per 64 dims, pad
  * untouched.  key/value: [num_tokens][num_kv_heads][head_dim] of in_dtype with
  * k_token_stride / v_token_stride elements between tokens (heads contiguous).  One launch
@@ -109,8 +110,11 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *   out_lse      optional fp32 [batch][num_q_heads], natural-log LSE of the scaled scores
  *   workspace    at least tq_decode_workspace_bytes(...) bytes, 256-byte aligned.  Its first int32 is a
  *                sticky status word (0 ok, 1 a bounded wait ran out, 2 too many sequences per block,
- *                3 shared-memory map did not fit): zero the workspace once if you want to read it;
- *                no call clears it and nothing else in the workspace needs initialising
+ *                3 shared-memory map did not fit, 4 a sequence is longer than its page table: nothing
+ *                is read and out is zero, 5 a page id outside [0, num_blocks): that page is replaced
+ *                by page 0, out is wrong but no address is formed from the id): zero the workspace
+ *                once if you want to read it; no call clears it and nothing else in the workspace
+ *                needs initialising
  *   num_ctas     thread blocks to balance over; 0 = one per SM of the current device
  *
  * Supported geometry: head_dim 128, or 96 (q and out rows of 96 elements; the rotation pads them
@@ -124,6 +128,10 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *   TurboQuantFusedImpl._choose_num_splits/_get_v5_ws (turboquant/vllm_backend_fused.py:129-215). */
 size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim,
                                  int num_ctas);
+/* Widest query tile of the decode kernels: queries_per_seq x (num_q_heads / num_kv_heads) of
+ * tq_decode_paged_multi may not exceed it.  The reference's kernel has a fixed tile of 4 query
+ * heads per KV head (csrc/src/decode_v5_tc_binding.cu:779-785). */
+int tq_decode_max_query_columns(void);
 int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
                     int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,
                     int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
@@ -193,10 +201,13 @@ int tq_pages_scatter(void* kv_cache, int64_t num_blocks, int block_size, int num
  *                  256-byte aligned, zeroed once on every rank before any rank's first call.
  * The step counter lives in the buffer, so the call can be captured in a CUDA graph and replayed.
  * Word 1 of the buffer is a sticky status: 1 = a wait for a peer ran out (out is then not written).
- * All ranks must make the same sequence of calls.  Replaces the reference-side plan of an
+ * tq_set_exchange_wait_limit sets, for the calls this process makes afterwards, how many polls
+ * (256 ns apart) that wait may take before it gives up; 0 restores the default (2^22, about a
+ * second).  All ranks must make the same sequence of calls.  Replaces the reference-side plan of an
  * all-gather of split partials followed by SplitKVCombineKernel (combine.cuh:18-79) across GPUs;
  * the reference itself has no multi-GPU decode. */
 size_t tq_exchange_bytes(int64_t rows, int world);
+int tq_set_exchange_wait_limit(int polls);
 int tq_decode_paged_exchange(const void* q, int q_dtype, int batch, int queries_per_seq, int num_q_heads,
                              int num_kv_heads, int head_dim, const void* kv_cache, int64_t num_blocks,
                              int block_size, int slot_bytes, const int32_t* page_indices,
@@ -237,29 +248,49 @@ int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_
  * split-KV workspaces, turboquant/vllm_backend_fused.py:158-215).  The split-KV scratch is a
  * fixed array of TQ_STATIC_SCRATCH_BYTES (8 MiB) inside the library image; every GPU
  * that loads the library holds it until the process exits.  Arguments and results are those of
- * tq_decode_paged without the workspace pair.
- *   - Calls whose scratch need (it grows with batch, num_q_heads and num_ctas; see
- *     tq_decode_workspace_bytes) exceeds the array fail with TQ_ERR_WORKSPACE and a message; at
- *     32 query heads that is a batch of roughly 170 with one block per SM on a 148-SM part.
+ * tq_decode_paged without the workspace pair, with num_kv_heads restricted to 1, 2, 4, 8 or 16.
+ *   - Calls whose scratch need (tq_decode_workspace_bytes: it grows with batch, num_q_heads and
+ *     num_ctas) exceeds the array fail with TQ_ERR_WORKSPACE and a message.  With one block per
+ *     SM on a 148-SM part: 32 query / 8 KV heads fit up to batch 105; a tensor-parallel shard
+ *     with 32 query heads over 4 KV heads needs 9.8 MB already at batch 1 and never fits (pass a
+ *     smaller num_ctas, or use tq_decode_paged with your own workspace).
  *   - The first call on each device looks up the array's device address; make that call before
  *     starting any stream capture.  No call allocates or frees device memory.
  *   - All calls on one device share the array and find the previous call's contents in it: every
  *     part that a call reads is overwritten by that call first, and the only word that has to
  *     start at zero, the sticky status word, does so because the array is zero-initialised at
  *     load.  Two calls that can overlap on the GPU (different streams) race on the array; keep
- *     them on one stream or order them. */
+ *     them on one stream or order them.
+ *   - tq_decode_static_status copies that status word (same codes as the workspace's first word
+ *     in tq_decode_paged) to status_out, device or pinned host memory, asynchronously on
+ *     `stream`: a non-zero value after a call means that call (or an earlier one) left partials
+ *     unwritten and out must not be trusted. */
 #define TQ_STATIC_SCRATCH_BYTES (8u << 20)
 int tq_decode_paged_static(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads,
                            int head_dim, const void* kv_cache, int64_t num_blocks, int block_size,
                            int slot_bytes, const int32_t* page_indices, const int32_t* page_indptr,
                            int max_pages, const int32_t* seq_lens, const float* signs, float sm_scale,
                            void* out, int out_dtype, float* out_lse, int num_ctas, void* stream);
+int tq_decode_static_status(int32_t* status_out, void* stream);
 
-/* Measurement hook (diagnostics; no reference counterpart).  While three CUDA events are set
- * for the calling thread, tq_decode_paged / tq_decode_paged_partial record them on the call's
- * stream: ev_start before the decode kernel, ev_mid between the decode kernel and the merge
- * kernel, ev_end after the merge kernel.  Pass NULLs to switch it off.  Not for use inside a
- * stream capture. */
+/* ---------------------------------------------------------------------------------------
+ * Diagnostics.  Not part of the data path and without a reference counterpart: an integration
+ * does not need to bind these.
+ * --------------------------------------------------------------------------------------- */
+
+/* Index faults that the kernels without a workspace caught instead of dereferencing, since the
+ * library was loaded on the current device: counts3[0] tokens whose slot was at or beyond
+ * num_blocks * block_size in tq_write_kv_cache (dropped like a negative slot), counts3[1] page
+ * halves tq_dequant_paged skipped (page id outside the cache, or a sequence longer than its page
+ * list; their output rows stay unwritten), counts3[2] pages tq_pages_gather / _scatter skipped.
+ * Host array of three; synchronises the device.  The reference only checks shapes
+ * (csrc/src/quantize_write_binding.cu:216-227). */
+int tq_fault_counts(int32_t* counts3);
+
+/* Measurement hook.  While three CUDA events are set for the calling thread, the decode entry
+ * points record them on the call's stream: ev_start before the decode kernel, ev_mid between
+ * the decode kernel and the merge kernel, ev_end after the merge kernel.  Pass NULLs to switch
+ * it off.  Not for use inside a stream capture. */
 int tq_debug_set_decode_events(void* ev_start, void* ev_mid, void* ev_end);
 
 #ifdef __cplusplus

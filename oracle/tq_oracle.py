@@ -145,6 +145,42 @@ def decode_paged(q, kv_cache: np.ndarray, block_table, seq_lens, signs, sm_scale
     return (out, lse) if return_lse else out
 
 
+def decode_paged_parallel(q, kv_cache: np.ndarray, block_table, seq_lens, signs, sm_scale: float,
+                          threads: int | None = None, chunk_tokens: int = 8192, return_lse: bool = False):
+    """``decode_paged`` at benchmark sizes: every sequence's token range is cut into chunks of
+    ``chunk_tokens``, the chunks run on ``threads`` host threads (the C call releases the GIL) and
+    the per-chunk (out, lse) pairs are combined with ``merge_partials``.  Same arithmetic per
+    chunk as ``decode_paged``; the merge is the log-sum-exp identity in double precision."""
+    from concurrent.futures import ThreadPoolExecutor
+    q = _f32(q)
+    B, Hq, D = q.shape
+    bt = np.ascontiguousarray(block_table, np.int32)
+    sl = np.ascontiguousarray(seq_lens, np.int32)
+    threads = threads or os.cpu_count() or 1
+    jobs = []
+    for b in range(B):
+        n = int(sl[b])
+        cuts = list(range(0, n, chunk_tokens)) or [0]
+        for a in cuts:
+            jobs.append((b, a, min(a + chunk_tokens, n)))
+
+    def one(job):
+        b, a, e = job
+        return decode_paged(q[b:b + 1], kv_cache, bt[b:b + 1], sl[b:b + 1], signs, sm_scale,
+                            kv_begin=a, kv_end=max(e, a), return_lse=True)
+    lib()
+    with ThreadPoolExecutor(max_workers=threads) as ex:
+        parts = list(ex.map(one, jobs))
+    out = np.zeros((B, Hq, D), np.float32)
+    lse = np.full((B, Hq), -np.inf, np.float32)
+    for b in range(B):
+        mine = [p for j, p in zip(jobs, parts) if j[0] == b]
+        po = np.stack([p[0][0] for p in mine])
+        pl = np.stack([p[1][0] for p in mine])
+        out[b], lse[b] = merge_partials(po, pl)
+    return (out, lse) if return_lse else out
+
+
 def merge_partials(partial_o, partial_lse):
     """partial_o fp32 [S, rows..., D], partial_lse fp32 [S, rows...] (natural log)."""
     po, pl = _f32(partial_o), _f32(partial_lse)

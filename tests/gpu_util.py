@@ -38,11 +38,15 @@ def run_decode(q, cache_dev, block_table, seq_lens, sm_scale=None, out_dtype=Non
     return (out, lse) if want_lse else out
 
 
-def assert_attention_close(got, want, what=""):
-    """Parity bar for attention outputs against the dequant-attention oracle:
-    every element within max-abs 2e-3 + relative 1e-2 of the oracle value (an fp16/bf16 output
-    of magnitude ~1 cannot be closer than its own rounding step), and the whole tensor within
-    1e-2 relative error in the Frobenius norm."""
+def assert_attention_close(got, want, what="", strict=False):
+    """Parity bar for attention outputs against the dequant-attention oracle.
+
+    Mixed bar (always): every element within max-abs 2e-3 + relative 1e-2 of the oracle value
+    (an fp16/bf16 output of magnitude ~1 cannot be closer than its own rounding step, 1.95e-3
+    for bf16), and the whole tensor within 1e-2 relative error in the Frobenius norm.
+    ``strict`` additionally asserts the plain reading of the bar, max-abs <= 2e-3 AND relative
+    <= 1e-2; it holds wherever the outputs are well below 1 (the long-context configs) or the
+    output type is fp32/fp16.  Returns (max-abs, relative) so that callers can record them."""
     got = np.asarray(got, np.float64)
     want = np.asarray(want, np.float64)
     err = np.abs(got - want)
@@ -51,4 +55,19 @@ def assert_attention_close(got, want, what=""):
     worst = (err - bound).max()
     assert worst <= 0, f"{what}: element error {err.max():.3e} exceeds 2e-3 + 1e-2*|ref| by {worst:.3e} (rel {rel:.3e})"
     assert rel <= 1e-2, f"{what}: relative {rel:.3e} > 1e-2 (max-abs {err.max():.3e})"
+    if strict:
+        assert err.max() <= 2e-3, f"{what}: strict max-abs {err.max():.3e} > 2e-3 (rel {rel:.3e})"
     return err.max(), rel
+
+
+def fill_cache_gpu(cache, block_table_row, n_tokens, gen, chunk=65536, heads=8):
+    """Seeded N(0,1) bf16 K/V for one sequence, quantized into its pages by the CUDA write kernel
+    (bit-identical to the oracle's write, which the write tests establish)."""
+    signs = signs_dev()
+    for t0 in range(0, n_tokens, chunk):
+        n = min(chunk, n_tokens - t0)
+        k = torch.randn(n, heads, 128, generator=gen, device=DEV).to(torch.bfloat16)
+        v = torch.randn(n, heads, 128, generator=gen, device=DEV).to(torch.bfloat16)
+        tok = torch.arange(t0, t0 + n, device=DEV)
+        slots = block_table_row.long()[tok // 16] * 16 + tok % 16
+        _cabi.write_kv_cache(cache, k, v, signs, slots, 128)

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from turboquant_b200 import _cabi, synthetic
-from tests.gpu_util import DEV, assert_attention_close, oracle_cache, run_decode, signs_dev
+from tests.gpu_util import DEV, assert_attention_close, fill_cache_gpu, oracle_cache, run_decode, signs_dev
 
 pytestmark = pytest.mark.gpu
 SCALE = 1.0 / math.sqrt(128)
@@ -28,7 +28,7 @@ def test_config0_vs_reference_output(golden, oracle):
     cache = oracle_cache(oracle, c0, golden["signs_seed42_d128"])
     out, lse = run_decode(c0.q.to(DEV), torch.from_numpy(cache).to(DEV), c0.block_table.to(DEV),
                           c0.seq_lens.to(DEV), want_lse=True)
-    assert_attention_close(out.float().cpu().numpy(), golden["cfg0_out"], "config 0")
+    assert_attention_close(out.float().cpu().numpy(), golden["cfg0_out"], "config 0", strict=True)
     np.testing.assert_allclose(lse.cpu().numpy(), golden["cfg0_lse"], atol=2e-3)
 
 
@@ -179,6 +179,85 @@ def test_config1_full_size_properties():
     out2 = run_decode(q, cache, bt, sl2, out_dtype=torch.float32).cpu().numpy()
     assert np.abs(out2[2:] - ref[2:]).max() <= 2e-4
     assert np.abs(out2[0] - ref[0]).max() > 1e-4
+
+
+def test_config1_full_size_vs_oracle(oracle, golden):
+    """One full layer of the benchmark's workload (batch 8 x 32768 tokens, bf16 queries and
+    outputs, pages permuted) against the dequant-attention oracle run over the same bytes; the
+    strict bar (max-abs 2e-3 and relative 1e-2) is asserted, not only the mixed one."""
+    B, L = 8, 32768
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(1)
+    nb = B * L // 16
+    cache = torch.zeros((2, nb, 16, 8, 80), dtype=torch.uint8, device=DEV)
+    bt = torch.randperm(nb, generator=torch.Generator().manual_seed(1)).view(B, L // 16).to(torch.int32).to(DEV)
+    for b in range(B):
+        fill_cache_gpu(cache, bt[b], L, gen)
+    q = torch.randn(B, 32, 128, generator=gen, device=DEV).to(torch.bfloat16)
+    sl = torch.full((B,), L, dtype=torch.int32, device=DEV)
+    out, lse = run_decode(q, cache, bt, sl, out_dtype=torch.bfloat16, want_lse=True)
+    want, want_lse = oracle.decode_paged_parallel(q.float().cpu().numpy(), cache.cpu().numpy(), bt.cpu().numpy(),
+                                                  sl.cpu().numpy(), golden["signs_seed42_d128"], SCALE, return_lse=True)
+    max_abs, rel = assert_attention_close(out.float().cpu().numpy(), want, "config 1, one full layer", strict=True)
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=2e-3)
+    print(f"config 1 full size: max-abs {max_abs:.3e}, relative {rel:.3e}")
+
+
+def test_config3_full_size_vs_oracle(oracle, golden):
+    """The mixed-length config at its real size: 64 sequences, lengths log-uniform in
+    [512, 131072] (seed 3), one layer, random block table, against the oracle."""
+    lens = synthetic.mixed_lengths(seed=3, n=64)
+    bt_cpu, _, nb = synthetic.paged_layout(lens, seed=3)
+    bt = bt_cpu.to(DEV)
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(3)
+    cache = torch.zeros((2, nb, 16, 8, 80), dtype=torch.uint8, device=DEV)
+    for b, n in enumerate(lens):
+        fill_cache_gpu(cache, bt[b], n, gen)
+    q = torch.randn(len(lens), 32, 128, generator=gen, device=DEV).to(torch.bfloat16)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out, lse = run_decode(q, cache, bt, sl, out_dtype=torch.bfloat16, want_lse=True)
+    want, want_lse = oracle.decode_paged_parallel(q.float().cpu().numpy(), cache.cpu().numpy(), bt_cpu.numpy(),
+                                                  sl.cpu().numpy(), golden["signs_seed42_d128"], SCALE, return_lse=True)
+    max_abs, rel = assert_attention_close(out.float().cpu().numpy(), want, "config 3, 64 mixed lengths", strict=True)
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=2e-3)
+    print(f"config 3 full size: {sum(lens)} tokens, max-abs {max_abs:.3e}, relative {rel:.3e}")
+
+
+def test_config4_full_size_vs_oracle(oracle, golden):
+    """One sequence of 1,048,576 tokens with 8 decode queries that share its KV
+    (tq_decode_paged_multi) against the oracle: the oracle sees the 8 queries as 32 query heads
+    per KV head of one batch row, so it too dequantizes every token once."""
+    total, nq = 1_048_576, 8
+    pages = total // 16
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(4)
+    bt_row = torch.randperm(pages, generator=torch.Generator().manual_seed(4)).to(torch.int32).to(DEV)
+    cache = torch.zeros((2, pages, 16, 8, 80), dtype=torch.uint8, device=DEV)
+    fill_cache_gpu(cache, bt_row, total, gen)
+    q = torch.randn(nq, 32, 128, generator=gen, device=DEV).to(torch.bfloat16)
+    share = _cabi.decode_max_queries_per_seq(32, 8)
+    rows = nq // share
+    qm = q.view(rows, share, 32, 128).contiguous()
+    bt = bt_row.unsqueeze(0).expand(rows, -1).contiguous()
+    sl = torch.full((rows,), total, dtype=torch.int32, device=DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(rows, share * 32, 8), dtype=torch.uint8, device=DEV)
+    out = torch.empty_like(qm)
+    lse = torch.empty(rows, share, 32, dtype=torch.float32, device=DEV)
+    _cabi.decode_paged_multi(qm, cache, bt, sl, signs_dev(), SCALE, ws, out, out_lse=lse)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 0
+    # oracle: one batch row with 8 x 4 query heads per KV head; virtual head = kv * 32 + query * 4 + g
+    qv = q.float().cpu().numpy().reshape(nq, 8, 4, 128).transpose(1, 0, 2, 3).reshape(1, 256, 128)
+    want, want_lse = oracle.decode_paged_parallel(qv, cache.cpu().numpy(), bt_row.cpu().numpy()[None],
+                                                  np.array([total], np.int32), golden["signs_seed42_d128"], SCALE,
+                                                  chunk_tokens=16384, return_lse=True)
+    want = want.reshape(8, nq, 4, 128).transpose(1, 0, 2, 3).reshape(nq, 32, 128)
+    want_lse = want_lse.reshape(8, nq, 4).transpose(1, 0, 2).reshape(nq, 32)
+    max_abs, rel = assert_attention_close(out.float().cpu().numpy().reshape(nq, 32, 128), want,
+                                          "config 4, 1M tokens x 8 queries", strict=True)
+    np.testing.assert_allclose(lse.cpu().numpy().reshape(nq, 32), want_lse, atol=2e-3)
+    print(f"config 4 full size: max-abs {max_abs:.3e}, relative {rel:.3e}")
 
 
 @pytest.mark.parametrize("nq,hq,hkv", [(2, 32, 8), (8, 8, 8), (3, 8, 4), (4, 4, 2), (1, 32, 8)])

@@ -31,6 +31,7 @@ EXPORTS = (
     "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
     "tq_decode_paged_static", "tq_decode_paged_multi", "tq_exchange_bytes", "tq_decode_paged_exchange",
     "tq_dequant_paged", "tq_pages_packed_bytes", "tq_pages_gather", "tq_pages_scatter",
+    "tq_decode_max_query_columns", "tq_set_exchange_wait_limit", "tq_decode_static_status", "tq_fault_counts",
 )
 
 _lib = None
@@ -73,6 +74,41 @@ def _cuda(t: torch.Tensor, name: str) -> None:
         raise TurboQuantError(f"{name} must be a CUDA tensor (no CPU fallback)")
 
 
+def debug_checks() -> bool:
+    """TQ_DEBUG_CHECKS=1 makes every call validate its index tensors on the host first (minimum /
+    maximum of slots, page ids and lengths against the cache geometry).  Each check synchronises,
+    so this is for bringing up an integration, not for serving."""
+    return os.environ.get("TQ_DEBUG_CHECKS", "0") not in ("", "0")
+
+
+def _check_slots(slot_mapping: torch.Tensor, num_blocks: int, block_size: int) -> None:
+    if slot_mapping.numel() and int(slot_mapping.max().item()) >= num_blocks * block_size:
+        raise TurboQuantError(f"slot_mapping holds slot {int(slot_mapping.max().item())} but the cache has "
+                              f"{num_blocks} x {block_size} = {num_blocks * block_size} slots")
+
+
+def _check_pages(page_indices, page_indptr, max_pages, seq_lens, num_blocks: int, block_size: int) -> None:
+    lens = seq_lens.to(torch.int64)
+    if lens.numel() and int(lens.min().item()) < 0:
+        raise TurboQuantError("seq_lens holds a negative length")
+    need = (lens + block_size - 1) // block_size
+    if page_indptr is None:
+        if lens.numel() and int(need.max().item()) > max_pages:
+            raise TurboQuantError(f"a sequence needs {int(need.max().item())} pages but the block table has {max_pages} per row")
+        rows = page_indices.reshape(lens.numel(), -1)[:, :max_pages].to(torch.int64)
+        used = torch.arange(rows.shape[1], device=rows.device)[None, :] < need[:, None]
+        ids = rows[used]
+    else:
+        ptr = page_indptr.to(torch.int64)
+        have = ptr[1:] - ptr[:-1]
+        if bool((need > have[: need.numel()]).any().item()):
+            raise TurboQuantError("a sequence is longer than its page list (page_indptr)")
+        ids = page_indices[: int(ptr[-1].item())].to(torch.int64)
+    if ids.numel() and (int(ids.min().item()) < 0 or int(ids.max().item()) >= num_blocks):
+        raise TurboQuantError(f"page id out of range: [{int(ids.min().item())}, {int(ids.max().item())}] "
+                              f"with {num_blocks} pages in the cache")
+
+
 def dtype_code(dt: torch.dtype) -> int:
     try:
         return _DTYPES[dt]
@@ -112,6 +148,8 @@ def write_kv_cache(kv_cache: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         raise TurboQuantError("signs must be contiguous fp32 of padded head size")
     if slot_mapping.dtype not in (torch.int32, torch.int64) or not slot_mapping.is_contiguous():
         raise TurboQuantError("slot_mapping must be contiguous int32 or int64")
+    if debug_checks():
+        _check_slots(slot_mapping, nb, bs)
     _check(lib().tq_write_kv_cache(
         _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(H), ctypes.c_int(ebs),
         _ptr(key), _ptr(value), ctypes.c_int(dtype_code(key.dtype)), ctypes.c_int64(T),
@@ -187,6 +225,27 @@ def _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, si
         raise TurboQuantError("page_indptr must be a CUDA int32 tensor")
     if seq_lens.shape[0] != q.shape[0]:
         raise TurboQuantError("seq_lens must have one entry per query row")
+    if debug_checks():
+        _check_pages(page_indices, page_indptr, max_pages, seq_lens, kv_cache.shape[1], kv_cache.shape[2])
+
+
+def decode_max_queries_per_seq(num_q_heads: int, num_kv_heads: int) -> int:
+    """How many decode queries that share one sequence's KV fit one pass of ``decode_paged_multi``."""
+    cols = int(lib().tq_decode_max_query_columns())
+    return max(1, cols // max(1, num_q_heads // num_kv_heads))
+
+
+def fault_counts():
+    """(dropped cache-write tokens, skipped dequant page halves, skipped offload pages) that the
+    kernels caught as out-of-range indices since the library was loaded; synchronises."""
+    c = (ctypes.c_int32 * 3)()
+    _check(lib().tq_fault_counts(c))
+    return tuple(int(x) for x in c)
+
+
+def set_exchange_wait_limit(polls: int) -> None:
+    """Polls (256 ns apart) the KV-split exchange may wait for a peer's partial; 0 = default."""
+    _check(lib().tq_set_exchange_wait_limit(ctypes.c_int(polls)))
 
 
 def decode_paged(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, workspace, out,
@@ -395,3 +454,12 @@ def decode_paged_static(q, kv_cache, page_indices, seq_lens, signs, sm_scale: fl
         ctypes.c_float(sm_scale), _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse),
         ctypes.c_int(num_ctas), _stream(q)))
     return out
+
+
+def decode_static_status(device=None) -> int:
+    """Sticky status word of the built-in scratch of ``decode_paged_static`` on the current device
+    (0 = every call so far wrote all its partials); synchronises the current stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = torch.zeros(1, dtype=torch.int32, device=dev)
+    _check(lib().tq_decode_static_status(_ptr(word), _stream(word)))
+    return int(word.item())

@@ -55,7 +55,19 @@ int device_sm_count(int* out) {
     return TQ_OK;
 }
 
+int write_fault_count(int32_t* out);
+int dequant_fault_count(int32_t* out);
+int pages_fault_count(int32_t* out);
+
 }  // namespace tq
+
+extern "C" int tq_fault_counts(int32_t* counts3) {
+    TQ_REQUIRE(counts3 != nullptr, TQ_ERR_INVALID, "null pointer");
+    int rc = tq::write_fault_count(counts3);
+    if (rc == TQ_OK) rc = tq::dequant_fault_count(counts3 + 1);
+    if (rc == TQ_OK) rc = tq::pages_fault_count(counts3 + 2);
+    return rc;
+}
 
 extern "C" int tq_abi_version(void) { return TQ_ABI_VERSION; }
 

@@ -58,7 +58,12 @@ constexpr int kConsumerWarps = 16;
 constexpr int kDecodeThreads = (kConsumerWarps + 4) * 32;
 constexpr int kStages = 3;  // ring depth: one stage below the lookup table, two above it
 constexpr int kMaxExchangeRanks = 16;
-constexpr int kExchangeSpinLimit = 1 << 22;  // x 256 ns sleeps: a second or so, then status 1
+constexpr int kExchangeSpinLimit = 1 << 22;  // default, x 256 ns sleeps: a second or so, then status 1
+// status words (workspace header word 0, sticky): 1 a bounded wait ran out, 2 more sequences inside
+// one block's page range than its list holds, 3 the shared-memory map did not fit, 4 a sequence is
+// longer than its page table (nothing is read, the output is zero), 5 a page id outside
+// [0, num_blocks) (the page is replaced by page 0, the output is wrong but nothing faults)
+constexpr int kStatusSeqTooLong = 4, kStatusBadPage = 5;
 constexpr int kMaxSegments = 96;
 constexpr int kMinPagesPerCta = 4;
 // Starting a sequence inside a block (rotate its queries, later write its partial) costs about as
@@ -81,6 +86,7 @@ struct DecodeParams {
     float* partial_lse;     // workspace: [slots][num_q_heads]
     float* partial_o;       // workspace: [slots][num_q_heads][128]
     int64_t slab_bytes;
+    int64_t num_blocks;        // pages in the cache: page ids outside [0, num_blocks) are never dereferenced
     int64_t kv_begin, kv_end;  // token window applied to every sequence (kv_end < 0: none)
     // A sequence may carry several decode queries that share its KV (queries_per_seq).  Inside the
     // kernels they are extra columns of the query tile: num_q_heads and group below are the VIRTUAL
@@ -368,13 +374,34 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         // pass 1: total pages and the number of non-empty sequences
         int total_real = 0, nonempty = 0;
         int np_first = 0;  // this lane's sequence of the first 32: kept for pass 2 (one global round trip less)
+        bool too_long = false;
         for (int base = 0; base < p.batch; base += 32) {
-            int np = 0, fp, le;
-            if (base + lane < p.batch) seq_pages(p, base + lane, fp, np, le);
+            int np = 0, fp = 0, le;
+            if (base + lane < p.batch) {
+                seq_pages(p, base + lane, fp, np, le);
+                // pages the sequence has in its table (dense: the row; CSR: its indptr span)
+                const int have = p.page_indptr ? p.page_indptr[base + lane + 1] - p.page_indptr[base + lane] : p.max_pages;
+                too_long |= np > 0 && fp + np > have;
+            }
             if (base == 0) np_first = np;
             nonempty += __popc(__ballot_sync(0xffffffffu, np > 0));
             for (int o = 16; o > 0; o >>= 1) np += __shfl_xor_sync(0xffffffffu, np, o);
             total_real += np;
+        }
+        if (__any_sync(0xffffffffu, too_long)) {
+            // A length that its page table cannot back would walk off the table: read nothing, let the
+            // merge write zeros (no parts for any sequence) and say so in the status word.
+            if (blockIdx.x == 0) {
+                for (int b = lane; b <= p.batch; b += 32) p.page_prefix[b] = 0;
+                if (lane == 0) {
+                    p.header[1] = 1;
+                    p.header[2] = 0;
+                    p.header[3] = 0;
+                    atomicExch(&p.header[0], kStatusSeqTooLong);
+                }
+            }
+            if (lane == 0) num_segments = 0;
+            total_real = -1;
         }
         int n_eff = (total_real + kMinPagesPerCta * PPS - 1) / (kMinPagesPerCta * PPS);
         n_eff = n_eff < 1 ? 1 : (n_eff > (int)gridDim.x ? (int)gridDim.x : n_eff);
@@ -386,7 +413,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         const int64_t hi = c < n_eff ? ((int64_t)(c + 1) * total) / n_eff : 0;
         // pass 2: prefix sums, segments, and (block 0) the prefix array for the merge kernel
         int run = 0, nseg = 0;
-        for (int base = 0; base < p.batch; base += 32) {
+        for (int base = 0; base < p.batch && total_real >= 0; base += 32) {
             int np = 0, fp = 0, le;
             const int b = base + lane;
             if (base == 0) np = np_first;
@@ -413,7 +440,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             nseg += __popc(mask);
             run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        if (lane == 0) {
+        if (lane == 0 && total_real >= 0) {
             if (c == 0) {
                 p.page_prefix[p.batch] = run;
                 p.header[1] = n_eff;
@@ -437,6 +464,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
         if (warp > kConsumerWarps) return;
         // =============================== producer warp ======================================
         int st = 0, round = 0;
+        bool bad_page = false;
         const uint64_t stream_policy = l2_policy_evict_first();  // the cache is read once per launch
         for (int sg = 0; sg < nseg && !abort_flag; sg++) {
             const int b = seg_seq[sg];
@@ -447,7 +475,11 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
             constexpr int kIdBlock = (32 / PPS) * PPS;  // page ids fetched per round: a whole number of stages
             for (int base = p0; base < p1; base += kIdBlock) {
                 const int mine = base + lane;
-                const int my_page = mine < p1 ? p.page_indices[tbl + first_page + mine] : 0;
+                int my_page = mine < p1 ? p.page_indices[tbl + first_page + mine] : 0;
+                if ((uint64_t)(int64_t)my_page >= (uint64_t)p.num_blocks) {  // never form an address from it
+                    my_page = 0;
+                    bad_page = true;
+                }
                 const int cnt = (p1 - base) < kIdBlock ? (p1 - base) : kIdBlock;
                 for (int j = 0; j < cnt; j += PPS) {
                     const int np = (cnt - j) < PPS ? (cnt - j) : PPS;
@@ -484,6 +516,7 @@ decode_paged_kernel(const __grid_constant__ DecodeParams p) {
                 if (abort_flag) break;
             }
         }
+        if (bad_page) atomicExch(&p.header[0], kStatusBadPage);
         return;
     }
 
@@ -747,6 +780,7 @@ struct MergeParams {
     // every rank owns an exchange buffer (ExchangeLayout) that all ranks have mapped.
     int xmode;                       // 0 none, 1 push this rank's partial to all ranks, 2 wait for all ranks and merge
     int xrank, xworld;
+    int xspin;                       // polls (256 ns apart) the wait for a peer may take before it gives up
     int64_t xrows;                   // output rows (batch x queries x heads) of one rank's partial
     unsigned char* xbuf[kMaxExchangeRanks];  // xbuf[r] = rank r's exchange buffer as mapped here
 };
@@ -811,7 +845,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
             for (int w = 0; w < p.xworld && ok; w++) {
                 int spins = 0;
                 while ((int32_t)(ld_acquire_sys(flags + w) - xepoch) < 0) {
-                    if (++spins > kExchangeSpinLimit) { ok = 0; break; }
+                    if (++spins > p.xspin) { ok = 0; break; }
                     __nanosleep(256);
                 }
             }
@@ -966,6 +1000,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
 int device_sm_count(int* out);
 
 static thread_local cudaEvent_t g_events[3] = {nullptr, nullptr, nullptr};
+static int g_exchange_spin_limit = kExchangeSpinLimit;
 
 struct WorkspaceLayout {
     size_t header, prefix, lse, o, total;
@@ -1065,6 +1100,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
                "kv_cache must be 16-byte and workspace 256-byte aligned");
     TQ_REQUIRE(kv_begin >= 0 && kv_begin % kPageTokens == 0, TQ_ERR_INVALID, "kv_begin must be a multiple of 16");
     TQ_REQUIRE(page_indptr || max_pages > 0, TQ_ERR_INVALID, "max_pages must be positive for a dense block table");
+    TQ_REQUIRE(num_blocks >= 1, TQ_ERR_INVALID, "the cache has no pages (num_blocks = %lld)", (long long)num_blocks);
     int ctas = 0;
     int rc = resolve_ctas(num_ctas, &ctas);
     if (rc != TQ_OK) return rc;
@@ -1086,6 +1122,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     p.partial_lse = reinterpret_cast<float*>(ws + w.lse);
     p.partial_o = reinterpret_cast<float*>(ws + w.o);
     p.slab_bytes = num_blocks * (int64_t)block_size * num_kv_heads * slot_bytes;
+    p.num_blocks = num_blocks;
     p.kv_begin = kv_begin;
     p.kv_end = kv_end;
     p.batch = batch;
@@ -1157,6 +1194,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
             m.xrank = x->rank;
             m.xworld = x->world;
             m.xrows = (int64_t)batch * nq * real_q_heads;
+            m.xspin = g_exchange_spin_limit;
             for (int w = 0; w < x->world; w++) m.xbuf[w] = static_cast<unsigned char*>(x->bufs[w]);
         }
         // parts per sequence: about (blocks x page lanes) / batch; many of them -> the wide merge
@@ -1191,6 +1229,8 @@ extern "C" int tq_debug_set_decode_events(void* ev_start, void* ev_mid, void* ev
     tq::g_events[2] = static_cast<cudaEvent_t>(ev_end);
     return TQ_OK;
 }
+
+extern "C" int tq_decode_max_query_columns(void) { return 8; }
 
 extern "C" size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads,
                                             int head_dim, int num_ctas) {
@@ -1232,6 +1272,11 @@ extern "C" int tq_decode_paged_multi(const void* q, int q_dtype, int batch, int 
                              num_blocks, block_size, slot_bytes, page_indices, page_indptr, max_pages,
                              seq_lens, kv_begin, kv_end, signs, sm_scale, workspace, workspace_bytes, out,
                              out_dtype, out_lse, rotated_partial ? 1 : 0, num_ctas, stream);
+}
+
+extern "C" int tq_set_exchange_wait_limit(int polls) {
+    tq::g_exchange_spin_limit = polls > 0 ? polls : tq::kExchangeSpinLimit;
+    return TQ_OK;
 }
 
 extern "C" size_t tq_exchange_bytes(int64_t rows, int world) {
@@ -1358,4 +1403,14 @@ extern "C" int tq_decode_paged_static(const void* q, int q_dtype, int batch, int
                          block_size, slot_bytes, page_indices, page_indptr, max_pages, seq_lens, 0, -1,
                          signs, sm_scale, scratch, kStaticScratchBytes, out, out_dtype, out_lse, 0, ctas,
                          stream);
+}
+
+extern "C" int tq_decode_static_status(int32_t* status_out, void* stream) {
+    using namespace tq;
+    TQ_REQUIRE(status_out != nullptr, TQ_ERR_INVALID, "null pointer");
+    void* scratch = nullptr;
+    int rc = static_scratch_pointer(&scratch);
+    if (rc != TQ_OK) return rc;
+    TQ_CUDA(cudaMemcpyAsync(status_out, scratch, sizeof(int32_t), cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+    return TQ_OK;
 }

@@ -31,6 +31,7 @@ constexpr int kDqSlotCodes = 64;
 struct DequantParams {
     const uint8_t* kv_cache;
     int64_t slab_bytes;
+    int64_t num_blocks;           // page ids outside [0, num_blocks) are skipped and counted
     const int32_t* page_indices;
     const int32_t* page_indptr;   // null: dense block table [batch][max_pages]
     const int32_t* seq_lens;
@@ -114,6 +115,10 @@ struct DqStage {
 // What one warp needs of one work item (the K or V half of one page): its rows' codes and norm
 // are fetched one item ahead, so that the loads of the next page are in flight during the
 // arithmetic of the current one.
+// Page halves skipped because the page id lay outside the cache or the sequence was longer than
+// its page list; read back by tq_fault_counts.
+static __device__ int32_t g_dequant_skipped = 0;
+
 struct DqItem {
     uint4 c0, c1;
     float norm;
@@ -136,7 +141,12 @@ __device__ __forceinline__ void fetch_item(const DequantParams& p, int64_t item,
     const int tok0 = page_in_seq * p.block_size;
     if (tok0 >= len) return;
     const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
-    const int64_t page = p.page_indices[tbl + page_in_seq];
+    const bool listed = !p.page_indptr || tbl + page_in_seq < (int64_t)p.page_indptr[b + 1];
+    const int64_t page = listed ? (int64_t)p.page_indices[tbl + page_in_seq] : -1;
+    if ((uint64_t)page >= (uint64_t)p.num_blocks) {  // never form an address from it: the rows stay unwritten
+        if (warp == 0 && lane == 0 && which == 0) atomicAdd(&g_dequant_skipped, 1);
+        return;
+    }
     const int ntok = len - tok0 < p.block_size ? len - tok0 : p.block_size;
     it.rows = ntok * p.H;
     it.which = which;
@@ -305,6 +315,11 @@ static int launch_dequant(const DequantParams& p, dim3 grid, cudaStream_t stream
 }
 void host_codebook(int dim, int bits, float* centroids, float* boundaries);
 
+int dequant_fault_count(int32_t* out) {
+    TQ_CUDA(cudaMemcpyFromSymbol(out, g_dequant_skipped, sizeof(int32_t)));
+    return TQ_OK;
+}
+
 }  // namespace tq
 
 extern "C" int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads,
@@ -328,6 +343,7 @@ extern "C" int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int bl
     DequantParams p{};
     p.kv_cache = static_cast<const uint8_t*>(kv_cache);
     p.slab_bytes = num_blocks * block_size * (int64_t)num_kv_heads * slot_bytes;
+    p.num_blocks = num_blocks;
     p.page_indices = page_indices;
     p.page_indptr = page_indptr;
     p.seq_lens = seq_lens;

@@ -24,8 +24,12 @@ struct PageMoveParams {
     const int32_t* page_ids;
     int64_t slab_bytes;   // K slab -> V slab
     int64_t half_bytes;   // one page half in the cache: block_size * H * slot_bytes
+    int64_t num_blocks;   // page ids outside [0, num_blocks) are skipped and counted
     int n_pages, slots_per_half, slot_bytes;
 };
+
+// Pages skipped because their id lay outside the cache; read back by tq_fault_counts.
+static __device__ int32_t g_pages_skipped = 0;
 
 // One block per (page, K / V); thread i moves word i % 17 of slot i / 17.
 template <bool GATHER>
@@ -34,6 +38,10 @@ __global__ void __launch_bounds__(256) page_move_kernel(const __grid_constant__ 
     grid_dependency_wait();
     const int n = blockIdx.x, which = blockIdx.y;
     const int64_t page = p.page_ids[n];
+    if ((uint64_t)page >= (uint64_t)p.num_blocks) {
+        if (threadIdx.x == 0 && which == 0) atomicAdd(&g_pages_skipped, 1);
+        return;
+    }
     uint8_t* cache_half = p.kv_cache + (size_t)which * p.slab_bytes + (size_t)page * p.half_bytes;
     uint8_t* packed_half = p.packed + ((size_t)n * 2 + which) * (size_t)p.slots_per_half * kPagePayload;
     const int words = p.slots_per_half * kPayloadWords;
@@ -64,6 +72,7 @@ static int page_move(bool gather, void* kv_cache, int64_t num_blocks, int block_
     p.page_ids = page_ids;
     p.half_bytes = (int64_t)block_size * num_kv_heads * slot_bytes;
     p.slab_bytes = num_blocks * p.half_bytes;
+    p.num_blocks = num_blocks;
     p.n_pages = n_pages;
     p.slots_per_half = block_size * num_kv_heads;
     p.slot_bytes = slot_bytes;
@@ -71,6 +80,11 @@ static int page_move(bool gather, void* kv_cache, int64_t num_blocks, int block_
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (gather) TQ_CUDA(launch_serialized(page_move_kernel<true>, grid, dim3(256), 0, s, p));
     else TQ_CUDA(launch_serialized(page_move_kernel<false>, grid, dim3(256), 0, s, p));
+    return TQ_OK;
+}
+
+int pages_fault_count(int32_t* out) {
+    TQ_CUDA(cudaMemcpyFromSymbol(out, g_pages_skipped, sizeof(int32_t)));
     return TQ_OK;
 }
 

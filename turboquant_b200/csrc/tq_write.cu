@@ -44,6 +44,7 @@ struct WriteParams {
     const void* slot_mapping;
     int64_t num_tokens;
     int64_t slab_bytes;       // bytes between the K slab and the V slab
+    int64_t total_slots;      // num_blocks * block_size: a slot at or beyond it is dropped and counted
     int num_kv_heads;
     int head_shift;           // log2(num_kv_heads) when that is a power of two, else -1
     int block_size;
@@ -114,6 +115,10 @@ __device__ __forceinline__ void split_row(int64_t r, int H, int head_shift, int6
         h = (int)(r - t * H);
     }
 }
+
+// Rows dropped because their slot lay outside the cache (a stale or garbage slot id must never
+// become a store address); read back by tq_fault_counts.
+static __device__ int32_t g_write_dropped = 0;
 
 template <typename T>
 struct RowLoad;
@@ -376,6 +381,10 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
             for (int j = 0; j < 16; j++) *reinterpret_cast<uint16_t*>(orow + 4 * j + 2 * m) = 0xffffu;
         }
         __syncwarp();
+        if (row_ok && slot >= p.total_slots) {
+            if (m == 0 && h == 0) atomicAdd(&g_write_dropped, 1);  // once per token
+            slot = -1;
+        }
         if (row_ok && slot >= 0) {
             // slot = block * block_size + entry and the cache is [block][entry][head][slot_bytes]
             uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)slot * H + h) * p.slot_bytes;
@@ -415,6 +424,11 @@ static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream)
 
 int device_sm_count(int* out);
 
+int write_fault_count(int32_t* out) {
+    TQ_CUDA(cudaMemcpyFromSymbol(out, g_write_dropped, sizeof(int32_t)));
+    return TQ_OK;
+}
+
 }  // namespace tq
 
 extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_size,
@@ -452,6 +466,7 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     p.slot_mapping = slot_mapping;
     p.num_tokens = num_tokens;
     p.slab_bytes = num_blocks * block_size * (int64_t)num_kv_heads * slot_bytes;
+    p.total_slots = num_blocks * (int64_t)block_size;
     p.num_kv_heads = num_kv_heads;
     p.head_shift = -1;
     for (int sft = 0; sft < 16; sft++)

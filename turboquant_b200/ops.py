@@ -57,9 +57,17 @@ def _decode(q, kv_cache, indices, indptr, seq_lens, num_kv_heads, page_size, hea
     if padded_dim != 128:
         raise _cabi.TurboQuantError("decode supports padded head size 128 only")  # as the reference's v5 op
     b, hq, _ = q.shape
+    # The op runs inside CUDA graphs: a silent cast or copy here would be an extra kernel and an
+    # allocation on every replay.  The reference passes int32 tables and a contiguous q
+    # (turboquant/vllm_backend_fused.py:396-402); anything else is refused.
+    for t, name in ((indices, "indices"), (indptr, "indptr"), (seq_lens, "seq_lens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise _cabi.TurboQuantError(f"{name} must be a contiguous int32 tensor, got {t.dtype}")
+    if not q.is_contiguous():
+        raise _cabi.TurboQuantError("q must be contiguous")
     ws = _workspace(b, hq, num_kv_heads, q.device)
-    _cabi.decode_paged(q.contiguous(), _bytes(kv_cache), indices.to(torch.int32), seq_lens.to(torch.int32), signs,
-                       float(sm_scale), ws, o_ws, page_indptr=indptr.to(torch.int32), max_pages=1)
+    _cabi.decode_paged(q, _bytes(kv_cache), indices, seq_lens, signs, float(sm_scale), ws, o_ws,
+                       page_indptr=indptr, max_pages=1)
     return o_ws
 
 
