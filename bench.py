@@ -16,8 +16,17 @@ Prints ONE JSON line (rank 0).  `value` is timed on the device with inputs resid
 public API with host buffers: the step's queries and new K/V rows are copied from pinned host
 memory, the new rows are written into the cache, and the outputs are copied back, all inside
 the timed region.  `roofline` is for the decode kernel alone, timed per launch with CUDA events
-recorded by the library around that kernel.  `cpu_baseline` / `--impl reference` time the CPU
-oracle (a C restatement of the reference's torch CPU path) on a bounded sample of the same data.
+recorded by the library around that kernel.  `parity` compares layer 0's output of the timed
+workload with the CPU oracle (the run fails if the bar is missed).  `cpu_baseline` / `--impl
+reference` time the reference's CPU path on full 32768-token sequence passes of the same data:
+its torch calls restated (oracle/torch_cpu_path.py, all torch threads) and, beside it under
+`port`, the C restatement on all host threads.
+
+Further sections of the same line: `mixed` (64 mixed-length sequences, sharded over the GPUs by
+sequence) and `kv_split` (one 1,048,576-token sequence with 8 queries, KV axis split over the
+GPUs, partials exchanged by the kernels themselves and, for comparison, by an NCCL all-gather),
+each with its own oracle parity check; with N > 1 also `strong` (the stated batch of 8 split
+over the GPUs by sequence and by KV head).  `--sections none` leaves them out.
 """
 from __future__ import annotations
 
@@ -57,6 +66,8 @@ def parse():
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="config4 on several GPUs: partials exchanged by the kernels themselves (peer stores + "
                          "flags) or by an NCCL all-gather")
+    ap.add_argument("--sections", default="all",
+                    help="comma list of the extra sections of the config-1 line: mixed, kv_split, strong; all | none")
     ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4", "sweep"],
                     help="config1 (default, the headline): batch 8 x 32k per GPU; config3: 64 mixed lengths sharded by "
                          "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge")
@@ -151,6 +162,67 @@ def cpu_decode_rate(cache_np, block_table_np, q_np, signs_np, ctx_sample: int, t
     return threads * reps * ctx_sample * HKV / dt, dt
 
 
+def cpu_model() -> str:
+    try:
+        for ln in Path("/proc/cpuinfo").read_text().splitlines():
+            if ln.startswith("model name"):
+                return ln.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def torch_decode_rate(cache_np, block_table_np, q_np, signs_np, ctx: int, passes: int):
+    """KV token-heads per second of the reference's torch CPU path (oracle/torch_cpu_path.py), one
+    full `ctx`-token sequence per pass, torch's own intra-op threads; returns (rate, seconds)."""
+    from oracle import torch_cpu_path, tq_oracle
+    cen, _ = tq_oracle.codebook(D, 4)
+    cache = torch.from_numpy(cache_np)
+    bt = torch.from_numpy(block_table_np)
+    q = torch.from_numpy(q_np)
+    signs = torch.from_numpy(signs_np)
+    cen = torch.from_numpy(cen)
+    nseq = q.shape[0]
+    lens = [ctx]
+    t0 = time.perf_counter()
+    for i in range(passes):
+        b = i % nseq
+        torch_cpu_path.decode_attention(q[b:b + 1], cache, bt[b:b + 1], lens, signs, cen, 1.0 / math.sqrt(D))
+    dt = time.perf_counter() - t0
+    return passes * ctx * HKV / dt, dt
+
+
+def torch_write_rate(k, v, slots, signs, num_blocks: int, reps: int = 1):
+    """Tokens per second of the reference's torch CPU quantizer + pack + scatter."""
+    from oracle import torch_cpu_path, tq_oracle
+    _, bnd = tq_oracle.codebook(D, 4)
+    bnd = torch.from_numpy(bnd)
+    cache = torch.zeros((2, num_blocks, PAGE, HKV, SLOT), dtype=torch.uint8)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        torch_cpu_path.write_kv_cache(cache, k, v, signs, bnd, slots)
+    dt = time.perf_counter() - t0
+    return k.shape[0] * reps / dt, dt
+
+
+def oracle_parity(got, want, what: str) -> dict:
+    """The parity bar of the tests, evaluated inside the benchmark: per element
+    |got - want| <= 2e-3 + 1e-2 |want| and relative (Frobenius) <= 1e-2 must hold or the run fails;
+    the strict reading (max-abs <= 2e-3) is reported beside it."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    err = np.abs(got - want)
+    rel = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+    ok = bool((err <= 2e-3 + 1e-2 * np.abs(want)).all() and rel <= 1e-2)
+    res = {"against": "CPU oracle (dequant-attention restatement) on the same bytes", "what": what,
+           "max_abs": float(err.max()), "rel": rel, "strict_2e-3": bool(err.max() <= 2e-3), "ok": ok,
+           "ref_max_abs": float(np.abs(want).max()), "ref_rms": float(np.sqrt((want ** 2).mean()))}
+    if not ok:
+        print(json.dumps({"parity_failure": res}), flush=True)
+        raise SystemExit(f"parity bar missed: {res}")
+    return res
+
+
 def cpu_write_rate(k_np, v_np, slots_np, signs_np, num_blocks: int, threads: int, reps: int = 1):
     """Tokens per second of the CPU cache write (the C port of the torch quantizer + pack + scatter),
     `threads` chunks of the sample in parallel (ctypes releases the GIL)."""
@@ -183,32 +255,55 @@ def synthetic_host_cache(ctx: int, batch: int, seed: int):
     return cache, case.block_table.numpy(), case.q.float().numpy(), signs
 
 
+def cpu_arm(cache_np, bt_np, q_np, signs_np, ctx: int, layers: int, torch_passes: int, port_reps: int):
+    """Both CPU figures on full `ctx`-token sequence passes of one layer's quantized cache,
+    as tokens/s of the whole `layers`-layer step: the torch path (the named baseline) and the C port."""
+    threads = os.cpu_count() or 1
+    per_token = ctx * HKV * layers                        # KV token-heads one decode token attends
+    t_rate, t_dt = torch_decode_rate(cache_np, bt_np, q_np, signs_np, ctx, torch_passes)
+    p_rate, p_dt = cpu_decode_rate(cache_np, bt_np, q_np, signs_np, ctx, threads, port_reps)
+    scaled = f"x {HKV} KV heads of one layer's config-1 cache, scaled to {layers} layers per token"
+    return {
+        "value": t_rate / per_token, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "torch-restatement",
+        "sample": f"{torch_passes} sequence passes x {ctx} tokens {scaled} ({t_dt:.2f} s)",
+        "cpu": cpu_model(), "host_cores": threads, "torch": torch.__version__,
+        "port": {"value": p_rate / per_token, "unit": "tokens/s", "cores": threads, "kind": "port",
+                 "sample": f"{threads * port_reps} sequence passes x {ctx} tokens {scaled} ({p_dt:.2f} s)"},
+    }
+
+
 def run_reference(args):
-    """The reference's CPU implementation of the path (its torch modules cannot travel to the
-    GPU box, so the oracle port stands in), all host threads, bounded sample per step."""
+    """The reference's CPU implementation of the path on the box's host cores: its torch calls
+    restated (the reference's own modules cannot travel to the GPU box), one full 32768-token
+    sequence pass of one layer per step, torch's intra-op threads; the C port beside it."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
-    ctx_s = min(8192, args.ctx)
-    cache, bt, q, signs = synthetic_host_cache(ctx_s, min(args.batch, 8), seed=1)
+    ctx = args.ctx
+    cache, bt, q, signs = synthetic_host_cache(ctx, 2, seed=1)
     rates = []
     for i in range(args.warmup + args.steps):
-        r, dt = cpu_decode_rate(cache, bt, q, signs, ctx_s, threads)
+        r, dt = torch_decode_rate(cache, bt, q, signs, ctx, 1)
         if i >= args.warmup:
             rates.append((r, dt))
     rate = statistics.median(r for r, _ in rates)
-    per_token = args.ctx * HKV * args.layers           # KV token-heads one decode token attends
+    per_token = ctx * HKV * args.layers
     value = rate / per_token
-    sample = (f"{threads} sequences x {ctx_s} tokens x {HKV} KV heads of config-1-shaped quantized cache per step "
-              f"(one layer), scaled to ctx {args.ctx} x {args.layers} layers per token")
+    threads = os.cpu_count() or 1
+    p_rate, p_dt = cpu_decode_rate(cache, bt, q, signs, ctx, threads, 1)
+    sample = (f"one sequence pass x {ctx} tokens x {HKV} KV heads of config-1-shaped quantized cache per step "
+              f"(one layer), scaled to {args.layers} layers per token")
     line = {
         "impl": "reference", "metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * statistics.median(dt for _, dt in rates), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args), "note": "CPU arm: C port of the reference torch CPU path"},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": workload_name(args), "global_batch": args.batch * args.gpus,
+                   "note": "CPU arm: the reference's torch CPU path (restated call for call), torch intra-op threads"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "torch-restatement",
+                         "sample": sample, "cpu": cpu_model(), "host_cores": threads, "torch": torch.__version__,
+                         "port": {"value": p_rate / per_token, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                  "sample": f"{threads} sequence passes x {ctx} tokens ({p_dt:.2f} s)"}},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -218,6 +313,213 @@ def run_reference(args):
 def workload_name(args):
     return (f"config1: Qwen3-8B-shaped decode layer, batch {args.batch}/GPU x ctx {args.ctx}, {HQ}q/{HKV}kv heads, "
             f"head_dim {D}, bf16 q, 16-token pages (seeded random permutation), {args.layers} layers per step")
+
+
+# ------------------------------------------------------------------------------------------------
+# Extra sections of the config-1 line: the other BASELINE configs and the multi-GPU splits
+# ------------------------------------------------------------------------------------------------
+def _dist_max(ms: float, world: int, dev) -> float:
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def _time_steps(fn, steps: int, world: int, dev) -> float:
+    """ms per step: barrier + synchronize on both sides, CUDA events, max over ranks."""
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = _dist_max(e0.elapsed_time(e1), world, dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    return ms / steps
+
+
+def _fill_sequence(attn, cache, block_table_row, n_tokens, gen, dev, chunk=65536, heads=HKV):
+    """Quantize seeded N(0,1) K/V for one sequence into its pages with the cache-write kernel."""
+    for t0 in range(0, n_tokens, chunk):
+        n = min(chunk, n_tokens - t0)
+        k = torch.randn(n, heads, D, generator=gen, device=dev).to(torch.bfloat16)
+        v = torch.randn(n, heads, D, generator=gen, device=dev).to(torch.bfloat16)
+        tok = torch.arange(t0, t0 + n, device=dev)
+        slots = block_table_row.long()[tok // PAGE] * PAGE + tok % PAGE
+        attn.write(k, v, cache, slots)
+
+
+def section_mixed(args, rank, world, dev, peak):
+    """Config 3: 64 sequences, lengths log-uniform in [512, 131072] (seed 3), one layer, sharded
+    over the ranks by sequence (longest first): no collective on the data path.  Every rank
+    checks its own shard against the oracle."""
+    from oracle import tq_oracle
+    from turboquant_b200 import synthetic
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    from turboquant_b200.parallel import shard_sequences
+    lens_all = synthetic.mixed_lengths(seed=3, n=64)
+    shards = shard_sequences(lens_all, world)
+    lens = [lens_all[i] for i in shards[rank]]
+    attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, num_ctas=args.num_ctas)
+    bt_cpu, _, nb = synthetic.paged_layout(lens, seed=3 + rank)
+    bt = bt_cpu.to(dev)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3 + 1000 * rank)
+    ncache = 2   # alternated so that consecutive launches stream different memory (each far larger than L2)
+    caches = [torch.zeros(kv_cache_shape(nb, PAGE, HKV, D), dtype=torch.uint8, device=dev) for _ in range(ncache)]
+    for c in caches:
+        for b, n in enumerate(lens):
+            _fill_sequence(attn, c, bt[b], n, gen, dev)
+    q = torch.randn(len(lens), HQ, D, generator=gen, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    state = {"i": 0}
+
+    def step():
+        attn.decode(q, caches[state["i"] % ncache], bt, sl, out)
+        state["i"] += 1
+    for _ in range(4):
+        step()
+    steps = max(args.steps, 10)
+    ms = _time_steps(step, steps, world, dev)
+    attn.decode(q, caches[0], bt, sl, out)
+    torch.cuda.synchronize()
+    status = attn.status(len(lens), dev)
+    want = tq_oracle.decode_paged_parallel(q.float().cpu().numpy(), caches[0].cpu().numpy(), bt_cpu.numpy(),
+                                           np.asarray(lens, np.int32), attn.signs(dev).cpu().numpy(), 1.0 / math.sqrt(D),
+                                           threads=max(1, (os.cpu_count() or 1) // world))
+    par = oracle_parity(out.float().cpu().numpy(), want, f"rank {rank}'s shard, all {len(lens)} sequences")
+    worst = _dist_max(par["max_abs"], world, dev)
+    loads = [sum(lens_all[i] for i in sh) for sh in shards]
+    alg = sum(lens_all) * HKV * ALG_BYTES_PER_TOKEN_HEAD
+    ach = alg / (ms * 1e-3) / 1e9
+    del caches
+    torch.cuda.empty_cache()
+    return {"workload": "config3: 64 sequences, lengths log-uniform in [512, 131072] (seed 3), one layer, sharded over "
+                        "the GPUs by sequence (greedy by length), no collective",
+            "total_tokens": sum(lens_all), "ms_per_step": ms, "tokens_per_s": 64 / (ms * 1e-3), "steps": steps,
+            "achieved_GBps": ach, "frac_of_n_peak": ach / (peak * world), "algorithmic_bytes": alg,
+            "load_imbalance_max_over_mean": max(loads) / (sum(loads) / world), "status": status,
+            "parity": dict(par, max_abs_over_ranks=worst), "scaling": "strong",
+            "limit": "whole call (decode + merge); bounded by the most loaded rank and the fixed cost of a call"}
+
+
+def section_kv_split(args, rank, world, dev, peak):
+    """Config 4: one sequence of 1,048,576 tokens, 8 decode queries, one layer.  The KV axis is split
+    contiguously over the ranks; every rank decodes its range for all queries, the rotated partials
+    + LSE are exchanged (kernel-side: peer stores + flags; and through an NCCL all-gather) and merged
+    on every rank.  Parity: every rank runs the oracle over its own range for two of the queries,
+    the oracle partials are merged on rank 0 and compared with the GPU result."""
+    from oracle import tq_oracle
+    from turboquant_b200 import _cabi
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    from turboquant_b200.parallel import kv_ranges, kv_split_decode
+    total, nq = 1_048_576, 8
+    a, b = kv_ranges(total, world)[rank]
+    n_local = b - a
+    attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, num_ctas=args.num_ctas)
+    pages = (n_local + PAGE - 1) // PAGE
+    bt_row = torch.randperm(pages, generator=torch.Generator().manual_seed(4 + rank)).to(torch.int32).to(dev)
+    cache = torch.zeros(kv_cache_shape(pages, PAGE, HKV, D), dtype=torch.uint8, device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4 + 1000 * rank)
+    _fill_sequence(attn, cache, bt_row, n_local, gen, dev)
+    qgen = torch.Generator(device=dev)
+    qgen.manual_seed(4)                                   # the same queries on every rank
+    share = min(nq, _cabi.decode_max_queries_per_seq(HQ, HKV))   # queries that ride one pass over the KV
+    rows = nq // share
+    q = torch.randn(rows, share, HQ, D, generator=qgen, device=dev).to(torch.bfloat16)
+    bt = bt_row.unsqueeze(0).expand(rows, -1).contiguous()  # every row is the same sequence
+    sl = torch.full((rows,), n_local, dtype=torch.int32, device=dev)
+    out = torch.empty_like(q)
+    steps = max(args.steps, 10)
+    res = {"workload": "config4: one 1,048,576-token sequence, 8 decode queries, one layer, KV axis split contiguously "
+                       "over the GPUs, partial (o, lse) exchanged and merged on every GPU",
+           "passes_over_the_kv": rows, "queries_per_pass": share, "steps": steps,
+           "exchange_bytes_per_rank": nq * HQ * (D + 1) * 4, "scaling": "strong"}
+    alg = total * HKV * ALG_BYTES_PER_TOKEN_HEAD
+
+    def rate(ms):
+        ach = alg / (ms * 1e-3) / 1e9
+        return {"ms_per_step": ms, "tokens_per_s": nq / (ms * 1e-3), "achieved_GBps": ach,
+                "frac_of_n_peak": ach / (peak * world)}
+    if world > 1:
+        from turboquant_b200.parallel import KVSplitExchange
+        ex = KVSplitExchange(attn, rows, share, dev)
+        for _ in range(4):
+            ex.decode(q, cache, bt, sl, out)
+        res["kernel_exchange"] = rate(_time_steps(lambda: ex.decode(q, cache, bt, sl, out), steps, world, dev))
+        out_nccl = torch.empty_like(q)
+        for _ in range(4):
+            kv_split_decode(attn, q, cache, bt, sl, out_nccl)
+        res["nccl_all_gather"] = rate(_time_steps(lambda: kv_split_decode(attn, q, cache, bt, sl, out_nccl), steps, world, dev))
+        ex.decode(q, cache, bt, sl, out)
+        torch.cuda.synchronize()
+        res["exchange_status"] = int(_dist_max(float(ex.status()), world, dev))
+        res["nccl_equals_kernel_exchange"] = bool(torch.equal(out, out_nccl))
+        res.update(res["kernel_exchange"])
+    else:
+        for _ in range(4):
+            attn.decode(q, cache, bt, sl, out)
+        res.update(rate(_time_steps(lambda: attn.decode(q, cache, bt, sl, out), steps, world, dev)))
+        torch.cuda.synchronize()
+    res["decode_status"] = int(_dist_max(float(attn.status(rows, dev, share)), world, dev))
+    # ---- parity of two of the queries: oracle partial per rank (natural-log LSE), merged on rank 0
+    pq = [0, nq - 1]
+    qsel = q.view(nq, HQ, D)[pq].float().cpu().numpy()                      # [2, 32, 128]
+    qv = qsel.reshape(len(pq), HKV, HQ // HKV, D).transpose(1, 0, 2, 3).reshape(1, len(pq) * HQ, D)
+    po, pl = tq_oracle.decode_paged_parallel(qv, cache.cpu().numpy(), bt_row.cpu().numpy()[None],
+                                             np.array([n_local], np.int32), attn.signs(dev).cpu().numpy(),
+                                             1.0 / math.sqrt(D), threads=max(1, (os.cpu_count() or 1) // world),
+                                             chunk_tokens=16384, return_lse=True)
+    po_t, pl_t = torch.from_numpy(po).to(dev), torch.from_numpy(pl).to(dev)
+    if world > 1:
+        import torch.distributed as dist
+        go = [torch.empty_like(po_t) for _ in range(world)]
+        gl = [torch.empty_like(pl_t) for _ in range(world)]
+        dist.all_gather(go, po_t)
+        dist.all_gather(gl, pl_t)
+        po_all = torch.stack(go).cpu().numpy()
+        pl_all = torch.stack(gl).cpu().numpy()
+    else:
+        po_all, pl_all = po[None], pl[None]
+    if rank == 0:
+        merged, _ = tq_oracle.merge_partials(po_all, pl_all)
+        want = merged.reshape(HKV, len(pq), HQ // HKV, D).transpose(1, 0, 2, 3).reshape(len(pq), HQ, D)
+        got = out.view(nq, HQ, D)[pq].float().cpu().numpy()
+        res["parity"] = oracle_parity(got, want, f"queries {pq} of 8, all 1,048,576 tokens, oracle partials merged over the ranks")
+    # ---- the same sequence whole on one GPU, same run (rank 0), for the speed-up
+    if world > 1:
+        import torch.distributed as dist
+        if rank == 0:
+            pages1 = total // PAGE
+            bt1 = torch.randperm(pages1, generator=torch.Generator().manual_seed(4)).to(torch.int32).to(dev)
+            cache1 = torch.zeros(kv_cache_shape(pages1, PAGE, HKV, D), dtype=torch.uint8, device=dev)
+            _fill_sequence(attn, cache1, bt1, total, gen, dev)
+            bt1r = bt1.unsqueeze(0).expand(rows, -1).contiguous()
+            sl1 = torch.full((rows,), total, dtype=torch.int32, device=dev)
+            for _ in range(3):
+                attn.decode(q, cache1, bt1r, sl1, out_nccl)
+            ms1 = _time_steps(lambda: attn.decode(q, cache1, bt1r, sl1, out_nccl), steps, 1, dev)
+            res["one_gpu_same_run"] = rate(ms1)
+            res["one_gpu_same_run"]["frac_of_n_peak"] *= world          # one GPU's peak
+            res["speedup_over_one_gpu"] = ms1 / res["ms_per_step"]
+            del cache1
+        dist.barrier()
+        res["limit"] = ("per rank: 1/N of the KV (the streaming part scales) + the fixed cost of a call (plan, query rotation, "
+                        "first stage, merge: about 20 us) + the exchange: peer stores of 132 KB to every rank, a release flag "
+                        "per source, then the flag-gated merge")
+    del cache
+    torch.cuda.empty_cache()
+    return res
 
 
 # ------------------------------------------------------------------------------------------------
@@ -404,17 +706,87 @@ def run_ours(args):
     alg_bytes = B * L * HKV * ALG_BYTES_PER_TOKEN_HEAD
     peak, peak_src = measured_peak()
     achieved = alg_bytes / (dec_avg * 1e-3) / 1e9
-    # DRAM traffic per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this
-    # kernel on this workload (profiles/decode_paged_kernel_config1_layer.md: 335.7 MB + 3.3 MB for
-    # batch 8 x ctx 32768), scaled by the tokens of the launch.  The physical slots are 160 B per 136
-    # algorithmic bytes, so 1.18x is the floor; the rest is the partial outputs.
-    traffic = 339.09e6 * (B * L) / (8 * 32768)
+    # DRAM traffic per launch is not measured by this run: it is dram__bytes_read.sum + dram__bytes_write.sum
+    # of one ncu capture of this kernel on this very shape (335.7 MB + 3.3 MB at batch 8 x ctx 32768) and is
+    # only reported for that shape.  The physical slots are 160 B per 136 algorithmic bytes, so 1.18x the
+    # algorithmic bytes is the floor; the rest is the partial outputs.
+    traffic = 339.09e6 if (B, L) == (8, 32768) else None
     roofline = {"bound": "hbm", "kernel": "decode_paged_kernel<8>", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-                "traffic": traffic, "expected_min_traffic": alg_bytes * 160.0 / 136.0,
+                "traffic": traffic, "traffic_source": "ncu capture of this kernel and shape (one launch, --clock-control none), "
+                                                      "not measured in this run",
+                "expected_min_traffic": alg_bytes * 160.0 / 136.0,
                 "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_ms": dec_avg,
                 "merge_avg_launch_ms": sum(mrg_ms) / len(mrg_ms),
                 "frac_whole_step": (alg_bytes * NL / (ms_step * 1e-3) / 1e9) / peak}
+
+    # ---- parity of the timed workload: layer 0's output against the oracle over the same bytes ----
+    parity = None
+    if rank == 0:
+        from oracle import tq_oracle
+        attn.decode(q_dev[0], caches[0], block_table, seq_lens, out_dev[0])
+        torch.cuda.synchronize()
+        want0 = tq_oracle.decode_paged_parallel(q_dev[0].float().cpu().numpy(), caches[0].cpu().numpy(),
+                                                block_table.cpu().numpy(), seq_lens.cpu().numpy(),
+                                                attn.signs(dev).cpu().numpy(), 1.0 / math.sqrt(D))
+        parity = oracle_parity(out_dev[0].float().cpu().numpy(), want0,
+                               f"layer 0 of the timed step: batch {B} x {L} tokens, bf16 output")
+        del want0
+
+    # ---- strong scaling of the stated batch: the same B sequences split over the GPUs ------------
+    wanted = {x.strip() for x in args.sections.split(",")} if args.sections not in ("all", "") else {"mixed", "kv_split", "strong"}
+    if args.sections == "none":
+        wanted = set()
+    strong = None
+    if world > 1 and "strong" in wanted and B % world == 0 and HKV % world == 0:
+        def graph_ms(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            side2 = torch.cuda.Stream(dev)
+            side2.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side2):
+                with torch.cuda.graph(g, stream=side2):
+                    fn()
+            torch.cuda.current_stream().wait_stream(side2)
+            g.replay()
+            torch.cuda.synchronize()
+            return timed(g.replay, args.steps) / args.steps
+        # (a) by sequence: this rank decodes B / world of its sequences, all KV heads
+        bs = B // world
+        bt_s, sl_s = block_table[rank * bs:(rank + 1) * bs].contiguous(), seq_lens[:bs].contiguous()
+        q_s, o_s = q_dev[:, rank * bs:(rank + 1) * bs].contiguous(), torch.empty(NL, bs, HQ, D, dtype=torch.bfloat16, device=dev)
+
+        def step_seq():
+            for layer in range(NL):
+                attn.decode(q_s[layer], caches[layer], bt_s, sl_s, o_s[layer])
+        ms_seq = graph_ms(step_seq)
+        # (b) by KV head: this rank holds HKV / world heads of every token of all B sequences
+        hk, hq = HKV // world, HQ // world
+        attn_h = TurboQuantPagedAttention(hq, D, 1.0 / math.sqrt(D), hk, seed=42, num_ctas=args.num_ctas)
+        caches_h = torch.zeros((NL,) + kv_cache_shape(nb, PAGE, hk, D), dtype=torch.uint8, device=dev)
+        for layer in range(NL):
+            for b in range(B):
+                _fill_sequence(attn_h, caches_h[layer], block_table[b], L, gen, dev, heads=hk)
+        q_h = torch.randn(NL, B, hq, D, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        o_h = torch.empty_like(q_h)
+
+        def step_head():
+            for layer in range(NL):
+                attn_h.decode(q_h[layer], caches_h[layer], block_table, seq_lens, o_h[layer])
+        ms_head = graph_ms(step_head)
+        del caches_h
+        torch.cuda.empty_cache()
+        strong = {"workload": f"the stated batch of {B} x ctx {L}, {NL} layers per step, split over {world} GPUs (total work fixed)",
+                  "one_gpu_ms_per_step_same_run": ms_step, "one_gpu_tokens_per_s": B / (ms_step * 1e-3),
+                  "by_sequence": {"sequences_per_gpu": bs, "ms_per_step": ms_seq, "tokens_per_s": B / (ms_seq * 1e-3),
+                                  "speedup": ms_step / ms_seq},
+                  "by_kv_head": {"kv_heads_per_gpu": hk, "ms_per_step": ms_head, "tokens_per_s": B / (ms_head * 1e-3),
+                                 "speedup": ms_step / ms_head},
+                  "scaling": "strong",
+                  "limit": "no collective on either split; what stays constant as the data per GPU shrinks is the fixed cost of "
+                           "a call (two launches, the device-side plan, query rotation, first stage, merge: about 20 us per layer)"}
 
     # ---- cache-write path (the prefill-quantization config): 32768 tokens x 8 KV heads, bf16 ------
     write = None
@@ -446,8 +818,13 @@ def run_ours(args):
             w_rate, w_dt = cpu_write_rate(wk[:nsample].float().cpu().numpy(), wv[:nsample].float().cpu().numpy(),
                                           wslots[:nsample].cpu().numpy(), attn.signs(dev).cpu().numpy(), wnb,
                                           os.cpu_count() or 1, w_reps)
-            write["cpu_baseline"] = {"value": w_rate, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
-                                     "sample": f"{w_reps} passes over the {nsample} tokens of the same case ({w_dt:.2f} s)"}
+            t_rate, t_dt = torch_write_rate(wk[:nsample].float().cpu(), wv[:nsample].float().cpu(), wslots[:nsample].cpu(),
+                                            attn.signs(dev).cpu(), wnb, 2)
+            write["cpu_baseline"] = {"value": t_rate, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                                     "kind": "torch-restatement",
+                                     "sample": f"2 passes over the {nsample} tokens of the same case ({t_dt:.2f} s)",
+                                     "port": {"value": w_rate, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                              "sample": f"{w_reps} passes over the {nsample} tokens of the same case ({w_dt:.2f} s)"}}
         del wk, wv, wcaches
         # ---- bulk dequantization of cached tokens (continuation of a prefill): layer caches of the
         # decode workload, first ctx_d tokens of every sequence -> dense bf16 K / V
@@ -475,35 +852,44 @@ def run_ours(args):
                    "tokens_per_s": B * ctx_d / (dt_[len(dt_) // 2] * 1e-3)}
         del dk, dv
 
+    # ---- host copy of what the CPU baseline needs, then the big caches can go -------------------
+    cpu_sample = None
+    if rank == 0 and not args.no_cpu_baseline:
+        pages_s = (L + PAGE - 1) // PAGE
+        # the sample attends all L tokens of every sequence of layer 0: the same bytes as the GPU
+        ids = block_table[:, :pages_s].long()
+        cpu_sample = (np.ascontiguousarray(caches[0][:, ids.reshape(-1)].cpu().numpy()),
+                      np.arange(B * pages_s, dtype=np.int32).reshape(B, pages_s),
+                      q_dev[0].float().cpu().numpy(), attn.signs(dev).cpu().numpy())
+
+    # ---- the other configs, each with its own oracle check (all ranks take part) ------------------
+    mixed = kv_split = None
+    if "mixed" in wanted or "kv_split" in wanted:
+        del caches
+        torch.cuda.empty_cache()
+        if "mixed" in wanted:
+            mixed = section_mixed(args, rank, world, dev, peak)
+        if "kv_split" in wanted:
+            kv_split = section_kv_split(args, rank, world, dev, peak)
+
     if rank != 0:
         if world > 1:
             import torch.distributed as dist
             dist.destroy_process_group()
         return
     cpu = None
-    if not args.no_cpu_baseline:
-        threads = os.cpu_count() or 1
-        ctx_s = L
-        pages_s = (ctx_s + PAGE - 1) // PAGE
-        # the sample attends the first ctx_s tokens of every sequence of layer 0, same bytes as the GPU
-        ids = block_table[:, :pages_s].long()
-        sub = caches[0][:, ids.reshape(-1)].cpu().numpy()
-        bt_s = np.arange(B * pages_s, dtype=np.int32).reshape(B, pages_s)
-        signs = attn.signs(dev).cpu().numpy()
-        reps = 3
-        rate, dt = cpu_decode_rate(np.ascontiguousarray(sub), bt_s, q_dev[0].float().cpu().numpy(), signs, ctx_s, threads,
-                                   reps)
-        cpu = {"value": rate / (L * HKV * NL), "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": f"{threads * reps} sequence passes x {ctx_s} tokens x {HKV} KV heads of layer 0's cache ({dt:.2f} s), "
-                         f"scaled to ctx {L} x {NL} layers per token"}
+    if cpu_sample is not None:
+        cpu = cpu_arm(*cpu_sample, ctx=L, layers=NL, torch_passes=min(B, 6), port_reps=3)
     line = {
         "metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": workload_name(args), "global_batch": B * world, "parallelism": f"dp{world} (by sequence)",
                    "l2": f"inputs larger than L2: {alg_bytes / 1e6:.0f} MB streamed per launch, {NL} distinct layer caches",
-                   "cuda_graph": graph is not None, "algorithmic_bytes_per_step": alg_bytes * NL},
-        "roofline": roofline, "write": write, "dequant": dequant, "cpu_baseline": cpu,
+                   "cuda_graph": graph is not None, "algorithmic_bytes_per_step": alg_bytes * NL,
+                   "arithmetic": "f16 x f16 tensor-core products with f32 accumulation over 4-bit codes; bf16 queries and outputs"},
+        "roofline": roofline, "parity": parity, "write": write, "dequant": dequant, "cpu_baseline": cpu,
+        "mixed": mixed, "kv_split": kv_split, "strong": strong,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "api": "TurboQuantPagedAttention.write + .decode per layer, pinned host buffers, copies on two copy streams beside the kernels" + ("" if args.no_graph else ", step captured in a CUDA graph")},
         "gpu_launches": args.steps * NL * 2, "clocks": clocks,

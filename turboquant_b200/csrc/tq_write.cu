@@ -382,7 +382,7 @@ write_kv_cache_kernel(const __grid_constant__ WriteParams p) {
         }
         __syncwarp();
         if (row_ok && slot >= p.total_slots) {
-            if (m == 0 && h == 0) atomicAdd(&g_write_dropped, 1);  // once per token
+            if (m == 0 && h == 0 && which == 0) atomicAdd(&g_write_dropped, 1);  // once per token
             slot = -1;
         }
         if (row_ok && slot >= 0) {
