@@ -42,7 +42,11 @@ enum {
 /* flags of tq_write_kv_cache */
 enum {
     TQ_WRITE_DEFAULT = 0,
-    TQ_WRITE_ZERO_PAD = 1 /* also store zeros to the pad bytes after the norms (the reference leaves them alone) */
+    TQ_WRITE_ZERO_PAD = 1, /* also store zeros to the pad bytes after the norms (the reference leaves them alone) */
+    TQ_WRITE_EXACT_PATH = 2, /* always run the kernel that evaluates the reference's arithmetic for every element
+                                (default: large writes of 16-bit rows take the tensor-core kernel, which produces
+                                the same bytes and re-derives only the codes next to a boundary that way) */
+    TQ_WRITE_TENSOR_PATH = 4 /* always run the tensor-core kernel (fp16 / bf16 rows of 128 elements only) */
 };
 
 int tq_abi_version(void);
@@ -286,6 +290,12 @@ int tq_decode_static_status(int32_t* status_out, void* stream);
  * Host array of three; synchronises the device.  The reference only checks shapes
  * (csrc/src/quantize_write_binding.cu:216-227). */
 int tq_fault_counts(int32_t* counts3);
+
+/* Rows (K and V rows of every token and head, tile padding included) the tensor-core write kernel
+ * has processed on the current device since the library was loaded, and how many of them it
+ * re-derived with the exact path because a value lay within 2^-18 of a code boundary or the
+ * row's norm was zero, huge or not finite.  Synchronises the device. */
+int tq_write_guard_stats(int64_t* rows_total, int64_t* rows_exact);
 
 /* Measurement hook.  While three CUDA events are set for the calling thread, the decode entry
  * points record them on the call's stream: ev_start before the decode kernel, ev_mid between

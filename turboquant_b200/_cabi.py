@@ -20,7 +20,7 @@ LIB_PATH = Path(os.environ.get("TURBOQUANT_B200_LIB", _PKG / "lib" / "libturboqu
 TQ_F32, TQ_F16, TQ_BF16 = 0, 1, 2
 TQ_I32, TQ_I64 = 0, 1
 TQ_PACK_LOW_FIRST, TQ_PACK_CACHE = 0, 1
-TQ_WRITE_ZERO_PAD = 1
+TQ_WRITE_ZERO_PAD, TQ_WRITE_EXACT_PATH, TQ_WRITE_TENSOR_PATH = 1, 2, 4
 STATIC_SCRATCH_BYTES = 8 << 20  # TQ_STATIC_SCRATCH_BYTES
 
 _DTYPES = {torch.float32: TQ_F32, torch.float16: TQ_F16, torch.bfloat16: TQ_BF16}
@@ -32,6 +32,7 @@ EXPORTS = (
     "tq_decode_paged_static", "tq_decode_paged_multi", "tq_exchange_bytes", "tq_decode_paged_exchange",
     "tq_dequant_paged", "tq_pages_packed_bytes", "tq_pages_gather", "tq_pages_scatter",
     "tq_decode_max_query_columns", "tq_set_exchange_wait_limit", "tq_decode_static_status", "tq_fault_counts",
+    "tq_write_guard_stats",
 )
 
 _lib = None
@@ -126,8 +127,10 @@ def codebook(dim: int, bits: int):
 
 def write_kv_cache(kv_cache: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                    signs: torch.Tensor, slot_mapping: torch.Tensor, head_dim: int,
-                   zero_pad: bool = False) -> None:
-    """kv_cache uint8-addressable [2, nb, bs, H, slot]; key/value [T, H, D] (token stride free)."""
+                   zero_pad: bool = False, path: str = "auto") -> None:
+    """kv_cache uint8-addressable [2, nb, bs, H, slot]; key/value [T, H, D] (token stride free).
+    ``path``: "auto" (large fp16 / bf16 writes take the tensor-core kernel), "exact" or "tensor";
+    all three produce the same bytes."""
     for t, n in ((kv_cache, "kv_cache"), (key, "key"), (value, "value"), (signs, "signs"),
                  (slot_mapping, "slot_mapping")):
         _cuda(t, n)
@@ -155,7 +158,10 @@ def write_kv_cache(kv_cache: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         _ptr(key), _ptr(value), ctypes.c_int(dtype_code(key.dtype)), ctypes.c_int64(T),
         ctypes.c_int64(key.stride(0)), ctypes.c_int64(value.stride(0)), _ptr(signs),
         _ptr(slot_mapping), ctypes.c_int(TQ_I64 if slot_mapping.dtype == torch.int64 else TQ_I32),
-        ctypes.c_int(head_dim), ctypes.c_int(TQ_WRITE_ZERO_PAD if zero_pad else 0), _stream(kv_cache)))
+        ctypes.c_int(head_dim),
+        ctypes.c_int((TQ_WRITE_ZERO_PAD if zero_pad else 0) | {"auto": 0, "exact": TQ_WRITE_EXACT_PATH,
+                                                                "tensor": TQ_WRITE_TENSOR_PATH}[path]),
+        _stream(kv_cache)))
 
 
 def quantize_flat(x: torch.Tensor, signs: torch.Tensor, bits: int, cache_order: bool = False):
@@ -241,6 +247,13 @@ def fault_counts():
     c = (ctypes.c_int32 * 3)()
     _check(lib().tq_fault_counts(c))
     return tuple(int(x) for x in c)
+
+
+def write_guard_stats():
+    """(rows the tensor-core write kernel processed, rows it re-derived exactly); synchronises."""
+    a, b = ctypes.c_int64(0), ctypes.c_int64(0)
+    _check(lib().tq_write_guard_stats(ctypes.byref(a), ctypes.byref(b)))
+    return int(a.value), int(b.value)
 
 
 def set_exchange_wait_limit(polls: int) -> None:

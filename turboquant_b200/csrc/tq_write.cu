@@ -23,8 +23,11 @@
 //     instruction);
 //   * the code index comes from a table over 1/64-wide bins of y (each bin holds at most one of
 //     the 15 boundaries): boundaries below the bin + one exact comparison with the boundary inside.
+#include <cuda.h>  // CUtensorMap and its enums only: the encoder is looked up at run time, nothing links against the driver
+
 #include <cmath>
 #include <cstring>
+#include <type_traits>
 
 #include "tq_common.cuh"
 
@@ -54,6 +57,8 @@ struct WriteParams {
     const float* signs;       // [128] +-1, device
     float2 bin_table[kBins];  // per bin of y: {boundary inside the bin or +inf, number of boundaries in lower bins}
     float fwht_scale;         // (float)(1/sqrt(128))
+    // tensor-core kernel, dense inputs: key / value as [rows][128] tensors, boxes of 16 rows x 64 elements
+    alignas(64) CUtensorMap tmap[2];
 };
 
 // Two fp32 values in one 64-bit register and the packed arithmetic of sm_100 (add/sub/mul/fma
@@ -119,6 +124,9 @@ __device__ __forceinline__ void split_row(int64_t r, int H, int head_shift, int6
 // Rows dropped because their slot lay outside the cache (a stale or garbage slot id must never
 // become a store address); read back by tq_fault_counts.
 static __device__ int32_t g_write_dropped = 0;
+// Rows the tensor-core kernel handled, and how many of them it re-derived with the exact path
+// (read back by tq_write_guard_stats).
+static __device__ unsigned long long g_guard_rows[2] = {0ull, 0ull};
 
 template <typename T>
 struct RowLoad;
@@ -422,6 +430,520 @@ static int launch_write(const WriteParams& p, int sm_count, cudaStream_t stream)
     return TQ_OK;
 }
 
+
+// =============================================================================================
+// 16-bit inputs, head size 128: tensor-core transform with guarded codes.
+//
+// The kernel above spends about 23 instructions per element, most of them on arithmetic whose
+// exact rounding only matters for the few elements that land next to a code boundary.  This
+// kernel gets the same bytes with fewer instructions:
+//
+//   * The norm is computed exactly as above (bf16 / fp16 squares are exact in fp32; the adds run
+//     in the reference order: eight interleaved accumulators over j, combined left to right).  A
+//     thread of an MMA fragment holds, for its two rows, exactly the elements of accumulators
+//     2tg and 2tg+1, in order of j; their fp32 values come from a tensor-core product with the
+//     identity (one non-zero addend per output, hence exact), so no unpacking is needed.
+//   * The transform is H128 = H8 (x) H16: the H16 factor (butterfly stages h = 1..8) is one
+//     m16n8k16 tensor-core product per 16-element chunk of a 16-row tile against a +-1 matrix
+//     with the sign vector folded in (products with +-1 are exact; the accumulator starts at zero),
+//     the H8 factor (h = 16..64) is three register-local butterfly stages in fp32.  The result Y is
+//     the transform of the raw row; y = Y * SCALE / norm is never formed: its bin and its distance
+//     from the bin's boundary come from one FMA each with per-row constants.
+//   * Guard.  Let y_ref be what the reference computes (division, seven rounded stages, one
+//     multiply) and y_fast = Y * SCALE / norm as evaluated here, both with the same fp32 norm.
+//     Against exact arithmetic on that norm, |y_ref - y| <= 26 u (u = 2^-24: 11.3 u from the
+//     divisions, 282 u from the stage roundings, both in units of the unscaled transform, times
+//     SCALE, plus the final multiply), and |y_fast - y| <= 29 u: 34 u * max|x| per chunk product --
+//     the tensor core adds 16 exact addends after aligning them to the largest one and keeps at
+//     least 24 bits, so each addend loses less than 2^-23 of that largest one -- times 8 chunks,
+//     50 u * norm from the three fp32 stages, 1.5 u relative from the rounded scale factor.
+//     Together |y_fast - y_ref| < 55 u = 3.3e-6.  A code is taken from y_fast only when y_fast is
+//     farther than 2^-18 = 3.8e-6 from the boundary of its bin: z = (y_fast - b) * 2^17 + 1/2,
+//     s = saturate(z) is exactly 0 or 1 then, and code = (boundaries in lower bins) + s.  Any
+//     s strictly between 0 and 1 makes sum s (1 - s) positive for the row (non-negative terms, so
+//     nothing cancels), and such a row is done again by the exact path below, 32 lanes on one row,
+//     from the staged input.  About 3.6 % of N(0,1) rows take it.  Rows whose norm is not a
+//     moderate finite number (zero rows, overflowing or non-finite rows) always take it.
+//   * The bins of y_fast are formed from Y * (64 * f) rather than from the rounded y, so next to a
+//     bin edge the two paths may pick neighbouring bins; the host checks that no boundary lies
+//     within 2^-13 of a bin edge, which makes both bins give the same code there.
+//   * Staging.  Dense inputs (token stride = heads x 128) are fetched by tiled tensor copies
+//     (cp.async.bulk.tensor, two boxes of 16 rows x 128 bytes per tile, 128-byte swizzle, issued
+//     by one lane); the swizzle makes the ldmatrix reads conflict free.  Strided inputs (K / V as
+//     column slices of a fused projection) use one bulk copy per row into rows of 272 bytes.
+// =============================================================================================
+constexpr float kGuardBig = 131072.0f;  // 2^17
+
+template <typename T>
+struct MmaOps;
+template <>
+struct MmaOps<__nv_bfloat16> {
+    static constexpr uint32_t kOne = 0x3F80u, kMinusOne = 0xBF80u;
+    // the accumulator input is the constant zero: nothing has to be cleared first
+    static __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+    }
+    static __device__ __forceinline__ P2 unpack(uint32_t w) {
+        return pk(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+};
+template <>
+struct MmaOps<__half> {
+    static constexpr uint32_t kOne = 0x3C00u, kMinusOne = 0xBC00u;
+    static __device__ __forceinline__ void mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+    }
+    static __device__ __forceinline__ P2 unpack(uint32_t w) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        return pk(f.x, f.y);
+    }
+};
+
+// Shared-memory map of the tensor-core kernel.  A warp's stage buffer holds its 16-row tile either
+// as two swizzled halves of 16 rows x 128 bytes (tensor copies) or as rows of 272 bytes (per-row
+// copies; 272 = 16 mod 128, so the eight rows of an ldmatrix hit different banks).
+struct MmaShape {
+    static constexpr int kThreads = 512, kWarps = 16, kRows = 16;
+    static constexpr int kRowBytes = 256, kPitch = 272;
+    static constexpr int kWarpStage = 5120;                        // >= 16 x 272, a multiple of 1024 (swizzle atom)
+    static constexpr size_t kStageBytes = (size_t)2 * kWarps * kWarpStage;
+    static constexpr size_t kTableBytes = (size_t)kBins * 16 * 8 + 1024;  // 16 columns of 8-byte entries + the boundaries
+    static constexpr size_t kBfragBytes = (size_t)8 * 32 * 16;     // B fragments of the 8 chunks, per lane
+    static constexpr int kOutPitch = 72;
+    static constexpr size_t kOutBytes = (size_t)kWarps * kRows * kOutPitch;
+    static constexpr size_t kSmem = kStageBytes + kTableBytes + kBfragBytes + kOutBytes + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(addr));
+}
+// Tiled tensor copy global -> shared of one box at element coordinates (x, y), completing on an
+// mbarrier.  x times the element size is a multiple of 16 bytes at both call sites (0 and 128).
+__device__ __forceinline__ void tensor_g2s_2d(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// One code byte (even dim in the high nibble) of the pair (Y0, Y1) of one row, as a float, and the
+// row's ambiguity sum.  Table entry of a bin (8 bytes, 16 columns: an 8-byte load is served half a
+// warp at a time, so lookups never conflict): {1/2 - b * 2^17 (or -inf), boundaries in lower bins}.
+__device__ __forceinline__ float guarded_byte(P2 Y2, P2 kf2, float zf, uint32_t table_lane, P2& amb) {
+    float Y0, Y1, k0, k1;
+    up(Y2, Y0, Y1);
+    up(fma2(Y2, kf2, pk(kBinMagic, kBinMagic)), k0, k1);
+    float c0, below0, c1, below1;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(c0), "=f"(below0) : "r"(__float_as_uint(k0) * 128u + table_lane));
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(c1), "=f"(below1) : "r"(__float_as_uint(k1) * 128u + table_lane));
+    const float s0 = fma_sat(Y0, zf, c0), s1 = fma_sat(Y1, zf, c1);
+    const P2 s2 = pk(s0, s1);
+    amb = fma2(s2, sub2(pk(1.0f, 1.0f), s2), amb);  // s (1 - s): zero exactly when s is 0 or 1
+    return __fmaf_rn(__fadd_rn(s0, below0), 16.0f, __fadd_rn(s1, below1));
+}
+
+template <typename T, bool TMA>
+__global__ void __launch_bounds__(MmaShape::kThreads, 1)
+write_kv_cache_mma_kernel(const __grid_constant__ WriteParams p) {
+    using O = MmaOps<T>;
+    using W = MmaShape;
+    constexpr int kPitch = W::kPitch, kRows = W::kRows;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[W::kWarps][2];
+    __shared__ __align__(16) float signs_s[kD];
+    // the swizzle pattern of a tensor copy is a function of the shared-memory address: 1024-byte aligned stages
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, tg = lane & 3;   // fragment coordinates: rows g and g + 8, column pair tg
+    const int m = lane & 1;                   // store phase: two lanes per row
+    const int row_in_warp = lane >> 1;
+    const int H = p.num_kv_heads;
+    const int64_t rows = p.num_tokens * H;
+    const int64_t num_tiles = 2 * ((rows + kRows - 1) / kRows);  // K and V tiles alternate
+
+    grid_launch_dependents();
+    if (lane == 0) {
+        mbar_init(&full_bar[warp][0], 1);
+        mbar_init(&full_bar[warp][1], 1);
+    }
+    if (tid == 0) fence_barrier_init();
+    float2* tab_s = reinterpret_cast<float2*>(smem + W::kStageBytes);
+    float* bnd_s = reinterpret_cast<float*>(smem + W::kStageBytes + (size_t)kBins * 16 * 8);  // exact path only
+    for (int i = tid; i < kBins * 16; i += W::kThreads) {
+        const float2 e = p.bin_table[i >> 4];  // {boundary inside the bin or +inf, boundaries in lower bins}
+        tab_s[i] = make_float2(e.x < INFINITY ? __fmaf_rn(-e.x, kGuardBig, 0.5f) : -INFINITY, e.y);
+        if ((i & 15) == 0) bnd_s[i >> 4] = e.x;
+    }
+    const uint32_t table_lane = smem_u32(tab_s) + 8u * (lane & 15) - 0x80000000u;
+    uint4* bfrag_s = reinterpret_cast<uint4*>(smem + W::kStageBytes + W::kTableBytes);
+    uint8_t* out_s = smem + W::kStageBytes + W::kTableBytes + W::kBfragBytes;
+    if (tid < kD) signs_s[tid] = p.signs[tid];
+    __syncthreads();
+    // B fragments: column n of n-tile j computes output dim 4 (n / 2) + 2 j + (n % 2) of the chunk,
+    // so that a thread ends up with four consecutive dims (two code bytes) of its rows.
+    for (int i = tid; i < 8 * 32 * 4; i += W::kThreads) {
+        const int c = i >> 7, l = (i >> 2) & 31, r = i & 3;
+        const int j = r >> 1, n = l >> 2, k0 = 2 * (l & 3) + 8 * (r & 1);
+        const int dout = 4 * (n >> 1) + 2 * j + (n & 1);
+        uint32_t w = 0;
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int k = k0 + e;
+            const bool neg = ((__popc(k & dout) & 1) != 0) != (signs_s[16 * c + k] < 0.0f);
+            w |= (neg ? O::kMinusOne : O::kOne) << (16 * e);
+        }
+        reinterpret_cast<uint32_t*>(bfrag_s)[i] = w;
+    }
+    grid_dependency_wait();  // K, V, the slots and the cache belong to earlier kernels
+    __syncthreads();
+
+    auto issue = [&](int64_t tile, int buf) {
+        const int which = (int)(tile & 1);
+        const int64_t row0 = (tile >> 1) * kRows;
+        uint8_t* dst0 = smem + ((size_t)buf * W::kWarps + warp) * W::kWarpStage;
+        fence_proxy_async();  // earlier shared-memory reads of this buffer precede the copy engine's writes
+        if (TMA) {
+            // two boxes of 16 rows x 64 elements; rows past the end of the tensor arrive as zeros
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&full_bar[warp][buf], (uint32_t)(kRows * W::kRowBytes));
+                tensor_g2s_2d(dst0, &p.tmap[which], 0, (int)row0, &full_bar[warp][buf]);
+                tensor_g2s_2d(dst0 + 2048, &p.tmap[which], 64, (int)row0, &full_bar[warp][buf]);
+            }
+        } else {
+            const int64_t left = rows - row0;
+            const int64_t nrows = left < kRows ? left : (int64_t)kRows;
+            if (lane == 0) mbar_arrive_expect_tx(&full_bar[warp][buf], (uint32_t)(nrows * W::kRowBytes));
+            __syncwarp();
+            if (lane < nrows) {
+                const int64_t r = row0 + lane;
+                int64_t t;
+                int h;
+                split_row(r, H, p.head_shift, t, h);
+                const T* src = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * kD;
+                bulk_g2s(dst0 + (size_t)lane * kPitch, src, W::kRowBytes, &full_bar[warp][buf]);
+            }
+        }
+    };
+
+    // B fragment of the 8 x 8 identity: rows 2tg, 2tg + 1 of column g
+    const uint32_t ident = (g == 2 * tg ? O::kOne : 0u) | (g == 2 * tg + 1 ? O::kOne << 16 : 0u);
+    // ldmatrix: lane l supplies the address of row (l & 7) + 8 ((l >> 3) & 1), 16-byte piece (l >> 4) of the chunk
+    const int lm_row = (lane & 7) + 8 * ((lane >> 3) & 1), lm_hi = lane >> 4;
+    const int64_t warp_stride = (int64_t)gridDim.x * W::kWarps;
+    int64_t tile = (int64_t)warp * gridDim.x + blockIdx.x;
+    if (tile < num_tiles) issue(tile, 0);
+    unsigned int stat_rows = 0, stat_exact = 0;  // this warp's share of g_guard_rows, added once at the end
+    for (int it = 0; tile < num_tiles; tile += warp_stride, it++) {
+        const int buf = it & 1;
+        const int64_t next = tile + warp_stride;
+        if (next < num_tiles) issue(next, buf ^ 1);
+
+        const int which = (int)(tile & 1);
+        const int64_t r = (tile >> 1) * kRows + row_in_warp;  // the row this lane stores
+        const bool row_ok = r < rows;
+        int64_t slot = -1;
+        int h = 0;
+        if (row_ok) {
+            int64_t t;
+            split_row(r, H, p.head_shift, t, h);
+            slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
+                                 : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
+        }
+        if (!mbar_wait(&full_bar[warp][buf], (it >> 1) & 1)) return;
+        const uint8_t* stage = smem + ((size_t)buf * W::kWarps + warp) * W::kWarpStage;
+        // Rows past the end of the tensor hold zeros or stale bytes: they are computed like any
+        // others (whatever they contain ends in a finite code or in the exact path) and never stored.
+        // byte address of 16-byte piece `piece` (0..15) of row `row` of the staged tile
+        auto piece_addr = [&](int row, int piece) -> uint32_t {
+            if (TMA) return smem_u32(stage) + (piece >> 3) * 2048 + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
+            return smem_u32(stage) + row * kPitch + piece * 16;
+        };
+
+        // ---- chunk products (stages h = 1..8) and the exact sums of squares -----------------------
+        P2 v[8][2][2];  // [chunk][n-tile][row half]: {dims 4tg + 2j, 4tg + 2j + 1} of rows g / g + 8
+        P2 n_lo = pk(0.0f, 0.0f), n_hi = pk(0.0f, 0.0f);  // accumulators 2tg, 2tg+1 of rows g and g + 8
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(piece_addr(lm_row, 2 * c + lm_hi), a0, a1, a2, a3);
+            const uint4 b = bfrag_s[c * 32 + lane];
+            float d0[4], d1[4], e0[4], e1[4];
+            O::mma(d0, a0, a1, a2, a3, b.x, b.y);
+            O::mma(d1, a0, a1, a2, a3, b.z, b.w);
+            v[c][0][0] = pk(d0[0], d0[1]); v[c][0][1] = pk(d0[2], d0[3]);
+            v[c][1][0] = pk(d1[0], d1[1]); v[c][1][1] = pk(d1[2], d1[3]);
+            // The fp32 values of the fragment's own elements, for the squares: e0 = rows g / g + 8,
+            // elements 8 (2c) + 2tg, +1; e1 = elements 8 (2c + 1) + 2tg, +1.
+            O::mma(e0, a0, a1, a2, a3, ident, 0u);
+            O::mma(e1, a0, a1, a2, a3, 0u, ident);
+            P2 x2 = pk(e0[0], e0[1]); n_lo = add2(n_lo, mul2(x2, x2));
+            x2 = pk(e0[2], e0[3]); n_hi = add2(n_hi, mul2(x2, x2));
+            x2 = pk(e1[0], e1[1]); n_lo = add2(n_lo, mul2(x2, x2));
+            x2 = pk(e1[2], e1[3]); n_hi = add2(n_hi, mul2(x2, x2));
+        }
+        // the eight accumulators of a row sit in its quad, two per lane: combine them left to right
+        float norm_lo, norm_hi;
+        {
+            float l0, l1, h0, h1;
+            up(n_lo, l0, l1);
+            up(n_hi, h0, h1);
+            const int qb = lane & ~3;
+            float s_lo = __shfl_sync(0xffffffffu, l0, qb), s_hi = __shfl_sync(0xffffffffu, h0, qb);
+            s_lo = __fadd_rn(s_lo, __shfl_sync(0xffffffffu, l1, qb));
+            s_hi = __fadd_rn(s_hi, __shfl_sync(0xffffffffu, h1, qb));
+#pragma unroll
+            for (int t = 1; t < 4; t++) {
+                s_lo = __fadd_rn(s_lo, __shfl_sync(0xffffffffu, l0, qb + t));
+                s_hi = __fadd_rn(s_hi, __shfl_sync(0xffffffffu, h0, qb + t));
+                s_lo = __fadd_rn(s_lo, __shfl_sync(0xffffffffu, l1, qb + t));
+                s_hi = __fadd_rn(s_hi, __shfl_sync(0xffffffffu, h1, qb + t));
+            }
+            norm_lo = __fsqrt_rn(s_lo);
+            norm_hi = __fsqrt_rn(s_hi);
+            if (!(norm_lo >= 1e-8f)) norm_lo = (norm_lo != norm_lo) ? __uint_as_float(0x7fc00000u) : 1e-8f;
+            if (!(norm_hi >= 1e-8f)) norm_hi = (norm_hi != norm_hi) ? __uint_as_float(0x7fc00000u) : 1e-8f;
+        }
+        const bool fast_lo = norm_lo > 1e-8f && norm_lo < 1e30f, fast_hi = norm_hi > 1e-8f && norm_hi < 1e30f;
+        const float f_lo = __fmul_rn(p.fwht_scale, __frcp_rn(norm_lo)), f_hi = __fmul_rn(p.fwht_scale, __frcp_rn(norm_hi));
+
+        // ---- stages h = 16, 32, 64 across the chunks ------------------------------------------------
+#pragma unroll
+        for (int hc = 1; hc < 8; hc <<= 1)
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                if (!(c & hc)) {
+#pragma unroll
+                    for (int j = 0; j < 2; j++)
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const P2 a = v[c][j][e], b = v[c | hc][j][e];
+                            v[c][j][e] = add2(a, b);
+                            v[c | hc][j][e] = sub2(a, b);
+                        }
+                }
+
+        // ---- guarded codes: bytes 8c + 2tg and 8c + 2tg + 1 of rows g and g + 8 ---------------------
+        uint8_t* orow_lo = out_s + (size_t)(warp * kRows + g) * W::kOutPitch + 2 * tg;
+        uint8_t* orow_hi = orow_lo + 8 * W::kOutPitch;
+        P2 amb_lo = pk(0.0f, 0.0f), amb_hi = pk(0.0f, 0.0f);
+        const float zf_lo = f_lo * kGuardBig, zf_hi = f_hi * kGuardBig;
+        const P2 kf_lo = pk(f_lo * 64.0f, f_lo * 64.0f), kf_hi = pk(f_hi * 64.0f, f_hi * 64.0f);
+        // A row off the fast path (norm zero, huge or not finite) may hold values whose bin is not a
+        // table index: it forms no lookup address at all.  The branch is uniform unless such a row
+        // exists (the four lanes of a quad agree on their rows' flags).
+        if (__all_sync(0xffffffffu, fast_lo && fast_hi)) {
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float b0 = guarded_byte(v[c][0][0], kf_lo, zf_lo, table_lane, amb_lo);
+                const float b1 = guarded_byte(v[c][1][0], kf_lo, zf_lo, table_lane, amb_lo);
+                *reinterpret_cast<uint16_t*>(orow_lo + 8 * c) =
+                    (uint16_t)__float_as_uint(__fadd_rn(__fmaf_rn(b1, 256.0f, b0), 8388608.0f));
+                const float b2 = guarded_byte(v[c][0][1], kf_hi, zf_hi, table_lane, amb_hi);
+                const float b3 = guarded_byte(v[c][1][1], kf_hi, zf_hi, table_lane, amb_hi);
+                *reinterpret_cast<uint16_t*>(orow_hi + 8 * c) =
+                    (uint16_t)__float_as_uint(__fadd_rn(__fmaf_rn(b3, 256.0f, b2), 8388608.0f));
+            }
+        } else {
+            if (fast_lo) {
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const float b0 = guarded_byte(v[c][0][0], kf_lo, zf_lo, table_lane, amb_lo);
+                    const float b1 = guarded_byte(v[c][1][0], kf_lo, zf_lo, table_lane, amb_lo);
+                    *reinterpret_cast<uint16_t*>(orow_lo + 8 * c) =
+                        (uint16_t)__float_as_uint(__fadd_rn(__fmaf_rn(b1, 256.0f, b0), 8388608.0f));
+                }
+            }
+            if (fast_hi) {
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const float b2 = guarded_byte(v[c][0][1], kf_hi, zf_hi, table_lane, amb_hi);
+                    const float b3 = guarded_byte(v[c][1][1], kf_hi, zf_hi, table_lane, amb_hi);
+                    *reinterpret_cast<uint16_t*>(orow_hi + 8 * c) =
+                        (uint16_t)__float_as_uint(__fadd_rn(__fmaf_rn(b3, 256.0f, b2), 8388608.0f));
+                }
+            }
+        }
+        float al0, al1, ah0, ah1;
+        up(amb_lo, al0, al1);
+        up(amb_hi, ah0, ah1);
+        // NaN compares false on "== 0": a row that produced NaNs is flagged as well
+        const bool flag_lo = !fast_lo || !(__fadd_rn(al0, al1) == 0.0f);
+        const bool flag_hi = !fast_hi || !(__fadd_rn(ah0, ah1) == 0.0f);
+        uint32_t m_lo = __ballot_sync(0xffffffffu, flag_lo), m_hi = __ballot_sync(0xffffffffu, flag_hi);
+        m_lo = (m_lo | (m_lo >> 1) | (m_lo >> 2) | (m_lo >> 3)) & 0x11111111u;  // bit 4g: row g flagged
+        m_hi = (m_hi | (m_hi >> 1) | (m_hi >> 2) | (m_hi >> 3)) & 0x11111111u;
+        stat_rows += kRows;
+        stat_exact += __popc(m_lo) + __popc(m_hi);
+        __syncwarp();
+
+        // ---- exact path for the flagged rows: the whole warp on one row, lane L on elements 4L..4L+3 ---
+        for (int half = 0; half < 2; half++) {
+            uint32_t todo = half ? m_hi : m_lo;
+            while (todo) {
+                const int rr = (__ffs(todo) - 1) >> 2;
+                todo &= todo - 1;
+                float norm = __shfl_sync(0xffffffffu, half ? norm_hi : norm_lo, 4 * rr);
+                const int row = rr + 8 * half;
+                uint2 w;
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y)
+                             : "r"(piece_addr(row, lane >> 1) + 8 * (lane & 1)));
+                float x0, x1, x2, x3;
+                up(O::unpack(w.x), x0, x1);
+                up(O::unpack(w.y), x2, x3);
+                if (norm != norm) {
+                    // The identity products turn a row with an infinite element into NaNs (inf x 0).
+                    // The sum of squares is NaN only if an element is; with infinities alone it is +inf.
+                    const bool has_nan = __any_sync(0xffffffffu, x0 != x0 || x1 != x1 || x2 != x2 || x3 != x3);
+                    if (!has_nan) {
+                        norm = INFINITY;
+                        if ((lane >> 2) == rr) {
+                            if (half) norm_hi = norm;
+                            else norm_lo = norm;
+                        }
+                    }
+                }
+                const float4 sg = *reinterpret_cast<const float4*>(&signs_s[4 * lane]);
+                x0 = __fmul_rn(__fdiv_rn(x0, norm), sg.x);
+                x1 = __fmul_rn(__fdiv_rn(x1, norm), sg.y);
+                x2 = __fmul_rn(__fdiv_rn(x2, norm), sg.z);
+                x3 = __fmul_rn(__fdiv_rn(x3, norm), sg.w);
+                const float a0 = __fadd_rn(x0, x1), a1 = __fsub_rn(x0, x1), a2 = __fadd_rn(x2, x3), a3 = __fsub_rn(x2, x3);
+                float y[4] = {__fadd_rn(a0, a2), __fadd_rn(a1, a3), __fsub_rn(a0, a2), __fsub_rn(a1, a3)};
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float o = __shfl_xor_sync(0xffffffffu, y[i], d);
+                        y[i] = (lane & d) ? __fsub_rn(o, y[i]) : __fadd_rn(y[i], o);
+                    }
+                }
+                float code[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float yy = __fmul_rn(y[i], p.fwht_scale);
+                    if (yy != yy) {  // torch's bucketize sends NaN to the last bucket
+                        code[i] = 15.0f;
+                    } else {
+                        const float kf = __fmaf_rn(yy, 64.0f, kBinMagic);
+                        const uint32_t bin = __float_as_uint(kf) - 0x4B000000u;
+                        const float below = tab_s[bin * 16 + (lane & 15)].y;
+                        code[i] = yy > bnd_s[bin] ? __fadd_rn(below, 1.0f) : below;
+                    }
+                }
+                const float both = __fadd_rn(__fmaf_rn(__fmaf_rn(code[2], 16.0f, code[3]), 256.0f,
+                                                        __fmaf_rn(code[0], 16.0f, code[1])), 8388608.0f);
+                *reinterpret_cast<uint16_t*>(out_s + (size_t)(warp * kRows + row) * W::kOutPitch + 2 * lane) =
+                    (uint16_t)__float_as_uint(both);
+            }
+        }
+        __syncwarp();
+
+        // ---- store: two lanes per row, 32 code bytes each, the norm from lane m = 0 ------------------
+        const float na = __shfl_sync(0xffffffffu, norm_lo, 4 * (row_in_warp & 7));
+        const float nb = __shfl_sync(0xffffffffu, norm_hi, 4 * (row_in_warp & 7));
+        const float norm = (row_in_warp & 8) ? nb : na;
+        if (row_ok && slot >= p.total_slots) {
+            if (m == 0 && h == 0 && which == 0) atomicAdd(&g_write_dropped, 1);
+            slot = -1;
+        }
+        if (row_ok && slot >= 0) {
+            const uint8_t* orow = out_s + (size_t)(warp * kRows + row_in_warp) * W::kOutPitch;
+            uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)slot * H + h) * p.slot_bytes;
+            const uint2* src8 = reinterpret_cast<const uint2*>(orow + 32 * m);
+            const uint2 c0 = src8[0], c1 = src8[1], c2 = src8[2], c3 = src8[3];
+            uint4* dst16 = reinterpret_cast<uint4*>(dst + 32 * m);
+            dst16[0] = make_uint4(c0.x, c0.y, c1.x, c1.y);
+            dst16[1] = make_uint4(c2.x, c2.y, c3.x, c3.y);
+            if (m == 0) {
+                const uint32_t nh = (norm != norm) ? 0x7e00u : (uint32_t)__half_as_ushort(__float2half_rn(norm));
+                if (p.zero_pad) *reinterpret_cast<uint4*>(dst + 64) = make_uint4(nh | (nh << 16), 0u, 0u, 0u);
+                else *reinterpret_cast<uint32_t*>(dst + 64) = nh | (nh << 16);
+            }
+        }
+        __syncwarp();
+    }
+    if (lane == 0 && stat_rows) {
+        atomicAdd(&g_guard_rows[0], (unsigned long long)stat_rows);
+        if (stat_exact) atomicAdd(&g_guard_rows[1], (unsigned long long)stat_exact);
+    }
+}
+
+// cuTensorMapEncodeTiled, looked up through the runtime (no link-time dependency on the driver library)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        tried = true;
+    }
+    return fn;
+}
+
+// [rows][128] 16-bit elements, row pitch 256 bytes, boxes of 16 rows x 64 elements with the 128-byte swizzle
+static bool encode_rows_map(CUtensorMap* map, const void* base, int64_t rows, bool is_bf16) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)kD, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)kD * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)MmaShape::kRows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T>
+static int launch_write_mma(WriteParams& p, int sm_count, cudaStream_t stream) {
+    using W = MmaShape;
+    const int64_t rows = p.num_tokens * p.num_kv_heads;
+    // tensor copies need dense [rows][128] tensors whose row index fits the copy's 32-bit coordinate
+    const bool dense = p.token_stride[0] == (int64_t)p.num_kv_heads * kD && p.token_stride[1] == (int64_t)p.num_kv_heads * kD &&
+                       rows < (int64_t)0x7fffffff;
+    const bool tma = dense && encode_rows_map(&p.tmap[0], p.src[0], rows, sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) &&
+                     encode_rows_map(&p.tmap[1], p.src[1], rows, std::is_same<T, __nv_bfloat16>::value);
+    auto kernel = tma ? write_kv_cache_mma_kernel<T, true> : write_kv_cache_mma_kernel<T, false>;
+    static bool configured[2][64] = {};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[tma][dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)W::kSmem));
+        if (dev >= 0 && dev < 64) configured[tma][dev] = true;
+    }
+    const int64_t tiles = 2 * ((rows + W::kRows - 1) / W::kRows);
+    const int64_t grid = tiles < (int64_t)sm_count ? tiles : (int64_t)sm_count;
+    TQ_CUDA(launch_serialized(kernel, dim3((unsigned)grid), dim3(W::kThreads), W::kSmem, stream, p));
+    return TQ_OK;
+}
+
+int write_guard_stats(unsigned long long* out2) {
+    TQ_CUDA(cudaMemcpyFromSymbol(out2, g_guard_rows, 2 * sizeof(unsigned long long)));
+    return TQ_OK;
+}
+
 int device_sm_count(int* out);
 
 int write_fault_count(int32_t* out) {
@@ -488,6 +1010,11 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
             bin_of[i] = (int)(bits - 0x4B000000u);
             TQ_REQUIRE(bin_of[i] >= 0 && bin_of[i] < kBins && (i == 0 || bin_of[i] > bin_of[i - 1]), TQ_ERR_UNSUPPORTED,
                        "boundaries too close for the bin table");
+            // the guarded kernel may look a value next to a bin edge up in either neighbour: no
+            // boundary may sit that close to an edge (edges are at (k +- 1/2) / 64)
+            const double pos = (double)bnd[i] * 64.0 - std::floor((double)bnd[i] * 64.0 + 0.5);
+            TQ_REQUIRE(std::fabs(std::fabs(pos) - 0.5) * (1.0 / 64.0) > 1.0 / 8192.0, TQ_ERR_UNSUPPORTED,
+                       "a boundary lies next to a bin edge");
         }
         for (int k = 0; k < kBins; k++) {
             int below = 0;
@@ -504,6 +1031,14 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     int rc = device_sm_count(&sms);
     if (rc != TQ_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Large writes of 16-bit rows go to the tensor-core kernel; small ones (a decode step's new
+    // tokens), fp32 rows and padded heads keep the kernel that needs no tables beyond one.
+    const bool exact_only = (flags & TQ_WRITE_EXACT_PATH) != 0, tensor_only = (flags & TQ_WRITE_TENSOR_PATH) != 0;
+    TQ_REQUIRE(!(exact_only && tensor_only), TQ_ERR_INVALID, "TQ_WRITE_EXACT_PATH and TQ_WRITE_TENSOR_PATH exclude each other");
+    TQ_REQUIRE(!tensor_only || (head_dim == 128 && in_dtype != TQ_F32), TQ_ERR_UNSUPPORTED,
+               "the tensor-core write kernel takes fp16 / bf16 rows of 128 elements");
+    if (!exact_only && head_dim == 128 && in_dtype != TQ_F32 && (tensor_only || num_tokens * num_kv_heads >= 4096))
+        return in_dtype == TQ_F16 ? launch_write_mma<__half>(p, sms, s) : launch_write_mma<__nv_bfloat16>(p, sms, s);
     if (head_dim == 96) {
         switch (in_dtype) {
             case TQ_F32: return launch_write<float, 96>(p, sms, s);
@@ -516,4 +1051,14 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
         case TQ_F16: return launch_write<__half, 128>(p, sms, s);
         default: return launch_write<__nv_bfloat16, 128>(p, sms, s);
     }
+}
+
+extern "C" int tq_write_guard_stats(int64_t* rows_total, int64_t* rows_exact) {
+    TQ_REQUIRE(rows_total && rows_exact, TQ_ERR_INVALID, "null pointer");
+    unsigned long long v[2] = {0, 0};
+    int rc = tq::write_guard_stats(v);
+    if (rc != TQ_OK) return rc;
+    *rows_total = (int64_t)v[0];
+    *rows_exact = (int64_t)v[1];
+    return TQ_OK;
 }
