@@ -22,13 +22,14 @@ _lib = None
 
 
 def build(force: bool = False) -> Path:
-    """Compile the C restatement (and, when the reference tree is present, its pack.cpp)."""
+    """Compile the C restatement (and, when TURBOQUANT_REFERENCE names the reference tree, its pack.cpp)."""
     src = _HERE / "tq_oracle.c"
     if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < src.stat().st_mtime:
         subprocess.check_call(["make", "-C", str(_HERE), "-B", "libtq_oracle.so"],
                               stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference") and not (_HERE / "_ref" / "libref_pack.so").exists():
-        subprocess.call(["make", "-C", str(_HERE), "ref"], stdout=subprocess.DEVNULL)
+    ref = os.environ.get("TURBOQUANT_REFERENCE", "")
+    if ref and os.path.isdir(ref) and not (_HERE / "_ref" / "libref_pack.so").exists():
+        subprocess.call(["make", "-C", str(_HERE), "ref", f"REF={ref}"], stdout=subprocess.DEVNULL)
     return _LIB_PATH
 
 

@@ -8,6 +8,7 @@ Nothing here is needed at test time; the .npz files are committed.
 """
 import hashlib
 import math
+import os
 import sys
 from pathlib import Path
 
@@ -16,7 +17,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TURBOQUANT_REFERENCE", "")
+if not REF:
+    raise SystemExit("usage: make_golden.py <root of the reference tree>  (or set TURBOQUANT_REFERENCE)")
 sys.path.insert(0, REF)
 sys.path.insert(1, str(REPO))
 

@@ -138,34 +138,37 @@ def test_vllm_backend_impl_write_and_decode(oracle, golden):
     assert_attention_close(out.float().cpu().numpy().reshape(4, 32, 128), want, "vLLM impl decode")
 
 
-def test_vllm_backend_continuation_prefill(oracle, golden):
-    """A chunk of new tokens over sequences with cached context: the backend dequantizes the cached
-    tokens, appends the chunk's fresh K/V and runs causal varlen attention; checked against plain
-    torch attention over the same dense K/V (oracle-dequantized cache + fresh chunk)."""
+def _backend_step(oracle, golden, cached, chunk, with_builder_facts):
+    """One forward of the vLLM backend on a step with the given cached / new token counts per
+    sequence, checked against plain torch attention: rows with one new token and cached context are
+    decode rows (every key, the new one included, is read from the quantized cache); all other rows
+    attend their dequantized cached tokens followed by the chunk's fresh K/V."""
     pytest.importorskip("vllm")
-    from turboquant_b200.vllm_backend_fused import TurboQuantBackend, TurboQuantFusedImpl
+    from turboquant_b200.vllm_backend_fused import TurboQuantBackend, TurboQuantFusedImpl, step_shape
     try:
         impl = TurboQuantFusedImpl(32, 128, SCALE, 8, None, None, "fp8")
         from vllm.vllm_flash_attn import flash_attn_varlen_func  # noqa: F401
     except Exception as e:
         pytest.skip(f"vLLM attention pieces not usable here: {type(e).__name__}: {e}")
-    cached = [100, 0, 37]
-    chunk = [5, 8, 3]
+    B = len(cached)
     total = [c + q for c, q in zip(cached, chunk)]
-    case = synthetic.decode_case(seed=83, seq_lens=total, dtype=torch.bfloat16)
+    case = synthetic.decode_case(seed=83 + B + sum(chunk), seq_lens=total, dtype=torch.bfloat16)
     shape = TurboQuantBackend.get_kv_cache_shape(case.num_blocks, 16, 8, 128, "fp8")
     kv_cache = torch.zeros(shape, dtype=torch.uint8, device=DEV)
     impl.do_kv_cache_update(None, case.k.to(DEV), case.v.to(DEV), kv_cache, case.slot_mapping.to(DEV))
     # the chunk: the last chunk[b] tokens of every sequence (their K/V are case.k / case.v rows)
     starts = np.concatenate([[0], np.cumsum(total)])
-    rows = np.concatenate([np.arange(starts[b] + cached[b], starts[b + 1]) for b in range(3)])
+    rows = np.concatenate([np.arange(starts[b] + cached[b], starts[b + 1]) for b in range(B)])
     n = len(rows)
     g = torch.Generator().manual_seed(11)
     q = torch.randn(n, 32, 128, generator=g).to(torch.bfloat16)
     key, value = case.k[rows], case.v[rows]
-    qsl = torch.tensor(np.concatenate([[0], np.cumsum(chunk)]), dtype=torch.int32, device=DEV)
+    qsl_cpu = torch.tensor(np.concatenate([[0], np.cumsum(chunk)]), dtype=torch.int32)
     md = types.SimpleNamespace(max_query_len=max(chunk), num_actual_tokens=n, block_table=case.block_table.to(DEV),
-                               seq_lens=case.seq_lens.to(DEV), query_start_loc=qsl, max_seq_len=max(total))
+                               seq_lens=case.seq_lens.to(DEV), query_start_loc=qsl_cpu.to(DEV), max_seq_len=max(total))
+    if with_builder_facts:
+        md.tq_step = step_shape(types.SimpleNamespace(query_start_loc_cpu=qsl_cpu, num_reqs=B,
+                                                      seq_lens_cpu=case.seq_lens))
     out = torch.zeros(n, 32 * 128, dtype=torch.bfloat16, device=DEV)
     try:
         impl.forward(None, q.to(DEV).reshape(n, -1), key.to(DEV), value.to(DEV), kv_cache, md, output=out)
@@ -174,24 +177,50 @@ def test_vllm_backend_continuation_prefill(oracle, golden):
             pytest.skip(f"vLLM's FlashAttention does not run on this device: {e}")
         raise
     got = out.float().cpu().numpy().reshape(n, 32, 128)
-    # reference: dense K/V per sequence = oracle dequant of the cached rows + the fresh chunk, fp32 softmax
     cache_np = kv_cache.cpu().numpy()
     signs = golden["signs_seed42_d128"]
     want = np.zeros_like(got)
     qi = 0
-    for b in range(3):
-        t = np.arange(cached[b])
+    for b in range(B):
+        is_decode = chunk[b] == 1 and cached[b] > 0
+        t = np.arange(total[b] if is_decode else cached[b])
         pages = case.block_table.numpy()[b, t // 16]
         kc = oracle.dequant_cache_rows(cache_np[0, pages, t % 16], signs, 128).reshape(-1, 8, 128)
         vc = oracle.dequant_cache_rows(cache_np[1, pages, t % 16], signs, 128).reshape(-1, 8, 128)
-        kc = torch.from_numpy(kc).to(torch.bfloat16).float()        # the backend holds them in the query dtype
-        vc = torch.from_numpy(vc).to(torch.bfloat16).float()
-        ka = torch.cat([kc, case.k[starts[b] + cached[b]:starts[b + 1]].float()])
-        va = torch.cat([vc, case.v[starts[b] + cached[b]:starts[b + 1]].float()])
+        kc, vc = torch.from_numpy(kc), torch.from_numpy(vc)
+        if is_decode:
+            ka, va = kc, vc
+        else:                                                        # the backend holds them in the query dtype
+            ka = torch.cat([kc.to(torch.bfloat16).float(), case.k[starts[b] + cached[b]:starts[b + 1]].float()])
+            va = torch.cat([vc.to(torch.bfloat16).float(), case.v[starts[b] + cached[b]:starts[b + 1]].float()])
         for i in range(chunk[b]):
             kk, vv = ka[: cached[b] + i + 1], va[: cached[b] + i + 1]
             qq = q[qi].float().view(8, 4, 128)
             sc = torch.einsum("hgd,thd->hgt", qq, kk) * SCALE
             want[qi] = torch.einsum("hgt,thd->hgd", torch.softmax(sc, -1), vv).reshape(32, 128).numpy()
             qi += 1
-    assert_attention_close(got, want, "continuation prefill")
+    assert_attention_close(got, want, f"backend step cached={cached} chunk={chunk}")
+
+
+@pytest.mark.parametrize("with_builder_facts", [False, True])
+def test_vllm_backend_continuation_prefill(oracle, golden, with_builder_facts):
+    """Chunks of new tokens over sequences with cached context (and one without)."""
+    _backend_step(oracle, golden, [100, 0, 37], [5, 8, 3], with_builder_facts)
+
+
+@pytest.mark.parametrize("with_builder_facts", [False, True])
+def test_vllm_backend_long_first_chunk_beside_a_short_continuation(oracle, golden, with_builder_facts):
+    """The longest sequence of the step is a first chunk: max_seq_len == max_query_len although
+    another sequence has cached context, which must still be attended."""
+    _backend_step(oracle, golden, [0, 1400], [2048, 100], with_builder_facts)
+
+
+@pytest.mark.parametrize("with_builder_facts", [False, True])
+def test_vllm_backend_mixed_decode_and_prefill_rows(oracle, golden, with_builder_facts):
+    """vLLM's default mixed batches: decode rows ride the paged decode kernel, the prefill rows the
+    dense path, in one step; a one-token prompt (nothing cached) stays on the dense path."""
+    _backend_step(oracle, golden, [500, 0, 37, 1200, 0], [1, 8, 3, 1, 1], with_builder_facts)
+
+
+def test_vllm_backend_pure_first_chunks_use_fresh_kv(oracle, golden):
+    _backend_step(oracle, golden, [0, 0], [33, 70], True)

@@ -8,15 +8,18 @@ methods and cache layout of the reference (turboquant/vllm_backend_fused.py:32-4
 * ``TurboQuantFusedImpl.do_kv_cache_update``: quantizes K and V of the step and scatters them into
   the cache (one launch; bf16/fp16 K/V and int64 slots are read as they are).
 * ``TurboQuantFusedImpl.forward``: decode steps (``max_query_len == 1``) run the paged decode
-  kernel on the quantized cache.  A prefill step whose sequences have nothing cached yet runs
-  FlashAttention on the step's fresh K/V, exactly as the reference does.  A prefill chunk that
-  continues sequences with cached context (which the reference does not handle: its prefill never
-  reads the quantized cache, vllm_backend_fused.py:336-369) first dequantizes the cached tokens
-  into a dense varlen K/V (``tq_dequant_paged``), puts the chunk's fresh K/V behind them and runs
-  the same varlen FlashAttention with bottom-right causal masking.
+  kernel on the quantized cache.  A prefill step whose sequences have nothing cached yet (known
+  from the builder's host-side facts) runs FlashAttention on the step's fresh K/V, exactly as the
+  reference does.  Any other step is a mixed step (``_mixed_step``): its decode rows go through the
+  paged decode kernel, and every other row (first chunks, chunks that continue a sequence with
+  cached context, which the reference does not handle: its prefill never reads the quantized
+  cache, vllm_backend_fused.py:336-369) attends its cached tokens, dequantized into a dense varlen
+  K/V (``tq_dequant_paged``), followed by the chunk's fresh K/V through the same varlen
+  FlashAttention with bottom-right causal masking.
 * ``TurboQuantMetadataBuilder``: the reference's is an empty subclass that sizes a uniform split
-  count on the host; here the split plan is made inside the kernel from ``seq_lens``, so the
-  builder only has to keep the FlashAttention metadata (block table, lengths) as it is.
+  count on the host; here the split plan is made inside the kernel from ``seq_lens``.  The builder
+  adds what only the host knows without a synchronisation (``step_shape``): whether any sequence
+  has cached context, how many rows are decode rows and how many dense K/V rows the others need.
 
 All cache work goes through ``TurboQuantPagedAttention`` (C ABI); a failure raises, there is no
 fallback to another backend for a quantized cache.
@@ -76,7 +79,40 @@ class TurboQuantBackend(FlashAttentionBackend):
 
 
 class TurboQuantMetadataBuilder(FlashAttentionMetadataBuilder):
-    """Split planning needs nothing from the host (see the module docstring)."""
+    """Split planning needs nothing from the host (see the module docstring).  What the host does
+    know at build time, and the kernels cannot tell the Python side without a synchronisation, is
+    the shape of the step: whether any sequence has cached context, which rows are plain decode
+    rows, and how many dense K/V rows the prefill rows need.  ``build`` attaches that as
+    ``tq_step`` to the FlashAttention metadata; ``TurboQuantFusedImpl.forward`` works without it
+    (it then takes the general path with a worst-case buffer)."""
+
+    def build(self, common_prefix_len, common_attn_metadata, fast_build: bool = False):
+        md = super().build(common_prefix_len, common_attn_metadata, fast_build)
+        try:
+            md.tq_step = step_shape(common_attn_metadata)
+        except Exception:          # metadata without host copies: forward falls back to the general path
+            pass
+        return md
+
+
+def step_shape(common):
+    """Host-side facts about a step from vLLM's CommonAttentionMetadata (its CPU copies of the query
+    offsets and sequence lengths): a dict with ``any_cached`` (some sequence attends tokens that are
+    only in the quantized cache), ``num_decode_rows`` (rows with one query token and cached context)
+    and ``dense_rows`` (dense K/V rows the other rows need: the sum of their sequence lengths)."""
+    qsl = common.query_start_loc_cpu
+    n = int(common.num_reqs)
+    q_lens = (qsl[1:n + 1] - qsl[:n]).to(torch.int64)
+    seq = getattr(common, "seq_lens_cpu", None)
+    if seq is None:
+        seq = getattr(common, "_seq_lens_cpu", None)
+    if seq is None:
+        seq = common.seq_lens_cpu_upper_bound
+    seq = seq[:n].to(torch.int64)
+    cached = seq - q_lens
+    is_decode = (q_lens == 1) & (cached > 0)
+    return {"any_cached": bool((cached > 0).any()), "num_decode_rows": int(is_decode.sum()),
+            "dense_rows": int(seq[~is_decode].sum()), "max_prefill_seq": int(seq[~is_decode].max()) if bool((~is_decode).any()) else 0}
 
 
 class TurboQuantFusedImpl(FlashAttentionImpl):
@@ -122,19 +158,23 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
             from vllm.vllm_flash_attn import flash_attn_varlen_func
             if output is None:
                 output = torch.empty_like(query[:n])
-            max_seq_len = getattr(attn_metadata, "max_seq_len", attn_metadata.max_query_len)
-            if max_seq_len > attn_metadata.max_query_len:
-                out = self._continuation_prefill(query[:n], key[:n], value[:n], kv_cache, attn_metadata, max_seq_len,
-                                                 flash_attn_varlen_func)
-                output[:n] = out.to(output.dtype).view(output[:n].shape)
-                return output
-            # first chunk: attention over the fresh K/V of this step; the quantized cache is not read
-            out = flash_attn_varlen_func(query[:n], key[:n], value[:n],
-                                         cu_seqlens_q=attn_metadata.query_start_loc,
-                                         cu_seqlens_k=attn_metadata.query_start_loc,
-                                         max_seqlen_q=attn_metadata.max_query_len,
-                                         max_seqlen_k=attn_metadata.max_query_len,
-                                         softmax_scale=self.scale, causal=True)
+            step = getattr(attn_metadata, "tq_step", None)
+            if step is not None and not step["any_cached"]:
+                # first chunks only: attention over the fresh K/V of this step, as the reference does
+                # (vllm_backend_fused.py:336-369); the quantized cache is not read
+                out = flash_attn_varlen_func(query[:n], key[:n], value[:n],
+                                             cu_seqlens_q=attn_metadata.query_start_loc,
+                                             cu_seqlens_k=attn_metadata.query_start_loc,
+                                             max_seqlen_q=attn_metadata.max_query_len,
+                                             max_seqlen_k=attn_metadata.max_query_len,
+                                             softmax_scale=self.scale, causal=True)
+            else:
+                # Some sequence may have cached context (known from the builder, or not known at all:
+                # the two maxima of the metadata cannot rule it out, a long first chunk hides a short
+                # continuation): decode rows go through the paged decode kernel, every other row
+                # attends its dequantized cached tokens followed by the chunk's fresh K/V.
+                out = self._mixed_step(query[:n], key[:n], value[:n], kv_cache, attn_metadata, step,
+                                       flash_attn_varlen_func)
             output[:n] = out.to(output.dtype).view(output[:n].shape)
             return output
         q = query[:n].view(n, self.num_heads, self.head_size)
@@ -144,36 +184,65 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         self._attn.decode(q, kv_cache, attn_metadata.block_table[:n], attn_metadata.seq_lens[:n], out)
         return output
 
-    def _continuation_prefill(self, query, key, value, kv_cache, md, max_seq_len, flash_attn_varlen_func):
-        """Chunk of new tokens over sequences with cached context.  Sequence b contributes
-        ``seq_lens[b]`` keys: its ``seq_lens[b] - q_len[b]`` cached tokens, dequantized from the
-        cache, then the chunk's own fresh K/V (the chunk is already in the cache as well, quantized;
-        its fresh values are used, as a first chunk would).  No host synchronisation: the dense
-        buffer is sized by the ``batch x max_seq_len`` bound, rows beyond ``cu_k[-1]`` are unused."""
+    def _mixed_step(self, query, key, value, kv_cache, md, step, flash_attn_varlen_func):
+        """A step whose sequences may have cached context: prefill chunks, continuing chunks and
+        decode rows in any mix.  No host synchronisation; every shape comes from the metadata.
+
+        * Decode rows (one query token, cached context) run through the paged decode kernel over
+          the quantized cache: all rows are handed to it with the length of every other row set
+          to zero, and their outputs are dropped.
+        * Every other row b contributes ``seq_lens[b]`` keys to a dense varlen K/V: its cached
+          tokens, dequantized from the cache, then the chunk's own fresh K/V (the chunk is already
+          in the cache as well, quantized; its fresh values are used, as a first chunk would).  The
+          buffer has ``step["dense_rows"]`` rows when the builder attached the step's shape, else
+          the ``batch x max_seq_len`` bound (rows beyond ``cu_k[-1]`` are unused)."""
         dev = query.device
+        n = query.shape[0]
         qsl = md.query_start_loc.to(torch.int32)
         B = qsl.shape[0] - 1
         seq_lens = md.seq_lens[:B].to(torch.int32)
         q_lens = qsl[1:] - qsl[:-1]
         cached = seq_lens - q_lens
-        cu_k = torch.zeros(B + 1, dtype=torch.int32, device=dev)
-        cu_k[1:] = torch.cumsum(seq_lens, 0)
-        rows = B * int(max_seq_len)
-        k_all = torch.empty((rows, self.num_kv_heads, self.head_size), dtype=query.dtype, device=dev)
-        v_all = torch.empty_like(k_all)
-        from . import _cabi
+        is_dec = (q_lens == 1) & (cached > 0)
+        zero = torch.zeros_like(seq_lens)
         bt = md.block_table[:B]
         if bt.dtype != torch.int32:
             bt = bt.to(torch.int32)
-        _cabi.dequant_paged(self._attn._as_bytes(kv_cache), bt.contiguous(), cached.contiguous(), cu_k,
+        bt = bt.contiguous()
+        q3 = query.view(n, self.num_heads, self.head_size)
+        first_tok = qsl[:-1].long()
+
+        # ---- prefill / continuation rows: dense K/V = dequantized cached tokens + fresh chunk -------
+        pf_seq = torch.where(is_dec, zero, seq_lens)
+        pf_cached = torch.where(is_dec, zero, cached)
+        cu_k = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+        cu_k[1:] = torch.cumsum(pf_seq, 0)
+        max_seq_len = int(getattr(md, "max_seq_len", md.max_query_len))
+        if step is not None:
+            rows, max_k = max(step["dense_rows"], 1), max(step["max_prefill_seq"], 1)
+        else:
+            rows, max_k = B * max_seq_len, max_seq_len
+        # one spare row at the end takes the fresh K/V of the decode rows' tokens, which nobody reads
+        k_all = torch.empty((rows + 1, self.num_kv_heads, self.head_size), dtype=query.dtype, device=dev)
+        v_all = torch.empty_like(k_all)
+        from . import _cabi
+        _cabi.dequant_paged(self._attn._as_bytes(kv_cache), bt, pf_cached.contiguous(), cu_k,
                             self._attn.signs(dev), k_all, v_all, max_pages=bt.shape[-1])
-        # fresh rows of the chunk go behind the cached rows of their sequence
-        n = query.shape[0]
+        # the chunk's fresh rows go behind the cached rows of their sequence
         tok = torch.arange(n, device=dev, dtype=torch.int32)
         seq_of = torch.bucketize(tok, qsl[1:], right=True)
-        dest = (cu_k[:-1][seq_of] + cached[seq_of] + (tok - qsl[:-1][seq_of])).long()
+        dest = (cu_k[:-1][seq_of] + pf_cached[seq_of] + (tok - qsl[:-1][seq_of])).long()
+        dest = torch.where(is_dec[seq_of], torch.full_like(dest, rows), dest)
         k_all[dest] = key.view(n, self.num_kv_heads, self.head_size).to(k_all.dtype)
         v_all[dest] = value.view(n, self.num_kv_heads, self.head_size).to(v_all.dtype)
-        return flash_attn_varlen_func(query.view(n, self.num_heads, self.head_size), k_all, v_all,
-                                      cu_seqlens_q=qsl, cu_seqlens_k=cu_k, max_seqlen_q=md.max_query_len,
-                                      max_seqlen_k=int(max_seq_len), softmax_scale=self.scale, causal=True)
+        out = flash_attn_varlen_func(q3, k_all, v_all, cu_seqlens_q=qsl, cu_seqlens_k=cu_k,
+                                     max_seqlen_q=md.max_query_len, max_seqlen_k=max_k,
+                                     softmax_scale=self.scale, causal=True)
+        # ---- decode rows: the paged decode kernel, one query per row, other rows masked out ---------
+        if step is None or step["num_decode_rows"] > 0:
+            dec_lens = torch.where(is_dec, seq_lens, zero).contiguous()
+            q_rows = q3[first_tok].contiguous()
+            dec_out = torch.empty_like(q_rows)
+            self._attn.decode(q_rows, kv_cache, bt, dec_lens, dec_out)
+            out[first_tok] = torch.where(is_dec[:, None, None], dec_out.to(out.dtype), out[first_tok])
+        return out
