@@ -68,7 +68,10 @@ int tq_codebook(int dim, int bits, float* centroids, float* boundaries);
  * k_token_stride / v_token_stride elements between tokens (heads contiguous).  One launch
  * covers K and V.  Codes and norms are bit-identical to TurboQuantMSE.quantize on the CPU.
  * head_dim 128, or 96 (rows of 96 elements, zero-padded to 128 by the rotation; signs has 128
- * entries either way).  signs is a constant of the context, as in the reference (one seeded
+ * entries either way).  Any other head size from 33 to 256 (64 with 48-byte slots, 256 with
+ * 144-byte slots: turboquant/vllm_backend_fused.py:64-72, turboquant/kernel_config.py:75-109)
+ * goes through plain, untuned kernels with the same arithmetic; signs then has next_pow2(head_dim)
+ * entries.  signs is a constant of the context, as in the reference (one seeded
  * vector per process): the kernel reads it ahead of its wait on the preceding kernel, so it must
  * be complete before that kernel is launched.
  * Replaces: torch.ops.turboquant_write.quantize_write_kv_cache
@@ -121,6 +124,10 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *                needs initialising
  *   num_ctas     thread blocks to balance over; 0 = one per SM of the current device
  *
+ * Other head sizes (33..256; 64 and 256 are the reference's other presets) run plain, untuned
+ * kernels behind the same entry points: block_size 16, slot_bytes >= the slot of that head size,
+ * up to 8 query heads per KV head, any number of KV heads, one query per sequence; pass head_dim
+ * to tq_decode_workspace_bytes.  The rest of this paragraph is the tuned path.
  * Supported geometry: head_dim 128, or 96 (q and out rows of 96 elements; the rotation pads them
  * with zeros to 128 and the slot is the same 80 bytes); block_size 16, slot_bytes 80,
  * num_q_heads/num_kv_heads <= 8, num_kv_heads in {1, 2, 4, 8, 16} (one launch) or a larger
@@ -187,6 +194,10 @@ int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int block_size, i
  * stream.  The reference measures this trade (restore over PCIe against re-running the prefill)
  * with a raw copy of a whole slab, pad bytes included (tests/bench_kv_offload.py:23-62). */
 size_t tq_pages_packed_bytes(int n_pages, int block_size, int num_kv_heads);
+/* The same for other slot sizes: 48-byte slots (head size 64) move 36 bytes, 144-byte slots (head
+ * size 256) 136, any other size is moved whole; tq_pages_gather / _scatter pick the payload from
+ * slot_bytes the same way. */
+size_t tq_pages_packed_bytes_for_slot(int n_pages, int block_size, int num_kv_heads, int slot_bytes);
 int tq_pages_gather(const void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads,
                     int slot_bytes, const int32_t* page_ids, int n_pages, void* packed,
                     size_t packed_bytes, void* stream);

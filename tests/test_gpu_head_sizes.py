@@ -1,0 +1,115 @@
+"""Head sizes 64 and 256 (the reference's qwen3-0.6b and gemma-2 presets) and an odd size through
+the paged write, decode, dequantization and page moves: bit-exact writes against the oracle and
+the reference-generated quantizer fixtures, attention against the dequant-attention oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from turboquant_b200 import _cabi, synthetic
+from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape, slot_bytes
+from tests.gpu_util import DEV, assert_attention_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _signs(golden, d):
+    pd = 1 << (d - 1).bit_length()
+    key = f"signs_seed42_d{pd}"
+    return torch.from_numpy(golden[key]) if key in golden.files else synthetic.make_signs(pd, 42)
+
+
+@pytest.mark.parametrize("d", [64, 256])
+def test_write_matches_reference_quantizer_fixture(golden, oracle, d):
+    rows = torch.from_numpy(golden[f"q_rows_d{d}"])
+    n = rows.shape[0] // 8 * 8
+    k = rows[:n].reshape(n // 8, 8, d)
+    sb = slot_bytes(d)
+    assert sb == {64: 48, 256: 144}[d]
+    nb = (n // 8 + 15) // 16
+    cache = torch.zeros((2, nb, 16, 8, sb), dtype=torch.uint8, device=DEV)
+    slots = torch.arange(n // 8, dtype=torch.int64)
+    signs = _signs(golden, d)
+    _cabi.write_kv_cache(cache, k.to(DEV), k.to(DEV), signs.to(DEV), slots.to(DEV), d)
+    got = cache.cpu().numpy()[0].reshape(-1, sb)[:n]
+    np.testing.assert_array_equal(got[:, :d // 2], oracle.low_first_to_cache_order(golden[f"q_packed_d{d}"][:n]))
+    want_n = torch.from_numpy(golden[f"q_norms_d{d}"][:n]).to(torch.float16).numpy()
+    for c in range(d // 64):
+        np.testing.assert_array_equal(got[:, d // 2 + 2 * c:d // 2 + 2 * c + 2].copy().view(np.uint16).reshape(-1),
+                                      want_n.view(np.uint16))
+    assert (got[:, d // 2 + 2 * (d // 64):] == 0).all()              # pad untouched
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 16, 8), (256, 16, 8), (256, 8, 4), (80, 8, 2), (192, 4, 4)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_write_decode_dequant_vs_oracle(oracle, golden, d, hq, hkv, dtype):
+    lens = [1, 47, 0, 300, 1030]
+    case = synthetic.decode_case(seed=200 + d + hq, seq_lens=lens, dtype=dtype, heads=(hq, hkv), head_dim=d)
+    signs = _signs(golden, d)
+    sb = slot_bytes(d)
+    scale = 1.0 / math.sqrt(d)
+    want_cache = np.zeros((2, case.num_blocks, 16, hkv, sb), np.uint8)
+    oracle.write_kv_cache(want_cache, case.k.float().numpy(), case.v.float().numpy(), signs.numpy(),
+                          case.slot_mapping.numpy(), d)
+    attn = TurboQuantPagedAttention(hq, d, scale, hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    assert cache.shape[-1] == sb
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    np.testing.assert_array_equal(cache.cpu().numpy(), want_cache)
+    want, want_lse = oracle.decode_paged(case.q.float().numpy(), want_cache, case.block_table.numpy(),
+                                         case.seq_lens.numpy(), signs.numpy(), scale, return_lse=True)
+    for ctas in (0, 3):
+        attn_c = TurboQuantPagedAttention(hq, d, scale, hkv, num_ctas=ctas)
+        out = torch.full(case.q.shape, float("nan"), dtype=torch.float32, device=DEV)
+        lse = torch.empty(case.q.shape[:2], dtype=torch.float32, device=DEV)
+        attn_c.decode(case.q.to(DEV), cache, case.block_table.to(DEV), case.seq_lens.to(DEV), out, out_lse=lse)
+        torch.cuda.synchronize()
+        assert attn_c.status(len(lens), DEV) == 0
+        got = out.cpu().numpy()
+        assert_attention_close(got, want, f"head size {d}, {hq}/{hkv} heads, ctas={ctas}")
+        assert (got[2] == 0).all()
+        ok = np.isfinite(want_lse)
+        np.testing.assert_allclose(lse.cpu().numpy()[ok], want_lse[ok], atol=2e-3)
+    # bulk dequantization of the cached tokens: bit-identical to the oracle in fp32
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+    k_out, v_out = attn.dequant_cached(cache, case.block_table.to(DEV), case.seq_lens.to(DEV), cu, sum(lens), dtype=torch.float32)
+    torch.cuda.synchronize()
+    at = 0
+    for b, n in enumerate(lens):
+        t = np.arange(n)
+        pages = case.block_table.numpy()[b, t // 16]
+        for which, got_t in ((0, k_out), (1, v_out)):
+            want_rows = oracle.dequant_cache_rows(want_cache[which, pages, t % 16], signs.numpy(), d)
+            np.testing.assert_array_equal(got_t[at:at + n].cpu().numpy(), want_rows)
+        at += n
+
+
+@pytest.mark.parametrize("d", [64, 256])
+def test_page_offload_round_trip(d):
+    hkv = 4
+    attn = TurboQuantPagedAttention(8, d, 1.0 / math.sqrt(d), hkv)
+    g = torch.Generator().manual_seed(d)
+    cache = torch.randint(0, 256, kv_cache_shape(12, 16, hkv, d), dtype=torch.uint8, generator=g).to(DEV)
+    ids = torch.tensor([7, 2, 11], dtype=torch.int32, device=DEV)
+    host = attn.offload_pages(cache, ids)
+    torch.cuda.synchronize()
+    other = torch.zeros_like(cache)
+    dst = torch.tensor([0, 5, 1], dtype=torch.int32, device=DEV)
+    attn.restore_pages(other, dst, host)
+    torch.cuda.synchronize()
+    payload = d // 2 + 2 * (d // 64)
+    a, b = cache.cpu().numpy(), other.cpu().numpy()
+    for s, t in zip((7, 2, 11), (0, 5, 1)):
+        np.testing.assert_array_equal(b[:, t, ..., :payload], a[:, s, ..., :payload])
+    assert (b[:, [2, 3, 4, 6]] == 0).all()
+
+
+def test_rejected_geometries():
+    with pytest.raises(_cabi.TurboQuantError, match="head_size"):
+        TurboQuantPagedAttention(8, 16, 0.25, 8)
+    attn = TurboQuantPagedAttention(32, 64, 0.125, 2)               # 16 query heads per KV head
+    cache = torch.zeros(kv_cache_shape(2, 16, 2, 64), dtype=torch.uint8, device=DEV)
+    q = torch.zeros(1, 32, 64, dtype=torch.float16, device=DEV)
+    with pytest.raises(_cabi.TurboQuantError, match="query heads per KV head"):
+        attn.decode(q, cache, torch.zeros(1, 2, dtype=torch.int32, device=DEV), torch.ones(1, dtype=torch.int32, device=DEV))

@@ -32,7 +32,7 @@ EXPORTS = (
     "tq_decode_paged_static", "tq_decode_paged_multi", "tq_exchange_bytes", "tq_decode_paged_exchange",
     "tq_dequant_paged", "tq_pages_packed_bytes", "tq_pages_gather", "tq_pages_scatter",
     "tq_decode_max_query_columns", "tq_set_exchange_wait_limit", "tq_decode_static_status", "tq_fault_counts",
-    "tq_write_guard_stats",
+    "tq_write_guard_stats", "tq_pages_packed_bytes_for_slot",
 )
 
 _lib = None
@@ -147,8 +147,9 @@ def write_kv_cache(kv_cache: torch.Tensor, key: torch.Tensor, value: torch.Tenso
             raise TurboQuantError(f"{n} must be [>=num_tokens, {H}, {head_dim}], got {tuple(t.shape)}")
         if t.stride(2) != 1 or t.stride(1) != head_dim:
             raise TurboQuantError(f"{n}: heads of one token must be contiguous")
-    if signs.dtype != torch.float32 or signs.numel() < 128 or not signs.is_contiguous():
-        raise TurboQuantError("signs must be contiguous fp32 of padded head size")
+    padded = 1 << (head_dim - 1).bit_length()
+    if signs.dtype != torch.float32 or signs.numel() < padded or not signs.is_contiguous():
+        raise TurboQuantError(f"signs must be contiguous fp32 with {padded} entries (the padded head size)")
     if slot_mapping.dtype not in (torch.int32, torch.int64) or not slot_mapping.is_contiguous():
         raise TurboQuantError("slot_mapping must be contiguous int32 or int64")
     if debug_checks():
@@ -335,10 +336,10 @@ def dequant_paged(kv_cache, page_indices, seq_lens, cu_seqlens, signs, k_out, v_
     return k_out, v_out
 
 
-def pages_packed_bytes(n_pages: int, block_size: int, num_kv_heads: int) -> int:
-    f = lib().tq_pages_packed_bytes
+def pages_packed_bytes(n_pages: int, block_size: int, num_kv_heads: int, slot_bytes: int = 80) -> int:
+    f = lib().tq_pages_packed_bytes_for_slot
     f.restype = ctypes.c_size_t
-    return f(ctypes.c_int(n_pages), ctypes.c_int(block_size), ctypes.c_int(num_kv_heads))
+    return f(ctypes.c_int(n_pages), ctypes.c_int(block_size), ctypes.c_int(num_kv_heads), ctypes.c_int(slot_bytes))
 
 
 def _pages_args(kv_cache, page_ids, packed):

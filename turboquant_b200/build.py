@@ -28,6 +28,7 @@ UNITS = {
     "tq_decode.cu": [],
     "tq_dequant.cu": ["-fmad=false"],
     "tq_pages.cu": [],
+    "tq_generic.cu": ["-fmad=false"],
 }
 
 

@@ -998,6 +998,12 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
 }
 
 int device_sm_count(int* out);
+size_t generic_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim, int num_ctas);
+int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                   const void* kv_cache, int64_t num_blocks, int block_size, int slot_bytes, const int32_t* page_indices,
+                   const int32_t* page_indptr, int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
+                   const float* signs, float sm_scale, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                   float* out_lse, int emit_rotated, int num_ctas, void* stream);
 
 static thread_local cudaEvent_t g_events[3] = {nullptr, nullptr, nullptr};
 static int g_exchange_spin_limit = kExchangeSpinLimit;
@@ -1080,8 +1086,15 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
                        "exchange buffer %d is null or not 256-byte aligned", w);
     }
     TQ_REQUIRE(q && kv_cache && page_indices && seq_lens && signs && workspace && out, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == kHeadDim || head_dim == 96, TQ_ERR_UNSUPPORTED,
-               "decode supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
+    if (head_dim != kHeadDim && head_dim != 96) {  // other head sizes (64, 256, ...): the plain kernels
+        TQ_REQUIRE(nq == 1 && !x, TQ_ERR_UNSUPPORTED,
+                   "head size %d: one query per sequence and no KV-split exchange (those are built for padded size 128)", head_dim);
+        TQ_REQUIRE(q_dtype >= TQ_F32 && q_dtype <= TQ_BF16 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad dtype");
+        TQ_REQUIRE(((uintptr_t)workspace % 256) == 0, TQ_ERR_INVALID, "workspace must be 256-byte aligned");
+        return generic_decode(q, q_dtype, batch, real_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks, block_size,
+                              slot_bytes, page_indices, page_indptr, max_pages, seq_lens, kv_begin, kv_end, signs, sm_scale,
+                              workspace, workspace_bytes, out, out_dtype, out_lse, emit_rotated, num_ctas, stream);
+    }
     TQ_REQUIRE(block_size == kPageTokens, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
     TQ_REQUIRE(slot_bytes == kSlotBytes, TQ_ERR_UNSUPPORTED, "decode supports 80-byte slots, got %d", slot_bytes);
     TQ_REQUIRE(single_launch(num_kv_heads) || (num_kv_heads > 8 && num_kv_heads % 4 == 0), TQ_ERR_UNSUPPORTED,
@@ -1234,8 +1247,9 @@ extern "C" int tq_decode_max_query_columns(void) { return 8; }
 
 extern "C" size_t tq_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads,
                                             int head_dim, int num_ctas) {
-    (void)head_dim;
     if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) return 0;
+    if (head_dim != tq::kHeadDim && head_dim != 96 && head_dim > 0)
+        return head_dim > 32 && head_dim <= 256 ? tq::generic_workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_ctas) : 0;
     if (!tq::single_launch(num_kv_heads) && !(num_kv_heads > 8 && num_kv_heads % 4 == 0)) return 0;
     int ctas = 0;
     if (tq::resolve_ctas(num_ctas, &ctas) != TQ_OK) return 0;

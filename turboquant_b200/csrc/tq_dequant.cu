@@ -315,8 +315,18 @@ static int launch_dequant(const DequantParams& p, dim3 grid, cudaStream_t stream
 }
 void host_codebook(int dim, int bits, float* centroids, float* boundaries);
 
+int generic_dequant(const void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads, int slot_bytes,
+                    const int32_t* page_indices, const int32_t* page_indptr, int max_pages, const int32_t* seq_lens,
+                    const int32_t* cu_seqlens, int batch, const float* signs, int head_dim, void* k_out, void* v_out,
+                    int out_dtype, int64_t out_token_stride, void* stream);
+int generic_fault_counts(int32_t* write_dropped, int32_t* dequant_skipped);
+
 int dequant_fault_count(int32_t* out) {
-    TQ_CUDA(cudaMemcpyFromSymbol(out, g_dequant_skipped, sizeof(int32_t)));
+    int32_t a = 0, b = 0, c = 0;
+    TQ_CUDA(cudaMemcpyFromSymbol(&a, g_dequant_skipped, sizeof(int32_t)));
+    int rc = generic_fault_counts(&b, &c);
+    if (rc != TQ_OK) return rc;
+    *out = a + c;
     return TQ_OK;
 }
 
@@ -331,8 +341,12 @@ extern "C" int tq_dequant_paged(const void* kv_cache, int64_t num_blocks, int bl
     TQ_REQUIRE(batch >= 0 && num_blocks >= 0, TQ_ERR_INVALID, "negative size");
     if (batch == 0 || max_pages == 0) return TQ_OK;
     TQ_REQUIRE(kv_cache && page_indices && seq_lens && cu_seqlens && signs && k_out && v_out, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == kDqDim || head_dim == 96, TQ_ERR_UNSUPPORTED,
-               "bulk dequantization supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
+    if (head_dim != kDqDim && head_dim != 96) {  // other head sizes (64, 256, ...): the plain kernel
+        TQ_REQUIRE(num_kv_heads >= 1 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16 &&
+                       out_token_stride >= (int64_t)num_kv_heads * head_dim, TQ_ERR_INVALID, "bad geometry");
+        return generic_dequant(kv_cache, num_blocks, block_size, num_kv_heads, slot_bytes, page_indices, page_indptr, max_pages,
+                               seq_lens, cu_seqlens, batch, signs, head_dim, k_out, v_out, out_dtype, out_token_stride, stream);
+    }
     TQ_REQUIRE(slot_bytes >= 80 && slot_bytes % 16 == 0, TQ_ERR_INVALID, "slot_bytes must be a multiple of 16 and >= 80");
     TQ_REQUIRE(block_size >= 1 && num_kv_heads >= 1 && max_pages >= 1 && batch >= 1, TQ_ERR_INVALID, "bad geometry");
     TQ_REQUIRE(out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad out_dtype");

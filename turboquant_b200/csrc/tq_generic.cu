@@ -1,0 +1,603 @@
+// Paged cache write, decode attention, merge and bulk dequantization for head sizes whose padded
+// size is not 128 (64: 48-byte slots, 256: 144-byte slots; any head size up to 256).
+//
+// The reference declares these geometries (turboquant/kernel_config.py:75-109: qwen3-0.6b with
+// head size 64, gemma-2 with 256; slot size turboquant/vllm_backend_fused.py:64-72: 32 code bytes
+// and one fp16 norm per 64 padded dims, rounded up to 16 bytes) but its decode op rejects
+// everything except 128 (csrc/src/decode_v5_tc_binding.cu:779).  These kernels are the plain
+// formulation of the same arithmetic -- one warp per row, shared-memory butterflies, fp32 math --
+// with the interfaces, the split-KV workspace contract and the parity bars of the tuned 128-wide
+// kernels; they are not tuned for bandwidth.  Quantizer arithmetic as in tq_flat.cu (the torch
+// evaluation order), compiled with -fmad=false.
+#include <cmath>
+#include <cstring>
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+constexpr int kGenMaxDim = 256;
+constexpr int kGenWarps = 4;
+constexpr int kGenMaxGroup = 8;
+constexpr int kGenPage = 16;
+constexpr int kGenStatusSeqTooLong = 4, kGenStatusBadPage = 5;
+
+struct GenGeom {
+    int head_dim, padded, qbytes, dc, slot_bytes;
+};
+
+__host__ __device__ inline int gen_next_pow2(int n) {
+    int p = 1;
+    while (p < n) p <<= 1;
+    return p;
+}
+
+static GenGeom make_geom(int head_dim, int slot_bytes) {
+    GenGeom g;
+    g.head_dim = head_dim;
+    g.padded = gen_next_pow2(head_dim);  // 64, 128 or 256: callers admit head sizes 33..256 only
+    g.dc = g.padded / 64;
+    g.qbytes = g.padded / 2;
+    g.slot_bytes = slot_bytes;
+    return g;
+}
+
+// butterflies h = 1 .. padded/2 on a shared-memory row, by one warp
+__device__ __forceinline__ void gen_warp_fwht(float* buf, int padded, int lane) {
+    for (int h = 1; h < padded; h <<= 1) {
+        for (int idx = lane; idx < padded / 2; idx += 32) {
+            const int i = (idx / h) * 2 * h + (idx % h);
+            const float a = buf[i], b = buf[i + h];
+            buf[i] = __fadd_rn(a, b);
+            buf[i + h] = __fsub_rn(a, b);
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// cache write
+// ---------------------------------------------------------------------------------------------
+struct GenWriteParams {
+    uint8_t* kv_cache;
+    const void* src[2];
+    int64_t token_stride[2];
+    const void* slot_mapping;
+    const float* signs;
+    int64_t num_tokens, slab_bytes, total_slots;
+    int num_kv_heads, slot_is_i64, zero_pad;
+    GenGeom g;
+    float scale;
+    float boundaries[15];
+};
+
+static __device__ int32_t g_gen_write_dropped = 0;
+
+template <typename T>
+__global__ void __launch_bounds__(kGenWarps * 32) write_generic_kernel(const __grid_constant__ GenWriteParams p) {
+    __shared__ float buf_s[kGenWarps][kGenMaxDim];
+    __shared__ uint8_t idx_s[kGenWarps][kGenMaxDim];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* buf = buf_s[warp];
+    uint8_t* idx = idx_s[warp];
+    const int H = p.num_kv_heads, pd = p.g.padded, hd = p.g.head_dim;
+    const int64_t rows = 2 * p.num_tokens * H;
+    for (int64_t r = (int64_t)blockIdx.x * kGenWarps + warp; r < rows; r += (int64_t)gridDim.x * kGenWarps) {
+        const int which = (int)(r & 1);
+        const int64_t th = r >> 1, t = th / H;
+        const int h = (int)(th - t * H);
+        int64_t slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
+                                     : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
+        if (slot >= p.total_slots) {
+            if (lane == 0 && h == 0 && which == 0) atomicAdd(&g_gen_write_dropped, 1);
+            slot = -1;
+        }
+        if (slot < 0) continue;
+        const T* row = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * hd;
+        for (int i = lane; i < pd; i += 32) buf[i] = i < hd ? to_f32(row[i]) : 0.0f;
+        __syncwarp();
+        // norm in the reference order: eight interleaved accumulators, combined left to right, then the tail
+        float acc = 0.0f;
+        const int full = hd & ~7;
+        if (lane < 8)
+            for (int j = lane; j < full; j += 8) acc = __fadd_rn(acc, __fmul_rn(buf[j], buf[j]));
+        float s = 0.0f;
+        for (int k = 0; k < 8; k++) {
+            const float a = __shfl_sync(0xffffffffu, acc, k);
+            s = k == 0 ? a : __fadd_rn(s, a);
+        }
+        for (int j = full; j < hd; j++) s = __fadd_rn(s, __fmul_rn(buf[j], buf[j]));
+        float norm = __fsqrt_rn(s);
+        if (!(norm >= 1e-8f)) norm = (norm != norm) ? __uint_as_float(0x7fc00000u) : 1e-8f;
+        for (int i = lane; i < pd; i += 32)
+            buf[i] = i < hd ? __fmul_rn(__fdiv_rn(buf[i], norm), p.signs[i]) : 0.0f;
+        __syncwarp();
+        gen_warp_fwht(buf, pd, lane);
+        for (int i = lane; i < pd; i += 32) {
+            const float y = __fmul_rn(buf[i], p.scale);
+            int c = 0;
+            for (int k = 0; k < 15; k++) c += (p.boundaries[k] < y) ? 1 : 0;
+            if (y != y) c = 15;
+            idx[i] = (uint8_t)c;
+        }
+        __syncwarp();
+        uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)slot * H + h) * p.g.slot_bytes;
+        for (int b = lane; b < p.g.qbytes; b += 32) dst[b] = (uint8_t)((idx[2 * b] << 4) | idx[2 * b + 1]);
+        const uint16_t nh = (norm != norm) ? (uint16_t)0x7e00u : __half_as_ushort(__float2half_rn(norm));
+        if (lane < p.g.dc) *reinterpret_cast<uint16_t*>(dst + p.g.qbytes + 2 * lane) = nh;
+        if (p.zero_pad)
+            for (int b = p.g.qbytes + 2 * p.g.dc + lane; b < p.g.slot_bytes; b += 32) dst[b] = 0;
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode: one block per (split, sequence, KV head), four warps striding over the split's tokens
+// ---------------------------------------------------------------------------------------------
+struct GenDecodeParams {
+    const void* q;
+    const uint8_t* kv_cache;
+    const int32_t* page_indices;
+    const int32_t* page_indptr;
+    const int32_t* seq_lens;
+    const float* signs;
+    int32_t* header;       // workspace word 0: sticky status
+    float* partial_lse;    // [batch][splits][num_q_heads], base 2
+    float* partial_o;      // [batch][splits][num_q_heads][padded], normalized, rotated domain
+    int64_t slab_bytes, num_blocks, kv_begin, kv_end;
+    int batch, num_q_heads, num_kv_heads, group, max_pages, q_dtype, splits;
+    GenGeom g;
+    float score_scale;     // sm_scale * log2(e)
+    float scale;           // 1 / sqrt(padded)
+    float centroids[16];   // already divided by sqrt(padded)
+};
+
+__device__ __forceinline__ float gen_load(const void* q, int dtype, int64_t i) {
+    if (dtype == TQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[i]);
+    if (dtype == TQ_F16) return __half2float(reinterpret_cast<const __half*>(q)[i]);
+    return reinterpret_cast<const float*>(q)[i];
+}
+
+__global__ void __launch_bounds__(kGenWarps * 32) decode_generic_kernel(const __grid_constant__ GenDecodeParams p) {
+    extern __shared__ float gsm[];
+    const int pd = p.g.padded, G = p.group;
+    float* q_s = gsm;                               // [G][pd] rotated queries
+    float* o_s = gsm + kGenMaxGroup * kGenMaxDim;   // [warps][G][pd]
+    __shared__ float m_s[kGenWarps][kGenMaxGroup], l_s[kGenWarps][kGenMaxGroup];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+
+    // window of this split, in pages
+    int64_t len = p.seq_lens[b];
+    if (p.kv_end >= 0 && p.kv_end < len) len = p.kv_end;
+    const int64_t begin = p.kv_begin > 0 ? p.kv_begin : 0;
+    const int first_page = (int)(begin / kGenPage);
+    const int last_page = (int)((len + kGenPage - 1) / kGenPage);
+    int npages = last_page > first_page ? last_page - first_page : 0;
+    const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
+    const int have = p.page_indptr ? p.page_indptr[b + 1] - p.page_indptr[b] : p.max_pages;
+    if (npages > 0 && first_page + npages > have) {  // the table cannot back this length: read nothing
+        if (tid == 0) atomicExch(&p.header[0], kGenStatusSeqTooLong);
+        npages = 0;
+    }
+    const int per = (npages + p.splits - 1) / p.splits;
+    const int pg0 = first_page + split * per;
+    const int pg1 = min(first_page + npages, pg0 + per);
+
+    // rotate the group's queries: signs, butterflies, 1/sqrt(pd)
+    for (int i = tid; i < G * pd; i += blockDim.x) {
+        const int g = i / pd, d = i - g * pd;
+        q_s[i] = d < p.g.head_dim
+                     ? gen_load(p.q, p.q_dtype, ((int64_t)b * p.num_q_heads + h * G + g) * p.g.head_dim + d) * p.signs[d]
+                     : 0.0f;
+    }
+    __syncthreads();
+    for (int hh = 1; hh < pd; hh <<= 1) {
+        for (int i = tid; i < G * pd / 2; i += blockDim.x) {
+            const int g = i / (pd / 2), idx = i - g * (pd / 2);
+            const int j = (idx / hh) * 2 * hh + (idx % hh);
+            float* row = q_s + g * pd;
+            const float a = row[j], c = row[j + hh];
+            row[j] = a + c;
+            row[j + hh] = a - c;
+        }
+        __syncthreads();
+    }
+    for (int i = tid; i < G * pd; i += blockDim.x) q_s[i] *= p.scale;
+    __syncthreads();
+
+    const int bpl = p.g.qbytes / 32;  // code bytes per lane: 1, 2 or 4 (bytes lane, lane + 32, ...)
+    float m[kGenMaxGroup], l[kGenMaxGroup], o[kGenMaxGroup][8];
+#pragma unroll
+    for (int g = 0; g < kGenMaxGroup; g++) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[g][e] = 0.0f;
+    }
+    bool bad_page = false;
+    for (int pg = pg0; pg < pg1; pg++) {
+        const int64_t page = p.page_indices[tbl + pg];
+        if ((uint64_t)page >= (uint64_t)p.num_blocks) {  // never form an address from it
+            bad_page = true;
+            continue;
+        }
+        for (int e = warp; e < kGenPage; e += kGenWarps) {
+            const int64_t t = (int64_t)pg * kGenPage + e;
+            if (t < begin || t >= len) continue;
+            const uint8_t* ks = p.kv_cache + ((size_t)(page * kGenPage + e) * p.num_kv_heads + h) * p.g.slot_bytes;
+            const uint8_t* vs = ks + p.slab_bytes;
+            const float kn = __half2float(*reinterpret_cast<const __half*>(ks + p.g.qbytes));
+            const float vn = __half2float(*reinterpret_cast<const __half*>(vs + p.g.qbytes));
+            float kd[8], vd[8];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (j < bpl) {
+                    const uint8_t kb = ks[lane + 32 * j], vb = vs[lane + 32 * j];
+                    kd[2 * j] = p.centroids[kb >> 4] * kn;
+                    kd[2 * j + 1] = p.centroids[kb & 15] * kn;
+                    vd[2 * j] = p.centroids[vb >> 4] * vn;
+                    vd[2 * j + 1] = p.centroids[vb & 15] * vn;
+                } else {
+                    kd[2 * j] = kd[2 * j + 1] = vd[2 * j] = vd[2 * j + 1] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < kGenMaxGroup; g++) {
+                if (g >= G) break;
+                const float* qr = q_s + g * pd;
+                float sc = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (j < bpl) {
+                        const int d = 2 * (lane + 32 * j);
+                        sc += qr[d] * kd[2 * j] + qr[d + 1] * kd[2 * j + 1];
+                    }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, off);
+                sc *= p.score_scale;
+                const float m_new = fmaxf(m[g], sc);
+                const float corr = exp2f(m[g] - m_new), w = exp2f(sc - m_new);
+                m[g] = m_new;
+                l[g] = l[g] * corr + w;
+#pragma unroll
+                for (int e2 = 0; e2 < 8; e2++) o[g][e2] = o[g][e2] * corr + w * vd[e2];
+            }
+        }
+    }
+    if (bad_page && lane == 0) atomicExch(&p.header[0], kGenStatusBadPage);
+    // combine the four warps
+#pragma unroll
+    for (int g = 0; g < kGenMaxGroup; g++) {
+        if (g >= G) break;
+        if (lane == 0) {
+            m_s[warp][g] = m[g];
+            l_s[warp][g] = l[g];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (j < bpl) {
+                const int d = 2 * (lane + 32 * j);
+                o_s[(warp * G + g) * pd + d] = o[g][2 * j];
+                o_s[(warp * G + g) * pd + d + 1] = o[g][2 * j + 1];
+            }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * pd; i += blockDim.x) {
+        const int g = i / pd, d = i - g * pd;
+        float mm = -INFINITY;
+        for (int w = 0; w < kGenWarps; w++) mm = fmaxf(mm, m_s[w][g]);
+        float ll = 0.0f, acc = 0.0f;
+        if (mm > -INFINITY) {
+            for (int w = 0; w < kGenWarps; w++) {
+                const float sc = exp2f(m_s[w][g] - mm);
+                if (sc > 0.0f) {
+                    ll += sc * l_s[w][g];
+                    acc += sc * o_s[(w * G + g) * pd + d];
+                }
+            }
+        }
+        const int64_t row = ((int64_t)b * p.splits + split) * p.num_q_heads + h * G + g;
+        p.partial_o[row * pd + d] = ll > 0.0f ? acc / ll : 0.0f;
+        if (d == 0) p.partial_lse[row] = ll > 0.0f ? mm + log2f(ll) : -INFINITY;
+    }
+}
+
+struct GenMergeParams {
+    const float* partial_o;
+    const float* partial_lse;
+    const float* signs;
+    void* out;
+    float* out_lse;
+    int num_q_heads, splits, out_dtype, emit_rotated;
+    GenGeom g;
+    float scale;
+};
+
+// one block of `padded` threads per (sequence, query head)
+__global__ void __launch_bounds__(kGenMaxDim) merge_generic_kernel(const __grid_constant__ GenMergeParams p) {
+    __shared__ float buf[kGenMaxDim];
+    const int d = threadIdx.x, pd = p.g.padded;
+    const int64_t b = blockIdx.x;
+    const int hq = blockIdx.y;
+    float mm = -INFINITY;
+    for (int s = 0; s < p.splits; s++) mm = fmaxf(mm, p.partial_lse[(b * p.splits + s) * p.num_q_heads + hq]);
+    float wsum = 0.0f, acc = 0.0f;
+    if (mm > -INFINITY) {
+        for (int s = 0; s < p.splits; s++) {
+            const int64_t row = (b * p.splits + s) * p.num_q_heads + hq;
+            const float w = exp2f(p.partial_lse[row] - mm);
+            if (w > 0.0f) {
+                wsum += w;
+                acc += w * p.partial_o[row * pd + d];
+            }
+        }
+    }
+    float o = wsum > 0.0f ? acc / wsum : 0.0f;
+    const float lse2 = wsum > 0.0f ? mm + log2f(wsum) : -INFINITY;
+    const int64_t orow = b * p.num_q_heads + hq;
+    if (p.emit_rotated) {
+        reinterpret_cast<float*>(p.out)[orow * pd + d] = o;
+        if (p.out_lse && d == 0) p.out_lse[orow] = lse2;
+        return;
+    }
+    buf[d] = o;
+    __syncthreads();
+    for (int h = 1; h < pd; h <<= 1) {
+        const float a = buf[d & ~h], c = buf[d | h];
+        __syncthreads();
+        buf[d] = (d & h) ? a - c : a + c;
+        __syncthreads();
+    }
+    o = buf[d] * p.scale * p.signs[d];
+    if (d < p.g.head_dim) {
+        const int64_t at = orow * p.g.head_dim + d;
+        if (p.out_dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(o);
+        else if (p.out_dtype == TQ_F16) reinterpret_cast<__half*>(p.out)[at] = __float2half_rn(o);
+        else reinterpret_cast<float*>(p.out)[at] = o;
+    }
+    if (p.out_lse && d == 0) p.out_lse[orow] = lse2 * 0.6931471805599453f;
+}
+
+// ---------------------------------------------------------------------------------------------
+// bulk dequantization: one warp per (sequence, token, head, K / V)
+// ---------------------------------------------------------------------------------------------
+struct GenDequantParams {
+    const uint8_t* kv_cache;
+    const int32_t* page_indices;
+    const int32_t* page_indptr;
+    const int32_t* seq_lens;
+    const int32_t* cu_seqlens;
+    const float* signs;
+    void* out[2];
+    int64_t slab_bytes, num_blocks, out_token_stride;
+    int batch, max_pages, num_kv_heads, out_dtype;
+    GenGeom g;
+    float scale;
+    float centroids[16];
+};
+
+static __device__ int32_t g_gen_dequant_skipped = 0;
+
+__global__ void __launch_bounds__(kGenWarps * 32) dequant_generic_kernel(const __grid_constant__ GenDequantParams p) {
+    __shared__ float buf_s[kGenWarps][kGenMaxDim];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* buf = buf_s[warp];
+    const int H = p.num_kv_heads, pd = p.g.padded;
+    const int64_t per_seq = (int64_t)p.max_pages * kGenPage * H * 2;
+    const int64_t items = per_seq * p.batch;
+    for (int64_t it = (int64_t)blockIdx.x * kGenWarps + warp; it < items; it += (int64_t)gridDim.x * kGenWarps) {
+        const int b = (int)(it / per_seq);
+        int64_t rem = it - (int64_t)b * per_seq;
+        const int which = (int)(rem & 1);
+        rem >>= 1;
+        const int h = (int)(rem % H);
+        const int64_t t = rem / H;
+        if (t >= p.seq_lens[b]) continue;
+        const int pg = (int)(t / kGenPage), e = (int)(t % kGenPage);
+        const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
+        const bool listed = !p.page_indptr || tbl + pg < (int64_t)p.page_indptr[b + 1];
+        const int64_t page = listed ? (int64_t)p.page_indices[tbl + pg] : -1;
+        if ((uint64_t)page >= (uint64_t)p.num_blocks) {
+            if (lane == 0 && h == 0 && which == 0 && e == 0) atomicAdd(&g_gen_dequant_skipped, 1);
+            continue;
+        }
+        const uint8_t* slot = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)(page * kGenPage + e) * H + h) * p.g.slot_bytes;
+        for (int i = lane; i < p.g.qbytes; i += 32) {
+            const uint8_t c = slot[i];
+            buf[2 * i] = p.centroids[c >> 4];
+            buf[2 * i + 1] = p.centroids[c & 15];
+        }
+        __syncwarp();
+        gen_warp_fwht(buf, pd, lane);
+        const float norm = __half2float(*reinterpret_cast<const __half*>(slot + p.g.qbytes));
+        const int64_t orow = ((int64_t)p.cu_seqlens[b] + t) * p.out_token_stride + (int64_t)h * p.g.head_dim;
+        for (int d = lane; d < p.g.head_dim; d += 32) {
+            const float v = __fmul_rn(__fmul_rn(__fmul_rn(buf[d], p.scale), p.signs[d]), norm);
+            if (p.out_dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(p.out[which])[orow + d] = __float2bfloat16_rn(v);
+            else if (p.out_dtype == TQ_F16) reinterpret_cast<__half*>(p.out[which])[orow + d] = __float2half_rn(v);
+            else reinterpret_cast<float*>(p.out[which])[orow + d] = v;
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side (called from the C-ABI entry points when the geometry is not the 128-wide one)
+// ---------------------------------------------------------------------------------------------
+int device_sm_count(int* out);
+
+int generic_slot_bytes(int head_dim) {
+    const int pd = gen_next_pow2(head_dim);
+    const int dc = pd / 64;
+    return (dc * 32 + dc * 2 + 15) & ~15;
+}
+
+int generic_write(void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads, int slot_bytes, const void* key,
+                  const void* value, int in_dtype, int64_t num_tokens, int64_t k_token_stride, int64_t v_token_stride,
+                  const float* signs, const void* slot_mapping, int slot_dtype, int head_dim, int flags, void* stream) {
+    TQ_REQUIRE(head_dim > 32 && head_dim <= kGenMaxDim, TQ_ERR_UNSUPPORTED, "head_dim must be 33..%d, got %d", kGenMaxDim, head_dim);
+    TQ_REQUIRE(slot_bytes >= generic_slot_bytes(head_dim), TQ_ERR_INVALID, "slot_bytes %d is smaller than head size %d needs (%d)",
+               slot_bytes, head_dim, generic_slot_bytes(head_dim));
+    GenWriteParams p{};
+    p.kv_cache = static_cast<uint8_t*>(kv_cache);
+    p.src[0] = key;
+    p.src[1] = value;
+    p.token_stride[0] = k_token_stride;
+    p.token_stride[1] = v_token_stride;
+    p.slot_mapping = slot_mapping;
+    p.signs = signs;
+    p.num_tokens = num_tokens;
+    p.slab_bytes = num_blocks * block_size * (int64_t)num_kv_heads * slot_bytes;
+    p.total_slots = num_blocks * (int64_t)block_size;
+    p.num_kv_heads = num_kv_heads;
+    p.slot_is_i64 = slot_dtype == TQ_I64;
+    p.zero_pad = (flags & TQ_WRITE_ZERO_PAD) != 0;
+    p.g = make_geom(head_dim, slot_bytes);
+    p.scale = (float)(1.0 / std::sqrt((double)p.g.padded));
+    float cen[16];
+    host_codebook(p.g.padded, 4, cen, p.boundaries);
+    const int64_t rows = 2 * num_tokens * num_kv_heads;
+    const int64_t blocks = (rows + kGenWarps - 1) / kGenWarps;
+    const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (in_dtype) {
+        case TQ_F32: write_generic_kernel<float><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        case TQ_F16: write_generic_kernel<__half><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        default: write_generic_kernel<__nv_bfloat16><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+    }
+    TQ_CUDA(cudaGetLastError());
+    return TQ_OK;
+}
+
+static int generic_splits(int batch, int num_kv_heads, int num_ctas) {
+    int ctas = num_ctas;
+    if (ctas <= 0 && device_sm_count(&ctas) != TQ_OK) ctas = 148;
+    int s = (4 * ctas) / (batch * num_kv_heads > 0 ? batch * num_kv_heads : 1);
+    return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
+
+size_t generic_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim, int num_ctas) {
+    const int pd = make_geom(head_dim, 0).padded;
+    const size_t rows = (size_t)batch * generic_splits(batch, num_kv_heads, num_ctas) * num_q_heads;
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    return 256 + up(rows * sizeof(float)) + up(rows * pd * sizeof(float));
+}
+
+int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                   const void* kv_cache, int64_t num_blocks, int block_size, int slot_bytes, const int32_t* page_indices,
+                   const int32_t* page_indptr, int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
+                   const float* signs, float sm_scale, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
+                   float* out_lse, int emit_rotated, int num_ctas, void* stream) {
+    TQ_REQUIRE(head_dim > 32 && head_dim <= kGenMaxDim, TQ_ERR_UNSUPPORTED, "head_dim must be 33..%d, got %d", kGenMaxDim, head_dim);
+    TQ_REQUIRE(block_size == kGenPage, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
+    TQ_REQUIRE(slot_bytes >= generic_slot_bytes(head_dim), TQ_ERR_INVALID, "slot_bytes %d is smaller than head size %d needs (%d)",
+               slot_bytes, head_dim, generic_slot_bytes(head_dim));
+    TQ_REQUIRE(num_kv_heads >= 1 && num_q_heads % num_kv_heads == 0 && num_q_heads / num_kv_heads <= kGenMaxGroup,
+               TQ_ERR_UNSUPPORTED, "query heads per KV head must be 1..%d", kGenMaxGroup);
+    TQ_REQUIRE(kv_begin >= 0 && kv_begin % kGenPage == 0, TQ_ERR_INVALID, "kv_begin must be a multiple of 16");
+    TQ_REQUIRE(page_indptr || max_pages > 0, TQ_ERR_INVALID, "max_pages must be positive for a dense block table");
+    TQ_REQUIRE(num_blocks >= 1, TQ_ERR_INVALID, "the cache has no pages");
+    TQ_REQUIRE(workspace_bytes >= generic_workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_ctas), TQ_ERR_WORKSPACE,
+               "workspace too small: %zu < %zu", workspace_bytes,
+               generic_workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_ctas));
+    GenDecodeParams p{};
+    p.g = make_geom(head_dim, slot_bytes);
+    p.splits = generic_splits(batch, num_kv_heads, num_ctas);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    const size_t rows = (size_t)batch * p.splits * num_q_heads;
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    p.header = reinterpret_cast<int32_t*>(ws);
+    p.partial_lse = reinterpret_cast<float*>(ws + 256);
+    p.partial_o = reinterpret_cast<float*>(ws + 256 + up(rows * sizeof(float)));
+    p.q = q;
+    p.kv_cache = static_cast<const uint8_t*>(kv_cache);
+    p.page_indices = page_indices;
+    p.page_indptr = page_indptr;
+    p.seq_lens = seq_lens;
+    p.signs = signs;
+    p.slab_bytes = num_blocks * (int64_t)block_size * num_kv_heads * slot_bytes;
+    p.num_blocks = num_blocks;
+    p.kv_begin = kv_begin;
+    p.kv_end = kv_end;
+    p.batch = batch;
+    p.num_q_heads = num_q_heads;
+    p.num_kv_heads = num_kv_heads;
+    p.group = num_q_heads / num_kv_heads;
+    p.max_pages = max_pages;
+    p.q_dtype = q_dtype;
+    p.score_scale = (float)((double)sm_scale * 1.4426950408889634);
+    p.scale = (float)(1.0 / std::sqrt((double)p.g.padded));
+    float bnd[15];
+    host_codebook(p.g.padded, 4, p.centroids, bnd);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t smem = (size_t)(kGenMaxGroup * kGenMaxDim + kGenWarps * kGenMaxGroup * kGenMaxDim) * sizeof(float);
+    static bool configured[64] = {};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    decode_generic_kernel<<<dim3((unsigned)p.splits, (unsigned)batch, (unsigned)num_kv_heads), kGenWarps * 32, smem, s>>>(p);
+    TQ_CUDA(cudaGetLastError());
+    GenMergeParams m{};
+    m.partial_o = p.partial_o;
+    m.partial_lse = p.partial_lse;
+    m.signs = signs;
+    m.out = out;
+    m.out_lse = out_lse;
+    m.num_q_heads = num_q_heads;
+    m.splits = p.splits;
+    m.out_dtype = out_dtype;
+    m.emit_rotated = emit_rotated;
+    m.g = p.g;
+    m.scale = p.scale;
+    merge_generic_kernel<<<dim3((unsigned)batch, (unsigned)num_q_heads), p.g.padded, 0, s>>>(m);
+    TQ_CUDA(cudaGetLastError());
+    return TQ_OK;
+}
+
+int generic_dequant(const void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads, int slot_bytes,
+                    const int32_t* page_indices, const int32_t* page_indptr, int max_pages, const int32_t* seq_lens,
+                    const int32_t* cu_seqlens, int batch, const float* signs, int head_dim, void* k_out, void* v_out,
+                    int out_dtype, int64_t out_token_stride, void* stream) {
+    TQ_REQUIRE(head_dim > 32 && head_dim <= kGenMaxDim, TQ_ERR_UNSUPPORTED, "head_dim must be 33..%d, got %d", kGenMaxDim, head_dim);
+    TQ_REQUIRE(block_size == kGenPage, TQ_ERR_UNSUPPORTED, "bulk dequantization supports 16-token pages, got %d", block_size);
+    TQ_REQUIRE(slot_bytes >= generic_slot_bytes(head_dim), TQ_ERR_INVALID, "slot_bytes %d is smaller than head size %d needs", slot_bytes,
+               head_dim);
+    GenDequantParams p{};
+    p.kv_cache = static_cast<const uint8_t*>(kv_cache);
+    p.page_indices = page_indices;
+    p.page_indptr = page_indptr;
+    p.seq_lens = seq_lens;
+    p.cu_seqlens = cu_seqlens;
+    p.signs = signs;
+    p.out[0] = k_out;
+    p.out[1] = v_out;
+    p.slab_bytes = num_blocks * (int64_t)block_size * num_kv_heads * slot_bytes;
+    p.num_blocks = num_blocks;
+    p.out_token_stride = out_token_stride;
+    p.batch = batch;
+    p.max_pages = max_pages;
+    p.num_kv_heads = num_kv_heads;
+    p.out_dtype = out_dtype;
+    p.g = make_geom(head_dim, slot_bytes);
+    p.scale = (float)(1.0 / std::sqrt((double)p.g.padded));
+    float bnd[15];
+    host_codebook(p.g.padded, 4, p.centroids, bnd);
+    const int64_t items = (int64_t)batch * max_pages * kGenPage * num_kv_heads * 2;
+    const int64_t blocks = (items + kGenWarps - 1) / kGenWarps;
+    const unsigned grid = (unsigned)(blocks < 148 * 32 ? (blocks > 0 ? blocks : 1) : 148 * 32);
+    dequant_generic_kernel<<<grid, kGenWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    TQ_CUDA(cudaGetLastError());
+    return TQ_OK;
+}
+
+int generic_fault_counts(int32_t* write_dropped, int32_t* dequant_skipped) {
+    TQ_CUDA(cudaMemcpyFromSymbol(write_dropped, g_gen_write_dropped, sizeof(int32_t)));
+    TQ_CUDA(cudaMemcpyFromSymbol(dequant_skipped, g_gen_dequant_skipped, sizeof(int32_t)));
+    return TQ_OK;
+}
+
+}  // namespace tq

@@ -15,8 +15,12 @@
 
 namespace tq {
 
-constexpr int kPagePayload = 68;  // bytes of a slot that carry information
-constexpr int kPayloadWords = kPagePayload / 4;
+constexpr int kPagePayload = 68;  // bytes of an 80-byte slot that carry information
+// Payload of the other slot sizes: 48 bytes (head size 64) carry 32 code bytes + one fp16 norm,
+// moved as 36; 144 bytes (head size 256) carry 128 + 8; anything else is moved whole.
+static __host__ __device__ inline int slot_payload(int slot_bytes) {
+    return slot_bytes == 80 ? kPagePayload : slot_bytes == 48 ? 36 : slot_bytes == 144 ? 136 : slot_bytes;
+}
 
 struct PageMoveParams {
     uint8_t* kv_cache;
@@ -25,7 +29,7 @@ struct PageMoveParams {
     int64_t slab_bytes;   // K slab -> V slab
     int64_t half_bytes;   // one page half in the cache: block_size * H * slot_bytes
     int64_t num_blocks;   // page ids outside [0, num_blocks) are skipped and counted
-    int n_pages, slots_per_half, slot_bytes;
+    int n_pages, slots_per_half, slot_bytes, payload_words;
 };
 
 // Pages skipped because their id lay outside the cache; read back by tq_fault_counts.
@@ -43,10 +47,11 @@ __global__ void __launch_bounds__(256) page_move_kernel(const __grid_constant__ 
         return;
     }
     uint8_t* cache_half = p.kv_cache + (size_t)which * p.slab_bytes + (size_t)page * p.half_bytes;
-    uint8_t* packed_half = p.packed + ((size_t)n * 2 + which) * (size_t)p.slots_per_half * kPagePayload;
-    const int words = p.slots_per_half * kPayloadWords;
+    const int pw = p.payload_words;
+    uint8_t* packed_half = p.packed + ((size_t)n * 2 + which) * (size_t)p.slots_per_half * pw * 4;
+    const int words = p.slots_per_half * pw;
     for (int i = threadIdx.x; i < words; i += blockDim.x) {
-        const int slot = i / kPayloadWords, w = i - slot * kPayloadWords;
+        const int slot = i / pw, w = i - slot * pw;
         uint32_t* c = reinterpret_cast<uint32_t*>(cache_half + (size_t)slot * p.slot_bytes) + w;
         uint32_t* q = reinterpret_cast<uint32_t*>(packed_half) + i;
         if (GATHER) *q = *c;
@@ -60,11 +65,11 @@ static int page_move(bool gather, void* kv_cache, int64_t num_blocks, int block_
     TQ_REQUIRE(n_pages >= 0 && num_blocks >= 0, TQ_ERR_INVALID, "negative size");
     if (n_pages == 0) return TQ_OK;
     TQ_REQUIRE(kv_cache && page_ids && packed, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(block_size >= 1 && num_kv_heads >= 1 && slot_bytes >= kPagePayload && slot_bytes % 4 == 0,
+    TQ_REQUIRE(block_size >= 1 && num_kv_heads >= 1 && slot_bytes >= 4 && slot_bytes % 4 == 0,
                TQ_ERR_INVALID, "bad geometry");
     TQ_REQUIRE(((uintptr_t)kv_cache % 4) == 0 && ((uintptr_t)packed % 4) == 0, TQ_ERR_INVALID,
                "kv_cache and packed must be 4-byte aligned");
-    const size_t need = (size_t)n_pages * 2 * block_size * num_kv_heads * kPagePayload;
+    const size_t need = (size_t)n_pages * 2 * block_size * num_kv_heads * slot_payload(slot_bytes);
     TQ_REQUIRE(packed_bytes >= need, TQ_ERR_WORKSPACE, "packed buffer too small: %zu < %zu", packed_bytes, need);
     PageMoveParams p{};
     p.kv_cache = static_cast<uint8_t*>(kv_cache);
@@ -76,6 +81,7 @@ static int page_move(bool gather, void* kv_cache, int64_t num_blocks, int block_
     p.n_pages = n_pages;
     p.slots_per_half = block_size * num_kv_heads;
     p.slot_bytes = slot_bytes;
+    p.payload_words = slot_payload(slot_bytes) / 4;
     const dim3 grid((unsigned)n_pages, 2);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (gather) TQ_CUDA(launch_serialized(page_move_kernel<true>, grid, dim3(256), 0, s, p));
@@ -93,6 +99,11 @@ int pages_fault_count(int32_t* out) {
 extern "C" size_t tq_pages_packed_bytes(int n_pages, int block_size, int num_kv_heads) {
     if (n_pages <= 0 || block_size <= 0 || num_kv_heads <= 0) return 0;
     return (size_t)n_pages * 2 * block_size * num_kv_heads * tq::kPagePayload;
+}
+
+extern "C" size_t tq_pages_packed_bytes_for_slot(int n_pages, int block_size, int num_kv_heads, int slot_bytes) {
+    if (n_pages <= 0 || block_size <= 0 || num_kv_heads <= 0 || slot_bytes < 4 || slot_bytes % 4) return 0;
+    return (size_t)n_pages * 2 * block_size * num_kv_heads * tq::slot_payload(slot_bytes);
 }
 
 extern "C" int tq_pages_gather(const void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads,

@@ -945,9 +945,17 @@ int write_guard_stats(unsigned long long* out2) {
 }
 
 int device_sm_count(int* out);
+int generic_write(void* kv_cache, int64_t num_blocks, int block_size, int num_kv_heads, int slot_bytes, const void* key,
+                  const void* value, int in_dtype, int64_t num_tokens, int64_t k_token_stride, int64_t v_token_stride,
+                  const float* signs, const void* slot_mapping, int slot_dtype, int head_dim, int flags, void* stream);
+int generic_fault_counts(int32_t* write_dropped, int32_t* dequant_skipped);
 
 int write_fault_count(int32_t* out) {
-    TQ_CUDA(cudaMemcpyFromSymbol(out, g_write_dropped, sizeof(int32_t)));
+    int32_t a = 0, b = 0, c = 0;
+    TQ_CUDA(cudaMemcpyFromSymbol(&a, g_write_dropped, sizeof(int32_t)));
+    int rc = generic_fault_counts(&b, &c);
+    if (rc != TQ_OK) return rc;
+    *out = a + b;
     return TQ_OK;
 }
 
@@ -963,13 +971,19 @@ extern "C" int tq_write_kv_cache(void* kv_cache, int64_t num_blocks, int block_s
     TQ_REQUIRE(num_tokens >= 0 && num_blocks >= 0, TQ_ERR_INVALID, "negative size");
     if (num_tokens == 0) return TQ_OK;
     TQ_REQUIRE(kv_cache && key && value && signs && slot_mapping, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == 128 || head_dim == 96, TQ_ERR_UNSUPPORTED,
-               "cache write supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
     TQ_REQUIRE(num_kv_heads >= 1 && block_size >= 1, TQ_ERR_INVALID, "bad geometry");
-    TQ_REQUIRE(slot_bytes >= 80 && slot_bytes % 16 == 0, TQ_ERR_INVALID,
-               "slot_bytes must be a multiple of 16 and >= 80, got %d", slot_bytes);
     TQ_REQUIRE(in_dtype == TQ_F32 || in_dtype == TQ_F16 || in_dtype == TQ_BF16, TQ_ERR_INVALID, "bad in_dtype");
     TQ_REQUIRE(slot_dtype == TQ_I32 || slot_dtype == TQ_I64, TQ_ERR_INVALID, "bad slot_dtype");
+    if (head_dim != 128 && head_dim != 96) {  // other head sizes (64, 256, ...): the plain kernels
+        TQ_REQUIRE(k_token_stride >= (int64_t)num_kv_heads * head_dim && v_token_stride >= (int64_t)num_kv_heads * head_dim,
+                   TQ_ERR_INVALID, "token stride smaller than one token");
+        TQ_REQUIRE((flags & TQ_WRITE_TENSOR_PATH) == 0, TQ_ERR_UNSUPPORTED,
+                   "the tensor-core write kernel takes fp16 / bf16 rows of 128 elements");
+        return generic_write(kv_cache, num_blocks, block_size, num_kv_heads, slot_bytes, key, value, in_dtype, num_tokens,
+                             k_token_stride, v_token_stride, signs, slot_mapping, slot_dtype, head_dim, flags, stream);
+    }
+    TQ_REQUIRE(slot_bytes >= 80 && slot_bytes % 16 == 0, TQ_ERR_INVALID,
+               "slot_bytes must be a multiple of 16 and >= 80, got %d", slot_bytes);
     const int esz = in_dtype == TQ_F32 ? 4 : 2;
     TQ_REQUIRE(((uintptr_t)key % 16) == 0 && ((uintptr_t)value % 16) == 0 &&
                    (k_token_stride * esz) % 16 == 0 && (v_token_stride * esz) % 16 == 0,

@@ -42,6 +42,7 @@ class KernelConfig:
     stage_bytes: int
     supported: bool = True
     reason: str = ""
+    tuned: bool = True    # False: the plain kernels for head sizes other than 128 / 96
 
     @property
     def threads_per_block(self) -> int:
@@ -56,8 +57,11 @@ class KernelConfig:
 def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> KernelConfig:
     h, g = model.num_kv_heads, model.gqa_ratio
     if model.head_dim not in (128, 96):
+        if 32 < model.head_dim <= 256 and 1 <= g <= 8:
+            # plain kernels: four warps per (split, sequence, KV head), no staging ring
+            return KernelConfig(4, 1, 0, 0, True, "plain kernels (head sizes other than 128 / 96 are not tuned)", False)
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False,
-                            f"head_dim {model.head_dim}: 128 (and 96, padded to 128) are implemented")
+                            f"head_dim {model.head_dim} with GQA ratio {g}: head sizes 33..256 and ratios 1..8 are implemented")
     if h not in (1, 2, 4, 8, 16):
         if h > 8 and h % 4 == 0:
             # several launches of 16, 8 or 4 heads on strided token rows (one copy per token row)

@@ -45,8 +45,8 @@ class TurboQuantPagedAttention:
 
     def __init__(self, num_heads: int, head_size: int, scale: float, num_kv_heads: int,
                  seed: int = 42, num_ctas: int = 0):
-        if head_size not in (128, 96):
-            raise _cabi.TurboQuantError(f"head_size {head_size} is not supported (128, or 96 padded to 128)")
+        if not 32 < head_size <= 256:
+            raise _cabi.TurboQuantError(f"head_size {head_size} is not supported (33..256; 128 and 96 run the tuned kernels)")
         self.num_heads = num_heads
         self.head_size = head_size
         self.scale = float(scale)
@@ -157,7 +157,7 @@ class TurboQuantPagedAttention:
         reference's offload study copies a whole slab, pad bytes included (tests/bench_kv_offload.py)."""
         _, _, bs, H, _ = kv_cache.shape
         n = page_ids.shape[0]
-        nbytes = _cabi.pages_packed_bytes(n, bs, H) if n else 0
+        nbytes = _cabi.pages_packed_bytes(n, bs, H, kv_cache.shape[-1]) if n else 0
         staging = torch.empty(nbytes, dtype=torch.uint8, device=kv_cache.device)
         if host is None:
             host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
@@ -172,7 +172,7 @@ class TurboQuantPagedAttention:
         n = page_ids.shape[0]
         if n == 0:
             return
-        nbytes = _cabi.pages_packed_bytes(n, bs, H)
+        nbytes = _cabi.pages_packed_bytes(n, bs, H, kv_cache.shape[-1])
         staging = torch.empty(nbytes, dtype=torch.uint8, device=kv_cache.device)
         staging.copy_(host[:nbytes], non_blocking=True)
         _cabi.pages_scatter(self._as_bytes(kv_cache), page_ids.to(torch.int32), staging)

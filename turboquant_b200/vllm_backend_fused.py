@@ -162,7 +162,9 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
             if step is not None and not step["any_cached"]:
                 # first chunks only: attention over the fresh K/V of this step, as the reference does
                 # (vllm_backend_fused.py:336-369); the quantized cache is not read
-                out = flash_attn_varlen_func(query[:n], key[:n], value[:n],
+                out = flash_attn_varlen_func(query[:n].view(n, self.num_heads, self.head_size),
+                                             key[:n].view(n, self.num_kv_heads, self.head_size),
+                                             value[:n].view(n, self.num_kv_heads, self.head_size),
                                              cu_seqlens_q=attn_metadata.query_start_loc,
                                              cu_seqlens_k=attn_metadata.query_start_loc,
                                              max_seqlen_q=attn_metadata.max_query_len,
