@@ -260,7 +260,9 @@ def test_config4_full_size_vs_oracle(oracle, golden):
     print(f"config 4 full size: max-abs {max_abs:.3e}, relative {rel:.3e}")
 
 
-@pytest.mark.parametrize("nq,hq,hkv", [(2, 32, 8), (8, 8, 8), (3, 8, 4), (4, 4, 2), (1, 32, 8)])
+# the last five go through the wide-tile (tensor-memory) kernel: 9 to 32 query columns per KV head
+@pytest.mark.parametrize("nq,hq,hkv", [(2, 32, 8), (8, 8, 8), (3, 8, 4), (4, 4, 2), (1, 32, 8),
+                                       (8, 32, 8), (3, 32, 8), (5, 8, 4), (16, 4, 2), (9, 16, 16)])
 def test_shared_kv_queries_match_repeated_rows(oracle, golden, nq, hq, hkv):
     """Several queries per sequence (tq_decode_paged_multi) against (a) the oracle with each query
     as its own batch row and (b) tq_decode_paged on the same repeated rows."""
@@ -293,12 +295,13 @@ def test_shared_kv_queries_match_repeated_rows(oracle, golden, nq, hq, hkv):
         np.testing.assert_allclose(lse.cpu().numpy().reshape(B * nq, hq)[ok], want_lse[ok], atol=2e-3)
 
 
-def test_shared_kv_rejects_more_than_8_columns():
-    q = torch.zeros(1, 3, 32, 128, dtype=torch.float16, device=DEV)
+def test_shared_kv_rejects_more_than_32_columns():
+    assert _cabi.decode_max_queries_per_seq(32, 8) == 8
+    q = torch.zeros(1, 9, 32, 128, dtype=torch.float16, device=DEV)
     cache = torch.zeros(2, 4, 16, 8, 80, dtype=torch.uint8, device=DEV)
     bt = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
     sl = torch.ones(1, dtype=torch.int32, device=DEV)
-    ws = torch.zeros(_cabi.decode_workspace_bytes(1, 96, 8, 128, 0), dtype=torch.uint8, device=DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(1, 288, 8, 128, 0), dtype=torch.uint8, device=DEV)
     with pytest.raises(_cabi.TurboQuantError, match="queries_per_seq"):
         _cabi.decode_paged_multi(q, cache, bt, sl, signs_dev(), SCALE, ws, torch.empty_like(q))
 

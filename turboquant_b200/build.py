@@ -26,6 +26,7 @@ UNITS = {
     "tq_write.cu": ["-fmad=false"],
     "tq_flat.cu": ["-fmad=false"],
     "tq_decode.cu": [],
+    "tq_decode_mq.cu": [],
     "tq_dequant.cu": ["-fmad=false"],
     "tq_pages.cu": [],
     "tq_generic.cu": ["-fmad=false"],
@@ -43,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
     obj_dir = PKG / "build"
     obj_dir.mkdir(exist_ok=True)
-    deps = [CSRC / "tq_common.cuh", HEADER, Path(__file__)]
+    deps = [CSRC / "tq_common.cuh", CSRC / "tq_decode_common.cuh", HEADER, Path(__file__)]
 
     def compile_one(item):
         name, extra = item
