@@ -15,21 +15,24 @@
 // csrc/include/flashinfer_decode_turboquant_combine.cuh:18-79, merged by merge_kernel (tq_decode.cu).
 //
 // One thread block = one KV-head PAIR of a contiguous page range (the device-side plan of the
-// other kernel, over gridDim.x / (heads / 2) ranges).  640 threads in five warpgroups:
-//   warps 0-3    control: warp 0 streams raw pages (tiled tensor copies: boxes of 16 tokens x
-//                160 bytes = both heads' slots, into a ring of four 64-token stages), warp 1 issues
-//                the tensor-core instructions, warps 2-3 only give their registers away;
+// other kernel, over gridDim.x / (heads / 2) ranges).  896 threads in seven warpgroups:
+//   warps 0-3    control: warp 0 streams the raw K pages and warp 2 the raw V pages (tiled tensor
+//                copies: boxes of 16 tokens x 160 bytes = both heads' slots, each into its own ring of
+//                four 64-token stages), warp 1 issues the tensor-core instructions;
 //   warps 4-7    softmax of the pair's first head, warps 8-11 of its second head: thread t owns
 //                token t of the 128-token tile: reads its row of S from tensor memory, applies the
 //                K norm and the scale, keeps a lazily raised running maximum per column, writes P
 //                (fp16, times the V norm) to shared memory;
-//   warps 12-19  dequantize: 16 code bytes per thread and step through the lookup table (one lookup
-//                per code byte, as in the other kernel) into the K^ / V^ operand buffers, laid out
-//                as the un-swizzled canonical core-matrix layouts the instruction descriptors name.
+//   warps 12-19  dequantize K, warps 20-27 dequantize V: 16 code bytes per thread and step through
+//                the lookup table (one lookup per code byte, as in the other kernel) into the K^ / V^
+//                operand buffers, laid out as the un-swizzled canonical core-matrix layouts the
+//                instruction descriptors name.  The two teams run independently of each other: K^ of
+//                a tile-head is typically written while V^ of the one before is.
 // K^ and V^ are produced in halves (64 of the 128 contraction indices each) into two 16 KB buffers
 // per operand, so that the tensor core works on one half while the next is being written.
-// Q^T (per head: 32 columns x 128 dims, fp16) and P (128 tokens x 32 columns) live in the unused
-// upper halves of the lookup table's 256-byte rows: a core matrix is exactly 128 bytes.
+// Q^T (per head: 32 columns x 128 dims, fp16), P of the first head (128 tokens x 32 columns) and
+// the norms live in the unused upper halves of the lookup table's 256-byte rows: a core matrix is
+// exactly 128 bytes.  P of the second head has a buffer of its own.
 //
 // Every wait is bounded; a wait that runs out raises the sticky status word, the block stops
 // taking work, frees its tensor memory and returns.
@@ -42,28 +45,31 @@
 
 namespace tq {
 
-constexpr int kMqThreads = 640;
+constexpr int kMqThreads = 896;
 constexpr int kMqCols = 32;            // query columns per KV head (shorter tiles are padded with zeros)
 constexpr int kMqTile = 128;           // tokens per tile
-constexpr int kMqStages = 4;
+constexpr int kMqStages = 4;           // per ring (K, V)
 constexpr int kMqBoxBytes = 16 * 160;  // one page half of a head pair
-constexpr int kMqStageBytes = 8 * kMqBoxBytes;  // 4 pages x (K, V)
+constexpr int kMqStageBytes = 4 * kMqBoxBytes;  // 4 pages of K or of V
 constexpr int kMqOperandHalf = 16384;  // 64 contraction indices x 128 rows x 2 bytes
 constexpr uint32_t kMqWaitLimit = 1u << 18;
 constexpr int kMqTmemCols = 128;       // S x 2, O x 2 heads, 32 columns each
 
-// shared-window offsets: three raw stages below the table, the table (with Q^T, P and the norms in
-// its holes), then the operand buffers and the fourth raw stage
-constexpr uint32_t kMqStage0 = 4096;   // 4096 + 3 x 20480 = 65536
-constexpr uint32_t kMqKhat = kLutAddr + kLutSpan;            // 2 x 16 KB
-constexpr uint32_t kMqVhat = kMqKhat + 2 * kMqOperandHalf;   // 2 x 16 KB
-constexpr uint32_t kMqStage3 = kMqVhat + 2 * kMqOperandHalf;
-constexpr uint32_t kMqSmemEnd = kMqStage3 + kMqStageBytes;   // 217088
+// shared-window offsets: the K ring and half of the V ring below the table, the table (with Q^T, one P
+// and the norms in its holes), then the operand buffers, the rest of the V ring and the other P
+constexpr uint32_t kMqRawK = 4096;                              // 4 x 10240
+constexpr uint32_t kMqRawV01 = kMqRawK + 4 * kMqStageBytes;     // 2 x 10240, ends at 65536
+constexpr uint32_t kMqKhat = kLutAddr + kLutSpan;               // 2 x 16 KB
+constexpr uint32_t kMqVhat = kMqKhat + 2 * kMqOperandHalf;      // 2 x 16 KB
+constexpr uint32_t kMqRawV23 = kMqVhat + 2 * kMqOperandHalf;    // 2 x 10240
+constexpr uint32_t kMqP1 = kMqRawV23 + 2 * kMqStageBytes;       // 8 KB: [16 token groups][4 column groups][8][16 B]
+constexpr uint32_t kMqSmemEnd = kMqP1 + 8192;                   // 225280
+static_assert(kMqRawV01 + 2 * kMqStageBytes == kLutAddr, "the rings below the table end where it starts");
 
 __device__ __forceinline__ uint32_t mq_hole(int i) { return kLutAddr + 256u * (uint32_t)i + 128u; }
-// holes: [0, 128) Q^T of the two heads, [128, 192) P, [192, 224) norms (4 tile-heads x {K, V} x 128 floats: a
-// buffer is rewritten four tile-heads later, which the S buffers' hand-over orders after its last read),
-// [224, 232) per-column scratch of the two softmax groups, [232, 234) the running maxima of the two heads
+// holes: [0, 128) Q^T of the two heads, [128, 192) P of the first head, [192, 224) norms (4 tile-heads x
+// {K, V} x 128 floats: a buffer is rewritten four tile-heads later, which the S and P hand-overs order after
+// its last read), [224, 232) per-column scratch of the two softmax groups, [232, 234) the running maxima
 constexpr int kHoleQ = 0, kHoleP = 128, kHoleNorm = 192, kHoleCol = 224, kHoleMax = 232;
 
 struct MqParams {
@@ -80,7 +86,7 @@ __device__ __forceinline__ bool mq_wait(uint64_t* bar, uint32_t parity) {
     return __all_sync(0xffffffffu, done);
 }
 
-__device__ __forceinline__ uint64_t mq_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+__host__ __device__ constexpr uint64_t mq_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
            ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46);  // version 1, no swizzle
 }
@@ -160,8 +166,8 @@ __device__ __forceinline__ void bar_sync_named(int id, int count) { asm volatile
 __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_constant__ MqParams mp) {
     const DecodeParams& p = mp.d;
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ __align__(8) uint64_t raw_full[kMqStages], raw_empty[kMqStages];
-    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[2], vq_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_done[2];
+    __shared__ __align__(8) uint64_t rawk_full[kMqStages], rawk_empty[kMqStages], rawv_full[kMqStages], rawv_empty[kMqStages];
+    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[2], vq_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2], o_done[2], vn_full[2];
     __shared__ int seg_seq[kMaxSegments], seg_p0[kMaxSegments], seg_p1[kMaxSegments];
     __shared__ int num_segments, abort_flag;
     __shared__ uint32_t tmem_slot;
@@ -170,19 +176,24 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = smem_u32(smem);
     grid_launch_dependents();
-    // the map above assumes that the dynamic shared memory starts below kMqStage0 of the shared window
-    if (smem_base > kMqStage0) {
+    // the map above assumes that the dynamic shared memory starts below kMqRawK of the shared window
+    if (smem_base > kMqRawK) {
         grid_dependency_wait();
         if (tid == 0) atomicExch(&p.header[0], 3);
         return;
     }
-    auto stage_addr = [&](int s) -> uint32_t { return s < 3 ? kMqStage0 + (uint32_t)s * kMqStageBytes : kMqStage3; };
+    auto rawk_addr = [&](int s) -> uint32_t { return kMqRawK + (uint32_t)s * kMqStageBytes; };
+    auto rawv_addr = [&](int s) -> uint32_t {
+        return s < 2 ? kMqRawV01 + (uint32_t)s * kMqStageBytes : kMqRawV23 + (uint32_t)(s - 2) * kMqStageBytes;
+    };
     uint32_t* lut_s = reinterpret_cast<uint32_t*>(smem + (kLutAddr - smem_base));
 
     if (tid == 0) {
         for (int s = 0; s < kMqStages; s++) {
-            mbar_init(&raw_full[s], 1);
-            mbar_init(&raw_empty[s], 8);
+            mbar_init(&rawk_full[s], 1);
+            mbar_init(&rawk_empty[s], 4);   // the four K warps that read the stage's tokens
+            mbar_init(&rawv_full[s], 1);
+            mbar_init(&rawv_empty[s], 8);   // every V warp reads every stage
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(&kq_full[i], 8);
@@ -191,10 +202,11 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             mbar_init(&vq_empty[i], 1);
             mbar_init(&s_full[i], 1);
             mbar_init(&s_empty[i], 4);
+            mbar_init(&p_full[i], 4);
+            mbar_init(&p_empty[i], 1);
             mbar_init(&o_done[i], 1);   // one phase per segment: the head's last PV has completed
+            mbar_init(&vn_full[i], 8);  // one phase per tile: the V norms of this half of the tile's tokens are written
         }
-        mbar_init(&p_full, 4);
-        mbar_init(&p_empty, 1);
         num_segments = 0;
         abort_flag = 0;
         fence_barrier_init();
@@ -299,111 +311,127 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     const uint32_t tmem = tmem_slot;
     const uint32_t tm_s0 = tmem, tm_o0 = tmem + 64;   // S buffers at +32 sb, O accumulators at +32 h2
 
-    // The three roles part here for good: each lowers or raises its register count first, runs its own
-    // loop over the block's segments, and meets the others only at barrier 1 (twice per segment: the
-    // rotated queries are in place / the segment has drained).  u counts tile-heads and tile_n tiles
-    // across the segments; they fix the barrier phases and advance identically in every role.
+    // The roles part here for good: each lowers or raises its register count first, runs its own loop
+    // over the block's segments, and meets the others only at barrier 1 (twice per segment: the rotated
+    // queries are in place / the segment has drained).  u counts tile-heads and tile_n tiles across the
+    // segments; they fix the barrier phases and advance identically in every role.
     if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         int u = 0, tile_n = 0;
         for (int sg = 0; sg < nseg; sg++) {
-        const int b = seg_seq[sg];
-        int first_page, npages_b, len_eff;
-        seq_pages(p, b, first_page, npages_b, len_eff);
-        const int p0 = seg_p0[sg], p1 = seg_p1[sg];
-        const int ntiles = (p1 - p0 + PPS - 1) / PPS;
+            const int b = seg_seq[sg];
+            int first_page, npages_b, len_eff;
+            seq_pages(p, b, first_page, npages_b, len_eff);
+            const int p0 = seg_p0[sg], p1 = seg_p1[sg];
+            const int ntiles = (p1 - p0 + PPS - 1) / PPS;
             bar_sync_named(1, kMqThreads);
-            if (warp == 0) {
-            // =============================== producer: raw pages ===================================
-            const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
-            bool bad_page = false;
-            for (int t = 0; t < ntiles && !abort_flag; t++) {
-                const int n = tile_n + t;
-                for (int rs = 0; rs < 2; rs++) {
-                    const int st = (2 * n + rs) & 3;
-                    const int pg0 = p0 + t * PPS + rs * 4;
-                    const int np = min(4, p1 - pg0);        // pages of this stage (may be <= 0 in the last tile)
-                    if (n >= 2 && !mq_wait(&raw_empty[st], ((n >> 1) - 1) & 1)) {
-                        abort_flag = 1;
-                        atomicExch(&p.header[0], 1);
-                        break;
-                    }
-                    int page = 0;
-                    if (lane < 8 && (lane >> 1) < np) {
-                        page = p.page_indices[tbl + first_page + pg0 + (lane >> 1)];
-                        if ((uint64_t)(int64_t)page >= (uint64_t)p.num_blocks) {
-                            page = 0;
-                            bad_page = true;
+            if (warp == 0 || warp == 2) {
+                // =============================== producers: raw K pages (warp 0), raw V pages (warp 2) =====
+                const int z = warp >> 1;
+                uint64_t* full = z ? rawv_full : rawk_full;
+                uint64_t* empty = z ? rawv_empty : rawk_empty;
+                const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
+                bool bad_page = false;
+                for (int t = 0; t < ntiles && !abort_flag; t++) {
+                    const int n = tile_n + t;
+                    for (int rs = 0; rs < 2; rs++) {
+                        const int st = (2 * n + rs) & 3;
+                        const int pg0 = p0 + t * PPS + rs * 4;
+                        const int np = min(4, p1 - pg0);        // pages of this stage (may be <= 0 in the last tile)
+                        if (n >= 2 && !mq_wait(&empty[st], ((n >> 1) - 1) & 1)) {
+                            abort_flag = 1;
+                            atomicExch(&p.header[0], 1);
+                            break;
                         }
+                        int page = 0;
+                        if (lane < 4 && lane < np) {
+                            page = p.page_indices[tbl + first_page + pg0 + lane];
+                            if ((uint64_t)(int64_t)page >= (uint64_t)p.num_blocks) {
+                                page = 0;
+                                bad_page = true;
+                            }
+                        }
+                        if (lane == 0) mbar_arrive_expect_tx(&full[st], (uint32_t)((np > 0 ? np : 0) * kMqBoxBytes));
+                        __syncwarp();
+                        if (lane < 4 && lane < np)
+                            mq_box_g2s((z ? rawv_addr(st) : rawk_addr(st)) + lane * kMqBoxBytes, &mp.cache_map,
+                                       hp * 160 + p.kv_head_off, page * kPageTokens, z, &full[st]);
                     }
-                    if (lane == 0) mbar_arrive_expect_tx(&raw_full[st], (uint32_t)((np > 0 ? np : 0) * 2 * kMqBoxBytes));
-                    __syncwarp();
-                    if (lane < 8 && (lane >> 1) < np)
-                        mq_box_g2s(stage_addr(st) + lane * kMqBoxBytes, &mp.cache_map, hp * 160 + p.kv_head_off,
-                                   page * kPageTokens, lane & 1, &raw_full[st]);
                 }
-            }
-            if (bad_page && lane == 0) atomicExch(&p.header[0], kStatusBadPage);
+                if (bad_page && lane == 0) atomicExch(&p.header[0], kStatusBadPage);
             } else if (warp == 1) {
-            // =============================== tensor-core issue ======================================
-            const uint32_t idesc_qk = (1u << 4) | ((uint32_t)(kMqCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            const uint32_t idesc_pv = idesc_qk | (1u << 15) | (1u << 16);
-            for (int t = 0; t < ntiles && !abort_flag; t++) {
-                for (int h2 = 0; h2 < 2; h2++) {
-                    const int uu = u + 2 * t + h2;
-                    const int sb = uu & 1;
-                    bool ok = true;
-                    // S = K^ Q^T: two halves of the contraction
-                    for (int hh = 0; hh < 2 && ok; hh++) {
-                        ok = mq_wait(&kq_full[hh], uu & 1);
-                        if (ok && hh == 0 && uu >= 2) ok = mq_wait(&s_empty[sb], ((uu >> 1) - 1) & 1);
-                        if (!ok) break;
+                // =============================== tensor-core issue ======================================
+                constexpr uint32_t idesc_qk = (1u << 4) | ((uint32_t)(kMqCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                constexpr uint32_t idesc_pv = idesc_qk | (1u << 15) | (1u << 16);
+                // S = K^ Q^T of tile-head i: two halves of the contraction
+                auto issue_qk = [&](int i) -> bool {
+                    const int uu = u + i, h2 = i & 1;   // u is even: the S buffer is the head's
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {
+                        if (!mq_wait(&kq_full[hh], uu & 1)) return false;
+                        if (hh == 0 && uu >= 2 && !mq_wait(&s_empty[h2], ((uu >> 1) - 1) & 1)) return false;
                         tc_fence_after();
                         if (lane == 0) {
+                            const uint64_t qoff = (uint64_t)((uint32_t)h2 * (64u * 256u) >> 4);
 #pragma unroll
                             for (int jj = 0; jj < 4; jj++) {
-                                const uint64_t da = mq_desc(kMqKhat + hh * kMqOperandHalf + jj * 4096, 2048, 128);
-                                const uint64_t db = mq_desc(mq_hole(kHoleQ + h2 * 64 + (hh * 8 + jj * 2) * 4), 1024, 256);
-                                mq_mma(tm_s0 + 32 * sb, da, db, idesc_qk, (hh | jj) ? 1u : 0u);
+                                constexpr uint64_t dk0 = mq_desc(kMqKhat, 2048, 128);
+                                constexpr uint64_t dq0 = mq_desc(kLutAddr + 128u, 1024, 256);
+                                const uint64_t da = dk0 + (uint64_t)((hh * kMqOperandHalf + jj * 4096) >> 4);
+                                const uint64_t db = dq0 + (uint64_t)(((hh * 8 + jj * 2) * 4 * 256) >> 4) + qoff;
+                                mq_mma(tm_s0 + 32 * h2, da, db, idesc_qk, (hh | jj) ? 1u : 0u);
                             }
                             mq_commit(&kq_empty[hh]);
-                            if (hh == 1) mq_commit(&s_full[sb]);
+                            if (hh == 1) mq_commit(&s_full[h2]);
                         }
                         __syncwarp();
                     }
-                    // O^T += V^^T P: two halves of the tile's tokens
-                    if (ok) ok = mq_wait(&p_full, uu & 1);
-                    for (int th = 0; th < 2 && ok; th++) {
-                        ok = mq_wait(&vq_full[th], uu & 1);
-                        if (!ok) break;
+                    return true;
+                };
+                // O^T += V^^T P of tile-head i: two halves of the tile's tokens
+                auto issue_pv = [&](int i) -> bool {
+                    const int uu = u + i, h2 = i & 1, t = i >> 1;
+                    if (!mq_wait(&p_full[h2], (uu >> 1) & 1)) return false;
+#pragma unroll
+                    for (int th = 0; th < 2; th++) {
+                        if (!mq_wait(&vq_full[th], uu & 1)) return false;
                         tc_fence_after();
                         if (lane == 0) {
 #pragma unroll
                             for (int jj = 0; jj < 4; jj++) {
-                                const uint64_t da = mq_desc(kMqVhat + th * kMqOperandHalf + jj * 4096, 2048, 128);
-                                const uint64_t db = mq_desc(mq_hole(kHoleP + (th * 8 + jj * 2) * 4), 1024, 256);
+                                constexpr uint64_t dv0 = mq_desc(kMqVhat, 2048, 128);
+                                constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
+                                constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
+                                const uint64_t da = dv0 + (uint64_t)((th * kMqOperandHalf + jj * 4096) >> 4);
+                                const uint64_t db = h2 ? dp1 + (uint64_t)(((th * 8 + jj * 2) * 512) >> 4)
+                                                       : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
                                 mq_mma(tm_o0 + 32 * h2, da, db, idesc_pv, (t | th | jj) ? 1u : 0u);
                             }
                             mq_commit(&vq_empty[th]);
                             if (th == 1) {
-                                mq_commit(&p_empty);
+                                mq_commit(&p_empty[h2]);
                                 if (t == ntiles - 1) mq_commit(&o_done[h2]);
                             }
                         }
                         __syncwarp();
                     }
-                    if (!ok) {
-                        abort_flag = 1;
-                        if (lane == 0) atomicExch(&p.header[0], 1);
-                        break;
-                    }
+                    return true;
+                };
+                // S of the next tile-head is issued before this one's PV, so that the two softmax groups overlap
+                bool ok = !abort_flag && issue_qk(0);
+                for (int i = 0; i < 2 * ntiles && ok && !abort_flag; i++) {
+                    if (i + 1 < 2 * ntiles) ok = issue_qk(i + 1);
+                    if (ok) ok = issue_pv(i);
+                }
+                if (!ok && !abort_flag) {
+                    abort_flag = 1;
+                    if (lane == 0) atomicExch(&p.header[0], 1);
                 }
             }
-            }
-        u += 2 * ntiles;
-        tile_n += ntiles;
-        bar_sync_named(1, kMqThreads);   // every instruction of this segment has completed before Q^T and tensor memory are reused
-        if (abort_flag) break;
+            u += 2 * ntiles;
+            tile_n += ntiles;
+            bar_sync_named(1, kMqThreads);   // every instruction of this segment has completed before Q^T and tensor memory are reused
+            if (abort_flag) break;
         }
         tc_fence_before();
         bar_sync_named(1, kMqThreads);
@@ -414,18 +442,21 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
         return;
     }
     if (warp >= 12) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        const bool vteam = warp >= 20;
+        const int dt = (tid - 384) & 255;   // thread of its team
+        const uint32_t lut_lane = kLutAddr + 4u * lane;
         int u = 0, tile_n = 0;
         for (int sg = 0; sg < nseg; sg++) {
-        const int b = seg_seq[sg];
-        int first_page, npages_b, len_eff;
-        seq_pages(p, b, first_page, npages_b, len_eff);
-        const int p0 = seg_p0[sg], p1 = seg_p1[sg];
-        const int ntiles = (p1 - p0 + PPS - 1) / PPS;
-            // ---- rotated queries of both heads into the Q^T holes (8 columns per warp) ----------------
+            const int b = seg_seq[sg];
+            int first_page, npages_b, len_eff;
+            seq_pages(p, b, first_page, npages_b, len_eff);
+            const int p0 = seg_p0[sg], p1 = seg_p1[sg];
+            const int ntiles = (p1 - p0 + PPS - 1) / PPS;
+            // ---- rotated queries of both heads into the Q^T holes (4 columns per warp) ----------------
             {
             const float4 sg4 = reinterpret_cast<const float4*>(p.signs)[lane];
-            for (int rr = warp - 12; rr < 2 * kMqCols; rr += 8) {
+            for (int rr = warp - 12; rr < 2 * kMqCols; rr += 16) {
                 const int h2 = rr >> 5, col = rr & 31;
                 float w[4] = {0.f, 0.f, 0.f, 0.f};
                 if (col < mp.ncols && 4 * lane < p.head_dim) {
@@ -457,90 +488,113 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             fence_proxy_async();
             }
             bar_sync_named(1, kMqThreads);
-            // =============================== dequantize ==============================================
-            {
-            const int dt = tid - 384;
-            const uint32_t lut_lane = kLutAddr + 4u * lane;
-            for (int t = 0; t < ntiles && !abort_flag; t++) {
-                const int n = tile_n + t;
-                const int st0 = (2 * n) & 3, st1 = (2 * n + 1) & 3;
-                bool ok = mq_wait(&raw_full[st0], (n >> 1) & 1) && mq_wait(&raw_full[st1], (n >> 1) & 1);
-                for (int h2 = 0; h2 < 2 && ok; h2++) {
-                    const int uu = u + 2 * t + h2;
-                    // ---- K^ halves: thread = (token, 16-byte piece of the half) -------------------------
-                    const int tok = dt & 127, piece = dt >> 7;
-                    const uint32_t krow = stage_addr(tok < 64 ? st0 : st1) + (((tok & 63) >> 4) * 2) * kMqBoxBytes +
-                                          (tok & 15) * 160 + h2 * 80;
-                    for (int hh = 0; hh < 2 && ok; hh++) {
-                        if (uu >= 1) ok = mq_wait(&kq_empty[hh], (uu - 1) & 1);
-                        if (!ok) break;
-                        const uint4 cw = lds128(krow + 32 * hh + 16 * piece);
-                        if (hh == 0) {  // the norms of the tile, times the scales, for the softmax warps
-                            const float nrm = lds_half(krow + (piece ? kMqBoxBytes : 0) + 64);
-                            sts32f(mq_hole(kHoleNorm + (uu & 3) * 8 + piece * 4 + (tok >> 5)) + (tok & 31) * 4,
-                                   nrm * (piece ? p.v_scale : p.k_scale));
-                        }
-                        const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
-                        const uint32_t dst = kMqKhat + hh * kMqOperandHalf + (4 * piece) * 2048 + tok * 16;
+            bool ok = true;
+            if (!vteam) {
+                // =============================== dequantize K ========================================
+                // thread = (token, 16-byte piece of the half); the warp's 32 tokens lie in one stage
+                const int tok = dt & 127, piece = dt >> 7;
+                for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
+                    const int n = tile_n + t;
+                    const int st = (2 * n + (tok >> 6)) & 3;
+                    ok = mq_wait(&rawk_full[st], (n >> 1) & 1);
+                    const uint32_t krow0 = rawk_addr(st) + ((tok & 63) >> 4) * kMqBoxBytes + (tok & 15) * 160;
+                    for (int h2 = 0; h2 < 2 && ok; h2++) {
+                        const int uu = u + 2 * t + h2;
+                        const uint32_t krow = krow0 + h2 * 80;
 #pragma unroll
-                        for (int w = 0; w < 4; w++) {
-                            uint32_t r[4];
-                            dequant8(w4[w], lut_lane, r);
-                            sts128(dst + w * 2048, r[0], r[1], r[2], r[3]);
-                        }
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&kq_full[hh]);
-                    }
-                    // ---- V^ halves: thread = (token of the half, 16-byte piece of the row) ---------------
-                    for (int th = 0; th < 2 && ok; th++) {
-                        if (uu >= 1) ok = mq_wait(&vq_empty[th], (uu - 1) & 1);
-                        if (!ok) break;
-                        const int tl = dt & 63, pc = dt >> 6;
-                        const uint32_t vrow = stage_addr(th ? st1 : st0) + ((tl >> 4) * 2 + 1) * kMqBoxBytes + (tl & 15) * 160 + h2 * 80;
-                        const uint4 cw = lds128(vrow + 16 * pc);
-                        const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
-                        const uint32_t dst = kMqVhat + th * kMqOperandHalf + (tl >> 3) * 2048 + (4 * pc) * 128 + (tl & 7) * 16;
+                        for (int hh = 0; hh < 2; hh++) {
+                            if (uu >= 1) ok = mq_wait(&kq_empty[hh], (uu - 1) & 1);
+                            if (!ok) break;
+                            const uint4 cw = lds128(krow + 32 * hh + 16 * piece);
+                            if (hh == 0 && piece == 0)   // the K norms of the tile, times the scales, for the softmax warps
+                                sts32f(mq_hole(kHoleNorm + (uu & 3) * 8 + (tok >> 5)) + (tok & 31) * 4, lds_half(krow + 64) * p.k_scale);
+                            const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
+                            const uint32_t dst = kMqKhat + hh * kMqOperandHalf + (4 * piece) * 2048 + tok * 16;
 #pragma unroll
-                        for (int w = 0; w < 4; w++) {
-                            uint32_t r[4];
-                            dequant8(w4[w], lut_lane, r);
-                            sts128(dst + w * 128, r[0], r[1], r[2], r[3]);
-                        }
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive(&vq_full[th]);
-                            if (h2 == 1) mbar_arrive(&raw_empty[th ? st1 : st0]);   // both heads have read this stage
+                            for (int w = 0; w < 4; w++) {
+                                uint32_t r[4];
+                                dequant8(w4[w], lut_lane, r);
+                                sts128(dst + w * 2048, r[0], r[1], r[2], r[3]);
+                            }
+                            fence_proxy_async();
+                            __syncwarp();
+                            if (lane == 0) {
+                                mbar_arrive(&kq_full[hh]);
+                                if (h2 == 1 && hh == 1) mbar_arrive(&rawk_empty[st]);   // both heads have read this stage
+                            }
                         }
                     }
                 }
-                if (!ok) {
-                    abort_flag = 1;
-                    if (lane == 0) atomicExch(&p.header[0], 1);
-                    break;
+            } else {
+                // =============================== dequantize V ========================================
+                // thread = (token of the half, 16-byte piece of the row)
+                const int tl = dt & 63, pc = dt >> 6;
+                for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
+                    const int n = tile_n + t;
+                    for (int h2 = 0; h2 < 2 && ok; h2++) {
+                        const int uu = u + 2 * t + h2;
+#pragma unroll
+                        for (int th = 0; th < 2; th++) {
+                            const int st = (2 * n + th) & 3;
+                            ok = mq_wait(&rawv_full[st], (n >> 1) & 1);
+                            if (!ok) break;
+                            const uint32_t vrow0 = rawv_addr(st) + (tl >> 4) * kMqBoxBytes + (tl & 15) * 160;
+                            const uint32_t vrow = vrow0 + h2 * 80;
+                            if (h2 == 0) {
+                                // The V norms of BOTH heads for this half of the tile, times the scale, as soon as the raw
+                                // rows are here: the softmax warps need them before this team gets to write V^.
+                                if (pc < 2) {
+                                    const int tok = th * 64 + tl;
+                                    sts32f(mq_hole(kHoleNorm + ((uu + pc) & 3) * 8 + 4 + (tok >> 5)) + (tok & 31) * 4,
+                                           lds_half(vrow0 + pc * 80 + 64) * p.v_scale);
+                                }
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&vn_full[th]);
+                            }
+                            if (uu >= 1) ok = mq_wait(&vq_empty[th], (uu - 1) & 1);
+                            if (!ok) break;
+                            const uint4 cw = lds128(vrow + 16 * pc);
+                            const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
+                            const uint32_t dst = kMqVhat + th * kMqOperandHalf + (tl >> 3) * 2048 + (4 * pc) * 128 + (tl & 7) * 16;
+#pragma unroll
+                            for (int w = 0; w < 4; w++) {
+                                uint32_t r[4];
+                                dequant8(w4[w], lut_lane, r);
+                                sts128(dst + w * 128, r[0], r[1], r[2], r[3]);
+                            }
+                            fence_proxy_async();
+                            __syncwarp();
+                            if (lane == 0) {
+                                mbar_arrive(&vq_full[th]);
+                                if (h2 == 1) mbar_arrive(&rawv_empty[st]);   // both heads have read this stage
+                            }
+                        }
+                    }
                 }
             }
+            if (!ok && !abort_flag) {
+                abort_flag = 1;
+                if (lane == 0) atomicExch(&p.header[0], 1);
             }
-        u += 2 * ntiles;
-        tile_n += ntiles;
-        bar_sync_named(1, kMqThreads);   // every instruction of this segment has completed before Q^T and tensor memory are reused
-        if (abort_flag) break;
+            u += 2 * ntiles;
+            tile_n += ntiles;
+            bar_sync_named(1, kMqThreads);   // every instruction of this segment has completed before Q^T and tensor memory are reused
+            if (abort_flag) break;
         }
         tc_fence_before();
         bar_sync_named(1, kMqThreads);
         return;
     }
     // =============================== softmax ======================================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     {
         int u = 0, tile_n = 0;
         for (int sg = 0; sg < nseg; sg++) {
-        const int b = seg_seq[sg];
-        int first_page, npages_b, len_eff;
-        seq_pages(p, b, first_page, npages_b, len_eff);
-        const int p0 = seg_p0[sg], p1 = seg_p1[sg];
-        const int ntiles = (p1 - p0 + PPS - 1) / PPS;
+            const int b = seg_seq[sg];
+            int first_page, npages_b, len_eff;
+            seq_pages(p, b, first_page, npages_b, len_eff);
+            const int p0 = seg_p0[sg], p1 = seg_p1[sg];
+            const int ntiles = (p1 - p0 + PPS - 1) / PPS;
             bar_sync_named(1, kMqThreads);
             {
             const int h2 = (warp - 4) >> 2;
@@ -567,7 +621,6 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 if (ok) ok = mq_wait(&s_full[h2], (uu >> 1) & 1);
                 tc_fence_after();
                 const float kf = lds32f(mq_hole(kHoleNorm + (uu & 3) * 8 + (stid >> 5)) + (stid & 31) * 4);
-                const float vf = lds32f(mq_hole(kHoleNorm + (uu & 3) * 8 + 4 + (stid >> 5)) + (stid & 31) * 4);
                 // S is read from tensor memory sixteen columns at a time, once to look for a raised maximum and
                 // once to exponentiate (and once more in the rare tile that raises one): reading it again is
                 // cheaper than holding 32 scores beside the 32 column sums.  The running maxima stay in shared
@@ -591,7 +644,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 if (lane == 0) raise_flag[4 * h2 + wq] = wraise;
                 bar_sync_named(bar_id, 128);
                 const bool any_raise = raise_flag[4 * h2] | raise_flag[4 * h2 + 1] | raise_flag[4 * h2 + 2] | raise_flag[4 * h2 + 3];
-                if (ok && uu >= 1) ok = mq_wait(&p_empty, (uu - 1) & 1);   // P's buffer is free; this head's PVs are done
+                if (ok && (uu >> 1) >= 1) ok = mq_wait(&p_empty[h2], ((uu >> 1) - 1) & 1);   // the head's P buffer is free, its PVs are done
                 tc_fence_after();
                 if (any_raise) {   // the same answer in the group's four warps
                     // column maxima over the 128 tokens: warp reduction, then across the four warps
@@ -634,7 +687,12 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                     if (stid < kMqCols) sts32f(mq_hole(kHoleMax + h2) + stid * 4, mine);
                 }
                 bar_sync_named(bar_id, 128);   // maxima written; the flags and the column scratch may be reused
-                const uint32_t pdst = mq_hole(kHoleP + (stid >> 3) * 4) + (stid & 7) * 16;
+                // the V norms come from the V team, which may be behind: one phase per tile and half of its tokens
+                if (ok) ok = mq_wait(&vn_full[stid >> 6], (uu >> 1) & 1);
+                const float vf = lds32f(mq_hole(kHoleNorm + (uu & 3) * 8 + 4 + (stid >> 5)) + (stid & 31) * 4);
+                // P: [token group][column group][token in group][8 columns]; the first head's in the table's holes
+                const uint32_t pdst = h2 ? kMqP1 + (stid >> 3) * 512 + (stid & 7) * 16 : mq_hole(kHoleP + (stid >> 3) * 4) + (stid & 7) * 16;
+                const uint32_t pcg = h2 ? 128u : 256u;
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
                     if (!ok) break;
@@ -653,15 +711,15 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                             ph[(cc + i) >> 1] = valid ? pack_half2(e0 * vf, e1 * vf) : 0u;
                         }
                     }
-                    sts128(pdst + (2 * half) * 256, ph[0], ph[1], ph[2], ph[3]);
-                    sts128(pdst + (2 * half + 1) * 256, ph[4], ph[5], ph[6], ph[7]);
+                    sts128(pdst + (2 * half) * pcg, ph[0], ph[1], ph[2], ph[3]);
+                    sts128(pdst + (2 * half + 1) * pcg, ph[4], ph[5], ph[6], ph[7]);
                 }
                 fence_proxy_async();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0 && ok) {
                     mbar_arrive(&s_empty[h2]);
-                    mbar_arrive(&p_full);
+                    mbar_arrive(&p_full[h2]);
                 }
             }
             // ---- segment epilogue: wait for this head's last PV, normalize, write the partials ---------
@@ -709,10 +767,10 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 tc_fence_before();
             }
             }
-        u += 2 * ntiles;
-        tile_n += ntiles;
-        bar_sync_named(1, kMqThreads);   // every instruction of this segment has completed before Q^T and tensor memory are reused
-        if (abort_flag) break;
+            u += 2 * ntiles;
+            tile_n += ntiles;
+            bar_sync_named(1, kMqThreads);   // every instruction of this segment has completed before Q^T and tensor memory are reused
+            if (abort_flag) break;
         }
         tc_fence_before();
         bar_sync_named(1, kMqThreads);
@@ -766,9 +824,9 @@ int launch_decode_mq(const DecodeParams& d, int num_kv_heads, int64_t num_blocks
         TQ_CUDA(cudaFuncSetAttribute(decode_mq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    // whole page ranges for every head pair
-    const int g = (grid / mp.head_pairs) * mp.head_pairs;
-    TQ_REQUIRE(g >= mp.head_pairs, TQ_ERR_INVALID, "num_ctas %d is smaller than the number of KV-head pairs %d", grid, mp.head_pairs);
+    // whole page ranges for every head pair (a grid smaller than the head pairs is rounded up to one range)
+    const int ranges = grid / mp.head_pairs > 0 ? grid / mp.head_pairs : 1;
+    const int g = ranges * mp.head_pairs;
     TQ_CUDA(launch_serialized(decode_mq_kernel, dim3((unsigned)g), dim3(kMqThreads), (size_t)smem, stream, mp));
     return TQ_OK;
 }
