@@ -18,7 +18,8 @@
 // other kernel, over gridDim.x / (heads / 2) ranges).  896 threads in seven warpgroups:
 //   warps 0-3    control: warp 0 streams the raw K pages and warp 2 the raw V pages (tiled tensor
 //                copies: boxes of 16 tokens x 160 bytes = both heads' slots, each into its own ring of
-//                four 64-token stages), warp 1 issues the tensor-core instructions;
+//                four 64-token stages), warp 1 issues the S = K^ Q^T instructions and warp 3 the
+//                O^T += V^^T P instructions;
 //   warps 4-7    softmax of the pair's first head, warps 8-11 of its second head: thread t owns
 //                token t of the 128-token tile: reads its row of S from tensor memory, applies the
 //                K norm and the scale, keeps a lazily raised running maximum per column, writes P
@@ -100,6 +101,12 @@ __device__ __forceinline__ void mq_mma(uint32_t tmem_d, uint64_t da, uint64_t db
 }
 __device__ __forceinline__ void mq_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -359,69 +366,67 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                     }
                 }
                 if (bad_page && lane == 0) atomicExch(&p.header[0], kStatusBadPage);
-            } else if (warp == 1) {
+            } else {
                 // =============================== tensor-core issue ======================================
+                // Warp 1 issues S = K^ Q^T and warp 3 O^T += V^^T P, each in tile-head order: S of a later
+                // tile-head never waits behind a PV that is still waiting for its softmax.  One elected lane
+                // issues; every descriptor is a compile-time constant (the head is unrolled).
                 constexpr uint32_t idesc_qk = (1u << 4) | ((uint32_t)(kMqCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
                 constexpr uint32_t idesc_pv = idesc_qk | (1u << 15) | (1u << 16);
-                // S = K^ Q^T of tile-head i: two halves of the contraction
-                auto issue_qk = [&](int i) -> bool {
-                    const int uu = u + i, h2 = i & 1;   // u is even: the S buffer is the head's
+                bool ok = true;
+                for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
 #pragma unroll
-                    for (int hh = 0; hh < 2; hh++) {
-                        if (!mq_wait(&kq_full[hh], uu & 1)) return false;
-                        if (hh == 0 && uu >= 2 && !mq_wait(&s_empty[h2], ((uu >> 1) - 1) & 1)) return false;
-                        tc_fence_after();
-                        if (lane == 0) {
-                            const uint64_t qoff = (uint64_t)((uint32_t)h2 * (64u * 256u) >> 4);
+                    for (int h2 = 0; h2 < 2; h2++) {
+                        const int uu = u + 2 * t + h2;   // u is even: buffers that alternate with uu are the head's
+                        if (warp == 1) {
 #pragma unroll
-                            for (int jj = 0; jj < 4; jj++) {
-                                constexpr uint64_t dk0 = mq_desc(kMqKhat, 2048, 128);
-                                constexpr uint64_t dq0 = mq_desc(kLutAddr + 128u, 1024, 256);
-                                const uint64_t da = dk0 + (uint64_t)((hh * kMqOperandHalf + jj * 4096) >> 4);
-                                const uint64_t db = dq0 + (uint64_t)(((hh * 8 + jj * 2) * 4 * 256) >> 4) + qoff;
-                                mq_mma(tm_s0 + 32 * h2, da, db, idesc_qk, (hh | jj) ? 1u : 0u);
+                            for (int hh = 0; hh < 2; hh++) {
+                                if (ok) ok = mq_wait(&kq_full[hh], uu & 1);
+                                if (ok && hh == 0 && uu >= 2) ok = mq_wait(&s_empty[h2], ((uu >> 1) - 1) & 1);
+                                if (!ok) break;
+                                tc_fence_after();
+                                if (elect_one()) {
+#pragma unroll
+                                    for (int jj = 0; jj < 4; jj++) {
+                                        constexpr uint64_t dk0 = mq_desc(kMqKhat, 2048, 128);
+                                        constexpr uint64_t dq0 = mq_desc(kLutAddr + 128u, 1024, 256);
+                                        const uint64_t da = dk0 + (uint64_t)((hh * kMqOperandHalf + jj * 4096) >> 4);
+                                        const uint64_t db = dq0 + (uint64_t)(((h2 * 64 + (hh * 8 + jj * 2) * 4) * 256) >> 4);
+                                        mq_mma(tm_s0 + 32 * h2, da, db, idesc_qk, (hh | jj) ? 1u : 0u);
+                                    }
+                                    mq_commit(&kq_empty[hh]);
+                                    if (hh == 1) mq_commit(&s_full[h2]);
+                                }
+                                __syncwarp();
                             }
-                            mq_commit(&kq_empty[hh]);
-                            if (hh == 1) mq_commit(&s_full[h2]);
+                        } else {
+                            if (ok) ok = mq_wait(&p_full[h2], (uu >> 1) & 1);
+#pragma unroll
+                            for (int th = 0; th < 2; th++) {
+                                if (ok) ok = mq_wait(&vq_full[th], uu & 1);
+                                if (!ok) break;
+                                tc_fence_after();
+                                if (elect_one()) {
+#pragma unroll
+                                    for (int jj = 0; jj < 4; jj++) {
+                                        constexpr uint64_t dv0 = mq_desc(kMqVhat, 2048, 128);
+                                        constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
+                                        constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
+                                        const uint64_t da = dv0 + (uint64_t)((th * kMqOperandHalf + jj * 4096) >> 4);
+                                        const uint64_t db = h2 ? dp1 + (uint64_t)(((th * 8 + jj * 2) * 512) >> 4)
+                                                               : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
+                                        mq_mma(tm_o0 + 32 * h2, da, db, idesc_pv, (th | jj) ? 1u : (uint32_t)(t > 0));
+                                    }
+                                    mq_commit(&vq_empty[th]);
+                                    if (th == 1) {
+                                        mq_commit(&p_empty[h2]);
+                                        if (t == ntiles - 1) mq_commit(&o_done[h2]);
+                                    }
+                                }
+                                __syncwarp();
+                            }
                         }
-                        __syncwarp();
                     }
-                    return true;
-                };
-                // O^T += V^^T P of tile-head i: two halves of the tile's tokens
-                auto issue_pv = [&](int i) -> bool {
-                    const int uu = u + i, h2 = i & 1, t = i >> 1;
-                    if (!mq_wait(&p_full[h2], (uu >> 1) & 1)) return false;
-#pragma unroll
-                    for (int th = 0; th < 2; th++) {
-                        if (!mq_wait(&vq_full[th], uu & 1)) return false;
-                        tc_fence_after();
-                        if (lane == 0) {
-#pragma unroll
-                            for (int jj = 0; jj < 4; jj++) {
-                                constexpr uint64_t dv0 = mq_desc(kMqVhat, 2048, 128);
-                                constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
-                                constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
-                                const uint64_t da = dv0 + (uint64_t)((th * kMqOperandHalf + jj * 4096) >> 4);
-                                const uint64_t db = h2 ? dp1 + (uint64_t)(((th * 8 + jj * 2) * 512) >> 4)
-                                                       : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
-                                mq_mma(tm_o0 + 32 * h2, da, db, idesc_pv, (t | th | jj) ? 1u : 0u);
-                            }
-                            mq_commit(&vq_empty[th]);
-                            if (th == 1) {
-                                mq_commit(&p_empty[h2]);
-                                if (t == ntiles - 1) mq_commit(&o_done[h2]);
-                            }
-                        }
-                        __syncwarp();
-                    }
-                    return true;
-                };
-                // S of the next tile-head is issued before this one's PV, so that the two softmax groups overlap
-                bool ok = !abort_flag && issue_qk(0);
-                for (int i = 0; i < 2 * ntiles && ok && !abort_flag; i++) {
-                    if (i + 1 < 2 * ntiles) ok = issue_qk(i + 1);
-                    if (ok) ok = issue_pv(i);
                 }
                 if (!ok && !abort_flag) {
                     abort_flag = 1;
