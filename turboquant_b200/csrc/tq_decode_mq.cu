@@ -53,7 +53,8 @@ constexpr int kMqStages = 4;           // per ring (K, V)
 constexpr int kMqBoxBytes = 16 * 160;  // one page half of a head pair
 constexpr int kMqStageBytes = 4 * kMqBoxBytes;  // 4 pages of K or of V
 constexpr int kMqOperandHalf = 16384;  // 64 contraction indices x 128 rows x 2 bytes
-constexpr uint32_t kMqWaitLimit = 1u << 18;
+constexpr uint32_t kMqWaitLimit = 1u << 18;   // tries per wait: at most about a quarter of a second
+constexpr uint32_t kMqSuspendNs = 1000;       // suspend-time hint of one try
 constexpr int kMqTmemCols = 128;       // S x 2, O x 2 heads, 32 columns each
 
 // shared-window offsets: the K ring and half of the V ring below the table, the table (with Q^T, one P
@@ -80,10 +81,23 @@ struct MqParams {
     int ncols;                          // valid query columns per KV head (queries x GQA ratio)
 };
 
-// Bounded wait of a whole warp; the answer is the same in every lane.
+// Bounded wait of a whole warp; the answer is the same in every lane.  The try carries a suspend-time
+// hint: a waiting warp sleeps in the barrier unit until the phase completes (or the hint runs out)
+// instead of spinning through the issue slots of the warps that have work.
+__device__ __forceinline__ bool mq_try_wait_hint(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kMqSuspendNs)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mq_wait(uint64_t* bar, uint32_t parity) {
     bool done = false;
-    for (uint32_t i = 0; i < kMqWaitLimit && !done; i++) done = mbar_try_wait(bar, parity);
+    for (uint32_t i = 0; i < kMqWaitLimit && !done; i++) done = mq_try_wait_hint(bar, parity);
     return __all_sync(0xffffffffu, done);
 }
 
@@ -497,7 +511,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             if (!vteam) {
                 // =============================== dequantize K ========================================
                 // thread = (token, 16-byte piece of the half); the warp's 32 tokens lie in one stage
-                const int tok = dt & 127, piece = dt >> 7;
+                // (lanes four tokens apart would meet in the same banks, 4 x 160 bytes = 5 x 128: they take different pieces)
+                const int tok = dt & 127, piece = (dt >> 7) ^ ((tok >> 2) & 1);
                 for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
                     const int n = tile_n + t;
                     const int st = (2 * n + (tok >> 6)) & 3;
@@ -533,7 +548,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             } else {
                 // =============================== dequantize V ========================================
                 // thread = (token of the half, 16-byte piece of the row)
-                const int tl = dt & 63, pc = dt >> 6;
+                const int tl = dt & 63, pc = (dt >> 6) ^ ((tl >> 2) & 1);   // pieces swapped as in the K team
                 for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
                     const int n = tile_n + t;
                     for (int h2 = 0; h2 < 2 && ok; h2++) {
