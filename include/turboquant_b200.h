@@ -154,8 +154,11 @@ int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads, int 
  * of the 1M-token configuration, or any caller that would otherwise repeat a sequence as batch
  * rows): q and out are [batch][queries_per_seq][num_q_heads][head_dim], out_lse
  * [batch][queries_per_seq][num_q_heads]; seq_lens and the page table are per sequence.  The
- * queries ride in the otherwise padded columns of the 8-wide query tile, so the KV is streamed
- * and dequantized once for all of them: queries_per_seq x (num_q_heads / num_kv_heads) <= 8.
+ * queries ride in the columns of one query tile, so the KV is streamed and dequantized once for
+ * all of them.  queries_per_seq x (num_q_heads / num_kv_heads) <= 8 takes the 8-wide tile of the
+ * mma.sync kernel; 9 ... 32 columns take the wide-tile kernel (tcgen05.mma, accumulators in tensor
+ * memory), which needs head_dim 128 and 2, 4, 8 or 16 KV heads and ignores num_ctas below the
+ * number of KV-head pairs.
  * The workspace is sized with tq_decode_workspace_bytes(batch, queries_per_seq * num_q_heads, ...).
  * kv_begin / kv_end restrict the tokens as in tq_decode_paged_partial (0, -1: all of them);
  * rotated_partial != 0 makes out (fp32) and out_lse (required) the rotated-domain partial and
