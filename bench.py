@@ -61,6 +61,8 @@ def parse():
     ap.add_argument("--ctx", type=int, default=32768)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--num-ctas", type=int, default=0)
+    ap.add_argument("--c4-tokens", type=int, default=1_048_576,
+                    help="--workload config4: tokens of the sequence (a smaller case for a profiler capture)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
@@ -1008,7 +1010,7 @@ def run_config4(args):
     from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
     from turboquant_b200.parallel import kv_ranges, kv_split_decode
     rank, world, dev = _setup_dist()
-    total, nq = 1_048_576, 8
+    total, nq = args.c4_tokens, 8
     a, b = kv_ranges(total, world)[rank]
     n_local = b - a
     attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, num_ctas=args.num_ctas)
@@ -1052,7 +1054,7 @@ def run_config4(args):
             "metric": "decode_attn_tokens_per_s", "value": nq / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "config4: one 1,048,576-token sequence, 8 decode queries, one layer, KV axis split "
+            "config": {"workload": f"config4: one {total:,}-token sequence, 8 decode queries, one layer, KV axis split "
                                    "contiguously over the GPUs, partial (o, lse) exchanged, merged on every GPU",
                        "exchange_bytes_per_rank": nq * HQ * (D + 1) * 4,
                        "exchange": ("none (one GPU)" if world == 1 else
@@ -1061,7 +1063,7 @@ def run_config4(args):
                        "note": f"the 8 queries run as {rows} row(s) of {share} queries that share one pass over the KV "
                                "(the wide-tile tcgen05 kernel: 32 query columns per KV head); the algorithmic bytes "
                                "below count the KV once",
-                       "l2": "1.34 GB of pages per pass, far larger than L2"},
+                       "l2": f"{total * HKV * 160 / 1e9:.2f} GB of pages per pass, larger than L2"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak * world, "unit": "GB/s",
                          "frac": ach / (peak * world), "peak_source": peak_src, "algorithmic_bytes_per_launch": alg,
                          "physical_kv_bytes_streamed": rows * total * HKV * 160},
