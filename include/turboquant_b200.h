@@ -173,6 +173,25 @@ int tq_decode_paged_multi(const void* q, int q_dtype, int batch, int queries_per
                           void* workspace, size_t workspace_bytes, void* out, int out_dtype, float* out_lse,
                           int rotated_partial, int num_ctas, void* stream);
 
+/* tq_decode_paged_multi with a causal mask among the queries of a sequence: the queries_per_seq
+ * queries of a row are the LAST queries_per_seq tokens of that sequence, in order, their K / V already
+ * written to the cache (seq_lens counts them); query i attends to the first
+ * seq_len - (queries_per_seq - 1 - i) tokens.  This is a chunk of a prefill that continues over the
+ * quantized cache, or the verification step of speculative decoding, in one pass over the KV for
+ * up to 32 / (num_q_heads / num_kv_heads) query tokens; a longer chunk is several batch rows that
+ * share the page table and differ in seq_lens.  Always the wide-tile kernel: head_dim 128 or 96,
+ * 2, 4, 8 or 16 KV heads, whole sequences.  A query without a visible token gets zeros and LSE -inf.
+ * The reference's prefill does not read the cache at all (turboquant/vllm_backend_fused.py:336-369:
+ * FlashAttention over the fresh K / V only), so a chunk after the first one is wrong there; its
+ * upstream successor dequantizes the whole context to dense K / V first
+ * (docs/reference/vllm-upstream-turboquant-architecture.md:241-270). */
+int tq_decode_paged_causal(const void* q, int q_dtype, int batch, int queries_per_seq, int num_q_heads,
+                           int num_kv_heads, int head_dim, const void* kv_cache, int64_t num_blocks,
+                           int block_size, int slot_bytes, const int32_t* page_indices,
+                           const int32_t* page_indptr, int max_pages, const int32_t* seq_lens,
+                           const float* signs, float sm_scale, void* workspace, size_t workspace_bytes,
+                           void* out, int out_dtype, float* out_lse, int num_ctas, void* stream);
+
 /* Bulk dequantization of the cached tokens of `batch` sequences into dense, varlen-packed K and V
  * ([total_tokens][num_kv_heads][head_dim], row cu_seqlens[b] + t for token t of sequence b,
  * out_token_stride elements between tokens): what a chunk of new query tokens needs in order to

@@ -141,8 +141,9 @@ def test_vllm_backend_impl_write_and_decode(oracle, golden):
 def _backend_step(oracle, golden, cached, chunk, with_builder_facts):
     """One forward of the vLLM backend on a step with the given cached / new token counts per
     sequence, checked against plain torch attention: rows with one new token and cached context are
-    decode rows (every key, the new one included, is read from the quantized cache); all other rows
-    attend their dequantized cached tokens followed by the chunk's fresh K/V."""
+    decode rows, rows with up to eight new tokens and cached context are short rows (for both, every
+    key, the new ones included, is read from the quantized cache); all other rows attend their
+    dequantized cached tokens followed by the chunk's fresh K/V."""
     pytest.importorskip("vllm")
     from turboquant_b200.vllm_backend_fused import TurboQuantBackend, TurboQuantFusedImpl, step_shape
     try:
@@ -183,9 +184,9 @@ def _backend_step(oracle, golden, cached, chunk, with_builder_facts):
     decode_rows = []
     qi = 0
     for b in range(B):
-        is_decode = chunk[b] == 1 and cached[b] > 0
+        is_decode = 1 <= chunk[b] <= 8 and cached[b] > 0   # decode and short rows: this package's kernels
         if is_decode:
-            decode_rows.append(qi)
+            decode_rows.extend(range(qi, qi + chunk[b]))
         t = np.arange(total[b] if is_decode else cached[b])
         pages = case.block_table.numpy()[b, t // 16]
         kc = oracle.dequant_cache_rows(cache_np[0, pages, t % 16], signs, 128).reshape(-1, 8, 128)
@@ -238,3 +239,11 @@ def test_vllm_backend_mixed_decode_and_prefill_rows(oracle, golden, with_builder
 
 def test_vllm_backend_pure_first_chunks_use_fresh_kv(oracle, golden):
     _backend_step(oracle, golden, [0, 0], [33, 70], True)
+
+
+@pytest.mark.parametrize("with_builder_facts", [False, True])
+def test_vllm_backend_short_chunks_attend_the_quantized_cache(oracle, golden, with_builder_facts):
+    """Rows with two to eight new tokens over cached context (short continuation chunks, speculative
+    verification) go through the causal wide-tile kernel, next to decode rows, a longer chunk and a
+    first chunk; one of them has fewer cached tokens than pad queries."""
+    _backend_step(oracle, golden, [500, 3, 37, 1200, 0, 64], [1, 6, 3, 12, 2, 8], with_builder_facts)

@@ -295,6 +295,62 @@ def test_shared_kv_queries_match_repeated_rows(oracle, golden, nq, hq, hkv):
         np.testing.assert_allclose(lse.cpu().numpy().reshape(B * nq, hq)[ok], want_lse[ok], atol=2e-3)
 
 
+@pytest.mark.parametrize("nq,hq,hkv", [(8, 32, 8), (5, 32, 8), (2, 8, 4), (1, 32, 8), (16, 4, 2), (4, 16, 16)])
+def test_causal_queries_match_rows_of_their_own_length(oracle, golden, nq, hq, hkv):
+    """tq_decode_paged_causal: the queries of a row are the last tokens of its sequence; query i must
+    equal a plain decode row of length seq_len - (nq - 1 - i) (the oracle with one batch row per
+    query).  Lengths around page, tile and query-count boundaries, one shorter than the queries."""
+    lens = [40, 3, 1000, 16, 2100, 129, 128, 0]
+    B = len(lens)
+    case = synthetic.decode_case(seed=91 + nq, seq_lens=lens, heads=(hq, hkv), dtype=torch.float16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(B, nq, hq, 128, generator=g).to(torch.float16)
+    rep_bt = case.block_table.repeat_interleave(nq, dim=0)
+    off = torch.arange(nq - 1, -1, -1, dtype=torch.int32).repeat(B)
+    rep_len = (case.seq_lens.repeat_interleave(nq) - off).clamp(min=0)
+    want, want_lse = oracle.decode_paged(q.view(B * nq, hq, 128).float().numpy(), cache, rep_bt.numpy(),
+                                         rep_len.numpy(), golden["signs_seed42_d128"], SCALE, return_lse=True)
+    cache_d = torch.from_numpy(cache).to(DEV)
+    for ctas in (0, 5):
+        ws = torch.zeros(_cabi.decode_workspace_bytes(B, nq * hq, hkv, 128, ctas), dtype=torch.uint8, device=DEV)
+        out = torch.full((B, nq, hq, 128), float("nan"), dtype=torch.float16, device=DEV)
+        lse = torch.empty(B, nq, hq, dtype=torch.float32, device=DEV)
+        _cabi.decode_paged_causal(q.to(DEV), cache_d, case.block_table.to(DEV), case.seq_lens.to(DEV), signs_dev(),
+                                  SCALE, ws, out, out_lse=lse, num_ctas=ctas)
+        torch.cuda.synchronize()
+        assert ws[:4].view(torch.int32).item() == 0
+        got = out.float().cpu().numpy().reshape(B * nq, hq, 128)
+        assert_attention_close(got, want, f"causal nq={nq} ctas={ctas}")
+        empty = (rep_len == 0).numpy()
+        assert (got[empty] == 0).all()
+        ok = np.isfinite(want_lse)
+        np.testing.assert_allclose(lse.cpu().numpy().reshape(B * nq, hq)[ok], want_lse[ok], atol=2e-3)
+        assert np.isneginf(lse.cpu().numpy().reshape(B * nq, hq)[~ok]).all()
+
+
+def test_causal_chunk_as_rows_sharing_a_page_table(oracle, golden):
+    """A 40-token chunk after 1000 cached tokens as five rows of eight causal queries: the rows share
+    the sequence's page table and differ in seq_lens."""
+    total, chunk, nq = 1040, 40, 8
+    case = synthetic.decode_case(seed=5, seq_lens=[total], heads=(32, 8), dtype=torch.float16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(chunk, 32, 128, generator=g).to(torch.float16)
+    lens_q = torch.arange(total - chunk + 1, total + 1, dtype=torch.int32)       # what each query token sees
+    want = oracle.decode_paged(q.float().numpy(), cache, case.block_table.repeat(chunk, 1).numpy(), lens_q.numpy(),
+                               golden["signs_seed42_d128"], SCALE)
+    rows = chunk // nq
+    row_lens = lens_q[nq - 1::nq].contiguous()
+    ws = torch.zeros(_cabi.decode_workspace_bytes(rows, nq * 32, 8), dtype=torch.uint8, device=DEV)
+    out = torch.empty(rows, nq, 32, 128, dtype=torch.float16, device=DEV)
+    _cabi.decode_paged_causal(q.view(rows, nq, 32, 128).to(DEV), torch.from_numpy(cache).to(DEV),
+                              case.block_table.repeat(rows, 1).contiguous().to(DEV), row_lens.to(DEV), signs_dev(), SCALE, ws, out)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 0
+    assert_attention_close(out.float().cpu().numpy().reshape(chunk, 32, 128), want, "40-token chunk over 1000 cached tokens")
+
+
 def test_shared_kv_rejects_more_than_32_columns():
     assert _cabi.decode_max_queries_per_seq(32, 8) == 8
     q = torch.zeros(1, 9, 32, 128, dtype=torch.float16, device=DEV)

@@ -29,7 +29,7 @@ EXPORTS = (
     "tq_abi_version", "tq_last_error", "tq_codebook", "tq_write_kv_cache", "tq_quantize_flat",
     "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
     "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
-    "tq_decode_paged_static", "tq_decode_paged_multi", "tq_exchange_bytes", "tq_decode_paged_exchange",
+    "tq_decode_paged_static", "tq_decode_paged_multi", "tq_decode_paged_causal", "tq_exchange_bytes", "tq_decode_paged_exchange",
     "tq_dequant_paged", "tq_pages_packed_bytes", "tq_pages_gather", "tq_pages_scatter",
     "tq_decode_max_query_columns", "tq_set_exchange_wait_limit", "tq_decode_static_status", "tq_fault_counts",
     "tq_write_guard_stats", "tq_pages_packed_bytes_for_slot",
@@ -303,6 +303,29 @@ def decode_paged_multi(q, kv_cache, page_indices, seq_lens, signs, sm_scale: flo
         ctypes.c_float(sm_scale), _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
         _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), ctypes.c_int(1 if rotated_partial else 0),
         ctypes.c_int(num_ctas), _stream(q)))
+    return out
+
+
+def decode_paged_causal(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, workspace, out,
+                        page_indptr=None, max_pages: int | None = None, out_lse=None, num_ctas: int = 0):
+    """``decode_paged_multi`` with a causal mask among the queries of a row: ``q`` [batch, queries, Hq, D]
+    holds the last ``queries`` tokens of every sequence (already written to the cache and counted in
+    ``seq_lens``); query i sees the first ``seq_len - (queries - 1 - i)`` tokens."""
+    if max_pages is None:
+        max_pages = page_indices.shape[-1] if page_indices.dim() == 2 else 0
+    if q.dim() != 4:
+        raise TurboQuantError("q must be [batch, queries, num_q_heads, head_dim]")
+    if not q.is_contiguous():
+        raise TurboQuantError("q must be contiguous")
+    _decode_args(q.view(q.shape[0], -1, q.shape[3]), kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs)
+    B, NQ, Hq, D = q.shape
+    _, nb, bs, H, ebs = kv_cache.shape
+    _check(lib().tq_decode_paged_causal(
+        _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(NQ), ctypes.c_int(Hq),
+        ctypes.c_int(H), ctypes.c_int(D), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(ebs),
+        _ptr(page_indices), _ptr(page_indptr), ctypes.c_int(max_pages), _ptr(seq_lens), _ptr(signs),
+        ctypes.c_float(sm_scale), _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size()),
+        _ptr(out), ctypes.c_int(dtype_code(out.dtype)), _ptr(out_lse), ctypes.c_int(num_ctas), _stream(q)))
     return out
 
 

@@ -845,7 +845,7 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
                    float* out_lse, int emit_rotated, int num_ctas, void* stream);
 
 bool mq_applicable(int num_kv_heads, int cols);
-int launch_decode_mq(const DecodeParams& d, int num_kv_heads, int64_t num_blocks, int grid, cudaStream_t stream);
+int launch_decode_mq(const DecodeParams& d, int num_kv_heads, int64_t num_blocks, int grid, int causal, cudaStream_t stream);
 
 static thread_local cudaEvent_t g_events[3] = {nullptr, nullptr, nullptr};
 static int g_exchange_spin_limit = kExchangeSpinLimit;
@@ -915,7 +915,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
                          int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
                          const float* signs, float sm_scale, void* workspace, size_t workspace_bytes,
                          void* out, int out_dtype, float* out_lse, int emit_rotated, int num_ctas,
-                         void* stream, const ExchangeArgs* x = nullptr) {
+                         void* stream, const ExchangeArgs* x = nullptr, int causal = 0) {
     TQ_REQUIRE(batch >= 0, TQ_ERR_INVALID, "negative batch");
     if (batch == 0) return TQ_OK;
     if (x) {
@@ -929,7 +929,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     }
     TQ_REQUIRE(q && kv_cache && page_indices && seq_lens && signs && workspace && out, TQ_ERR_INVALID, "null pointer");
     if (head_dim != kHeadDim && head_dim != 96) {  // other head sizes (64, 256, ...): the plain kernels
-        TQ_REQUIRE(nq == 1 && !x, TQ_ERR_UNSUPPORTED,
+        TQ_REQUIRE(nq == 1 && !x && !causal, TQ_ERR_UNSUPPORTED,
                    "head size %d: one query per sequence and no KV-split exchange (those are built for padded size 128)", head_dim);
         TQ_REQUIRE(q_dtype >= TQ_F32 && q_dtype <= TQ_BF16 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad dtype");
         TQ_REQUIRE(((uintptr_t)workspace % 256) == 0, TQ_ERR_INVALID, "workspace must be 256-byte aligned");
@@ -947,7 +947,11 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
                "query heads must be a positive multiple of the KV heads, queries_per_seq >= 1");
     // up to 8 query columns per KV head: the mma.sync kernel; up to 32: the tcgen05 kernel
     const int cols = nq * (real_q_heads / num_kv_heads);
-    const bool wide = cols > 8;
+    // (causal queries always take the wide-tile kernel: it masks per column)
+    const bool wide = cols > 8 || causal;
+    TQ_REQUIRE(!causal || (mq_applicable(num_kv_heads, cols < 9 ? 9 : cols) && !x && kv_begin == 0 && kv_end < 0 && !emit_rotated),
+               TQ_ERR_UNSUPPORTED, "causal queries: queries_per_seq x query heads per KV head up to 32, 2, 4, 8 or 16 KV heads, "
+               "whole sequences (got %d x %d, %d KV heads)", nq, real_q_heads / num_kv_heads, num_kv_heads);
     TQ_REQUIRE(cols <= 8 || mq_applicable(num_kv_heads, cols), TQ_ERR_UNSUPPORTED,
                "queries_per_seq x query heads per KV head must be 1..8, or up to 32 with 2, 4, 8 or 16 KV heads (got %d x %d, "
                "%d KV heads)", nq, real_q_heads / num_kv_heads, num_kv_heads);
@@ -1012,7 +1016,7 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
         p.kv_head_off = kv0 * slot_bytes;
         p.q_head_base = kv0 * real_group;
         if (wide) {
-            rc = launch_decode_mq(p, num_kv_heads, num_blocks, ctas, s);
+            rc = launch_decode_mq(p, num_kv_heads, num_blocks, ctas, causal, s);
         } else if (strided) {
             switch (hk) {
                 case 16: rc = launch_decode<16, true>(p, ctas, s); break;
@@ -1144,6 +1148,19 @@ extern "C" int tq_set_exchange_wait_limit(int polls) {
 extern "C" size_t tq_exchange_bytes(int64_t rows, int world) {
     if (rows <= 0 || world < 1 || world > tq::kMaxExchangeRanks) return 0;
     return tq::ExchangeLayout(world, rows).total;
+}
+
+extern "C" int tq_decode_paged_causal(const void* q, int q_dtype, int batch, int queries_per_seq, int num_q_heads,
+                                      int num_kv_heads, int head_dim, const void* kv_cache, int64_t num_blocks,
+                                      int block_size, int slot_bytes, const int32_t* page_indices,
+                                      const int32_t* page_indptr, int max_pages, const int32_t* seq_lens,
+                                      const float* signs, float sm_scale, void* workspace, size_t workspace_bytes,
+                                      void* out, int out_dtype, float* out_lse, int num_ctas, void* stream) {
+    TQ_REQUIRE(queries_per_seq >= 1, TQ_ERR_INVALID, "queries_per_seq must be positive");
+    return tq::decode_common(q, q_dtype, batch, queries_per_seq, num_q_heads, num_kv_heads, head_dim, kv_cache,
+                             num_blocks, block_size, slot_bytes, page_indices, page_indptr, max_pages, seq_lens, 0,
+                             -1, signs, sm_scale, workspace, workspace_bytes, out, out_dtype, out_lse, 0, num_ctas,
+                             stream, nullptr, 1);
 }
 
 extern "C" int tq_decode_paged_exchange(const void* q, int q_dtype, int batch, int queries_per_seq,

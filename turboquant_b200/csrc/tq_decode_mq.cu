@@ -79,6 +79,7 @@ struct MqParams {
     alignas(64) CUtensorMap cache_map;  // uint8 [2][num_blocks * 16][H * 80], boxes of [1][16][160]
     int head_pairs;                     // KV heads / 2
     int ncols;                          // valid query columns per KV head (queries x GQA ratio)
+    int causal;                         // query i of n sees the first len - (n - 1 - i) tokens of its sequence
 };
 
 // Bounded wait of a whole warp; the answer is the same in every lane.  The try carries a suspend-time
@@ -637,6 +638,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 const int tok_global = (first_page + p0 + t * PPS) * kPageTokens + stid;
                 const bool valid = tok_global < len_eff && (p0 + t * PPS) * kPageTokens + stid < (p1 * kPageTokens);
                 const int uu = u + 2 * t + h2;
+                // causal queries: column cc belongs to query cc / group, which sees this token iff cc >= cmin
+                const int cmin = mp.causal ? (p.nq - len_eff + tok_global) * p.real_group : 0;
                 if (abort_flag) ok = false;
                 if (ok) ok = mq_wait(&s_full[h2], (uu >> 1) & 1);
                 tc_fence_after();
@@ -656,7 +659,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                         const uint4 mv = lds128(mq_hole(kHoleMax + h2) + (16 * half + cc) * 4);
                         const float m4[4] = {__uint_as_float(mv.x), __uint_as_float(mv.y), __uint_as_float(mv.z), __uint_as_float(mv.w)};
 #pragma unroll
-                        for (int i = 0; i < 4; i++) raise |= valid && __uint_as_float(sr[cc + i]) * kf > m4[i] + kRaiseThreshold;
+                        for (int i = 0; i < 4; i++)
+                            raise |= valid && 16 * half + cc + i >= cmin && __uint_as_float(sr[cc + i]) * kf > m4[i] + kRaiseThreshold;
                     }
                 }
                 // does any token of the tile exceed the running maximum of its column by 2^6?
@@ -674,7 +678,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                         tmem_ld16(tm_s + lane_base + 16 * half, sr);
 #pragma unroll
                         for (int cc = 0; cc < 16; cc++) {
-                            float v = valid ? __uint_as_float(sr[cc]) * kf : -INFINITY;
+                            float v = valid && 16 * half + cc >= cmin ? __uint_as_float(sr[cc]) * kf : -INFINITY;
 #pragma unroll
                             for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
                             if (lane == 16 * half + cc) sts32f(mq_hole(hole_col + wq) + lane * 4, v);
@@ -724,8 +728,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                         const float m4[4] = {__uint_as_float(mv.x), __uint_as_float(mv.y), __uint_as_float(mv.z), __uint_as_float(mv.w)};
 #pragma unroll
                         for (int i = 0; i < 4; i += 2) {
-                            const float e0 = valid ? fast_exp2(__uint_as_float(sr[cc + i]) * kf - m4[i]) : 0.f;
-                            const float e1 = valid ? fast_exp2(__uint_as_float(sr[cc + i + 1]) * kf - m4[i + 1]) : 0.f;
+                            const float e0 = valid && 16 * half + cc + i >= cmin ? fast_exp2(__uint_as_float(sr[cc + i]) * kf - m4[i]) : 0.f;
+                            const float e1 = valid && 16 * half + cc + i + 1 >= cmin ? fast_exp2(__uint_as_float(sr[cc + i + 1]) * kf - m4[i + 1]) : 0.f;
                             l_acc[16 * half + cc + i] += e0;
                             l_acc[16 * half + cc + i + 1] += e1;
                             ph[(cc + i) >> 1] = valid ? pack_half2(e0 * vf, e1 * vf) : 0u;
@@ -820,11 +824,12 @@ bool mq_applicable(int num_kv_heads, int cols) {
     return cols > 8 && cols <= kMqCols && (num_kv_heads == 2 || num_kv_heads == 4 || num_kv_heads == 8 || num_kv_heads == 16);
 }
 
-int launch_decode_mq(const DecodeParams& d, int num_kv_heads, int64_t num_blocks, int grid, cudaStream_t stream) {
+int launch_decode_mq(const DecodeParams& d, int num_kv_heads, int64_t num_blocks, int grid, int causal, cudaStream_t stream) {
     MqParams mp{};
     mp.d = d;
     mp.head_pairs = num_kv_heads / 2;
     mp.ncols = d.group;
+    mp.causal = causal;
     MqEncodeFn enc = mq_encode_fn();
     TQ_REQUIRE(enc != nullptr, TQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t row_bytes = (cuuint64_t)num_kv_heads * kSlotBytes;

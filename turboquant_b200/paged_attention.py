@@ -133,6 +133,28 @@ class TurboQuantPagedAttention:
                                  num_ctas=self.num_ctas, max_pages=block_table.shape[-1])
         return output
 
+    def decode_causal(self, query: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor,
+                      seq_lens: torch.Tensor, output: torch.Tensor | None = None,
+                      out_lse: torch.Tensor | None = None) -> torch.Tensor:
+        """Attention of the LAST ``queries`` tokens of every row's sequence over the quantized cache with
+        a causal mask among them: ``query`` [batch, queries, heads, head_size]; the tokens' K / V are
+        already in the cache and counted in ``seq_lens``.  One pass over the KV for
+        queries x (heads / kv_heads) <= 32 query columns: a chunk of a continuing prefill, or the
+        verification step of speculative decoding.  The reference's prefill ignores the cache
+        (turboquant/vllm_backend_fused.py:336-369)."""
+        B, NQ = query.shape[0], query.shape[1]
+        if output is None:
+            output = torch.empty_like(query)
+        if block_table.dtype != torch.int32:
+            block_table = block_table.to(torch.int32)
+        if seq_lens.dtype != torch.int32:
+            seq_lens = seq_lens.to(torch.int32)
+        _cabi.decode_paged_causal(query.contiguous(), self._as_bytes(kv_cache), block_table.contiguous(), seq_lens,
+                                  self.signs(query.device), self.scale, self.workspace(B, query.device, NQ),
+                                  output.view(B, NQ, self.num_heads, self.head_size), out_lse=out_lse,
+                                  num_ctas=self.num_ctas, max_pages=block_table.shape[-1])
+        return output
+
     def dequant_cached(self, kv_cache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                        cu_seqlens: torch.Tensor, total_tokens: int, dtype=torch.bfloat16):
         """Dense K / V ``[total_tokens, kv_heads, head_size]`` of the tokens already in the cache

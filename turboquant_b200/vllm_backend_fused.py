@@ -95,11 +95,19 @@ class TurboQuantMetadataBuilder(FlashAttentionMetadataBuilder):
         return md
 
 
+# Rows with cached context and at most this many new tokens (a short continuation chunk, the
+# verification step of speculative decoding) attend over the quantized cache in one pass of the
+# causal wide-tile decode kernel instead of a dequantized dense copy of their whole context.
+FUSED_CHUNK_MAX = 8
+
+
 def step_shape(common):
     """Host-side facts about a step from vLLM's CommonAttentionMetadata (its CPU copies of the query
     offsets and sequence lengths): a dict with ``any_cached`` (some sequence attends tokens that are
     only in the quantized cache), ``num_decode_rows`` (rows with one query token and cached context)
-    and ``dense_rows`` (dense K/V rows the other rows need: the sum of their sequence lengths)."""
+    ``num_short_rows`` (rows with 2 ... FUSED_CHUNK_MAX query tokens and cached context: they attend
+    straight over the quantized cache with a causal mask among their tokens) and ``dense_rows`` (dense
+    K/V rows the remaining rows need: the sum of their sequence lengths)."""
     qsl = common.query_start_loc_cpu
     n = int(common.num_reqs)
     q_lens = (qsl[1:n + 1] - qsl[:n]).to(torch.int64)
@@ -111,8 +119,11 @@ def step_shape(common):
     seq = seq[:n].to(torch.int64)
     cached = seq - q_lens
     is_decode = (q_lens == 1) & (cached > 0)
+    is_short = (q_lens > 1) & (q_lens <= FUSED_CHUNK_MAX) & (cached > 0)
+    dense = ~(is_decode | is_short)
     return {"any_cached": bool((cached > 0).any()), "num_decode_rows": int(is_decode.sum()),
-            "dense_rows": int(seq[~is_decode].sum()), "max_prefill_seq": int(seq[~is_decode].max()) if bool((~is_decode).any()) else 0}
+            "num_short_rows": int(is_short.sum()), "dense_rows": int(seq[dense].sum()),
+            "max_prefill_seq": int(seq[dense].max()) if bool(dense.any()) else 0}
 
 
 class TurboQuantFusedImpl(FlashAttentionImpl):
@@ -193,6 +204,10 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         * Decode rows (one query token, cached context) run through the paged decode kernel over
           the quantized cache: all rows are handed to it with the length of every other row set
           to zero, and their outputs are dropped.
+        * Rows with cached context and 2 ... FUSED_CHUNK_MAX new tokens run through the causal
+          wide-tile decode kernel: their tokens are already in the cache, the row's queries are
+          padded at the front to FUSED_CHUNK_MAX (a pad query sees fewer tokens than the first real
+          one and its output is dropped), every other row has length zero there.
         * Every other row b contributes ``seq_lens[b]`` keys to a dense varlen K/V: its cached
           tokens, dequantized from the cache, then the chunk's own fresh K/V (the chunk is already
           in the cache as well, quantized; its fresh values are used, as a first chunk would).  The
@@ -206,6 +221,8 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         q_lens = qsl[1:] - qsl[:-1]
         cached = seq_lens - q_lens
         is_dec = (q_lens == 1) & (cached > 0)
+        is_short = (q_lens > 1) & (q_lens <= FUSED_CHUNK_MAX) & (cached > 0)
+        fused = is_dec | is_short
         zero = torch.zeros_like(seq_lens)
         bt = md.block_table[:B]
         if bt.dtype != torch.int32:
@@ -215,8 +232,8 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         first_tok = qsl[:-1].long()
 
         # ---- prefill / continuation rows: dense K/V = dequantized cached tokens + fresh chunk -------
-        pf_seq = torch.where(is_dec, zero, seq_lens)
-        pf_cached = torch.where(is_dec, zero, cached)
+        pf_seq = torch.where(fused, zero, seq_lens)
+        pf_cached = torch.where(fused, zero, cached)
         cu_k = torch.zeros(B + 1, dtype=torch.int32, device=dev)
         cu_k[1:] = torch.cumsum(pf_seq, 0)
         max_seq_len = int(getattr(md, "max_seq_len", md.max_query_len))
@@ -224,7 +241,7 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
             rows, max_k = max(step["dense_rows"], 1), max(step["max_prefill_seq"], 1)
         else:
             rows, max_k = B * max_seq_len, max_seq_len
-        # one spare row at the end takes the fresh K/V of the decode rows' tokens, which nobody reads
+        # one spare row at the end takes the fresh K/V of the decode and short rows' tokens, which nobody reads
         k_all = torch.empty((rows + 1, self.num_kv_heads, self.head_size), dtype=query.dtype, device=dev)
         v_all = torch.empty_like(k_all)
         from . import _cabi
@@ -234,7 +251,7 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         tok = torch.arange(n, device=dev, dtype=torch.int32)
         seq_of = torch.bucketize(tok, qsl[1:], right=True)
         dest = (cu_k[:-1][seq_of] + pf_cached[seq_of] + (tok - qsl[:-1][seq_of])).long()
-        dest = torch.where(is_dec[seq_of], torch.full_like(dest, rows), dest)
+        dest = torch.where(fused[seq_of], torch.full_like(dest, rows), dest)
         k_all[dest] = key.view(n, self.num_kv_heads, self.head_size).to(k_all.dtype)
         v_all[dest] = value.view(n, self.num_kv_heads, self.head_size).to(v_all.dtype)
         out = flash_attn_varlen_func(q3, k_all, v_all, cu_seqlens_q=qsl, cu_seqlens_k=cu_k,
@@ -247,4 +264,17 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
             dec_out = torch.empty_like(q_rows)
             self._attn.decode(q_rows, kv_cache, bt, dec_lens, dec_out)
             out[first_tok] = torch.where(is_dec[:, None, None], dec_out.to(out.dtype), out[first_tok])
+        # ---- short rows: causal queries over the quantized cache, padded at the front --------------
+        if step is None or step.get("num_short_rows", 0) > 0:
+            nq = FUSED_CHUNK_MAX
+            slot = (seq_of * nq + (nq - q_lens[seq_of]) + (tok - qsl[:-1][seq_of])).long()
+            slot = torch.where(is_short[seq_of], slot, torch.full_like(slot, B * nq))   # others: the spare row
+            q_pad = torch.zeros((B * nq + 1, self.num_heads, self.head_size), dtype=query.dtype, device=dev)
+            q_pad[slot] = q3
+            short_lens = torch.where(is_short, seq_lens, zero).contiguous()
+            short_out = torch.empty((B, nq, self.num_heads, self.head_size), dtype=query.dtype, device=dev)
+            self._attn.decode_causal(q_pad[:B * nq].view(B, nq, self.num_heads, self.head_size), kv_cache, bt,
+                                     short_lens, short_out)
+            picked = short_out.view(B * nq, self.num_heads, self.head_size)[slot.clamp(max=B * nq - 1)]
+            out = torch.where(is_short[seq_of][:, None, None], picked.to(out.dtype), out)
         return out
