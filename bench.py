@@ -26,7 +26,9 @@ Further sections of the same line: `mixed` (64 mixed-length sequences, sharded o
 sequence) and `kv_split` (one 1,048,576-token sequence with 8 queries, KV axis split over the
 GPUs, partials exchanged by the kernels themselves and, for comparison, by an NCCL all-gather),
 each with its own oracle parity check; with N > 1 also `strong` (the stated batch of 8 split
-over the GPUs by sequence and by KV head).  `--sections none` leaves them out.
+over the GPUs by sequence and by KV head), and `short_chunk` (8 new tokens per sequence over batch
+8 x 32768 cached tokens through the causal wide-tile kernel, against the same tokens as decode
+rows).  `--sections none` leaves them out.
 """
 from __future__ import annotations
 
@@ -69,7 +71,7 @@ def parse():
                     help="config4 on several GPUs: partials exchanged by the kernels themselves (peer stores + "
                          "flags) or by an NCCL all-gather")
     ap.add_argument("--sections", default="all",
-                    help="comma list of the extra sections of the config-1 line: mixed, kv_split, strong; all | none")
+                    help="comma list of the extra sections of the config-1 line: mixed, kv_split, strong, short_chunk; all | none")
     ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4", "sweep"],
                     help="config1 (default, the headline): batch 8 x 32k per GPU; config3: 64 mixed lengths sharded by "
                          "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge")
@@ -414,6 +416,74 @@ def section_mixed(args, rank, world, dev, peak):
             "limit": "whole call (decode + merge); bounded by the most loaded rank and the fixed cost of a call"}
 
 
+def section_short_chunk(args, rank, world, dev, peak):
+    """A chunk of 8 new tokens per sequence over batch 8 x 32768 cached tokens (a short continuation
+    of a prefill, or the verification step of speculative decoding with 8 draft tokens), one layer,
+    the same on every rank: (a) one pass of the causal wide-tile kernel over the quantized cache,
+    (b) the same 8 tokens as 8 plain decode rows per sequence (what the reference's decode op would
+    need: one query per batch row), (c) the bulk dequantization of the whole context to dense bf16
+    K / V alone, which a dense attention kernel would still have to follow.  Parity of (a) against
+    the oracle with one batch row per query token, first sequence."""
+    from oracle import tq_oracle
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    B, L, NQ = 8, 32768, 8
+    attn = TurboQuantPagedAttention(HQ, D, 1.0 / math.sqrt(D), HKV, num_ctas=args.num_ctas)
+    pages = L // PAGE
+    nb = B * pages
+    bt = torch.randperm(nb, generator=torch.Generator().manual_seed(8)).view(B, pages).to(torch.int32).to(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(8)
+    caches = [torch.zeros(kv_cache_shape(nb, PAGE, HKV, D), dtype=torch.uint8, device=dev) for _ in range(2)]
+    for c in caches:
+        for b in range(B):
+            _fill_sequence(attn, c, bt[b], L, gen, dev)
+    q = torch.randn(B, NQ, HQ, D, generator=gen, device=dev).to(torch.bfloat16)
+    sl = torch.full((B,), L, dtype=torch.int32, device=dev)
+    out = torch.empty_like(q)
+    state = {"i": 0}
+
+    def causal():
+        attn.decode_causal(q, caches[state["i"] % 2], bt, sl, out)
+        state["i"] += 1
+    rep_bt = bt.repeat_interleave(NQ, dim=0).contiguous()
+    rep_sl = (sl.repeat_interleave(NQ) - torch.arange(NQ - 1, -1, -1, dtype=torch.int32, device=dev).repeat(B)).contiguous()
+    q_rows, out_rows = q.view(B * NQ, HQ, D), torch.empty(B * NQ, HQ, D, dtype=q.dtype, device=dev)
+
+    def rows():
+        attn.decode(q_rows, caches[state["i"] % 2], rep_bt, rep_sl, out_rows)
+        state["i"] += 1
+    for _ in range(3):
+        causal()
+        rows()
+    steps = max(args.steps, 10)
+    ms_causal = _time_steps(causal, steps, world, dev)
+    ms_rows = _time_steps(rows, steps, world, dev)
+    cached = torch.full((B,), L - NQ, dtype=torch.int32, device=dev)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=dev) * (L - NQ)
+    for _ in range(2):
+        attn.dequant_cached(caches[0], bt, cached, cu, B * (L - NQ))
+    ms_dequant = _time_steps(lambda: attn.dequant_cached(caches[state["i"] % 2], bt, cached, cu, B * (L - NQ)), steps, world, dev)
+    attn.decode_causal(q, caches[0], bt, sl, out)
+    attn.decode(q_rows, caches[0], rep_bt, rep_sl, out_rows)
+    torch.cuda.synchronize()
+    status = attn.status(B, dev, NQ)
+    want = tq_oracle.decode_paged_parallel(q[0].float().cpu().numpy(), caches[0].cpu().numpy(), rep_bt[:NQ].cpu().numpy(),
+                                           rep_sl[:NQ].cpu().numpy(), attn.signs(dev).cpu().numpy(), 1.0 / math.sqrt(D),
+                                           threads=max(1, (os.cpu_count() or 1) // world))
+    par = oracle_parity(out[0].float().cpu().numpy(), want, "the 8 query tokens of sequence 0, 32768 cached tokens")
+    same = float((out.view(B * NQ, HQ, D).float() - out_rows.float()).abs().max())
+    alg = B * L * HKV * ALG_BYTES_PER_TOKEN_HEAD
+    del caches
+    torch.cuda.empty_cache()
+    return {"workload": "8 new tokens per sequence over batch 8 x 32768 cached tokens, one layer, per GPU",
+            "causal_one_pass": {"ms": ms_causal, "new_tokens_per_s": B * NQ / (ms_causal * 1e-3),
+                                "achieved_GBps": alg / (ms_causal * 1e-3) / 1e9, "frac": alg / (ms_causal * 1e-3) / 1e9 / peak},
+            "as_decode_rows": {"ms": ms_rows, "rows": B * NQ, "new_tokens_per_s": B * NQ / (ms_rows * 1e-3)},
+            "bulk_dequant_of_the_context_alone": {"ms": ms_dequant},
+            "speedup_over_decode_rows": ms_rows / ms_causal, "max_abs_difference_from_decode_rows": same,
+            "status": status, "parity": par, "steps": steps}
+
+
 def section_kv_split(args, rank, world, dev, peak):
     """Config 4: one sequence of 1,048,576 tokens, 8 decode queries, one layer.  The KV axis is split
     contiguously over the ranks; every rank decodes its range for all queries, the rotated partials
@@ -737,7 +807,7 @@ def run_ours(args):
         del want0
 
     # ---- strong scaling of the stated batch: the same B sequences split over the GPUs ------------
-    wanted = {x.strip() for x in args.sections.split(",")} if args.sections not in ("all", "") else {"mixed", "kv_split", "strong"}
+    wanted = {x.strip() for x in args.sections.split(",")} if args.sections not in ("all", "") else {"mixed", "kv_split", "strong", "short_chunk"}
     if args.sections == "none":
         wanted = set()
     strong = None
@@ -866,14 +936,16 @@ def run_ours(args):
                       q_dev[0].float().cpu().numpy(), attn.signs(dev).cpu().numpy())
 
     # ---- the other configs, each with its own oracle check (all ranks take part) ------------------
-    mixed = kv_split = None
-    if "mixed" in wanted or "kv_split" in wanted:
+    mixed = kv_split = short_chunk = None
+    if "mixed" in wanted or "kv_split" in wanted or "short_chunk" in wanted:
         del caches
         torch.cuda.empty_cache()
         if "mixed" in wanted:
             mixed = section_mixed(args, rank, world, dev, peak)
         if "kv_split" in wanted:
             kv_split = section_kv_split(args, rank, world, dev, peak)
+        if "short_chunk" in wanted:
+            short_chunk = section_short_chunk(args, rank, world, dev, peak)
 
     if rank != 0:
         if world > 1:
@@ -892,7 +964,7 @@ def run_ours(args):
                    "cuda_graph": graph is not None, "algorithmic_bytes_per_step": alg_bytes * NL,
                    "arithmetic": "f16 x f16 tensor-core products with f32 accumulation over 4-bit codes; bf16 queries and outputs"},
         "roofline": roofline, "parity": parity, "write": write, "dequant": dequant, "cpu_baseline": cpu,
-        "mixed": mixed, "kv_split": kv_split, "strong": strong,
+        "mixed": mixed, "kv_split": kv_split, "strong": strong, "short_chunk": short_chunk,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "api": "TurboQuantPagedAttention.write + .decode per layer, pinned host buffers, copies on two copy streams beside the kernels" + ("" if args.no_graph else ", step captured in a CUDA graph")},
         "gpu_launches": args.steps * NL * 2, "clocks": clocks,
