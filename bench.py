@@ -505,8 +505,8 @@ def section_kv_split(args, rank, world, dev, peak):
     gen.manual_seed(4 + 1000 * rank)
     _fill_sequence(attn, cache, bt_row, n_local, gen, dev)
     qgen = torch.Generator(device=dev)
-    qgen.manual_seed(4004)                                # the same queries on every rank; a stream of their own,
-    #                                                       not the one the K/V rows are drawn from
+    qgen.manual_seed(123457)                              # the same queries on every rank; a stream of their own,
+    #                                                       not one of the ranks' K/V streams (seeds 4 + 1000 r)
     share = min(nq, _cabi.decode_max_queries_per_seq(HQ, HKV))   # queries that ride one pass over the KV
     rows = nq // share
     q = torch.randn(rows, share, HQ, D, generator=qgen, device=dev).to(torch.bfloat16)
