@@ -792,6 +792,26 @@ def run_ours(args):
                 "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_ms": dec_avg,
                 "merge_avg_launch_ms": sum(mrg_ms) / len(mrg_ms),
                 "frac_whole_step": (alg_bytes * NL / (ms_step * 1e-3) / 1e9) / peak}
+    # The tcgen05 / tensor-memory variant of the loop on the same launch, for the record: the wide-tile kernel takes
+    # any number of query columns through its causal entry point (one query per sequence: the mask is a no-op).
+    try:
+        ev0 = [torch.cuda.Event(enable_timing=True) for _ in range(2 * min(NL, 6))]
+        alt = torch.empty_like(out_dev[0]).unsqueeze(1)
+        for layer in range(min(NL, 6) + 2):
+            lay = layer % min(NL, 6)
+            if layer >= 2:
+                ev0[2 * lay].record()
+            attn.decode_causal(q_dev[lay].unsqueeze(1), caches[lay], block_table, seq_lens, alt)
+            if layer >= 2:
+                ev0[2 * lay + 1].record()
+        torch.cuda.synchronize()
+        wide_ms = sorted(ev0[2 * i].elapsed_time(ev0[2 * i + 1]) for i in range(min(NL, 6)))
+        roofline["tcgen05_variant_same_launch"] = {
+            "kernel": "decode_mq_kernel + merge (whole call)", "ms": wide_ms[len(wide_ms) // 2],
+            "frac": alg_bytes / (wide_ms[len(wide_ms) // 2] * 1e-3) / 1e9 / peak,
+            "note": "operands through shared memory into tensor memory; kept for more than 8 query columns only"}
+    except Exception as e:  # geometry the wide-tile kernel does not take (odd KV head counts)
+        roofline["tcgen05_variant_same_launch"] = {"unavailable": str(e)[:200]}
 
     # ---- parity of the timed workload: layer 0's output against the oracle over the same bytes ----
     parity = None
