@@ -336,6 +336,35 @@ int tq_write_guard_stats(int64_t* rows_total, int64_t* rows_exact);
  * it off.  Not for use inside a stream capture. */
 int tq_debug_set_decode_events(void* ev_start, void* ev_mid, void* ev_end);
 
+/* ---- The slot format of vLLM's native TurboQuant backend ("turboquant_4bit_nc") --------------
+ * A second wire format behind the same library, as the reference documents it
+ * (docs/reference/vllm-upstream-turboquant-architecture.md:33-94 layout, :100-175 store, :178-240
+ * decode): ONE cache tensor uint8 [num_blocks][block_size][num_kv_heads][slot_bytes], slot =
+ * [K codes d/2 | ||k|| fp16 | V codes d/2 | V scale fp16 | V zero fp16] (134 bytes at d = 128), the
+ * even dim in the LOW nibble.  K: x / (||x|| + 1e-8), Hadamard / sqrt(d) WITHOUT the sign vector,
+ * 4-bit Lloyd-Max of N(0, 1/d); V: uniform 4 bits between the row's minimum and maximum
+ * (scale = (max - min) / 15, code = clamp(trunc((v - min) / scale + 1/2), 0, 15), zero = min; a
+ * constant row gets code 0), dequantized as code * scale + zero in the original domain.
+ * head_dim 64, 128 or 256; 16-token pages for the decode; up to 8 query heads per KV head.
+ * Plain kernels (a warp per row, a block per (split, sequence, KV head)), not tuned for bandwidth.
+ * tq_nc_write_kv_cache stands in for upstream's do_kv_cache_update / _tq_fused_store_mse,
+ * tq_nc_decode_paged for _tq_decode_stage1 + the stage-2 merge.  A slot id outside the cache is
+ * skipped and counted (tq_nc_write_dropped); the decode's workspace starts with the sticky status
+ * word of the other decode kernels (4: sequence longer than its page table, 5: page id outside the
+ * cache; both skip the access). */
+int tq_nc_slot_bytes(int head_dim);
+int tq_nc_write_kv_cache(const void* key, const void* value, int in_dtype, int64_t num_tokens, int num_kv_heads,
+                         int head_dim, int64_t k_token_stride, int64_t v_token_stride, void* kv_cache,
+                         int64_t num_blocks, int block_size, int slot_bytes, const void* slot_mapping,
+                         int slot_dtype, void* stream);
+size_t tq_nc_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim, int num_ctas);
+int tq_nc_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                       const void* kv_cache, int64_t num_blocks, int block_size, int slot_bytes,
+                       const int32_t* page_indices, const int32_t* page_indptr, int max_pages,
+                       const int32_t* seq_lens, float sm_scale, void* workspace, size_t workspace_bytes,
+                       void* out, int out_dtype, float* out_lse, int num_ctas, void* stream);
+int tq_nc_write_dropped(int32_t* count);
+
 #ifdef __cplusplus
 }
 #endif

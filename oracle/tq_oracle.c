@@ -393,3 +393,61 @@ void tqo_merge_partials(const float* partial_o, const float* partial_lse, int S,
         if (lse_out) lse_out[r] = (float)(m + log(wsum));
     }
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * The slot format of vLLM's native backend ("turboquant_4bit_nc") as the reference documents it
+ * (docs/reference/vllm-upstream-turboquant-architecture.md:33-94 layout, :100-175 store):
+ *   slot = [K codes d/2 | ||k|| fp16 | V codes d/2 | V scale fp16 | V zero fp16], even dim in the
+ *   LOW nibble; K: x / (||x|| + 1e-8), Hadamard / sqrt(d) without signs, Lloyd-Max of N(0, 1/d);
+ *   V: scale = (max - min) / 15, code = clamp(trunc((v - min) / scale + 1/2), 0, 15), zero = min.
+ * PARITY UNPINNED: the reference tree holds no code and no vectors for this format (upstream's
+ * kernels live in vLLM); this restates the description.  Choices the description leaves open are
+ * made here and in the kernels alike: the norm uses the summation order of row_norm above, the
+ * Hadamard product is evaluated as butterflies, a constant V row gets code 0 everywhere.
+ * ------------------------------------------------------------------------------------------- */
+void tqo_nc_store_rows(const float* k, const float* v, int64_t rows, int d, uint8_t* slots, int slot_bytes) {
+    float bnd[15], cen[16];
+    tqo_codebook(d, 4, cen, bnd);
+    float* y = (float*)malloc(sizeof(float) * (size_t)d);
+    uint8_t* idx = (uint8_t*)malloc((size_t)d);
+    const int qb = d / 2, kps = qb + 2;
+    for (int64_t r = 0; r < rows; r++) {
+        const float* kr = k + r * d;
+        const float* vr = v + r * d;
+        uint8_t* dst = slots + r * slot_bytes;
+        const float norm = row_norm(kr, d);
+        const float den = norm + 1e-8f;
+        for (int i = 0; i < d; i++) y[i] = kr[i] / den;
+        tqo_fwht(y, d);
+        for (int i = 0; i < d; i++) idx[i] = (uint8_t)bucketize(y[i], bnd, 15);
+        for (int b = 0; b < qb; b++) dst[b] = (uint8_t)(idx[2 * b] | (idx[2 * b + 1] << 4));
+        const uint16_t nh = f32_to_f16(norm);
+        dst[qb] = (uint8_t)(nh & 0xFF);
+        dst[qb + 1] = (uint8_t)(nh >> 8);
+        float mn = vr[0], mx = vr[0];
+        for (int i = 1; i < d; i++) {
+            mn = fminf(mn, vr[i]);
+            mx = fmaxf(mx, vr[i]);
+        }
+        const float vs = (mx - mn) / 15.0f;
+        for (int i = 0; i < d; i++) {
+            float qv = 0.0f;
+            if (vs > 0.0f) {
+                const float num = vr[i] - mn;
+                const float quo = num / vs;
+                qv = quo + 0.5f;
+            }
+            qv = fminf(fmaxf(qv, 0.0f), 15.0f);
+            idx[i] = (uint8_t)(int)qv;
+        }
+        uint8_t* vd = dst + kps;
+        for (int b = 0; b < qb; b++) vd[b] = (uint8_t)(idx[2 * b] | (idx[2 * b + 1] << 4));
+        const uint16_t sh = f32_to_f16(vs), zh = f32_to_f16(mn);
+        vd[qb] = (uint8_t)(sh & 0xFF);
+        vd[qb + 1] = (uint8_t)(sh >> 8);
+        vd[qb + 2] = (uint8_t)(zh & 0xFF);
+        vd[qb + 3] = (uint8_t)(zh >> 8);
+    }
+    free(y);
+    free(idx);
+}

@@ -204,3 +204,66 @@ def low_first_to_cache_order(packed: np.ndarray) -> np.ndarray:
     """Swap nibbles: TurboQuantMSE's _pack_bits order -> the paged cache's order."""
     packed = np.asarray(packed, np.uint8)
     return (((packed & 0x0F) << 4) | (packed >> 4)).astype(np.uint8)
+
+
+# ---------------------------------------------------------------------------------------------
+# The slot format of vLLM's native backend ("turboquant_4bit_nc"), restated from the description
+# in docs/reference/vllm-upstream-turboquant-architecture.md:33-94 (layout), :100-175 (store),
+# :178-240 (decode).  PARITY UNPINNED: the reference tree has neither code nor vectors for it.
+# ---------------------------------------------------------------------------------------------
+def nc_slot_bytes(head_dim: int) -> int:
+    return (head_dim // 2 + 2) + (head_dim // 2 + 4)
+
+
+def nc_store(kv_cache: np.ndarray, key, value, slot_mapping) -> None:
+    """kv_cache uint8 [nb, bs, H, slot]; key / value [T, H, d] (values as the kernel sees them after
+    the cast to fp32); slots with a negative id are skipped."""
+    key, value = _f32(key), _f32(value)
+    T, H, d = key.shape
+    nb, bs, _, sb = kv_cache.shape
+    rows = np.zeros((T * H, sb), np.uint8)
+    L = lib()
+    L.tqo_nc_store_rows.restype = None
+    L.tqo_nc_store_rows(_p(key.reshape(T * H, d)), _p(value.reshape(T * H, d)), ctypes.c_int64(T * H), ctypes.c_int(d),
+                        _p(rows), ctypes.c_int(sb))
+    rows = rows.reshape(T, H, sb)
+    flat = kv_cache.reshape(nb * bs, H, sb)
+    n = nc_slot_bytes(d)
+    for t, s in enumerate(np.asarray(slot_mapping).tolist()):
+        if s >= 0:
+            flat[s, :, :n] = rows[t, :, :n]
+
+
+def nc_decode(q, kv_cache: np.ndarray, block_table, seq_lens, sm_scale: float, return_lse: bool = False):
+    """q [B, Hq, d] -> out [B, Hq, d]: scores in the rotated domain (q H / sqrt(d) against the K
+    centroids times the fp16 norm), values code * scale + zero, fp32 softmax."""
+    q = _f32(q)
+    B, Hq, d = q.shape
+    nb, bs, H, sb = kv_cache.shape
+    g = Hq // H
+    cen, _ = codebook(d, 4)
+    qb, kps = d // 2, d // 2 + 2
+    out = np.zeros((B, Hq, d), np.float32)
+    lse = np.full((B, Hq), -np.inf, np.float32)
+    for b in range(B):
+        n = int(seq_lens[b])
+        if n == 0:
+            continue
+        t = np.arange(n)
+        slots = kv_cache[np.asarray(block_table)[b, t // bs], t % bs]          # [n, H, sb]
+        kc = slots[..., :qb]
+        kidx = np.stack((kc & 15, kc >> 4), -1).reshape(n, H, d)
+        kn = slots[..., qb:qb + 2].copy().view(np.float16).astype(np.float32)[..., 0]
+        khat = cen[kidx] * kn[..., None]
+        vc = slots[..., kps:kps + qb]
+        vidx = np.stack((vc & 15, vc >> 4), -1).reshape(n, H, d).astype(np.float32)
+        vsz = slots[..., kps + qb:kps + qb + 4].copy().view(np.float16).astype(np.float32)   # [n, H, 2]
+        vhat = vidx * vsz[..., :1] + vsz[..., 1:]
+        qr = fwht(q[b].reshape(Hq, d)).reshape(H, g, d)
+        s = np.einsum("hgd,nhd->hgn", qr, khat).astype(np.float64) * sm_scale
+        m = s.max(-1, keepdims=True)
+        e = np.exp(s - m)
+        l = e.sum(-1, keepdims=True)
+        out[b] = np.einsum("hgn,nhd->hgd", e / l, vhat.astype(np.float64)).reshape(Hq, d).astype(np.float32)
+        lse[b] = (m + np.log(l)).reshape(Hq).astype(np.float32)
+    return (out, lse) if return_lse else out

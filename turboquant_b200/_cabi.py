@@ -29,7 +29,8 @@ EXPORTS = (
     "tq_abi_version", "tq_last_error", "tq_codebook", "tq_write_kv_cache", "tq_quantize_flat",
     "tq_dequantize_flat", "tq_fwht", "tq_decode_workspace_bytes", "tq_decode_paged",
     "tq_decode_paged_partial", "tq_merge_rotated", "tq_debug_set_decode_events",
-    "tq_decode_paged_static", "tq_decode_paged_multi", "tq_decode_paged_causal", "tq_exchange_bytes", "tq_decode_paged_exchange",
+    "tq_decode_paged_static", "tq_decode_paged_multi", "tq_decode_paged_causal", "tq_nc_slot_bytes",
+    "tq_nc_write_kv_cache", "tq_nc_decode_workspace_bytes", "tq_nc_decode_paged", "tq_nc_write_dropped", "tq_exchange_bytes", "tq_decode_paged_exchange",
     "tq_dequant_paged", "tq_pages_packed_bytes", "tq_pages_gather", "tq_pages_scatter",
     "tq_decode_max_query_columns", "tq_set_exchange_wait_limit", "tq_decode_static_status", "tq_fault_counts",
     "tq_write_guard_stats", "tq_pages_packed_bytes_for_slot",
@@ -500,3 +501,72 @@ def decode_static_status(device=None) -> int:
     word = torch.zeros(1, dtype=torch.int32, device=dev)
     _check(lib().tq_decode_static_status(_ptr(word), _stream(word)))
     return int(word.item())
+
+
+# ---- the slot format of vLLM's native backend ("turboquant_4bit_nc"): one cache tensor ------------
+def nc_slot_bytes(head_dim: int) -> int:
+    n = int(lib().tq_nc_slot_bytes(ctypes.c_int(head_dim)))
+    if n == 0:
+        raise TurboQuantError(f"head_dim {head_dim}: the upstream slot format takes 64, 128 or 256")
+    return n
+
+
+def nc_write_kv_cache(key, value, kv_cache, slot_mapping) -> None:
+    """key / value [T, H, d] (fp32 / fp16 / bf16, last two dims contiguous) into kv_cache uint8
+    [num_blocks, block_size, H, slot]; slot_mapping int32 / int64 [T], negative ids skipped."""
+    for t, n in ((key, "key"), (value, "value"), (kv_cache, "kv_cache"), (slot_mapping, "slot_mapping")):
+        _cuda(t, n)
+    if key.dim() != 3 or key.shape != value.shape or key.dtype != value.dtype:
+        raise TurboQuantError("key and value must both be [tokens, kv_heads, head_dim] of one dtype")
+    if key.stride(2) != 1 or value.stride(2) != 1 or key.stride(1) != key.shape[2] or value.stride(1) != value.shape[2]:
+        raise TurboQuantError("key / value: the last two dims must be contiguous")
+    if kv_cache.dim() != 4 or not kv_cache.is_contiguous() or kv_cache.element_size() != 1:
+        raise TurboQuantError("kv_cache must be contiguous 1-byte [num_blocks, block_size, kv_heads, slot_bytes]")
+    if slot_mapping.dtype not in (torch.int32, torch.int64) or not slot_mapping.is_contiguous():
+        raise TurboQuantError("slot_mapping must be contiguous int32 or int64")
+    T, H, D = key.shape
+    nb, bs, Hc, sb = kv_cache.shape
+    if Hc != H or slot_mapping.numel() < T:
+        raise TurboQuantError("kv_cache heads / slot_mapping length do not match key")
+    _check(lib().tq_nc_write_kv_cache(
+        _ptr(key), _ptr(value), ctypes.c_int(dtype_code(key.dtype)), ctypes.c_int64(T), ctypes.c_int(H), ctypes.c_int(D),
+        ctypes.c_int64(key.stride(0)), ctypes.c_int64(value.stride(0)), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs),
+        ctypes.c_int(sb), _ptr(slot_mapping), ctypes.c_int(1 if slot_mapping.dtype == torch.int64 else 0), _stream(key)))
+
+
+def nc_decode_workspace_bytes(batch: int, num_q_heads: int, num_kv_heads: int, head_dim: int, num_ctas: int = 0) -> int:
+    lib().tq_nc_decode_workspace_bytes.restype = ctypes.c_size_t
+    return int(lib().tq_nc_decode_workspace_bytes(ctypes.c_int(batch), ctypes.c_int(num_q_heads), ctypes.c_int(num_kv_heads),
+                                                  ctypes.c_int(head_dim), ctypes.c_int(num_ctas)))
+
+
+def nc_decode_paged(q, kv_cache, page_indices, seq_lens, sm_scale: float, workspace, out, page_indptr=None,
+                    max_pages: int | None = None, out_lse=None, num_ctas: int = 0):
+    """One decode step over a cache in the upstream slot format: q / out [batch, Hq, d]."""
+    for t, n in ((q, "q"), (kv_cache, "kv_cache"), (page_indices, "page_indices"), (seq_lens, "seq_lens"),
+                 (workspace, "workspace"), (out, "out")):
+        _cuda(t, n)
+    if q.dim() != 3 or not q.is_contiguous() or out.shape != q.shape or not out.is_contiguous():
+        raise TurboQuantError("q and out must be contiguous [batch, num_q_heads, head_dim]")
+    if kv_cache.dim() != 4 or not kv_cache.is_contiguous() or kv_cache.element_size() != 1:
+        raise TurboQuantError("kv_cache must be contiguous 1-byte [num_blocks, block_size, kv_heads, slot_bytes]")
+    for t, n in ((page_indices, "page_indices"), (seq_lens, "seq_lens")):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise TurboQuantError(f"{n} must be contiguous int32")
+    if max_pages is None:
+        max_pages = page_indices.shape[-1] if page_indices.dim() == 2 else 0
+    B, Hq, D = q.shape
+    nb, bs, H, sb = kv_cache.shape
+    _check(lib().tq_nc_decode_paged(
+        _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(Hq), ctypes.c_int(H), ctypes.c_int(D),
+        _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(sb), _ptr(page_indices), _ptr(page_indptr),
+        ctypes.c_int(max_pages), _ptr(seq_lens), ctypes.c_float(sm_scale), _ptr(workspace),
+        ctypes.c_size_t(workspace.numel() * workspace.element_size()), _ptr(out), ctypes.c_int(dtype_code(out.dtype)),
+        _ptr(out_lse), ctypes.c_int(num_ctas), _stream(q)))
+    return out
+
+
+def nc_write_dropped() -> int:
+    n = ctypes.c_int32(0)
+    _check(lib().tq_nc_write_dropped(ctypes.byref(n)))
+    return int(n.value)

@@ -30,6 +30,7 @@ UNITS = {
     "tq_dequant.cu": ["-fmad=false"],
     "tq_pages.cu": [],
     "tq_generic.cu": ["-fmad=false"],
+    "tq_nc.cu": ["-fmad=false"],
 }
 
 
