@@ -45,7 +45,11 @@ def test_store_bytes_equal_the_oracle(d, dtype):
     cache = torch.full((nb, 16, 2, sb), 0x5A, dtype=torch.uint8, device=DEV)
     _cabi.nc_write_kv_cache(k.to(DEV), v.to(DEV), cache, slots.to(DEV))
     torch.cuda.synchronize()
-    assert np.array_equal(cache.cpu().numpy(), want)
+    got = cache.cpu().numpy()
+    diff = np.argwhere(got != want)
+    assert len(diff) == 0, f"{len(diff)} bytes differ, first at (page, entry, head, byte) {diff[0].tolist()}: " \
+                           f"{int(got[tuple(diff[0])])} vs {int(want[tuple(diff[0])])}; bytes of the slot that differ: " \
+                           f"{sorted(set(int(x[3]) for x in diff if (x[:3] == diff[0][:3]).all()))}"
     # int32 slots and a slot id outside the cache: skipped and counted
     before = _cabi.nc_write_dropped()
     bad = slots.to(torch.int32).clone()

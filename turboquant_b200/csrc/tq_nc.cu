@@ -114,11 +114,8 @@ __global__ void __launch_bounds__(kNcWarps * 32) write_nc_kernel(const __grid_co
         }
         __syncwarp();
         for (int b = lane; b < p.g.qbytes; b += 32) dst[b] = (uint8_t)(idx[2 * b] | (idx[2 * b + 1] << 4));
-        if (lane == 0) {
-            const uint16_t nh = __half_as_ushort(__float2half_rn(norm));
-            dst[p.g.qbytes] = (uint8_t)(nh & 0xFF);
-            dst[p.g.qbytes + 1] = (uint8_t)(nh >> 8);
-        }
+        // (slot sizes are even and the cache is 2-byte aligned: the fp16 fields take 16-bit stores)
+        if (lane == 0) *reinterpret_cast<__half*>(dst + p.g.qbytes) = __float2half_rn(norm);
         __syncwarp();
         // ---- V: uniform 4-bit between the row's minimum and maximum --------------------------------
         const T* vrow = reinterpret_cast<const T*>(p.src[1]) + t * p.token_stride[1] + (int64_t)h * d;
@@ -144,11 +141,8 @@ __global__ void __launch_bounds__(kNcWarps * 32) write_nc_kernel(const __grid_co
         uint8_t* vdst = dst + p.g.kps;
         for (int b = lane; b < p.g.qbytes; b += 32) vdst[b] = (uint8_t)(idx[2 * b] | (idx[2 * b + 1] << 4));
         if (lane == 0) {
-            const uint16_t sh = __half_as_ushort(__float2half_rn(vs)), zh = __half_as_ushort(__float2half_rn(mn));
-            vdst[p.g.qbytes] = (uint8_t)(sh & 0xFF);
-            vdst[p.g.qbytes + 1] = (uint8_t)(sh >> 8);
-            vdst[p.g.qbytes + 2] = (uint8_t)(zh & 0xFF);
-            vdst[p.g.qbytes + 3] = (uint8_t)(zh >> 8);
+            *reinterpret_cast<__half*>(vdst + p.g.qbytes) = __float2half_rn(vs);
+            *reinterpret_cast<__half*>(vdst + p.g.qbytes + 2) = __float2half_rn(mn);
         }
         __syncwarp();
     }
@@ -179,9 +173,7 @@ __device__ __forceinline__ float nc_load(const void* q, int dtype, int64_t i) {
     if (dtype == TQ_F16) return __half2float(reinterpret_cast<const __half*>(q)[i]);
     return reinterpret_cast<const float*>(q)[i];
 }
-__device__ __forceinline__ float nc_half_at(const uint8_t* p) {
-    return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
-}
+__device__ __forceinline__ float nc_half_at(const uint8_t* p) { return __half2float(*reinterpret_cast<const __half*>(p)); }
 
 __global__ void __launch_bounds__(kNcWarps * 32) decode_nc_kernel(const __grid_constant__ NcDecodeParams p) {
     extern __shared__ float ncsm[];
@@ -382,8 +374,9 @@ extern "C" int tq_nc_write_kv_cache(const void* key, const void* value, int in_d
     TQ_REQUIRE(in_dtype >= TQ_F32 && in_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad input dtype");
     TQ_REQUIRE(slot_dtype == TQ_I32 || slot_dtype == TQ_I64, TQ_ERR_INVALID, "slot_mapping must be int32 or int64");
     TQ_REQUIRE(num_kv_heads >= 1 && num_blocks >= 1 && block_size >= 1, TQ_ERR_INVALID, "bad cache geometry");
-    TQ_REQUIRE(slot_bytes >= nc_slot_bytes(head_dim), TQ_ERR_INVALID, "slot_bytes %d is smaller than head size %d needs (%d)",
-               slot_bytes, head_dim, nc_slot_bytes(head_dim));
+    TQ_REQUIRE(slot_bytes >= nc_slot_bytes(head_dim) && slot_bytes % 2 == 0 && ((uintptr_t)kv_cache % 2) == 0, TQ_ERR_INVALID,
+               "slot_bytes %d must be even and at least %d for head size %d; the cache 2-byte aligned", slot_bytes,
+               nc_slot_bytes(head_dim), head_dim);
     NcWriteParams p{};
     p.kv_cache = static_cast<uint8_t*>(kv_cache);
     p.src[0] = key;
@@ -429,8 +422,9 @@ extern "C" int tq_nc_decode_paged(const void* q, int q_dtype, int batch, int num
     TQ_REQUIRE(q && kv_cache && page_indices && seq_lens && workspace && out, TQ_ERR_INVALID, "null pointer");
     TQ_REQUIRE(nc_head_dim_ok(head_dim), TQ_ERR_UNSUPPORTED, "head_dim must be 64, 128 or 256 (a Hadamard size), got %d", head_dim);
     TQ_REQUIRE(block_size == kNcPage, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
-    TQ_REQUIRE(slot_bytes >= nc_slot_bytes(head_dim), TQ_ERR_INVALID, "slot_bytes %d is smaller than head size %d needs (%d)",
-               slot_bytes, head_dim, nc_slot_bytes(head_dim));
+    TQ_REQUIRE(slot_bytes >= nc_slot_bytes(head_dim) && slot_bytes % 2 == 0 && ((uintptr_t)kv_cache % 2) == 0, TQ_ERR_INVALID,
+               "slot_bytes %d must be even and at least %d for head size %d; the cache 2-byte aligned", slot_bytes,
+               nc_slot_bytes(head_dim), head_dim);
     TQ_REQUIRE(num_kv_heads >= 1 && num_q_heads % num_kv_heads == 0 && num_q_heads / num_kv_heads <= kNcMaxGroup,
                TQ_ERR_UNSUPPORTED, "query heads per KV head must be 1..%d", kNcMaxGroup);
     TQ_REQUIRE(q_dtype >= TQ_F32 && q_dtype <= TQ_BF16 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad dtype");
