@@ -351,6 +351,48 @@ def test_causal_chunk_as_rows_sharing_a_page_table(oracle, golden):
     assert_attention_close(out.float().cpu().numpy().reshape(chunk, 32, 128), want, "40-token chunk over 1000 cached tokens")
 
 
+def test_wide_tile_csr_table_and_kv_windows(oracle, golden):
+    """The wide-tile kernel (8 queries x GQA 4 = 32 columns) with a CSR page table, and as
+    rotated partials over KV windows merged by tq_merge_rotated (the multi-GPU contract)."""
+    lens = [1500, 90, 0, 300]
+    B, nq, hq = len(lens), 8, 32
+    case = synthetic.decode_case(seed=61, seq_lens=lens, dtype=torch.bfloat16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    q = torch.randn(B, nq, hq, 128, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+    rep_bt = case.block_table.repeat_interleave(nq, dim=0)
+    rep_len = case.seq_lens.repeat_interleave(nq)
+    want, want_lse = oracle.decode_paged(q.view(B * nq, hq, 128).float().numpy(), cache, rep_bt.numpy(), rep_len.numpy(),
+                                         golden["signs_seed42_d128"], SCALE, return_lse=True)
+    cache_d, qd, sl = torch.from_numpy(cache).to(DEV), q.to(DEV), case.seq_lens.to(DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(B, nq * hq, 8), dtype=torch.uint8, device=DEV)
+    # CSR table
+    pages = [(int(n) + 15) // 16 for n in lens]
+    indptr = torch.tensor([0] + list(np.cumsum(pages)), dtype=torch.int32, device=DEV)
+    indices = torch.cat([case.block_table[b, :p] for b, p in enumerate(pages)]).to(torch.int32).to(DEV)
+    out = torch.full((B, nq, hq, 128), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _cabi.decode_paged_multi(qd, cache_d, indices, sl, signs_dev(), SCALE, ws, out, page_indptr=indptr)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 0
+    assert_attention_close(out.float().cpu().numpy().reshape(B * nq, hq, 128), want, "wide tile, CSR table")
+    # KV windows -> rotated partials -> merge
+    windows = [(0, 512), (512, 1024), (1024, -1), (2048, -1)]
+    po = torch.empty(len(windows), B * nq, hq, 128, dtype=torch.float32, device=DEV)
+    pl = torch.empty(len(windows), B * nq, hq, dtype=torch.float32, device=DEV)
+    bt = case.block_table.to(DEV)
+    for i, (a, b) in enumerate(windows):
+        _cabi.decode_paged_multi(qd, cache_d, bt, sl, signs_dev(), SCALE, ws, po[i].view(B, nq, hq, 128),
+                                 out_lse=pl[i].view(B, nq, hq), kv_begin=a, kv_end=b, rotated_partial=True)
+    assert torch.isneginf(pl[3]).all()
+    merged = torch.empty(B * nq, hq, 128, dtype=torch.float32, device=DEV)
+    lse = torch.empty(B * nq, hq, dtype=torch.float32, device=DEV)
+    _cabi.merge_rotated(po, pl, signs_dev(), merged, lse)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 0
+    assert_attention_close(merged.cpu().numpy(), want, "wide tile, merged windows")
+    ok = np.isfinite(want_lse)
+    np.testing.assert_allclose(lse.cpu().numpy()[ok], want_lse[ok], atol=2e-3)
+
+
 def test_shared_kv_rejects_more_than_32_columns():
     assert _cabi.decode_max_queries_per_seq(32, 8) == 8
     q = torch.zeros(1, 9, 32, 128, dtype=torch.float16, device=DEV)

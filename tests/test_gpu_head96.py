@@ -77,3 +77,26 @@ def test_decode_and_dequant_head96(oracle, golden, heads):
         ks.append(oracle.dequant_cache_rows(cache[0, pages, t % 16], signs_np, D))
     assert k.shape == (total, heads[1], D)
     np.testing.assert_array_equal(k.cpu().numpy(), np.concatenate(ks))
+
+
+def test_wide_tile_and_causal_queries_head96(oracle, golden):
+    """Head size 96 through the wide-tile kernel: 8 shared-KV queries and 5 causal ones."""
+    lens = [700, 0, 33, 2049]
+    heads = (32, 8)
+    case = _case(8, lens, heads)
+    signs_np = golden["signs_seed42_d128"]
+    cache = np.zeros((2, case.num_blocks, 16, heads[1], 80), np.uint8)
+    oracle.write_kv_cache(cache, case.k.float().numpy(), case.v.float().numpy(), signs_np, case.slot_mapping.numpy(), D)
+    attn = TurboQuantPagedAttention(heads[0], D, SCALE, heads[1])
+    cache_d, bt, sl = torch.from_numpy(cache).to(DEV), case.block_table.to(DEV), case.seq_lens.to(DEV)
+    B = len(lens)
+    for nq, causal in ((8, False), (5, True)):
+        q = torch.randn(B, nq, heads[0], D, generator=torch.Generator().manual_seed(nq)).to(torch.float16)
+        off = torch.arange(nq - 1, -1, -1, dtype=torch.int32).repeat(B) if causal else torch.zeros(B * nq, dtype=torch.int32)
+        rep_len = (case.seq_lens.repeat_interleave(nq) - off).clamp(min=0)
+        want = oracle.decode_paged(q.view(B * nq, heads[0], D).float().numpy(), cache,
+                                   case.block_table.repeat_interleave(nq, dim=0).numpy(), rep_len.numpy(), signs_np, SCALE)
+        out = (attn.decode_causal if causal else attn.decode_shared)(q.to(DEV), cache_d, bt, sl)
+        torch.cuda.synchronize()
+        assert attn.status(B, DEV, nq) == 0 and out.shape == (B, nq, heads[0], D)
+        assert_attention_close(out.float().cpu().numpy().reshape(B * nq, heads[0], D), want, f"head 96, nq={nq}, causal={causal}")

@@ -284,7 +284,7 @@ def decode_paged_multi(q, kv_cache, page_indices, seq_lens, signs, sm_scale: flo
                        page_indptr=None, max_pages: int | None = None, out_lse=None, num_ctas: int = 0,
                        kv_begin: int = 0, kv_end: int = -1, rotated_partial: bool = False):
     """One decode step for sequences that carry several queries sharing their KV: ``q`` and ``out``
-    are [batch, queries, Hq, D], ``out_lse`` fp32 [batch, queries, Hq]; queries x (Hq / H) <= 8.
+    are [batch, queries, Hq, D], ``out_lse`` fp32 [batch, queries, Hq]; queries x (Hq / H) <= 32 (more than 8: the wide-tile kernel).
     The workspace is sized for queries x Hq heads.  ``rotated_partial``: fp32 rotated-domain
     partial + base-2 LSE over tokens [kv_begin, kv_end), as ``decode_paged_partial``."""
     if max_pages is None:
