@@ -55,7 +55,7 @@ constexpr int kMqStageBytes = 4 * kMqBoxBytes;  // 4 pages of K or of V
 constexpr int kMqOperandHalf = 16384;  // 64 contraction indices x 128 rows x 2 bytes
 constexpr uint32_t kMqWaitLimit = 1u << 18;   // tries per wait: at most about a quarter of a second
 constexpr uint32_t kMqSuspendNs = 1000;       // suspend-time hint of one try
-constexpr int kMqTmemCols = 128;       // S x 2, O x 2 heads, 32 columns each
+constexpr int kMqTmemCols = 256;       // S and O^T of the two heads (32 columns each), K^ of the two heads (64 each)
 
 // shared-window offsets: the K ring and half of the V ring below the table, the table (with Q^T, one P
 // and the norms in its holes), then the operand buffers, the rest of the V ring and the other P
@@ -114,6 +114,14 @@ __device__ __forceinline__ void mq_mma(uint32_t tmem_d, uint64_t da, uint64_t db
         ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// the same with the A operand in tensor memory (lane = row, two 16-bit elements per column)
+__device__ __forceinline__ void mq_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
 __device__ __forceinline__ void mq_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -165,6 +173,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&a)[4], const uint32_t (&b)[4]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};"
+                 ::"r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // tiled tensor copy of one box [1][16 tokens][160 bytes] at (x = byte in the token row, y = token, z = K / V)
 __device__ __forceinline__ void mq_box_g2s(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
@@ -218,8 +233,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             mbar_init(&rawv_empty[s], 8);   // every V warp reads every stage
         }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&kq_full[i], 8);
-            mbar_init(&kq_empty[i], 1);
+            mbar_init(&kq_full[i], 8);    // per head: K^ of a tile-head is in tensor memory
+            mbar_init(&kq_empty[i], 1);   // per head: its S has been computed
             mbar_init(&vq_full[i], 8);
             mbar_init(&vq_empty[i], 1);
             mbar_init(&s_full[i], 1);
@@ -331,7 +346,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tm_s0 = tmem, tm_o0 = tmem + 64;   // S buffers at +32 sb, O accumulators at +32 h2
+    const uint32_t tm_s0 = tmem, tm_o0 = tmem + 64, tm_k0 = tmem + 128;   // S, O^T at +32 h2; K^ at +64 h2
 
     // The roles part here for good: each lowers or raises its register count first, runs its own loop
     // over the block's segments, and meets the others only at barrier 1 (twice per segment: the rotated
@@ -394,26 +409,21 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                     for (int h2 = 0; h2 < 2; h2++) {
                         const int uu = u + 2 * t + h2;   // u is even: buffers that alternate with uu are the head's
                         if (warp == 1) {
+                            if (ok) ok = mq_wait(&kq_full[h2], (uu >> 1) & 1);
+                            if (ok && uu >= 2) ok = mq_wait(&s_empty[h2], ((uu >> 1) - 1) & 1);
+                            if (!ok) break;
+                            tc_fence_after();
+                            if (elect_one()) {
 #pragma unroll
-                            for (int hh = 0; hh < 2; hh++) {
-                                if (ok) ok = mq_wait(&kq_full[hh], uu & 1);
-                                if (ok && hh == 0 && uu >= 2) ok = mq_wait(&s_empty[h2], ((uu >> 1) - 1) & 1);
-                                if (!ok) break;
-                                tc_fence_after();
-                                if (elect_one()) {
-#pragma unroll
-                                    for (int jj = 0; jj < 4; jj++) {
-                                        constexpr uint64_t dk0 = mq_desc(kMqKhat, 2048, 128);
-                                        constexpr uint64_t dq0 = mq_desc(kLutAddr + 128u, 1024, 256);
-                                        const uint64_t da = dk0 + (uint64_t)((hh * kMqOperandHalf + jj * 4096) >> 4);
-                                        const uint64_t db = dq0 + (uint64_t)(((h2 * 64 + (hh * 8 + jj * 2) * 4) * 256) >> 4);
-                                        mq_mma(tm_s0 + 32 * h2, da, db, idesc_qk, (hh | jj) ? 1u : 0u);
-                                    }
-                                    mq_commit(&kq_empty[hh]);
-                                    if (hh == 1) mq_commit(&s_full[h2]);
+                                for (int j = 0; j < 8; j++) {   // K^ from tensor memory, 8 columns (16 positions) per instruction
+                                    constexpr uint64_t dq0 = mq_desc(kLutAddr + 128u, 1024, 256);
+                                    const uint64_t db = dq0 + (uint64_t)(((h2 * 64 + 2 * j * 4) * 256) >> 4);
+                                    mq_mma_ts(tm_s0 + 32 * h2, tm_k0 + 64 * h2 + 8 * j, db, idesc_qk, j ? 1u : 0u);
                                 }
-                                __syncwarp();
+                                mq_commit(&kq_empty[h2]);
+                                mq_commit(&s_full[h2]);
                             }
+                            __syncwarp();
                         } else {
                             if (ok) ok = mq_wait(&p_full[h2], (uu >> 1) & 1);
 #pragma unroll
@@ -511,38 +521,45 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             bool ok = true;
             if (!vteam) {
                 // =============================== dequantize K ========================================
-                // thread = (token, 16-byte piece of the half); the warp's 32 tokens lie in one stage
-                // (lanes four tokens apart would meet in the same banks, 4 x 160 bytes = 5 x 128: they take different pieces)
-                const int tok = dt & 127, piece = (dt >> 7) ^ ((tok >> 2) & 1);
+                // thread = (token, 32 of its 64 code bytes): K^ goes to TENSOR MEMORY, where it is the A operand of
+                // S = K^ Q^T: lane = token, column c = contraction positions 2c, 2c + 1 (one half2), 64 columns per
+                // tile-head, one buffer per head of the pair.  The warp's 32 tokens are its lane quarter and lie in
+                // one raw stage.  (Lanes four tokens apart would meet in the same banks, 4 x 160 bytes = 5 x 128:
+                // they read their two 16-byte pieces in opposite order.)
+                const int tok = dt & 127, piece = dt >> 7, swap = (tok >> 2) & 1;
+                const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
                 for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
                     const int n = tile_n + t;
                     const int st = (2 * n + (tok >> 6)) & 3;
                     ok = mq_wait(&rawk_full[st], (n >> 1) & 1);
                     const uint32_t krow0 = rawk_addr(st) + ((tok & 63) >> 4) * kMqBoxBytes + (tok & 15) * 160;
                     for (int h2 = 0; h2 < 2 && ok; h2++) {
-                        const int uu = u + 2 * t + h2;
-                        const uint32_t krow = krow0 + h2 * 80;
+                        const int uu = u + 2 * t + h2;   // u is even: the head's own buffer and barriers
+                        const uint32_t krow = krow0 + h2 * 80 + 16 * piece;
+                        const uint4 ca = lds128(krow + 32 * swap), cb = lds128(krow + 32 * (swap ^ 1));
+                        if (piece == 0)   // the K norms of the tile, times the scales, for the softmax warps
+                            sts32f(mq_hole(kHoleNorm + (uu & 3) * 8 + (tok >> 5)) + (tok & 31) * 4, lds_half(krow0 + h2 * 80 + 64) * p.k_scale);
+                        if ((uu >> 1) >= 1) ok = mq_wait(&kq_empty[h2], ((uu >> 1) - 1) & 1);   // S of the head's previous tile is done
+                        if (!ok) break;
+                        tc_fence_after();
 #pragma unroll
                         for (int hh = 0; hh < 2; hh++) {
-                            if (uu >= 1) ok = mq_wait(&kq_empty[hh], (uu - 1) & 1);
-                            if (!ok) break;
-                            const uint4 cw = lds128(krow + 32 * hh + 16 * piece);
-                            if (hh == 0 && piece == 0)   // the K norms of the tile, times the scales, for the softmax warps
-                                sts32f(mq_hole(kHoleNorm + (uu & 3) * 8 + (tok >> 5)) + (tok & 31) * 4, lds_half(krow + 64) * p.k_scale);
+                            const uint4 cw = (hh == 0) == (swap == 0) ? ca : cb;
                             const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
-                            const uint32_t dst = kMqKhat + hh * kMqOperandHalf + (4 * piece) * 2048 + tok * 16;
 #pragma unroll
-                            for (int w = 0; w < 4; w++) {
-                                uint32_t r[4];
-                                dequant8(w4[w], lut_lane, r);
-                                sts128(dst + w * 2048, r[0], r[1], r[2], r[3]);
+                            for (int w2 = 0; w2 < 2; w2++) {   // eight columns (two code words) per store
+                                uint32_t ra[4], rb[4];
+                                dequant8(w4[2 * w2], lut_lane, ra);
+                                dequant8(w4[2 * w2 + 1], lut_lane, rb);
+                                tmem_st8(tm_k0 + 64 * h2 + 32 * hh + 16 * piece + 8 * w2 + lane_base, ra, rb);
                             }
-                            fence_proxy_async();
-                            __syncwarp();
-                            if (lane == 0) {
-                                mbar_arrive(&kq_full[hh]);
-                                if (h2 == 1 && hh == 1) mbar_arrive(&rawk_empty[st]);   // both heads have read this stage
-                            }
+                        }
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(&kq_full[h2]);
+                            if (h2 == 1) mbar_arrive(&rawk_empty[st]);   // both heads have read this stage
                         }
                     }
                 }
