@@ -29,8 +29,9 @@
 //                operand buffers, laid out as the un-swizzled canonical core-matrix layouts the
 //                instruction descriptors name.  The two teams run independently of each other: K^ of
 //                a tile-head is typically written while V^ of the one before is.
-// K^ and V^ are produced in halves (64 of the 128 contraction indices each) into two 16 KB buffers
-// per operand, so that the tensor core works on one half while the next is being written.
+// K^ goes to TENSOR MEMORY (the A operand of S = K^ Q^T may live there: lane = token, two fp16 per
+// column; 64 columns per head), V^ to shared memory in halves of 64 tokens, one 32 KB buffer per head.
+// S is double-buffered per head, so K^, S and V^ of a head run ahead of its softmax.
 // Q^T (per head: 32 columns x 128 dims, fp16), P of the first head (128 tokens x 32 columns) and
 // the norms live in the unused upper halves of the lookup table's 256-byte rows: a core matrix is
 // exactly 128 bytes.  P of the second head has a buffer of its own.
@@ -55,24 +56,23 @@ constexpr int kMqStageBytes = 4 * kMqBoxBytes;  // 4 pages of K or of V
 constexpr int kMqOperandHalf = 16384;  // 64 contraction indices x 128 rows x 2 bytes
 constexpr uint32_t kMqWaitLimit = 1u << 18;   // tries per wait: at most about a quarter of a second
 constexpr uint32_t kMqSuspendNs = 1000;       // suspend-time hint of one try
-constexpr int kMqTmemCols = 256;       // S and O^T of the two heads (32 columns each), K^ of the two heads (64 each)
+constexpr int kMqTmemCols = 512;       // O^T (32 columns per head), K^ (64 per head), S (2 x 32 per head); 320 used
 
 // shared-window offsets: the K ring and half of the V ring below the table, the table (with Q^T, one P
 // and the norms in its holes), then the operand buffers, the rest of the V ring and the other P
 constexpr uint32_t kMqRawK = 4096;                              // 4 x 10240
 constexpr uint32_t kMqRawV01 = kMqRawK + 4 * kMqStageBytes;     // 2 x 10240, ends at 65536
-constexpr uint32_t kMqKhat = kLutAddr + kLutSpan;               // 2 x 16 KB
-constexpr uint32_t kMqVhat = kMqKhat + 2 * kMqOperandHalf;      // 2 x 16 KB
-constexpr uint32_t kMqRawV23 = kMqVhat + 2 * kMqOperandHalf;    // 2 x 10240
+constexpr uint32_t kMqVhat = kLutAddr + kLutSpan;               // per head 2 x 16 KB: 64 KB
+constexpr uint32_t kMqRawV23 = kMqVhat + 4 * kMqOperandHalf;    // 2 x 10240
 constexpr uint32_t kMqP1 = kMqRawV23 + 2 * kMqStageBytes;       // 8 KB: [16 token groups][4 column groups][8][16 B]
 constexpr uint32_t kMqSmemEnd = kMqP1 + 8192;                   // 225280
 static_assert(kMqRawV01 + 2 * kMqStageBytes == kLutAddr, "the rings below the table end where it starts");
 
 __device__ __forceinline__ uint32_t mq_hole(int i) { return kLutAddr + 256u * (uint32_t)i + 128u; }
-// holes: [0, 128) Q^T of the two heads, [128, 192) P of the first head, [192, 224) norms (4 tile-heads x
-// {K, V} x 128 floats: a buffer is rewritten four tile-heads later, which the S and P hand-overs order after
-// its last read), [224, 232) per-column scratch of the two softmax groups, [232, 234) the running maxima
-constexpr int kHoleQ = 0, kHoleP = 128, kHoleNorm = 192, kHoleCol = 224, kHoleMax = 232;
+// holes: [0, 128) Q^T of the two heads, [128, 192) P of the first head, [192, 224) K norms (8 tile-heads x 128
+// floats: K^ of a head runs up to three tiles ahead of its softmax), [224, 240) V norms (4 tile-heads), [240, 248)
+// per-column scratch of the two softmax groups, [248, 250) the running maxima
+constexpr int kHoleQ = 0, kHoleP = 128, kHoleNormK = 192, kHoleNormV = 224, kHoleCol = 240, kHoleMax = 248;
 
 struct MqParams {
     DecodeParams d;
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     const DecodeParams& p = mp.d;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t rawk_full[kMqStages], rawk_empty[kMqStages], rawv_full[kMqStages], rawv_empty[kMqStages];
-    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[2], vq_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2], o_done[2], vn_full[2];
+    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[4], vq_empty[4], s_full[4], s_empty[4], p_full[2], p_empty[2], o_done[2], vn_full[4];
     __shared__ int seg_seq[kMaxSegments], seg_p0[kMaxSegments], seg_p1[kMaxSegments];
     __shared__ int num_segments, abort_flag;
     __shared__ uint32_t tmem_slot;
@@ -235,14 +235,19 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
         for (int i = 0; i < 2; i++) {
             mbar_init(&kq_full[i], 8);    // per head: K^ of a tile-head is in tensor memory
             mbar_init(&kq_empty[i], 1);   // per head: its S has been computed
-            mbar_init(&vq_full[i], 8);
-            mbar_init(&vq_empty[i], 1);
-            mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 4);
+            for (int j = 0; j < 2; j++) {
+                mbar_init(&vq_full[2 * i + j], 8);    // [head][half of the tile's tokens]
+                mbar_init(&vq_empty[2 * i + j], 1);
+                mbar_init(&s_full[2 * i + j], 1);     // [head][parity of the tile]: S is double-buffered per head
+                mbar_init(&s_empty[2 * i + j], 4);
+            }
             mbar_init(&p_full[i], 4);
             mbar_init(&p_empty[i], 1);
             mbar_init(&o_done[i], 1);   // one phase per segment: the head's last PV has completed
-            mbar_init(&vn_full[i], 8);  // one phase per tile: the V norms of this half of the tile's tokens are written
+            // [half of the tile's tokens][parity of the tile]: the V norms are written.  Two barriers per half, since
+            // the V team of the first head may be a tile ahead of the second head's softmax.
+            mbar_init(&vn_full[2 * i], 8);
+            mbar_init(&vn_full[2 * i + 1], 8);
         }
         num_segments = 0;
         abort_flag = 0;
@@ -346,7 +351,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tm_s0 = tmem, tm_o0 = tmem + 64, tm_k0 = tmem + 128;   // S, O^T at +32 h2; K^ at +64 h2
+    // O^T at +32 h2, K^ at +64 h2, S at +64 h2 + 32 (tile parity)
+    const uint32_t tm_o0 = tmem, tm_k0 = tmem + 64, tm_s0 = tmem + 192;
 
     // The roles part here for good: each lowers or raises its register count first, runs its own loop
     // over the block's segments, and meets the others only at barrier 1 (twice per segment: the rotated
@@ -410,7 +416,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                         const int uu = u + 2 * t + h2;   // u is even: buffers that alternate with uu are the head's
                         if (warp == 1) {
                             if (ok) ok = mq_wait(&kq_full[h2], (uu >> 1) & 1);
-                            if (ok && uu >= 2) ok = mq_wait(&s_empty[h2], ((uu >> 1) - 1) & 1);
+                            const int tg = uu >> 1, sp = tg & 1;   // tile counter of the block, S buffer of the head
+                            if (ok && tg >= 2) ok = mq_wait(&s_empty[2 * h2 + sp], ((tg >> 1) - 1) & 1);
                             if (!ok) break;
                             tc_fence_after();
                             if (elect_one()) {
@@ -418,23 +425,23 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                                 for (int j = 0; j < 8; j++) {   // K^ from tensor memory, 8 columns (16 positions) per instruction
                                     constexpr uint64_t dq0 = mq_desc(kLutAddr + 128u, 1024, 256);
                                     const uint64_t db = dq0 + (uint64_t)(((h2 * 64 + 2 * j * 4) * 256) >> 4);
-                                    mq_mma_ts(tm_s0 + 32 * h2, tm_k0 + 64 * h2 + 8 * j, db, idesc_qk, j ? 1u : 0u);
+                                    mq_mma_ts(tm_s0 + 64 * h2 + 32 * sp, tm_k0 + 64 * h2 + 8 * j, db, idesc_qk, j ? 1u : 0u);
                                 }
                                 mq_commit(&kq_empty[h2]);
-                                mq_commit(&s_full[h2]);
+                                mq_commit(&s_full[2 * h2 + sp]);
                             }
                             __syncwarp();
                         } else {
                             if (ok) ok = mq_wait(&p_full[h2], (uu >> 1) & 1);
 #pragma unroll
                             for (int th = 0; th < 2; th++) {
-                                if (ok) ok = mq_wait(&vq_full[th], uu & 1);
+                                if (ok) ok = mq_wait(&vq_full[2 * h2 + th], (uu >> 1) & 1);
                                 if (!ok) break;
                                 tc_fence_after();
                                 if (elect_one()) {
 #pragma unroll
                                     for (int jj = 0; jj < 4; jj++) {
-                                        constexpr uint64_t dv0 = mq_desc(kMqVhat, 2048, 128);
+                                        const uint64_t dv0 = mq_desc(kMqVhat + h2 * 2 * kMqOperandHalf, 2048, 128);
                                         constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
                                         constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
                                         const uint64_t da = dv0 + (uint64_t)((th * kMqOperandHalf + jj * 4096) >> 4);
@@ -442,7 +449,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                                                                : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
                                         mq_mma(tm_o0 + 32 * h2, da, db, idesc_pv, (th | jj) ? 1u : (uint32_t)(t > 0));
                                     }
-                                    mq_commit(&vq_empty[th]);
+                                    mq_commit(&vq_empty[2 * h2 + th]);
                                     if (th == 1) {
                                         mq_commit(&p_empty[h2]);
                                         if (t == ntiles - 1) mq_commit(&o_done[h2]);
@@ -538,7 +545,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                         const uint32_t krow = krow0 + h2 * 80 + 16 * piece;
                         const uint4 ca = lds128(krow + 32 * swap), cb = lds128(krow + 32 * (swap ^ 1));
                         if (piece == 0)   // the K norms of the tile, times the scales, for the softmax warps
-                            sts32f(mq_hole(kHoleNorm + (uu & 3) * 8 + (tok >> 5)) + (tok & 31) * 4, lds_half(krow0 + h2 * 80 + 64) * p.k_scale);
+                            sts32f(mq_hole(kHoleNormK + (uu & 7) * 4 + (tok >> 5)) + (tok & 31) * 4, lds_half(krow0 + h2 * 80 + 64) * p.k_scale);
                         if ((uu >> 1) >= 1) ok = mq_wait(&kq_empty[h2], ((uu >> 1) - 1) & 1);   // S of the head's previous tile is done
                         if (!ok) break;
                         tc_fence_after();
@@ -583,17 +590,17 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                                 // rows are here: the softmax warps need them before this team gets to write V^.
                                 if (pc < 2) {
                                     const int tok = th * 64 + tl;
-                                    sts32f(mq_hole(kHoleNorm + ((uu + pc) & 3) * 8 + 4 + (tok >> 5)) + (tok & 31) * 4,
+                                    sts32f(mq_hole(kHoleNormV + ((uu + pc) & 3) * 4 + (tok >> 5)) + (tok & 31) * 4,
                                            lds_half(vrow0 + pc * 80 + 64) * p.v_scale);
                                 }
                                 __syncwarp();
-                                if (lane == 0) mbar_arrive(&vn_full[th]);
+                                if (lane == 0) mbar_arrive(&vn_full[2 * th + ((uu >> 1) & 1)]);
                             }
-                            if (uu >= 1) ok = mq_wait(&vq_empty[th], (uu - 1) & 1);
+                            if ((uu >> 1) >= 1) ok = mq_wait(&vq_empty[2 * h2 + th], ((uu >> 1) - 1) & 1);   // the head's PV of the tile before
                             if (!ok) break;
                             const uint4 cw = lds128(vrow + 16 * pc);
                             const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
-                            const uint32_t dst = kMqVhat + th * kMqOperandHalf + (tl >> 3) * 2048 + (4 * pc) * 128 + (tl & 7) * 16;
+                            const uint32_t dst = kMqVhat + (2 * h2 + th) * kMqOperandHalf + (tl >> 3) * 2048 + (4 * pc) * 128 + (tl & 7) * 16;
 #pragma unroll
                             for (int w = 0; w < 4; w++) {
                                 uint32_t r[4];
@@ -603,7 +610,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                             fence_proxy_async();
                             __syncwarp();
                             if (lane == 0) {
-                                mbar_arrive(&vq_full[th]);
+                                mbar_arrive(&vq_full[2 * h2 + th]);
                                 if (h2 == 1) mbar_arrive(&rawv_empty[st]);   // both heads have read this stage
                             }
                         }
@@ -639,7 +646,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             const int stid = (tid - 128) & 127;              // token of the tile = lane of tensor memory
             const int wq = warp & 3;
             const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-            const uint32_t tm_s = tm_s0 + 32 * h2, tm_o = tm_o0 + 32 * h2;
+            const uint32_t tm_o = tm_o0 + 32 * h2;
             const int bar_id = 2 + h2;
             const int hole_col = kHoleCol + 4 * h2;
             float l_acc[kMqCols];   // this token's share of the column sums
@@ -658,9 +665,11 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 // causal queries: column cc belongs to query cc / group, which sees this token iff cc >= cmin
                 const int cmin = mp.causal ? (p.nq - len_eff + tok_global) * p.real_group : 0;
                 if (abort_flag) ok = false;
-                if (ok) ok = mq_wait(&s_full[h2], (uu >> 1) & 1);
+                const int tg = uu >> 1, sp = tg & 1;
+                const uint32_t tm_s = tm_s0 + 64 * h2 + 32 * sp;
+                if (ok) ok = mq_wait(&s_full[2 * h2 + sp], (tg >> 1) & 1);
                 tc_fence_after();
-                const float kf = lds32f(mq_hole(kHoleNorm + (uu & 3) * 8 + (stid >> 5)) + (stid & 31) * 4);
+                const float kf = lds32f(mq_hole(kHoleNormK + (uu & 7) * 4 + (stid >> 5)) + (stid & 31) * 4);
                 // S is read from tensor memory sixteen columns at a time, once to look for a raised maximum and
                 // once to exponentiate (and once more in the rare tile that raises one): reading it again is
                 // cheaper than holding 32 scores beside the 32 column sums.  The running maxima stay in shared
@@ -729,8 +738,8 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 }
                 bar_sync_named(bar_id, 128);   // maxima written; the flags and the column scratch may be reused
                 // the V norms come from the V team, which may be behind: one phase per tile and half of its tokens
-                if (ok) ok = mq_wait(&vn_full[stid >> 6], (uu >> 1) & 1);
-                const float vf = lds32f(mq_hole(kHoleNorm + (uu & 3) * 8 + 4 + (stid >> 5)) + (stid & 31) * 4);
+                if (ok) ok = mq_wait(&vn_full[2 * (stid >> 6) + sp], (tg >> 1) & 1);
+                const float vf = lds32f(mq_hole(kHoleNormV + (uu & 3) * 4 + (stid >> 5)) + (stid & 31) * 4);
                 // P: [token group][column group][token in group][8 columns]; the first head's in the table's holes
                 const uint32_t pdst = h2 ? kMqP1 + (stid >> 3) * 512 + (stid & 7) * 16 : mq_hole(kHoleP + (stid >> 3) * 4) + (stid & 7) * 16;
                 const uint32_t pcg = h2 ? 128u : 256u;
@@ -759,7 +768,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0 && ok) {
-                    mbar_arrive(&s_empty[h2]);
+                    mbar_arrive(&s_empty[2 * h2 + sp]);
                     mbar_arrive(&p_full[h2]);
                 }
             }
