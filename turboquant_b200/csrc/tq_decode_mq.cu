@@ -56,7 +56,8 @@ constexpr int kMqStageBytes = 4 * kMqBoxBytes;  // 4 pages of K or of V
 constexpr int kMqOperandHalf = 16384;  // 64 contraction indices x 128 rows x 2 bytes
 constexpr uint32_t kMqWaitLimit = 1u << 18;   // tries per wait: at most about a quarter of a second
 constexpr uint32_t kMqSuspendNs = 1000;       // suspend-time hint of one try
-constexpr int kMqTmemCols = 512;       // O^T (32 columns per head), K^ (64 per head), S (2 x 32 per head); 320 used
+constexpr int kMqTmemCols = 512;       // O^T (32 columns per head), K^ (64 per head), S (2 x 32 per head), a block of
+                                       // ones (64) and the column sums (32 per head): 448 used
 
 // shared-window offsets: the K ring and half of the V ring below the table, the table (with Q^T, one P
 // and the norms in its holes), then the operand buffers, the rest of the V ring and the other P
@@ -70,9 +71,9 @@ static_assert(kMqRawV01 + 2 * kMqStageBytes == kLutAddr, "the rings below the ta
 
 __device__ __forceinline__ uint32_t mq_hole(int i) { return kLutAddr + 256u * (uint32_t)i + 128u; }
 // holes: [0, 128) Q^T of the two heads, [128, 192) P of the first head, [192, 224) K norms (8 tile-heads x 128
-// floats: K^ of a head runs up to three tiles ahead of its softmax), [224, 240) V norms (4 tile-heads), [240, 248)
+// floats: K^ of a head runs up to three tiles ahead of its softmax), [240, 248)
 // per-column scratch of the two softmax groups, [248, 250) the running maxima
-constexpr int kHoleQ = 0, kHoleP = 128, kHoleNormK = 192, kHoleNormV = 224, kHoleCol = 240, kHoleMax = 248;
+constexpr int kHoleQ = 0, kHoleP = 128, kHoleNormK = 192, kHoleCol = 240, kHoleMax = 248;
 
 struct MqParams {
     DecodeParams d;
@@ -179,6 +180,11 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&a)[4],
                  ::"r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(taddr)
                  : "memory");
 }
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // tiled tensor copy of one box [1][16 tokens][160 bytes] at (x = byte in the token row, y = token, z = K / V)
@@ -204,11 +210,11 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     const DecodeParams& p = mp.d;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t rawk_full[kMqStages], rawk_empty[kMqStages], rawv_full[kMqStages], rawv_empty[kMqStages];
-    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[4], vq_empty[4], s_full[4], s_empty[4], p_full[2], p_empty[2], o_done[2], vn_full[4];
+    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[4], vq_empty[4], s_full[4], s_empty[4], p_full[2], p_empty[2], o_done[2];
     __shared__ int seg_seq[kMaxSegments], seg_p0[kMaxSegments], seg_p1[kMaxSegments];
     __shared__ int num_segments, abort_flag;
     __shared__ uint32_t tmem_slot;
-    __shared__ int raise_flag[8];
+    __shared__ int raise_flag[16];   // [tile parity][head][warp]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = smem_u32(smem);
@@ -244,10 +250,6 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             mbar_init(&p_full[i], 4);
             mbar_init(&p_empty[i], 1);
             mbar_init(&o_done[i], 1);   // one phase per segment: the head's last PV has completed
-            // [half of the tile's tokens][parity of the tile]: the V norms are written.  Two barriers per half, since
-            // the V team of the first head may be a tile ahead of the second head's softmax.
-            mbar_init(&vn_full[2 * i], 8);
-            mbar_init(&vn_full[2 * i + 1], 8);
         }
         num_segments = 0;
         abort_flag = 0;
@@ -352,12 +354,22 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     // O^T at +32 h2, K^ at +64 h2, S at +64 h2 + 32 (tile parity)
-    const uint32_t tm_o0 = tmem, tm_k0 = tmem + 64, tm_s0 = tmem + 192;
+    const uint32_t tm_o0 = tmem, tm_k0 = tmem + 64, tm_s0 = tmem + 192, tm_ones = tmem + 320, tm_l0 = tmem + 384;
 
+    if (warp >= 4 && warp < 8) {   // 128 lanes x 64 columns of half2(1, 1)
+        uint32_t ones[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) ones[i] = 0x3C003C00u;
+#pragma unroll
+        for (int i = 0; i < 4; i++) tmem_st16(tm_ones + 16 * i + ((uint32_t)((warp & 3) * 32) << 16), ones);
+        tc_fence_before();
+    }
     // The roles part here for good: each lowers or raises its register count first, runs its own loop
     // over the block's segments, and meets the others only at barrier 1 (twice per segment: the rotated
     // queries are in place / the segment has drained).  u counts tile-heads and tile_n tiles across the
     // segments; they fix the barrier phases and advance identically in every role.
+    // Register budget per scheduler (one control, two softmax, four dequantize warps of the 512 warp-registers):
+    // 40 + 2 x 104 + 4 x 64 = 504.  An exact fit (control at 48) never got its registers: setmaxnreg.inc waits.
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
         int u = 0, tile_n = 0;
@@ -409,6 +421,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 // issues; every descriptor is a compile-time constant (the head is unrolled).
                 constexpr uint32_t idesc_qk = (1u << 4) | ((uint32_t)(kMqCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
                 constexpr uint32_t idesc_pv = idesc_qk | (1u << 15) | (1u << 16);
+                constexpr uint32_t idesc_l = idesc_qk | (1u << 16);   // A (ones) from tensor memory, B = P with the columns contiguous
                 bool ok = true;
                 for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
 #pragma unroll
@@ -448,6 +461,16 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                                         const uint64_t db = h2 ? dp1 + (uint64_t)(((th * 8 + jj * 2) * 512) >> 4)
                                                                : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
                                         mq_mma(tm_o0 + 32 * h2, da, db, idesc_pv, (th | jj) ? 1u : (uint32_t)(t > 0));
+                                    }
+                                    // column sums of P: the same B operand against a block of ones in tensor memory; every
+                                    // row of the result holds l[column] = sum over the tile's tokens of P[token][column]
+#pragma unroll
+                                    for (int jj = 0; jj < 4; jj++) {
+                                        constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
+                                        constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
+                                        const uint64_t db = h2 ? dp1 + (uint64_t)(((th * 8 + jj * 2) * 512) >> 4)
+                                                               : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
+                                        mq_mma_ts(tm_l0 + 32 * h2, tm_ones + 8 * jj, db, idesc_l, (th | jj) ? 1u : (uint32_t)(t > 0));
                                     }
                                     mq_commit(&vq_empty[2 * h2 + th]);
                                     if (th == 1) {
@@ -583,29 +606,24 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                             const int st = (2 * n + th) & 3;
                             ok = mq_wait(&rawv_full[st], (n >> 1) & 1);
                             if (!ok) break;
-                            const uint32_t vrow0 = rawv_addr(st) + (tl >> 4) * kMqBoxBytes + (tl & 15) * 160;
-                            const uint32_t vrow = vrow0 + h2 * 80;
-                            if (h2 == 0) {
-                                // The V norms of BOTH heads for this half of the tile, times the scale, as soon as the raw
-                                // rows are here: the softmax warps need them before this team gets to write V^.
-                                if (pc < 2) {
-                                    const int tok = th * 64 + tl;
-                                    sts32f(mq_hole(kHoleNormV + ((uu + pc) & 3) * 4 + (tok >> 5)) + (tok & 31) * 4,
-                                           lds_half(vrow0 + pc * 80 + 64) * p.v_scale);
-                                }
-                                __syncwarp();
-                                if (lane == 0) mbar_arrive(&vn_full[2 * th + ((uu >> 1) & 1)]);
-                            }
+                            const uint32_t vrow = rawv_addr(st) + (tl >> 4) * kMqBoxBytes + (tl & 15) * 160 + h2 * 80;
                             if ((uu >> 1) >= 1) ok = mq_wait(&vq_empty[2 * h2 + th], ((uu >> 1) - 1) & 1);   // the head's PV of the tile before
                             if (!ok) break;
                             const uint4 cw = lds128(vrow + 16 * pc);
+                            // The row's norm times the scale is folded into V^ (P then holds the bare weights, whose
+                            // column sums the tensor core forms).  A token past the sequence or past this block's pages
+                            // gets the factor zero: whatever its slot holds, its V^ row is exactly zero.
+                            const int tok_rel = (p0 + t * PPS) * kPageTokens + th * 64 + tl;
+                            const bool valid = first_page * kPageTokens + tok_rel < len_eff && tok_rel < p1 * kPageTokens;
+                            const float vf = valid ? lds_half(vrow + 64) * p.v_scale : 0.f;
+                            const uint32_t vf2 = pack_half2(vf, vf);
                             const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
                             const uint32_t dst = kMqVhat + (2 * h2 + th) * kMqOperandHalf + (tl >> 3) * 2048 + (4 * pc) * 128 + (tl & 7) * 16;
 #pragma unroll
                             for (int w = 0; w < 4; w++) {
                                 uint32_t r[4];
                                 dequant8(w4[w], lut_lane, r);
-                                sts128(dst + w * 128, r[0], r[1], r[2], r[3]);
+                                sts128(dst + w * 128, hmul2(r[0], vf2), hmul2(r[1], vf2), hmul2(r[2], vf2), hmul2(r[3], vf2));
                             }
                             fence_proxy_async();
                             __syncwarp();
@@ -646,12 +664,9 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             const int stid = (tid - 128) & 127;              // token of the tile = lane of tensor memory
             const int wq = warp & 3;
             const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-            const uint32_t tm_o = tm_o0 + 32 * h2;
+            const uint32_t tm_o = tm_o0 + 32 * h2, tm_l = tm_l0 + 32 * h2;
             const int bar_id = 2 + h2;
             const int hole_col = kHoleCol + 4 * h2;
-            float l_acc[kMqCols];   // this token's share of the column sums
-#pragma unroll
-            for (int cc = 0; cc < kMqCols; cc++) l_acc[cc] = 0.f;
             if (stid < kMqCols) sts32f(mq_hole(kHoleMax + h2) + stid * 4, -INFINITY);
             bar_sync_named(bar_id, 128);
             // The four warps of a group meet at named barriers inside this loop, so none of them may leave it
@@ -666,56 +681,54 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 const int cmin = mp.causal ? (p.nq - len_eff + tok_global) * p.real_group : 0;
                 if (abort_flag) ok = false;
                 const int tg = uu >> 1, sp = tg & 1;
-                const uint32_t tm_s = tm_s0 + 64 * h2 + 32 * sp;
                 if (ok) ok = mq_wait(&s_full[2 * h2 + sp], (tg >> 1) & 1);
                 tc_fence_after();
                 const float kf = lds32f(mq_hole(kHoleNormK + (uu & 7) * 4 + (stid >> 5)) + (stid & 31) * 4);
-                // S is read from tensor memory sixteen columns at a time, once to look for a raised maximum and
-                // once to exponentiate (and once more in the rare tile that raises one): reading it again is
-                // cheaper than holding 32 scores beside the 32 column sums.  The running maxima stay in shared
-                // memory and are read four at a time.
+                // The token's row of S: read once, kept in registers (the column sums are not kept here: the tensor
+                // core forms them, see the issue warp), and the S buffer is handed back at once.
+                uint32_t sr[32];
+                if (ok) tmem_ld32(tm_s0 + 64 * h2 + 32 * sp + lane_base, sr);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&s_empty[2 * h2 + sp]);
                 bool raise = false;
+                if (ok) {
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    if (!ok) break;   // the warp's own choice: no barrier inside
-                    uint32_t sr[16];
-                    tmem_ld16(tm_s + lane_base + 16 * half, sr);
-#pragma unroll
-                    for (int cc = 0; cc < 16; cc += 4) {
-                        const uint4 mv = lds128(mq_hole(kHoleMax + h2) + (16 * half + cc) * 4);
+                    for (int cc = 0; cc < kMqCols; cc += 4) {
+                        const uint4 mv = lds128(mq_hole(kHoleMax + h2) + cc * 4);
                         const float m4[4] = {__uint_as_float(mv.x), __uint_as_float(mv.y), __uint_as_float(mv.z), __uint_as_float(mv.w)};
 #pragma unroll
                         for (int i = 0; i < 4; i++)
-                            raise |= valid && 16 * half + cc + i >= cmin && __uint_as_float(sr[cc + i]) * kf > m4[i] + kRaiseThreshold;
+                            raise |= valid && cc + i >= cmin && __uint_as_float(sr[cc + i]) * kf > m4[i] + kRaiseThreshold;
                     }
                 }
-                // does any token of the tile exceed the running maximum of its column by 2^6?
+                // does any token of the tile exceed the running maximum of its column by 2^6?  (flags by tile parity:
+                // the common path has only this one barrier per tile)
                 const bool wraise = __any_sync(0xffffffffu, raise);
-                if (lane == 0) raise_flag[4 * h2 + wq] = wraise;
+                if (lane == 0) raise_flag[8 * sp + 4 * h2 + wq] = wraise;
                 bar_sync_named(bar_id, 128);
-                const bool any_raise = raise_flag[4 * h2] | raise_flag[4 * h2 + 1] | raise_flag[4 * h2 + 2] | raise_flag[4 * h2 + 3];
-                if (ok && (uu >> 1) >= 1) ok = mq_wait(&p_empty[h2], ((uu >> 1) - 1) & 1);   // the head's P buffer is free, its PVs are done
+                const int* rf = &raise_flag[8 * sp + 4 * h2];
+                const bool any_raise = rf[0] | rf[1] | rf[2] | rf[3];
+                if (ok && tg >= 1) ok = mq_wait(&p_empty[h2], (tg - 1) & 1);   // the head's P buffer is free, its PVs are done
                 tc_fence_after();
                 if (any_raise) {   // the same answer in the group's four warps
                     // column maxima over the 128 tokens: warp reduction, then across the four warps
 #pragma unroll
-                    for (int half = 0; half < 2; half++) {
-                        uint32_t sr[16];
-                        tmem_ld16(tm_s + lane_base + 16 * half, sr);
+                    for (int cc = 0; cc < kMqCols; cc++) {
+                        float v = ok && valid && cc >= cmin ? __uint_as_float(sr[cc]) * kf : -INFINITY;
 #pragma unroll
-                        for (int cc = 0; cc < 16; cc++) {
-                            float v = valid && 16 * half + cc >= cmin ? __uint_as_float(sr[cc]) * kf : -INFINITY;
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-                            if (lane == 16 * half + cc) sts32f(mq_hole(hole_col + wq) + lane * 4, v);
-                        }
+                        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+                        if (lane == cc) sts32f(mq_hole(hole_col + wq) + lane * 4, v);
                     }
                     bar_sync_named(bar_id, 128);
                     float mine = 0.f;
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
-                        uint32_t orow[16];
-                        if (t > 0) tmem_ld16(tm_o + lane_base + 16 * half, orow);   // earlier tiles are rescaled with the sums
+                        uint32_t orow[16], lrow[16];
+                        if (t > 0) {   // earlier tiles are rescaled: O^T (this thread's dim row) and the sums' row
+                            tmem_ld16(tm_o + lane_base + 16 * half, orow);
+                            tmem_ld16(tm_l + lane_base + 16 * half, lrow);
+                        }
 #pragma unroll
                         for (int c16 = 0; c16 < 16; c16++) {
                             const int cc = 16 * half + c16;
@@ -727,50 +740,46 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                             const float m_new = fmaxf(m_old, v);
                             const float factor = m_new > m_old ? fast_exp2(m_old - m_new) : 1.f;   // exp2(-inf) = 0 the first time
                             if (cc == stid) mine = m_new;
-                            l_acc[cc] *= factor;
-                            if (t > 0) orow[c16] = __float_as_uint(__uint_as_float(orow[c16]) * factor);
+                            if (t > 0) {
+                                orow[c16] = __float_as_uint(__uint_as_float(orow[c16]) * factor);
+                                lrow[c16] = __float_as_uint(__uint_as_float(lrow[c16]) * factor);
+                            }
                         }
-                        if (t > 0) tmem_st16(tm_o + lane_base + 16 * half, orow);
+                        if (t > 0) {
+                            tmem_st16(tm_o + lane_base + 16 * half, orow);
+                            tmem_st16(tm_l + lane_base + 16 * half, lrow);
+                        }
                     }
                     tc_fence_before();
                     bar_sync_named(bar_id, 128);   // every thread has read the old maxima
                     if (stid < kMqCols) sts32f(mq_hole(kHoleMax + h2) + stid * 4, mine);
+                    bar_sync_named(bar_id, 128);   // maxima written
                 }
-                bar_sync_named(bar_id, 128);   // maxima written; the flags and the column scratch may be reused
-                // the V norms come from the V team, which may be behind: one phase per tile and half of its tokens
-                if (ok) ok = mq_wait(&vn_full[2 * (stid >> 6) + sp], (tg >> 1) & 1);
-                const float vf = lds32f(mq_hole(kHoleNormV + (uu & 3) * 4 + (stid >> 5)) + (stid & 31) * 4);
-                // P: [token group][column group][token in group][8 columns]; the first head's in the table's holes
-                const uint32_t pdst = h2 ? kMqP1 + (stid >> 3) * 512 + (stid & 7) * 16 : mq_hole(kHoleP + (stid >> 3) * 4) + (stid & 7) * 16;
-                const uint32_t pcg = h2 ? 128u : 256u;
+                // P = exp2(x - m) as fp16 (the V norm is folded into V^): [token group][column group][token][8 columns];
+                // the first head's in the table's holes
+                if (ok) {
+                    const uint32_t pdst = h2 ? kMqP1 + (stid >> 3) * 512 + (stid & 7) * 16 : mq_hole(kHoleP + (stid >> 3) * 4) + (stid & 7) * 16;
+                    const uint32_t pcg = h2 ? 128u : 256u;
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    if (!ok) break;
-                    uint32_t sr[16], ph[8];
-                    tmem_ld16(tm_s + lane_base + 16 * half, sr);
+                    for (int cg = 0; cg < 4; cg++) {
+                        uint32_t ph[4];
+                        const uint4 ma = lds128(mq_hole(kHoleMax + h2) + cg * 32), mb = lds128(mq_hole(kHoleMax + h2) + cg * 32 + 16);
+                        const float m8[8] = {__uint_as_float(ma.x), __uint_as_float(ma.y), __uint_as_float(ma.z), __uint_as_float(ma.w),
+                                             __uint_as_float(mb.x), __uint_as_float(mb.y), __uint_as_float(mb.z), __uint_as_float(mb.w)};
 #pragma unroll
-                    for (int cc = 0; cc < 16; cc += 4) {
-                        const uint4 mv = lds128(mq_hole(kHoleMax + h2) + (16 * half + cc) * 4);
-                        const float m4[4] = {__uint_as_float(mv.x), __uint_as_float(mv.y), __uint_as_float(mv.z), __uint_as_float(mv.w)};
-#pragma unroll
-                        for (int i = 0; i < 4; i += 2) {
-                            const float e0 = valid && 16 * half + cc + i >= cmin ? fast_exp2(__uint_as_float(sr[cc + i]) * kf - m4[i]) : 0.f;
-                            const float e1 = valid && 16 * half + cc + i + 1 >= cmin ? fast_exp2(__uint_as_float(sr[cc + i + 1]) * kf - m4[i + 1]) : 0.f;
-                            l_acc[16 * half + cc + i] += e0;
-                            l_acc[16 * half + cc + i + 1] += e1;
-                            ph[(cc + i) >> 1] = valid ? pack_half2(e0 * vf, e1 * vf) : 0u;
+                        for (int i = 0; i < 8; i += 2) {
+                            const int cc = 8 * cg + i;
+                            const float e0 = valid && cc >= cmin ? fast_exp2(__uint_as_float(sr[cc]) * kf - m8[i]) : 0.f;
+                            const float e1 = valid && cc + 1 >= cmin ? fast_exp2(__uint_as_float(sr[cc + 1]) * kf - m8[i + 1]) : 0.f;
+                            ph[i >> 1] = pack_half2(e0, e1);
                         }
+                        sts128(pdst + cg * pcg, ph[0], ph[1], ph[2], ph[3]);
                     }
-                    sts128(pdst + (2 * half) * pcg, ph[0], ph[1], ph[2], ph[3]);
-                    sts128(pdst + (2 * half + 1) * pcg, ph[4], ph[5], ph[6], ph[7]);
                 }
                 fence_proxy_async();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0 && ok) {
-                    mbar_arrive(&s_empty[2 * h2 + sp]);
-                    mbar_arrive(&p_full[h2]);
-                }
+                if (lane == 0 && ok) mbar_arrive(&p_full[h2]);
             }
             // ---- segment epilogue: wait for this head's last PV, normalize, write the partials ---------
             // (a barrier of the head's own, one phase per segment: P's barrier may be a phase further on)
@@ -779,38 +788,27 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             if (!ok) {
                 abort_flag = 1;
                 if (lane == 0) atomicExch(&p.header[0], 1);
-            }
-            {
+            } else {
                 tc_fence_after();
                 const int64_t slot = (int64_t)c + b;   // one partial per (page range, sequence)
-                // column sums over the 128 tokens
-#pragma unroll
-                for (int cc = 0; cc < kMqCols; cc++) {
-                    float v = l_acc[cc];
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                    if (lane == cc) sts32f(mq_hole(hole_col + wq) + cc * 4, v);
-                }
-                bar_sync_named(bar_id, 128);
                 const int kvh = 2 * hp + h2;
                 const int dim = stid ^ 1;   // row 2i of O^T is dim 2i + 1 and vice versa
                 float* po = p.partial_o + (slot * p.num_q_heads + (int64_t)kvh * mp.ncols) * kHeadDim + dim;
                 float mine = 0.f;
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
-                    if (!ok) break;
-                    uint32_t orow[16];
+                    uint32_t orow[16], lrow[16];   // every row of the sums' accumulator holds the column sums
                     tmem_ld16(tm_o + lane_base + 16 * half, orow);
+                    tmem_ld16(tm_l + lane_base + 16 * half, lrow);
 #pragma unroll
                     for (int c16 = 0; c16 < 16; c16++) {
                         const int cc = 16 * half + c16;
-                        const float ls = lds32f(mq_hole(hole_col) + cc * 4) + lds32f(mq_hole(hole_col + 1) + cc * 4) +
-                                         lds32f(mq_hole(hole_col + 2) + cc * 4) + lds32f(mq_hole(hole_col + 3) + cc * 4);
+                        const float ls = __uint_as_float(lrow[c16]);
                         if (cc == stid) mine = ls;
                         if (cc < mp.ncols) po[(int64_t)cc * kHeadDim] = ls > 0.f ? __uint_as_float(orow[c16]) / ls : 0.f;
                     }
                 }
-                if (ok && stid < mp.ncols) {
+                if (stid < mp.ncols) {
                     const float mm = lds32f(mq_hole(kHoleMax + h2) + stid * 4);
                     p.partial_lse[slot * p.num_q_heads + (int64_t)kvh * mp.ncols + stid] = mine > 0.f ? mm + log2f(mine) : -INFINITY;
                 }
