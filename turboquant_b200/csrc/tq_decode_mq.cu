@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
     const DecodeParams& p = mp.d;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t rawk_full[kMqStages], rawk_empty[kMqStages], rawv_full[kMqStages], rawv_empty[kMqStages];
-    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[4], vq_empty[4], s_full[4], s_empty[4], p_full[2], p_empty[2], o_done[2];
+    __shared__ __align__(8) uint64_t kq_full[2], kq_empty[2], vq_full[2], vq_empty[2], s_full[4], s_empty[4], p_full[2], p_empty[2], o_done[2];
     __shared__ int seg_seq[kMaxSegments], seg_p0[kMaxSegments], seg_p1[kMaxSegments];
     __shared__ int num_segments, abort_flag;
     __shared__ uint32_t tmem_slot;
@@ -236,14 +236,14 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
             mbar_init(&rawk_full[s], 1);
             mbar_init(&rawk_empty[s], 4);   // the four K warps that read the stage's tokens
             mbar_init(&rawv_full[s], 1);
-            mbar_init(&rawv_empty[s], 8);   // every V warp reads every stage
+            mbar_init(&rawv_empty[s], 4);   // the four V warps that read the stage's tokens
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(&kq_full[i], 8);    // per head: K^ of a tile-head is in tensor memory
             mbar_init(&kq_empty[i], 1);   // per head: its S has been computed
+            mbar_init(&vq_full[i], 8);    // per head: V^ of a tile-head is in shared memory
+            mbar_init(&vq_empty[i], 1);   // per head: its PV has been computed
             for (int j = 0; j < 2; j++) {
-                mbar_init(&vq_full[2 * i + j], 8);    // [head][half of the tile's tokens]
-                mbar_init(&vq_empty[2 * i + j], 1);
                 mbar_init(&s_full[2 * i + j], 1);     // [head][parity of the tile]: S is double-buffered per head
                 mbar_init(&s_empty[2 * i + j], 4);
             }
@@ -446,40 +446,30 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                             __syncwarp();
                         } else {
                             if (ok) ok = mq_wait(&p_full[h2], (uu >> 1) & 1);
+                            if (ok) ok = mq_wait(&vq_full[h2], (uu >> 1) & 1);
+                            if (!ok) break;
+                            tc_fence_after();
+                            if (elect_one()) {
+                                constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
+                                constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
 #pragma unroll
-                            for (int th = 0; th < 2; th++) {
-                                if (ok) ok = mq_wait(&vq_full[2 * h2 + th], (uu >> 1) & 1);
-                                if (!ok) break;
-                                tc_fence_after();
-                                if (elect_one()) {
-#pragma unroll
-                                    for (int jj = 0; jj < 4; jj++) {
-                                        const uint64_t dv0 = mq_desc(kMqVhat + h2 * 2 * kMqOperandHalf, 2048, 128);
-                                        constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
-                                        constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
-                                        const uint64_t da = dv0 + (uint64_t)((th * kMqOperandHalf + jj * 4096) >> 4);
-                                        const uint64_t db = h2 ? dp1 + (uint64_t)(((th * 8 + jj * 2) * 512) >> 4)
-                                                               : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
-                                        mq_mma(tm_o0 + 32 * h2, da, db, idesc_pv, (th | jj) ? 1u : (uint32_t)(t > 0));
-                                    }
-                                    // column sums of P: the same B operand against a block of ones in tensor memory; every
-                                    // row of the result holds l[column] = sum over the tile's tokens of P[token][column]
-#pragma unroll
-                                    for (int jj = 0; jj < 4; jj++) {
-                                        constexpr uint64_t dp0 = mq_desc(kLutAddr + 128u + 256u * kHoleP, 1024, 256);
-                                        constexpr uint64_t dp1 = mq_desc(kMqP1, 512, 128);
-                                        const uint64_t db = h2 ? dp1 + (uint64_t)(((th * 8 + jj * 2) * 512) >> 4)
-                                                               : dp0 + (uint64_t)(((th * 8 + jj * 2) * 4 * 256) >> 4);
-                                        mq_mma_ts(tm_l0 + 32 * h2, tm_ones + 8 * jj, db, idesc_l, (th | jj) ? 1u : (uint32_t)(t > 0));
-                                    }
-                                    mq_commit(&vq_empty[2 * h2 + th]);
-                                    if (th == 1) {
-                                        mq_commit(&p_empty[h2]);
-                                        if (t == ntiles - 1) mq_commit(&o_done[h2]);
-                                    }
+                                for (int j = 0; j < 8; j++) {   // 16 tokens per instruction
+                                    const uint64_t da = mq_desc(kMqVhat + h2 * 2 * kMqOperandHalf, 2048, 128) + (uint64_t)((j * 4096) >> 4);
+                                    const uint64_t db = h2 ? dp1 + (uint64_t)((j * 2 * 512) >> 4) : dp0 + (uint64_t)((j * 2 * 4 * 256) >> 4);
+                                    mq_mma(tm_o0 + 32 * h2, da, db, idesc_pv, j ? 1u : (uint32_t)(t > 0));
                                 }
-                                __syncwarp();
+                                // column sums of P: the same B operand against a block of ones in tensor memory; every
+                                // row of the result holds l[column] = sum over the tile's tokens of P[token][column]
+#pragma unroll
+                                for (int j = 0; j < 8; j++) {
+                                    const uint64_t db = h2 ? dp1 + (uint64_t)((j * 2 * 512) >> 4) : dp0 + (uint64_t)((j * 2 * 4 * 256) >> 4);
+                                    mq_mma_ts(tm_l0 + 32 * h2, tm_ones + 8 * (j & 3), db, idesc_l, j ? 1u : (uint32_t)(t > 0));
+                                }
+                                mq_commit(&vq_empty[h2]);
+                                mq_commit(&p_empty[h2]);
+                                if (t == ntiles - 1) mq_commit(&o_done[h2]);
                             }
+                            __syncwarp();
                         }
                     }
                 }
@@ -595,42 +585,44 @@ __global__ void __launch_bounds__(kMqThreads, 1) decode_mq_kernel(const __grid_c
                 }
             } else {
                 // =============================== dequantize V ========================================
-                // thread = (token of the half, 16-byte piece of the row)
-                const int tl = dt & 63, pc = (dt >> 6) ^ ((tl >> 2) & 1);   // pieces swapped as in the K team
+                // thread = (token, 32 of its 64 code bytes): one step per tile-head.  The warp's 32 tokens lie in one
+                // raw stage; lanes four tokens apart read their two 16-byte pieces in opposite order (banks).
+                const int tok = dt & 127, pc2 = dt >> 7, swap = (tok >> 2) & 1;
                 for (int t = 0; t < ntiles && ok && !abort_flag; t++) {
                     const int n = tile_n + t;
+                    const int st = (2 * n + (tok >> 6)) & 3;
+                    ok = mq_wait(&rawv_full[st], (n >> 1) & 1);
+                    const uint32_t vrow0 = rawv_addr(st) + ((tok & 63) >> 4) * kMqBoxBytes + (tok & 15) * 160;
+                    // The row's norm times the scale is folded into V^ (P then holds the bare weights, whose column
+                    // sums the tensor core forms).  A token past the sequence or past this block's pages gets the
+                    // factor zero: whatever its slot holds, its V^ row is exactly zero.
+                    const int tok_rel = (p0 + t * PPS) * kPageTokens + tok;
+                    const bool valid = first_page * kPageTokens + tok_rel < len_eff && tok_rel < p1 * kPageTokens;
                     for (int h2 = 0; h2 < 2 && ok; h2++) {
                         const int uu = u + 2 * t + h2;
+                        const uint32_t vrow = vrow0 + h2 * 80 + 32 * pc2;
+                        const uint4 ca = lds128(vrow + 16 * swap), cb = lds128(vrow + 16 * (swap ^ 1));
+                        const float vf = valid ? lds_half(vrow0 + h2 * 80 + 64) * p.v_scale : 0.f;
+                        const uint32_t vf2 = pack_half2(vf, vf);
+                        if ((uu >> 1) >= 1) ok = mq_wait(&vq_empty[h2], ((uu >> 1) - 1) & 1);   // the head's PV of the tile before
+                        if (!ok) break;
+                        const uint32_t dst = kMqVhat + h2 * 2 * kMqOperandHalf + (tok >> 3) * 2048 + (8 * pc2) * 128 + (tok & 7) * 16;
 #pragma unroll
-                        for (int th = 0; th < 2; th++) {
-                            const int st = (2 * n + th) & 3;
-                            ok = mq_wait(&rawv_full[st], (n >> 1) & 1);
-                            if (!ok) break;
-                            const uint32_t vrow = rawv_addr(st) + (tl >> 4) * kMqBoxBytes + (tl & 15) * 160 + h2 * 80;
-                            if ((uu >> 1) >= 1) ok = mq_wait(&vq_empty[2 * h2 + th], ((uu >> 1) - 1) & 1);   // the head's PV of the tile before
-                            if (!ok) break;
-                            const uint4 cw = lds128(vrow + 16 * pc);
-                            // The row's norm times the scale is folded into V^ (P then holds the bare weights, whose
-                            // column sums the tensor core forms).  A token past the sequence or past this block's pages
-                            // gets the factor zero: whatever its slot holds, its V^ row is exactly zero.
-                            const int tok_rel = (p0 + t * PPS) * kPageTokens + th * 64 + tl;
-                            const bool valid = first_page * kPageTokens + tok_rel < len_eff && tok_rel < p1 * kPageTokens;
-                            const float vf = valid ? lds_half(vrow + 64) * p.v_scale : 0.f;
-                            const uint32_t vf2 = pack_half2(vf, vf);
+                        for (int q = 0; q < 2; q++) {
+                            const uint4 cw = (q == 0) == (swap == 0) ? ca : cb;
                             const uint32_t w4[4] = {cw.x, cw.y, cw.z, cw.w};
-                            const uint32_t dst = kMqVhat + (2 * h2 + th) * kMqOperandHalf + (tl >> 3) * 2048 + (4 * pc) * 128 + (tl & 7) * 16;
 #pragma unroll
                             for (int w = 0; w < 4; w++) {
                                 uint32_t r[4];
                                 dequant8(w4[w], lut_lane, r);
-                                sts128(dst + w * 128, hmul2(r[0], vf2), hmul2(r[1], vf2), hmul2(r[2], vf2), hmul2(r[3], vf2));
+                                sts128(dst + (4 * q + w) * 128, hmul2(r[0], vf2), hmul2(r[1], vf2), hmul2(r[2], vf2), hmul2(r[3], vf2));
                             }
-                            fence_proxy_async();
-                            __syncwarp();
-                            if (lane == 0) {
-                                mbar_arrive(&vq_full[2 * h2 + th]);
-                                if (h2 == 1) mbar_arrive(&rawv_empty[st]);   // both heads have read this stage
-                            }
+                        }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(&vq_full[h2]);
+                            if (h2 == 1) mbar_arrive(&rawv_empty[st]);   // both heads have read this stage
                         }
                     }
                 }
