@@ -1,12 +1,12 @@
 // Paged decode attention for WIDE query tiles (more than 8 and up to 32 query columns per KV head:
-// several decode queries that share one sequence's KV, times the GQA ratio), on the 5th-generation
-// tensor cores: tcgen05.mma with both accumulators in tensor memory.
+// several decode queries that share one sequence's KV, times the GQA ratio; causal query chunks),
+// on the 5th-generation tensor cores: tcgen05.mma with the accumulators and one operand in tensor
+// memory.
 //
 // The mma.sync kernel (tq_decode.cu) holds eight query columns in registers; 32 columns would need
 // 128 accumulator registers per thread, so a query tile of 8 queries x GQA 4 made four passes over
-// the KV there.  Here one pass serves all 32 columns: the dequantized K and V tiles go to shared
-// memory once and the tensor core contracts them against all columns, with S = K^ Q^T (128 tokens
-// x 32 columns) and O^T = V^^T P (128 dims x 32 columns) living in tensor memory.
+// the KV there.  Here one pass serves all 32 columns: S = K^ Q^T (128 tokens x 32 columns),
+// O^T = V^^T P (128 dims x 32 columns) and the column sums of P all live in tensor memory.
 //
 // The reference has no counterpart: its decode op takes one query per batch row
 // (csrc/src/decode_v5_tc_binding.cu:783-785) and re-reads the KV for each.  The per-tile arithmetic
@@ -18,23 +18,25 @@
 // other kernel, over gridDim.x / (heads / 2) ranges).  896 threads in seven warpgroups:
 //   warps 0-3    control: warp 0 streams the raw K pages and warp 2 the raw V pages (tiled tensor
 //                copies: boxes of 16 tokens x 160 bytes = both heads' slots, each into its own ring of
-//                four 64-token stages), warp 1 issues the S = K^ Q^T instructions and warp 3 the
-//                O^T += V^^T P instructions;
+//                four 64-token stages); warp 1 issues S = K^ Q^T, warp 3 issues O^T += V^^T P and the
+//                column sums (one elected lane, compile-time descriptors, tcgen05.commit on mbarriers);
 //   warps 4-7    softmax of the pair's first head, warps 8-11 of its second head: thread t owns
-//                token t of the 128-token tile: reads its row of S from tensor memory, applies the
-//                K norm and the scale, keeps a lazily raised running maximum per column, writes P
-//                (fp16, times the V norm) to shared memory;
-//   warps 12-19  dequantize K, warps 20-27 dequantize V: 16 code bytes per thread and step through
-//                the lookup table (one lookup per code byte, as in the other kernel) into the K^ / V^
-//                operand buffers, laid out as the un-swizzled canonical core-matrix layouts the
-//                instruction descriptors name.  The two teams run independently of each other: K^ of
-//                a tile-head is typically written while V^ of the one before is.
-// K^ goes to TENSOR MEMORY (the A operand of S = K^ Q^T may live there: lane = token, two fp16 per
-// column; 64 columns per head), V^ to shared memory in halves of 64 tokens, one 32 KB buffer per head.
-// S is double-buffered per head, so K^, S and V^ of a head run ahead of its softmax.
+//                token t of the 128-token tile: reads its row of S from tensor memory once, hands
+//                the buffer back, applies the K norm and the scale, keeps a lazily raised running
+//                maximum per column, writes P = exp2(x - m) as fp16 to shared memory;
+//   warps 12-19  dequantize K, warps 20-27 dequantize V: 32 code bytes per thread and tile-head
+//                through the lookup table (one lookup per code byte, as in the other kernel).
+// K^ goes to TENSOR MEMORY with tcgen05.st: the A operand of S = K^ Q^T may live there (lane =
+// token, two fp16 per column; 64 columns per head), which keeps it out of the shared-memory pipe.
+// V^ (times the token's V norm, zero for tokens past the sequence) goes to shared memory in the
+// un-swizzled MN-major core-matrix layout, 32 KB per head.  The column sums l = sum_t P[t][c] come
+// from the tensor core as well: P against a block of ones in tensor memory, so every row of that
+// accumulator holds the sums and the softmax threads keep no running sums in registers.
+// S is double-buffered per head; K^, S and V^ of a head run ahead of its softmax.
 // Q^T (per head: 32 columns x 128 dims, fp16), P of the first head (128 tokens x 32 columns) and
-// the norms live in the unused upper halves of the lookup table's 256-byte rows: a core matrix is
+// the K norms live in the unused upper halves of the lookup table's 256-byte rows: a core matrix is
 // exactly 128 bytes.  P of the second head has a buffer of its own.
+// Tensor memory (512 columns allocated, 448 used): O^T 2 x 32, K^ 2 x 64, S 4 x 32, ones 64, sums 2 x 32.
 //
 // Every wait is bounded; a wait that runs out raises the sticky status word, the block stops
 // taking work, frees its tensor memory and returns.
