@@ -393,6 +393,33 @@ def test_wide_tile_csr_table_and_kv_windows(oracle, golden):
     np.testing.assert_allclose(lse.cpu().numpy()[ok], want_lse[ok], atol=2e-3)
 
 
+def test_wide_tile_many_short_sequences(oracle, golden):
+    """120 short sequences (empty ones among them) with 8 shared-KV queries each: many segments per
+    thread block in the wide-tile kernel, plain and causal."""
+    rng = np.random.default_rng(11)
+    lens = [int(x) for x in rng.integers(0, 150, size=120)]
+    B, nq, hq = len(lens), 8, 32
+    case = synthetic.decode_case(seed=34, seq_lens=lens, dtype=torch.float16)
+    cache = oracle_cache(oracle, case, golden["signs_seed42_d128"])
+    q = torch.randn(B, nq, hq, 128, generator=torch.Generator().manual_seed(12)).to(torch.float16)
+    rep_bt = case.block_table.repeat_interleave(nq, dim=0)
+    cache_d, bt, sl = torch.from_numpy(cache).to(DEV), case.block_table.to(DEV), case.seq_lens.to(DEV)
+    for causal in (False, True):
+        off = torch.arange(nq - 1, -1, -1, dtype=torch.int32).repeat(B) if causal else torch.zeros(B * nq, dtype=torch.int32)
+        rep_len = (case.seq_lens.repeat_interleave(nq) - off).clamp(min=0)
+        want = oracle.decode_paged(q.view(B * nq, hq, 128).float().numpy(), cache, rep_bt.numpy(), rep_len.numpy(),
+                                   golden["signs_seed42_d128"], SCALE)
+        for ctas in (0, 8):
+            ws = torch.zeros(_cabi.decode_workspace_bytes(B, nq * hq, 8, 128, ctas), dtype=torch.uint8, device=DEV)
+            out = torch.full((B, nq, hq, 128), float("nan"), dtype=torch.float16, device=DEV)
+            fn = _cabi.decode_paged_causal if causal else _cabi.decode_paged_multi
+            fn(q.to(DEV), cache_d, bt, sl, signs_dev(), SCALE, ws, out, num_ctas=ctas)
+            torch.cuda.synchronize()
+            assert ws[:4].view(torch.int32).item() == 0
+            assert_attention_close(out.float().cpu().numpy().reshape(B * nq, hq, 128), want,
+                                   f"120 short sequences x 8 queries, causal={causal}, ctas={ctas}")
+
+
 def test_shared_kv_rejects_more_than_32_columns():
     assert _cabi.decode_max_queries_per_seq(32, 8) == 8
     q = torch.zeros(1, 9, 32, 128, dtype=torch.float16, device=DEV)
