@@ -17,7 +17,8 @@ pytestmark = pytest.mark.gpu
 SCALE = 1.0 / math.sqrt(128)
 
 
-def test_write_drops_slots_beyond_the_cache(oracle, golden):
+def test_write_drops_slots_beyond_the_cache(oracle, golden, monkeypatch):
+    monkeypatch.delenv("TQ_DEBUG_CHECKS", raising=False)   # the device-side handling is what is tested
     k, v, slots, nb = synthetic.write_case(seed=12, num_tokens=300, num_skipped=5)
     bad = slots.clone()
     bad[7] = nb * 16                 # first slot past the end
@@ -50,7 +51,8 @@ def _decode(q, cache, bt, sl, **kw):
     return out.cpu().numpy(), int(ws[:4].view(torch.int32).item())
 
 
-def test_decode_reports_page_ids_outside_the_cache(oracle, golden):
+def test_decode_reports_page_ids_outside_the_cache(oracle, golden, monkeypatch):
+    monkeypatch.delenv("TQ_DEBUG_CHECKS", raising=False)   # the device-side handling is what is tested
     case = synthetic.decode_case(seed=14, seq_lens=[200, 900, 48], dtype=torch.float16)
     cache_np = oracle_cache(oracle, case, golden["signs_seed42_d128"])
     cache = torch.from_numpy(cache_np).to(DEV)
@@ -70,7 +72,8 @@ def test_decode_reports_page_ids_outside_the_cache(oracle, golden):
         assert_attention_close(out[[0, 2]], want[[0, 2]], f"rows beside the bad page id {bad_id}")
 
 
-def test_decode_reports_a_sequence_longer_than_its_page_table(oracle, golden):
+def test_decode_reports_a_sequence_longer_than_its_page_table(oracle, golden, monkeypatch):
+    monkeypatch.delenv("TQ_DEBUG_CHECKS", raising=False)   # the device-side handling is what is tested
     case = synthetic.decode_case(seed=15, seq_lens=[100, 64], dtype=torch.float16)
     cache = torch.from_numpy(oracle_cache(oracle, case, golden["signs_seed42_d128"])).to(DEV)
     sl = torch.tensor([100, 64 + 16 * case.block_table.shape[1]], dtype=torch.int32, device=DEV)

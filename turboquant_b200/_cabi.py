@@ -79,8 +79,11 @@ def _cuda(t: torch.Tensor, name: str) -> None:
 def debug_checks() -> bool:
     """TQ_DEBUG_CHECKS=1 makes every call validate its index tensors on the host first (minimum /
     maximum of slots, page ids and lengths against the cache geometry).  Each check synchronises,
-    so this is for bringing up an integration, not for serving."""
-    return os.environ.get("TQ_DEBUG_CHECKS", "0") not in ("", "0")
+    so this is for bringing up an integration, not for serving; inside a stream capture, where a
+    synchronisation is illegal, the checks are skipped."""
+    if os.environ.get("TQ_DEBUG_CHECKS", "0") in ("", "0"):
+        return False
+    return not (torch.cuda.is_available() and torch.cuda.is_current_stream_capturing())
 
 
 def _check_slots(slot_mapping: torch.Tensor, num_blocks: int, block_size: int) -> None:
