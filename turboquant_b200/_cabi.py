@@ -241,8 +241,10 @@ def _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, si
 
 
 def decode_max_queries_per_seq(num_q_heads: int, num_kv_heads: int) -> int:
-    """How many decode queries that share one sequence's KV fit one pass of ``decode_paged_multi``."""
-    cols = int(lib().tq_decode_max_query_columns())
+    """How many decode queries that share one sequence's KV fit one pass of ``decode_paged_multi``:
+    the wide-tile kernel (up to ``tq_decode_max_query_columns()`` columns) takes 2, 4, 8 or 16 KV heads,
+    any other count keeps the 8 columns of the mma.sync kernel."""
+    cols = int(lib().tq_decode_max_query_columns()) if num_kv_heads in (2, 4, 8, 16) else 8
     return max(1, cols // max(1, num_q_heads // num_kv_heads))
 
 
