@@ -55,7 +55,7 @@ constexpr int kMqTile = 128;           // tokens per tile
 constexpr int kMqStages = 4;           // per ring (K, V)
 constexpr int kMqBoxBytes = 16 * 160;  // one page half of a head pair
 constexpr int kMqStageBytes = 4 * kMqBoxBytes;  // 4 pages of K or of V
-constexpr int kMqOperandHalf = 16384;  // 64 contraction indices x 128 rows x 2 bytes
+constexpr int kMqOperandHalf = 16384;  // half of one head's V^: 64 tokens x 128 dims x 2 bytes
 constexpr uint32_t kMqWaitLimit = 1u << 18;   // tries per wait: at most about a quarter of a second
 constexpr uint32_t kMqSuspendNs = 1000;       // suspend-time hint of one try
 constexpr int kMqTmemCols = 512;       // O^T (32 columns per head), K^ (64 per head), S (2 x 32 per head), a block of
@@ -65,7 +65,7 @@ constexpr int kMqTmemCols = 512;       // O^T (32 columns per head), K^ (64 per 
 // and the norms in its holes), then the operand buffers, the rest of the V ring and the other P
 constexpr uint32_t kMqRawK = 4096;                              // 4 x 10240
 constexpr uint32_t kMqRawV01 = kMqRawK + 4 * kMqStageBytes;     // 2 x 10240, ends at 65536
-constexpr uint32_t kMqVhat = kLutAddr + kLutSpan;               // per head 2 x 16 KB: 64 KB
+constexpr uint32_t kMqVhat = kLutAddr + kLutSpan;               // 32 KB per head: 64 KB
 constexpr uint32_t kMqRawV23 = kMqVhat + 4 * kMqOperandHalf;    // 2 x 10240
 constexpr uint32_t kMqP1 = kMqRawV23 + 2 * kMqStageBytes;       // 8 KB: [16 token groups][4 column groups][8][16 B]
 constexpr uint32_t kMqSmemEnd = kMqP1 + 8192;                   // 225280
