@@ -152,20 +152,32 @@ struct GenDecodeParams {
     float centroids[16];   // already divided by sqrt(padded)
 };
 
+// 2^x, hardware approximation (2 ulp), exp2(-inf) = 0
+__device__ __forceinline__ float gen_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float gen_load(const void* q, int dtype, int64_t i) {
     if (dtype == TQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[i]);
     if (dtype == TQ_F16) return __half2float(reinterpret_cast<const __half*>(q)[i]);
     return reinterpret_cast<const float*>(q)[i];
 }
 
-__global__ void __launch_bounds__(kGenWarps * 32) decode_generic_kernel(const __grid_constant__ GenDecodeParams p) {
+// BPL = code bytes per lane and token: 1, 2 or 4 for padded head sizes 64, 128, 256.  (This file is compiled without
+// FMA contraction for the quantizer's sake; the attention arithmetic asks for its FMAs explicitly.)
+template <int BPL>
+__global__ void __launch_bounds__(kGenWarps * 32, 4) decode_generic_kernel(const __grid_constant__ GenDecodeParams p) {
     extern __shared__ float gsm[];
     const int pd = p.g.padded, G = p.group;
     float* q_s = gsm;                               // [G][pd] rotated queries
     float* o_s = gsm + kGenMaxGroup * kGenMaxDim;   // [warps][G][pd]
     __shared__ float m_s[kGenWarps][kGenMaxGroup], l_s[kGenWarps][kGenMaxGroup];
+    __shared__ float cent_s[16];   // a lookup indexed per lane: shared memory, not the parameter bank
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    if (tid < 16) cent_s[tid] = p.centroids[tid];
 
     // window of this split, in pages
     int64_t len = p.seq_lens[b];
@@ -206,41 +218,59 @@ __global__ void __launch_bounds__(kGenWarps * 32) decode_generic_kernel(const __
     for (int i = tid; i < G * pd; i += blockDim.x) q_s[i] *= p.scale;
     __syncthreads();
 
-    const int bpl = p.g.qbytes / 32;  // code bytes per lane: 1, 2 or 4 (bytes lane, lane + 32, ...)
-    float m[kGenMaxGroup], l[kGenMaxGroup], o[kGenMaxGroup][8];
+    constexpr int bpl = BPL;  // code bytes per lane (bytes lane, lane + 32, ...)
+    float m[kGenMaxGroup], l[kGenMaxGroup], o[kGenMaxGroup][2 * BPL];
 #pragma unroll
     for (int g = 0; g < kGenMaxGroup; g++) {
         m[g] = -INFINITY;
         l[g] = 0.0f;
 #pragma unroll
-        for (int e = 0; e < 8; e++) o[g][e] = 0.0f;
+        for (int e = 0; e < 2 * BPL; e++) o[g][e] = 0.0f;
     }
     bool bad_page = false;
+    int64_t page_next = pg0 < pg1 ? (int64_t)p.page_indices[tbl + pg0] : 0;
     for (int pg = pg0; pg < pg1; pg++) {
-        const int64_t page = p.page_indices[tbl + pg];
+        const int64_t page = page_next;
+        if (pg + 1 < pg1) page_next = p.page_indices[tbl + pg + 1];
         if ((uint64_t)page >= (uint64_t)p.num_blocks) {  // never form an address from it
             bad_page = true;
             continue;
         }
-        for (int e = warp; e < kGenPage; e += kGenWarps) {
-            const int64_t t = (int64_t)pg * kGenPage + e;
-            if (t < begin || t >= len) continue;
-            const uint8_t* ks = p.kv_cache + ((size_t)(page * kGenPage + e) * p.num_kv_heads + h) * p.g.slot_bytes;
-            const uint8_t* vs = ks + p.slab_bytes;
-            const float kn = __half2float(*reinterpret_cast<const __half*>(ks + p.g.qbytes));
-            const float vn = __half2float(*reinterpret_cast<const __half*>(vs + p.g.qbytes));
-            float kd[8], vd[8];
+        // A warp takes tokens warp, warp + 4, warp + 8, warp + 12 of the page: all their loads are issued
+        // before the arithmetic of the first one, so four tokens' latencies overlap.
+        uint8_t kb[4][BPL], vb[4][BPL];
+        float kn[4], vn[4];
+        bool tv[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                if (j < bpl) {
-                    const uint8_t kb = ks[lane + 32 * j], vb = vs[lane + 32 * j];
-                    kd[2 * j] = p.centroids[kb >> 4] * kn;
-                    kd[2 * j + 1] = p.centroids[kb & 15] * kn;
-                    vd[2 * j] = p.centroids[vb >> 4] * vn;
-                    vd[2 * j + 1] = p.centroids[vb & 15] * vn;
-                } else {
-                    kd[2 * j] = kd[2 * j + 1] = vd[2 * j] = vd[2 * j + 1] = 0.0f;
+        for (int i = 0; i < 4; i++) {
+            const int e = warp + kGenWarps * i;
+            const int64_t t = (int64_t)pg * kGenPage + e;
+            tv[i] = t >= begin && t < len;
+            kn[i] = vn[i] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < BPL; j++) kb[i][j] = vb[i][j] = 0;
+            if (tv[i]) {
+                const uint8_t* ks = p.kv_cache + ((size_t)(page * kGenPage + e) * p.num_kv_heads + h) * p.g.slot_bytes;
+                const uint8_t* vs = ks + p.slab_bytes;
+#pragma unroll
+                for (int j = 0; j < BPL; j++) {
+                    kb[i][j] = ks[lane + 32 * j];
+                    vb[i][j] = vs[lane + 32 * j];
                 }
+                kn[i] = __half2float(*reinterpret_cast<const __half*>(ks + p.g.qbytes));
+                vn[i] = __half2float(*reinterpret_cast<const __half*>(vs + p.g.qbytes));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (!tv[i]) continue;
+            float kd[2 * BPL], vd[2 * BPL];
+#pragma unroll
+            for (int j = 0; j < BPL; j++) {
+                kd[2 * j] = cent_s[kb[i][j] >> 4] * kn[i];
+                kd[2 * j + 1] = cent_s[kb[i][j] & 15] * kn[i];
+                vd[2 * j] = cent_s[vb[i][j] >> 4] * vn[i];
+                vd[2 * j + 1] = cent_s[vb[i][j] & 15] * vn[i];
             }
 #pragma unroll
             for (int g = 0; g < kGenMaxGroup; g++) {
@@ -248,20 +278,19 @@ __global__ void __launch_bounds__(kGenWarps * 32) decode_generic_kernel(const __
                 const float* qr = q_s + g * pd;
                 float sc = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    if (j < bpl) {
-                        const int d = 2 * (lane + 32 * j);
-                        sc += qr[d] * kd[2 * j] + qr[d + 1] * kd[2 * j + 1];
-                    }
+                for (int j = 0; j < BPL; j++) {
+                    const float2 q2 = *reinterpret_cast<const float2*>(qr + 2 * (lane + 32 * j));
+                    sc = __fmaf_rn(q2.x, kd[2 * j], __fmaf_rn(q2.y, kd[2 * j + 1], sc));
+                }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, off);
                 sc *= p.score_scale;
                 const float m_new = fmaxf(m[g], sc);
-                const float corr = exp2f(m[g] - m_new), w = exp2f(sc - m_new);
+                const float corr = gen_exp2(m[g] - m_new), w = gen_exp2(sc - m_new);
                 m[g] = m_new;
-                l[g] = l[g] * corr + w;
+                l[g] = __fmaf_rn(l[g], corr, w);
 #pragma unroll
-                for (int e2 = 0; e2 < 8; e2++) o[g][e2] = o[g][e2] * corr + w * vd[e2];
+                for (int e2 = 0; e2 < 2 * BPL; e2++) o[g][e2] = __fmaf_rn(w, vd[e2], o[g][e2] * corr);
             }
         }
     }
@@ -275,12 +304,11 @@ __global__ void __launch_bounds__(kGenWarps * 32) decode_generic_kernel(const __
             l_s[warp][g] = l[g];
         }
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-            if (j < bpl) {
-                const int d = 2 * (lane + 32 * j);
-                o_s[(warp * G + g) * pd + d] = o[g][2 * j];
-                o_s[(warp * G + g) * pd + d + 1] = o[g][2 * j + 1];
-            }
+        for (int j = 0; j < BPL; j++) {
+            const int d = 2 * (lane + 32 * j);
+            o_s[(warp * G + g) * pd + d] = o[g][2 * j];
+            o_s[(warp * G + g) * pd + d + 1] = o[g][2 * j + 1];
+        }
     }
     __syncthreads();
     for (int i = tid; i < G * pd; i += blockDim.x) {
@@ -536,10 +564,17 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_generic_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_generic_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_generic_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    decode_generic_kernel<<<dim3((unsigned)p.splits, (unsigned)batch, (unsigned)num_kv_heads), kGenWarps * 32, smem, s>>>(p);
+    const dim3 grid((unsigned)p.splits, (unsigned)batch, (unsigned)num_kv_heads);
+    switch (p.g.qbytes / 32) {
+        case 1: decode_generic_kernel<1><<<grid, kGenWarps * 32, smem, s>>>(p); break;
+        case 2: decode_generic_kernel<2><<<grid, kGenWarps * 32, smem, s>>>(p); break;
+        default: decode_generic_kernel<4><<<grid, kGenWarps * 32, smem, s>>>(p); break;
+    }
     TQ_CUDA(cudaGetLastError());
     GenMergeParams m{};
     m.partial_o = p.partial_o;
