@@ -173,16 +173,27 @@ __device__ __forceinline__ float nc_load(const void* q, int dtype, int64_t i) {
     if (dtype == TQ_F16) return __half2float(reinterpret_cast<const __half*>(q)[i]);
     return reinterpret_cast<const float*>(q)[i];
 }
+// 2^x, hardware approximation (2 ulp), exp2(-inf) = 0
+__device__ __forceinline__ float nc_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float nc_half_at(const uint8_t* p) { return __half2float(*reinterpret_cast<const __half*>(p)); }
 
-__global__ void __launch_bounds__(kNcWarps * 32) decode_nc_kernel(const __grid_constant__ NcDecodeParams p) {
+// BPL = code bytes per lane and token: 1, 2 or 4 for head sizes 64, 128, 256.  (This file is compiled without FMA
+// contraction for the quantizer's sake; the attention arithmetic asks for its FMAs explicitly.)
+template <int BPL>
+__global__ void __launch_bounds__(kNcWarps * 32, 4) decode_nc_kernel(const __grid_constant__ NcDecodeParams p) {
     extern __shared__ float ncsm[];
     const int d = p.g.d, G = p.group;
     float* q_s = ncsm;                             // [G][d] rotated queries
     float* o_s = ncsm + kNcMaxGroup * kNcMaxDim;   // [warps][G][d]
     __shared__ float m_s[kNcWarps][kNcMaxGroup], l_s[kNcWarps][kNcMaxGroup];
+    __shared__ float cent_s[16];   // a lookup indexed per lane: shared memory, not the parameter bank
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    if (tid < 16) cent_s[tid] = p.centroids[tid];
 
     const int64_t len = p.seq_lens[b];
     int npages = (int)((len + kNcPage - 1) / kNcPage);
@@ -216,41 +227,59 @@ __global__ void __launch_bounds__(kNcWarps * 32) decode_nc_kernel(const __grid_c
     for (int i = tid; i < G * d; i += blockDim.x) q_s[i] *= p.scale;
     __syncthreads();
 
-    const int bpl = p.g.qbytes / 32;  // code bytes per lane: 1, 2 or 4 (bytes lane, lane + 32, ...)
-    float m[kNcMaxGroup], l[kNcMaxGroup], o[kNcMaxGroup][8];
+    float m[kNcMaxGroup], l[kNcMaxGroup], o[kNcMaxGroup][2 * BPL];
 #pragma unroll
     for (int g = 0; g < kNcMaxGroup; g++) {
         m[g] = -INFINITY;
         l[g] = 0.0f;
 #pragma unroll
-        for (int e = 0; e < 8; e++) o[g][e] = 0.0f;
+        for (int e = 0; e < 2 * BPL; e++) o[g][e] = 0.0f;
     }
     bool bad_page = false;
+    int64_t page_next = pg0 < pg1 ? (int64_t)p.page_indices[tbl + pg0] : 0;
     for (int pg = pg0; pg < pg1; pg++) {
-        const int64_t page = p.page_indices[tbl + pg];
+        const int64_t page = page_next;
+        if (pg + 1 < pg1) page_next = p.page_indices[tbl + pg + 1];
         if ((uint64_t)page >= (uint64_t)p.num_blocks) {  // never form an address from it
             bad_page = true;
             continue;
         }
-        for (int e = warp; e < kNcPage; e += kNcWarps) {
-            const int64_t t = (int64_t)pg * kNcPage + e;
-            if (t >= len) continue;
-            const uint8_t* ks = p.kv_cache + ((size_t)(page * kNcPage + e) * p.num_kv_heads + h) * p.g.slot_bytes;
-            const uint8_t* vs = ks + p.g.kps;
-            const float kn = nc_half_at(ks + p.g.qbytes);
-            const float vsc = nc_half_at(vs + p.g.qbytes), vz = nc_half_at(vs + p.g.qbytes + 2);
-            float kd[8], vd[8];
+        // A warp takes tokens warp, warp + 4, warp + 8, warp + 12 of the page: all their loads are issued
+        // before the arithmetic of the first one, so four tokens' latencies overlap.
+        uint8_t kb[4][BPL], vb[4][BPL];
+        float kn[4], vsc[4], vz[4];
+        bool tv[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                if (j < bpl) {   // the even dim sits in the low nibble
-                    const uint8_t kb = ks[lane + 32 * j], vb = vs[lane + 32 * j];
-                    kd[2 * j] = p.centroids[kb & 15] * kn;
-                    kd[2 * j + 1] = p.centroids[kb >> 4] * kn;
-                    vd[2 * j] = (float)(vb & 15) * vsc + vz;
-                    vd[2 * j + 1] = (float)(vb >> 4) * vsc + vz;
-                } else {
-                    kd[2 * j] = kd[2 * j + 1] = vd[2 * j] = vd[2 * j + 1] = 0.0f;
+        for (int i = 0; i < 4; i++) {
+            const int e = warp + kNcWarps * i;
+            const int64_t t = (int64_t)pg * kNcPage + e;
+            tv[i] = t < len;
+            kn[i] = vsc[i] = vz[i] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < BPL; j++) kb[i][j] = vb[i][j] = 0;
+            if (tv[i]) {
+                const uint8_t* ks = p.kv_cache + ((size_t)(page * kNcPage + e) * p.num_kv_heads + h) * p.g.slot_bytes;
+                const uint8_t* vs = ks + p.g.kps;
+#pragma unroll
+                for (int j = 0; j < BPL; j++) {
+                    kb[i][j] = ks[lane + 32 * j];
+                    vb[i][j] = vs[lane + 32 * j];
                 }
+                kn[i] = nc_half_at(ks + p.g.qbytes);
+                vsc[i] = nc_half_at(vs + p.g.qbytes);
+                vz[i] = nc_half_at(vs + p.g.qbytes + 2);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (!tv[i]) continue;
+            float kd[2 * BPL], vd[2 * BPL];
+#pragma unroll
+            for (int j = 0; j < BPL; j++) {   // the even dim sits in the low nibble
+                kd[2 * j] = cent_s[kb[i][j] & 15] * kn[i];
+                kd[2 * j + 1] = cent_s[kb[i][j] >> 4] * kn[i];
+                vd[2 * j] = __fmaf_rn((float)(vb[i][j] & 15), vsc[i], vz[i]);
+                vd[2 * j + 1] = __fmaf_rn((float)(vb[i][j] >> 4), vsc[i], vz[i]);
             }
 #pragma unroll
             for (int g = 0; g < kNcMaxGroup; g++) {
@@ -258,20 +287,19 @@ __global__ void __launch_bounds__(kNcWarps * 32) decode_nc_kernel(const __grid_c
                 const float* qr = q_s + g * d;
                 float sc = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    if (j < bpl) {
-                        const int e2 = 2 * (lane + 32 * j);
-                        sc += qr[e2] * kd[2 * j] + qr[e2 + 1] * kd[2 * j + 1];
-                    }
+                for (int j = 0; j < BPL; j++) {
+                    const float2 q2 = *reinterpret_cast<const float2*>(qr + 2 * (lane + 32 * j));
+                    sc = __fmaf_rn(q2.x, kd[2 * j], __fmaf_rn(q2.y, kd[2 * j + 1], sc));
+                }
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, off);
                 sc *= p.score_scale;
                 const float m_new = fmaxf(m[g], sc);
-                const float corr = exp2f(m[g] - m_new), w = exp2f(sc - m_new);
+                const float corr = nc_exp2(m[g] - m_new), w = nc_exp2(sc - m_new);
                 m[g] = m_new;
-                l[g] = l[g] * corr + w;
+                l[g] = __fmaf_rn(l[g], corr, w);
 #pragma unroll
-                for (int e2 = 0; e2 < 8; e2++) o[g][e2] = o[g][e2] * corr + w * vd[e2];
+                for (int e2 = 0; e2 < 2 * BPL; e2++) o[g][e2] = __fmaf_rn(w, vd[e2], o[g][e2] * corr);
             }
         }
     }
@@ -284,12 +312,11 @@ __global__ void __launch_bounds__(kNcWarps * 32) decode_nc_kernel(const __grid_c
             l_s[warp][g] = l[g];
         }
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-            if (j < bpl) {
-                const int e2 = 2 * (lane + 32 * j);
-                o_s[(warp * G + g) * d + e2] = o[g][2 * j];
-                o_s[(warp * G + g) * d + e2 + 1] = o[g][2 * j + 1];
-            }
+        for (int j = 0; j < BPL; j++) {
+            const int e2 = 2 * (lane + 32 * j);
+            o_s[(warp * G + g) * d + e2] = o[g][2 * j];
+            o_s[(warp * G + g) * d + e2 + 1] = o[g][2 * j + 1];
+        }
     }
     __syncthreads();
     for (int i = tid; i < G * d; i += blockDim.x) {
@@ -464,10 +491,17 @@ extern "C" int tq_nc_decode_paged(const void* q, int q_dtype, int batch, int num
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_nc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_nc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_nc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_nc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    decode_nc_kernel<<<dim3((unsigned)p.splits, (unsigned)batch, (unsigned)num_kv_heads), kNcWarps * 32, smem, s>>>(p);
+    const dim3 grid((unsigned)p.splits, (unsigned)batch, (unsigned)num_kv_heads);
+    switch (head_dim / 64) {
+        case 1: decode_nc_kernel<1><<<grid, kNcWarps * 32, smem, s>>>(p); break;
+        case 2: decode_nc_kernel<2><<<grid, kNcWarps * 32, smem, s>>>(p); break;
+        default: decode_nc_kernel<4><<<grid, kNcWarps * 32, smem, s>>>(p); break;
+    }
     TQ_CUDA(cudaGetLastError());
     NcMergeParams m{};
     m.partial_o = p.partial_o;
