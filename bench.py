@@ -792,6 +792,11 @@ def run_ours(args):
                 "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_ms": dec_avg,
                 "merge_avg_launch_ms": sum(mrg_ms) / len(mrg_ms),
                 "frac_whole_step": (alg_bytes * NL / (ms_step * 1e-3) / 1e9) / peak}
+    # The same launch counted on the packed cache bytes it streams (80-byte slots: 68 information bytes + pad), the
+    # figure the DRAM counters see; `frac` above counts the 136 information bytes per (token, KV head).
+    phys = alg_bytes * 160.0 / 136.0
+    roofline["packed_cache_bytes"] = {"bytes_per_launch": phys, "achieved": phys / (dec_avg * 1e-3) / 1e9,
+                                      "frac": phys / (dec_avg * 1e-3) / 1e9 / peak}
     # The tcgen05 / tensor-memory variant of the loop on the same launch, for the record: the wide-tile kernel takes
     # any number of query columns through its causal entry point (one query per sequence: the mask is a no-op).
     try:
