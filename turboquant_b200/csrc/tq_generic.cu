@@ -218,7 +218,6 @@ __global__ void __launch_bounds__(kGenWarps * 32, 4) decode_generic_kernel(const
     for (int i = tid; i < G * pd; i += blockDim.x) q_s[i] *= p.scale;
     __syncthreads();
 
-    constexpr int bpl = BPL;  // code bytes per lane (bytes lane, lane + 32, ...)
     float m[kGenMaxGroup], l[kGenMaxGroup], o[kGenMaxGroup][2 * BPL];
 #pragma unroll
     for (int g = 0; g < kGenMaxGroup; g++) {
