@@ -113,3 +113,26 @@ def test_rejected_geometries():
     q = torch.zeros(1, 32, 64, dtype=torch.float16, device=DEV)
     with pytest.raises(_cabi.TurboQuantError, match="query heads per KV head"):
         attn.decode(q, cache, torch.zeros(1, 2, dtype=torch.int32, device=DEV), torch.ones(1, dtype=torch.int32, device=DEV))
+
+
+@pytest.mark.parametrize("d,sb", [(64, 52), (256, 150)])
+def test_slots_that_are_not_16_byte_multiples_take_the_plain_kernel(oracle, golden, d, sb):
+    """The tensor-core decode kernel for these head sizes reads codes with 16-byte loads; a cache
+    whose slots are not a multiple of 16 bytes (a caller's own padding) falls back to the plain
+    kernel and must give the same answer."""
+    lens, hq, hkv = [33, 700], 8, 4
+    case = synthetic.decode_case(seed=300 + d, seq_lens=lens, dtype=torch.float16, heads=(hq, hkv), head_dim=d)
+    signs = _signs(golden, d)
+    scale = 1.0 / math.sqrt(d)
+    cache_np = np.zeros((2, case.num_blocks, 16, hkv, sb), np.uint8)
+    oracle.write_kv_cache(cache_np, case.k.float().numpy(), case.v.float().numpy(), signs.numpy(), case.slot_mapping.numpy(), d)
+    want = oracle.decode_paged(case.q.float().numpy(), cache_np, case.block_table.numpy(), case.seq_lens.numpy(), signs.numpy(), scale)
+    cache = torch.zeros((2, case.num_blocks, 16, hkv, sb), dtype=torch.uint8, device=DEV)
+    _cabi.write_kv_cache(cache, case.k.to(DEV), case.v.to(DEV), signs.to(DEV), case.slot_mapping.to(DEV), d)
+    np.testing.assert_array_equal(cache.cpu().numpy(), cache_np)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(len(lens), hq, hkv, d, 0), dtype=torch.uint8, device=DEV)
+    out = torch.empty(case.q.shape, dtype=torch.float32, device=DEV)
+    _cabi.decode_paged(case.q.to(DEV), cache, case.block_table.to(DEV), case.seq_lens.to(DEV), signs.to(DEV), scale, ws, out)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 0
+    assert_attention_close(out.cpu().numpy(), want, f"head size {d}, slots of {sb} bytes")

@@ -330,6 +330,244 @@ __global__ void __launch_bounds__(kGenWarps * 32, 4) decode_generic_kernel(const
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// decode on the tensor cores for the same head sizes: a warp takes whole pages.  Its 32 lanes load
+// the page's code bytes with 16-byte loads (lane = token, half of the row), dequantize them through
+// a byte-keyed table of fp16 centroid pairs into two small shared-memory tiles K^ and V^ ([16 tokens]
+// [PD dims], rows padded by 16 bytes), and the products run as mma.sync.m16n8k16 on ldmatrix
+// fragments: S = K^ Q^T (16 tokens x 8 query columns), O^T += V^^T P (PD dims x 8 columns, V^ read
+// with ldmatrix.trans), P moved into place with movmatrix.  Online softmax in base 2 per page; the
+// K norm is folded into the scores, the V norm into P.  Same grid, workspace and merge as the
+// plain kernel above, which stays as the fallback for caches that are not 16-byte aligned.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t gen_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gen_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void gen_ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void gen_mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t gen_movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t gen_pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int PD>
+struct TileShape {
+    static constexpr int kRowBytes = (PD + 8) * 2;             // 16 mod 128: ldmatrix rows hit different banks
+    static constexpr int kTileBytes = 16 * kRowBytes;
+    static constexpr int kWords = PD / 16;                      // code words (4 bytes) per lane and operand
+    static constexpr size_t kSmem = (size_t)kGenMaxGroup * PD * 4 + (size_t)kGenWarps * 2 * kTileBytes;
+};
+
+template <int PD>
+__global__ void __launch_bounds__(kGenWarps * 32, PD == 256 ? 2 : 4) decode_tiles_kernel(const __grid_constant__ GenDecodeParams p) {
+    using T = TileShape<PD>;
+    extern __shared__ __align__(16) uint8_t tsm[];
+    __shared__ float m_s[kGenWarps][kGenMaxGroup], l_s[kGenWarps][kGenMaxGroup];
+    __shared__ uint32_t lut_s[256];          // code byte -> (centroid of the even dim, centroid of the odd dim) as half2
+    __shared__ float nk_s[kGenWarps][16], nv_s[kGenWarps][16];
+    constexpr int pd = PD;
+    const int G = p.group;
+    float* q_s = reinterpret_cast<float*>(tsm);                          // [G][pd] rotated queries
+    uint8_t* tiles = tsm + (size_t)kGenMaxGroup * PD * 4;
+    float* o_s = reinterpret_cast<float*>(tiles);                        // [warps][G][pd], after the loop
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tg = lane & 3;
+    const int split = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
+    for (int v = tid; v < 256; v += blockDim.x) lut_s[v] = gen_pack_half2(p.centroids[v >> 4], p.centroids[v & 15]);
+
+    // window of this split, in pages
+    int64_t len = p.seq_lens[b];
+    if (p.kv_end >= 0 && p.kv_end < len) len = p.kv_end;
+    const int64_t begin = p.kv_begin > 0 ? p.kv_begin : 0;
+    const int first_page = (int)(begin / kGenPage);
+    const int last_page = (int)((len + kGenPage - 1) / kGenPage);
+    int npages = last_page > first_page ? last_page - first_page : 0;
+    const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
+    const int have = p.page_indptr ? p.page_indptr[b + 1] - p.page_indptr[b] : p.max_pages;
+    if (npages > 0 && first_page + npages > have) {  // the table cannot back this length: read nothing
+        if (tid == 0) atomicExch(&p.header[0], kGenStatusSeqTooLong);
+        npages = 0;
+    }
+    const int per = (npages + p.splits - 1) / p.splits;
+    const int pg0 = first_page + split * per;
+    const int pg1 = min(first_page + npages, pg0 + per);
+
+    // rotate the group's queries: signs, butterflies, 1/sqrt(pd)
+    for (int i = tid; i < G * pd; i += blockDim.x) {
+        const int gg = i / pd, d = i - gg * pd;
+        q_s[i] = d < p.g.head_dim
+                     ? gen_load(p.q, p.q_dtype, ((int64_t)b * p.num_q_heads + h * G + gg) * p.g.head_dim + d) * p.signs[d]
+                     : 0.0f;
+    }
+    __syncthreads();
+    for (int hh = 1; hh < pd; hh <<= 1) {
+        for (int i = tid; i < G * pd / 2; i += blockDim.x) {
+            const int gg = i / (pd / 2), idx = i - gg * (pd / 2);
+            const int j = (idx / hh) * 2 * hh + (idx % hh);
+            float* row = q_s + gg * pd;
+            const float a = row[j], c = row[j + hh];
+            row[j] = a + c;
+            row[j + hh] = a - c;
+        }
+        __syncthreads();
+    }
+    // B fragments of Q^T: column g of the query tile (zero beyond the group), k-steps of 16 dims
+    uint32_t qf[PD / 8];
+#pragma unroll
+    for (int s = 0; s < PD / 16; s++) {
+        const float* row = q_s + g * pd + 16 * s + 2 * tg;
+        const bool on = g < G;
+        qf[2 * s] = on ? gen_pack_half2(row[0] * p.scale, row[1] * p.scale) : 0u;
+        qf[2 * s + 1] = on ? gen_pack_half2(row[8] * p.scale, row[9] * p.scale) : 0u;
+    }
+
+    float o_acc[PD / 16][4];
+#pragma unroll
+    for (int i = 0; i < PD / 16; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) o_acc[i][j] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    const int tk = lane >> 1, hf = lane & 1;                       // loads: lane = (token, half of its code bytes)
+    const uint32_t tile_k = gen_smem_u32(tiles) + (uint32_t)warp * 2 * T::kTileBytes, tile_v = tile_k + T::kTileBytes;
+    const uint32_t st_k = tile_k + tk * T::kRowBytes + hf * PD, st_v = tile_v + tk * T::kRowBytes + hf * PD;
+    const uint32_t lm_k = tile_k + (lane & 15) * T::kRowBytes + (lane >> 4) * 16;
+    const uint32_t lm_v = tile_v + ((lane & 7) + 8 * (lane >> 4)) * T::kRowBytes + ((lane >> 3) & 1) * 16;
+    bool bad_page = false;
+    for (int pg = pg0 + warp; pg < pg1; pg += kGenWarps) {
+        const int64_t page = p.page_indices[tbl + pg];
+        if ((uint64_t)page >= (uint64_t)p.num_blocks) {  // never form an address from it
+            bad_page = true;
+            continue;
+        }
+        // ---- load and dequantize the page's codes into the two tiles ---------------------------------
+        const uint8_t* ks = p.kv_cache + ((size_t)(page * kGenPage + tk) * p.num_kv_heads + h) * p.g.slot_bytes;
+        const uint8_t* vs = ks + p.slab_bytes;
+        uint4 kc[PD / 64], vc[PD / 64];
+#pragma unroll
+        for (int i = 0; i < PD / 64; i++) {
+            kc[i] = reinterpret_cast<const uint4*>(ks + hf * (PD / 4))[i];
+            vc[i] = reinterpret_cast<const uint4*>(vs + hf * (PD / 4))[i];
+        }
+        if (hf == 0) {
+            nk_s[warp][tk] = __half2float(*reinterpret_cast<const __half*>(ks + p.g.qbytes));
+            nv_s[warp][tk] = __half2float(*reinterpret_cast<const __half*>(vs + p.g.qbytes));
+        }
+#pragma unroll
+        for (int i = 0; i < PD / 64; i++) {
+            const uint32_t kw[4] = {kc[i].x, kc[i].y, kc[i].z, kc[i].w}, vw[4] = {vc[i].x, vc[i].y, vc[i].z, vc[i].w};
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t a[4], c[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    a[j] = lut_s[(kw[w] >> (8 * j)) & 0xFF];
+                    c[j] = lut_s[(vw[w] >> (8 * j)) & 0xFF];
+                }
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_k + (4 * i + w) * 16), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_v + (4 * i + w) * 16), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
+            }
+        }
+        __syncwarp();
+        // ---- S = K^ Q^T ----------------------------------------------------------------------------------
+        float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int s = 0; s < PD / 16; s++) {
+            uint32_t a[4];
+            gen_ldmatrix_x4(lm_k + s * 32, a);
+            gen_mma16816(s_acc, a, qf[2 * s], qf[2 * s + 1]);
+        }
+        // ---- online softmax (base 2); rows g and g + 8 are tokens, columns 2tg and 2tg + 1 query heads -----
+        const int64_t t0 = (int64_t)pg * kGenPage;
+        const bool va = t0 + g >= begin && t0 + g < len, vb = t0 + g + 8 >= begin && t0 + g + 8 < len;
+        const float kfa = va ? nk_s[warp][g] * p.score_scale : 0.0f, kfb = vb ? nk_s[warp][g + 8] * p.score_scale : 0.0f;
+        const float vfa = va ? nv_s[warp][g] : 0.0f, vfb = vb ? nv_s[warp][g + 8] : 0.0f;
+        const float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
+        const float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
+        float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+        }
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float c0 = n0 > m0 ? gen_exp2(m0 - n0) : 1.0f, c1 = n1 > m1 ? gen_exp2(m1 - n1) : 1.0f;
+        m0 = n0;
+        m1 = n1;
+        const float e0 = va ? gen_exp2(x0 - m0) : 0.0f, e1 = va ? gen_exp2(x1 - m1) : 0.0f;
+        const float e2 = vb ? gen_exp2(x2 - m0) : 0.0f, e3 = vb ? gen_exp2(x3 - m1) : 0.0f;
+        l0 = __fmaf_rn(l0, c0, e0 + e2);
+        l1 = __fmaf_rn(l1, c1, e1 + e3);
+        const uint32_t pb0 = gen_movmatrix_trans(gen_pack_half2(e0 * vfa, e1 * vfa));
+        const uint32_t pb1 = gen_movmatrix_trans(gen_pack_half2(e2 * vfb, e3 * vfb));
+        // ---- O^T += V^^T P ------------------------------------------------------------------------------------
+#pragma unroll
+        for (int mt = 0; mt < PD / 16; mt++) {
+            uint32_t a[4];
+            gen_ldmatrix_x4_trans(lm_v + mt * 32, a);
+            o_acc[mt][0] *= c0; o_acc[mt][1] *= c1; o_acc[mt][2] *= c0; o_acc[mt][3] *= c1;
+            gen_mma16816(o_acc[mt], a, pb0, pb1);
+        }
+        __syncwarp();   // the tiles are rewritten by the next page
+    }
+    if (bad_page && lane == 0) atomicExch(&p.header[0], kGenStatusBadPage);
+    // this warp's sums over its token lanes, then everything to shared memory for the block's combine
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    }
+    __syncthreads();   // every warp has left its tiles: the region becomes o_s
+    if (g == 0) {
+        if (2 * tg < G) { m_s[warp][2 * tg] = m0; l_s[warp][2 * tg] = l0; }
+        if (2 * tg + 1 < G) { m_s[warp][2 * tg + 1] = m1; l_s[warp][2 * tg + 1] = l1; }
+    }
+#pragma unroll
+    for (int mt = 0; mt < PD / 16; mt++) {
+        const int d0 = 16 * mt + g;
+        if (2 * tg < G) {
+            o_s[(warp * G + 2 * tg) * pd + d0] = o_acc[mt][0];
+            o_s[(warp * G + 2 * tg) * pd + d0 + 8] = o_acc[mt][2];
+        }
+        if (2 * tg + 1 < G) {
+            o_s[(warp * G + 2 * tg + 1) * pd + d0] = o_acc[mt][1];
+            o_s[(warp * G + 2 * tg + 1) * pd + d0 + 8] = o_acc[mt][3];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * pd; i += blockDim.x) {
+        const int gg = i / pd, d = i - gg * pd;
+        float mm = -INFINITY;
+        for (int w = 0; w < kGenWarps; w++) mm = fmaxf(mm, m_s[w][gg]);
+        float ll = 0.0f, acc = 0.0f;
+        if (mm > -INFINITY) {
+            for (int w = 0; w < kGenWarps; w++) {
+                const float sc = gen_exp2(m_s[w][gg] - mm);
+                if (sc > 0.0f) {
+                    ll += sc * l_s[w][gg];
+                    acc += sc * o_s[(w * G + gg) * pd + d];
+                }
+            }
+        }
+        const int64_t row = ((int64_t)b * p.splits + split) * p.num_q_heads + h * G + gg;
+        p.partial_o[row * pd + d] = ll > 0.0f ? acc / ll : 0.0f;
+        if (d == 0) p.partial_lse[row] = ll > 0.0f ? mm + log2f(ll) : -INFINITY;
+    }
+}
+
 struct GenMergeParams {
     const float* partial_o;
     const float* partial_lse;
@@ -569,10 +807,27 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const dim3 grid((unsigned)p.splits, (unsigned)batch, (unsigned)num_kv_heads);
-    switch (p.g.qbytes / 32) {
-        case 1: decode_generic_kernel<1><<<grid, kGenWarps * 32, smem, s>>>(p); break;
-        case 2: decode_generic_kernel<2><<<grid, kGenWarps * 32, smem, s>>>(p); break;
-        default: decode_generic_kernel<4><<<grid, kGenWarps * 32, smem, s>>>(p); break;
+    // the tensor-core kernel reads the codes with 16-byte loads; anything else keeps the plain one
+    const bool aligned = slot_bytes % 16 == 0 && ((uintptr_t)kv_cache % 16) == 0 && p.slab_bytes % 16 == 0;
+    if (aligned) {
+        static bool tiles_configured[64] = {};
+        if (dev < 0 || dev >= 64 || !tiles_configured[dev]) {
+            TQ_CUDA(cudaFuncSetAttribute(decode_tiles_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileShape<64>::kSmem));
+            TQ_CUDA(cudaFuncSetAttribute(decode_tiles_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileShape<128>::kSmem));
+            TQ_CUDA(cudaFuncSetAttribute(decode_tiles_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileShape<256>::kSmem));
+            if (dev >= 0 && dev < 64) tiles_configured[dev] = true;
+        }
+        switch (p.g.padded) {
+            case 64: decode_tiles_kernel<64><<<grid, kGenWarps * 32, TileShape<64>::kSmem, s>>>(p); break;
+            case 128: decode_tiles_kernel<128><<<grid, kGenWarps * 32, TileShape<128>::kSmem, s>>>(p); break;
+            default: decode_tiles_kernel<256><<<grid, kGenWarps * 32, TileShape<256>::kSmem, s>>>(p); break;
+        }
+    } else {
+        switch (p.g.qbytes / 32) {
+            case 1: decode_generic_kernel<1><<<grid, kGenWarps * 32, smem, s>>>(p); break;
+            case 2: decode_generic_kernel<2><<<grid, kGenWarps * 32, smem, s>>>(p); break;
+            default: decode_generic_kernel<4><<<grid, kGenWarps * 32, smem, s>>>(p); break;
+        }
     }
     TQ_CUDA(cudaGetLastError());
     GenMergeParams m{};
