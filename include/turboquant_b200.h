@@ -346,7 +346,8 @@ int tq_debug_set_decode_events(void* ev_start, void* ev_mid, void* ev_end);
  * (scale = (max - min) / 15, code = clamp(trunc((v - min) / scale + 1/2), 0, 15), zero = min; a
  * constant row gets code 0), dequantized as code * scale + zero in the original domain.
  * head_dim 64, 128 or 256; 16-token pages for the decode; up to 8 query heads per KV head.
- * Plain kernels (a warp per row, a block per (split, sequence, KV head)), not tuned for bandwidth.
+ * The store takes a warp per row; the decode runs on the tensor cores over shared-memory tiles (a block per
+ * (split, sequence, KV head)), without the staged copy pipelines of the tuned kernels.
  * tq_nc_write_kv_cache stands in for upstream's do_kv_cache_update / _tq_fused_store_mse,
  * tq_nc_decode_paged for _tq_decode_stage1 + the stage-2 merge.  A slot id outside the cache is
  * skipped and counted (tq_nc_write_dropped); the decode's workspace starts with the sticky status

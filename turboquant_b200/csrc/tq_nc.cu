@@ -11,10 +11,11 @@
 // dequantizes to code * scale + zero in the original domain (no rotation on the V side).
 //
 // The reference repository holds no code for this format (upstream's kernels are Triton inside
-// vLLM), only the description above; these kernels follow that description with plain CUDA: one
-// warp per row for the store, one block per (split, sequence, KV head) for the decode, the split-KV
-// partial / LSE contract of the other decode kernels.  They are a second wire format behind the
-// same C ABI, not tuned for bandwidth.  Compiled with -fmad=false (quantizer arithmetic).
+// vLLM), only the description above; these kernels follow that description: one warp per row for the
+// store, a tensor-core decode on shared-memory tiles (one block per (split, sequence, KV head)), the
+// split-KV partial / LSE contract of the other decode kernels.  They are a second wire format behind
+// the same C ABI, without the staged copy pipelines of the tuned kernels.  Compiled with -fmad=false
+// (quantizer arithmetic).
 #include <cmath>
 #include <cstring>
 
@@ -148,9 +149,6 @@ __global__ void __launch_bounds__(kNcWarps * 32) write_nc_kernel(const __grid_co
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// decode: one block per (split, sequence, KV head), four warps striding over the split's tokens
-// ---------------------------------------------------------------------------------------------
 struct NcDecodeParams {
     const void* q;
     const uint8_t* kv_cache;
@@ -179,163 +177,253 @@ __device__ __forceinline__ float nc_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ float nc_half_at(const uint8_t* p) { return __half2float(*reinterpret_cast<const __half*>(p)); }
 
-// BPL = code bytes per lane and token: 1, 2 or 4 for head sizes 64, 128, 256.  (This file is compiled without FMA
-// contraction for the quantizer's sake; the attention arithmetic asks for its FMAs explicitly.)
-template <int BPL>
-__global__ void __launch_bounds__(kNcWarps * 32, 4) decode_nc_kernel(const __grid_constant__ NcDecodeParams p) {
-    extern __shared__ float ncsm[];
-    const int d = p.g.d, G = p.group;
-    float* q_s = ncsm;                             // [G][d] rotated queries
-    float* o_s = ncsm + kNcMaxGroup * kNcMaxDim;   // [warps][G][d]
+// ---------------------------------------------------------------------------------------------
+// decode: one block per (split, sequence, KV head); a warp takes whole pages.  Its 32 lanes load the
+// page's code bytes (lane = token, half of the row; 16-bit loads, the slots being only 2-byte
+// aligned), dequantize them into two small shared-memory tiles K^ and V^ ([16 tokens][PD dims] fp16,
+// rows padded by 16 bytes) -- K through a byte-keyed table of centroid pairs, V as code * scale + zero
+// in packed fp16 arithmetic -- and the products run as mma.sync.m16n8k16 on ldmatrix fragments:
+// S = K^ Q^T (16 tokens x 8 query columns), O^T += V^^T P (PD dims x 8 columns, V^ read with
+// ldmatrix.trans), P moved into place with movmatrix.  Online softmax in base 2 per page; the K norm
+// is folded into the scores.  V was never rotated, so the partials are in the original domain.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t nct_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void nct_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void nct_ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void nct_mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t nct_movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t nct_hfma2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t nct_pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int PD>
+struct NcTileShape {
+    static constexpr int kRowBytes = (PD + 8) * 2;             // 16 mod 128: ldmatrix rows hit different banks
+    static constexpr int kTileBytes = 16 * kRowBytes;
+    static constexpr int kWords = PD / 16;                      // code words (4 bytes) per lane and operand
+    static constexpr size_t kSmem = (size_t)kNcMaxGroup * PD * 4 + (size_t)kNcWarps * 2 * kTileBytes;
+};
+
+template <int PD>
+__global__ void __launch_bounds__(kNcWarps * 32, PD == 256 ? 2 : 4) decode_nc_tiles_kernel(const __grid_constant__ NcDecodeParams p) {
+    using T = NcTileShape<PD>;
+    extern __shared__ __align__(16) uint8_t tsm[];
     __shared__ float m_s[kNcWarps][kNcMaxGroup], l_s[kNcWarps][kNcMaxGroup];
-    __shared__ float cent_s[16];   // a lookup indexed per lane: shared memory, not the parameter bank
+    __shared__ uint32_t lut_s[256];          // K code byte -> (centroid of the even dim = low nibble, of the odd dim) as half2
+    __shared__ uint32_t lutv_s[256];         // V code byte -> (low nibble, high nibble) as half2 numbers 0..15
+    __shared__ float nk_s[kNcWarps][16];
+    constexpr int pd = PD;
+    const int G = p.group;
+    float* q_s = reinterpret_cast<float*>(tsm);                          // [G][pd] rotated queries
+    uint8_t* tiles = tsm + (size_t)kNcMaxGroup * PD * 4;
+    float* o_s = reinterpret_cast<float*>(tiles);                        // [warps][G][pd], after the loop
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tg = lane & 3;
     const int split = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
-    if (tid < 16) cent_s[tid] = p.centroids[tid];
+    for (int v = tid; v < 256; v += blockDim.x) {
+        lut_s[v] = nct_pack_half2(p.centroids[v & 15], p.centroids[v >> 4]);
+        lutv_s[v] = nct_pack_half2((float)(v & 15), (float)(v >> 4));
+    }
 
+    // window of this split, in pages
     const int64_t len = p.seq_lens[b];
+    const int64_t begin = 0;
+    const int first_page = 0;
     int npages = (int)((len + kNcPage - 1) / kNcPage);
     const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
     const int have = p.page_indptr ? p.page_indptr[b + 1] - p.page_indptr[b] : p.max_pages;
-    if (npages > have) {   // the table cannot back this length: read nothing
+    if (npages > have) {  // the table cannot back this length: read nothing
         if (tid == 0) atomicExch(&p.header[0], 4);
         npages = 0;
     }
     const int per = (npages + p.splits - 1) / p.splits;
-    const int pg0 = split * per;
-    const int pg1 = min(npages, pg0 + per);
+    const int pg0 = first_page + split * per;
+    const int pg1 = min(first_page + npages, pg0 + per);
 
-    // rotate the group's queries: q H / sqrt(d), no signs in this format
-    for (int i = tid; i < G * d; i += blockDim.x) {
-        const int g = i / d, e = i - g * d;
-        q_s[i] = nc_load(p.q, p.q_dtype, ((int64_t)b * p.num_q_heads + h * G + g) * d + e);
+    // rotate the group's queries: signs, butterflies, 1/sqrt(pd)
+    for (int i = tid; i < G * pd; i += blockDim.x) {
+        const int gg = i / pd, d = i - gg * pd;
+        q_s[i] = nc_load(p.q, p.q_dtype, ((int64_t)b * p.num_q_heads + h * G + gg) * pd + d);
     }
     __syncthreads();
-    for (int hh = 1; hh < d; hh <<= 1) {
-        for (int i = tid; i < G * d / 2; i += blockDim.x) {
-            const int g = i / (d / 2), idx = i - g * (d / 2);
+    for (int hh = 1; hh < pd; hh <<= 1) {
+        for (int i = tid; i < G * pd / 2; i += blockDim.x) {
+            const int gg = i / (pd / 2), idx = i - gg * (pd / 2);
             const int j = (idx / hh) * 2 * hh + (idx % hh);
-            float* row = q_s + g * d;
+            float* row = q_s + gg * pd;
             const float a = row[j], c = row[j + hh];
             row[j] = a + c;
             row[j + hh] = a - c;
         }
         __syncthreads();
     }
-    for (int i = tid; i < G * d; i += blockDim.x) q_s[i] *= p.scale;
-    __syncthreads();
-
-    float m[kNcMaxGroup], l[kNcMaxGroup], o[kNcMaxGroup][2 * BPL];
+    // B fragments of Q^T: column g of the query tile (zero beyond the group), k-steps of 16 dims
+    uint32_t qf[PD / 8];
 #pragma unroll
-    for (int g = 0; g < kNcMaxGroup; g++) {
-        m[g] = -INFINITY;
-        l[g] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 2 * BPL; e++) o[g][e] = 0.0f;
+    for (int s = 0; s < PD / 16; s++) {
+        const float* row = q_s + g * pd + 16 * s + 2 * tg;
+        const bool on = g < G;
+        qf[2 * s] = on ? nct_pack_half2(row[0] * p.scale, row[1] * p.scale) : 0u;
+        qf[2 * s + 1] = on ? nct_pack_half2(row[8] * p.scale, row[9] * p.scale) : 0u;
     }
+
+    float o_acc[PD / 16][4];
+#pragma unroll
+    for (int i = 0; i < PD / 16; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) o_acc[i][j] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    const int tk = lane >> 1, hf = lane & 1;                       // loads: lane = (token, half of its code bytes)
+    const uint32_t tile_k = nct_smem_u32(tiles) + (uint32_t)warp * 2 * T::kTileBytes, tile_v = tile_k + T::kTileBytes;
+    const uint32_t st_k = tile_k + tk * T::kRowBytes + hf * PD, st_v = tile_v + tk * T::kRowBytes + hf * PD;
+    const uint32_t lm_k = tile_k + (lane & 15) * T::kRowBytes + (lane >> 4) * 16;
+    const uint32_t lm_v = tile_v + ((lane & 7) + 8 * (lane >> 4)) * T::kRowBytes + ((lane >> 3) & 1) * 16;
     bool bad_page = false;
-    int64_t page_next = pg0 < pg1 ? (int64_t)p.page_indices[tbl + pg0] : 0;
-    for (int pg = pg0; pg < pg1; pg++) {
-        const int64_t page = page_next;
-        if (pg + 1 < pg1) page_next = p.page_indices[tbl + pg + 1];
+    for (int pg = pg0 + warp; pg < pg1; pg += kNcWarps) {
+        const int64_t page = p.page_indices[tbl + pg];
         if ((uint64_t)page >= (uint64_t)p.num_blocks) {  // never form an address from it
             bad_page = true;
             continue;
         }
-        // A warp takes tokens warp, warp + 4, warp + 8, warp + 12 of the page: all their loads are issued
-        // before the arithmetic of the first one, so four tokens' latencies overlap.
-        uint8_t kb[4][BPL], vb[4][BPL];
-        float kn[4], vsc[4], vz[4];
-        bool tv[4];
+        // ---- load and dequantize the page's codes into the two tiles ---------------------------------
+        const uint8_t* ks = p.kv_cache + ((size_t)(page * kNcPage + tk) * p.num_kv_heads + h) * p.g.slot_bytes;
+        const uint8_t* vs = ks + p.g.kps;
+        // the slots of this format are only 2-byte aligned: 16-bit loads, two per code word
+        uint4 kc[PD / 64], vc[PD / 64];
+        {
+            const uint16_t* k16 = reinterpret_cast<const uint16_t*>(ks + hf * (PD / 4));
+            const uint16_t* v16 = reinterpret_cast<const uint16_t*>(vs + hf * (PD / 4));
+            uint32_t* kd = reinterpret_cast<uint32_t*>(kc);
+            uint32_t* vd = reinterpret_cast<uint32_t*>(vc);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int e = warp + kNcWarps * i;
-            const int64_t t = (int64_t)pg * kNcPage + e;
-            tv[i] = t < len;
-            kn[i] = vsc[i] = vz[i] = 0.0f;
-#pragma unroll
-            for (int j = 0; j < BPL; j++) kb[i][j] = vb[i][j] = 0;
-            if (tv[i]) {
-                const uint8_t* ks = p.kv_cache + ((size_t)(page * kNcPage + e) * p.num_kv_heads + h) * p.g.slot_bytes;
-                const uint8_t* vs = ks + p.g.kps;
-#pragma unroll
-                for (int j = 0; j < BPL; j++) {
-                    kb[i][j] = ks[lane + 32 * j];
-                    vb[i][j] = vs[lane + 32 * j];
-                }
-                kn[i] = nc_half_at(ks + p.g.qbytes);
-                vsc[i] = nc_half_at(vs + p.g.qbytes);
-                vz[i] = nc_half_at(vs + p.g.qbytes + 2);
+            for (int i = 0; i < PD / 16; i++) {
+                kd[i] = (uint32_t)k16[2 * i] | ((uint32_t)k16[2 * i + 1] << 16);
+                vd[i] = (uint32_t)v16[2 * i] | ((uint32_t)v16[2 * i + 1] << 16);
             }
         }
+        // (scale, scale) and (zero, zero) of this lane's token, as half2
+        const uint32_t sc16 = *reinterpret_cast<const uint16_t*>(vs + p.g.qbytes), ze16 = *reinterpret_cast<const uint16_t*>(vs + p.g.qbytes + 2);
+        const uint32_t vsz = sc16 | (sc16 << 16), vzz = ze16 | (ze16 << 16);
+        if (hf == 0) nk_s[warp][tk] = __half2float(*reinterpret_cast<const __half*>(ks + p.g.qbytes));
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            if (!tv[i]) continue;
-            float kd[2 * BPL], vd[2 * BPL];
+        for (int i = 0; i < PD / 64; i++) {
+            const uint32_t kw[4] = {kc[i].x, kc[i].y, kc[i].z, kc[i].w}, vw[4] = {vc[i].x, vc[i].y, vc[i].z, vc[i].w};
 #pragma unroll
-            for (int j = 0; j < BPL; j++) {   // the even dim sits in the low nibble
-                kd[2 * j] = cent_s[kb[i][j] & 15] * kn[i];
-                kd[2 * j + 1] = cent_s[kb[i][j] >> 4] * kn[i];
-                vd[2 * j] = __fmaf_rn((float)(vb[i][j] & 15), vsc[i], vz[i]);
-                vd[2 * j + 1] = __fmaf_rn((float)(vb[i][j] >> 4), vsc[i], vz[i]);
-            }
+            for (int w = 0; w < 4; w++) {
+                uint32_t a[4], c[4];
 #pragma unroll
-            for (int g = 0; g < kNcMaxGroup; g++) {
-                if (g >= G) break;
-                const float* qr = q_s + g * d;
-                float sc = 0.0f;
-#pragma unroll
-                for (int j = 0; j < BPL; j++) {
-                    const float2 q2 = *reinterpret_cast<const float2*>(qr + 2 * (lane + 32 * j));
-                    sc = __fmaf_rn(q2.x, kd[2 * j], __fmaf_rn(q2.y, kd[2 * j + 1], sc));
+                for (int j = 0; j < 4; j++) {
+                    a[j] = lut_s[(kw[w] >> (8 * j)) & 0xFF];
+                    c[j] = nct_hfma2(lutv_s[(vw[w] >> (8 * j)) & 0xFF], vsz, vzz);   // code * scale + zero
                 }
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, off);
-                sc *= p.score_scale;
-                const float m_new = fmaxf(m[g], sc);
-                const float corr = nc_exp2(m[g] - m_new), w = nc_exp2(sc - m_new);
-                m[g] = m_new;
-                l[g] = __fmaf_rn(l[g], corr, w);
-#pragma unroll
-                for (int e2 = 0; e2 < 2 * BPL; e2++) o[g][e2] = __fmaf_rn(w, vd[e2], o[g][e2] * corr);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_k + (4 * i + w) * 16), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_v + (4 * i + w) * 16), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
             }
         }
+        __syncwarp();
+        // ---- S = K^ Q^T ----------------------------------------------------------------------------------
+        float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int s = 0; s < PD / 16; s++) {
+            uint32_t a[4];
+            nct_ldmatrix_x4(lm_k + s * 32, a);
+            nct_mma16816(s_acc, a, qf[2 * s], qf[2 * s + 1]);
+        }
+        // ---- online softmax (base 2); rows g and g + 8 are tokens, columns 2tg and 2tg + 1 query heads -----
+        const int64_t t0 = (int64_t)pg * kNcPage;
+        const bool va = t0 + g >= begin && t0 + g < len, vb = t0 + g + 8 >= begin && t0 + g + 8 < len;
+        const float kfa = va ? nk_s[warp][g] * p.score_scale : 0.0f, kfb = vb ? nk_s[warp][g + 8] * p.score_scale : 0.0f;
+        const float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
+        const float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
+        float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+        }
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float c0 = n0 > m0 ? nc_exp2(m0 - n0) : 1.0f, c1 = n1 > m1 ? nc_exp2(m1 - n1) : 1.0f;
+        m0 = n0;
+        m1 = n1;
+        const float e0 = va ? nc_exp2(x0 - m0) : 0.0f, e1 = va ? nc_exp2(x1 - m1) : 0.0f;
+        const float e2 = vb ? nc_exp2(x2 - m0) : 0.0f, e3 = vb ? nc_exp2(x3 - m1) : 0.0f;
+        l0 = __fmaf_rn(l0, c0, e0 + e2);
+        l1 = __fmaf_rn(l1, c1, e1 + e3);
+        const uint32_t pb0 = nct_movmatrix_trans(nct_pack_half2(e0, e1));
+        const uint32_t pb1 = nct_movmatrix_trans(nct_pack_half2(e2, e3));
+        // ---- O^T += V^^T P ------------------------------------------------------------------------------------
+#pragma unroll
+        for (int mt = 0; mt < PD / 16; mt++) {
+            uint32_t a[4];
+            nct_ldmatrix_x4_trans(lm_v + mt * 32, a);
+            o_acc[mt][0] *= c0; o_acc[mt][1] *= c1; o_acc[mt][2] *= c0; o_acc[mt][3] *= c1;
+            nct_mma16816(o_acc[mt], a, pb0, pb1);
+        }
+        __syncwarp();   // the tiles are rewritten by the next page
     }
     if (bad_page && lane == 0) atomicExch(&p.header[0], 5);
+    // this warp's sums over its token lanes, then everything to shared memory for the block's combine
 #pragma unroll
-    for (int g = 0; g < kNcMaxGroup; g++) {
-        if (g >= G) break;
-        if (lane == 0) {
-            m_s[warp][g] = m[g];
-            l_s[warp][g] = l[g];
+    for (int o = 4; o < 32; o <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    }
+    __syncthreads();   // every warp has left its tiles: the region becomes o_s
+    if (g == 0) {
+        if (2 * tg < G) { m_s[warp][2 * tg] = m0; l_s[warp][2 * tg] = l0; }
+        if (2 * tg + 1 < G) { m_s[warp][2 * tg + 1] = m1; l_s[warp][2 * tg + 1] = l1; }
+    }
+#pragma unroll
+    for (int mt = 0; mt < PD / 16; mt++) {
+        const int d0 = 16 * mt + g;
+        if (2 * tg < G) {
+            o_s[(warp * G + 2 * tg) * pd + d0] = o_acc[mt][0];
+            o_s[(warp * G + 2 * tg) * pd + d0 + 8] = o_acc[mt][2];
         }
-#pragma unroll
-        for (int j = 0; j < BPL; j++) {
-            const int e2 = 2 * (lane + 32 * j);
-            o_s[(warp * G + g) * d + e2] = o[g][2 * j];
-            o_s[(warp * G + g) * d + e2 + 1] = o[g][2 * j + 1];
+        if (2 * tg + 1 < G) {
+            o_s[(warp * G + 2 * tg + 1) * pd + d0] = o_acc[mt][1];
+            o_s[(warp * G + 2 * tg + 1) * pd + d0 + 8] = o_acc[mt][3];
         }
     }
     __syncthreads();
-    for (int i = tid; i < G * d; i += blockDim.x) {
-        const int g = i / d, e = i - g * d;
+    for (int i = tid; i < G * pd; i += blockDim.x) {
+        const int gg = i / pd, d = i - gg * pd;
         float mm = -INFINITY;
-        for (int w = 0; w < kNcWarps; w++) mm = fmaxf(mm, m_s[w][g]);
+        for (int w = 0; w < kNcWarps; w++) mm = fmaxf(mm, m_s[w][gg]);
         float ll = 0.0f, acc = 0.0f;
         if (mm > -INFINITY) {
             for (int w = 0; w < kNcWarps; w++) {
-                const float sc = exp2f(m_s[w][g] - mm);
+                const float sc = nc_exp2(m_s[w][gg] - mm);
                 if (sc > 0.0f) {
-                    ll += sc * l_s[w][g];
-                    acc += sc * o_s[(w * G + g) * d + e];
+                    ll += sc * l_s[w][gg];
+                    acc += sc * o_s[(w * G + gg) * pd + d];
                 }
             }
         }
-        const int64_t row = ((int64_t)b * p.splits + split) * p.num_q_heads + h * G + g;
-        p.partial_o[row * d + e] = ll > 0.0f ? acc / ll : 0.0f;
-        if (e == 0) p.partial_lse[row] = ll > 0.0f ? mm + log2f(ll) : -INFINITY;
+        const int64_t row = ((int64_t)b * p.splits + split) * p.num_q_heads + h * G + gg;
+        p.partial_o[row * pd + d] = ll > 0.0f ? acc / ll : 0.0f;
+        if (d == 0) p.partial_lse[row] = ll > 0.0f ? mm + log2f(ll) : -INFINITY;
     }
 }
 
@@ -486,21 +574,20 @@ extern "C" int tq_nc_decode_paged(const void* q, int q_dtype, int batch, int num
     float bnd[15];
     host_codebook(head_dim, 4, p.centroids, bnd);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const size_t smem = (size_t)(kNcMaxGroup * kNcMaxDim + kNcWarps * kNcMaxGroup * kNcMaxDim) * sizeof(float);
     static bool configured[64] = {};
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(decode_nc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        TQ_CUDA(cudaFuncSetAttribute(decode_nc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        TQ_CUDA(cudaFuncSetAttribute(decode_nc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_nc_tiles_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NcTileShape<64>::kSmem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_nc_tiles_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NcTileShape<128>::kSmem));
+        TQ_CUDA(cudaFuncSetAttribute(decode_nc_tiles_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NcTileShape<256>::kSmem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const dim3 grid((unsigned)p.splits, (unsigned)batch, (unsigned)num_kv_heads);
-    switch (head_dim / 64) {
-        case 1: decode_nc_kernel<1><<<grid, kNcWarps * 32, smem, s>>>(p); break;
-        case 2: decode_nc_kernel<2><<<grid, kNcWarps * 32, smem, s>>>(p); break;
-        default: decode_nc_kernel<4><<<grid, kNcWarps * 32, smem, s>>>(p); break;
+    switch (head_dim) {
+        case 64: decode_nc_tiles_kernel<64><<<grid, kNcWarps * 32, NcTileShape<64>::kSmem, s>>>(p); break;
+        case 128: decode_nc_tiles_kernel<128><<<grid, kNcWarps * 32, NcTileShape<128>::kSmem, s>>>(p); break;
+        default: decode_nc_tiles_kernel<256><<<grid, kNcWarps * 32, NcTileShape<256>::kSmem, s>>>(p); break;
     }
     TQ_CUDA(cudaGetLastError());
     NcMergeParams m{};
