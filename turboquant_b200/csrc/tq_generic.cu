@@ -42,17 +42,43 @@ static GenGeom make_geom(int head_dim, int slot_bytes) {
     return g;
 }
 
-// butterflies h = 1 .. padded/2 on a shared-memory row, by one warp
-__device__ __forceinline__ void gen_warp_fwht(float* buf, int padded, int lane) {
-    for (int h = 1; h < padded; h <<= 1) {
-        for (int idx = lane; idx < padded / 2; idx += 32) {
-            const int i = (idx / h) * 2 * h + (idx % h);
-            const float a = buf[i], b = buf[i + h];
-            buf[i] = __fadd_rn(a, b);
-            buf[i + h] = __fsub_rn(a, b);
+// butterflies h = 1 .. padded/2 on a shared-memory row, by one warp: lane l takes elements l E .. l E + E - 1
+// (E = padded / 32) into registers, runs the stages h < E there and the stages h >= E as one shuffle per
+// element, and puts the row back.  Every stage forms the same a + b and a - b as the in-place loop would,
+// so the result is bit-identical to it.
+template <int E>
+__device__ __forceinline__ void gen_warp_fwht_regs(float* buf, int lane) {
+    float v[E];
+#pragma unroll
+    for (int i = 0; i < E; i++) v[i] = buf[lane * E + i];
+#pragma unroll
+    for (int h = 1; h < E; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            if ((i & h) == 0) {
+                const float a = v[i], b = v[i + h];
+                v[i] = __fadd_rn(a, b);
+                v[i + h] = __fsub_rn(a, b);
+            }
         }
-        __syncwarp();
     }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {   // element stride h = m E: the partner sits in lane ^ m
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
+            v[i] = (lane & m) ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < E; i++) buf[lane * E + i] = v[i];
+    __syncwarp();
+}
+__device__ __forceinline__ void gen_warp_fwht(float* buf, int padded, int lane) {
+    if (padded == 64) gen_warp_fwht_regs<2>(buf, lane);
+    else if (padded == 128) gen_warp_fwht_regs<4>(buf, lane);
+    else gen_warp_fwht_regs<8>(buf, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -646,6 +672,9 @@ static __device__ int32_t g_gen_dequant_skipped = 0;
 
 __global__ void __launch_bounds__(kGenWarps * 32) dequant_generic_kernel(const __grid_constant__ GenDequantParams p) {
     __shared__ float buf_s[kGenWarps][kGenMaxDim];
+    __shared__ float cent_s[16];   // a lookup indexed per lane: shared memory, not the parameter bank
+    if (threadIdx.x < 16) cent_s[threadIdx.x] = p.centroids[threadIdx.x];
+    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* buf = buf_s[warp];
     const int H = p.num_kv_heads, pd = p.g.padded;
@@ -670,8 +699,8 @@ __global__ void __launch_bounds__(kGenWarps * 32) dequant_generic_kernel(const _
         const uint8_t* slot = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)(page * kGenPage + e) * H + h) * p.g.slot_bytes;
         for (int i = lane; i < p.g.qbytes; i += 32) {
             const uint8_t c = slot[i];
-            buf[2 * i] = p.centroids[c >> 4];
-            buf[2 * i + 1] = p.centroids[c & 15];
+            buf[2 * i] = cent_s[c >> 4];
+            buf[2 * i + 1] = cent_s[c & 15];
         }
         __syncwarp();
         gen_warp_fwht(buf, pd, lane);
