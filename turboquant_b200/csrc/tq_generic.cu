@@ -103,6 +103,9 @@ template <typename T>
 __global__ void __launch_bounds__(kGenWarps * 32) write_generic_kernel(const __grid_constant__ GenWriteParams p) {
     __shared__ float buf_s[kGenWarps][kGenMaxDim];
     __shared__ uint8_t idx_s[kGenWarps][kGenMaxDim];
+    __shared__ float bnd_s[16];
+    if (threadIdx.x < 15) bnd_s[threadIdx.x] = p.boundaries[threadIdx.x];
+    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* buf = buf_s[warp];
     uint8_t* idx = idx_s[warp];
@@ -141,8 +144,11 @@ __global__ void __launch_bounds__(kGenWarps * 32) write_generic_kernel(const __g
         gen_warp_fwht(buf, pd, lane);
         for (int i = lane; i < pd; i += 32) {
             const float y = __fmul_rn(buf[i], p.scale);
-            int c = 0;
-            for (int k = 0; k < 15; k++) c += (p.boundaries[k] < y) ? 1 : 0;
+            // boundaries strictly below y (they ascend): a binary search over the shared copy
+            int c = (bnd_s[7] < y) ? 8 : 0;
+            c += (bnd_s[c + 3] < y) ? 4 : 0;
+            c += (bnd_s[c + 1] < y) ? 2 : 0;
+            c += (bnd_s[c] < y) ? 1 : 0;
             if (y != y) c = 15;
             idx[i] = (uint8_t)c;
         }

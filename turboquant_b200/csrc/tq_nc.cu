@@ -57,22 +57,50 @@ struct NcWriteParams {
     float boundaries[15];   // Lloyd-Max boundaries of N(0, 1/d)
 };
 
-__device__ __forceinline__ void nc_warp_fwht(float* buf, int d, int lane) {
-    for (int h = 1; h < d; h <<= 1) {
-        for (int idx = lane; idx < d / 2; idx += 32) {
-            const int i = (idx / h) * 2 * h + (idx % h);
-            const float a = buf[i], b = buf[i + h];
-            buf[i] = __fadd_rn(a, b);
-            buf[i + h] = __fsub_rn(a, b);
+// butterflies h = 1 .. d/2 on a shared-memory row, by one warp: lane l takes elements l E .. l E + E - 1 (E = d / 32)
+// into registers, runs the stages h < E there and the stages h >= E as one shuffle per element
+template <int E>
+__device__ __forceinline__ void nc_warp_fwht_regs(float* buf, int lane) {
+    float v[E];
+#pragma unroll
+    for (int i = 0; i < E; i++) v[i] = buf[lane * E + i];
+#pragma unroll
+    for (int h = 1; h < E; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            if ((i & h) == 0) {
+                const float a = v[i], b = v[i + h];
+                v[i] = __fadd_rn(a, b);
+                v[i + h] = __fsub_rn(a, b);
+            }
         }
-        __syncwarp();
     }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
+            v[i] = (lane & m) ? __fsub_rn(o, v[i]) : __fadd_rn(v[i], o);
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < E; i++) buf[lane * E + i] = v[i];
+    __syncwarp();
+}
+__device__ __forceinline__ void nc_warp_fwht(float* buf, int d, int lane) {
+    if (d == 64) nc_warp_fwht_regs<2>(buf, lane);
+    else if (d == 128) nc_warp_fwht_regs<4>(buf, lane);
+    else nc_warp_fwht_regs<8>(buf, lane);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kNcWarps * 32) write_nc_kernel(const __grid_constant__ NcWriteParams p) {
     __shared__ float buf_s[kNcWarps][kNcMaxDim];
     __shared__ uint8_t idx_s[kNcWarps][kNcMaxDim];
+    __shared__ float bnd_s[16];
+    if (threadIdx.x < 15) bnd_s[threadIdx.x] = p.boundaries[threadIdx.x];
+    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* buf = buf_s[warp];
     uint8_t* idx = idx_s[warp];
@@ -108,8 +136,11 @@ __global__ void __launch_bounds__(kNcWarps * 32) write_nc_kernel(const __grid_co
         nc_warp_fwht(buf, d, lane);
         for (int i = lane; i < d; i += 32) {
             const float y = __fmul_rn(buf[i], p.scale);
-            int c = 0;
-            for (int k = 0; k < 15; k++) c += (p.boundaries[k] < y) ? 1 : 0;
+            // boundaries strictly below y (they ascend): a binary search over the shared copy
+            int c = (bnd_s[7] < y) ? 8 : 0;
+            c += (bnd_s[c + 3] < y) ? 4 : 0;
+            c += (bnd_s[c + 1] < y) ? 2 : 0;
+            c += (bnd_s[c] < y) ? 1 : 0;
             if (y != y) c = 15;
             idx[i] = (uint8_t)c;
         }
