@@ -99,67 +99,176 @@ struct GenWriteParams {
 
 static __device__ int32_t g_gen_write_dropped = 0;
 
-template <typename T>
-__global__ void __launch_bounds__(kGenWarps * 32) write_generic_kernel(const __grid_constant__ GenWriteParams p) {
-    __shared__ float buf_s[kGenWarps][kGenMaxDim];
-    __shared__ uint8_t idx_s[kGenWarps][kGenMaxDim];
+// Eight lanes own one row and a warp works on four rows at a time.  Lane q of a row holds elements
+// q, q + 8, q + 16, ... (E = padded / 8 registers), which is the torch evaluation order of the norm laid out
+// across lanes: accumulator k of the eight interleaved ones is lane k's running sum over its registers.  Butterfly
+// stages h = 1, 2, 4 are one shuffle per element, stages h >= 8 are register-local.  The quotient x / norm is
+// q = x r, e = fma(-q, norm, x), q' = fma(e, r, q) with r the correctly rounded reciprocal, which equals the IEEE
+// quotient when every square of the row is a normal number, the norm is moderate and its significand is not all
+// ones (checked per row; the row takes the division instruction otherwise).  The codes of a row are assembled
+// in shared memory and leave as 16-byte stores when the slots are 16-byte aligned.
+template <int E>
+struct GenRows8 {
+    static constexpr int kPd = 8 * E, kQb = kPd / 2, kDc = kPd / 64;
+    static constexpr int kRowStride = kQb + 16;   // rows of a pass in different banks
+};
+
+template <typename T, int E>
+__global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __grid_constant__ GenWriteParams p) {
+    using G = GenRows8<E>;
     __shared__ float bnd_s[16];
+    __shared__ __align__(16) uint8_t code_s[kGenWarps][4][G::kRowStride];
+    __shared__ float sg_s[G::kPd];
     if (threadIdx.x < 15) bnd_s[threadIdx.x] = p.boundaries[threadIdx.x];
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* buf = buf_s[warp];
-    uint8_t* idx = idx_s[warp];
-    const int H = p.num_kv_heads, pd = p.g.padded, hd = p.g.head_dim;
+    const int q = lane & 7, rg = lane >> 3;
+    const int H = p.num_kv_heads, hd = p.g.head_dim;
+    const int full = hd & ~7, ntail = hd - full;
     const int64_t rows = 2 * p.num_tokens * H;
-    for (int64_t r = (int64_t)blockIdx.x * kGenWarps + warp; r < rows; r += (int64_t)gridDim.x * kGenWarps) {
-        const int which = (int)(r & 1);
-        const int64_t th = r >> 1, t = th / H;
-        const int h = (int)(th - t * H);
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.kv_cache) | (uintptr_t)p.slab_bytes | (uintptr_t)p.g.slot_bytes) & 15) == 0;
+    uint8_t* stage = code_s[warp][rg];
+
+    // signs in shared memory (1 for the padding, which stays +0): E registers less than holding them
+    for (int j = threadIdx.x; j < G::kPd; j += kGenWarps * 32) sg_s[j] = j < hd ? p.signs[j] : 1.0f;
+    __syncthreads();
+    const float* sg = sg_s + q;
+
+    for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < rows; base += (int64_t)gridDim.x * kGenWarps * 4) {
+        // a group past the end works on the last row again and stores nothing: the shuffles below take every lane
+        const bool live = base + rg < rows;
+        const int64_t r64 = live ? base + rg : rows - 1;
+        const int which = (int)(r64 & 1);
+        const int64_t th = r64 >> 1;
+        int64_t t;
+        int h;
+        if (th < 0x7fffffff) {
+            const uint32_t t32 = (uint32_t)th / (uint32_t)H;
+            t = t32;
+            h = (int)((uint32_t)th - t32 * (uint32_t)H);
+        } else {
+            t = th / H;
+            h = (int)(th - t * H);
+        }
         int64_t slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
                                      : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
         if (slot >= p.total_slots) {
-            if (lane == 0 && h == 0 && which == 0) atomicAdd(&g_gen_write_dropped, 1);
+            if (live && q == 0 && h == 0 && which == 0) atomicAdd(&g_gen_write_dropped, 1);
             slot = -1;
         }
-        if (slot < 0) continue;
+        const bool store = live && slot >= 0;
         const T* row = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * hd;
-        for (int i = lane; i < pd; i += 32) buf[i] = i < hd ? to_f32(row[i]) : 0.0f;
-        __syncwarp();
-        // norm in the reference order: eight interleaved accumulators, combined left to right, then the tail
-        float acc = 0.0f;
-        const int full = hd & ~7;
-        if (lane < 8)
-            for (int j = lane; j < full; j += 8) acc = __fadd_rn(acc, __fmul_rn(buf[j], buf[j]));
-        float s = 0.0f;
-        for (int k = 0; k < 8; k++) {
-            const float a = __shfl_sync(0xffffffffu, acc, k);
-            s = k == 0 ? a : __fadd_rn(s, a);
+        float x[E];
+#pragma unroll
+        for (int r = 0; r < E; r++) x[r] = q + 8 * r < hd ? to_f32(row[q + 8 * r]) : 0.0f;
+
+        // norm in the reference order: eight interleaved accumulators (one per lane), combined left to right,
+        // then the elements past the last multiple of eight
+        float acc = 0.0f, minsq = 3.0e38f, tail_sq = 0.0f;
+#pragma unroll
+        for (int r = 0; r < E; r++) {
+            const float sq = __fmul_rn(x[r], x[r]);
+            if (8 * r < full) {
+                acc = __fadd_rn(acc, sq);
+                minsq = fminf(minsq, sq);
+            } else if (8 * r == full) {
+                tail_sq = sq;
+                if (q < ntail) minsq = fminf(minsq, sq);
+            }
         }
-        for (int j = full; j < hd; j++) s = __fadd_rn(s, __fmul_rn(buf[j], buf[j]));
+        float s = __shfl_sync(0xffffffffu, acc, 0, 8);
+#pragma unroll
+        for (int k = 1; k < 8; k++) s = __fadd_rn(s, __shfl_sync(0xffffffffu, acc, k, 8));
+        for (int k = 0; k < ntail; k++) s = __fadd_rn(s, __shfl_sync(0xffffffffu, tail_sq, k, 8));
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) minsq = fminf(minsq, __shfl_xor_sync(0xffffffffu, minsq, m));
         float norm = __fsqrt_rn(s);
         if (!(norm >= 1e-8f)) norm = (norm != norm) ? __uint_as_float(0x7fc00000u) : 1e-8f;
-        for (int i = lane; i < pd; i += 32)
-            buf[i] = i < hd ? __fmul_rn(__fdiv_rn(buf[i], norm), p.signs[i]) : 0.0f;
-        __syncwarp();
-        gen_warp_fwht(buf, pd, lane);
-        for (int i = lane; i < pd; i += 32) {
-            const float y = __fmul_rn(buf[i], p.scale);
-            // boundaries strictly below y (they ascend): a binary search over the shared copy
-            int c = (bnd_s[7] < y) ? 8 : 0;
-            c += (bnd_s[c + 3] < y) ? 4 : 0;
-            c += (bnd_s[c + 1] < y) ? 2 : 0;
-            c += (bnd_s[c] < y) ? 1 : 0;
-            if (y != y) c = 15;
-            idx[i] = (uint8_t)c;
+
+        const bool fast = minsq >= 1.1754944e-38f && norm >= 9.0949470e-13f && norm <= 1.0995116e12f &&
+                          (__float_as_uint(norm) & 0x7fffffu) != 0x7fffffu;
+        if (fast) {
+            const float rcp = __frcp_rn(norm), nneg = -norm;
+#pragma unroll
+            for (int r = 0; r < E; r++) {
+                const float qv = __fmul_rn(x[r], rcp);
+                const float err = __fmaf_rn(qv, nneg, x[r]);   // x - q norm, exact
+                x[r] = __fmul_rn(__fmaf_rn(err, rcp, qv), sg[8 * r]);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < E; r++) x[r] = q + 8 * r < hd ? __fmul_rn(__fdiv_rn(x[r], norm), sg[8 * r]) : 0.0f;
+        }
+
+        // butterflies in stage order: h = 1, 2, 4 between the lanes of the row, h = 8 ... between registers
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+            for (int r = 0; r < E; r++) {
+                const float o = __shfl_xor_sync(0xffffffffu, x[r], m);
+                x[r] = (q & m) ? __fsub_rn(o, x[r]) : __fadd_rn(x[r], o);
+            }
+        }
+#pragma unroll
+        for (int hr = 1; hr < E; hr <<= 1) {
+#pragma unroll
+            for (int r = 0; r < E; r++) {
+                if ((r & hr) == 0) {
+                    const float a = x[r], b = x[r + hr];
+                    x[r] = __fadd_rn(a, b);
+                    x[r + hr] = __fsub_rn(a, b);
+                }
+            }
+        }
+
+        // codes: element q + 8 r is the high (q even) or low (q odd) nibble of byte q / 2 + 4 r
+        uint32_t word[E / 4];
+        const int nib = (q & 1) ? 0 : 4;
+#pragma unroll
+        for (int w = 0; w < E / 4; w++) {
+            uint32_t acc_w = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float y = __fmul_rn(x[4 * w + i], p.scale);
+                // boundaries strictly below y (they ascend): a binary search over the shared copy
+                int c = (bnd_s[7] < y) ? 8 : 0;
+                c += (bnd_s[c + 3] < y) ? 4 : 0;
+                c += (bnd_s[c + 1] < y) ? 2 : 0;
+                c += (bnd_s[c] < y) ? 1 : 0;
+                if (y != y) c = 15;
+                acc_w |= (uint32_t)c << (8 * i + nib);
+            }
+            word[w] = acc_w | __shfl_xor_sync(0xffffffffu, acc_w, 1);
+        }
+        __syncwarp();   // the previous pass has read its rows out of the staging buffer
+        if ((q & 1) == 0) {
+#pragma unroll
+            for (int w = 0; w < E / 4; w++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) stage[(q >> 1) + 16 * w + 4 * i] = (uint8_t)(word[w] >> (8 * i));
         }
         __syncwarp();
-        uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)slot * H + h) * p.g.slot_bytes;
-        for (int b = lane; b < p.g.qbytes; b += 32) dst[b] = (uint8_t)((idx[2 * b] << 4) | idx[2 * b + 1]);
-        const uint16_t nh = (norm != norm) ? (uint16_t)0x7e00u : __half_as_ushort(__float2half_rn(norm));
-        if (lane < p.g.dc) *reinterpret_cast<uint16_t*>(dst + p.g.qbytes + 2 * lane) = nh;
-        if (p.zero_pad)
-            for (int b = p.g.qbytes + 2 * p.g.dc + lane; b < p.g.slot_bytes; b += 32) dst[b] = 0;
-        __syncwarp();
+        if (store) {
+            uint8_t* dst = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)slot * H + h) * p.g.slot_bytes;
+            if (vec_ok) {
+                for (int v = q; v < G::kQb / 16; v += 8)
+                    reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(stage)[v];
+            } else {
+                for (int b = q; b < G::kQb; b += 8) dst[b] = stage[b];
+            }
+            const uint16_t nh = (norm != norm) ? (uint16_t)0x7e00u : __half_as_ushort(__float2half_rn(norm));
+            if (q < G::kDc) *reinterpret_cast<uint16_t*>(dst + G::kQb + 2 * q) = nh;
+            if (p.zero_pad)
+                for (int b = G::kQb + 2 * G::kDc + q; b < p.g.slot_bytes; b += 8) dst[b] = 0;
+        }
+    }
+}
+
+template <typename T>
+static void launch_write_rows8(const GenWriteParams& p, unsigned grid, cudaStream_t s) {
+    switch (p.g.padded) {
+        case 64: write_rows8_kernel<T, 8><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        case 128: write_rows8_kernel<T, 16><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        default: write_rows8_kernel<T, 32><<<grid, kGenWarps * 32, 0, s>>>(p); break;
     }
 }
 
@@ -758,13 +867,13 @@ int generic_write(void* kv_cache, int64_t num_blocks, int block_size, int num_kv
     float cen[16];
     host_codebook(p.g.padded, 4, cen, p.boundaries);
     const int64_t rows = 2 * num_tokens * num_kv_heads;
-    const int64_t blocks = (rows + kGenWarps - 1) / kGenWarps;
+    const int64_t blocks = (rows + 4 * kGenWarps - 1) / (4 * kGenWarps);   // four rows per warp and pass
     const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (in_dtype) {
-        case TQ_F32: write_generic_kernel<float><<<grid, kGenWarps * 32, 0, s>>>(p); break;
-        case TQ_F16: write_generic_kernel<__half><<<grid, kGenWarps * 32, 0, s>>>(p); break;
-        default: write_generic_kernel<__nv_bfloat16><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        case TQ_F32: launch_write_rows8<float>(p, grid, s); break;
+        case TQ_F16: launch_write_rows8<__half>(p, grid, s); break;
+        default: launch_write_rows8<__nv_bfloat16>(p, grid, s); break;
     }
     TQ_CUDA(cudaGetLastError());
     return TQ_OK;
