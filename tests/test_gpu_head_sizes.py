@@ -136,3 +136,37 @@ def test_slots_that_are_not_16_byte_multiples_take_the_plain_kernel(oracle, gold
     torch.cuda.synchronize()
     assert ws[:4].view(torch.int32).item() == 0
     assert_attention_close(out.cpu().numpy(), want, f"head size {d}, slots of {sb} bytes")
+    # bulk dequantization out of the odd-sized slots: byte loads instead of vector loads, same values
+    cu = torch.tensor([0, lens[0], sum(lens)], dtype=torch.int32, device=DEV)
+    k_out = torch.empty(sum(lens), hkv, d, dtype=torch.float32, device=DEV)
+    v_out = torch.empty_like(k_out)
+    _cabi.dequant_paged(cache, case.block_table.to(DEV), case.seq_lens.to(DEV), cu, signs.to(DEV), k_out, v_out,
+                        max_pages=case.block_table.shape[-1])
+    torch.cuda.synchronize()
+    at = 0
+    for b, n in enumerate(lens):
+        t = np.arange(n)
+        pages = case.block_table.numpy()[b, t // 16]
+        for which, got_t in ((0, k_out), (1, v_out)):
+            want_rows = oracle.dequant_cache_rows(cache_np[which, pages, t % 16][..., :slot_bytes(d)], signs.numpy(), d)
+            np.testing.assert_array_equal(got_t[at:at + n].cpu().numpy(), want_rows)
+        at += n
+
+
+@pytest.mark.parametrize("d,hkv", [(64, 8), (256, 4), (80, 2), (72, 3), (192, 4)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dequant_16_bit_outputs_are_the_rounded_fp32_ones(golden, d, hkv, dtype):
+    """The 16-bit outputs leave as packed 16-byte stores where the rows allow it (head size 72: they do not);
+    every element must be the fp32 result rounded once."""
+    lens = [5, 0, 130, 64]
+    case = synthetic.decode_case(seed=400 + d, seq_lens=lens, dtype=torch.float16, heads=(hkv, hkv), head_dim=d)
+    attn = TurboQuantPagedAttention(hkv, d, 1.0 / math.sqrt(d), hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+    args = (cache, case.block_table.to(DEV), case.seq_lens.to(DEV), cu, sum(lens))
+    k32, v32 = attn.dequant_cached(*args, dtype=torch.float32)
+    k16, v16 = attn.dequant_cached(*args, dtype=dtype)
+    torch.cuda.synchronize()
+    assert torch.equal(k16, k32.to(dtype)) and torch.equal(v16, v32.to(dtype))
+    assert k32.abs().max().item() > 0

@@ -5,9 +5,9 @@
 // head size 64, gemma-2 with 256; slot size turboquant/vllm_backend_fused.py:64-72: 32 code bytes
 // and one fp16 norm per 64 padded dims, rounded up to 16 bytes) but its decode op rejects
 // everything except 128 (csrc/src/decode_v5_tc_binding.cu:779).  These kernels are the plain
-// formulation of the same arithmetic -- one warp per row, shared-memory butterflies, fp32 math --
+// formulation of the same arithmetic -- eight lanes (write, dequantization) or a warp (decode) per row, fp32 math --
 // with the interfaces, the split-KV workspace contract and the parity bars of the tuned 128-wide
-// kernels; they are not tuned for bandwidth.  Quantizer arithmetic as in tq_flat.cu (the torch
+// kernels; they are not tuned to the HBM roofline.  Quantizer arithmetic as in tq_flat.cu (the torch
 // evaluation order), compiled with -fmad=false.
 #include <cmath>
 #include <cstring>
@@ -766,7 +766,7 @@ __global__ void __launch_bounds__(kGenMaxDim) merge_generic_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------------------------
-// bulk dequantization: one warp per (sequence, token, head, K / V)
+// bulk dequantization: eight lanes per (sequence, token, head, K / V)
 // ---------------------------------------------------------------------------------------------
 struct GenDequantParams {
     const uint8_t* kv_cache;
@@ -785,49 +785,161 @@ struct GenDequantParams {
 
 static __device__ int32_t g_gen_dequant_skipped = 0;
 
-__global__ void __launch_bounds__(kGenWarps * 32) dequant_generic_kernel(const __grid_constant__ GenDequantParams p) {
-    __shared__ float buf_s[kGenWarps][kGenMaxDim];
+// Eight lanes own one row and a warp works on four rows at a time.  Lane q holds elements q E ... q E + E - 1
+// (E = padded / 8: the code bytes q E / 2 ... of the slot, one load), so the butterfly stages h < E are
+// register-local and the stages h >= E one shuffle per element, in the same stage order as everywhere else;
+// the row leaves as 16-byte stores when the output rows are 16-byte aligned.
+template <int E>
+__global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const __grid_constant__ GenDequantParams p) {
+    constexpr int kPd = 8 * E, kQb = kPd / 2, kCb = E / 2;   // code bytes per lane: 4, 8 or 16
     __shared__ float cent_s[16];   // a lookup indexed per lane: shared memory, not the parameter bank
+    __shared__ float sg_s[kPd];
     if (threadIdx.x < 16) cent_s[threadIdx.x] = p.centroids[threadIdx.x];
+    for (int j = threadIdx.x; j < kPd; j += kGenWarps * 32) sg_s[j] = j < p.g.head_dim ? p.signs[j] : 0.0f;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* buf = buf_s[warp];
-    const int H = p.num_kv_heads, pd = p.g.padded;
+    const int q = lane & 7, rg = lane >> 3;
+    const int H = p.num_kv_heads, hd = p.g.head_dim;
     const int64_t per_seq = (int64_t)p.max_pages * kGenPage * H * 2;
     const int64_t items = per_seq * p.batch;
-    for (int64_t it = (int64_t)blockIdx.x * kGenWarps + warp; it < items; it += (int64_t)gridDim.x * kGenWarps) {
-        const int b = (int)(it / per_seq);
-        int64_t rem = it - (int64_t)b * per_seq;
-        const int which = (int)(rem & 1);
-        rem >>= 1;
-        const int h = (int)(rem % H);
-        const int64_t t = rem / H;
-        if (t >= p.seq_lens[b]) continue;
-        const int pg = (int)(t / kGenPage), e = (int)(t % kGenPage);
-        const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
-        const bool listed = !p.page_indptr || tbl + pg < (int64_t)p.page_indptr[b + 1];
-        const int64_t page = listed ? (int64_t)p.page_indices[tbl + pg] : -1;
-        if ((uint64_t)page >= (uint64_t)p.num_blocks) {
-            if (lane == 0 && h == 0 && which == 0 && e == 0) atomicAdd(&g_gen_dequant_skipped, 1);
-            continue;
+    const bool small = items < 0x7fffffff;
+    const int esize = p.out_dtype == TQ_F32 ? 4 : 2;
+    const bool in_vec = ((reinterpret_cast<uintptr_t>(p.kv_cache) | (uintptr_t)p.slab_bytes | (uintptr_t)p.g.slot_bytes) & 15) == 0;
+    const bool out_vec = ((reinterpret_cast<uintptr_t>(p.out[0]) | reinterpret_cast<uintptr_t>(p.out[1])) & 15) == 0 &&
+                         ((p.out_token_stride * esize) & 15) == 0 && ((hd * esize) & 15) == 0;
+    const float* sg = sg_s + q * E;
+
+    for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < items; base += (int64_t)gridDim.x * kGenWarps * 4) {
+        // a group without a row (past the end, past its sequence, an unlisted page) runs the shuffles on zeros
+        const int64_t it = base + rg;
+        bool live = it < items;
+        int b = 0, which = 0, h = 0;
+        int64_t t = 0;
+        if (live) {
+            if (small) {
+                const uint32_t i32 = (uint32_t)it, ps = (uint32_t)per_seq;
+                const uint32_t bb = i32 / ps;
+                uint32_t rem = i32 - bb * ps;
+                which = (int)(rem & 1);
+                rem >>= 1;
+                const uint32_t tt = rem / (uint32_t)H;
+                h = (int)(rem - tt * (uint32_t)H);
+                b = (int)bb;
+                t = tt;
+            } else {
+                b = (int)(it / per_seq);
+                int64_t rem = it - (int64_t)b * per_seq;
+                which = (int)(rem & 1);
+                rem >>= 1;
+                t = rem / H;
+                h = (int)(rem - t * H);
+            }
+            live = t < p.seq_lens[b];
         }
-        const uint8_t* slot = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)(page * kGenPage + e) * H + h) * p.g.slot_bytes;
-        for (int i = lane; i < p.g.qbytes; i += 32) {
-            const uint8_t c = slot[i];
-            buf[2 * i] = cent_s[c >> 4];
-            buf[2 * i + 1] = cent_s[c & 15];
+        const uint8_t* slot = nullptr;
+        if (live) {
+            const int pg = (int)(t / kGenPage), e = (int)(t % kGenPage);
+            const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
+            const bool listed = !p.page_indptr || tbl + pg < (int64_t)p.page_indptr[b + 1];
+            const int64_t page = listed ? (int64_t)p.page_indices[tbl + pg] : -1;
+            if ((uint64_t)page >= (uint64_t)p.num_blocks) {
+                if (q == 0 && h == 0 && which == 0 && e == 0) atomicAdd(&g_gen_dequant_skipped, 1);
+                live = false;
+            } else {
+                slot = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)(page * kGenPage + e) * H + h) * p.g.slot_bytes;
+            }
         }
-        __syncwarp();
-        gen_warp_fwht(buf, pd, lane);
-        const float norm = __half2float(*reinterpret_cast<const __half*>(slot + p.g.qbytes));
-        const int64_t orow = ((int64_t)p.cu_seqlens[b] + t) * p.out_token_stride + (int64_t)h * p.g.head_dim;
-        for (int d = lane; d < p.g.head_dim; d += 32) {
-            const float v = __fmul_rn(__fmul_rn(__fmul_rn(buf[d], p.scale), p.signs[d]), norm);
-            if (p.out_dtype == TQ_BF16) reinterpret_cast<__nv_bfloat16*>(p.out[which])[orow + d] = __float2bfloat16_rn(v);
-            else if (p.out_dtype == TQ_F16) reinterpret_cast<__half*>(p.out[which])[orow + d] = __float2half_rn(v);
-            else reinterpret_cast<float*>(p.out[which])[orow + d] = v;
+        // code bytes q E / 2 ... of the slot
+        uint32_t cw[(kCb + 3) / 4];
+#pragma unroll
+        for (int i = 0; i < (kCb + 3) / 4; i++) cw[i] = 0;
+        float norm = 0.0f;
+        if (live) {
+            const uint8_t* src = slot + q * kCb;
+            if (in_vec) {
+                if constexpr (kCb == 4) cw[0] = *reinterpret_cast<const uint32_t*>(src);
+                else if constexpr (kCb == 8) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(src);
+                    cw[0] = v.x; cw[1] = v.y;
+                } else {
+                    const uint4 v = *reinterpret_cast<const uint4*>(src);
+                    cw[0] = v.x; cw[1] = v.y; cw[2] = v.z; cw[3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < kCb; i++) cw[i >> 2] |= (uint32_t)src[i] << (8 * (i & 3));
+            }
+            norm = __half2float(*reinterpret_cast<const __half*>(slot + kQb));
         }
-        __syncwarp();
+        float x[E];
+#pragma unroll
+        for (int i = 0; i < kCb; i++) {
+            const uint32_t c = (cw[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            x[2 * i] = cent_s[c >> 4];
+            x[2 * i + 1] = cent_s[c & 15];
+        }
+#pragma unroll
+        for (int hr = 1; hr < E; hr <<= 1) {
+#pragma unroll
+            for (int r = 0; r < E; r++) {
+                if ((r & hr) == 0) {
+                    const float a = x[r], c = x[r + hr];
+                    x[r] = __fadd_rn(a, c);
+                    x[r + hr] = __fsub_rn(a, c);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) {
+#pragma unroll
+            for (int r = 0; r < E; r++) {
+                const float o = __shfl_xor_sync(0xffffffffu, x[r], m);
+                x[r] = (q & m) ? __fsub_rn(o, x[r]) : __fadd_rn(x[r], o);
+            }
+        }
+        if (!live) continue;
+#pragma unroll
+        for (int r = 0; r < E; r++) x[r] = __fmul_rn(__fmul_rn(__fmul_rn(x[r], p.scale), sg[r]), norm);
+        const int64_t orow = ((int64_t)p.cu_seqlens[b] + t) * p.out_token_stride + (int64_t)h * hd;
+        const int d0 = q * E;
+        if (p.out_dtype == TQ_F32) {
+            float* out = reinterpret_cast<float*>(p.out[which]) + orow + d0;
+#pragma unroll
+            for (int c = 0; c < E / 4; c++) {
+                if (out_vec && d0 + 4 * c + 4 <= hd) {
+                    reinterpret_cast<float4*>(out)[c] = make_float4(x[4 * c], x[4 * c + 1], x[4 * c + 2], x[4 * c + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        if (d0 + 4 * c + i < hd) out[4 * c + i] = x[4 * c + i];
+                }
+            }
+        } else {
+            uint16_t* out = reinterpret_cast<uint16_t*>(p.out[which]) + orow + d0;
+            const bool bf = p.out_dtype == TQ_BF16;
+#pragma unroll
+            for (int c = 0; c < E / 8; c++) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float lo = x[8 * c + 2 * i], hi = x[8 * c + 2 * i + 1];
+                    if (bf) {
+                        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                        w[i] = *reinterpret_cast<const uint32_t*>(&v);
+                    } else {
+                        const __half2 v = __floats2half2_rn(lo, hi);
+                        w[i] = *reinterpret_cast<const uint32_t*>(&v);
+                    }
+                }
+                if (out_vec && d0 + 8 * c + 8 <= hd) {
+                    reinterpret_cast<uint4*>(out)[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        if (d0 + 8 * c + i < hd) out[8 * c + i] = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
+                }
+            }
+        }
     }
 }
 
@@ -1020,9 +1132,14 @@ int generic_dequant(const void* kv_cache, int64_t num_blocks, int block_size, in
     float bnd[15];
     host_codebook(p.g.padded, 4, p.centroids, bnd);
     const int64_t items = (int64_t)batch * max_pages * kGenPage * num_kv_heads * 2;
-    const int64_t blocks = (items + kGenWarps - 1) / kGenWarps;
+    const int64_t blocks = (items + 4 * kGenWarps - 1) / (4 * kGenWarps);   // four rows per warp and pass
     const unsigned grid = (unsigned)(blocks < 148 * 32 ? (blocks > 0 ? blocks : 1) : 148 * 32);
-    dequant_generic_kernel<<<grid, kGenWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (p.g.padded) {
+        case 64: dequant_rows8_kernel<8><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        case 128: dequant_rows8_kernel<16><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        default: dequant_rows8_kernel<32><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+    }
     TQ_CUDA(cudaGetLastError());
     return TQ_OK;
 }
