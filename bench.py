@@ -72,7 +72,7 @@ def parse():
                          "flags) or by an NCCL all-gather")
     ap.add_argument("--sections", default="all",
                     help="comma list of the extra sections of the config-1 line: mixed, kv_split, strong, short_chunk; all | none")
-    ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4", "sweep"],
+    ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4", "sweep", "head_sizes"],
                     help="config1 (default, the headline): batch 8 x 32k per GPU; config3: 64 mixed lengths sharded by "
                          "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge")
     return ap.parse_args()
@@ -1230,6 +1230,111 @@ def run_sweep(args):
                           "rows": rows}), flush=True)
 
 
+def run_head_sizes(args):
+    """Head sizes 64 and 256 (48- and 144-byte slots; the reference declares them, its decode op rejects
+    them): cache write of 32768 tokens x 8 KV heads, one decode call over batch 8 x 32768 tokens and the
+    bulk dequantization of 8 x 4096 tokens, each against its algorithmic bytes; head size 128 through
+    the same calls beside them.  Parity: the written cache byte for byte and the decode output against
+    the oracle, on the first sequence cut to 2048 tokens.  One GPU's figures; every rank runs the same."""
+    from oracle import tq_oracle
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    rank, world, dev = _setup_dist()
+    peak, peak_src = measured_peak()
+    steps = args.steps
+    T, H, B, L = 32768, 8, 8, 32768
+    rows = []
+    for d, hq in ((64, 16), (256, 16), (128, 32)):
+        attn = TurboQuantPagedAttention(hq, d, 1.0 / math.sqrt(d), H, num_ctas=args.num_ctas)
+        dc = max(d, 64) // 64
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(d)
+        # ---- write ----
+        k = torch.randn(T, H, d, generator=gen, device=dev).to(torch.bfloat16)
+        v = torch.randn(T, H, d, generator=gen, device=dev).to(torch.bfloat16)
+        nb_w = T // PAGE
+        perm = torch.randperm(nb_w, generator=torch.Generator().manual_seed(d)).to(dev)
+        slots = perm.repeat_interleave(PAGE) * PAGE + torch.arange(T, device=dev) % PAGE
+        wcaches = [torch.zeros(kv_cache_shape(nb_w, PAGE, H, d), dtype=torch.uint8, device=dev) for _ in range(4)]
+        st = {"i": 0}
+
+        def write():
+            attn.write(k, v, wcaches[st["i"] % 4], slots)
+            st["i"] += 1
+        for _ in range(3):
+            write()
+        ms_w = _time_steps(write, steps, world, dev)
+        alg_w = 2 * T * H * d * 2 + 2 * T * H * (d // 2 + 2 * dc) + T * 8
+        # parity of the write: the first 2048 tokens, byte for byte
+        n_par = 2048
+        signs = attn.signs(dev).cpu().numpy()
+        want_cache = np.zeros((2, nb_w, PAGE, H, wcaches[0].shape[-1]), np.uint8)
+        tq_oracle.write_kv_cache(want_cache, k[:n_par].float().cpu().numpy(), v[:n_par].float().cpu().numpy(), signs,
+                                 slots[:n_par].cpu().numpy(), d)
+        pages_par = perm[:n_par // PAGE].cpu().numpy()
+        write_equal = bool((wcaches[0][:, pages_par].cpu().numpy() == want_cache[:, pages_par]).all())
+        if not write_equal:
+            raise SystemExit(f"head size {d}: the written cache differs from the oracle's")
+        # ---- dequantization of 8 x 4096 of the written tokens ----
+        Bq, Lq = 8, 4096
+        bt_q = perm.to(torch.int32).view(Bq, Lq // PAGE).contiguous()
+        sl_q = torch.full((Bq,), Lq, dtype=torch.int32, device=dev)
+        cu_q = torch.arange(Bq + 1, dtype=torch.int32, device=dev) * Lq
+
+        def dequant():
+            attn.dequant_cached(wcaches[st["i"] % 4], bt_q, sl_q, cu_q, Bq * Lq)
+            st["i"] += 1
+        for _ in range(3):
+            dequant()
+        ms_q = _time_steps(dequant, steps, world, dev)
+        alg_q = Bq * Lq * H * (d + 4 * dc + 2 * d * 2)
+        del wcaches, k, v
+        # ---- decode: batch 8 x 32768, random codes with unit norms (the time does not depend on the values) ----
+        nb = B * L // PAGE
+        bt = torch.randperm(nb, generator=torch.Generator().manual_seed(d + 1)).view(B, L // PAGE).to(torch.int32).to(dev)
+        sl = torch.full((B,), L, dtype=torch.int32, device=dev)
+        caches = torch.randint(0, 256, (3,) + kv_cache_shape(nb, PAGE, H, d), dtype=torch.uint8, device=dev, generator=gen)
+        caches[..., d // 2:d // 2 + 2 * dc] = torch.tensor([0, 60], dtype=torch.uint8, device=dev).repeat(dc)   # fp16 1.0
+        q = torch.randn(B, hq, d, generator=gen, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+
+        def decode():
+            attn.decode(q, caches[st["i"] % 3], bt, sl, out)
+            st["i"] += 1
+        for _ in range(3):
+            decode()
+        ms_d = _time_steps(decode, steps, world, dev)
+        alg_d = B * L * H * (d + 4 * dc)
+        # parity of the decode: sequence 0 cut to 2048 tokens
+        sl_p = torch.tensor([n_par], dtype=torch.int32, device=dev)
+        out_p = torch.empty(1, hq, d, dtype=torch.float32, device=dev)
+        attn.decode(q[:1], caches[0], bt[:1].contiguous(), sl_p, out_p)
+        torch.cuda.synchronize()
+        pages_d = bt[0, :n_par // PAGE].long()
+        small = caches[0][:, pages_d].cpu().numpy()
+        want = tq_oracle.decode_paged(q[:1].float().cpu().numpy(), small, np.arange(n_par // PAGE, dtype=np.int32)[None],
+                                      np.array([n_par], np.int32), signs, 1.0 / math.sqrt(d))
+        par = oracle_parity(out_p.cpu().numpy(), want, f"head size {d}: sequence 0 cut to {n_par} tokens")
+        assert attn.status(B, dev) == 0
+        del caches
+        torch.cuda.empty_cache()
+
+        def part(ms, alg):
+            return {"ms": ms, "algorithmic_bytes": alg, "achieved_GBps": alg / (ms * 1e-3) / 1e9, "frac": alg / (ms * 1e-3) / 1e9 / peak}
+        rows.append({"head_size": d, "q_heads": hq, "kv_heads": H, "slot_bytes": int(kv_cache_shape(1, PAGE, H, d)[-1]),
+                     "write": dict(part(ms_w, alg_w), tokens=T, equal_to_oracle_first_tokens=n_par),
+                     "decode": dict(part(ms_d, alg_d), batch=B, ctx=L, parity=par),
+                     "dequant": dict(part(ms_q, alg_q), tokens=Bq * Lq)})
+    if rank == 0:
+        r64 = rows[0]
+        print(json.dumps({"metric": "decode_attn_tokens_per_s", "value": world * B / (r64["decode"]["ms"] * 1e-3), "unit": "tokens/s",
+                          "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": r64["decode"]["ms"], "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": "head_sizes: head 64 / 256 / 128 through the same calls; value = one decode call, "
+                                                 "batch 8 x 32768, head size 64, 16 q / 8 kv heads; one layer",
+                                     "l2": "three caches in rotation, each larger than L2"},
+                          "peak": peak, "peak_source": peak_src, "rows": rows}), flush=True)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -1240,6 +1345,8 @@ def main():
         run_config4(args)
     elif args.workload == "sweep":
         run_sweep(args)
+    elif args.workload == "head_sizes":
+        run_head_sizes(args)
     else:
         run_ours(args)
 

@@ -795,7 +795,8 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
     __shared__ float cent_s[16];   // a lookup indexed per lane: shared memory, not the parameter bank
     __shared__ float sg_s[kPd];
     if (threadIdx.x < 16) cent_s[threadIdx.x] = p.centroids[threadIdx.x];
-    for (int j = threadIdx.x; j < kPd; j += kGenWarps * 32) sg_s[j] = j < p.g.head_dim ? p.signs[j] : 0.0f;
+    // sign of element j = q E + r at [r][q]: the eight lanes of a row read eight neighbouring words
+    for (int j = threadIdx.x; j < kPd; j += kGenWarps * 32) sg_s[(j % E) * 8 + j / E] = j < p.g.head_dim ? p.signs[j] : 0.0f;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = lane & 7, rg = lane >> 3;
@@ -807,7 +808,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
     const bool in_vec = ((reinterpret_cast<uintptr_t>(p.kv_cache) | (uintptr_t)p.slab_bytes | (uintptr_t)p.g.slot_bytes) & 15) == 0;
     const bool out_vec = ((reinterpret_cast<uintptr_t>(p.out[0]) | reinterpret_cast<uintptr_t>(p.out[1])) & 15) == 0 &&
                          ((p.out_token_stride * esize) & 15) == 0 && ((hd * esize) & 15) == 0;
-    const float* sg = sg_s + q * E;
+    const float* sg = sg_s + q;
 
     for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < items; base += (int64_t)gridDim.x * kGenWarps * 4) {
         // a group without a row (past the end, past its sequence, an unlisted page) runs the shuffles on zeros
@@ -899,7 +900,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
         }
         if (!live) continue;
 #pragma unroll
-        for (int r = 0; r < E; r++) x[r] = __fmul_rn(__fmul_rn(__fmul_rn(x[r], p.scale), sg[r]), norm);
+        for (int r = 0; r < E; r++) x[r] = __fmul_rn(__fmul_rn(__fmul_rn(x[r], p.scale), sg[8 * r]), norm);
         const int64_t orow = ((int64_t)p.cu_seqlens[b] + t) * p.out_token_stride + (int64_t)h * hd;
         const int d0 = q * E;
         if (p.out_dtype == TQ_F32) {
