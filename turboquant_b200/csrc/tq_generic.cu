@@ -785,18 +785,20 @@ struct GenDequantParams {
 
 static __device__ int32_t g_gen_dequant_skipped = 0;
 
-// Eight lanes own one row and a warp works on four rows at a time.  Lane q holds elements q E ... q E + E - 1
-// (E = padded / 8: the code bytes q E / 2 ... of the slot, one load), so the butterfly stages h < E are
-// register-local and the stages h >= E one shuffle per element, in the same stage order as everywhere else;
-// the row leaves as 16-byte stores when the output rows are 16-byte aligned.
+// Eight lanes own one row and a warp works on four rows at a time.  The row is cut into chunks of 64 elements
+// (32 code bytes); lane q holds elements 8 q ... 8 q + 7 of every chunk, register r = 8 c + i being element
+// 64 c + 8 q + i.  So a chunk's code bytes are one 4-byte load per lane (32 contiguous bytes per row) and its
+// output one 16-byte store per lane (128 contiguous bytes per row); butterfly stages 1, 2, 4 and 64, 128 are
+// register-local and stages 8, 16, 32 one shuffle per element, in the same stage order as everywhere else.
 template <int E>
 __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const __grid_constant__ GenDequantParams p) {
-    constexpr int kPd = 8 * E, kQb = kPd / 2, kCb = E / 2;   // code bytes per lane: 4, 8 or 16
+    constexpr int kPd = 8 * E, kQb = kPd / 2, kChunks = E / 8;
     __shared__ float cent_s[16];   // a lookup indexed per lane: shared memory, not the parameter bank
     __shared__ float sg_s[kPd];
     if (threadIdx.x < 16) cent_s[threadIdx.x] = p.centroids[threadIdx.x];
-    // sign of element j = q E + r at [r][q]: the eight lanes of a row read eight neighbouring words
-    for (int j = threadIdx.x; j < kPd; j += kGenWarps * 32) sg_s[(j % E) * 8 + j / E] = j < p.g.head_dim ? p.signs[j] : 0.0f;
+    // sign of element j = 64 c + 8 q + i at [8 c + i][q]: the eight lanes of a row read eight neighbouring words
+    for (int j = threadIdx.x; j < kPd; j += kGenWarps * 32)
+        sg_s[((j >> 6) * 8 + (j & 7)) * 8 + ((j >> 3) & 7)] = j < p.g.head_dim ? p.signs[j] : 0.0f;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = lane & 7, rg = lane >> 3;
@@ -805,7 +807,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
     const int64_t items = per_seq * p.batch;
     const bool small = items < 0x7fffffff;
     const int esize = p.out_dtype == TQ_F32 ? 4 : 2;
-    const bool in_vec = ((reinterpret_cast<uintptr_t>(p.kv_cache) | (uintptr_t)p.slab_bytes | (uintptr_t)p.g.slot_bytes) & 15) == 0;
+    const bool in_vec = ((reinterpret_cast<uintptr_t>(p.kv_cache) | (uintptr_t)p.slab_bytes | (uintptr_t)p.g.slot_bytes) & 3) == 0;
     const bool out_vec = ((reinterpret_cast<uintptr_t>(p.out[0]) | reinterpret_cast<uintptr_t>(p.out[1])) & 15) == 0 &&
                          ((p.out_token_stride * esize) & 15) == 0 && ((hd * esize) & 15) == 0;
     const float* sg = sg_s + q;
@@ -850,37 +852,37 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
                 slot = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)(page * kGenPage + e) * H + h) * p.g.slot_bytes;
             }
         }
-        // code bytes q E / 2 ... of the slot
-        uint32_t cw[(kCb + 3) / 4];
+        // code bytes 4 q ... 4 q + 3 of every chunk
+        uint32_t cw[kChunks];
 #pragma unroll
-        for (int i = 0; i < (kCb + 3) / 4; i++) cw[i] = 0;
+        for (int c = 0; c < kChunks; c++) cw[c] = 0;
         float norm = 0.0f;
         if (live) {
-            const uint8_t* src = slot + q * kCb;
-            if (in_vec) {
-                if constexpr (kCb == 4) cw[0] = *reinterpret_cast<const uint32_t*>(src);
-                else if constexpr (kCb == 8) {
-                    const uint2 v = *reinterpret_cast<const uint2*>(src);
-                    cw[0] = v.x; cw[1] = v.y;
-                } else {
-                    const uint4 v = *reinterpret_cast<const uint4*>(src);
-                    cw[0] = v.x; cw[1] = v.y; cw[2] = v.z; cw[3] = v.w;
-                }
-            } else {
 #pragma unroll
-                for (int i = 0; i < kCb; i++) cw[i >> 2] |= (uint32_t)src[i] << (8 * (i & 3));
+            for (int c = 0; c < kChunks; c++) {
+                const uint8_t* src = slot + 32 * c + 4 * q;
+                if (in_vec) {
+                    cw[c] = *reinterpret_cast<const uint32_t*>(src);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) cw[c] |= (uint32_t)src[i] << (8 * i);
+                }
             }
             norm = __half2float(*reinterpret_cast<const __half*>(slot + kQb));
         }
         float x[E];
 #pragma unroll
-        for (int i = 0; i < kCb; i++) {
-            const uint32_t c = (cw[i >> 2] >> (8 * (i & 3))) & 0xffu;
-            x[2 * i] = cent_s[c >> 4];
-            x[2 * i + 1] = cent_s[c & 15];
-        }
+        for (int c = 0; c < kChunks; c++) {
 #pragma unroll
-        for (int hr = 1; hr < E; hr <<= 1) {
+            for (int i = 0; i < 4; i++) {
+                const uint32_t code = (cw[c] >> (8 * i)) & 0xffu;
+                x[8 * c + 2 * i] = cent_s[code >> 4];
+                x[8 * c + 2 * i + 1] = cent_s[code & 15];
+            }
+        }
+        // stages 1, 2, 4 (inside a lane's eight), 8, 16, 32 (between the lanes), 64, 128 (between the chunks)
+#pragma unroll
+        for (int hr = 1; hr < 8; hr <<= 1) {
 #pragma unroll
             for (int r = 0; r < E; r++) {
                 if ((r & hr) == 0) {
@@ -898,28 +900,40 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
                 x[r] = (q & m) ? __fsub_rn(o, x[r]) : __fadd_rn(x[r], o);
             }
         }
+#pragma unroll
+        for (int hr = 8; hr < E; hr <<= 1) {
+#pragma unroll
+            for (int r = 0; r < E; r++) {
+                if ((r & hr) == 0) {
+                    const float a = x[r], c = x[r + hr];
+                    x[r] = __fadd_rn(a, c);
+                    x[r + hr] = __fsub_rn(a, c);
+                }
+            }
+        }
         if (!live) continue;
 #pragma unroll
         for (int r = 0; r < E; r++) x[r] = __fmul_rn(__fmul_rn(__fmul_rn(x[r], p.scale), sg[8 * r]), norm);
         const int64_t orow = ((int64_t)p.cu_seqlens[b] + t) * p.out_token_stride + (int64_t)h * hd;
-        const int d0 = q * E;
         if (p.out_dtype == TQ_F32) {
-            float* out = reinterpret_cast<float*>(p.out[which]) + orow + d0;
+            float* out = reinterpret_cast<float*>(p.out[which]) + orow;
 #pragma unroll
             for (int c = 0; c < E / 4; c++) {
-                if (out_vec && d0 + 4 * c + 4 <= hd) {
-                    reinterpret_cast<float4*>(out)[c] = make_float4(x[4 * c], x[4 * c + 1], x[4 * c + 2], x[4 * c + 3]);
+                const int d0 = 64 * (c >> 1) + 8 * q + 4 * (c & 1);   // registers 4 c ... 4 c + 3
+                if (out_vec && d0 + 4 <= hd) {
+                    *reinterpret_cast<float4*>(out + d0) = make_float4(x[4 * c], x[4 * c + 1], x[4 * c + 2], x[4 * c + 3]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; i++)
-                        if (d0 + 4 * c + i < hd) out[4 * c + i] = x[4 * c + i];
+                        if (d0 + i < hd) out[d0 + i] = x[4 * c + i];
                 }
             }
         } else {
-            uint16_t* out = reinterpret_cast<uint16_t*>(p.out[which]) + orow + d0;
+            uint16_t* out = reinterpret_cast<uint16_t*>(p.out[which]) + orow;
             const bool bf = p.out_dtype == TQ_BF16;
 #pragma unroll
-            for (int c = 0; c < E / 8; c++) {
+            for (int c = 0; c < kChunks; c++) {
+                const int d0 = 64 * c + 8 * q;
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
@@ -932,12 +946,12 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
                         w[i] = *reinterpret_cast<const uint32_t*>(&v);
                     }
                 }
-                if (out_vec && d0 + 8 * c + 8 <= hd) {
-                    reinterpret_cast<uint4*>(out)[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                if (out_vec && d0 + 8 <= hd) {
+                    *reinterpret_cast<uint4*>(out + d0) = make_uint4(w[0], w[1], w[2], w[3]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; i++)
-                        if (d0 + 8 * c + i < hd) out[8 * c + i] = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
+                        if (d0 + i < hd) out[d0 + i] = (uint16_t)(w[i >> 1] >> (16 * (i & 1)));
                 }
             }
         }
