@@ -29,6 +29,10 @@ each with its own oracle parity check; with N > 1 also `strong` (the stated batc
 over the GPUs by sequence and by KV head), and `short_chunk` (8 new tokens per sequence over batch
 8 x 32768 cached tokens through the causal wide-tile kernel, against the same tokens as decode
 rows).  `--sections none` leaves them out.
+
+Other lines on request: `--workload config3 | config4 | sweep` (the parity-test shapes, timed) and
+`--workload head_sizes` (cache write, decode and bulk dequantization for head sizes 64 and 256 beside
+128, each against its algorithmic bytes, with oracle parity on a slice).
 """
 from __future__ import annotations
 
@@ -74,7 +78,8 @@ def parse():
                     help="comma list of the extra sections of the config-1 line: mixed, kv_split, strong, short_chunk; all | none")
     ap.add_argument("--workload", default="config1", choices=["config1", "config3", "config4", "sweep", "head_sizes"],
                     help="config1 (default, the headline): batch 8 x 32k per GPU; config3: 64 mixed lengths sharded by "
-                         "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge")
+                         "sequence; config4: one 1M-token sequence, KV axis split over the GPUs, NCCL merge; "
+                         "head_sizes: write / decode / dequantization for head sizes 64 and 256")
     return ap.parse_args()
 
 
