@@ -472,28 +472,29 @@ __global__ void __launch_bounds__(kGenWarps * 32, 4) decode_generic_kernel(const
 }
 
 // ---------------------------------------------------------------------------------------------
-// decode on the tensor cores for the same head sizes: a warp takes whole pages.  Its 32 lanes load
-// the page's code bytes with 16-byte loads (lane = token, half of the row), dequantize them through
-// a byte-keyed table of fp16 centroid pairs into two small shared-memory tiles K^ and V^ ([16 tokens]
-// [PD dims], rows padded by 16 bytes), and the products run as mma.sync.m16n8k16 on ldmatrix
-// fragments: S = K^ Q^T (16 tokens x 8 query columns), O^T += V^^T P (PD dims x 8 columns, V^ read
-// with ldmatrix.trans), P moved into place with movmatrix.  Online softmax in base 2 per page; the
-// K norm is folded into the scores, the V norm into P.  Same grid, workspace and merge as the
-// plain kernel above, which stays as the fallback for caches that are not 16-byte aligned.
+// decode on the tensor cores for the same head sizes: a warp takes whole pages, stages their slots in
+// shared memory with 16-byte asynchronous copies (its own ring of stages, no block-wide barrier in the
+// loop) and dequantizes the codes straight into mma.sync.m16n8k16 fragments.
+//   S = K^ Q^T (16 tokens x 8 query columns): lane (g, tg) reads bytes tg PD/8 ... of the code rows
+//   of tokens g and g + 8; a code byte looked up in a table of fp16 centroid pairs IS one A-fragment
+//   register (two neighbouring contraction slots of one token), so the contraction runs over the dims
+//   in the order the bytes come, and the Q^T fragments are built in that order once per block.
+//   O^T += V^^T P (PD dims x 8 columns): the contraction runs over tokens, so a fragment register
+//   pairs two tokens' values of one dim: lane (g, tg) reads bytes g PD/16 ... of tokens 2tg, 2tg + 1,
+//   2tg + 8, 2tg + 9 and zips the nibbles of a token pair into bytes before the lookup (low nibbles
+//   = odd dims -> accumulator row g, high nibbles = even dims -> row g + 8).
+// The table entry of byte v is {low half: centroid of the low nibble, high half: of the high nibble},
+// sixteen copies side by side (a lane reads column lane % 16).  Online softmax in base 2 per page; the
+// K norm is folded into the scores, the V norm into P (moved into place with movmatrix).  Same grid,
+// workspace and merge as the plain kernel above, which stays as the fallback for caches that are not
+// 16-byte aligned.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t gen_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void gen_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void gen_ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void gen_mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void gen_mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t gen_movmatrix_trans(uint32_t a) {
     uint32_t d;
@@ -504,31 +505,68 @@ __device__ __forceinline__ uint32_t gen_pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
+constexpr int kFragLutCols = 16;
+// table entry of byte j of word w (the table's column of this lane is folded into lut_lane)
+__device__ __forceinline__ uint32_t gen_lookup(uint32_t w, int j, uint32_t lut_lane) {
+    uint32_t r;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(lut_lane + ((w >> (8 * j)) & 0xffu) * (4u * kFragLutCols)));
+    return r;
+}
+// BYTES (4, 8, 16 or 32) of a staged code row into words
+template <int BYTES>
+__device__ __forceinline__ void gen_lds_words(uint32_t addr, uint32_t (&w)[BYTES / 4]) {
+    if constexpr (BYTES == 4) {
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(addr));
+    } else if constexpr (BYTES == 8) {
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr));
+    } else {
+#pragma unroll
+        for (int i = 0; i < BYTES / 16; i++)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(addr + 16 * i));
+    }
+}
+__device__ __forceinline__ float gen_lds_half(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ void gen_cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gen_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void gen_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int PD>
-struct TileShape {
-    static constexpr int kRowBytes = (PD + 8) * 2;             // 16 mod 128: ldmatrix rows hit different banks
-    static constexpr int kTileBytes = 16 * kRowBytes;
-    static constexpr int kWords = PD / 16;                      // code words (4 bytes) per lane and operand
-    static constexpr size_t kSmem = (size_t)kGenMaxGroup * PD * 4 + (size_t)kGenWarps * 2 * kTileBytes;
+struct FragShape {
+    static constexpr int kKBytes = PD / 8, kVBytes = PD / 16;   // code bytes per lane and token, K and V
+    static constexpr int kVWords = kVBytes / 4;
+    static constexpr int kRow = ((PD / 2 + 2 * (PD / 64)) + 15) & ~15;   // staged bytes of a slot: codes + norms, 48 / 80 / 144
+    static constexpr int kChunks = 2 * 16 * kRow / 16;          // 16-byte copies per page and head (K and V): 96 / 160 / 288
+    static constexpr int kStageBytes = 2 * 16 * kRow;
+    static constexpr int kStages = PD == 256 ? 2 : 3;
+    static constexpr size_t kRing = (size_t)kGenWarps * kStages * kStageBytes;
+    static constexpr size_t kCombine = (size_t)kGenWarps * kGenMaxGroup * PD * 4;   // also covers the rotated queries
+    static constexpr size_t kSmem = kRing > kCombine ? kRing : kCombine;
+    static_assert(kChunks % 32 == 0, "a page's copies divide evenly over the lanes");
 };
 
 template <int PD>
-__global__ void __launch_bounds__(kGenWarps * 32, PD == 256 ? 2 : 4) decode_tiles_kernel(const __grid_constant__ GenDecodeParams p) {
-    using T = TileShape<PD>;
+__global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 : 3) decode_frags_kernel(const __grid_constant__ GenDecodeParams p) {
+    using F = FragShape<PD>;
     extern __shared__ __align__(16) uint8_t tsm[];
     __shared__ float m_s[kGenWarps][kGenMaxGroup], l_s[kGenWarps][kGenMaxGroup];
-    __shared__ uint32_t lut_s[256];          // code byte -> (centroid of the even dim, centroid of the odd dim) as half2
-    __shared__ float nk_s[kGenWarps][16], nv_s[kGenWarps][16];
+    __shared__ float cent_s[16];
+    __shared__ __align__(16) uint32_t lut_s[256 * kFragLutCols];
     constexpr int pd = PD;
     const int G = p.group;
-    float* q_s = reinterpret_cast<float*>(tsm);                          // [G][pd] rotated queries
-    uint8_t* tiles = tsm + (size_t)kGenMaxGroup * PD * 4;
-    float* o_s = reinterpret_cast<float*>(tiles);                        // [warps][G][pd], after the loop
+    float* q_s = reinterpret_cast<float*>(tsm);   // [G][pd] rotated queries, before the loop
+    float* o_s = reinterpret_cast<float*>(tsm);   // [warps][G][pd], after the loop
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tg = lane & 3;
     const int split = blockIdx.x, b = blockIdx.y, h = blockIdx.z;
-    for (int v = tid; v < 256; v += blockDim.x) lut_s[v] = gen_pack_half2(p.centroids[v >> 4], p.centroids[v & 15]);
+    if (tid < 16) cent_s[tid] = p.centroids[tid];
 
     // window of this split, in pages
     int64_t len = p.seq_lens[b];
@@ -555,6 +593,12 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 256 ? 2 : 4) decode_tile
                      : 0.0f;
     }
     __syncthreads();
+    for (int v = tid; v < 256; v += blockDim.x) {   // a row of copies per byte value
+        const uint32_t e = gen_pack_half2(cent_s[v & 15], cent_s[v >> 4]);
+        uint4* row = reinterpret_cast<uint4*>(lut_s + v * kFragLutCols);
+#pragma unroll
+        for (int i = 0; i < kFragLutCols / 4; i++) row[i] = make_uint4(e, e, e, e);
+    }
     for (int hh = 1; hh < pd; hh <<= 1) {
         for (int i = tid; i < G * pd / 2; i += blockDim.x) {
             const int gg = i / (pd / 2), idx = i - gg * (pd / 2);
@@ -566,15 +610,17 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 256 ? 2 : 4) decode_tile
         }
         __syncthreads();
     }
-    // B fragments of Q^T: column g of the query tile (zero beyond the group), k-steps of 16 dims
+    // B fragments of Q^T: column g of the query tile (zero beyond the group).  Step s contracts over the dims of
+    // this lane's code bytes 2s and 2s + 1 (dims 4 (tg PD/16 + s) ...), each byte's odd dim in the lower slot.
     uint32_t qf[PD / 8];
 #pragma unroll
     for (int s = 0; s < PD / 16; s++) {
-        const float* row = q_s + g * pd + 16 * s + 2 * tg;
+        const float* row = q_s + g * pd + tg * (PD / 4) + 4 * s;
         const bool on = g < G;
-        qf[2 * s] = on ? gen_pack_half2(row[0] * p.scale, row[1] * p.scale) : 0u;
-        qf[2 * s + 1] = on ? gen_pack_half2(row[8] * p.scale, row[9] * p.scale) : 0u;
+        qf[2 * s] = on ? gen_pack_half2(row[1] * p.scale, row[0] * p.scale) : 0u;
+        qf[2 * s + 1] = on ? gen_pack_half2(row[3] * p.scale, row[2] * p.scale) : 0u;
     }
+    __syncthreads();   // the queries are in registers: their shared memory becomes the warps' stage rings
 
     float o_acc[PD / 16][4];
 #pragma unroll
@@ -582,88 +628,117 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 256 ? 2 : 4) decode_tile
 #pragma unroll
         for (int j = 0; j < 4; j++) o_acc[i][j] = 0.0f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
-    const int tk = lane >> 1, hf = lane & 1;                       // loads: lane = (token, half of its code bytes)
-    const uint32_t tile_k = gen_smem_u32(tiles) + (uint32_t)warp * 2 * T::kTileBytes, tile_v = tile_k + T::kTileBytes;
-    const uint32_t st_k = tile_k + tk * T::kRowBytes + hf * PD, st_v = tile_v + tk * T::kRowBytes + hf * PD;
-    const uint32_t lm_k = tile_k + (lane & 15) * T::kRowBytes + (lane >> 4) * 16;
-    const uint32_t lm_v = tile_v + ((lane & 7) + 8 * (lane >> 4)) * T::kRowBytes + ((lane >> 3) & 1) * 16;
+    const uint32_t lut_lane = gen_smem_u32(lut_s) + 4u * (lane & (kFragLutCols - 1));
+    const uint32_t ring = gen_smem_u32(tsm) + (uint32_t)warp * F::kStages * F::kStageBytes;
+    const size_t tok_stride = (size_t)p.num_kv_heads * p.g.slot_bytes;
+    const int my_pages = pg1 > pg0 + warp ? (pg1 - pg0 - warp + kGenWarps - 1) / kGenWarps : 0;
+    auto page_at = [&](int i) -> int64_t { return i < my_pages ? (int64_t)p.page_indices[tbl + pg0 + warp + i * kGenWarps] : -1; };
+    uint32_t staged = 0;   // bit s: stage s holds a page (its id was inside the cache)
+    // copies of one page into a stage: chunk c = (K / V, token, 16-byte piece); always one commit group
+    auto issue = [&](int stage, int64_t page) {
+        if ((uint64_t)page < (uint64_t)p.num_blocks) {
+            const uint8_t* base = p.kv_cache + (size_t)(page * kGenPage) * tok_stride + (size_t)h * p.g.slot_bytes;
+            const uint32_t dst0 = ring + stage * F::kStageBytes;
+#pragma unroll
+            for (int i = 0; i < F::kChunks / 32; i++) {
+                const int c = lane + 32 * i;
+                const int which = c / (F::kChunks / 2), rem = c % (F::kChunks / 2);
+                const int tok = rem / (F::kRow / 16), piece = rem % (F::kRow / 16);
+                gen_cp_async16(dst0 + which * 16 * F::kRow + tok * F::kRow + piece * 16,
+                               base + (which ? p.slab_bytes : 0) + tok * tok_stride + piece * 16);
+            }
+            staged |= 1u << stage;
+        } else {
+            staged &= ~(1u << stage);
+        }
+        gen_cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < F::kStages - 1; i++) issue(i, page_at(i));
+    int64_t page_issue = page_at(F::kStages - 1);
+    int st = 0, st_issue = F::kStages - 1;
     bool bad_page = false;
-    for (int pg = pg0 + warp; pg < pg1; pg += kGenWarps) {
-        const int64_t page = p.page_indices[tbl + pg];
-        if ((uint64_t)page >= (uint64_t)p.num_blocks) {  // never form an address from it
-            bad_page = true;
-            continue;
-        }
-        // ---- load and dequantize the page's codes into the two tiles ---------------------------------
-        const uint8_t* ks = p.kv_cache + ((size_t)(page * kGenPage + tk) * p.num_kv_heads + h) * p.g.slot_bytes;
-        const uint8_t* vs = ks + p.slab_bytes;
-        uint4 kc[PD / 64], vc[PD / 64];
+    for (int it = 0; it < my_pages; it++) {
+        const int64_t page_after = page_at(it + F::kStages);   // its id arrives while this page is worked on
+        issue(st_issue, page_issue);                            // into the stage the previous iteration has left
+        gen_cp_async_wait<F::kStages - 1>();
+        __syncwarp();
+        if (!((staged >> st) & 1u)) {
+            bad_page = true;   // no address was formed from the id
+        } else {
+            const uint32_t sk = ring + st * F::kStageBytes, sv = sk + 16 * F::kRow;
+            // ---- S = K^ Q^T -------------------------------------------------------------------------------
+            uint32_t ka[F::kKBytes / 4], kb[F::kKBytes / 4];
+            gen_lds_words<F::kKBytes>(sk + g * F::kRow + tg * F::kKBytes, ka);
+            gen_lds_words<F::kKBytes>(sk + (g + 8) * F::kRow + tg * F::kKBytes, kb);
+            float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s_acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int i = 0; i < PD / 64; i++) {
-            kc[i] = reinterpret_cast<const uint4*>(ks + hf * (PD / 4))[i];
-            vc[i] = reinterpret_cast<const uint4*>(vs + hf * (PD / 4))[i];
-        }
-        if (hf == 0) {
-            nk_s[warp][tk] = __half2float(*reinterpret_cast<const __half*>(ks + p.g.qbytes));
-            nv_s[warp][tk] = __half2float(*reinterpret_cast<const __half*>(vs + p.g.qbytes));
-        }
+            for (int s = 0; s < PD / 16; s++) {
+                const uint32_t wa = ka[s >> 1], wb = kb[s >> 1];
+                const int j = 2 * (s & 1);
+                const uint32_t a0 = gen_lookup(wa, j, lut_lane), a2 = gen_lookup(wa, j + 1, lut_lane);
+                const uint32_t a1 = gen_lookup(wb, j, lut_lane), a3 = gen_lookup(wb, j + 1, lut_lane);
+                gen_mma16816((s & 1) ? s_acc2 : s_acc, a0, a1, a2, a3, qf[2 * s], qf[2 * s + 1]);
+            }
 #pragma unroll
-        for (int i = 0; i < PD / 64; i++) {
-            const uint32_t kw[4] = {kc[i].x, kc[i].y, kc[i].z, kc[i].w}, vw[4] = {vc[i].x, vc[i].y, vc[i].z, vc[i].w};
+            for (int i = 0; i < 4; i++) s_acc[i] += s_acc2[i];
+            // ---- online softmax (base 2); rows g and g + 8 are tokens, columns 2tg and 2tg + 1 query heads --
+            const int64_t t0 = (int64_t)(pg0 + warp + it * kGenWarps) * kGenPage;
+            const bool va = t0 + g >= begin && t0 + g < len, vb = t0 + g + 8 >= begin && t0 + g + 8 < len;
+            const float kfa = va ? gen_lds_half(sk + g * F::kRow + PD / 2) * p.score_scale : 0.0f;
+            const float kfb = vb ? gen_lds_half(sk + (g + 8) * F::kRow + PD / 2) * p.score_scale : 0.0f;
+            const float vfa = va ? gen_lds_half(sv + g * F::kRow + PD / 2) : 0.0f;
+            const float vfb = vb ? gen_lds_half(sv + (g + 8) * F::kRow + PD / 2) : 0.0f;
+            const float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
+            const float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
+            float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
 #pragma unroll
-            for (int w = 0; w < 4; w++) {
-                uint32_t a[4], c[4];
+            for (int o = 4; o < 32; o <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+            }
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+            const bool raised = n0 > m0 || n1 > m1;   // the same in every lane
+            const float c0 = n0 > m0 ? gen_exp2(m0 - n0) : 1.0f, c1 = n1 > m1 ? gen_exp2(m1 - n1) : 1.0f;
+            m0 = n0;
+            m1 = n1;
+            const float e0 = va ? gen_exp2(x0 - m0) : 0.0f, e1 = va ? gen_exp2(x1 - m1) : 0.0f;
+            const float e2 = vb ? gen_exp2(x2 - m0) : 0.0f, e3 = vb ? gen_exp2(x3 - m1) : 0.0f;
+            l0 = __fmaf_rn(l0, c0, e0 + e2);
+            l1 = __fmaf_rn(l1, c1, e1 + e3);
+            const uint32_t pb0 = gen_movmatrix_trans(gen_pack_half2(e0 * vfa, e1 * vfa));
+            const uint32_t pb1 = gen_movmatrix_trans(gen_pack_half2(e2 * vfb, e3 * vfb));
+            if (raised) {
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    a[j] = lut_s[(kw[w] >> (8 * j)) & 0xFF];
-                    c[j] = lut_s[(vw[w] >> (8 * j)) & 0xFF];
+                for (int mt = 0; mt < PD / 16; mt++) {
+                    o_acc[mt][0] *= c0; o_acc[mt][1] *= c1; o_acc[mt][2] *= c0; o_acc[mt][3] *= c1;
                 }
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_k + (4 * i + w) * 16), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_v + (4 * i + w) * 16), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]) : "memory");
+            }
+            // ---- O^T += V^^T P: zip the nibbles of a token pair into bytes, look the pairs up ----------------
+            uint32_t v0[F::kVWords], v1[F::kVWords], v2[F::kVWords], v3[F::kVWords];
+            const uint32_t vrow = sv + (2 * tg) * F::kRow + g * F::kVBytes;
+            gen_lds_words<F::kVBytes>(vrow, v0);
+            gen_lds_words<F::kVBytes>(vrow + F::kRow, v1);
+            gen_lds_words<F::kVBytes>(vrow + 8 * F::kRow, v2);
+            gen_lds_words<F::kVBytes>(vrow + 9 * F::kRow, v3);
+#pragma unroll
+            for (int w = 0; w < F::kVWords; w++) {
+                const uint32_t lo01 = (v0[w] & 0x0F0F0F0Fu) | ((v1[w] << 4) & 0xF0F0F0F0u);
+                const uint32_t hi01 = ((v0[w] >> 4) & 0x0F0F0F0Fu) | (v1[w] & 0xF0F0F0F0u);
+                const uint32_t lo23 = (v2[w] & 0x0F0F0F0Fu) | ((v3[w] << 4) & 0xF0F0F0F0u);
+                const uint32_t hi23 = ((v2[w] >> 4) & 0x0F0F0F0Fu) | (v3[w] & 0xF0F0F0F0u);
+#pragma unroll
+                for (int j = 0; j < 4; j++)   // rows: g <- odd dim, g + 8 <- even dim of this lane's code byte 4w + j
+                    gen_mma16816(o_acc[4 * w + j], gen_lookup(lo01, j, lut_lane), gen_lookup(hi01, j, lut_lane),
+                                 gen_lookup(lo23, j, lut_lane), gen_lookup(hi23, j, lut_lane), pb0, pb1);
             }
         }
-        __syncwarp();
-        // ---- S = K^ Q^T ----------------------------------------------------------------------------------
-        float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int s = 0; s < PD / 16; s++) {
-            uint32_t a[4];
-            gen_ldmatrix_x4(lm_k + s * 32, a);
-            gen_mma16816(s_acc, a, qf[2 * s], qf[2 * s + 1]);
-        }
-        // ---- online softmax (base 2); rows g and g + 8 are tokens, columns 2tg and 2tg + 1 query heads -----
-        const int64_t t0 = (int64_t)pg * kGenPage;
-        const bool va = t0 + g >= begin && t0 + g < len, vb = t0 + g + 8 >= begin && t0 + g + 8 < len;
-        const float kfa = va ? nk_s[warp][g] * p.score_scale : 0.0f, kfb = vb ? nk_s[warp][g + 8] * p.score_scale : 0.0f;
-        const float vfa = va ? nv_s[warp][g] : 0.0f, vfb = vb ? nv_s[warp][g + 8] : 0.0f;
-        const float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
-        const float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
-        float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
-        }
-        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        const float c0 = n0 > m0 ? gen_exp2(m0 - n0) : 1.0f, c1 = n1 > m1 ? gen_exp2(m1 - n1) : 1.0f;
-        m0 = n0;
-        m1 = n1;
-        const float e0 = va ? gen_exp2(x0 - m0) : 0.0f, e1 = va ? gen_exp2(x1 - m1) : 0.0f;
-        const float e2 = vb ? gen_exp2(x2 - m0) : 0.0f, e3 = vb ? gen_exp2(x3 - m1) : 0.0f;
-        l0 = __fmaf_rn(l0, c0, e0 + e2);
-        l1 = __fmaf_rn(l1, c1, e1 + e3);
-        const uint32_t pb0 = gen_movmatrix_trans(gen_pack_half2(e0 * vfa, e1 * vfa));
-        const uint32_t pb1 = gen_movmatrix_trans(gen_pack_half2(e2 * vfb, e3 * vfb));
-        // ---- O^T += V^^T P ------------------------------------------------------------------------------------
-#pragma unroll
-        for (int mt = 0; mt < PD / 16; mt++) {
-            uint32_t a[4];
-            gen_ldmatrix_x4_trans(lm_v + mt * 32, a);
-            o_acc[mt][0] *= c0; o_acc[mt][1] *= c1; o_acc[mt][2] *= c0; o_acc[mt][3] *= c1;
-            gen_mma16816(o_acc[mt], a, pb0, pb1);
-        }
-        __syncwarp();   // the tiles are rewritten by the next page
+        __syncwarp();   // every lane has read the stage before the next iteration copies into it
+        page_issue = page_after;
+        st_issue = st;
+        st = st + 1 == F::kStages ? 0 : st + 1;
     }
+    gen_cp_async_wait<0>();
     if (bad_page && lane == 0) atomicExch(&p.header[0], kGenStatusBadPage);
     // this warp's sums over its token lanes, then everything to shared memory for the block's combine
 #pragma unroll
@@ -671,21 +746,21 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 256 ? 2 : 4) decode_tile
         l0 += __shfl_xor_sync(0xffffffffu, l0, o);
         l1 += __shfl_xor_sync(0xffffffffu, l1, o);
     }
-    __syncthreads();   // every warp has left its tiles: the region becomes o_s
+    __syncthreads();   // every warp has left its ring: the region becomes o_s
     if (g == 0) {
         if (2 * tg < G) { m_s[warp][2 * tg] = m0; l_s[warp][2 * tg] = l0; }
         if (2 * tg + 1 < G) { m_s[warp][2 * tg + 1] = m1; l_s[warp][2 * tg + 1] = l1; }
     }
 #pragma unroll
     for (int mt = 0; mt < PD / 16; mt++) {
-        const int d0 = 16 * mt + g;
+        const int d_even = 2 * (g * (PD / 16) + mt);   // accumulator rows g / g + 8 hold the odd / even dim of byte g PD/16 + mt
         if (2 * tg < G) {
-            o_s[(warp * G + 2 * tg) * pd + d0] = o_acc[mt][0];
-            o_s[(warp * G + 2 * tg) * pd + d0 + 8] = o_acc[mt][2];
+            o_s[(warp * G + 2 * tg) * pd + d_even + 1] = o_acc[mt][0];
+            o_s[(warp * G + 2 * tg) * pd + d_even] = o_acc[mt][2];
         }
         if (2 * tg + 1 < G) {
-            o_s[(warp * G + 2 * tg + 1) * pd + d0] = o_acc[mt][1];
-            o_s[(warp * G + 2 * tg + 1) * pd + d0 + 8] = o_acc[mt][3];
+            o_s[(warp * G + 2 * tg + 1) * pd + d_even + 1] = o_acc[mt][1];
+            o_s[(warp * G + 2 * tg + 1) * pd + d_even] = o_acc[mt][3];
         }
     }
     __syncthreads();
@@ -1006,16 +1081,19 @@ int generic_write(void* kv_cache, int64_t num_blocks, int block_size, int num_kv
     return TQ_OK;
 }
 
-static int generic_splits(int batch, int num_kv_heads, int num_ctas) {
+// blocks of the decode kernel an SM holds at a time (registers): the grid is sized to one wave of them
+static int generic_blocks_per_sm(int padded) { return padded == 64 ? 6 : padded == 128 ? 4 : 3; }
+
+static int generic_splits(int batch, int num_kv_heads, int num_ctas, int padded) {
     int ctas = num_ctas;
     if (ctas <= 0 && device_sm_count(&ctas) != TQ_OK) ctas = 148;
-    int s = (4 * ctas) / (batch * num_kv_heads > 0 ? batch * num_kv_heads : 1);
+    int s = (generic_blocks_per_sm(padded) * ctas) / (batch * num_kv_heads > 0 ? batch * num_kv_heads : 1);
     return s < 1 ? 1 : (s > 64 ? 64 : s);
 }
 
 size_t generic_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim, int num_ctas) {
     const int pd = make_geom(head_dim, 0).padded;
-    const size_t rows = (size_t)batch * generic_splits(batch, num_kv_heads, num_ctas) * num_q_heads;
+    const size_t rows = (size_t)batch * generic_splits(batch, num_kv_heads, num_ctas, pd) * num_q_heads;
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
     return 256 + up(rows * sizeof(float)) + up(rows * pd * sizeof(float));
 }
@@ -1039,7 +1117,7 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
                generic_workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim, num_ctas));
     GenDecodeParams p{};
     p.g = make_geom(head_dim, slot_bytes);
-    p.splits = generic_splits(batch, num_kv_heads, num_ctas);
+    p.splits = generic_splits(batch, num_kv_heads, num_ctas, p.g.padded);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     const size_t rows = (size_t)batch * p.splits * num_q_heads;
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
@@ -1081,17 +1159,17 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
     // the tensor-core kernel reads the codes with 16-byte loads; anything else keeps the plain one
     const bool aligned = slot_bytes % 16 == 0 && ((uintptr_t)kv_cache % 16) == 0 && p.slab_bytes % 16 == 0;
     if (aligned) {
-        static bool tiles_configured[64] = {};
-        if (dev < 0 || dev >= 64 || !tiles_configured[dev]) {
-            TQ_CUDA(cudaFuncSetAttribute(decode_tiles_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileShape<64>::kSmem));
-            TQ_CUDA(cudaFuncSetAttribute(decode_tiles_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileShape<128>::kSmem));
-            TQ_CUDA(cudaFuncSetAttribute(decode_tiles_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileShape<256>::kSmem));
-            if (dev >= 0 && dev < 64) tiles_configured[dev] = true;
+        static bool frags_configured[64] = {};
+        if (dev < 0 || dev >= 64 || !frags_configured[dev]) {
+            TQ_CUDA(cudaFuncSetAttribute(decode_frags_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FragShape<64>::kSmem));
+            TQ_CUDA(cudaFuncSetAttribute(decode_frags_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FragShape<128>::kSmem));
+            TQ_CUDA(cudaFuncSetAttribute(decode_frags_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FragShape<256>::kSmem));
+            if (dev >= 0 && dev < 64) frags_configured[dev] = true;
         }
         switch (p.g.padded) {
-            case 64: decode_tiles_kernel<64><<<grid, kGenWarps * 32, TileShape<64>::kSmem, s>>>(p); break;
-            case 128: decode_tiles_kernel<128><<<grid, kGenWarps * 32, TileShape<128>::kSmem, s>>>(p); break;
-            default: decode_tiles_kernel<256><<<grid, kGenWarps * 32, TileShape<256>::kSmem, s>>>(p); break;
+            case 64: decode_frags_kernel<64><<<grid, kGenWarps * 32, FragShape<64>::kSmem, s>>>(p); break;
+            case 128: decode_frags_kernel<128><<<grid, kGenWarps * 32, FragShape<128>::kSmem, s>>>(p); break;
+            default: decode_frags_kernel<256><<<grid, kGenWarps * 32, FragShape<256>::kSmem, s>>>(p); break;
         }
     } else {
         switch (p.g.qbytes / 32) {
