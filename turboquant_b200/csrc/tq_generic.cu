@@ -509,7 +509,9 @@ constexpr int kFragLutCols = 16;
 // table entry of byte j of word w (the table's column of this lane is folded into lut_lane)
 __device__ __forceinline__ uint32_t gen_lookup(uint32_t w, int j, uint32_t lut_lane) {
     uint32_t r;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(lut_lane + ((w >> (8 * j)) & 0xffu) * (4u * kFragLutCols)));
+    uint32_t v;
+    asm("prmt.b32 %0, %1, 0, %2;" : "=r"(v) : "r"(w), "r"(0x4440u | (uint32_t)j));   // byte j of w
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(v * (4u * kFragLutCols) + lut_lane));
     return r;
 }
 // BYTES (4, 8, 16 or 32) of a staged code row into words
@@ -634,18 +636,27 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
     const int my_pages = pg1 > pg0 + warp ? (pg1 - pg0 - warp + kGenWarps - 1) / kGenWarps : 0;
     auto page_at = [&](int i) -> int64_t { return i < my_pages ? (int64_t)p.page_indices[tbl + pg0 + warp + i * kGenWarps] : -1; };
     uint32_t staged = 0;   // bit s: stage s holds a page (its id was inside the cache)
-    // copies of one page into a stage: chunk c = (K / V, token, 16-byte piece); always one commit group
+    // copies of one page into a stage: the 16-byte pieces of the 16 K rows, then of the 16 V rows, dealt over
+    // the lanes; source and destination offsets of this lane's pieces are fixed
+    constexpr int kPieces = 16 * F::kRow / 16, kRounds = (kPieces + 31) / 32;
+    uint32_t src_off[kRounds], dst_off[kRounds];
+#pragma unroll
+    for (int i = 0; i < kRounds; i++) {
+        const int c = lane + 32 * i, tok = c / (F::kRow / 16), piece = c % (F::kRow / 16);
+        src_off[i] = (uint32_t)(tok * tok_stride) + piece * 16;
+        dst_off[i] = tok * F::kRow + piece * 16;
+    }
     auto issue = [&](int stage, int64_t page) {
         if ((uint64_t)page < (uint64_t)p.num_blocks) {
-            const uint8_t* base = p.kv_cache + (size_t)(page * kGenPage) * tok_stride + (size_t)h * p.g.slot_bytes;
-            const uint32_t dst0 = ring + stage * F::kStageBytes;
+            const uint8_t* base_k = p.kv_cache + (size_t)(page * kGenPage) * tok_stride + (size_t)h * p.g.slot_bytes;
+            const uint8_t* base_v = base_k + p.slab_bytes;
+            const uint32_t dst_k = ring + stage * F::kStageBytes, dst_v = dst_k + 16 * F::kRow;
 #pragma unroll
-            for (int i = 0; i < F::kChunks / 32; i++) {
-                const int c = lane + 32 * i;
-                const int which = c / (F::kChunks / 2), rem = c % (F::kChunks / 2);
-                const int tok = rem / (F::kRow / 16), piece = rem % (F::kRow / 16);
-                gen_cp_async16(dst0 + which * 16 * F::kRow + tok * F::kRow + piece * 16,
-                               base + (which ? p.slab_bytes : 0) + tok * tok_stride + piece * 16);
+            for (int i = 0; i < kRounds; i++) {
+                if (kPieces % 32 == 0 || i + 1 < kRounds || lane + 32 * i < kPieces) {
+                    gen_cp_async16(dst_k + dst_off[i], base_k + src_off[i]);
+                    gen_cp_async16(dst_v + dst_off[i], base_v + src_off[i]);
+                }
             }
             staged |= 1u << stage;
         } else {
@@ -683,37 +694,45 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
 #pragma unroll
             for (int i = 0; i < 4; i++) s_acc[i] += s_acc2[i];
             // ---- online softmax (base 2); rows g and g + 8 are tokens, columns 2tg and 2tg + 1 query heads --
+            // The window starts on a page boundary, so only the last page of a sequence can hold tokens outside it:
+            // their norms are zeroed (whatever the unwritten slots contain) and their scores biased to -inf.  Row 0 of
+            // every page is inside, so every column's maximum is finite from the first page on.
+            float kfa = gen_lds_half(sk + g * F::kRow + PD / 2) * p.score_scale, kfb = gen_lds_half(sk + (g + 8) * F::kRow + PD / 2) * p.score_scale;
+            float vfa = gen_lds_half(sv + g * F::kRow + PD / 2), vfb = gen_lds_half(sv + (g + 8) * F::kRow + PD / 2);
+            float bias_a = 0.0f, bias_b = 0.0f;
             const int64_t t0 = (int64_t)(pg0 + warp + it * kGenWarps) * kGenPage;
-            const bool va = t0 + g >= begin && t0 + g < len, vb = t0 + g + 8 >= begin && t0 + g + 8 < len;
-            const float kfa = va ? gen_lds_half(sk + g * F::kRow + PD / 2) * p.score_scale : 0.0f;
-            const float kfb = vb ? gen_lds_half(sk + (g + 8) * F::kRow + PD / 2) * p.score_scale : 0.0f;
-            const float vfa = va ? gen_lds_half(sv + g * F::kRow + PD / 2) : 0.0f;
-            const float vfb = vb ? gen_lds_half(sv + (g + 8) * F::kRow + PD / 2) : 0.0f;
-            const float x0 = va ? s_acc[0] * kfa : -INFINITY, x1 = va ? s_acc[1] * kfa : -INFINITY;
-            const float x2 = vb ? s_acc[2] * kfb : -INFINITY, x3 = vb ? s_acc[3] * kfb : -INFINITY;
-            float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
-#pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+            if (t0 + kGenPage > len) {
+                if (t0 + g >= len) { kfa = 0.0f; vfa = 0.0f; bias_a = -INFINITY; }
+                if (t0 + g + 8 >= len) { kfb = 0.0f; vfb = 0.0f; bias_b = -INFINITY; }
             }
-            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-            const bool raised = n0 > m0 || n1 > m1;   // the same in every lane
-            const float c0 = n0 > m0 ? gen_exp2(m0 - n0) : 1.0f, c1 = n1 > m1 ? gen_exp2(m1 - n1) : 1.0f;
-            m0 = n0;
-            m1 = n1;
-            const float e0 = va ? gen_exp2(x0 - m0) : 0.0f, e1 = va ? gen_exp2(x1 - m1) : 0.0f;
-            const float e2 = vb ? gen_exp2(x2 - m0) : 0.0f, e3 = vb ? gen_exp2(x3 - m1) : 0.0f;
-            l0 = __fmaf_rn(l0, c0, e0 + e2);
-            l1 = __fmaf_rn(l1, c1, e1 + e3);
-            const uint32_t pb0 = gen_movmatrix_trans(gen_pack_half2(e0 * vfa, e1 * vfa));
-            const uint32_t pb1 = gen_movmatrix_trans(gen_pack_half2(e2 * vfb, e3 * vfb));
-            if (raised) {
+            const float x0 = __fmaf_rn(s_acc[0], kfa, bias_a), x1 = __fmaf_rn(s_acc[1], kfa, bias_a);
+            const float x2 = __fmaf_rn(s_acc[2], kfb, bias_b), x3 = __fmaf_rn(s_acc[3], kfb, bias_b);
+            // The running maximum of a column is raised only when a score of the page exceeds it by more than 2^6
+            // (the weights stay within fp16): one vote decides, and only then is the page's maximum reduced across
+            // the lanes and the accumulators rescaled.
+            float mx0 = fmaxf(x0, x2), mx1 = fmaxf(x1, x3);
+            if (__any_sync(0xffffffffu, mx0 > m0 + 6.0f || mx1 > m1 + 6.0f)) {
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+                }
+                const bool r0 = mx0 > m0 + 6.0f, r1 = mx1 > m1 + 6.0f;
+                const float c0 = r0 ? gen_exp2(m0 - mx0) : 1.0f, c1 = r1 ? gen_exp2(m1 - mx1) : 1.0f;
+                if (r0) m0 = mx0;
+                if (r1) m1 = mx1;
+                l0 *= c0;
+                l1 *= c1;
 #pragma unroll
                 for (int mt = 0; mt < PD / 16; mt++) {
                     o_acc[mt][0] *= c0; o_acc[mt][1] *= c1; o_acc[mt][2] *= c0; o_acc[mt][3] *= c1;
                 }
             }
+            const float e0 = gen_exp2(x0 - m0), e1 = gen_exp2(x1 - m1), e2 = gen_exp2(x2 - m0), e3 = gen_exp2(x3 - m1);
+            l0 += e0 + e2;
+            l1 += e1 + e3;
+            const uint32_t pb0 = gen_movmatrix_trans(gen_pack_half2(e0 * vfa, e1 * vfa));
+            const uint32_t pb1 = gen_movmatrix_trans(gen_pack_half2(e2 * vfb, e3 * vfb));
             // ---- O^T += V^^T P: zip the nibbles of a token pair into bytes, look the pairs up ----------------
             uint32_t v0[F::kVWords], v1[F::kVWords], v2[F::kVWords], v3[F::kVWords];
             const uint32_t vrow = sv + (2 * tg) * F::kRow + g * F::kVBytes;
