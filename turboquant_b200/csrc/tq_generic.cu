@@ -1100,8 +1100,9 @@ int generic_write(void* kv_cache, int64_t num_blocks, int block_size, int num_kv
     return TQ_OK;
 }
 
-// blocks of the decode kernel an SM holds at a time (registers): the grid is sized to one wave of them
-static int generic_blocks_per_sm(int padded) { return padded == 64 ? 6 : padded == 128 ? 4 : 3; }
+// blocks per SM the decode grid is sized to: one wave of resident blocks for head size 64 (six fit; more blocks
+// cost more prologues than they balance: 93 us against 83), two waves for 256 (three fit; 221 us against 229)
+static int generic_blocks_per_sm(int padded) { return padded == 64 ? 6 : padded == 128 ? 4 : 6; }
 
 static int generic_splits(int batch, int num_kv_heads, int num_ctas, int padded) {
     int ctas = num_ctas;
