@@ -30,7 +30,7 @@ def test_kernel_config_presets():
     assert kc.stages * kc.stage_bytes + 65536 < 227 * 1024                     # three stages + the table
     assert compute_kernel_config(ModelConfig(64, 8, 128)).stages == 3          # 8 query heads per KV head
     assert compute_kernel_config(ModelConfig(16, 4, 128)).pages_per_stage == 4  # a TP shard with 4 KV heads
-    for name in ("gemma-2-9b", "gemma-2-2b", "qwen3-0.6b"):                    # head sizes 256 and 64: plain kernels
+    for name in ("gemma-2-9b", "gemma-2-2b", "qwen3-0.6b"):                    # head sizes 256 and 64: second-tier kernels
         kc2 = compute_kernel_config(MODEL_PRESETS[name])
         assert kc2.supported and not kc2.tuned
     assert all(compute_kernel_config(m).supported for m in MODEL_PRESETS.values())

@@ -42,7 +42,7 @@ class KernelConfig:
     stage_bytes: int
     supported: bool = True
     reason: str = ""
-    tuned: bool = True    # False: the plain kernels for head sizes other than 128 / 96
+    tuned: bool = True    # False: the second-tier kernels for head sizes other than 128 / 96
 
     @property
     def threads_per_block(self) -> int:
@@ -58,8 +58,11 @@ def compute_kernel_config(model: ModelConfig, max_threads: int = 1024) -> Kernel
     h, g = model.num_kv_heads, model.gqa_ratio
     if model.head_dim not in (128, 96):
         if 32 < model.head_dim <= 256 and 1 <= g <= 8:
-            # plain kernels: four warps per (split, sequence, KV head), no staging ring
-            return KernelConfig(4, 1, 0, 0, True, "plain kernels (head sizes other than 128 / 96 are not tuned)", False)
+            # four warps per (split, sequence, KV head), each with its own ring of one-page stages
+            pd = 64 if model.head_dim <= 64 else 128 if model.head_dim <= 128 else 256
+            row = (pd // 2 + 2 * (pd // 64) + 15) & ~15
+            return KernelConfig(4, 1, 2 if pd == 256 else 3, 2 * PAGE_TOKENS * row, True,
+                                "second-tier kernels (head sizes other than 128 / 96: 25 - 40 % of the HBM peak)", False)
         return KernelConfig(CONSUMER_WARPS, 0, 0, 0, False,
                             f"head_dim {model.head_dim} with GQA ratio {g}: head sizes 33..256 and ratios 1..8 are implemented")
     if h not in (1, 2, 4, 8, 16):
