@@ -255,7 +255,7 @@ int tq_decode_paged_exchange(const void* q, int q_dtype, int batch, int queries_
                              float* out_lse, int num_ctas, void* stream);
 
 /* As tq_decode_paged, but stops before the inverse rotation: writes the merged, normalized,
- * still-rotated output (fp32 [batch][num_q_heads][128], the padded width) and its base-2 LSE, restricted to
+ * still-rotated output (fp32 [batch][num_q_heads][padded width: 128, or 64 / 256 for those head sizes]) and its base-2 LSE, restricted to
  * tokens [kv_begin, kv_end) of every sequence (kv_end < 0: to the end).  This is the per-GPU
  * half of a KV-axis split across GPUs; the halves are exchanged and finished with
  * tq_merge_rotated.  No reference counterpart (the reference has no multi-GPU path); it
@@ -270,9 +270,10 @@ int tq_decode_paged_partial(const void* q, int q_dtype, int batch, int num_q_hea
                             void* stream);
 
 /* Log-sum-exp merge of num_parts rotated partial outputs, then inverse rotation:
- *   partial_o    fp32 [num_parts][rows][128]        (normalized, rotated domain: always 128 wide)
+ *   partial_o    fp32 [num_parts][rows][padded]     (normalized, rotated domain: the padded width,
+ *                                                     128 for head_dim 128 / 96, else 64, 128 or 256)
  *   partial_lse2 fp32 [num_parts][rows]             (base-2 LSE; -inf marks an empty part)
- *   out          [rows][head_dim] out_dtype (head_dim 128 or 96); out_lse optional natural-log LSE [rows]
+ *   out          [rows][head_dim] out_dtype (head_dim 33 ... 256); out_lse optional natural-log LSE [rows]
  * Replaces: SplitKVCombineKernel (csrc/include/flashinfer_decode_turboquant_combine.cuh:18-79)
  * plus the inverse rotation at flashinfer_decode_turboquant_v5_tc.cuh:709-765. */
 int tq_merge_rotated(const float* partial_o, const float* partial_lse2, int num_parts,

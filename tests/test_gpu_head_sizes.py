@@ -170,3 +170,41 @@ def test_dequant_16_bit_outputs_are_the_rounded_fp32_ones(golden, d, hkv, dtype)
     torch.cuda.synchronize()
     assert torch.equal(k16, k32.to(dtype)) and torch.equal(v16, v32.to(dtype))
     assert k32.abs().max().item() > 0
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 16, 8), (256, 8, 4)])
+def test_kv_windows_partials_and_merge(oracle, golden, d, hq, hkv):
+    """The KV-axis split contract for these head sizes: rotated partials over token windows, merged by
+    tq_merge_rotated, equal the one-call decode and the oracle; with a CSR page table."""
+    lens = [1500, 90]
+    case = synthetic.decode_case(seed=500 + d, seq_lens=lens, dtype=torch.bfloat16, heads=(hq, hkv), head_dim=d)
+    signs = _signs(golden, d)
+    scale = 1.0 / math.sqrt(d)
+    attn = TurboQuantPagedAttention(hq, d, scale, hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    q, sl = case.q.to(DEV), case.seq_lens.to(DEV)
+    pages = [(n + 15) // 16 for n in lens]
+    indptr = torch.tensor([0, pages[0], pages[0] + pages[1]], dtype=torch.int32, device=DEV)
+    indices = torch.cat([case.block_table[b, :p] for b, p in enumerate(pages)]).to(torch.int32).to(DEV)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(2, hq, hkv, d, 0), dtype=torch.uint8, device=DEV)
+    full = torch.empty(2, hq, d, dtype=torch.float32, device=DEV)
+    _cabi.decode_paged(q, cache, indices, sl, signs.to(DEV), scale, ws, full, page_indptr=indptr)
+    windows = [(0, 512), (512, 1024), (1024, -1), (2048, -1)]          # the last one is empty
+    po = torch.empty(len(windows), 2, hq, d, dtype=torch.float32, device=DEV)   # d is the padded width here
+    pl = torch.empty(len(windows), 2, hq, dtype=torch.float32, device=DEV)
+    for i, (a, b) in enumerate(windows):
+        _cabi.decode_paged_partial(q, cache, indices, sl, signs.to(DEV), scale, ws, po[i], pl[i], kv_begin=a, kv_end=b,
+                                   page_indptr=indptr)
+    assert torch.isneginf(pl[3]).all() and torch.isneginf(pl[1, 1]).all()
+    out = torch.empty(2, hq, d, dtype=torch.float32, device=DEV)
+    lse = torch.empty(2, hq, dtype=torch.float32, device=DEV)
+    _cabi.merge_rotated(po, pl, signs.to(DEV), out, lse)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 0
+    np.testing.assert_allclose(out.cpu().numpy(), full.cpu().numpy(), atol=3e-4, rtol=1e-3)
+    want_cache = cache.cpu().numpy()
+    want, want_lse = oracle.decode_paged(case.q.float().numpy(), want_cache, case.block_table.numpy(), case.seq_lens.numpy(),
+                                         signs.numpy(), scale, return_lse=True)
+    assert_attention_close(out.cpu().numpy(), want, f"head size {d}: merged windows")
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=2e-3)

@@ -458,7 +458,8 @@ def decode_paged_partial(q, kv_cache, page_indices, seq_lens, signs, sm_scale: f
 
 
 def merge_rotated(partial_o, partial_lse2, signs, out, out_lse=None):
-    """partial_o fp32 [parts, rows..., 128], partial_lse2 fp32 [parts, rows...] -> out [rows..., 128]."""
+    """partial_o fp32 [parts, rows..., padded], partial_lse2 fp32 [parts, rows...] -> out [rows..., head_dim]
+    (padded = 128 for head sizes 128 / 96, else 64, 128 or 256)."""
     _cuda(partial_o, "partial_o")
     _cuda(partial_lse2, "partial_lse2")
     if partial_o.dtype != torch.float32 or partial_lse2.dtype != torch.float32:

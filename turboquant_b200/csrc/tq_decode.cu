@@ -838,6 +838,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
 
 int device_sm_count(int* out);
 size_t generic_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim, int num_ctas);
+int generic_merge_rotated(const float* partial_o, const float* partial_lse2, int num_parts, int64_t rows, int head_dim,
+                          const float* signs, void* out, int out_dtype, float* out_lse, void* stream);
 int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads, int head_dim,
                    const void* kv_cache, int64_t num_blocks, int block_size, int slot_bytes, const int32_t* page_indices,
                    const int32_t* page_indptr, int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
@@ -1199,10 +1201,10 @@ extern "C" int tq_merge_rotated(const float* partial_o, const float* partial_lse
     using namespace tq;
     if (rows == 0) return TQ_OK;
     TQ_REQUIRE(partial_o && partial_lse2 && signs && out, TQ_ERR_INVALID, "null pointer");
-    TQ_REQUIRE(head_dim == kHeadDim || head_dim == 96, TQ_ERR_UNSUPPORTED,
-               "merge supports head_dim 128 and 96 (padded to 128), got %d", head_dim);
     TQ_REQUIRE(num_parts >= 1 && rows > 0, TQ_ERR_INVALID, "num_parts and rows must be positive");
     TQ_REQUIRE(out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad out_dtype");
+    if (head_dim != kHeadDim && head_dim != 96)   // partials of the other head sizes are [..][padded] wide
+        return generic_merge_rotated(partial_o, partial_lse2, num_parts, rows, head_dim, signs, out, out_dtype, out_lse, stream);
     MergeParams m{};
     m.partial_o = partial_o;
     m.partial_lse = partial_lse2;

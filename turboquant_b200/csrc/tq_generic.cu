@@ -818,8 +818,8 @@ struct GenMergeParams {
 __global__ void __launch_bounds__(kGenMaxDim) merge_generic_kernel(const __grid_constant__ GenMergeParams p) {
     __shared__ float buf[kGenMaxDim];
     const int d = threadIdx.x, pd = p.g.padded;
-    const int64_t b = blockIdx.x;
-    const int hq = blockIdx.y;
+    const int64_t b = blockIdx.x / p.num_q_heads;
+    const int hq = (int)(blockIdx.x - b * p.num_q_heads);
     float mm = -INFINITY;
     for (int s = 0; s < p.splits; s++) mm = fmaxf(mm, p.partial_lse[(b * p.splits + s) * p.num_q_heads + hq]);
     float wsum = 0.0f, acc = 0.0f;
@@ -1211,7 +1211,29 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
     m.emit_rotated = emit_rotated;
     m.g = p.g;
     m.scale = p.scale;
-    merge_generic_kernel<<<dim3((unsigned)batch, (unsigned)num_q_heads), p.g.padded, 0, s>>>(m);
+    merge_generic_kernel<<<(unsigned)batch * (unsigned)num_q_heads, p.g.padded, 0, s>>>(m);
+    TQ_CUDA(cudaGetLastError());
+    return TQ_OK;
+}
+
+// partials of several KV windows, [parts][rows][padded] rotated + base-2 LSEs [parts][rows] -> out [rows][head_dim]
+int generic_merge_rotated(const float* partial_o, const float* partial_lse2, int num_parts, int64_t rows, int head_dim,
+                          const float* signs, void* out, int out_dtype, float* out_lse, void* stream) {
+    TQ_REQUIRE(head_dim > 32 && head_dim <= kGenMaxDim, TQ_ERR_UNSUPPORTED, "head_dim must be 33..%d, got %d", kGenMaxDim, head_dim);
+    TQ_REQUIRE(rows < (int64_t)1 << 31, TQ_ERR_UNSUPPORTED, "too many rows for one launch");
+    GenMergeParams m{};
+    m.partial_o = partial_o;
+    m.partial_lse = partial_lse2;
+    m.signs = signs;
+    m.out = out;
+    m.out_lse = out_lse;
+    m.num_q_heads = (int)rows;   // one "sequence" whose parts are the windows: row (part, r) at part * rows + r
+    m.splits = num_parts;
+    m.out_dtype = out_dtype;
+    m.emit_rotated = 0;
+    m.g = make_geom(head_dim, 0);
+    m.scale = (float)(1.0 / std::sqrt((double)m.g.padded));
+    merge_generic_kernel<<<(unsigned)rows, m.g.padded, 0, static_cast<cudaStream_t>(stream)>>>(m);
     TQ_CUDA(cudaGetLastError());
     return TQ_OK;
 }
