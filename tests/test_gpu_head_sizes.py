@@ -208,3 +208,26 @@ def test_kv_windows_partials_and_merge(oracle, golden, d, hq, hkv):
                                          signs.numpy(), scale, return_lse=True)
     assert_attention_close(out.cpu().numpy(), want, f"head size {d}: merged windows")
     np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=2e-3)
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(96, 32, 8), (64, 16, 8), (80, 8, 2)])
+def test_kv_split_helper_sizes_partials_by_the_padded_head(monkeypatch, d, hq, hkv):
+    """parallel.kv_split_decode with a one-rank group (the collective replaced by a copy): the rotated partial
+    it allocates must be as wide as the padded head, and partial + merge must equal the plain decode."""
+    import torch.distributed as dist
+    from turboquant_b200 import parallel
+    monkeypatch.setattr(dist, "get_world_size", lambda group=None: 1)
+    monkeypatch.setattr(dist, "all_gather_into_tensor", lambda out, inp, group=None: out.copy_(inp))
+    lens = [700, 33]
+    case = synthetic.decode_case(seed=600 + d, seq_lens=lens, dtype=torch.float16, heads=(hq, hkv), head_dim=d)
+    attn = TurboQuantPagedAttention(hq, d, 1.0 / math.sqrt(d), hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    q, bt, sl = case.q.to(DEV), case.block_table.to(DEV), case.seq_lens.to(DEV)
+    want = torch.empty(len(lens), hq, d, dtype=torch.float32, device=DEV)
+    attn.decode(q, cache, bt, sl, want)
+    guard = torch.full((3, len(lens), hq, d), 7.0, dtype=torch.float32, device=DEV)   # neighbours of the output
+    parallel.kv_split_decode(attn, q, cache, bt, sl, guard[1])
+    torch.cuda.synchronize()
+    assert (guard[0] == 7.0).all() and (guard[2] == 7.0).all()
+    np.testing.assert_allclose(guard[1].cpu().numpy(), want.cpu().numpy(), atol=3e-4, rtol=1e-3)

@@ -67,7 +67,8 @@ def kv_split_decode(attn, query, kv_cache_local, block_table_local, seq_lens_loc
     that row's KV (streamed once for all of them)."""
     from . import _cabi
     dev = query.device
-    part_o = torch.empty(tuple(query.shape), dtype=torch.float32, device=dev)
+    # rotated partials are as wide as the padded head (96 -> 128, 80 -> 128, 192 -> 256)
+    part_o = torch.empty(tuple(query.shape[:-1]) + (attn.padded_dim,), dtype=torch.float32, device=dev)
     part_l = torch.empty(tuple(query.shape[:-1]), dtype=torch.float32, device=dev)
     if query.dim() == 4:
         _cabi.decode_paged_multi(query, attn._as_bytes(kv_cache_local), block_table_local, seq_lens_local,
