@@ -163,3 +163,23 @@ def test_exchange_wait_for_a_silent_peer_runs_out(oracle, golden):
     assert int(ws[:4].view(torch.int32).item()) == 0          # the decode itself was fine
     flags_silent = silent[64:72].view(torch.int32).cpu().numpy()
     assert flags_silent[0] == 1 and flags_silent[1] == 0      # rank 0 did push into the peer's buffer
+
+
+def test_rotated_partial_buffers_must_have_the_padded_width():
+    """A rotated partial is as wide as the padded head (96 -> 128): a head_size-wide buffer would be written
+    past its end, so the binding refuses it before the launch."""
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    d, hq, hkv = 96, 8, 2
+    attn = TurboQuantPagedAttention(hq, d, 1.0 / math.sqrt(d), hkv)
+    cache = torch.zeros(kv_cache_shape(4, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    q = torch.zeros(1, hq, d, dtype=torch.float16, device=DEV)
+    bt = torch.zeros(1, 4, dtype=torch.int32, device=DEV)
+    sl = torch.full((1,), 20, dtype=torch.int32, device=DEV)
+    ws = attn.workspace(1, DEV)
+    lse = torch.empty(1, hq, dtype=torch.float32, device=DEV)
+    with pytest.raises(_cabi.TurboQuantError, match="padded head size"):
+        _cabi.decode_paged_partial(q, cache, bt, sl, attn.signs(DEV), attn.scale, ws,
+                                   torch.empty(1, hq, d, dtype=torch.float32, device=DEV), lse)
+    _cabi.decode_paged_partial(q, cache, bt, sl, attn.signs(DEV), attn.scale, ws,
+                               torch.empty(1, hq, 128, dtype=torch.float32, device=DEV), lse)
+    torch.cuda.synchronize()

@@ -285,6 +285,14 @@ def decode_paged(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, wo
     return out
 
 
+def _check_rotated_partial(out_rot, head_dim: int):
+    """A rotated-domain partial is as wide as the padded head: 128 for head sizes 65 ... 128, else 64 or 256."""
+    padded = 64 if head_dim <= 64 else 128 if head_dim <= 128 else 256
+    if out_rot.dtype != torch.float32 or out_rot.shape[-1] != padded or not out_rot.is_contiguous():
+        raise TurboQuantError(f"a rotated partial must be contiguous fp32 with a last dim of {padded} "
+                              f"(the padded head size), got {tuple(out_rot.shape)} {out_rot.dtype}")
+
+
 def decode_paged_multi(q, kv_cache, page_indices, seq_lens, signs, sm_scale: float, workspace, out,
                        page_indptr=None, max_pages: int | None = None, out_lse=None, num_ctas: int = 0,
                        kv_begin: int = 0, kv_end: int = -1, rotated_partial: bool = False):
@@ -301,6 +309,8 @@ def decode_paged_multi(q, kv_cache, page_indices, seq_lens, signs, sm_scale: flo
     _decode_args(q.view(q.shape[0], -1, q.shape[3]), kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs)
     B, NQ, Hq, D = q.shape
     _, nb, bs, H, ebs = kv_cache.shape
+    if rotated_partial:
+        _check_rotated_partial(out, D)
     _check(lib().tq_decode_paged_multi(
         _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(NQ), ctypes.c_int(Hq),
         ctypes.c_int(H), ctypes.c_int(D), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(ebs),
@@ -447,6 +457,7 @@ def decode_paged_partial(q, kv_cache, page_indices, seq_lens, signs, sm_scale: f
     _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, signs)
     B, Hq, D = q.shape
     _, nb, bs, H, ebs = kv_cache.shape
+    _check_rotated_partial(out_rot, D)
     _check(lib().tq_decode_paged_partial(
         _ptr(q), ctypes.c_int(dtype_code(q.dtype)), ctypes.c_int(B), ctypes.c_int(Hq), ctypes.c_int(H),
         ctypes.c_int(D), _ptr(kv_cache), ctypes.c_int64(nb), ctypes.c_int(bs), ctypes.c_int(ebs),
