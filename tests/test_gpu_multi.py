@@ -124,3 +124,30 @@ def test_exchange_protocol_single_rank(oracle, golden):
         torch.cuda.synchronize()
         assert torch.equal(out, want)
     assert ex.status() == 0
+
+
+def test_exchange_head96_one_rank():
+    """The same protocol for a padded head (96 -> 128): the exchanged partials are 128 wide, the output 96."""
+    import math
+    from turboquant_b200 import _cabi, synthetic
+    from turboquant_b200.paged_attention import TurboQuantPagedAttention, kv_cache_shape
+    from turboquant_b200.parallel import KVSplitExchange
+    from tests.gpu_util import DEV
+    lens, d, hq, hkv, nq = [300, 1500], 96, 32, 8, 2
+    B = len(lens)
+    case = synthetic.decode_case(seed=32, seq_lens=lens, dtype=torch.float16, heads=(hq, hkv), head_dim=d)
+    attn = TurboQuantPagedAttention(hq, d, 1 / math.sqrt(d), hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    q = torch.randn(B, nq, hq, d, generator=torch.Generator().manual_seed(4)).to(torch.float16).to(DEV)
+    bt, sl = case.block_table.to(DEV), case.seq_lens.to(DEV)
+    want = attn.decode_shared(q, cache, bt, sl)
+    buf = torch.zeros(_cabi.exchange_bytes(B * nq * hq, 1), dtype=torch.uint8, device=DEV)
+    ex = KVSplitExchange(attn, B, nq, DEV, buffers=[buf])
+    guard = torch.full((3,) + tuple(want.shape), 7.0, dtype=want.dtype, device=DEV)
+    for step in range(2):
+        ex.decode(q, cache, bt, sl, guard[1])
+        torch.cuda.synchronize()
+        assert ex.status() == 0
+        assert torch.equal(guard[1], want)
+    assert (guard[0] == 7.0).all() and (guard[2] == 7.0).all()
