@@ -231,3 +231,28 @@ def test_kv_split_helper_sizes_partials_by_the_padded_head(monkeypatch, d, hq, h
     torch.cuda.synchronize()
     assert (guard[0] == 7.0).all() and (guard[2] == 7.0).all()
     np.testing.assert_allclose(guard[1].cpu().numpy(), want.cpu().numpy(), atol=3e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("d,hkv", [(64, 2), (256, 1), (80, 3)])
+def test_dequant_of_a_large_job(oracle, golden, d, hkv):
+    """From 16384 token positions on, a lane group of the dequantizer walks all rows of its token instead of
+    taking one row: same values, bit for bit, including the second sequence's ragged end."""
+    lens = [9000, 7001]
+    case = synthetic.decode_case(seed=700 + d, seq_lens=lens, dtype=torch.float16, heads=(hkv, hkv), head_dim=d)
+    assert len(lens) * case.block_table.shape[1] * 16 >= 16384
+    signs = _signs(golden, d)
+    attn = TurboQuantPagedAttention(hkv, d, 1.0 / math.sqrt(d), hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+    k_out, v_out = attn.dequant_cached(cache, case.block_table.to(DEV), case.seq_lens.to(DEV), cu, sum(lens), dtype=torch.float32)
+    torch.cuda.synchronize()
+    cache_np = cache.cpu().numpy()
+    at = 0
+    for b, n in enumerate(lens):
+        t = np.arange(n)
+        pages = case.block_table.numpy()[b, t // 16]
+        for which, got_t in ((0, k_out), (1, v_out)):
+            want_rows = oracle.dequant_cache_rows(cache_np[which, pages, t % 16], signs.numpy(), d)
+            np.testing.assert_array_equal(got_t[at:at + n].cpu().numpy(), want_rows)
+        at += n

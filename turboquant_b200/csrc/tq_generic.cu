@@ -860,7 +860,7 @@ __global__ void __launch_bounds__(kGenMaxDim) merge_generic_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------------------------
-// bulk dequantization: eight lanes per (sequence, token, head, K / V)
+// bulk dequantization: eight lanes per (sequence, token), walking its heads' K and V rows
 // ---------------------------------------------------------------------------------------------
 struct GenDequantParams {
     const uint8_t* kv_cache;
@@ -872,6 +872,7 @@ struct GenDequantParams {
     void* out[2];
     int64_t slab_bytes, num_blocks, out_token_stride;
     int batch, max_pages, num_kv_heads, out_dtype;
+    int walk;   // rows a lane group takes of its token: all 2 H (large jobs) or 1 (small ones: more groups in flight)
     GenGeom g;
     float scale;
     float centroids[16];
@@ -897,7 +898,8 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = lane & 7, rg = lane >> 3;
     const int H = p.num_kv_heads, hd = p.g.head_dim;
-    const int64_t per_seq = (int64_t)p.max_pages * kGenPage * H * 2;
+    const int parts = 2 * H / p.walk;                                   // lane groups per token
+    const int64_t per_seq = (int64_t)p.max_pages * kGenPage * parts;   // items of a sequence's table
     const int64_t items = per_seq * p.batch;
     const bool small = items < 0x7fffffff;
     const int esize = p.out_dtype == TQ_F32 ? 4 : 2;
@@ -905,64 +907,74 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
     const bool out_vec = ((reinterpret_cast<uintptr_t>(p.out[0]) | reinterpret_cast<uintptr_t>(p.out[1])) & 15) == 0 &&
                          ((p.out_token_stride * esize) & 15) == 0 && ((hd * esize) & 15) == 0;
     const float* sg = sg_s + q;
+    // code bytes 4 q ... 4 q + 3 of every chunk of a slot, and its norm
+    auto fetch = [&](const uint8_t* slot, uint32_t (&cw)[kChunks], float& norm) {
+#pragma unroll
+        for (int c = 0; c < kChunks; c++) {
+            const uint8_t* src = slot + 32 * c + 4 * q;
+            if (in_vec) {
+                cw[c] = *reinterpret_cast<const uint32_t*>(src);
+            } else {
+                cw[c] = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) cw[c] |= (uint32_t)src[i] << (8 * i);
+            }
+        }
+        norm = __half2float(*reinterpret_cast<const __half*>(slot + kQb));
+    };
 
+    // a group of eight lanes takes one token and walks `walk` of its 2 H rows (K heads, then V heads): the token's
+    // page lookup and output row are worked out once, and the next row's codes are fetched while this one is worked on
     for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < items; base += (int64_t)gridDim.x * kGenWarps * 4) {
-        // a group without a row (past the end, past its sequence, an unlisted page) runs the shuffles on zeros
+        // a group without a token (past the end, past its sequence, an unlisted page) runs the shuffles on zeros
         const int64_t it = base + rg;
         bool live = it < items;
-        int b = 0, which = 0, h = 0;
+        int b = 0, r0 = 0;
         int64_t t = 0;
         if (live) {
             if (small) {
-                const uint32_t i32 = (uint32_t)it, ps = (uint32_t)per_seq;
-                const uint32_t bb = i32 / ps;
-                uint32_t rem = i32 - bb * ps;
-                which = (int)(rem & 1);
-                rem >>= 1;
-                const uint32_t tt = rem / (uint32_t)H;
-                h = (int)(rem - tt * (uint32_t)H);
+                const uint32_t bb = (uint32_t)it / (uint32_t)per_seq;
+                const uint32_t rem = (uint32_t)it - bb * (uint32_t)per_seq, tt = rem / (uint32_t)parts;
                 b = (int)bb;
                 t = tt;
+                r0 = (int)(rem - tt * (uint32_t)parts) * p.walk;
             } else {
                 b = (int)(it / per_seq);
-                int64_t rem = it - (int64_t)b * per_seq;
-                which = (int)(rem & 1);
-                rem >>= 1;
-                t = rem / H;
-                h = (int)(rem - t * H);
+                const int64_t rem = it - (int64_t)b * per_seq;
+                t = rem / parts;
+                r0 = (int)(rem - t * parts) * p.walk;
             }
             live = t < p.seq_lens[b];
         }
-        const uint8_t* slot = nullptr;
+        const uint8_t* slot0 = nullptr;
         if (live) {
             const int pg = (int)(t / kGenPage), e = (int)(t % kGenPage);
             const int64_t tbl = p.page_indptr ? (int64_t)p.page_indptr[b] : (int64_t)b * p.max_pages;
             const bool listed = !p.page_indptr || tbl + pg < (int64_t)p.page_indptr[b + 1];
             const int64_t page = listed ? (int64_t)p.page_indices[tbl + pg] : -1;
             if ((uint64_t)page >= (uint64_t)p.num_blocks) {
-                if (q == 0 && h == 0 && which == 0 && e == 0) atomicAdd(&g_gen_dequant_skipped, 1);
+                if (q == 0 && e == 0 && r0 == 0) atomicAdd(&g_gen_dequant_skipped, 1);
                 live = false;
             } else {
-                slot = p.kv_cache + (size_t)which * p.slab_bytes + ((size_t)(page * kGenPage + e) * H + h) * p.g.slot_bytes;
+                slot0 = p.kv_cache + (size_t)(page * kGenPage + e) * H * p.g.slot_bytes;
             }
         }
-        // code bytes 4 q ... 4 q + 3 of every chunk
+        if (!__any_sync(0xffffffffu, live)) continue;
+        const int64_t orow0 = live ? ((int64_t)p.cu_seqlens[b] + t) * p.out_token_stride : 0;
+        uint32_t cw_next[kChunks];
+#pragma unroll
+        for (int c = 0; c < kChunks; c++) cw_next[c] = 0;
+        float norm_next = 0.0f;
+        if (live) fetch(slot0 + (r0 >= H ? (size_t)p.slab_bytes : 0) + (size_t)(r0 >= H ? r0 - H : r0) * p.g.slot_bytes, cw_next, norm_next);
+        for (int r = r0; r < r0 + p.walk; r++) {
+        const int which = r >= H ? 1 : 0, h = r - which * H;
         uint32_t cw[kChunks];
 #pragma unroll
-        for (int c = 0; c < kChunks; c++) cw[c] = 0;
-        float norm = 0.0f;
-        if (live) {
-#pragma unroll
-            for (int c = 0; c < kChunks; c++) {
-                const uint8_t* src = slot + 32 * c + 4 * q;
-                if (in_vec) {
-                    cw[c] = *reinterpret_cast<const uint32_t*>(src);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) cw[c] |= (uint32_t)src[i] << (8 * i);
-                }
-            }
-            norm = __half2float(*reinterpret_cast<const __half*>(slot + kQb));
+        for (int c = 0; c < kChunks; c++) cw[c] = cw_next[c];
+        const float norm = norm_next;
+        if (live && r + 1 < r0 + p.walk) {
+            const int wn = r + 1 >= H ? 1 : 0, hn = r + 1 - wn * H;
+            fetch(slot0 + (size_t)wn * p.slab_bytes + (size_t)hn * p.g.slot_bytes, cw_next, norm_next);
         }
         float x[E];
 #pragma unroll
@@ -978,37 +990,37 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
 #pragma unroll
         for (int hr = 1; hr < 8; hr <<= 1) {
 #pragma unroll
-            for (int r = 0; r < E; r++) {
-                if ((r & hr) == 0) {
-                    const float a = x[r], c = x[r + hr];
-                    x[r] = __fadd_rn(a, c);
-                    x[r + hr] = __fsub_rn(a, c);
+            for (int k = 0; k < E; k++) {
+                if ((k & hr) == 0) {
+                    const float a = x[k], c = x[k + hr];
+                    x[k] = __fadd_rn(a, c);
+                    x[k + hr] = __fsub_rn(a, c);
                 }
             }
         }
 #pragma unroll
         for (int m = 1; m < 8; m <<= 1) {
 #pragma unroll
-            for (int r = 0; r < E; r++) {
-                const float o = __shfl_xor_sync(0xffffffffu, x[r], m);
-                x[r] = (q & m) ? __fsub_rn(o, x[r]) : __fadd_rn(x[r], o);
+            for (int k = 0; k < E; k++) {
+                const float o = __shfl_xor_sync(0xffffffffu, x[k], m);
+                x[k] = (q & m) ? __fsub_rn(o, x[k]) : __fadd_rn(x[k], o);
             }
         }
 #pragma unroll
         for (int hr = 8; hr < E; hr <<= 1) {
 #pragma unroll
-            for (int r = 0; r < E; r++) {
-                if ((r & hr) == 0) {
-                    const float a = x[r], c = x[r + hr];
-                    x[r] = __fadd_rn(a, c);
-                    x[r + hr] = __fsub_rn(a, c);
+            for (int k = 0; k < E; k++) {
+                if ((k & hr) == 0) {
+                    const float a = x[k], c = x[k + hr];
+                    x[k] = __fadd_rn(a, c);
+                    x[k + hr] = __fsub_rn(a, c);
                 }
             }
         }
         if (!live) continue;
 #pragma unroll
-        for (int r = 0; r < E; r++) x[r] = __fmul_rn(__fmul_rn(__fmul_rn(x[r], p.scale), sg[8 * r]), norm);
-        const int64_t orow = ((int64_t)p.cu_seqlens[b] + t) * p.out_token_stride + (int64_t)h * hd;
+        for (int i = 0; i < E; i++) x[i] = __fmul_rn(__fmul_rn(__fmul_rn(x[i], p.scale), sg[8 * i]), norm);
+        const int64_t orow = orow0 + (int64_t)h * hd;
         if (p.out_dtype == TQ_F32) {
             float* out = reinterpret_cast<float*>(p.out[which]) + orow;
 #pragma unroll
@@ -1049,6 +1061,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
                 }
             }
         }
+        }   // rows of the token
     }
 }
 
@@ -1266,8 +1279,11 @@ int generic_dequant(const void* kv_cache, int64_t num_blocks, int block_size, in
     p.scale = (float)(1.0 / std::sqrt((double)p.g.padded));
     float bnd[15];
     host_codebook(p.g.padded, 4, p.centroids, bnd);
-    const int64_t items = (int64_t)batch * max_pages * kGenPage * num_kv_heads * 2;
-    const int64_t blocks = (items + 4 * kGenWarps - 1) / (4 * kGenWarps);   // four rows per warp and pass
+    // large jobs: a lane group walks all rows of its token; small ones: a row per group, so that the few tokens
+    // there are spread over many warps
+    p.walk = (int64_t)batch * max_pages * kGenPage >= 16384 ? 2 * num_kv_heads : 1;
+    const int64_t items = (int64_t)batch * max_pages * kGenPage * (2 * num_kv_heads / p.walk);
+    const int64_t blocks = (items + 4 * kGenWarps - 1) / (4 * kGenWarps);   // four lane groups per warp and pass
     const unsigned grid = (unsigned)(blocks < 148 * 32 ? (blocks > 0 ? blocks : 1) : 148 * 32);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (p.g.padded) {
