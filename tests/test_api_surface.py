@@ -105,6 +105,29 @@ def test_vllm_plugin_registers_custom_backend():
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
 
 
+def test_backend_step_facts_and_causal_kernel_geometries():
+    """Host logic of the vLLM backend: the step's row classes from the metadata's CPU copies (both dense-row
+    totals: with and without the short rows), and which geometries fuse short chunks."""
+    pytest.importorskip("vllm")
+    code = ("import sys, types; sys.path.insert(0, %r)\n"
+            "import torch\n"
+            "from turboquant_b200.vllm_backend_fused import step_shape, causal_chunk_supported\n"
+            "cached, chunk = [500, 3, 37, 1200, 0, 64], [1, 6, 3, 12, 2, 8]\n"
+            "qsl = torch.tensor([0, 1, 7, 10, 22, 24, 32], dtype=torch.int32)\n"
+            "seq = torch.tensor([c + q for c, q in zip(cached, chunk)], dtype=torch.int32)\n"
+            "st = step_shape(types.SimpleNamespace(query_start_loc_cpu=qsl, num_reqs=6, seq_lens_cpu=seq))\n"
+            "assert st['any_cached'] and st['num_decode_rows'] == 1 and st['num_short_rows'] == 3\n"
+            "assert st['dense_rows'] == 1212 + 2 and st['max_prefill_seq'] == 1212\n"
+            "assert st['dense_rows_with_short'] == 1214 + 9 + 40 + 72 and st['max_prefill_seq_with_short'] == 1212\n"
+            "assert causal_chunk_supported(32, 8, 128) and causal_chunk_supported(24, 8, 96)\n"
+            "assert not causal_chunk_supported(64, 8, 128)      # 8 x 8 query columns\n"
+            "assert not causal_chunk_supported(16, 8, 64)       # head size without the kernel\n"
+            "assert not causal_chunk_supported(8, 1, 128)       # one KV head\n"
+            "print('ok')\n") % str(ROOT)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd="/tmp", timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
 _RANK_SCRIPT = r"""
 import math, os, sys
 sys.path.insert(0, %(root)r)

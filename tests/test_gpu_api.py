@@ -138,23 +138,27 @@ def test_vllm_backend_impl_write_and_decode(oracle, golden):
     assert_attention_close(out.float().cpu().numpy().reshape(4, 32, 128), want, "vLLM impl decode")
 
 
-def _backend_step(oracle, golden, cached, chunk, with_builder_facts):
+def _backend_step(oracle, golden, cached, chunk, with_builder_facts, heads=(32, 8), d=128):
     """One forward of the vLLM backend on a step with the given cached / new token counts per
     sequence, checked against plain torch attention: rows with one new token and cached context are
     decode rows, rows with up to eight new tokens and cached context are short rows (for both, every
     key, the new ones included, is read from the quantized cache); all other rows attend their
     dequantized cached tokens followed by the chunk's fresh K/V."""
     pytest.importorskip("vllm")
-    from turboquant_b200.vllm_backend_fused import TurboQuantBackend, TurboQuantFusedImpl, step_shape
+    from turboquant_b200.vllm_backend_fused import (TurboQuantBackend, TurboQuantFusedImpl, causal_chunk_supported,
+                                                    step_shape)
+    hq, hkv = heads
+    grp, scale = hq // hkv, 1.0 / math.sqrt(d)
+    fuse_short = causal_chunk_supported(hq, hkv, d)    # else rows of 2 ... 8 new tokens go the dense way
     try:
-        impl = TurboQuantFusedImpl(32, 128, SCALE, 8, None, None, "fp8")
+        impl = TurboQuantFusedImpl(hq, d, scale, hkv, None, None, "fp8")
         from vllm.vllm_flash_attn import flash_attn_varlen_func  # noqa: F401
     except Exception as e:
         pytest.skip(f"vLLM attention pieces not usable here: {type(e).__name__}: {e}")
     B = len(cached)
     total = [c + q for c, q in zip(cached, chunk)]
-    case = synthetic.decode_case(seed=83 + B + sum(chunk), seq_lens=total, dtype=torch.bfloat16)
-    shape = TurboQuantBackend.get_kv_cache_shape(case.num_blocks, 16, 8, 128, "fp8")
+    case = synthetic.decode_case(seed=83 + B + sum(chunk), seq_lens=total, dtype=torch.bfloat16, heads=heads, head_dim=d)
+    shape = TurboQuantBackend.get_kv_cache_shape(case.num_blocks, 16, hkv, d, "fp8")
     kv_cache = torch.zeros(shape, dtype=torch.uint8, device=DEV)
     impl.do_kv_cache_update(None, case.k.to(DEV), case.v.to(DEV), kv_cache, case.slot_mapping.to(DEV))
     # the chunk: the last chunk[b] tokens of every sequence (their K/V are case.k / case.v rows)
@@ -162,7 +166,7 @@ def _backend_step(oracle, golden, cached, chunk, with_builder_facts):
     rows = np.concatenate([np.arange(starts[b] + cached[b], starts[b + 1]) for b in range(B)])
     n = len(rows)
     g = torch.Generator().manual_seed(11)
-    q = torch.randn(n, 32, 128, generator=g).to(torch.bfloat16)
+    q = torch.randn(n, hq, d, generator=g).to(torch.bfloat16)
     key, value = case.k[rows], case.v[rows]
     qsl_cpu = torch.tensor(np.concatenate([[0], np.cumsum(chunk)]), dtype=torch.int32)
     md = types.SimpleNamespace(max_query_len=max(chunk), num_actual_tokens=n, block_table=case.block_table.to(DEV),
@@ -170,27 +174,27 @@ def _backend_step(oracle, golden, cached, chunk, with_builder_facts):
     if with_builder_facts:
         md.tq_step = step_shape(types.SimpleNamespace(query_start_loc_cpu=qsl_cpu, num_reqs=B,
                                                       seq_lens_cpu=case.seq_lens))
-    out = torch.zeros(n, 32 * 128, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(n, hq * d, dtype=torch.bfloat16, device=DEV)
     try:
         impl.forward(None, q.to(DEV).reshape(n, -1), key.to(DEV), value.to(DEV), kv_cache, md, output=out)
     except (RuntimeError, ImportError) as e:
         if "flash" in str(e).lower() or "FA" in str(e):
             pytest.skip(f"vLLM's FlashAttention does not run on this device: {e}")
         raise
-    got = out.float().cpu().numpy().reshape(n, 32, 128)
+    got = out.float().cpu().numpy().reshape(n, hq, d)
     cache_np = kv_cache.cpu().numpy()
-    signs = golden["signs_seed42_d128"]
+    signs = golden[f"signs_seed42_d{max(64, 1 << (d - 1).bit_length())}"]
     want = np.zeros_like(got)
     decode_rows = []
     qi = 0
     for b in range(B):
-        is_decode = 1 <= chunk[b] <= 8 and cached[b] > 0   # decode and short rows: this package's kernels
+        is_decode = 1 <= chunk[b] <= (8 if fuse_short else 1) and cached[b] > 0   # decode and short rows: this package's kernels
         if is_decode:
             decode_rows.extend(range(qi, qi + chunk[b]))
         t = np.arange(total[b] if is_decode else cached[b])
         pages = case.block_table.numpy()[b, t // 16]
-        kc = oracle.dequant_cache_rows(cache_np[0, pages, t % 16], signs, 128).reshape(-1, 8, 128)
-        vc = oracle.dequant_cache_rows(cache_np[1, pages, t % 16], signs, 128).reshape(-1, 8, 128)
+        kc = oracle.dequant_cache_rows(cache_np[0, pages, t % 16], signs, d).reshape(-1, hkv, d)
+        vc = oracle.dequant_cache_rows(cache_np[1, pages, t % 16], signs, d).reshape(-1, hkv, d)
         kc, vc = torch.from_numpy(kc), torch.from_numpy(vc)
         if is_decode:
             ka, va = kc, vc
@@ -199,9 +203,9 @@ def _backend_step(oracle, golden, cached, chunk, with_builder_facts):
             va = torch.cat([vc.to(torch.bfloat16).float(), case.v[starts[b] + cached[b]:starts[b + 1]].float()])
         for i in range(chunk[b]):
             kk, vv = ka[: cached[b] + i + 1], va[: cached[b] + i + 1]
-            qq = q[qi].float().view(8, 4, 128)
-            sc = torch.einsum("hgd,thd->hgt", qq, kk) * SCALE
-            want[qi] = torch.einsum("hgt,thd->hgd", torch.softmax(sc, -1), vv).reshape(32, 128).numpy()
+            qq = q[qi].float().view(hkv, grp, d)
+            sc = torch.einsum("hgd,thd->hgt", qq, kk) * scale
+            want[qi] = torch.einsum("hgt,thd->hgd", torch.softmax(sc, -1), vv).reshape(hq, d).numpy()
             qi += 1
     # Decode rows come from this package's kernel: the usual bar.  The other rows come out of vLLM's
     # FlashAttention on bf16 K/V with bf16 probabilities (a library kernel, the same one the
@@ -247,3 +251,12 @@ def test_vllm_backend_short_chunks_attend_the_quantized_cache(oracle, golden, wi
     verification) go through the causal wide-tile kernel, next to decode rows, a longer chunk and a
     first chunk; one of them has fewer cached tokens than pad queries."""
     _backend_step(oracle, golden, [500, 3, 37, 1200, 0, 64], [1, 6, 3, 12, 2, 8], with_builder_facts)
+
+
+@pytest.mark.parametrize("heads,d", [((64, 8), 128), ((16, 8), 64), ((8, 1), 128)])
+@pytest.mark.parametrize("with_builder_facts", [False, True])
+def test_vllm_backend_short_chunks_without_the_causal_kernel(oracle, golden, with_builder_facts, heads, d):
+    """Geometries the causal wide-tile kernel does not take (eight query heads per KV head, head size 64, one KV
+    head): rows with two to eight new tokens go the dense way, decode rows still ride the paged kernel, and the
+    dense buffer is sized for them."""
+    _backend_step(oracle, golden, [500, 3, 37, 300, 0, 64], [1, 6, 3, 12, 2, 8], with_builder_facts, heads=heads, d=d)

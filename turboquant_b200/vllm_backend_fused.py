@@ -121,9 +121,22 @@ def step_shape(common):
     is_decode = (q_lens == 1) & (cached > 0)
     is_short = (q_lens > 1) & (q_lens <= FUSED_CHUNK_MAX) & (cached > 0)
     dense = ~(is_decode | is_short)
+    # an implementation without the causal kernel (``causal_chunk_supported``) treats the short rows as dense ones
+    dense2 = ~is_decode
     return {"any_cached": bool((cached > 0).any()), "num_decode_rows": int(is_decode.sum()),
             "num_short_rows": int(is_short.sum()), "dense_rows": int(seq[dense].sum()),
-            "max_prefill_seq": int(seq[dense].max()) if bool(dense.any()) else 0}
+            "max_prefill_seq": int(seq[dense].max()) if bool(dense.any()) else 0,
+            "dense_rows_with_short": int(seq[dense2].sum()),
+            "max_prefill_seq_with_short": int(seq[dense2].max()) if bool(dense2.any()) else 0}
+
+
+def causal_chunk_supported(num_heads: int, num_kv_heads: int, head_size: int) -> bool:
+    """Whether FUSED_CHUNK_MAX causal queries of a row fit one pass of the wide-tile decode kernel: head size
+    128 or 96, 2 / 4 / 8 / 16 KV heads, and FUSED_CHUNK_MAX x (query heads per KV head) within its 32 columns."""
+    from . import _cabi
+    if head_size not in (128, 96) or num_kv_heads not in (2, 4, 8, 16):
+        return False
+    return _cabi.decode_max_queries_per_seq(num_heads, num_kv_heads) >= FUSED_CHUNK_MAX
 
 
 class TurboQuantFusedImpl(FlashAttentionImpl):
@@ -141,6 +154,8 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         self._nbytes = self._dc * 2
         self._attn = (TurboQuantPagedAttention(self.num_heads, self.head_size, self.scale, self.num_kv_heads)
                       if self._is_fp8 else None)
+        # short continuing chunks attend the quantized cache directly only where the causal kernel exists
+        self._fuse_short = self._is_fp8 and causal_chunk_supported(self.num_heads, self.num_kv_heads, self.head_size)
 
     @staticmethod
     def _choose_num_splits(batch_size: int, max_len: int, num_kv_heads: int, device) -> int:
@@ -207,7 +222,9 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         * Rows with cached context and 2 ... FUSED_CHUNK_MAX new tokens run through the causal
           wide-tile decode kernel: their tokens are already in the cache, the row's queries are
           padded at the front to FUSED_CHUNK_MAX (a pad query sees fewer tokens than the first real
-          one and its output is dropped), every other row has length zero there.
+          one and its output is dropped), every other row has length zero there.  Geometries without that
+          kernel (``causal_chunk_supported``: other head sizes, more than four query heads per KV head, KV
+          head counts the wide tile does not take) send these rows the dense way below.
         * Every other row b contributes ``seq_lens[b]`` keys to a dense varlen K/V: its cached
           tokens, dequantized from the cache, then the chunk's own fresh K/V (the chunk is already
           in the cache as well, quantized; its fresh values are used, as a first chunk would).  The
@@ -222,6 +239,8 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         cached = seq_lens - q_lens
         is_dec = (q_lens == 1) & (cached > 0)
         is_short = (q_lens > 1) & (q_lens <= FUSED_CHUNK_MAX) & (cached > 0)
+        if not self._fuse_short:      # no causal kernel for this geometry: those rows go the dense way
+            is_short = torch.zeros_like(is_short)
         fused = is_dec | is_short
         zero = torch.zeros_like(seq_lens)
         bt = md.block_table[:B]
@@ -237,8 +256,10 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
         cu_k = torch.zeros(B + 1, dtype=torch.int32, device=dev)
         cu_k[1:] = torch.cumsum(pf_seq, 0)
         max_seq_len = int(getattr(md, "max_seq_len", md.max_query_len))
-        if step is not None:
+        if step is not None and self._fuse_short:
             rows, max_k = max(step["dense_rows"], 1), max(step["max_prefill_seq"], 1)
+        elif step is not None and "dense_rows_with_short" in step:
+            rows, max_k = max(step["dense_rows_with_short"], 1), max(step["max_prefill_seq_with_short"], 1)
         else:
             rows, max_k = B * max_seq_len, max_seq_len
         # one spare row at the end takes the fresh K/V of the decode and short rows' tokens, which nobody reads
@@ -265,7 +286,7 @@ class TurboQuantFusedImpl(FlashAttentionImpl):
             self._attn.decode(q_rows, kv_cache, bt, dec_lens, dec_out)
             out[first_tok] = torch.where(is_dec[:, None, None], dec_out.to(out.dtype), out[first_tok])
         # ---- short rows: causal queries over the quantized cache, padded at the front --------------
-        if step is None or step.get("num_short_rows", 0) > 0:
+        if self._fuse_short and (step is None or step.get("num_short_rows", 0) > 0):
             nq = FUSED_CHUNK_MAX
             slot = (seq_of * nq + (nq - q_lens[seq_of]) + (tok - qsl[:-1][seq_of])).long()
             slot = torch.where(is_short[seq_of], slot, torch.full_like(slot, B * nq))   # others: the spare row
