@@ -256,3 +256,58 @@ def test_dequant_of_a_large_job(oracle, golden, d, hkv):
             want_rows = oracle.dequant_cache_rows(cache_np[which, pages, t % 16], signs.numpy(), d)
             np.testing.assert_array_equal(got_t[at:at + n].cpu().numpy(), want_rows)
         at += n
+
+
+@pytest.mark.parametrize("d,hkv", [(64, 3), (256, 2), (80, 4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_write_edge_cases(oracle, golden, monkeypatch, d, hkv, dtype):
+    """The write of these head sizes on what an engine hands it: K / V as strided views of one fused tensor,
+    int32 and int64 slot ids, skipped (-1) and out-of-range slots (dropped and counted), a token count that is not
+    a multiple of the four rows a warp takes, degenerate rows; pad bytes untouched unless asked for."""
+    monkeypatch.delenv("TQ_DEBUG_CHECKS", raising=False)   # the device-side handling is what is tested
+    T, nb = 203, 16
+    g = torch.Generator().manual_seed(800 + d)
+    fused = torch.randn(T, 3 * hkv * d, generator=g).to(dtype)
+    fused[5, hkv * d:hkv * d + d] = 0                      # an all-zero K row: norm clamp
+    fused[6, hkv * d:hkv * d + d] = 1e-30                  # tiny values: the division instruction's path
+    fused[7, hkv * d + 3] = float("inf")                   # a non-finite row
+    fused[8, hkv * d:hkv * d + d] = 3.0                    # a constant row
+    key = fused[:, hkv * d:2 * hkv * d].view(T, hkv, d)
+    value = fused[:, 2 * hkv * d:].view(T, hkv, d)
+    assert key.stride(0) == 3 * hkv * d
+    slots = torch.randperm(nb * 16, generator=g)[:T]
+    slots[10] = -1
+    slots[50] = -1
+    bad = slots.clone()
+    bad[20] = nb * 16
+    bad[120] = 2 ** 40
+    sb = slot_bytes(d)
+    signs = _signs(golden, d)
+    ok = bad.clone()
+    ok[[20, 120]] = -1
+    for zero_pad in (False, True):
+        want = np.full((2, nb, 16, hkv, sb), 0xEE, np.uint8)
+        oracle.write_kv_cache(want, key.float().numpy(), value.float().numpy(), signs.numpy(), ok.numpy(), d)
+        before = _cabi.fault_counts()[0]
+        cache = torch.full((2, nb, 16, hkv, sb), 0xEE, dtype=torch.uint8, device=DEV)
+        fused_dev = fused.to(DEV)
+        _cabi.write_kv_cache(cache, fused_dev[:, hkv * d:2 * hkv * d].view(T, hkv, d), fused_dev[:, 2 * hkv * d:].view(T, hkv, d),
+                             signs.to(DEV), bad.to(DEV), d, zero_pad=zero_pad)
+        torch.cuda.synchronize()
+        assert _cabi.fault_counts()[0] - before == 2
+        got = cache.cpu().numpy()
+        pd = 1 << (d - 1).bit_length() if d > 64 else 64
+        used = pd // 2 + 2 * (pd // 64)
+        np.testing.assert_array_equal(got[..., :used], want[..., :used])
+        written = np.zeros((nb * 16,), bool)
+        written[ok[ok >= 0].numpy()] = True
+        pad = got.reshape(2, nb * 16, hkv, sb)[..., used:]
+        if used < sb:
+            assert (pad[:, ~written] == 0xEE).all()
+            assert (pad[:, written] == (0 if zero_pad else 0xEE)).all()
+    # int32 slot ids take the same path
+    cache32 = torch.full((2, nb, 16, hkv, sb), 0xEE, dtype=torch.uint8, device=DEV)
+    _cabi.write_kv_cache(cache32, fused_dev[:, hkv * d:2 * hkv * d].view(T, hkv, d), fused_dev[:, 2 * hkv * d:].view(T, hkv, d),
+                         signs.to(DEV), ok.to(torch.int32).to(DEV), d, zero_pad=True)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(cache32.cpu().numpy(), got)
