@@ -311,3 +311,59 @@ def test_write_edge_cases(oracle, golden, monkeypatch, d, hkv, dtype):
                          signs.to(DEV), ok.to(torch.int32).to(DEV), d, zero_pad=True)
     torch.cuda.synchronize()
     np.testing.assert_array_equal(cache32.cpu().numpy(), got)
+
+
+@pytest.mark.parametrize("d", [64, 256])
+def test_page_ids_and_lengths_that_cannot_be_trusted(oracle, golden, monkeypatch, d):
+    """Index validation of the kernels for these head sizes: a page id outside the cache is status 5 in the
+    decode (the access is skipped, other sequences are unaffected) and a counted skip in the dequantizer; a
+    sequence longer than its page table is status 4 and reads nothing."""
+    monkeypatch.delenv("TQ_DEBUG_CHECKS", raising=False)   # the device-side handling is what is tested
+    hq, hkv = 8, 4
+    case = synthetic.decode_case(seed=900 + d, seq_lens=[200, 900, 48], dtype=torch.float16, heads=(hq, hkv), head_dim=d)
+    signs = _signs(golden, d)
+    scale = 1.0 / math.sqrt(d)
+    attn = TurboQuantPagedAttention(hq, d, scale, hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    cache_np = cache.cpu().numpy()
+    want = oracle.decode_paged(case.q.float().numpy(), cache_np, case.block_table.numpy(), case.seq_lens.numpy(), signs.numpy(), scale)
+    q, sl = case.q.to(DEV), case.seq_lens.to(DEV)
+
+    def run(bt, lens):
+        ws = torch.zeros(_cabi.decode_workspace_bytes(3, hq, hkv, d, 0), dtype=torch.uint8, device=DEV)
+        out = torch.zeros(3, hq, d, dtype=torch.float32, device=DEV)
+        _cabi.decode_paged(q, cache, bt, lens, signs.to(DEV), scale, ws, out)
+        torch.cuda.synchronize()
+        return out.cpu().numpy(), int(ws[:4].view(torch.int32).item())
+
+    good, status = run(case.block_table.to(DEV), sl)
+    assert status == 0
+    assert_attention_close(good, want, f"head size {d}, in-range page table")
+    for bad_id in (case.num_blocks, -1, 2 ** 31 - 1):
+        bt = case.block_table.clone()
+        bt[1, 3] = bad_id
+        out, status = run(bt.to(DEV), sl)
+        assert status == 5, (bad_id, status)
+        assert np.isfinite(out).all()
+        assert_attention_close(out[[0, 2]], want[[0, 2]], f"head size {d}, rows beside the bad page id {bad_id}")
+    too_long = torch.tensor([200, 900, 48 + 16 * case.block_table.shape[1]], dtype=torch.int32, device=DEV)
+    out, status = run(case.block_table.to(DEV), too_long)
+    assert status == 4 and (out[2] == 0).all()
+    assert_attention_close(out[:2], want[:2], f"head size {d}, rows beside the over-long one")
+    # dequantization: the bad page's rows stay unwritten and are counted once
+    bt = case.block_table.clone()
+    bt[0, 2] = case.num_blocks + 3
+    lens = [200, 900, 48]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
+    k = torch.full((sum(lens), hkv, d), 7.0, dtype=torch.float32, device=DEV)
+    v = torch.full_like(k, 7.0)
+    before = _cabi.fault_counts()
+    _cabi.dequant_paged(cache, bt.to(DEV), sl, cu, signs.to(DEV), k, v)
+    torch.cuda.synchronize()
+    assert _cabi.fault_counts()[1] - before[1] == 1
+    kk = k.cpu().numpy()
+    assert (kk[32:48] == 7.0).all()
+    t = np.arange(32)
+    want_rows = oracle.dequant_cache_rows(cache_np[0, case.block_table.numpy()[0, t // 16], t % 16], signs.numpy(), d)
+    assert np.array_equal(kk[:32], want_rows)
