@@ -157,8 +157,8 @@ int tq_decode_paged(const void* q, int q_dtype, int batch, int num_q_heads, int 
  * queries ride in the columns of one query tile, so the KV is streamed and dequantized once for
  * all of them.  queries_per_seq x (num_q_heads / num_kv_heads) <= 8 takes the 8-wide tile of the
  * mma.sync kernel; 9 ... 32 columns take the wide-tile kernel (tcgen05.mma, accumulators in tensor
- * memory), which needs head_dim 128 and 2, 4, 8 or 16 KV heads and ignores num_ctas below the
- * number of KV-head pairs.
+ * memory), which needs head_dim 128 or 96 and 2, 4, 8 or 16 KV heads and ignores num_ctas below the
+ * number of KV-head pairs.  Other head sizes (33 ... 256) take up to 8 columns.
  * The workspace is sized with tq_decode_workspace_bytes(batch, queries_per_seq * num_q_heads, ...).
  * kv_begin / kv_end restrict the tokens as in tq_decode_paged_partial (0, -1: all of them);
  * rotated_partial != 0 makes out (fp32) and out_lse (required) the rotated-domain partial and

@@ -367,3 +367,68 @@ def test_page_ids_and_lengths_that_cannot_be_trusted(oracle, golden, monkeypatch
     t = np.arange(32)
     want_rows = oracle.dequant_cache_rows(cache_np[0, case.block_table.numpy()[0, t // 16], t % 16], signs.numpy(), d)
     assert np.array_equal(kk[:32], want_rows)
+
+
+@pytest.mark.parametrize("d,hq,hkv,nq", [(64, 8, 4, 4), (64, 16, 8, 2), (256, 4, 4, 7), (80, 4, 2, 3)])
+def test_queries_that_share_a_sequence(oracle, golden, d, hq, hkv, nq):
+    """Several decode queries per sequence (speculative tokens verified without a causal mask, or any caller that
+    would repeat the sequence as batch rows) ride as extra columns of the KV heads: up to 8 columns per KV head at
+    these head sizes.  Against the oracle with the rows repeated; rotated partials over windows merge to the same."""
+    lens = [700, 0, 33]
+    B = len(lens)
+    case = synthetic.decode_case(seed=1000 + d + nq, seq_lens=lens, dtype=torch.bfloat16, heads=(hq, hkv), head_dim=d)
+    signs = _signs(golden, d)
+    scale = 1.0 / math.sqrt(d)
+    attn = TurboQuantPagedAttention(hq, d, scale, hkv)
+    assert _cabi.decode_max_queries_per_seq(hq, hkv, d) >= nq
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    attn.write(case.k.to(DEV), case.v.to(DEV), cache, case.slot_mapping.to(DEV))
+    q = torch.randn(B, nq, hq, d, generator=torch.Generator().manual_seed(nq)).to(torch.bfloat16)
+    bt, sl = case.block_table.to(DEV), case.seq_lens.to(DEV)
+    lse = torch.empty(B, nq, hq, dtype=torch.float32, device=DEV)
+    out = attn.decode_shared(q.to(DEV), cache, bt, sl, out_lse=lse)
+    torch.cuda.synchronize()
+    assert attn.status(B, DEV, nq) == 0
+    rep_bt = np.repeat(case.block_table.numpy(), nq, axis=0)
+    rep_sl = np.repeat(case.seq_lens.numpy(), nq)
+    want, want_lse = oracle.decode_paged(q.float().numpy().reshape(B * nq, hq, d), cache.cpu().numpy(), rep_bt, rep_sl,
+                                         signs.numpy(), scale, return_lse=True)
+    assert_attention_close(out.float().cpu().numpy().reshape(B * nq, hq, d), want, f"head size {d}, {nq} queries per sequence")
+    ok = np.isfinite(want_lse)
+    np.testing.assert_allclose(lse.cpu().numpy().reshape(B * nq, hq)[ok], want_lse[ok], atol=2e-3)
+    assert (out[1] == 0).all()
+    # the same through rotated partials over two windows and the merge
+    pd = 64 if d <= 64 else 128 if d <= 128 else 256
+    ws = attn.workspace(B, DEV, nq)
+    po = torch.empty(2, B, nq, hq, pd, dtype=torch.float32, device=DEV)
+    pl = torch.empty(2, B, nq, hq, dtype=torch.float32, device=DEV)
+    for i, (a, b) in enumerate([(0, 256), (256, -1)]):
+        _cabi.decode_paged_multi(q.to(DEV), cache, bt, sl, signs.to(DEV), scale, ws, po[i], out_lse=pl[i],
+                                 kv_begin=a, kv_end=b, rotated_partial=True)
+    merged = torch.empty(B, nq, hq, d, dtype=torch.float32, device=DEV)
+    _cabi.merge_rotated(po, pl, signs.to(DEV), merged)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(merged.cpu().numpy(), out.float().cpu().numpy(), atol=2e-3, rtol=1e-2)
+    with pytest.raises(_cabi.TurboQuantError, match="queries_per_seq"):
+        attn.decode_shared(torch.zeros(B, 8 // (hq // hkv) + 1, hq, d, dtype=torch.bfloat16, device=DEV), cache, bt, sl)
+
+
+def test_shared_queries_through_the_plain_kernel(oracle, golden):
+    """Slots that are not 16-byte multiples take the plain decode kernel; queries that share a sequence work there too."""
+    d, sb, hq, hkv, nq, lens = 64, 52, 8, 4, 3, [33, 700]
+    B = len(lens)
+    case = synthetic.decode_case(seed=1100, seq_lens=lens, dtype=torch.float16, heads=(hq, hkv), head_dim=d)
+    signs = _signs(golden, d)
+    scale = 1.0 / math.sqrt(d)
+    cache_np = np.zeros((2, case.num_blocks, 16, hkv, sb), np.uint8)
+    oracle.write_kv_cache(cache_np, case.k.float().numpy(), case.v.float().numpy(), signs.numpy(), case.slot_mapping.numpy(), d)
+    q = torch.randn(B, nq, hq, d, generator=torch.Generator().manual_seed(5)).to(torch.float16)
+    want = oracle.decode_paged(q.float().numpy().reshape(B * nq, hq, d), cache_np, np.repeat(case.block_table.numpy(), nq, axis=0),
+                               np.repeat(case.seq_lens.numpy(), nq), signs.numpy(), scale)
+    ws = torch.zeros(_cabi.decode_workspace_bytes(B, nq * hq, hkv, d, 0), dtype=torch.uint8, device=DEV)
+    out = torch.empty(B, nq, hq, d, dtype=torch.float32, device=DEV)
+    _cabi.decode_paged_multi(q.to(DEV), torch.from_numpy(cache_np).to(DEV), case.block_table.to(DEV), case.seq_lens.to(DEV),
+                             signs.to(DEV), scale, ws, out)
+    torch.cuda.synchronize()
+    assert ws[:4].view(torch.int32).item() == 0
+    assert_attention_close(out.cpu().numpy().reshape(B * nq, hq, d), want, "plain kernel, 3 queries per sequence")

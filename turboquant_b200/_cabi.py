@@ -240,11 +240,12 @@ def _decode_args(q, kv_cache, page_indices, page_indptr, max_pages, seq_lens, si
         _check_pages(page_indices, page_indptr, max_pages, seq_lens, kv_cache.shape[1], kv_cache.shape[2])
 
 
-def decode_max_queries_per_seq(num_q_heads: int, num_kv_heads: int) -> int:
+def decode_max_queries_per_seq(num_q_heads: int, num_kv_heads: int, head_size: int = 128) -> int:
     """How many decode queries that share one sequence's KV fit one pass of ``decode_paged_multi``:
-    the wide-tile kernel (up to ``tq_decode_max_query_columns()`` columns) takes 2, 4, 8 or 16 KV heads,
-    any other count keeps the 8 columns of the mma.sync kernel."""
-    cols = int(lib().tq_decode_max_query_columns()) if num_kv_heads in (2, 4, 8, 16) else 8
+    the wide-tile kernel (up to ``tq_decode_max_query_columns()`` columns) takes 2, 4, 8 or 16 KV heads at head
+    size 128 / 96; any other KV-head count or head size keeps the 8 columns of the mma.sync kernels."""
+    wide = num_kv_heads in (2, 4, 8, 16) and head_size in (128, 96)
+    cols = int(lib().tq_decode_max_query_columns()) if wide else 8
     return max(1, cols // max(1, num_q_heads // num_kv_heads))
 
 

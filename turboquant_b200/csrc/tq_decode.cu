@@ -840,7 +840,7 @@ int device_sm_count(int* out);
 size_t generic_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim, int num_ctas);
 int generic_merge_rotated(const float* partial_o, const float* partial_lse2, int num_parts, int64_t rows, int head_dim,
                           const float* signs, void* out, int out_dtype, float* out_lse, void* stream);
-int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+int generic_decode(const void* q, int q_dtype, int batch, int nq, int real_q_heads, int num_kv_heads, int head_dim,
                    const void* kv_cache, int64_t num_blocks, int block_size, int slot_bytes, const int32_t* page_indices,
                    const int32_t* page_indptr, int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
                    const float* signs, float sm_scale, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
@@ -931,11 +931,11 @@ static int decode_common(const void* q, int q_dtype, int batch, int nq, int real
     }
     TQ_REQUIRE(q && kv_cache && page_indices && seq_lens && signs && workspace && out, TQ_ERR_INVALID, "null pointer");
     if (head_dim != kHeadDim && head_dim != 96) {  // other head sizes (64, 256, ...): the plain kernels
-        TQ_REQUIRE(nq == 1 && !x && !causal, TQ_ERR_UNSUPPORTED,
-                   "head size %d: one query per sequence and no KV-split exchange (those are built for padded size 128)", head_dim);
+        TQ_REQUIRE(!x && !causal, TQ_ERR_UNSUPPORTED,
+                   "head size %d: no causal queries and no KV-split exchange (those are built for padded size 128)", head_dim);
         TQ_REQUIRE(q_dtype >= TQ_F32 && q_dtype <= TQ_BF16 && out_dtype >= TQ_F32 && out_dtype <= TQ_BF16, TQ_ERR_INVALID, "bad dtype");
         TQ_REQUIRE(((uintptr_t)workspace % 256) == 0, TQ_ERR_INVALID, "workspace must be 256-byte aligned");
-        return generic_decode(q, q_dtype, batch, real_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks, block_size,
+        return generic_decode(q, q_dtype, batch, nq, real_q_heads, num_kv_heads, head_dim, kv_cache, num_blocks, block_size,
                               slot_bytes, page_indices, page_indptr, max_pages, seq_lens, kv_begin, kv_end, signs, sm_scale,
                               workspace, workspace_bytes, out, out_dtype, out_lse, emit_rotated, num_ctas, stream);
     }

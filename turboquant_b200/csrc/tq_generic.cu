@@ -286,7 +286,8 @@ struct GenDecodeParams {
     float* partial_lse;    // [batch][splits][num_q_heads], base 2
     float* partial_o;      // [batch][splits][num_q_heads][padded], normalized, rotated domain
     int64_t slab_bytes, num_blocks, kv_begin, kv_end;
-    int batch, num_q_heads, num_kv_heads, group, max_pages, q_dtype, splits;
+    int batch, num_q_heads, num_kv_heads, group, max_pages, q_dtype, splits;   // num_q_heads, group: virtual (x nq)
+    int nq, real_heads, real_group;   // queries that share a sequence's KV: column c of a KV head is (query c / real_group, head c % real_group)
     GenGeom g;
     float score_scale;     // sm_scale * log2(e)
     float scale;           // 1 / sqrt(padded)
@@ -304,6 +305,12 @@ __device__ __forceinline__ float gen_load(const void* q, int dtype, int64_t i) {
     if (dtype == TQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(q)[i]);
     if (dtype == TQ_F16) return __half2float(reinterpret_cast<const __half*>(q)[i]);
     return reinterpret_cast<const float*>(q)[i];
+}
+
+// row of q [batch][nq][real_heads] that column c of KV head h of sequence b stands for
+__device__ __forceinline__ int64_t gen_q_row(const GenDecodeParams& p, int b, int h, int c) {
+    const int qi = c / p.real_group, hh = c - qi * p.real_group;
+    return ((int64_t)b * p.nq + qi) * p.real_heads + h * p.real_group + hh;
 }
 
 // BPL = code bytes per lane and token: 1, 2 or 4 for padded head sizes 64, 128, 256.  (This file is compiled without
@@ -341,7 +348,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 4) decode_generic_kernel(const
     for (int i = tid; i < G * pd; i += blockDim.x) {
         const int g = i / pd, d = i - g * pd;
         q_s[i] = d < p.g.head_dim
-                     ? gen_load(p.q, p.q_dtype, ((int64_t)b * p.num_q_heads + h * G + g) * p.g.head_dim + d) * p.signs[d]
+                     ? gen_load(p.q, p.q_dtype, gen_q_row(p, b, h, g) * p.g.head_dim + d) * p.signs[d]
                      : 0.0f;
     }
     __syncthreads();
@@ -591,7 +598,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
     for (int i = tid; i < G * pd; i += blockDim.x) {
         const int gg = i / pd, d = i - gg * pd;
         q_s[i] = d < p.g.head_dim
-                     ? gen_load(p.q, p.q_dtype, ((int64_t)b * p.num_q_heads + h * G + gg) * p.g.head_dim + d) * p.signs[d]
+                     ? gen_load(p.q, p.q_dtype, gen_q_row(p, b, h, gg) * p.g.head_dim + d) * p.signs[d]
                      : 0.0f;
     }
     __syncthreads();
@@ -809,7 +816,8 @@ struct GenMergeParams {
     const float* signs;
     void* out;
     float* out_lse;
-    int num_q_heads, splits, out_dtype, emit_rotated;
+    int num_q_heads, splits, out_dtype, emit_rotated;   // num_q_heads: virtual (x nq)
+    int nq, real_heads, real_group, group;   // virtual head -> (query, real head) of the output row; nq = 1: identity
     GenGeom g;
     float scale;
 };
@@ -835,7 +843,9 @@ __global__ void __launch_bounds__(kGenMaxDim) merge_generic_kernel(const __grid_
     }
     float o = wsum > 0.0f ? acc / wsum : 0.0f;
     const float lse2 = wsum > 0.0f ? mm + log2f(wsum) : -INFINITY;
-    const int64_t orow = b * p.num_q_heads + hq;
+    // virtual head hq = (KV head, column); column = (query, head of the group): rows of the output are [batch][nq][real heads]
+    const int kvh = hq / p.group, col = hq - kvh * p.group, qi = col / p.real_group;
+    const int64_t orow = (b * p.nq + qi) * p.real_heads + kvh * p.real_group + (col - qi * p.real_group);
     if (p.emit_rotated) {
         reinterpret_cast<float*>(p.out)[orow * pd + d] = o;
         if (p.out_lse && d == 0) p.out_lse[orow] = lse2;
@@ -1131,7 +1141,7 @@ size_t generic_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int
     return 256 + up(rows * sizeof(float)) + up(rows * pd * sizeof(float));
 }
 
-int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+int generic_decode(const void* q, int q_dtype, int batch, int nq, int real_q_heads, int num_kv_heads, int head_dim,
                    const void* kv_cache, int64_t num_blocks, int block_size, int slot_bytes, const int32_t* page_indices,
                    const int32_t* page_indptr, int max_pages, const int32_t* seq_lens, int64_t kv_begin, int64_t kv_end,
                    const float* signs, float sm_scale, void* workspace, size_t workspace_bytes, void* out, int out_dtype,
@@ -1140,8 +1150,13 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
     TQ_REQUIRE(block_size == kGenPage, TQ_ERR_UNSUPPORTED, "decode supports 16-token pages, got %d", block_size);
     TQ_REQUIRE(slot_bytes >= generic_slot_bytes(head_dim), TQ_ERR_INVALID, "slot_bytes %d is smaller than head size %d needs (%d)",
                slot_bytes, head_dim, generic_slot_bytes(head_dim));
-    TQ_REQUIRE(num_kv_heads >= 1 && num_q_heads % num_kv_heads == 0 && num_q_heads / num_kv_heads <= kGenMaxGroup,
-               TQ_ERR_UNSUPPORTED, "query heads per KV head must be 1..%d", kGenMaxGroup);
+    TQ_REQUIRE(nq >= 1 && num_kv_heads >= 1 && real_q_heads >= 1 && real_q_heads % num_kv_heads == 0, TQ_ERR_INVALID,
+               "query heads must be a positive multiple of the KV heads, queries_per_seq >= 1");
+    // the queries that share a sequence ride as extra columns of its KV heads
+    const int num_q_heads = nq * real_q_heads;
+    TQ_REQUIRE(num_q_heads / num_kv_heads <= kGenMaxGroup, TQ_ERR_UNSUPPORTED,
+               "head size %d: queries_per_seq x query heads per KV head must be 1..%d, got %d x %d", head_dim, kGenMaxGroup, nq,
+               real_q_heads / num_kv_heads);
     TQ_REQUIRE(kv_begin >= 0 && kv_begin % kGenPage == 0, TQ_ERR_INVALID, "kv_begin must be a multiple of 16");
     TQ_REQUIRE(page_indptr || max_pages > 0, TQ_ERR_INVALID, "max_pages must be positive for a dense block table");
     TQ_REQUIRE(num_blocks >= 1, TQ_ERR_INVALID, "the cache has no pages");
@@ -1171,6 +1186,9 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
     p.num_q_heads = num_q_heads;
     p.num_kv_heads = num_kv_heads;
     p.group = num_q_heads / num_kv_heads;
+    p.nq = nq;
+    p.real_heads = real_q_heads;
+    p.real_group = real_q_heads / num_kv_heads;
     p.max_pages = max_pages;
     p.q_dtype = q_dtype;
     p.score_scale = (float)((double)sm_scale * 1.4426950408889634);
@@ -1219,6 +1237,10 @@ int generic_decode(const void* q, int q_dtype, int batch, int num_q_heads, int n
     m.out = out;
     m.out_lse = out_lse;
     m.num_q_heads = num_q_heads;
+    m.nq = nq;
+    m.real_heads = real_q_heads;
+    m.real_group = p.real_group;
+    m.group = p.group;
     m.splits = p.splits;
     m.out_dtype = out_dtype;
     m.emit_rotated = emit_rotated;
@@ -1241,6 +1263,9 @@ int generic_merge_rotated(const float* partial_o, const float* partial_lse2, int
     m.out = out;
     m.out_lse = out_lse;
     m.num_q_heads = (int)rows;   // one "sequence" whose parts are the windows: row (part, r) at part * rows + r
+    m.nq = 1;
+    m.real_heads = (int)rows;
+    m.real_group = m.group = 1;
     m.splits = num_parts;
     m.out_dtype = out_dtype;
     m.emit_rotated = 0;

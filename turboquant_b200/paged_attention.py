@@ -119,7 +119,8 @@ class TurboQuantPagedAttention:
         that row's KV (one ``seq_lens`` / ``block_table`` entry per row).  The reference would repeat
         the row ``queries`` times in the batch (its decode op has one query per batch row,
         csrc/src/decode_v5_tc_binding.cu:783-785) and stream the KV once per repeat; here the KV
-        is streamed once.  queries x (heads / kv_heads) must not exceed 32."""
+        is streamed once.  queries x (heads / kv_heads) must not exceed 32 (8 for head sizes other than
+        128 / 96 and for KV-head counts other than 2, 4, 8, 16: ``_cabi.decode_max_queries_per_seq``)."""
         B, NQ = query.shape[0], query.shape[1]
         if output is None:
             output = torch.empty_like(query)
