@@ -77,6 +77,40 @@ def test_torch_ops_with_reference_schemas(oracle, golden):
     assert torch.equal(o2, o_ws)
 
 
+@pytest.mark.parametrize("d,pd,hq,hkv", [(64, 64, 16, 8), (256, 256, 8, 4), (96, 128, 24, 8)])
+def test_torch_ops_take_the_other_head_sizes(oracle, golden, d, pd, hq, hkv):
+    """The reference declares these geometries (kernel_config presets) while its decode op takes 128 only; the
+    ops here take head sizes 33 ... 256 with the reference's padded size, and refuse a padded size that is not it."""
+    from turboquant_b200 import ops, _cabi  # noqa: F401
+    from turboquant_b200.paged_attention import kv_cache_shape
+    case = synthetic.decode_case(seed=84 + d, seq_lens=[300, 17, 640], dtype=torch.float16, heads=(hq, hkv), head_dim=d)
+    signs_np = golden[f"signs_seed42_d{d if d == 96 else pd}"]
+    signs = torch.from_numpy(signs_np).to(DEV)
+    scale = 1.0 / math.sqrt(d)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    torch.ops.turboquant_write.quantize_write_kv_cache(cache, case.k.float().to(DEV), case.v.float().to(DEV), signs,
+                                                       case.slot_mapping.to(torch.int32).to(DEV), d, pd)
+    want_cache = np.zeros(tuple(cache.shape), np.uint8)
+    oracle.write_kv_cache(want_cache, case.k.float().numpy(), case.v.float().numpy(), signs_np, case.slot_mapping.numpy(), d)
+    np.testing.assert_array_equal(cache.cpu().numpy(), want_cache)
+    want = oracle.decode_paged(case.q.float().numpy(), want_cache, case.block_table.numpy(), case.seq_lens.numpy(), signs_np, scale)
+    B, max_pages = 3, case.block_table.shape[1]
+    bt, sl = case.block_table.to(DEV), case.seq_lens.to(DEV)
+    indptr = torch.arange(B + 1, dtype=torch.int32, device=DEV) * max_pages
+    last = sl - ((sl + 15) // 16 - 1) * 16
+    o_ws = torch.empty(B, hq, d, dtype=torch.float16, device=DEV)
+    e = torch.empty(0, device=DEV)
+    ei = torch.empty(0, dtype=torch.int32, device=DEV)
+    out = torch.ops.turboquant_v5.decode_v5_from_cache_paged_splitkv_ws(
+        case.q.to(DEV), cache, bt.reshape(-1), indptr, last, sl, hkv, 16, d, pd, scale, signs, pd // 2, 2 * (pd // 64), o_ws,
+        max_pages * 16, e, e, ei, ei, ei, ei, 4)
+    assert out.data_ptr() == o_ws.data_ptr()
+    assert_attention_close(out.float().cpu().numpy(), want, f"paged split op, head size {d}")
+    with pytest.raises(Exception, match="padded"):
+        torch.ops.turboquant_write.quantize_write_kv_cache(cache, case.k.float().to(DEV), case.v.float().to(DEV), signs,
+                                                           case.slot_mapping.to(torch.int32).to(DEV), d, 2 * pd)
+
+
 def test_decoder_dispatch_returns_the_single_kernel():
     from turboquant_b200.decoder_dispatch import KERNEL_NAME, pick_decode_op
     pick_decode_op.cache_clear()

@@ -37,25 +37,32 @@ def _bytes(kv_cache: torch.Tensor) -> torch.Tensor:
     return kv_cache if kv_cache.dtype == torch.uint8 else kv_cache.view(torch.uint8)
 
 
-def _workspace(batch: int, hq: int, hkv: int, device) -> torch.Tensor:
-    key = (device.index, batch, hq, hkv)
+def _workspace(batch: int, hq: int, hkv: int, head_dim: int, device) -> torch.Tensor:
+    key = (device.index, batch, hq, hkv, head_dim)
     ws = _workspaces.get(key)
     if ws is None:
-        ws = torch.zeros(_cabi.decode_workspace_bytes(batch, hq, hkv), dtype=torch.uint8, device=device)
+        ws = torch.zeros(_cabi.decode_workspace_bytes(batch, hq, hkv, head_dim), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
 
+def _check_dims(head_dim: int, padded_dim: int) -> None:
+    """The reference pads the head to the next power of two, 64 at least (turboquant/vllm_backend_fused.py:28-29,
+    64-72); its own decode op takes 128 only, the kernels here head sizes 33 ... 256."""
+    want = max(64, 1 << (int(head_dim) - 1).bit_length()) if head_dim > 0 else 0
+    if not 32 < head_dim <= 256 or padded_dim != want:
+        raise _cabi.TurboQuantError(f"head_dim {head_dim} / padded_dim {padded_dim}: head sizes 33 ... 256 with the "
+                                    f"next power of two (64 at least) as padded size are implemented")
+
+
 def _quantize_write_kv_cache(kv_cache, key, value, signs, slot_mapping, head_dim, padded_dim):
-    if padded_dim != 128 or head_dim not in (128, 96):
-        raise _cabi.TurboQuantError(f"head_dim {head_dim} / padded_dim {padded_dim}: 128 (and 96 padded to 128) are implemented")
+    _check_dims(head_dim, padded_dim)
     _cabi.write_kv_cache(_bytes(kv_cache), key, value, signs, slot_mapping, head_dim)
 
 
 def _decode(q, kv_cache, indices, indptr, seq_lens, num_kv_heads, page_size, head_dim, padded_dim, sm_scale,
             signs, o_ws):
-    if padded_dim != 128:
-        raise _cabi.TurboQuantError("decode supports padded head size 128 only")  # as the reference's v5 op
+    _check_dims(head_dim, padded_dim)
     b, hq, _ = q.shape
     # The op runs inside CUDA graphs: a silent cast or copy here would be an extra kernel and an
     # allocation on every replay.  The reference passes int32 tables and a contiguous q
@@ -65,7 +72,7 @@ def _decode(q, kv_cache, indices, indptr, seq_lens, num_kv_heads, page_size, hea
             raise _cabi.TurboQuantError(f"{name} must be a contiguous int32 tensor, got {t.dtype}")
     if not q.is_contiguous():
         raise _cabi.TurboQuantError("q must be contiguous")
-    ws = _workspace(b, hq, num_kv_heads, q.device)
+    ws = _workspace(b, hq, num_kv_heads, head_dim, q.device)
     _cabi.decode_paged(q, _bytes(kv_cache), indices, seq_lens, signs, float(sm_scale), ws, o_ws,
                        page_indptr=indptr, max_pages=1)
     return o_ws
