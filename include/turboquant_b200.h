@@ -124,10 +124,13 @@ int tq_fwht(const float* x, int64_t n, int in_dim, int padded_dim, int out_dim,
  *                needs initialising
  *   num_ctas     thread blocks to balance over; 0 = one per SM of the current device
  *
- * Other head sizes (33..256; 64 and 256 are the reference's other presets) run plain, untuned
- * kernels behind the same entry points: block_size 16, slot_bytes >= the slot of that head size,
- * up to 8 query heads per KV head, any number of KV heads, one query per sequence; pass head_dim
- * to tq_decode_workspace_bytes.  The rest of this paragraph is the tuned path.
+ * Other head sizes (33..256; 64 and 256 are the reference's other presets) run a second tier of
+ * kernels behind the same entry points (a quarter to two fifths of the HBM peak against the tuned
+ * kernels' three fifths): block_size 16, slot_bytes >= the slot of that head size (a multiple of 16
+ * for the tensor-core decode, anything else takes a plain one), any number of KV heads, up to 8
+ * query columns per KV head (query heads per KV head x queries sharing a sequence), KV windows and
+ * tq_merge_rotated, no causal queries and no kernel-side exchange; pass head_dim to
+ * tq_decode_workspace_bytes.  The rest of this paragraph is the tuned path.
  * Supported geometry: head_dim 128, or 96 (q and out rows of 96 elements; the rotation pads them
  * with zeros to 128 and the slot is the same 80 bytes); block_size 16, slot_bytes 80,
  * num_q_heads/num_kv_heads <= 8, num_kv_heads in {1, 2, 4, 8, 16} (one launch) or a larger
