@@ -432,3 +432,23 @@ def test_shared_queries_through_the_plain_kernel(oracle, golden):
     torch.cuda.synchronize()
     assert ws[:4].view(torch.int32).item() == 0
     assert_attention_close(out.cpu().numpy().reshape(B * nq, hq, d), want, "plain kernel, 3 queries per sequence")
+
+
+@pytest.mark.parametrize("d,hkv", [(64, 2), (256, 1)])
+def test_write_of_a_large_job(oracle, golden, d, hkv):
+    """From 8192 tokens on, a lane group of the write kernel walks all rows of its token instead of taking one
+    row: same bytes, with skipped tokens among them."""
+    T, nb = 8200, 520
+    g = torch.Generator().manual_seed(1200 + d)
+    k = torch.randn(T, hkv, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, hkv, d, generator=g).to(torch.bfloat16)
+    slots = torch.randperm(nb * 16, generator=g)[:T]
+    slots[torch.randperm(T, generator=g)[:40]] = -1
+    slots[100:104] = -1                                   # four neighbouring tokens: a whole warp pass is skipped
+    signs = _signs(golden, d)
+    want = np.zeros((2, nb, 16, hkv, slot_bytes(d)), np.uint8)
+    oracle.write_kv_cache(want, k.float().numpy(), v.float().numpy(), signs.numpy(), slots.numpy(), d)
+    cache = torch.zeros(kv_cache_shape(nb, 16, hkv, d), dtype=torch.uint8, device=DEV)
+    _cabi.write_kv_cache(cache, k.to(DEV), v.to(DEV), signs.to(DEV), slots.to(DEV), d)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(cache.cpu().numpy(), want)

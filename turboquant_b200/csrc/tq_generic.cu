@@ -92,6 +92,7 @@ struct GenWriteParams {
     const float* signs;
     int64_t num_tokens, slab_bytes, total_slots;
     int num_kv_heads, slot_is_i64, zero_pad;
+    int walk;   // rows a lane group takes of its token: all 2 H (large jobs) or 1 (a decode step's few tokens: more groups in flight)
     GenGeom g;
     float scale;
     float boundaries[15];
@@ -124,7 +125,6 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
     const int q = lane & 7, rg = lane >> 3;
     const int H = p.num_kv_heads, hd = p.g.head_dim;
     const int full = hd & ~7, ntail = hd - full;
-    const int64_t rows = 2 * p.num_tokens * H;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.kv_cache) | (uintptr_t)p.slab_bytes | (uintptr_t)p.g.slot_bytes) & 15) == 0;
     uint8_t* stage = code_s[warp][rg];
 
@@ -133,29 +133,34 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
     __syncthreads();
     const float* sg = sg_s + q;
 
-    for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < rows; base += (int64_t)gridDim.x * kGenWarps * 4) {
-        // a group past the end works on the last row again and stores nothing: the shuffles below take every lane
-        const bool live = base + rg < rows;
-        const int64_t r64 = live ? base + rg : rows - 1;
-        const int which = (int)(r64 & 1);
-        const int64_t th = r64 >> 1;
+    // a group of eight lanes takes one token and `walk` of its 2 H rows (K heads, then V heads): the slot lookup and
+    // the index arithmetic are done once per token
+    const int parts = 2 * H / p.walk;
+    const int64_t items = p.num_tokens * parts;
+    for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < items; base += (int64_t)gridDim.x * kGenWarps * 4) {
+        // a group past the end works on the last item again and stores nothing: the shuffles below take every lane
+        const bool live = base + rg < items;
+        const int64_t it = live ? base + rg : items - 1;
         int64_t t;
-        int h;
-        if (th < 0x7fffffff) {
-            const uint32_t t32 = (uint32_t)th / (uint32_t)H;
+        int r0;
+        if (it < 0x7fffffff) {
+            const uint32_t t32 = (uint32_t)it / (uint32_t)parts;
             t = t32;
-            h = (int)((uint32_t)th - t32 * (uint32_t)H);
+            r0 = (int)((uint32_t)it - t32 * (uint32_t)parts) * p.walk;
         } else {
-            t = th / H;
-            h = (int)(th - t * H);
+            t = it / parts;
+            r0 = (int)(it - t * parts) * p.walk;
         }
         int64_t slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
                                      : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
         if (slot >= p.total_slots) {
-            if (live && q == 0 && h == 0 && which == 0) atomicAdd(&g_gen_write_dropped, 1);
+            if (live && q == 0 && r0 == 0) atomicAdd(&g_gen_write_dropped, 1);
             slot = -1;
         }
         const bool store = live && slot >= 0;
+        if (!__any_sync(0xffffffffu, store)) continue;   // four skipped tokens
+        for (int rr = r0; rr < r0 + p.walk; rr++) {
+        const int which = rr >= H ? 1 : 0, h = rr - which * H;
         const T* row = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * hd;
         float x[E];
 #pragma unroll
@@ -260,6 +265,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
             if (p.zero_pad)
                 for (int b = G::kQb + 2 * G::kDc + q; b < p.g.slot_bytes; b += 8) dst[b] = 0;
         }
+        }   // rows of the token
     }
 }
 
@@ -1110,8 +1116,12 @@ int generic_write(void* kv_cache, int64_t num_blocks, int block_size, int num_kv
     p.scale = (float)(1.0 / std::sqrt((double)p.g.padded));
     float cen[16];
     host_codebook(p.g.padded, 4, cen, p.boundaries);
-    const int64_t rows = 2 * num_tokens * num_kv_heads;
-    const int64_t blocks = (rows + 4 * kGenWarps - 1) / (4 * kGenWarps);   // four rows per warp and pass
+    // large jobs of the smallest head: a lane group walks all rows of its token (96 us against 101 for 32768 tokens x
+    // 8 heads); small jobs (a decode step's new tokens) and the larger heads, where the index arithmetic is a smaller
+    // share and fewer groups in flight cost more than it saves (347 us against 337 at head 256): a row per group
+    p.walk = num_tokens >= 8192 && p.g.padded == 64 ? 2 * num_kv_heads : 1;
+    const int64_t items = num_tokens * (2 * num_kv_heads / p.walk);
+    const int64_t blocks = (items + 4 * kGenWarps - 1) / (4 * kGenWarps);   // four lane groups per warp and pass
     const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (in_dtype) {
