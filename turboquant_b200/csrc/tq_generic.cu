@@ -518,13 +518,13 @@ __device__ __forceinline__ uint32_t gen_pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-constexpr int kFragLutCols = 16;
-// table entry of byte j of word w (the table's column of this lane is folded into lut_lane)
+// table entry of byte j of word w (the table's column of this lane is folded into lut_lane; COLS copies per byte value)
+template <int COLS>
 __device__ __forceinline__ uint32_t gen_lookup(uint32_t w, int j, uint32_t lut_lane) {
     uint32_t r;
     uint32_t v;
     asm("prmt.b32 %0, %1, 0, %2;" : "=r"(v) : "r"(w), "r"(0x4440u | (uint32_t)j));   // byte j of w
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(v * (4u * kFragLutCols) + lut_lane));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(v * (4u * COLS) + lut_lane));
     return r;
 }
 // BYTES (4, 8, 16 or 32) of a staged code row into words
@@ -553,6 +553,9 @@ __device__ __forceinline__ void gen_cp_async_commit() { asm volatile("cp.async.c
 template <int N>
 __device__ __forceinline__ void gen_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+#ifndef TQ_FRAG_COLS
+#define TQ_FRAG_COLS(PD) ((PD) == 256 ? 32 : 16)
+#endif
 template <int PD>
 struct FragShape {
     static constexpr int kKBytes = PD / 8, kVBytes = PD / 16;   // code bytes per lane and token, K and V
@@ -561,6 +564,7 @@ struct FragShape {
     static constexpr int kChunks = 2 * 16 * kRow / 16;          // 16-byte copies per page and head (K and V): 96 / 160 / 288
     static constexpr int kStageBytes = 2 * 16 * kRow;
     static constexpr int kStages = PD == 256 ? 2 : 3;
+    static constexpr int kLutCols = TQ_FRAG_COLS(PD);   // copies of the lookup table side by side
     static constexpr size_t kRing = (size_t)kGenWarps * kStages * kStageBytes;
     static constexpr size_t kCombine = (size_t)kGenWarps * kGenMaxGroup * PD * 4;   // also covers the rotated queries
     static constexpr size_t kSmem = kRing > kCombine ? kRing : kCombine;
@@ -573,7 +577,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
     extern __shared__ __align__(16) uint8_t tsm[];
     __shared__ float m_s[kGenWarps][kGenMaxGroup], l_s[kGenWarps][kGenMaxGroup];
     __shared__ float cent_s[16];
-    __shared__ __align__(16) uint32_t lut_s[256 * kFragLutCols];
+    __shared__ __align__(16) uint32_t lut_s[256 * F::kLutCols];
     constexpr int pd = PD;
     const int G = p.group;
     float* q_s = reinterpret_cast<float*>(tsm);   // [G][pd] rotated queries, before the loop
@@ -610,9 +614,9 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
     __syncthreads();
     for (int v = tid; v < 256; v += blockDim.x) {   // a row of copies per byte value
         const uint32_t e = gen_pack_half2(cent_s[v & 15], cent_s[v >> 4]);
-        uint4* row = reinterpret_cast<uint4*>(lut_s + v * kFragLutCols);
+        uint4* row = reinterpret_cast<uint4*>(lut_s + v * F::kLutCols);
 #pragma unroll
-        for (int i = 0; i < kFragLutCols / 4; i++) row[i] = make_uint4(e, e, e, e);
+        for (int i = 0; i < F::kLutCols / 4; i++) row[i] = make_uint4(e, e, e, e);
     }
     for (int hh = 1; hh < pd; hh <<= 1) {
         for (int i = tid; i < G * pd / 2; i += blockDim.x) {
@@ -643,7 +647,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
 #pragma unroll
         for (int j = 0; j < 4; j++) o_acc[i][j] = 0.0f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
-    const uint32_t lut_lane = gen_smem_u32(lut_s) + 4u * (lane & (kFragLutCols - 1));
+    const uint32_t lut_lane = gen_smem_u32(lut_s) + 4u * (lane & (F::kLutCols - 1));
     const uint32_t ring = gen_smem_u32(tsm) + (uint32_t)warp * F::kStages * F::kStageBytes;
     const size_t tok_stride = (size_t)p.num_kv_heads * p.g.slot_bytes;
     const int my_pages = pg1 > pg0 + warp ? (pg1 - pg0 - warp + kGenWarps - 1) / kGenWarps : 0;
@@ -700,8 +704,8 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
             for (int s = 0; s < PD / 16; s++) {
                 const uint32_t wa = ka[s >> 1], wb = kb[s >> 1];
                 const int j = 2 * (s & 1);
-                const uint32_t a0 = gen_lookup(wa, j, lut_lane), a2 = gen_lookup(wa, j + 1, lut_lane);
-                const uint32_t a1 = gen_lookup(wb, j, lut_lane), a3 = gen_lookup(wb, j + 1, lut_lane);
+                const uint32_t a0 = gen_lookup<F::kLutCols>(wa, j, lut_lane), a2 = gen_lookup<F::kLutCols>(wa, j + 1, lut_lane);
+                const uint32_t a1 = gen_lookup<F::kLutCols>(wb, j, lut_lane), a3 = gen_lookup<F::kLutCols>(wb, j + 1, lut_lane);
                 gen_mma16816((s & 1) ? s_acc2 : s_acc, a0, a1, a2, a3, qf[2 * s], qf[2 * s + 1]);
             }
 #pragma unroll
@@ -761,8 +765,8 @@ __global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 :
                 const uint32_t hi23 = ((v2[w] >> 4) & 0x0F0F0F0Fu) | (v3[w] & 0xF0F0F0F0u);
 #pragma unroll
                 for (int j = 0; j < 4; j++)   // rows: g <- odd dim, g + 8 <- even dim of this lane's code byte 4w + j
-                    gen_mma16816(o_acc[4 * w + j], gen_lookup(lo01, j, lut_lane), gen_lookup(hi01, j, lut_lane),
-                                 gen_lookup(lo23, j, lut_lane), gen_lookup(hi23, j, lut_lane), pb0, pb1);
+                    gen_mma16816(o_acc[4 * w + j], gen_lookup<F::kLutCols>(lo01, j, lut_lane), gen_lookup<F::kLutCols>(hi01, j, lut_lane),
+                                 gen_lookup<F::kLutCols>(lo23, j, lut_lane), gen_lookup<F::kLutCols>(hi23, j, lut_lane), pb0, pb1);
             }
         }
         __syncwarp();   // every lane has read the stage before the next iteration copies into it
