@@ -497,7 +497,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 4) decode_generic_kernel(const
 //   2tg + 8, 2tg + 9 and zips the nibbles of a token pair into bytes before the lookup (low nibbles
 //   = odd dims -> accumulator row g, high nibbles = even dims -> row g + 8).
 // The table entry of byte v is {low half: centroid of the low nibble, high half: of the high nibble},
-// sixteen copies side by side (a lane reads column lane % 16).  Online softmax in base 2 per page; the
+// one copy per lane side by side (32 KB).  Online softmax in base 2 per page; the
 // K norm is folded into the scores, the V norm into P (moved into place with movmatrix).  Same grid,
 // workspace and merge as the plain kernel above, which stays as the fallback for caches that are not
 // 16-byte aligned.
@@ -553,9 +553,6 @@ __device__ __forceinline__ void gen_cp_async_commit() { asm volatile("cp.async.c
 template <int N>
 __device__ __forceinline__ void gen_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-#ifndef TQ_FRAG_COLS
-#define TQ_FRAG_COLS(PD) ((PD) == 256 ? 32 : 16)
-#endif
 template <int PD>
 struct FragShape {
     static constexpr int kKBytes = PD / 8, kVBytes = PD / 16;   // code bytes per lane and token, K and V
@@ -564,7 +561,7 @@ struct FragShape {
     static constexpr int kChunks = 2 * 16 * kRow / 16;          // 16-byte copies per page and head (K and V): 96 / 160 / 288
     static constexpr int kStageBytes = 2 * 16 * kRow;
     static constexpr int kStages = PD == 256 ? 2 : 3;
-    static constexpr int kLutCols = TQ_FRAG_COLS(PD);   // copies of the lookup table side by side
+    static constexpr int kLutCols = 32;   // copies of the lookup table side by side: one per lane, no two lanes of a lookup share a bank
     static constexpr size_t kRing = (size_t)kGenWarps * kStages * kStageBytes;
     static constexpr size_t kCombine = (size_t)kGenWarps * kGenMaxGroup * PD * 4;   // also covers the rotated queries
     static constexpr size_t kSmem = kRing > kCombine ? kRing : kCombine;
@@ -572,7 +569,7 @@ struct FragShape {
 };
 
 template <int PD>
-__global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 6 : PD == 128 ? 4 : 3) decode_frags_kernel(const __grid_constant__ GenDecodeParams p) {
+__global__ void __launch_bounds__(kGenWarps * 32, PD == 64 ? 4 : PD == 128 ? 4 : 3) decode_frags_kernel(const __grid_constant__ GenDecodeParams p) {
     using F = FragShape<PD>;
     extern __shared__ __align__(16) uint8_t tsm[];
     __shared__ float m_s[kGenWarps][kGenMaxGroup], l_s[kGenWarps][kGenMaxGroup];
@@ -1137,9 +1134,10 @@ int generic_write(void* kv_cache, int64_t num_blocks, int block_size, int num_kv
     return TQ_OK;
 }
 
-// blocks per SM the decode grid is sized to: one wave of resident blocks for head size 64 (six fit; more blocks
-// cost more prologues than they balance: 93 us against 83), two waves for 256 (three fit; 221 us against 229)
-static int generic_blocks_per_sm(int padded) { return padded == 64 ? 6 : padded == 128 ? 4 : 6; }
+// blocks per SM the decode grid is sized to: one wave of resident blocks for head sizes up to 128 (four fit beside
+// their 32 KB tables; more, smaller blocks cost more prologues than they balance), two waves for 256 (three fit;
+// 221 us against 229 for batch 8 x 32768)
+static int generic_blocks_per_sm(int padded) { return padded == 64 ? 4 : padded == 128 ? 4 : 6; }
 
 static int generic_splits(int batch, int num_kv_heads, int num_ctas, int padded) {
     int ctas = num_ctas;
