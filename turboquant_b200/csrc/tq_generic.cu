@@ -114,7 +114,7 @@ struct GenRows8 {
     static constexpr int kRowStride = kQb + 16;   // rows of a pass in different banks
 };
 
-template <typename T, int E>
+template <typename T, int E, bool WALK>
 __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __grid_constant__ GenWriteParams p) {
     using G = GenRows8<E>;
     __shared__ float bnd_s[16];
@@ -135,7 +135,8 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
 
     // a group of eight lanes takes one token and `walk` of its 2 H rows (K heads, then V heads): the slot lookup and
     // the index arithmetic are done once per token
-    const int parts = 2 * H / p.walk;
+    const int walk = WALK ? p.walk : 1;   // WALK = false: p.walk is 1 and the row loop below is straight code
+    const int parts = 2 * H / walk;
     const int64_t items = p.num_tokens * parts;
     for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < items; base += (int64_t)gridDim.x * kGenWarps * 4) {
         // a group past the end works on the last item again and stores nothing: the shuffles below take every lane
@@ -146,10 +147,10 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
         if (it < 0x7fffffff) {
             const uint32_t t32 = (uint32_t)it / (uint32_t)parts;
             t = t32;
-            r0 = (int)((uint32_t)it - t32 * (uint32_t)parts) * p.walk;
+            r0 = (int)((uint32_t)it - t32 * (uint32_t)parts) * walk;
         } else {
             t = it / parts;
-            r0 = (int)(it - t * parts) * p.walk;
+            r0 = (int)(it - t * parts) * walk;
         }
         int64_t slot = p.slot_is_i64 ? reinterpret_cast<const int64_t*>(p.slot_mapping)[t]
                                      : (int64_t) reinterpret_cast<const int32_t*>(p.slot_mapping)[t];
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
         }
         const bool store = live && slot >= 0;
         if (!__any_sync(0xffffffffu, store)) continue;   // four skipped tokens
-        for (int rr = r0; rr < r0 + p.walk; rr++) {
+        for (int rr = r0; rr < r0 + walk; rr++) {
         const int which = rr >= H ? 1 : 0, h = rr - which * H;
         const T* row = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * hd;
         float x[E];
@@ -272,9 +273,12 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
 template <typename T>
 static void launch_write_rows8(const GenWriteParams& p, unsigned grid, cudaStream_t s) {
     switch (p.g.padded) {
-        case 64: write_rows8_kernel<T, 8><<<grid, kGenWarps * 32, 0, s>>>(p); break;
-        case 128: write_rows8_kernel<T, 16><<<grid, kGenWarps * 32, 0, s>>>(p); break;
-        default: write_rows8_kernel<T, 32><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        case 64:
+            if (p.walk > 1) write_rows8_kernel<T, 8, true><<<grid, kGenWarps * 32, 0, s>>>(p);
+            else write_rows8_kernel<T, 8, false><<<grid, kGenWarps * 32, 0, s>>>(p);
+            break;
+        case 128: write_rows8_kernel<T, 16, false><<<grid, kGenWarps * 32, 0, s>>>(p); break;
+        default: write_rows8_kernel<T, 32, false><<<grid, kGenWarps * 32, 0, s>>>(p); break;
     }
 }
 
