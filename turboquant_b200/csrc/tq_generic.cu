@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
     __syncthreads();
     const float* sg = sg_s + q;
 
-    // a group of eight lanes takes one token and `walk` of its 2 H rows (K heads, then V heads): the slot lookup and
+    // a group of eight lanes takes one token and `walk` of its 2 H rows (K and V of head 0, of head 1, ...; the two
+    // tensors alternating measured 3 % faster at head 256 than all K rows first): the slot lookup and
     // the index arithmetic are done once per token
     const int walk = WALK ? p.walk : 1;   // WALK = false: p.walk is 1 and the row loop below is straight code
     const int parts = 2 * H / walk;
@@ -161,7 +162,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) write_rows8_kernel(const __
         const bool store = live && slot >= 0;
         if (!__any_sync(0xffffffffu, store)) continue;   // four skipped tokens
         for (int rr = r0; rr < r0 + walk; rr++) {
-        const int which = rr >= H ? 1 : 0, h = rr - which * H;
+        const int which = rr & 1, h = rr >> 1;   // K and V rows of a head alternate
         const T* row = reinterpret_cast<const T*>(p.src[which]) + t * p.token_stride[which] + (int64_t)h * hd;
         float x[E];
 #pragma unroll
@@ -944,7 +945,7 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
         norm = __half2float(*reinterpret_cast<const __half*>(slot + kQb));
     };
 
-    // a group of eight lanes takes one token and walks `walk` of its 2 H rows (K heads, then V heads): the token's
+    // a group of eight lanes takes one token and walks `walk` of its 2 H rows (K and V of head 0, of head 1, ...): the token's
     // page lookup and output row are worked out once, and the next row's codes are fetched while this one is worked on
     for (int64_t base = ((int64_t)blockIdx.x * kGenWarps + warp) * 4; base < items; base += (int64_t)gridDim.x * kGenWarps * 4) {
         // a group without a token (past the end, past its sequence, an unlisted page) runs the shuffles on zeros
@@ -986,15 +987,15 @@ __global__ void __launch_bounds__(kGenWarps * 32, 8) dequant_rows8_kernel(const 
 #pragma unroll
         for (int c = 0; c < kChunks; c++) cw_next[c] = 0;
         float norm_next = 0.0f;
-        if (live) fetch(slot0 + (r0 >= H ? (size_t)p.slab_bytes : 0) + (size_t)(r0 >= H ? r0 - H : r0) * p.g.slot_bytes, cw_next, norm_next);
+        if (live) fetch(slot0 + ((r0 & 1) ? (size_t)p.slab_bytes : 0) + (size_t)(r0 >> 1) * p.g.slot_bytes, cw_next, norm_next);
         for (int r = r0; r < r0 + p.walk; r++) {
-        const int which = r >= H ? 1 : 0, h = r - which * H;
+        const int which = r & 1, h = r >> 1;   // K and V rows of a head alternate
         uint32_t cw[kChunks];
 #pragma unroll
         for (int c = 0; c < kChunks; c++) cw[c] = cw_next[c];
         const float norm = norm_next;
         if (live && r + 1 < r0 + p.walk) {
-            const int wn = r + 1 >= H ? 1 : 0, hn = r + 1 - wn * H;
+            const int wn = (r + 1) & 1, hn = (r + 1) >> 1;
             fetch(slot0 + (size_t)wn * p.slab_bytes + (size_t)hn * p.g.slot_bytes, cw_next, norm_next);
         }
         float x[E];
