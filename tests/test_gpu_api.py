@@ -118,12 +118,15 @@ def test_decoder_dispatch_returns_the_single_kernel():
     assert name == KERNEL_NAME and callable(op)
 
 
-def test_cuda_graph_capture_of_write_and_decode(oracle, golden):
+@pytest.mark.parametrize("d,hq,hkv", [(128, 32, 8), (64, 16, 8), (256, 8, 4)])
+def test_cuda_graph_capture_of_write_and_decode(oracle, golden, d, hq, hkv):
     """The step a serving engine replays: cache write + decode captured once, replayed on new data."""
     from turboquant_b200 import TurboQuantPagedAttention
-    case = synthetic.decode_case(seed=81, seq_lens=[400, 90], dtype=torch.bfloat16)
-    attn = TurboQuantPagedAttention(32, 128, SCALE, 8)
-    cache = torch.zeros((2, case.num_blocks, 16, 8, 80), dtype=torch.uint8, device=DEV)
+    from turboquant_b200.paged_attention import kv_cache_shape
+    SCALE = 1.0 / math.sqrt(d)
+    case = synthetic.decode_case(seed=81, seq_lens=[400, 90], dtype=torch.bfloat16, heads=(hq, hkv), head_dim=d)
+    attn = TurboQuantPagedAttention(hq, d, SCALE, hkv)
+    cache = torch.zeros(kv_cache_shape(case.num_blocks, 16, hkv, d), dtype=torch.uint8, device=DEV)
     k, v, slots = case.k.to(DEV), case.v.to(DEV), case.slot_mapping.to(DEV)
     q, bt, sl = case.q.to(DEV), case.block_table.to(DEV), case.seq_lens.to(DEV)
     out = torch.empty_like(q)
@@ -145,8 +148,8 @@ def test_cuda_graph_capture_of_write_and_decode(oracle, golden):
     graph.replay()
     torch.cuda.synchronize()
     want = oracle.decode_paged(q.float().cpu().numpy(), cache.cpu().numpy(), case.block_table.numpy(),
-                               case.seq_lens.numpy(), golden["signs_seed42_d128"], SCALE)
-    assert_attention_close(out.float().cpu().numpy(), want, "graph replay")
+                               case.seq_lens.numpy(), golden[f"signs_seed42_d{d}"], SCALE)
+    assert_attention_close(out.float().cpu().numpy(), want, f"graph replay, head size {d}")
     assert attn.status(2, q.device) == 0
 
 
