@@ -146,7 +146,8 @@ def dist_env():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     # stdout carries the one JSON line: a library banner (NCCL prints its version there at that debug level) goes
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+    # (the level may also come from NCCL's configuration file: the environment variable, when set, wins over it)
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
         os.environ["NCCL_DEBUG"] = "WARN"
     return rank, world, local
 
