@@ -40,6 +40,12 @@ import argparse
 import json
 import math
 import os
+
+# stdout carries the one JSON line: NCCL prints its version banner (debug levels VERSION and WARN) and its other
+# messages to stdout unless told where to write them, and it honours the file only above level VERSION
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 import statistics
 import subprocess
 import sys
@@ -145,10 +151,6 @@ def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    # stdout carries the one JSON line: a library banner (NCCL prints its version there at that debug level) goes
-    # (the level may also come from NCCL's configuration file: the environment variable, when set, wins over it)
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
     return rank, world, local
 
 
